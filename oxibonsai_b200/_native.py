@@ -130,6 +130,7 @@ def _declare_host(lib: C.CDLL) -> None:
         "bcpu_rope": (None, [vp, C.c_uint64, C.c_uint32, C.c_float]),
         "bcpu_swiglu": (None, [vp, vp, vp, C.c_uint64]),
         "bcpu_argmax_last": (C.c_int, [vp, C.c_uint64]),
+        "bcpu_rope_table": (None, [C.c_uint32, C.c_uint32, C.c_float, vp, vp]),
         "boracle_new": (vp, [vp, C.c_uint32]),
         "boracle_free": (None, [vp]),
         "boracle_forward": (C.c_int, [vp, C.c_uint32, C.c_uint32, vp]),

@@ -82,3 +82,11 @@ def write_synthetic_gguf(path: str, cfg: Qwen3Config, weight_type: int = TQ2_0_G
     check(_native.host().bonsai_write_synthetic(str(path).encode(), cfg.packed_u32(), cfg.packed_f32(), cfg.name.encode(),
                                                 weight_type, int(tied), seed, int(llm_keys)))
     return str(path)
+
+
+def rope_table(head_dim: int, max_pos: int, base: float) -> tuple[np.ndarray, np.ndarray]:
+    """cos / sin tables [max_pos, head_dim // 2] in f32, bit-identical to the oracle's per-token values."""
+    cos = np.empty((max_pos, head_dim // 2), dtype=np.float32)
+    sin = np.empty_like(cos)
+    _native.host().bcpu_rope_table(head_dim, max_pos, base, cos.ctypes.data, sin.ctypes.data)
+    return cos, sin

@@ -1,6 +1,7 @@
 // C ABI of the host library (GGUF container, block codecs, CPU oracle, synthetic checkpoints).
 // Every function returns 0 / a valid handle on success and a negative code / null on failure;
 // the message of the last failure on the calling thread is available from bonsai_last_error().
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -257,6 +258,18 @@ void bcpu_rmsnorm(const float* x, const float* w, float* out, uint64_t n, float 
 void bcpu_rope(float* x, uint64_t head_dim, uint32_t pos, float base) { cpu_rope_halfsplit(x, head_dim, pos, base); }
 void bcpu_swiglu(const float* g, const float* u, float* out, uint64_t n) { cpu_swiglu(g, u, out, n); }
 int bcpu_argmax_last(const float* x, uint64_t n) { return cpu_argmax_last(x, n); }
+// cos/sin tables [max_pos][head_dim/2] computed exactly as the oracle does per token:
+// freq = 1 / powf(base, 2i/head_dim), angle = (float)pos * freq, cosf / sinf.
+void bcpu_rope_table(uint32_t head_dim, uint32_t max_pos, float base, float* cos_out, float* sin_out) {
+  uint32_t half = head_dim / 2;
+  for (uint32_t p = 0; p < max_pos; ++p)
+    for (uint32_t i = 0; i < half; ++i) {
+      float freq = 1.0f / std::pow(base, 2.0f * (float)i / (float)head_dim);
+      float ang = (float)p * freq;
+      cos_out[(size_t)p * half + i] = std::cos(ang);
+      sin_out[(size_t)p * half + i] = std::sin(ang);
+    }
+}
 
 // ---- oracle ---------------------------------------------------------------------------------
 void* boracle_new(void* gguf, uint32_t max_seq) {

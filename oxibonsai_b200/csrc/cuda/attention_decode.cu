@@ -1,0 +1,312 @@
+// Decode-side attention: fused per-head QK RMSNorm + half-split RoPE + paged KV append, and
+// split-KV (flash-decode) GQA attention over paged F32 / F16 / Q8 / Q4 caches.
+//
+// Replaces the reference's seven attention launches per layer - fused_qk_norm, fused_qk_rope,
+// fused_qk_norm_rope, fused_kv_store, batched_attn_scores_v2, batched_softmax and
+// batched_attn_weighted_sum (crates/oxibonsai-kernels/src/gpu_backend/cuda_attn_kernels.rs:63-439) -
+// with two kernels plus a small merge.  Unlike the reference, whose score grid is sized for the
+// maximum sequence length, work is proportional to the live context, pages are looked up through
+// a block table (crates/oxibonsai-model/src/paged_kv_cache.rs:33-240), the KV heads of a GQA
+// group share every K/V load, and the cache can be stored as INT8 with one f32 scale per
+// (token, head) row (scale = absmax/127, crates/oxibonsai-model/src/kv_cache_quant.rs:46-71) or as
+// INT4 (scale = absmax/7, nibble = q + 8), a format the reference names in its policy levels but
+// never stores.
+//
+// Pool layout, per layer and separately for K and V:  data [page][kv_head][slot][row bytes],
+// scales f32 [page][kv_head][slot] (quantised formats only).  Position and block tables live in
+// device memory so a captured CUDA graph stays valid as sequences grow.
+#include "common.cuh"
+
+namespace bonsai {
+
+enum { KV_F32 = 0, KV_F16 = 1, KV_Q8 = 2, KV_Q4 = 3 };
+
+__host__ __device__ inline int kv_row_bytes(int kvt, int hd) {
+  return kvt == KV_F32 ? hd * 4 : (kvt == KV_F16 ? hd * 2 : (kvt == KV_Q8 ? hd : hd / 2));
+}
+
+struct KvPool {
+  uint8_t* k;       // this layer's K pool
+  uint8_t* v;       // this layer's V pool
+  float* k_scale;   // may be null for F32 / F16
+  float* v_scale;
+  int page_size;
+  int kv_heads;
+  int hd;
+  int kvt;
+};
+
+// One block per (head, sequence); blockDim.x == head_dim.  Heads [0, nq) are queries, [nq, nq+nkv)
+// keys, [nq+nkv, nq+2nkv) values.
+__global__ void qknorm_rope_kvstore_kernel(const float* __restrict__ qkv, int qkv_stride, const float* __restrict__ q_norm,
+                                           const float* __restrict__ k_norm, float eps, const float* __restrict__ rope_cos,
+                                           const float* __restrict__ rope_sin, const int* __restrict__ positions,
+                                           const int* __restrict__ block_table, int max_pages, float* __restrict__ q_out,
+                                           int nq, KvPool pool) {
+  extern __shared__ float sh[];  // hd floats + 32
+  const int hd = pool.hd, nkv = pool.kv_heads;
+  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int pos = positions[b];
+  const float* src = qkv + (size_t)b * qkv_stride + (size_t)head * hd;
+  float x = src[d];
+  const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+  float y = x;
+  if (is_q || is_k) {
+    float ss = block_sum(x * x, sh + hd);
+    float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+    float w = is_q ? q_norm[d] : k_norm[d];
+    float n = w * x * inv;
+    sh[d] = n;
+    __syncthreads();
+    int half = hd >> 1;
+    int i = d < half ? d : d - half;
+    float c = rope_cos[(size_t)pos * half + i], s = rope_sin[(size_t)pos * half + i];
+    float x0 = sh[i], x1 = sh[half + i];
+    y = d < half ? x0 * c - x1 * s : x0 * s + x1 * c;
+  }
+  if (is_q) {
+    q_out[((size_t)b * nq + head) * hd + d] = y;
+    return;
+  }
+  const int kvh = is_k ? head - nq : head - nq - nkv;
+  const int page = block_table[(size_t)b * max_pages + pos / pool.page_size];
+  const int slot = pos % pool.page_size;
+  const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + slot;
+  uint8_t* base = is_k ? pool.k : pool.v;
+  float* sc = is_k ? pool.k_scale : pool.v_scale;
+  if (pool.kvt == KV_F32) {
+    reinterpret_cast<float*>(base)[row * hd + d] = y;
+  } else if (pool.kvt == KV_F16) {
+    reinterpret_cast<__half*>(base)[row * hd + d] = __float2half_rn(y);
+  } else {
+    // quantised rows: absmax over the head, then round to nearest
+    __syncthreads();
+    float m = warp_max(fabsf(y));
+    if ((d & 31) == 0) sh[hd + (d >> 5)] = m;
+    __syncthreads();
+    float amax = 0.0f;
+    for (int w = 0; w < (hd + 31) / 32; ++w) amax = fmaxf(amax, sh[hd + w]);
+    float qmax = pool.kvt == KV_Q8 ? 127.0f : 7.0f;
+    float scale = fmaxf(amax / qmax, 1e-12f);
+    int q = __float2int_rn(y / scale);
+    q = max(-(int)qmax, min((int)qmax, q));
+    if (d == 0) sc[row] = scale;
+    if (pool.kvt == KV_Q8) {
+      reinterpret_cast<int8_t*>(base)[row * hd + d] = (int8_t)q;
+    } else {
+      int other = __shfl_xor_sync(0xffffffffu, q, 1);
+      if ((d & 1) == 0) base[row * (hd / 2) + (d >> 1)] = (uint8_t)((q + 8) | ((other + 8) << 4));
+    }
+  }
+}
+
+template <int KVT, int DPL>
+__device__ __forceinline__ void load_row(const uint8_t* base, const float* scales, size_t row, int hd, int lane, float* out) {
+  if (KVT == KV_F32) {
+    const float* p = reinterpret_cast<const float*>(base) + row * hd + lane * DPL;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) out[j] = p[j];
+  } else if (KVT == KV_F16) {
+    const __half2* p = reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(base) + row * hd + lane * DPL);
+#pragma unroll
+    for (int j = 0; j < DPL / 2; ++j) {
+      float2 f = __half22float2(p[j]);
+      out[2 * j] = f.x;
+      out[2 * j + 1] = f.y;
+    }
+  } else if (KVT == KV_Q8) {
+    const int8_t* p = reinterpret_cast<const int8_t*>(base) + row * hd + lane * DPL;
+    float s = scales[row];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) out[j] = s * (float)p[j];
+  } else {
+    const uint8_t* p = base + row * (hd / 2) + lane * (DPL / 2);
+    float s = scales[row];
+#pragma unroll
+    for (int j = 0; j < DPL / 2; ++j) {
+      uint32_t v = p[j];
+      out[2 * j] = s * (float)((int)(v & 15u) - 8);
+      out[2 * j + 1] = s * (float)((int)(v >> 4) - 8);
+    }
+  }
+}
+
+// grid (kv_heads, splits, batch), block 128 (4 warps).  Writes per-split partials.
+template <int KVT, int DPL, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, const int* __restrict__ positions,
+                                                         const int* __restrict__ block_table, int max_pages, KvPool pool,
+                                                         int nq, float sm_scale, float* __restrict__ ws_acc,
+                                                         float* __restrict__ ws_ml, int extra_len) {
+  extern __shared__ float sh[];  // [4 warps][G][hd + 2]
+  const int hd = pool.hd, nkv = pool.kv_heads;
+  const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int len = positions[b] + 1 + extra_len;
+  const int chunk = (len + nsplit - 1) / nsplit;
+  const int t0 = split * chunk, t1 = min(len, t0 + chunk);
+
+  float qr[G][DPL], acc[G][DPL], m[G], l[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float* qp = q + ((size_t)b * nq + kvh * G + g) * hd + lane * DPL;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      qr[g][j] = qp[j] * sm_scale;
+      acc[g][j] = 0.0f;
+    }
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+  }
+  const int* bt = block_table + (size_t)b * max_pages;
+  for (int t = t0 + warp; t < t1; t += 4) {
+    int page = bt[t / pool.page_size];
+    size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (t % pool.page_size);
+    float kr[DPL], vr[DPL];
+    load_row<KVT, DPL>(pool.k, pool.k_scale, row, hd, lane, kr);
+    load_row<KVT, DPL>(pool.v, pool.v_scale, row, hd, lane, vr);
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float a = 0.0f;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) a = fmaf(qr[g][j], kr[j], a);
+      s[g] = a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mn = fmaxf(m[g], s[g]);
+      float r = __expf(m[g] - mn);  // exp(-inf) = 0 on the first token
+      float p = __expf(s[g] - mn);
+      l[g] = l[g] * r + p;
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) acc[g][j] = fmaf(acc[g][j], r, p * vr[j]);
+      m[g] = mn;
+    }
+  }
+  // combine the four warps
+  const int stride = hd + 2;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float* dst = sh + ((size_t)warp * G + g) * stride;
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) dst[lane * DPL + j] = acc[g][j];
+    if (lane == 0) {
+      dst[hd] = m[g];
+      dst[hd + 1] = l[g];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    int g = idx / hd, d = idx - g * hd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
+    float a = 0.0f, L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = sh + ((size_t)w * G + g) * stride;
+      float f = (src[hd] == -INFINITY) ? 0.0f : __expf(src[hd] - M);
+      a += f * src[d];
+      L += f * src[hd + 1];
+    }
+    size_t o = (((size_t)b * nq + kvh * G + g) * nsplit + split);
+    ws_acc[o * hd + d] = a;
+    if (d == 0) {
+      ws_ml[o * 2] = M;
+      ws_ml[o * 2 + 1] = L;
+    }
+  }
+}
+
+// grid (heads, batch), block hd
+__global__ void attn_merge_kernel(const float* __restrict__ ws_acc, const float* __restrict__ ws_ml, int nsplit, int hd,
+                                  float* __restrict__ out) {
+  const size_t hb = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ws_ml[(hb * nsplit + s) * 2]);
+  float a = 0.0f, L = 0.0f;
+  for (int s = 0; s < nsplit; ++s) {
+    float ms = ws_ml[(hb * nsplit + s) * 2];
+    float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+    a += f * ws_acc[(hb * nsplit + s) * hd + d];
+    L += f * ws_ml[(hb * nsplit + s) * 2 + 1];
+  }
+  out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
+}
+
+template <int KVT, int DPL>
+int launch_decode_g(int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt, int max_pages,
+                    KvPool pool, int nq, float sc, float* wa, float* wm, int extra) {
+  switch (G) {
+    case 1: attn_decode_kernel<KVT, DPL, 1><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
+    case 2: attn_decode_kernel<KVT, DPL, 2><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
+    case 4: attn_decode_kernel<KVT, DPL, 4><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
+    case 8: attn_decode_kernel<KVT, DPL, 8><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+  return launch_status();
+}
+
+template <int KVT>
+int launch_decode_d(int dpl, int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt,
+                    int max_pages, KvPool pool, int nq, float sc, float* wa, float* wm, int extra) {
+  switch (dpl) {
+    case 2: return launch_decode_g<KVT, 2>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
+    case 4: return launch_decode_g<KVT, 4>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
+    case 8: return launch_decode_g<KVT, 8>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+}
+
+}  // namespace bonsai
+
+extern "C" {
+
+// qkv: f32 [batch][qkv_stride] holding q | k | v heads.  Writes normalised+rotated q to q_out
+// [batch][nq][hd] and appends k, v at positions[b] through block_table [batch][max_pages].
+int bonsai_qknorm_rope_kvstore(const float* qkv, int qkv_stride, const float* q_norm, const float* k_norm, float eps,
+                               const float* rope_cos, const float* rope_sin, const int* positions, const int* block_table,
+                               int max_pages, float* q_out, int batch, int nq, int nkv, int hd, int kvt, int page_size,
+                               void* kpool, void* vpool, float* kscale, float* vscale, cudaStream_t stream) {
+  using namespace bonsai;
+  if (hd % 32 != 0 || hd < 64 || hd > 256 || kvt < 0 || kvt > 3 || batch <= 0) return BONSAI_CUDA_BAD_ARG;
+  KvPool pool{(uint8_t*)kpool, (uint8_t*)vpool, kscale, vscale, page_size, nkv, hd, kvt};
+  dim3 grid(nq + 2 * nkv, batch);
+  qknorm_rope_kvstore_kernel<<<grid, hd, (hd + 32) * sizeof(float), stream>>>(qkv, qkv_stride, q_norm, k_norm, eps, rope_cos, rope_sin,
+                                                                              positions, block_table, max_pages, q_out, nq, pool);
+  return launch_status();
+}
+
+// q: f32 [batch][nq][hd] -> out f32 [batch][nq][hd].  Context length of sequence b is
+// positions[b] + 1 + extra_len.  ws_acc needs batch*nq*nsplit*hd floats, ws_ml batch*nq*nsplit*2.
+int bonsai_attn_decode(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
+                       int hd, int kvt, int page_size, const void* kpool, const void* vpool, const float* kscale,
+                       const float* vscale, int nsplit, float* ws_acc, float* ws_ml, float* out, int extra_len,
+                       cudaStream_t stream) {
+  using namespace bonsai;
+  if (hd % 32 != 0 || hd < 64 || hd > 256 || nq % nkv != 0 || nsplit < 1 || batch <= 0) return BONSAI_CUDA_BAD_ARG;
+  int G = nq / nkv, dpl = hd / 32;
+  KvPool pool{(uint8_t*)kpool, (uint8_t*)vpool, (float*)kscale, (float*)vscale, page_size, nkv, hd, kvt};
+  dim3 grid(nkv, nsplit, batch);
+  size_t smem = (size_t)4 * G * (hd + 2) * sizeof(float);
+  float sc = 1.0f / sqrtf((float)hd);
+  int rc;
+  switch (kvt) {
+    case KV_F32: rc = launch_decode_d<KV_F32>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
+    case KV_F16: rc = launch_decode_d<KV_F16>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
+    case KV_Q8: rc = launch_decode_d<KV_Q8>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
+    case KV_Q4: rc = launch_decode_d<KV_Q4>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+  if (rc != BONSAI_CUDA_OK) return rc;
+  attn_merge_kernel<<<dim3(nq, batch), hd, 0, stream>>>(ws_acc, ws_ml, nsplit, hd, out);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+// Batch-1 decode GEMV on CUDA cores, exact in f32: out = W x for a planar-SM packed matrix, with
+// optional fused RMSNorm prologue and residual / SwiGLU epilogues, plus the f16 LM-head GEMV.
+//
+// This is the numerically exact path (f32 activations, f32 accumulation) used for the greedy
+// token-stream gate and as the fallback of the tensor-core decode path.  It replaces the
+// reference's per-format decode kernels gemv_tq2_g128_v1, gemv_q1_g128_v7/_v8/_v9(+_residual),
+// fused_gate_up_swiglu_q1, rmsnorm_weighted_v2, residual_add and swiglu_fused
+// (crates/oxibonsai-kernels/src/gpu_backend/cuda_kernels.rs:76-776), folding the norm, the
+// residual add and the activation into the GEMV launch.
+//
+// Work split: a thread owns one 64-input chunk of x in registers for the whole launch and
+// streams that chunk of R rows at a time with 16-byte loads (R independent loads in flight);
+// the chunk partial sums of a row are reduced through shared memory in a fixed order, so the
+// result does not depend on the grid size.
+#include "common.cuh"
+
+namespace bonsai {
+
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+
+template <int R>
+__global__ void __launch_bounds__(256) bitgemv_kernel(const uint4* __restrict__ codes, const __half* __restrict__ scales,
+                                                     const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
+                                                     float* __restrict__ out, const float* __restrict__ residual, int N, int K,
+                                                     int epi) {
+  __shared__ float red[R][256];
+  __shared__ float s32[32];
+  const int t = threadIdx.x;
+  const int cpr = K >> 6;        // 64-input chunks per row
+  const int G = 256 / cpr;       // row groups handled side by side
+  const int g = t / cpr, c = t - g * cpr;
+  const bool active = g < G;
+
+  float xr[64];
+  if (active) {
+    const float4* xp = reinterpret_cast<const float4*>(x + (size_t)c * 64);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float4 v = xp[j];
+      xr[4 * j] = v.x; xr[4 * j + 1] = v.y; xr[4 * j + 2] = v.z; xr[4 * j + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 64; ++j) xr[j] = 0.0f;
+  }
+  if (norm_w != nullptr) {
+    float ss = 0.0f;
+    if (active && g == 0) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) ss += xr[j] * xr[j];
+    }
+    ss = block_sum(ss, s32);
+    float inv = 1.0f / sqrtf(ss / (float)K + eps);
+    if (active) {
+      const float4* wp = reinterpret_cast<const float4*>(norm_w + (size_t)c * 64);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float4 w = wp[j];
+        xr[4 * j] = w.x * xr[4 * j] * inv;
+        xr[4 * j + 1] = w.y * xr[4 * j + 1] * inv;
+        xr[4 * j + 2] = w.z * xr[4 * j + 2] * inv;
+        xr[4 * j + 3] = w.w * xr[4 * j + 3] * inv;
+      }
+    }
+  }
+
+  const int rows_per_tile = G * R;
+  const int ntiles = (N + rows_per_tile - 1) / rows_per_tile;
+  const int nsc = K >> 7;
+  const int lane = t & 31, warp = t >> 5;
+
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int row_base = tile * rows_per_tile + g * R;
+    uint4 q[R];
+    float d[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      int row = row_base + i;
+      if (active && row < N) {
+        q[i] = __ldg(codes + (size_t)row * cpr + c);
+        d[i] = __half2float(scales[(size_t)row * nsc + (c >> 1)]);
+      } else {
+        q[i] = make_uint4(0, 0, 0, 0);
+        d[i] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      float acc = dot_word16(q[i].x, xr) + dot_word16(q[i].y, xr + 16) + dot_word16(q[i].z, xr + 32) + dot_word16(q[i].w, xr + 48);
+      red[i][t] = acc * d[i];
+    }
+    __syncthreads();
+    if (epi == EPI_SWIGLU) {
+      for (int pr = warp; pr < rows_per_tile / 2; pr += 8) {
+        int rr = pr * 2;
+        int gg = rr / R, ii = rr - gg * R;
+        float a = 0.0f, b = 0.0f;
+        for (int j = lane; j < cpr; j += 32) {
+          a += red[ii][gg * cpr + j];
+          b += red[ii + 1][gg * cpr + j];
+        }
+        a = warp_sum(a) * kPow2_63;
+        b = warp_sum(b) * kPow2_63;
+        int row = tile * rows_per_tile + rr;
+        if (lane == 0 && row + 1 < N) out[row >> 1] = a / (1.0f + expf(-a)) * b;
+      }
+    } else {
+      for (int rr = warp; rr < rows_per_tile; rr += 8) {
+        int gg = rr / R, ii = rr - gg * R;
+        float a = 0.0f;
+        for (int j = lane; j < cpr; j += 32) a += red[ii][gg * cpr + j];
+        a = warp_sum(a) * kPow2_63;
+        int row = tile * rows_per_tile + rr;
+        if (lane == 0 && row < N) out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// f16 row-major matrix [N][K] times f32 x, optional fused RMSNorm prologue.  Thread t owns the
+// 8-input chunks t, t+256, ... (CH of them) of x.
+template <int CH, int R>
+__global__ void __launch_bounds__(256) f16gemv_kernel(const uint4* __restrict__ w, const float* __restrict__ x,
+                                                     const float* __restrict__ norm_w, float eps, float* __restrict__ out,
+                                                     int N, int K) {
+  __shared__ float red[R][256];
+  __shared__ float s32[32];
+  const int t = threadIdx.x;
+  const int cpr = K >> 3;
+  float xr[CH][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int h = 0; h < CH; ++h) {
+    int c = t + h * 256;
+    if (c < cpr) {
+      const float4* xp = reinterpret_cast<const float4*>(x + (size_t)c * 8);
+      float4 a = xp[0], b = xp[1];
+      xr[h][0] = a.x; xr[h][1] = a.y; xr[h][2] = a.z; xr[h][3] = a.w;
+      xr[h][4] = b.x; xr[h][5] = b.y; xr[h][6] = b.z; xr[h][7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xr[h][j] = 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += xr[h][j] * xr[h][j];
+  }
+  if (norm_w != nullptr) {
+    ss = block_sum(ss, s32);
+    float inv = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+    for (int h = 0; h < CH; ++h) {
+      int c = t + h * 256;
+      if (c < cpr) {
+        const float4* wp = reinterpret_cast<const float4*>(norm_w + (size_t)c * 8);
+        float4 a = wp[0], b = wp[1];
+        xr[h][0] = a.x * xr[h][0] * inv; xr[h][1] = a.y * xr[h][1] * inv;
+        xr[h][2] = a.z * xr[h][2] * inv; xr[h][3] = a.w * xr[h][3] * inv;
+        xr[h][4] = b.x * xr[h][4] * inv; xr[h][5] = b.y * xr[h][5] * inv;
+        xr[h][6] = b.z * xr[h][6] * inv; xr[h][7] = b.w * xr[h][7] * inv;
+      }
+    }
+  }
+  const int ntiles = (N + R - 1) / R;
+  const int lane = t & 31, warp = t >> 5;
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    uint4 q[R][CH];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      int row = tile * R + i;
+#pragma unroll
+      for (int h = 0; h < CH; ++h) {
+        int c = t + h * 256;
+        q[i][h] = (row < N && c < cpr) ? __ldg(w + (size_t)row * cpr + c) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int h = 0; h < CH; ++h) {
+        const __half2* hp = reinterpret_cast<const __half2*>(&q[i][h]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __half22float2(hp[j]);
+          acc = fmaf(f.x, xr[h][2 * j], acc);
+          acc = fmaf(f.y, xr[h][2 * j + 1], acc);
+        }
+      }
+      red[i][t] = acc;
+    }
+    __syncthreads();
+    for (int rr = warp; rr < R; rr += 8) {
+      float a = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a += red[rr][lane + 32 * j];
+      a = warp_sum(a);
+      int row = tile * R + rr;
+      if (lane == 0 && row < N) out[row] = a;
+    }
+    __syncthreads();
+  }
+}
+
+// h[0..hidden) = f16 embedding row of token *token_ptr (token id read on the device).
+__global__ void embed_f16_kernel(const __half* __restrict__ table, const int* __restrict__ token_ptr, float* __restrict__ h,
+                                 int hidden, int vocab) {
+  int tok = *token_ptr;
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const __half* row = table + (size_t)tok * hidden;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) h[i] = __half2float(row[i]);
+}
+
+}  // namespace bonsai
+
+extern "C" {
+
+// out[N] (or out[N/2] for epi = 2 with gate/up rows interleaved) = W x.  x is f32[K]; when norm_w is
+// non-null x is first RMS-normalised with that weight.  K must be a multiple of 128 and <= 16384.
+int bonsai_bitgemv(const void* codes, const void* scales, const float* x, const float* norm_w, float eps, float* out,
+                   const float* residual, int N, int K, int epi, cudaStream_t stream) {
+  using namespace bonsai;
+  if (K % 128 != 0 || K < 128 || K > 16384 || N <= 0 || epi < 0 || epi > 2) return BONSAI_CUDA_BAD_ARG;
+  if (epi == EPI_RESID && residual == nullptr) return BONSAI_CUDA_BAD_ARG;
+  int cpr = K / 64, G = 256 / cpr;
+  int tiles8 = (N + G * 8 - 1) / (G * 8);
+  if (tiles8 >= 2 * 148) {
+    int grid = tiles8 < 148 * 2 ? tiles8 : 148 * 2;
+    bitgemv_kernel<8><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi);
+  } else {
+    int tiles4 = (N + G * 4 - 1) / (G * 4);
+    int grid = tiles4 < 148 * 3 ? tiles4 : 148 * 3;
+    bitgemv_kernel<4><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi);
+  }
+  return launch_status();
+}
+
+// out[N] = W x for an f16 row-major matrix (LM head); optional fused RMSNorm.  K % 8 == 0, K <= 8192.
+int bonsai_f16gemv(const void* w, const float* x, const float* norm_w, float eps, float* out, int N, int K,
+                   cudaStream_t stream) {
+  using namespace bonsai;
+  if (K % 8 != 0 || K <= 0 || K > 8192 || N <= 0) return BONSAI_CUDA_BAD_ARG;
+  int ch = (K / 8 + 255) / 256;
+  int ntiles = (N + 7) / 8;
+  int grid = ntiles < 148 * 4 ? ntiles : 148 * 4;
+  switch (ch) {
+    case 1: f16gemv_kernel<1, 8><<<grid, 256, 0, stream>>>((const uint4*)w, x, norm_w, eps, out, N, K); break;
+    case 2: f16gemv_kernel<2, 8><<<grid, 256, 0, stream>>>((const uint4*)w, x, norm_w, eps, out, N, K); break;
+    case 3: f16gemv_kernel<3, 8><<<grid, 256, 0, stream>>>((const uint4*)w, x, norm_w, eps, out, N, K); break;
+    default: f16gemv_kernel<4, 8><<<grid, 256, 0, stream>>>((const uint4*)w, x, norm_w, eps, out, N, K); break;
+  }
+  return launch_status();
+}
+
+int bonsai_embed_f16(const void* table, const int* token_ptr, float* h, int hidden, int vocab, cudaStream_t stream) {
+  bonsai::embed_f16_kernel<<<(hidden + 255) / 256, 256, 0, stream>>>((const __half*)table, token_ptr, h, hidden, vocab);
+  return bonsai::launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Shared device helpers and the packed weight layout used by every kernel in this library.
+//
+// Device weight layout ("planar SM"): a quantised matrix of N output rows by K inputs is stored as
+//   codes  : uint32 [N][K/16]  - one word per 16 consecutive inputs k0..k0+15
+//   scales : f16    [N][K/128] - one scale per 128-input group (the GGUF block scale)
+// Inside a word, nibble i (bits 4i..4i+3) = { S(k0+i), S(k0+8+i), M(k0+i), M(k0+8+i) } from bit 3
+// down to bit 0, where M = 1 for a non-zero weight and S = 1 for a negative one.  Two masks turn a
+// word into sixteen e2m1 (fp4) values for the tensor cores:  (w & 0xAAAAAAAA) holds inputs
+// k0..k0+7 and ((w & 0x55555555) << 1) holds k0+8..k0+15, each nibble being S0M0 = +-1.0 or 0.
+// The same two bits, moved to bits 31 and 29 of a word, are the float +-2^-63 (or 0), which is
+// how the CUDA-core kernels multiply without any integer-to-float conversion.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BONSAI_CUDA_OK 0
+#define BONSAI_CUDA_BAD_ARG (-13)
+#define BONSAI_CUDA_LAUNCH_FAILED (-18)
+
+namespace bonsai {
+
+constexpr float kPow2_63 = 9223372036854775808.0f;  // 2^63
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the whole block (blockDim.x <= 1024, multiple of 32); every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem32[wid] = v;
+  __syncthreads();
+  float t = (lane < nw) ? smem32[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+
+// Dot of one packed word (16 ternary weights, scaled by 2^-63) with 16 floats.
+__device__ __forceinline__ float dot_word16(uint32_t w, const float* x) {
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float wa = __uint_as_float((w << (28 - 4 * i)) & 0xA0000000u);
+    float wb = __uint_as_float((w << (29 - 4 * i)) & 0xA0000000u);
+    acc = fmaf(wa, x[i], acc);
+    acc = fmaf(wb, x[8 + i], acc);
+  }
+  return acc;
+}
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
+}  // namespace bonsai

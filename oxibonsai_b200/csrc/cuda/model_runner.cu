@@ -1,0 +1,158 @@
+// Native decode-step runner: enqueues every kernel of one Qwen3 decoder step on a stream.
+//
+// The host loop of the reference builds per-layer parameter structs and issues 14 launches per
+// layer plus host round trips for the hidden state, the RoPE row and the logits on every token
+// (crates/oxibonsai-kernels/src/gpu_backend/cuda_full_layer/encode_ternary.rs:395-826).  Here a step
+// is: embed (token id read on the device) -> per layer { norm+QKV GEMV, QK-norm+RoPE+KV append,
+// split-KV attention, O-proj+residual, norm+gate/up+SwiGLU, down+residual } -> norm+LM head ->
+// sampler (writes the next token id and advances the position on the device).  Nothing crosses
+// the PCIe bus inside a step, so the whole step can be captured in one CUDA graph and replayed;
+// positions, block tables and sampler state are device buffers the graph reads.
+//
+// Tensor parallelism: q/k/v and gate/up are column-parallel (local heads / local intermediate
+// rows), attn-output and down are row-parallel (local K slice).  With tp_size > 1 the row-parallel
+// GEMVs write partial sums and the fused all-reduce+residual kernel of csrc/comm combines them.
+#include <vector>
+
+#include "common.cuh"
+
+extern "C" {
+int bonsai_bitgemv(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
+int bonsai_f16gemv(const void*, const float*, const float*, float, float*, int, int, cudaStream_t);
+int bonsai_embed_f16(const void*, const int*, float*, int, int, cudaStream_t);
+int bonsai_qknorm_rope_kvstore(const float*, int, const float*, const float*, float, const float*, const float*, const int*,
+                               const int*, int, float*, int, int, int, int, int, int, void*, void*, float*, float*, cudaStream_t);
+int bonsai_attn_decode(const float*, const int*, const int*, int, int, int, int, int, int, int, const void*, const void*,
+                       const float*, const float*, int, float*, float*, float*, int, cudaStream_t);
+int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
+                  const uint32_t*, int, cudaStream_t);
+int bonsai_allreduce_residual(void* comm, const float* partial, float* h, int n, int batch, cudaStream_t stream);
+}
+
+namespace bonsai {
+
+enum LayerPtr {
+  LP_QKV_CODES = 0, LP_QKV_SCALES, LP_O_CODES, LP_O_SCALES, LP_GU_CODES, LP_GU_SCALES, LP_DOWN_CODES, LP_DOWN_SCALES,
+  LP_ATTN_NORM, LP_FFN_NORM, LP_Q_NORM, LP_K_NORM, LP_KPOOL, LP_VPOOL, LP_KSCALE, LP_VSCALE, LP_COUNT
+};
+enum GlobalPtr {
+  GP_EMBD = 0, GP_LM_HEAD, GP_OUT_NORM, GP_ROPE_COS, GP_ROPE_SIN, GP_COUNT
+};
+enum IntCfg {
+  IC_HIDDEN = 0, IC_INTER_LOCAL, IC_LAYERS, IC_HEADS_LOCAL, IC_KV_HEADS_LOCAL, IC_HEAD_DIM, IC_VOCAB, IC_LM_ROWS_LOCAL,
+  IC_KVT, IC_PAGE_SIZE, IC_MAX_PAGES, IC_NSPLIT, IC_TP_SIZE, IC_TP_RANK, IC_COUNT
+};
+enum StepPtr {
+  SP_TOKENS = 0, SP_POSITIONS, SP_BLOCK_TABLE, SP_H, SP_QKV, SP_Q, SP_ATTN, SP_ACT, SP_LOGITS, SP_WS_ACC, SP_WS_ML,
+  SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_COUNT
+};
+
+struct Runner {
+  int ic[IC_COUNT];
+  float eps;
+  uint64_t gp[GP_COUNT];
+  std::vector<uint64_t> lp;  // [layers][LP_COUNT]
+  void* comm = nullptr;      // tensor-parallel communicator (csrc/comm), null when tp_size == 1
+};
+
+template <typename T>
+static inline T* P(uint64_t v) { return reinterpret_cast<T*>(v); }
+
+#define RC(expr) do { int _rc = (expr); if (_rc != 0) return _rc; } while (0)
+
+// flags: bit 0 = run the sampler and advance positions, bit 1 = skip the LM head
+static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int mask_words, cudaStream_t st) {
+  const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
+  const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
+  const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
+  const bool tp = r.ic[IC_TP_SIZE] > 1;
+  int* tokens = P<int>(sp[SP_TOKENS]);
+  int* positions = P<int>(sp[SP_POSITIONS]);
+  const int* bt = P<int>(sp[SP_BLOCK_TABLE]);
+  float* h = P<float>(sp[SP_H]);
+  float* qkv = P<float>(sp[SP_QKV]);
+  float* q = P<float>(sp[SP_Q]);
+  float* attn = P<float>(sp[SP_ATTN]);
+  float* act = P<float>(sp[SP_ACT]);
+  float* logits = P<float>(sp[SP_LOGITS]);
+  float* partial = P<float>(sp[SP_PARTIAL]);
+
+  for (int b = 0; b < batch; ++b)
+    RC(bonsai_embed_f16(P<void>(r.gp[GP_EMBD]), tokens + b, h + (size_t)b * hidden, hidden, vocab, st));
+  for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
+    const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
+    for (int b = 0; b < batch; ++b)
+      RC(bonsai_bitgemv(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]),
+                        r.eps, qkv + (size_t)b * qkv_n, nullptr, qkv_n, hidden, 0, st));
+    RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
+                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
+                                  r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
+                                  P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
+    RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
+                          P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
+                          r.ic[IC_NSPLIT], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), attn, 0, st));
+    if (!tp) {
+      for (int b = 0; b < batch; ++b)
+        RC(bonsai_bitgemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
+                          h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, 1, st));
+    } else {
+      for (int b = 0; b < batch; ++b)
+        RC(bonsai_bitgemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
+                          partial + (size_t)b * hidden, nullptr, hidden, qd, 0, st));
+      RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
+    }
+    for (int b = 0; b < batch; ++b)
+      RC(bonsai_bitgemv(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), r.eps,
+                        act + (size_t)b * inter, nullptr, 2 * inter, hidden, 2, st));
+    if (!tp) {
+      for (int b = 0; b < batch; ++b)
+        RC(bonsai_bitgemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
+                          h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, 1, st));
+    } else {
+      for (int b = 0; b < batch; ++b)
+        RC(bonsai_bitgemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
+                          partial + (size_t)b * hidden, nullptr, hidden, inter, 0, st));
+      RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
+    }
+  }
+  if (!(flags & 2)) {
+    for (int b = 0; b < batch; ++b)
+      RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), h + (size_t)b * hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps,
+                        logits + (size_t)b * vocab, lm_rows, hidden, st));
+  }
+  if (flags & 1) {
+    RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),
+                     P<unsigned long long>(sp[SP_RNG]), P<int>(sp[SP_OUT_TOKENS]), positions, 1,
+                     P<uint32_t>(sp[SP_ALLOW_MASK]), mask_words, st));
+  }
+  return 0;
+}
+
+}  // namespace bonsai
+
+extern "C" {
+
+// Weak default so the library links before the tensor-parallel communicator is built in.
+__attribute__((weak)) int bonsai_allreduce_residual(void*, const float*, float*, int, int, cudaStream_t) { return BONSAI_CUDA_BAD_ARG; }
+
+void* bonsai_runner_create(const int* icfg, float eps, const uint64_t* global_ptrs, const uint64_t* layer_ptrs) {
+  using namespace bonsai;
+  Runner* r = new Runner();
+  for (int i = 0; i < IC_COUNT; ++i) r->ic[i] = icfg[i];
+  r->eps = eps;
+  for (int i = 0; i < GP_COUNT; ++i) r->gp[i] = global_ptrs[i];
+  r->lp.assign(layer_ptrs, layer_ptrs + (size_t)icfg[IC_LAYERS] * LP_COUNT);
+  return r;
+}
+
+void bonsai_runner_destroy(void* r) { delete static_cast<bonsai::Runner*>(r); }
+void bonsai_runner_set_comm(void* r, void* comm) { static_cast<bonsai::Runner*>(r)->comm = comm; }
+void bonsai_runner_set_nsplit(void* r, int nsplit) { static_cast<bonsai::Runner*>(r)->ic[bonsai::IC_NSPLIT] = nsplit; }
+int bonsai_runner_layer_ptr_count() { return bonsai::LP_COUNT; }
+int bonsai_runner_step_ptr_count() { return bonsai::SP_COUNT; }
+
+int bonsai_runner_decode_step(void* r, const uint64_t* step_ptrs, int batch, int flags, int mask_words, cudaStream_t stream) {
+  return bonsai::decode_step(*static_cast<bonsai::Runner*>(r), step_ptrs, batch, flags, mask_words, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,290 @@
+"""Qwen3 decoder on the GPU: weight loading / repacking and the native step runner.
+
+Capability map to the reference: ``BonsaiModel::from_gguf`` + ``upload_weights_to_gpu``
+(crates/oxibonsai-model/src/model/types/mod.rs:71-142,210), the fused QKV / gate-up weight handles
+(block/types/upload.rs:8-39), the FP16 KV cache and activation buffers of the CUDA path
+(crates/oxibonsai-kernels/src/gpu_backend/cuda_full_layer/mod.rs:112-205) and the captured whole-model
+graph (encode_ternary.rs:546-660).  Differences by design: weights are repacked once into the
+planar-SM layout, q/k/v rows are concatenated and gate/up rows interleaved so each is one launch,
+the KV cache is paged, and every per-step scalar (token, position, sampler state) stays on the
+device so one CUDA graph covers embed -> layers -> LM head -> sampler.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..core import gguf as G
+from ..core.gguf import GgufFile, Qwen3Config
+from ..core.oracle import rope_table
+from ..ops import cuda_ops as K
+
+_QUANT_TYPES = (G.TQ2_0_G128, G.Q1_0_G128)
+
+
+@dataclass
+class LayerWeights:
+    qkv: K.PlanarWeight
+    o: K.PlanarWeight
+    gate_up: K.PlanarWeight
+    down: K.PlanarWeight
+    attn_norm: torch.Tensor
+    ffn_norm: torch.Tensor
+    q_norm: torch.Tensor
+    k_norm: torch.Tensor
+
+
+def _upload(arr: np.ndarray, device) -> torch.Tensor:
+    """Host bytes -> device uint8 tensor through a pinned staging copy."""
+    t = torch.from_numpy(np.array(arr, copy=True))
+    if device.type == "cuda":
+        t = t.pin_memory().to(device, non_blocking=True)
+    return t
+
+
+def _norm_vector(f: GgufFile, name: str, device) -> torch.Tensor:
+    info = f.tensor_info(name)
+    raw = f.tensor_bytes(name)
+    if info.type == G.F32:
+        v = np.frombuffer(raw, dtype=np.float32)
+    elif info.type == G.F16:
+        v = np.frombuffer(raw, dtype=np.float16).astype(np.float32)
+    else:
+        from ..core.blocks import dequantize
+        v = dequantize(info.type, raw)
+    return torch.from_numpy(np.array(v, copy=True)).to(device)
+
+
+def _f16_matrix(f: GgufFile, name: str, device, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
+    """Loads an embedding / LM-head matrix as f16 [rows, cols] (dequantising other storage types on the host)."""
+    info = f.tensor_info(name)
+    cols, rows = info.dims
+    nrows = rows - row0 if nrows is None else nrows
+    raw = f.tensor_bytes(name)
+    if info.type == G.F16:
+        m = np.frombuffer(raw, dtype=np.float16).reshape(rows, cols)[row0:row0 + nrows]
+        return _upload(m.view(np.uint8), device).view(torch.float16).reshape(nrows, cols)
+    if info.type == G.F32:
+        m = np.frombuffer(raw, dtype=np.float32).reshape(rows, cols)[row0:row0 + nrows].astype(np.float16)
+    else:
+        from ..core.blocks import dequantize
+        _, be, bb = G.type_info(info.type)
+        rb = cols // be * bb
+        m = dequantize(info.type, raw[row0 * rb:(row0 + nrows) * rb]).reshape(nrows, cols).astype(np.float16)
+    return torch.from_numpy(np.ascontiguousarray(m)).to(device)
+
+
+class Qwen3Weights:
+    """Device-resident weights of one tensor-parallel rank."""
+
+    def __init__(self, f: GgufFile, device, tp_rank: int = 0, tp_size: int = 1):
+        cfg = f.config()
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        if cfg.heads % tp_size or cfg.kv_heads % tp_size:
+            raise ValueError(f"tp_size {tp_size} must divide heads {cfg.heads} and kv_heads {cfg.kv_heads}")
+        self.heads_local = cfg.heads // tp_size
+        self.kv_heads_local = cfg.kv_heads // tp_size
+        nblk_inter = cfg.inter // 128
+        # split the intermediate dimension on 128-weight block boundaries (sizes may differ by one block)
+        base, extra = divmod(nblk_inter, tp_size)
+        counts = [base + (1 if r < extra else 0) for r in range(tp_size)]
+        self.inter_blk0 = sum(counts[:tp_rank])
+        self.inter_local = counts[tp_rank] * 128
+        if self.inter_local == 0:
+            raise ValueError("tensor-parallel degree leaves a rank without FFN rows")
+        hd, hidden = cfg.head_dim, cfg.hidden
+        qd_l, kvd_l = self.heads_local * hd, self.kv_heads_local * hd
+        dev = self.device
+
+        self.embd = _f16_matrix(f, "token_embd.weight", dev)
+        head_name = "output.weight" if f.has_tensor("output.weight") else "token_embd.weight"
+        if tp_size == 1:
+            same = head_name == "token_embd.weight"
+            self.lm_head = self.embd if same else _f16_matrix(f, head_name, dev)
+            self.lm_row0 = 0
+        else:
+            rows = (cfg.vocab + tp_size - 1) // tp_size
+            self.lm_row0 = tp_rank * rows
+            self.lm_head = _f16_matrix(f, head_name, dev, self.lm_row0, max(0, min(rows, cfg.vocab - self.lm_row0)))
+        self.out_norm = _norm_vector(f, "output_norm.weight", dev)
+        self.layers: list[LayerWeights] = []
+        self.weight_type = None
+        for l in range(cfg.layers):
+            p = f"blk.{l}."
+            infos = {n: f.tensor_info(p + n + ".weight") for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")}
+            for n, ti in infos.items():
+                if ti.type not in _QUANT_TYPES:
+                    raise NotImplementedError(f"{p}{n}: GPU path supports TQ2_0_g128 and Q1_0_g128 layer weights, got {ti.type_name}")
+            self.weight_type = infos["attn_q"].type
+            raws = {n: _upload(f.tensor_bytes(p + n + ".weight"), dev) for n in infos}
+            ty = lambda n: infos[n].type
+            qkv = K.PlanarWeight(qd_l + 2 * kvd_l, hidden, dev)
+            qkv.fill_from_gguf(raws["attn_q"], ty("attn_q"), hidden, tp_rank * qd_l, qd_l, dst_row0=0)
+            qkv.fill_from_gguf(raws["attn_k"], ty("attn_k"), hidden, tp_rank * kvd_l, kvd_l, dst_row0=qd_l)
+            qkv.fill_from_gguf(raws["attn_v"], ty("attn_v"), hidden, tp_rank * kvd_l, kvd_l, dst_row0=qd_l + kvd_l)
+            o = K.PlanarWeight(hidden, qd_l, dev)
+            o.fill_from_gguf(raws["attn_output"], ty("attn_output"), cfg.q_dim, 0, hidden, blk0=tp_rank * qd_l // 128, nblk=qd_l // 128)
+            gu = K.PlanarWeight(2 * self.inter_local, hidden, dev)
+            gu.fill_from_gguf(raws["ffn_gate"], ty("ffn_gate"), hidden, self.inter_blk0 * 128, self.inter_local, dst_row0=0, dst_row_stride=2)
+            gu.fill_from_gguf(raws["ffn_up"], ty("ffn_up"), hidden, self.inter_blk0 * 128, self.inter_local, dst_row0=1, dst_row_stride=2)
+            down = K.PlanarWeight(hidden, self.inter_local, dev)
+            down.fill_from_gguf(raws["ffn_down"], ty("ffn_down"), cfg.inter, 0, hidden, blk0=self.inter_blk0, nblk=self.inter_local // 128)
+            self.layers.append(LayerWeights(qkv, o, gu, down,
+                                            _norm_vector(f, p + "attn_norm.weight", dev), _norm_vector(f, p + "ffn_norm.weight", dev),
+                                            _norm_vector(f, p + "attn_q_norm.weight", dev), _norm_vector(f, p + "attn_k_norm.weight", dev)))
+            del raws
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
+
+    @property
+    def packed_bytes(self) -> int:
+        """Bytes a decode step must stream: packed layer weights + LM head."""
+        n = sum(lw.qkv.nbytes + lw.o.nbytes + lw.gate_up.nbytes + lw.down.nbytes for lw in self.layers)
+        return n + self.lm_head.numel() * 2
+
+
+class PagedKvCache:
+    """Page pool shared by all sequences of a rank; one K and one V pool per layer.
+
+    Reference: ``PagedKvCache`` / ``BlockPool`` / ``BlockTable`` (crates/oxibonsai-model/src/paged_kv_cache.rs:33-557),
+    with the storage formats of ``KvCacheFp16`` and ``QuantizedKvCache`` (kv_cache_fp16.rs, kv_cache_quant.rs) as page
+    formats, plus an INT4 page format.
+    """
+
+    def __init__(self, cfg: Qwen3Config, kv_heads_local: int, num_pages: int, page_size: int, kvt: int, device):
+        self.kvt, self.page_size, self.num_pages = kvt, page_size, num_pages
+        hd = cfg.head_dim
+        row = {K.KV_F32: hd, K.KV_F16: hd, K.KV_Q8: hd, K.KV_Q4: hd // 2}[kvt]
+        dt = K.KV_DTYPES[kvt]
+        shape = (cfg.layers, num_pages, kv_heads_local, page_size, row)
+        self.k = torch.zeros(shape, dtype=dt, device=device)
+        self.v = torch.zeros(shape, dtype=dt, device=device)
+        if kvt in (K.KV_Q8, K.KV_Q4):
+            self.k_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=device)
+            self.v_scale = torch.zeros(shape[:-1], dtype=torch.float32, device=device)
+        else:
+            self.k_scale = self.v_scale = None
+        self.free_pages = list(range(num_pages - 1, -1, -1))
+
+    def alloc(self, n: int) -> list[int]:
+        if n > len(self.free_pages):
+            raise MemoryError(f"KV cache exhausted: need {n} pages, {len(self.free_pages)} free")
+        return [self.free_pages.pop() for _ in range(n)]
+
+    def release(self, pages: list[int]) -> None:
+        self.free_pages.extend(reversed(pages))
+
+    @property
+    def utilization(self) -> float:
+        return 1.0 - len(self.free_pages) / max(1, self.num_pages)
+
+    @property
+    def nbytes(self) -> int:
+        n = self.k.numel() * self.k.element_size() * 2
+        if self.k_scale is not None:
+            n += self.k_scale.numel() * 8
+        return n
+
+
+class Qwen3Runner:
+    """Owns the activation buffers and the native step runner for a fixed maximum batch."""
+
+    def __init__(self, weights: Qwen3Weights, kv: PagedKvCache, max_batch: int, max_seq: int, nsplit: int | None = None):
+        self.w, self.kv, self.max_batch, self.max_seq = weights, kv, max_batch, max_seq
+        cfg, dev = weights.cfg, weights.device
+        self.cfg, self.device = cfg, dev
+        hd = cfg.head_dim
+        nq, nkv = weights.heads_local, weights.kv_heads_local
+        self.max_pages = (max_seq + kv.page_size - 1) // kv.page_size
+        self.nsplit = nsplit or max(1, min(32, (max_seq + 255) // 256))
+        B = max_batch
+        f32 = dict(dtype=torch.float32, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(B, **i32)
+        self.positions = torch.zeros(B, **i32)
+        self.block_table = torch.zeros((B, self.max_pages), **i32)
+        self.h = torch.zeros((B, cfg.hidden), **f32)
+        self.qkv = torch.zeros((B, (nq + 2 * nkv) * hd), **f32)
+        self.q = torch.zeros((B, nq, hd), **f32)
+        self.attn = torch.zeros((B, nq * hd), **f32)
+        self.act = torch.zeros((B, weights.inter_local), **f32)
+        self.logits = torch.zeros((B, cfg.vocab), **f32)
+        self.partial = torch.zeros((B, cfg.hidden), **f32)
+        self.ws_acc = torch.zeros((B, nq, self.nsplit, hd), **f32)
+        self.ws_ml = torch.zeros((B, nq, self.nsplit, 2), **f32)
+        self.temps = torch.zeros(B, **f32)
+        self.topks = torch.zeros(B, **i32)
+        self.topps = torch.ones(B, **f32)
+        self.rng = torch.full((B,), 42, dtype=torch.int64, device=dev)
+        self.out_tokens = torch.zeros(B, **i32)
+        cos, sin = rope_table(hd, max_seq, cfg.rope_base)
+        self.rope_cos = torch.from_numpy(cos).to(dev)
+        self.rope_sin = torch.from_numpy(sin).to(dev)
+        self._graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
+        self._build_native()
+
+    def _build_native(self) -> None:
+        lib = K.lib()
+        w, kv, cfg = self.w, self.kv, self.cfg
+        nlp, nsp = lib.bonsai_runner_layer_ptr_count(), lib.bonsai_runner_step_ptr_count()
+        icfg = (C.c_int * 14)(cfg.hidden, w.inter_local, cfg.layers, w.heads_local, w.kv_heads_local, cfg.head_dim, cfg.vocab,
+                              w.lm_head.shape[0], kv.kvt, kv.page_size, self.max_pages, self.nsplit, w.tp_size, w.tp_rank)
+        gp = (C.c_uint64 * 5)(w.embd.data_ptr(), w.lm_head.data_ptr(), w.out_norm.data_ptr(), self.rope_cos.data_ptr(), self.rope_sin.data_ptr())
+        lp = (C.c_uint64 * (nlp * cfg.layers))()
+        for l, lw in enumerate(w.layers):
+            ks = kv.k_scale[l].data_ptr() if kv.k_scale is not None else 0
+            vs = kv.v_scale[l].data_ptr() if kv.v_scale is not None else 0
+            vals = [lw.qkv.codes.data_ptr(), lw.qkv.scales.data_ptr(), lw.o.codes.data_ptr(), lw.o.scales.data_ptr(),
+                    lw.gate_up.codes.data_ptr(), lw.gate_up.scales.data_ptr(), lw.down.codes.data_ptr(), lw.down.scales.data_ptr(),
+                    lw.attn_norm.data_ptr(), lw.ffn_norm.data_ptr(), lw.q_norm.data_ptr(), lw.k_norm.data_ptr(),
+                    kv.k[l].data_ptr(), kv.v[l].data_ptr(), ks, vs]
+            assert len(vals) == nlp
+            for i, v in enumerate(vals):
+                lp[l * nlp + i] = v
+        self._native = lib.bonsai_runner_create(icfg, cfg.eps, gp, lp)
+        sp = [self.tokens, self.positions, self.block_table, self.h, self.qkv, self.q, self.attn, self.act, self.logits, self.ws_acc,
+              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None]
+        assert len(sp) == nsp
+        self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
+        self.launches_per_step = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_native", None):
+                K.lib().bonsai_runner_destroy(self._native)
+                self._native = None
+        except Exception:
+            pass
+
+    def set_comm(self, comm_handle: int) -> None:
+        K.lib().bonsai_runner_set_comm(self._native, comm_handle)
+
+    def kernel_launches(self, batch: int, sample: bool = True) -> int:
+        """Number of kernel launches in one decode step (each is one of this library's kernels)."""
+        per_layer = 4 * batch + 3 + (2 if self.w.tp_size > 1 else 0)
+        return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0)
+
+    def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:
+        flags = (1 if sample else 0) | (0 if lm_head else 2)
+        K.check(K.lib().bonsai_runner_decode_step(self._native, self._step_ptrs, batch, flags, 0, K.stream()), "decode_step")
+
+    def step(self, batch: int, sample: bool = True) -> None:
+        """One decode step for the first ``batch`` slots, replayed from a CUDA graph after the first call."""
+        key = (batch, int(sample))
+        g = self._graphs.get(key)
+        if g is None:
+            # capture without running: the capture itself executes nothing, so state is untouched
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(s):
+                with torch.cuda.graph(g, stream=s):
+                    self.step_eager(batch, sample)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            self._graphs[key] = g
+        g.replay()

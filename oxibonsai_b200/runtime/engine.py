@@ -1,0 +1,194 @@
+"""Inference engine: load a GGUF checkpoint, prefill, decode, sample, stream.
+
+Reference surface: ``InferenceEngine`` (crates/oxibonsai-runtime/src/engine.rs:98-118) with ``from_gguf`` /
+``from_gguf_path`` (:179-249, :1023-1045), ``generate`` (:376-445: prefill, then sample -> stop on token
+151645 before emitting it -> forward), the streaming and seeded variants (:459-709) and the warm-up that
+hides graph capture (:216-234).  The per-token loop here keeps the model state on the GPU: the host
+uploads (token, position) from pinned memory, replays one CUDA graph and reads back one token id.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Iterator, Sequence
+
+import torch
+
+from ..core.gguf import GgufFile, Qwen3Config
+from ..core.oracle import EOS_TOKEN
+from ..models.qwen3 import PagedKvCache, Qwen3Runner, Qwen3Weights
+from ..ops import cuda_ops as K
+from .presets import SamplingParams, SamplingPreset
+
+KV_NAMES = {"f32": K.KV_F32, "fp32": K.KV_F32, "f16": K.KV_F16, "fp16": K.KV_F16, "q8": K.KV_Q8, "int8": K.KV_Q8, "q4": K.KV_Q4, "int4": K.KV_Q4}
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    token_times: list[float] = field(default_factory=list)
+
+    @property
+    def tokens_per_second(self) -> float:
+        """The reference CLI's figure: generated / (prefill + decode) wall time (src/main.rs:604-621)."""
+        t = self.prefill_seconds + self.decode_seconds
+        return self.generated_tokens / t if t > 0 else 0.0
+
+    @property
+    def decode_tokens_per_second(self) -> float:
+        return self.generated_tokens / self.decode_seconds if self.decode_seconds > 0 else 0.0
+
+
+class InferenceEngine:
+    """Single-process engine for one GPU (or one tensor-parallel rank)."""
+
+    def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
+                 device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
+                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("InferenceEngine needs a CUDA device; use oxibonsai_b200.core.Oracle for the CPU path")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        K.lib()  # fail loudly if the native kernels are missing
+        self.model_path = str(model_path)
+        self.gguf = GgufFile.open(self.model_path)
+        self.config: Qwen3Config = self.gguf.config()
+        self.max_seq_len = int(max_seq_len)
+        self.max_batch = int(max_batch)
+        self.sampling = (sampling or SamplingPreset.BALANCED.params()).validate()
+        self.kvt = KV_NAMES[kv_dtype.lower()]
+        t0 = time.perf_counter()
+        self.weights = Qwen3Weights(self.gguf, self.device, tp_rank, tp_size)
+        pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
+        self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
+                               self.kvt, self.device)
+        self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len)
+        self.load_seconds = time.perf_counter() - t0
+        # pinned staging for the per-step host <-> device traffic
+        self._tok_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
+        self._pos_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
+        self._out_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
+        self._slot_pages: dict[int, list[int]] = {}
+        self.last_stats = GenerationStats()
+        if warmup:
+            self.warmup()
+
+    # ---- construction helpers -------------------------------------------------------------------
+    @classmethod
+    def from_gguf_path(cls, path: str, **kw) -> "InferenceEngine":
+        return cls(path, **kw)
+
+    def warmup(self) -> None:
+        """Captures the decode graph and touches every kernel once (hidden from the first request)."""
+        self._bind_slot(0, min(self.max_seq_len, 8))
+        self._set_sampling(0, SamplingPreset.GREEDY.params())
+        self._upload(0, 0, 0)
+        self.runner.step_eager(1, sample=True)
+        self._upload(0, 0, 1)
+        self.runner.step(1, sample=True)
+        torch.cuda.synchronize(self.device)
+        self._release_slot(0)
+
+    # ---- slot / page management -----------------------------------------------------------------
+    def _bind_slot(self, slot: int, n_tokens: int) -> None:
+        if n_tokens > self.max_seq_len:
+            raise ValueError(f"sequence of {n_tokens} tokens exceeds max_seq_len {self.max_seq_len}")
+        need = (n_tokens + self.kv.page_size - 1) // self.kv.page_size
+        have = self._slot_pages.setdefault(slot, [])
+        if need > len(have):
+            have.extend(self.kv.alloc(need - len(have)))
+            row = torch.tensor(have, dtype=torch.int32)
+            self.runner.block_table[slot, : len(have)].copy_(row.to(self.device))
+
+    def _release_slot(self, slot: int) -> None:
+        pages = self._slot_pages.pop(slot, [])
+        self.kv.release(pages)
+
+    def _set_sampling(self, slot: int, p: SamplingParams) -> None:
+        r = self.runner
+        r.temps[slot] = float(p.temperature)
+        r.topks[slot] = int(p.top_k)
+        r.topps[slot] = float(p.top_p)
+        seed = int(p.seed) & 0xFFFFFFFFFFFFFFFF
+        r.rng[slot] = seed - (1 << 64) if seed >= (1 << 63) else seed
+
+    def _upload(self, slot: int, token: int, pos: int) -> None:
+        self._tok_host[slot] = token
+        self._pos_host[slot] = pos
+        self.runner.tokens[slot: slot + 1].copy_(self._tok_host[slot: slot + 1], non_blocking=True)
+        self.runner.positions[slot: slot + 1].copy_(self._pos_host[slot: slot + 1], non_blocking=True)
+
+    # ---- generation -------------------------------------------------------------------------------
+    def prefill(self, prompt: Sequence[int], slot: int = 0) -> None:
+        """Runs the prompt through the model, leaving logits of the last prompt token in the runner."""
+        n = len(prompt)
+        for i, tok in enumerate(prompt):
+            self._upload(slot, int(tok), i)
+            last = i == n - 1
+            if slot == 0:
+                self.runner.step_eager(1, sample=False, lm_head=last)
+            else:
+                raise NotImplementedError("token-by-token prefill is wired for slot 0; batched prefill uses the prefill kernels")
+
+    def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
+                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None) -> Iterator[int]:
+        p = (params or self.sampling).validate()
+        max_new = p.max_tokens if max_tokens is None else max_tokens
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            return
+        stats = GenerationStats(prompt_tokens=len(prompt))
+        self.last_stats = stats
+        total = min(self.max_seq_len, len(prompt) + max_new)
+        self._bind_slot(0, total)
+        self._set_sampling(0, p)
+        r = self.runner
+        try:
+            t0 = time.perf_counter()
+            self.prefill(prompt, 0)
+            # first token: sample from the prefill logits on the device
+            K.sample(r.logits[:1], r.temps[:1], r.topks[:1], r.topps[:1], r.rng[:1], out=r.tokens[:1])
+            self._out_host[:1].copy_(r.tokens[:1], non_blocking=True)
+            torch.cuda.synchronize(self.device)
+            stats.prefill_seconds = time.perf_counter() - t0
+            pos = len(prompt)
+            t_dec = time.perf_counter()
+            tok = int(self._out_host[0])
+            for _ in range(max_new):
+                if stop_at_eos and tok == EOS_TOKEN:
+                    break
+                stats.generated_tokens += 1
+                stats.token_times.append(time.perf_counter())
+                if on_token is not None:
+                    on_token(tok)
+                yield tok
+                if pos >= self.max_seq_len:
+                    break
+                # the reference runs a forward after every emitted token, including the last
+                self._upload(0, tok, pos)
+                r.step(1, sample=True)
+                self._out_host[:1].copy_(r.tokens[:1], non_blocking=True)
+                torch.cuda.synchronize(self.device)
+                tok = int(self._out_host[0])
+                pos += 1
+            stats.decode_seconds = time.perf_counter() - t_dec
+        finally:
+            self._release_slot(0)
+
+    def generate(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
+                 stop_at_eos: bool = True) -> list[int]:
+        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos))
+
+    def generate_seeded(self, prompt: Sequence[int], max_tokens: int, seed: int, params: SamplingParams | None = None) -> list[int]:
+        from dataclasses import replace
+        return self.generate(prompt, max_tokens, replace(params or self.sampling, seed=seed))
+
+    # ---- introspection ----------------------------------------------------------------------------
+    def model_info(self) -> dict:
+        c = self.config
+        return {"name": c.name, "arch": c.arch, "layers": c.layers, "hidden": c.hidden, "heads": c.heads, "kv_heads": c.kv_heads,
+                "head_dim": c.head_dim, "intermediate": c.inter, "vocab": c.vocab, "context": c.context,
+                "weight_bytes": self.weights.packed_bytes, "kv_bytes": self.kv.nbytes, "load_seconds": self.load_seconds}

@@ -1,0 +1,165 @@
+"""sm_100a decode kernels against plain PyTorch fp32 references of the same ops."""
+import numpy as np
+import pytest
+import torch
+
+from oxibonsai_b200.core import Q1_0_G128, TQ2_0_G128, dequantize, quantize
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _random_quant(ty, rows, cols, seed):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((rows, cols)) * 0.05).astype(np.float32)
+    raw = quantize(ty, w)
+    wd = dequantize(ty, raw).reshape(rows, cols)
+    return raw, torch.from_numpy(wd)
+
+
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+def test_repack_round_trip_and_submatrix(ty):
+    from oxibonsai_b200.ops import cuda_ops as K
+    rows, cols = 96, 512
+    raw, wd = _random_quant(ty, rows, cols, 0)
+    rawd = torch.from_numpy(raw).to(_dev())
+    pw = K.PlanarWeight(rows, cols, _dev()).fill_from_gguf(rawd, ty, cols, 0, rows)
+    assert torch.equal(pw.to_f32().cpu(), wd)
+    # rows 32..63, input blocks 1..2, interleaved into even rows of a 64-row matrix
+    sub = K.PlanarWeight(64, 256, _dev())
+    sub.codes.zero_(); sub.scales.zero_()
+    sub.fill_from_gguf(rawd, ty, cols, 32, 32, blk0=1, nblk=2, dst_row0=0, dst_row_stride=2)
+    got = sub.to_f32().cpu()
+    assert torch.equal(got[0::2], wd[32:64, 128:384]) and (got[1::2] == 0).all()
+
+
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+@pytest.mark.parametrize("rows,cols", [(6144, 4096), (4096, 12288), (512, 2560), (200, 128), (1000, 9728)])
+def test_bitgemv_matches_fp32_matmul(ty, rows, cols):
+    from oxibonsai_b200.ops import cuda_ops as K
+    raw, wd = _random_quant(ty, rows, cols, 1)
+    pw = K.PlanarWeight(rows, cols, _dev()).fill_from_gguf(torch.from_numpy(raw).to(_dev()), ty, cols, 0, rows)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(cols, generator=g)
+    ref = wd.double() @ x.double()
+    y = K.bitgemv(pw, x.to(_dev()))
+    scale = ref.abs().max().item()
+    assert (y.cpu().double() - ref).abs().max().item() <= 2e-5 * scale + 1e-6
+
+
+def test_bitgemv_fused_norm_residual_swiglu():
+    from oxibonsai_b200.ops import cuda_ops as K
+    rows, cols = 1024, 2048
+    raw, wd = _random_quant(TQ2_0_G128, rows, cols, 2)
+    dev = _dev()
+    pw = K.PlanarWeight(rows, cols, dev).fill_from_gguf(torch.from_numpy(raw).to(dev), TQ2_0_G128, cols, 0, rows)
+    g = torch.Generator().manual_seed(4)
+    x, nw, res = torch.randn(cols, generator=g) * 3, torch.rand(cols, generator=g) + 0.5, torch.randn(rows, generator=g)
+    eps = 1e-6
+    xn = nw * x * torch.rsqrt((x * x).mean() + eps)
+    ref = wd.double() @ xn.double()
+    y = K.bitgemv(pw, x.to(dev), norm_w=nw.to(dev), eps=eps)
+    assert torch.allclose(y.cpu().double(), ref, rtol=1e-4, atol=1e-4)
+    y = K.bitgemv(pw, xn.to(dev), epi=K.EPI_RESID, residual=res.to(dev))
+    assert torch.allclose(y.cpu().double(), ref + res.double(), rtol=1e-4, atol=1e-4)
+    y = K.bitgemv(pw, xn.to(dev), epi=K.EPI_SWIGLU)
+    gate, up = ref[0::2], ref[1::2]
+    assert torch.allclose(y.cpu().double(), torch.nn.functional.silu(gate) * up, rtol=1e-4, atol=1e-4)
+    # in-place residual
+    h = res.to(dev).clone()
+    K.bitgemv(pw, xn.to(dev), epi=K.EPI_RESID, residual=h, out=h)
+    assert torch.allclose(h.cpu().double(), ref + res.double(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(151936, 2048), (5000, 4096), (333, 2560), (64, 8192)])
+def test_f16gemv_matches_fp32(rows, cols):
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(rows, cols, generator=g) * 0.02).half()
+    x, nw = torch.randn(cols, generator=g), torch.rand(cols, generator=g) + 0.5
+    y = K.f16gemv(w.to(dev), x.to(dev))
+    ref = w.double() @ x.double()
+    assert torch.allclose(y.cpu().double(), ref, rtol=1e-4, atol=1e-4)
+    xn = nw * x * torch.rsqrt((x * x).mean() + 1e-6)
+    y = K.f16gemv(w.to(dev), x.to(dev), norm_w=nw.to(dev), eps=1e-6)
+    assert torch.allclose(y.cpu().double(), w.double() @ xn.double(), rtol=1e-4, atol=1e-4)
+
+
+def _torch_attention_reference(qkv_steps, nq, nkv, hd, qn, kn, eps, base):
+    """Runs the QK-norm -> RoPE -> causal GQA of every step in fp32 and returns the last step's output."""
+    ks, vs = [], []
+    half = hd // 2
+    out = None
+    for pos, qkv in enumerate(qkv_steps):
+        q = qkv[: nq * hd].view(nq, hd)
+        k = qkv[nq * hd:(nq + nkv) * hd].view(nkv, hd)
+        v = qkv[(nq + nkv) * hd:].view(nkv, hd)
+        norm = lambda t, w: w * t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
+        q, k = norm(q, qn), norm(k, kn)
+        inv = 1.0 / (base ** (torch.arange(half, dtype=torch.float32) * 2 / hd))
+        ang = pos * inv
+        c, s = torch.cos(ang), torch.sin(ang)
+        rope = lambda t: torch.cat([t[:, :half] * c - t[:, half:] * s, t[:, :half] * s + t[:, half:] * c], -1)
+        q, k = rope(q), rope(k)
+        ks.append(k); vs.append(v)
+        Kc, Vc = torch.stack(ks, 1), torch.stack(vs, 1)  # [nkv, T, hd]
+        g = nq // nkv
+        sc = torch.einsum("hd,htd->ht", q, Kc.repeat_interleave(g, 0)) / hd ** 0.5
+        out = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.repeat_interleave(g, 0))
+    return out
+
+
+@pytest.mark.parametrize("kvt,tol", [(0, 2e-5), (1, 3e-3), (2, 3e-2), (3, 0.35)])
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 2, 128), (4, 4, 64), (16, 2, 128)])
+def test_qknorm_rope_kvstore_and_paged_attention(kvt, tol, nq, nkv, hd):
+    from oxibonsai_b200.core.oracle import rope_table
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    steps, page, base, eps = 70, 16, 1e6, 1e-6
+    g = torch.Generator().manual_seed(6)
+    qn, kn = torch.rand(hd, generator=g) + 0.5, torch.rand(hd, generator=g) + 0.5
+    qkvs = [torch.randn((nq + 2 * nkv) * hd, generator=g) for _ in range(steps)]
+    ref = _torch_attention_reference(qkvs, nq, nkv, hd, qn, kn, eps, base)
+    npages = 8
+    row = {0: hd, 1: hd, 2: hd, 3: hd // 2}[kvt]
+    kpool = torch.zeros((npages, nkv, page, row), dtype=K.KV_DTYPES[kvt], device=dev)
+    vpool = torch.zeros_like(kpool)
+    ksc = torch.zeros((npages, nkv, page), device=dev) if kvt >= 2 else None
+    vsc = torch.zeros((npages, nkv, page), device=dev) if kvt >= 2 else None
+    # a shuffled block table exercises the page indirection
+    bt = torch.tensor([[5, 2, 7, 0, 3, 1, 4, 6]], dtype=torch.int32, device=dev)
+    cos, sin = rope_table(hd, 128, base)
+    cos, sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+    q = torch.zeros((1, nq, hd), device=dev)
+    for t, qkv in enumerate(qkvs):
+        pos.fill_(t)
+        K.qknorm_rope_kvstore(qkv.to(dev).view(1, -1), qn.to(dev), kn.to(dev), eps, cos, sin, pos, bt, q, nq, nkv, hd, kvt, page, kpool, vpool, ksc, vsc)
+    for nsplit in (1, 3, 8):
+        out = K.attn_decode(q, pos, bt, nq, nkv, hd, kvt, page, kpool, vpool, ksc, vsc, nsplit=nsplit)
+        err = (out[0].cpu() - ref).abs().max().item()
+        assert err <= tol * max(1.0, ref.abs().max().item()), (kvt, nsplit, err)
+
+
+def test_attention_batch_with_different_lengths():
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    nq, nkv, hd, page = 4, 2, 64, 16
+    g = torch.Generator().manual_seed(8)
+    lens = [5, 37]
+    kpool = torch.randn((6, nkv, page, hd), generator=g).to(dev)
+    vpool = torch.randn((6, nkv, page, hd), generator=g).to(dev)
+    bt = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32, device=dev)
+    q = torch.randn((2, nq, hd), generator=g).to(dev)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
+    out = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F32, page, kpool, vpool, nsplit=4).cpu()
+    for b, L in enumerate(lens):
+        Kc = kpool[bt[b].long()].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :L].cpu()
+        Vc = vpool[bt[b].long()].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :L].cpu()
+        sc = torch.einsum("hd,htd->ht", q[b].cpu(), Kc.repeat_interleave(2, 0)) / hd ** 0.5
+        ref = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.repeat_interleave(2, 0))
+        assert torch.allclose(out[b], ref, rtol=1e-4, atol=1e-5)

