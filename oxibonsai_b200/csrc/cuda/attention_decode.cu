@@ -131,16 +131,26 @@ __device__ __forceinline__ void load_row(const uint8_t* base, const float* scale
   }
 }
 
-// grid (kv_heads, splits, batch), block 128 (4 warps).  Writes per-split partials.
+// grid (kv_heads, splits, batch), block 256 (8 warps).  Each warp walks its share of the split's
+// tokens four at a time (independent K/V loads in flight), the warps are combined in shared
+// memory and the split's partial (max, sum, weighted V) goes to the workspace; the last CTA of a
+// (sequence, kv head) to finish merges all splits in split order and writes the attention output.
+constexpr int kAttnWarps = 8;
+constexpr int kAttnUnroll = 4;
+
 template <int KVT, int DPL, int G>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, const int* __restrict__ positions,
+__global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const int* __restrict__ positions,
                                                          const int* __restrict__ block_table, int max_pages, KvPool pool,
                                                          int nq, float sm_scale, float* __restrict__ ws_acc,
-                                                         float* __restrict__ ws_ml, int extra_len) {
-  extern __shared__ float sh[];  // [4 warps][G][hd + 2]
+                                                         float* __restrict__ ws_ml, int* __restrict__ counters,
+                                                         float* __restrict__ out, int extra_len) {
+  extern __shared__ float sh[];  // [8 warps][G][hd + 2]
+  __shared__ int s_last;
   const int hd = pool.hd, nkv = pool.kv_heads;
   const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int len = positions[b] + 1 + extra_len;
   const int chunk = (len + nsplit - 1) / nsplit;
   const int t0 = split * chunk, t1 = min(len, t0 + chunk);
@@ -158,37 +168,60 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     l[g] = 0.0f;
   }
   const int* bt = block_table + (size_t)b * max_pages;
-  for (int t = t0 + warp; t < t1; t += 4) {
-    int page = bt[t / pool.page_size];
-    size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (t % pool.page_size);
-    float kr[DPL], vr[DPL];
-    load_row<KVT, DPL>(pool.k, pool.k_scale, row, hd, lane, kr);
-    load_row<KVT, DPL>(pool.v, pool.v_scale, row, hd, lane, vr);
-    float s[G];
+  for (int tb = t0 + warp; tb < t1; tb += kAttnWarps * kAttnUnroll) {
+    float kr[kAttnUnroll][DPL], vr[kAttnUnroll][DPL];
+    bool valid[kAttnUnroll];
+#pragma unroll
+    for (int u = 0; u < kAttnUnroll; ++u) {
+      const int t = tb + u * kAttnWarps;
+      valid[u] = t < t1;
+      const int tt = valid[u] ? t : t0;
+      const int page = bt[tt / pool.page_size];
+      const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (tt % pool.page_size);
+      load_row<KVT, DPL>(pool.k, pool.k_scale, row, hd, lane, kr[u]);
+      load_row<KVT, DPL>(pool.v, pool.v_scale, row, hd, lane, vr[u]);
+    }
+    float s[kAttnUnroll][G];
+#pragma unroll
+    for (int u = 0; u < kAttnUnroll; ++u)
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) a = fmaf(qr[g][j], kr[u][j], a);
+        s[u][g] = a;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < kAttnUnroll; ++u)
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float a = 0.0f;
+      float mn = m[g];
 #pragma unroll
-      for (int j = 0; j < DPL; ++j) a = fmaf(qr[g][j], kr[j], a);
-      s[g] = a;
-    }
+      for (int u = 0; u < kAttnUnroll; ++u)
+        if (valid[u]) mn = fmaxf(mn, s[u][g]);
+      const float r = expf(m[g] - mn);  // exp(-inf) = 0 before the first token
+      float p[kAttnUnroll], ps = 0.0f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+      for (int u = 0; u < kAttnUnroll; ++u) {
+        p[u] = valid[u] ? expf(s[u][g] - mn) : 0.0f;
+        ps += p[u];
+      }
+      l[g] = l[g] * r + ps;
 #pragma unroll
-      for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-    }
+      for (int j = 0; j < DPL; ++j) {
+        float a = acc[g][j] * r;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float mn = fmaxf(m[g], s[g]);
-      float r = __expf(m[g] - mn);  // exp(-inf) = 0 on the first token
-      float p = __expf(s[g] - mn);
-      l[g] = l[g] * r + p;
-#pragma unroll
-      for (int j = 0; j < DPL; ++j) acc[g][j] = fmaf(acc[g][j], r, p * vr[j]);
+        for (int u = 0; u < kAttnUnroll; ++u) a = fmaf(p[u], vr[u][j], a);
+        acc[g][j] = a;
+      }
       m[g] = mn;
     }
   }
-  // combine the four warps
+  // combine the warps
   const int stride = hd + 2;
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -205,12 +238,12 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     int g = idx / hd, d = idx - g * hd;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
     float a = 0.0f, L = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < kAttnWarps; ++w) {
       const float* src = sh + ((size_t)w * G + g) * stride;
-      float f = (src[hd] == -INFINITY) ? 0.0f : __expf(src[hd] - M);
+      float f = (src[hd] == -INFINITY) ? 0.0f : expf(src[hd] - M);
       a += f * src[d];
       L += f * src[hd + 1];
     }
@@ -221,45 +254,54 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
       ws_ml[o * 2 + 1] = L;
     }
   }
-}
-
-// grid (heads, batch), block hd
-__global__ void attn_merge_kernel(const float* __restrict__ ws_acc, const float* __restrict__ ws_ml, int nsplit, int hd,
-                                  float* __restrict__ out) {
-  const size_t hb = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-  const int d = threadIdx.x;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ws_ml[(hb * nsplit + s) * 2]);
-  float a = 0.0f, L = 0.0f;
-  for (int s = 0; s < nsplit; ++s) {
-    float ms = ws_ml[(hb * nsplit + s) * 2];
-    float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
-    a += f * ws_acc[(hb * nsplit + s) * hd + d];
-    L += f * ws_ml[(hb * nsplit + s) * 2 + 1];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ctr = counters + (size_t)b * nkv + kvh;
+    int prev = atomicAdd(ctr, 1);
+    s_last = (prev == nsplit - 1);
+    if (s_last) *ctr = 0;
   }
-  out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    int g = idx / hd, d = idx - g * hd;
+    size_t hb = ((size_t)b * nq + kvh * G + g);
+    float M = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ws_ml + (hb * nsplit + sp) * 2));
+    float a = 0.0f, L = 0.0f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      float ms = __ldcg(ws_ml + (hb * nsplit + sp) * 2);
+      float f = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+      a += f * __ldcg(ws_acc + (hb * nsplit + sp) * hd + d);
+      L += f * __ldcg(ws_ml + (hb * nsplit + sp) * 2 + 1);
+    }
+    out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
+  }
 }
 
 template <int KVT, int DPL>
 int launch_decode_g(int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt, int max_pages,
-                    KvPool pool, int nq, float sc, float* wa, float* wm, int extra) {
+                    KvPool pool, int nq, float sc, float* wa, float* wm, int* ctr, float* out, int extra) {
+  cudaError_t e;
   switch (G) {
-    case 1: attn_decode_kernel<KVT, DPL, 1><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
-    case 2: attn_decode_kernel<KVT, DPL, 2><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
-    case 4: attn_decode_kernel<KVT, DPL, 4><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
-    case 8: attn_decode_kernel<KVT, DPL, 8><<<grid, 128, smem, st>>>(q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra); break;
+    case 1: e = launch_pdl(attn_decode_kernel<KVT, DPL, 1>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    case 2: e = launch_pdl(attn_decode_kernel<KVT, DPL, 2>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    case 4: e = launch_pdl(attn_decode_kernel<KVT, DPL, 4>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    case 8: e = launch_pdl(attn_decode_kernel<KVT, DPL, 8>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
     default: return BONSAI_CUDA_BAD_ARG;
   }
-  return launch_status();
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 template <int KVT>
 int launch_decode_d(int dpl, int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt,
-                    int max_pages, KvPool pool, int nq, float sc, float* wa, float* wm, int extra) {
+                    int max_pages, KvPool pool, int nq, float sc, float* wa, float* wm, int* ctr, float* out, int extra) {
   switch (dpl) {
-    case 2: return launch_decode_g<KVT, 2>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
-    case 4: return launch_decode_g<KVT, 4>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
-    case 8: return launch_decode_g<KVT, 8>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, extra);
+    case 2: return launch_decode_g<KVT, 2>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra);
+    case 4: return launch_decode_g<KVT, 4>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra);
+    case 8: return launch_decode_g<KVT, 8>(G, grid, smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra);
     default: return BONSAI_CUDA_BAD_ARG;
   }
 }
@@ -284,29 +326,27 @@ int bonsai_qknorm_rope_kvstore(const float* qkv, int qkv_stride, const float* q_
 }
 
 // q: f32 [batch][nq][hd] -> out f32 [batch][nq][hd].  Context length of sequence b is
-// positions[b] + 1 + extra_len.  ws_acc needs batch*nq*nsplit*hd floats, ws_ml batch*nq*nsplit*2.
+// positions[b] + 1 + extra_len.  ws_acc needs batch*nq*nsplit*hd floats, ws_ml batch*nq*nsplit*2,
+// counters batch*nkv ints that are zero between launches (the kernel resets them).
 int bonsai_attn_decode(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
                        int hd, int kvt, int page_size, const void* kpool, const void* vpool, const float* kscale,
-                       const float* vscale, int nsplit, float* ws_acc, float* ws_ml, float* out, int extra_len,
+                       const float* vscale, int nsplit, float* ws_acc, float* ws_ml, int* counters, float* out, int extra_len,
                        cudaStream_t stream) {
   using namespace bonsai;
-  if (hd % 32 != 0 || hd < 64 || hd > 256 || nq % nkv != 0 || nsplit < 1 || batch <= 0) return BONSAI_CUDA_BAD_ARG;
+  if (hd % 32 != 0 || hd < 64 || hd > 256 || nq % nkv != 0 || nsplit < 1 || batch <= 0 || counters == nullptr) return BONSAI_CUDA_BAD_ARG;
   int G = nq / nkv, dpl = hd / 32;
   KvPool pool{(uint8_t*)kpool, (uint8_t*)vpool, (float*)kscale, (float*)vscale, page_size, nkv, hd, kvt};
   dim3 grid(nkv, nsplit, batch);
-  size_t smem = (size_t)4 * G * (hd + 2) * sizeof(float);
+  size_t smem = (size_t)kAttnWarps * G * (hd + 2) * sizeof(float);
+  if (smem > 48 * 1024) return BONSAI_CUDA_BAD_ARG;
   float sc = 1.0f / sqrtf((float)hd);
-  int rc;
   switch (kvt) {
-    case KV_F32: rc = launch_decode_d<KV_F32>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
-    case KV_F16: rc = launch_decode_d<KV_F16>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
-    case KV_Q8: rc = launch_decode_d<KV_Q8>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
-    case KV_Q4: rc = launch_decode_d<KV_Q4>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, extra_len); break;
+    case KV_F32: return launch_decode_d<KV_F32>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+    case KV_F16: return launch_decode_d<KV_F16>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+    case KV_Q8: return launch_decode_d<KV_Q8>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+    case KV_Q4: return launch_decode_d<KV_Q4>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
     default: return BONSAI_CUDA_BAD_ARG;
   }
-  if (rc != BONSAI_CUDA_OK) return rc;
-  attn_merge_kernel<<<dim3(nq, batch), hd, 0, stream>>>(ws_acc, ws_ml, nsplit, hd, out);
-  return launch_status();
 }
 
 }  // extern "C"

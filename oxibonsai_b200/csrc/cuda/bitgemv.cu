@@ -118,6 +118,158 @@ __global__ void __launch_bounds__(256) bitgemv_kernel(const uint4* __restrict__ 
   }
 }
 
+// Fast variant: activations held as half2 pairs, packed half-precision FMAs.  In the planar-SM word
+// the sign and magnitude bits of weight a_p sit two bits apart (4p+3, 4p+1), exactly the spacing of
+// the sign bit (15) and exponent bit 13 of a half, whose lone value is 2^-7.  One shift and one
+// mask therefore turn a word into the half2 (a_p, a_{p+4}) = (+-2^-7 or 0, +-2^-7 or 0); the same
+// holds for (b_p, b_{p+4}) one bit lower.  Three instructions (shift, mask, HFMA2) handle two
+// weights.  A 64-input chunk is accumulated in four half2 chains of depth eight, widened to f32
+// once per chunk, scaled by the group scale times 2^7 and reduced across chunks in f32.
+template <int R>
+__global__ void __launch_bounds__(256, 2) bitgemv_h2_kernel(const uint4* __restrict__ codes, const __half* __restrict__ scales,
+                                                           const float* __restrict__ x, const float* __restrict__ norm_w,
+                                                           float eps, float* __restrict__ out, const float* __restrict__ residual,
+                                                           int N, int K, int epi) {
+  __shared__ float red[R][256];
+  __shared__ float s32[32];
+  const int t = threadIdx.x;
+  const int cpr = K >> 6;
+  const int G = 256 / cpr;
+  const int g = t / cpr, c = t - g * cpr;
+  const bool active = g < G;
+  const int rows_per_tile = G * R;
+  const int ntiles = (N + rows_per_tile - 1) / rows_per_tile;
+  const int nsc = K >> 7;
+  const int lane = t & 31, warp = t >> 5;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the first tile's weights do not depend on the previous kernel: fetch them before waiting
+  uint4 q[R];
+  float d[R];
+  {
+    const int row_base = blockIdx.x * rows_per_tile + g * R;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      int row = row_base + i;
+      bool ok = active && row < N && blockIdx.x < ntiles;
+      q[i] = ok ? __ldg(codes + (size_t)row * cpr + c) : make_uint4(0, 0, 0, 0);
+      d[i] = ok ? __half2float(scales[(size_t)row * nsc + (c >> 1)]) : 0.0f;
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // activations: 64 floats -> 32 half2 in the pairing order of the packed words
+  __half2 xh[32];
+  {
+    float xr[64];
+    if (active) {
+      const float4* xp = reinterpret_cast<const float4*>(x + (size_t)c * 64);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float4 v = xp[j];
+        xr[4 * j] = v.x; xr[4 * j + 1] = v.y; xr[4 * j + 2] = v.z; xr[4 * j + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) xr[j] = 0.0f;
+    }
+    if (norm_w != nullptr) {
+      float ss = 0.0f;
+      if (active && g == 0) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) ss += xr[j] * xr[j];
+      }
+      ss = block_sum(ss, s32);
+      float inv = 1.0f / sqrtf(ss / (float)K + eps);
+      if (active) {
+        const float4* wp = reinterpret_cast<const float4*>(norm_w + (size_t)c * 64);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float4 w = wp[j];
+          xr[4 * j] = w.x * xr[4 * j] * inv;
+          xr[4 * j + 1] = w.y * xr[4 * j + 1] * inv;
+          xr[4 * j + 2] = w.z * xr[4 * j + 2] * inv;
+          xr[4 * j + 3] = w.w * xr[4 * j + 3] * inv;
+        }
+      }
+    }
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        xh[wd * 8 + p] = __floats2half2_rn(xr[wd * 16 + p], xr[wd * 16 + p + 4]);           // (a_p, a_{p+4})
+        xh[wd * 8 + 4 + p] = __floats2half2_rn(xr[wd * 16 + 8 + p], xr[wd * 16 + 12 + p]);  // (b_p, b_{p+4})
+      }
+    }
+  }
+
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    // issue the next tile's loads before consuming this one
+    uint4 qn[R];
+    float dn[R];
+    {
+      const int ntile = tile + gridDim.x;
+      const int row_base = ntile * rows_per_tile + g * R;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        int row = row_base + i;
+        bool ok = active && ntile < ntiles && row < N;
+        qn[i] = ok ? __ldg(codes + (size_t)row * cpr + c) : make_uint4(0, 0, 0, 0);
+        dn[i] = ok ? __half2float(scales[(size_t)row * nsc + (c >> 1)]) : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const uint32_t w4[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+      __half2 a0 = __float2half2_rn(0.0f), a1 = a0, a2 = a0, a3 = a0;
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        const uint32_t w = w4[wd];
+        uint32_t m;
+        m = (w << 12) & 0xA000A000u; a0 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 0], a0);
+        m = (w << 8) & 0xA000A000u;  a1 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 1], a1);
+        m = (w << 4) & 0xA000A000u;  a2 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 2], a2);
+        m = w & 0xA000A000u;         a3 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 3], a3);
+        m = (w << 13) & 0xA000A000u; a0 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 4], a0);
+        m = (w << 9) & 0xA000A000u;  a1 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 5], a1);
+        m = (w << 5) & 0xA000A000u;  a2 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 6], a2);
+        m = (w << 1) & 0xA000A000u;  a3 = __hfma2(*reinterpret_cast<__half2*>(&m), xh[wd * 8 + 7], a3);
+      }
+      float2 f0 = __half22float2(a0), f1 = __half22float2(a1), f2 = __half22float2(a2), f3 = __half22float2(a3);
+      float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+      red[i][t] = s * d[i];
+    }
+    __syncthreads();
+    if (epi == EPI_SWIGLU) {
+      for (int pr = warp; pr < rows_per_tile / 2; pr += 8) {
+        int rr = pr * 2;
+        int gg = rr / R, ii = rr - gg * R;
+        float a = 0.0f, b = 0.0f;
+        for (int j = lane; j < cpr; j += 32) {
+          a += red[ii][gg * cpr + j];
+          b += red[ii + 1][gg * cpr + j];
+        }
+        a = warp_sum(a) * 128.0f;
+        b = warp_sum(b) * 128.0f;
+        int row = tile * rows_per_tile + rr;
+        if (lane == 0 && row + 1 < N) out[row >> 1] = a / (1.0f + __expf(-a)) * b;
+      }
+    } else {
+      for (int rr = warp; rr < rows_per_tile; rr += 8) {
+        int gg = rr / R, ii = rr - gg * R;
+        float a = 0.0f;
+        for (int j = lane; j < cpr; j += 32) a += red[ii][gg * cpr + j];
+        a = warp_sum(a) * 128.0f;
+        int row = tile * rows_per_tile + rr;
+        if (lane == 0 && row < N) out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < R; ++i) { q[i] = qn[i]; d[i] = dn[i]; }
+  }
+}
+
 // f16 row-major matrix [N][K] times f32 x, optional fused RMSNorm prologue.  Thread t owns the
 // 8-input chunks t, t+256, ... (CH of them) of x.
 template <int CH, int R>
@@ -233,6 +385,29 @@ int bonsai_bitgemv(const void* codes, const void* scales, const float* x, const 
     bitgemv_kernel<4><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi);
   }
   return launch_status();
+}
+
+// Same contract as bonsai_bitgemv, computed with packed half-precision FMAs (activations rounded to
+// f16, 8-deep f16 accumulation chains widened to f32).  Launched with programmatic dependent launch.
+int bonsai_bitgemv_h2(const void* codes, const void* scales, const float* x, const float* norm_w, float eps, float* out,
+                      const float* residual, int N, int K, int epi, cudaStream_t stream) {
+  using namespace bonsai;
+  if (K % 128 != 0 || K < 128 || K > 16384 || N <= 0 || epi < 0 || epi > 2) return BONSAI_CUDA_BAD_ARG;
+  if (epi == EPI_RESID && residual == nullptr) return BONSAI_CUDA_BAD_ARG;
+  int cpr = K / 64, G = 256 / cpr;
+  int tiles8 = (N + G * 8 - 1) / (G * 8);
+  cudaError_t e;
+  if (tiles8 >= 2 * 148) {
+    int grid = tiles8 < 148 * 2 ? tiles8 : 148 * 2;
+    e = launch_pdl(bitgemv_h2_kernel<8>, dim3(grid), dim3(256), 0, stream, (const uint4*)codes, (const __half*)scales, x, norm_w, eps,
+                   out, residual, N, K, epi);
+  } else {
+    int tiles4 = (N + G * 4 - 1) / (G * 4);
+    int grid = tiles4 < 148 * 2 ? tiles4 : 148 * 2;
+    e = launch_pdl(bitgemv_h2_kernel<4>, dim3(grid), dim3(256), 0, stream, (const uint4*)codes, (const __half*)scales, x, norm_w, eps,
+                   out, residual, N, K, epi);
+  }
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 // out[N] = W x for an f16 row-major matrix (LM head); optional fused RMSNorm.  K % 8 == 0, K <= 8192.

@@ -59,6 +59,24 @@ __device__ __forceinline__ float dot_word16(uint32_t w, const float* x) {
   return acc;
 }
 
+// Launch with programmatic dependent launch enabled: the kernel may start while its predecessor in
+// the stream is still running and must execute griddepcontrol.wait before touching anything the
+// predecessor writes (or writing anything it reads).
+template <typename Kern, typename... Args>
+static inline cudaError_t launch_pdl(Kern kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;

@@ -23,7 +23,8 @@ int bonsai_embed_f16(const void*, const int*, float*, int, int, cudaStream_t);
 int bonsai_qknorm_rope_kvstore(const float*, int, const float*, const float*, float, const float*, const float*, const int*,
                                const int*, int, float*, int, int, int, int, int, int, void*, void*, float*, float*, cudaStream_t);
 int bonsai_attn_decode(const float*, const int*, const int*, int, int, int, int, int, int, int, const void*, const void*,
-                       const float*, const float*, int, float*, float*, float*, int, cudaStream_t);
+                       const float*, const float*, int, float*, float*, int*, float*, int, cudaStream_t);
+int bonsai_bitgemv_h2(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
                   const uint32_t*, int, cudaStream_t);
 int bonsai_allreduce_residual(void* comm, const float* partial, float* h, int n, int batch, cudaStream_t stream);
@@ -40,11 +41,11 @@ enum GlobalPtr {
 };
 enum IntCfg {
   IC_HIDDEN = 0, IC_INTER_LOCAL, IC_LAYERS, IC_HEADS_LOCAL, IC_KV_HEADS_LOCAL, IC_HEAD_DIM, IC_VOCAB, IC_LM_ROWS_LOCAL,
-  IC_KVT, IC_PAGE_SIZE, IC_MAX_PAGES, IC_NSPLIT, IC_TP_SIZE, IC_TP_RANK, IC_COUNT
+  IC_KVT, IC_PAGE_SIZE, IC_MAX_PAGES, IC_NSPLIT, IC_TP_SIZE, IC_TP_RANK, IC_FAST, IC_COUNT
 };
 enum StepPtr {
   SP_TOKENS = 0, SP_POSITIONS, SP_BLOCK_TABLE, SP_H, SP_QKV, SP_Q, SP_ATTN, SP_ACT, SP_LOGITS, SP_WS_ACC, SP_WS_ML,
-  SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_COUNT
+  SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_ATTN_COUNTERS, SP_COUNT
 };
 
 struct Runner {
@@ -66,6 +67,7 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
   const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
   const bool tp = r.ic[IC_TP_SIZE] > 1;
+  auto gemv = r.ic[IC_FAST] ? bonsai_bitgemv_h2 : bonsai_bitgemv;
   int* tokens = P<int>(sp[SP_TOKENS]);
   int* positions = P<int>(sp[SP_POSITIONS]);
   const int* bt = P<int>(sp[SP_BLOCK_TABLE]);
@@ -82,7 +84,7 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     for (int b = 0; b < batch; ++b)
-      RC(bonsai_bitgemv(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]),
+      RC(gemv(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]),
                         r.eps, qkv + (size_t)b * qkv_n, nullptr, qkv_n, hidden, 0, st));
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
                                   P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
@@ -90,27 +92,27 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
                                   P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
     RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
                           P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
-                          r.ic[IC_NSPLIT], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), attn, 0, st));
+                          r.ic[IC_NSPLIT], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
     if (!tp) {
       for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
+        RC(gemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
                           h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, 1, st));
     } else {
       for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
+        RC(gemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
                           partial + (size_t)b * hidden, nullptr, hidden, qd, 0, st));
       RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
     }
     for (int b = 0; b < batch; ++b)
-      RC(bonsai_bitgemv(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), r.eps,
+      RC(gemv(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), r.eps,
                         act + (size_t)b * inter, nullptr, 2 * inter, hidden, 2, st));
     if (!tp) {
       for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
+        RC(gemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
                           h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, 1, st));
     } else {
       for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
+        RC(gemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
                           partial + (size_t)b * hidden, nullptr, hidden, inter, 0, st));
       RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
     }
@@ -148,6 +150,7 @@ void* bonsai_runner_create(const int* icfg, float eps, const uint64_t* global_pt
 void bonsai_runner_destroy(void* r) { delete static_cast<bonsai::Runner*>(r); }
 void bonsai_runner_set_comm(void* r, void* comm) { static_cast<bonsai::Runner*>(r)->comm = comm; }
 void bonsai_runner_set_nsplit(void* r, int nsplit) { static_cast<bonsai::Runner*>(r)->ic[bonsai::IC_NSPLIT] = nsplit; }
+void bonsai_runner_set_fast(void* r, int fast) { static_cast<bonsai::Runner*>(r)->ic[bonsai::IC_FAST] = fast; }
 int bonsai_runner_layer_ptr_count() { return bonsai::LP_COUNT; }
 int bonsai_runner_step_ptr_count() { return bonsai::SP_COUNT; }
 

@@ -148,8 +148,8 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __res
       if (t < o) {
         float ov = s_val[t + o];
         int oi = s_idx[t + o];
-        // ranges are ordered by thread, so the right half always holds later indices
-        if (oi >= 0 && (s_idx[t] < 0 || !(ov < s_val[t]))) { s_val[t] = ov; s_idx[t] = oi; }
+        // equal values: the larger index wins (last maximal index overall)
+        if (oi >= 0 && (s_idx[t] < 0 || ov > s_val[t] || (ov == s_val[t] && oi > s_idx[t]))) { s_val[t] = ov; s_idx[t] = oi; }
       }
       __syncthreads();
     }

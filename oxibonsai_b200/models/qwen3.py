@@ -194,14 +194,17 @@ class PagedKvCache:
 class Qwen3Runner:
     """Owns the activation buffers and the native step runner for a fixed maximum batch."""
 
-    def __init__(self, weights: Qwen3Weights, kv: PagedKvCache, max_batch: int, max_seq: int, nsplit: int | None = None):
+    def __init__(self, weights: Qwen3Weights, kv: PagedKvCache, max_batch: int, max_seq: int, nsplit: int | None = None,
+                 fast: bool = True):
         self.w, self.kv, self.max_batch, self.max_seq = weights, kv, max_batch, max_seq
         cfg, dev = weights.cfg, weights.device
         self.cfg, self.device = cfg, dev
         hd = cfg.head_dim
         nq, nkv = weights.heads_local, weights.kv_heads_local
         self.max_pages = (max_seq + kv.page_size - 1) // kv.page_size
-        self.nsplit = nsplit or max(1, min(32, (max_seq + 255) // 256))
+        # enough splits to spread one sequence's heads over the GPU; empty splits cost almost nothing
+        self.nsplit = nsplit or max(1, min(32, 148 // max(1, nkv)))
+        self.fast = fast
         B = max_batch
         f32 = dict(dtype=torch.float32, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -222,6 +225,7 @@ class Qwen3Runner:
         self.topps = torch.ones(B, **f32)
         self.rng = torch.full((B,), 42, dtype=torch.int64, device=dev)
         self.out_tokens = torch.zeros(B, **i32)
+        self.attn_counters = torch.zeros(B * max(1, nkv), **i32)
         cos, sin = rope_table(hd, max_seq, cfg.rope_base)
         self.rope_cos = torch.from_numpy(cos).to(dev)
         self.rope_sin = torch.from_numpy(sin).to(dev)
@@ -232,8 +236,8 @@ class Qwen3Runner:
         lib = K.lib()
         w, kv, cfg = self.w, self.kv, self.cfg
         nlp, nsp = lib.bonsai_runner_layer_ptr_count(), lib.bonsai_runner_step_ptr_count()
-        icfg = (C.c_int * 14)(cfg.hidden, w.inter_local, cfg.layers, w.heads_local, w.kv_heads_local, cfg.head_dim, cfg.vocab,
-                              w.lm_head.shape[0], kv.kvt, kv.page_size, self.max_pages, self.nsplit, w.tp_size, w.tp_rank)
+        icfg = (C.c_int * 15)(cfg.hidden, w.inter_local, cfg.layers, w.heads_local, w.kv_heads_local, cfg.head_dim, cfg.vocab,
+                              w.lm_head.shape[0], kv.kvt, kv.page_size, self.max_pages, self.nsplit, w.tp_size, w.tp_rank, int(self.fast))
         gp = (C.c_uint64 * 5)(w.embd.data_ptr(), w.lm_head.data_ptr(), w.out_norm.data_ptr(), self.rope_cos.data_ptr(), self.rope_sin.data_ptr())
         lp = (C.c_uint64 * (nlp * cfg.layers))()
         for l, lw in enumerate(w.layers):
@@ -248,7 +252,7 @@ class Qwen3Runner:
                 lp[l * nlp + i] = v
         self._native = lib.bonsai_runner_create(icfg, cfg.eps, gp, lp)
         sp = [self.tokens, self.positions, self.block_table, self.h, self.qkv, self.q, self.attn, self.act, self.logits, self.ws_acc,
-              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None]
+              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None, self.attn_counters]
         assert len(sp) == nsp
         self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
         self.launches_per_step = None
@@ -266,7 +270,7 @@ class Qwen3Runner:
 
     def kernel_launches(self, batch: int, sample: bool = True) -> int:
         """Number of kernel launches in one decode step (each is one of this library's kernels)."""
-        per_layer = 4 * batch + 3 + (2 if self.w.tp_size > 1 else 0)
+        per_layer = 4 * batch + 2 + (2 if self.w.tp_size > 1 else 0)
         return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0)
 
     def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:

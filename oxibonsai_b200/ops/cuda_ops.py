@@ -20,20 +20,22 @@ _SIG = {
     "bonsai_repack_planar": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "bonsai_planar_to_f32": [_vp, _vp, _i, _i, _vp, _vp],
     "bonsai_bitgemv": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
+    "bonsai_bitgemv_h2": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_f16gemv": [_vp, _vp, _vp, _f, _vp, _i, _i, _vp],
     "bonsai_embed_f16": [_vp, _vp, _vp, _i, _i, _vp],
     "bonsai_qknorm_rope_kvstore": [_vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
-    "bonsai_attn_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp],
+    "bonsai_attn_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp],
     "bonsai_runner_create": [_vp, _f, _vp, _vp],
     "bonsai_runner_destroy": [_vp],
     "bonsai_runner_set_comm": [_vp, _vp],
     "bonsai_runner_set_nsplit": [_vp, _i],
+    "bonsai_runner_set_fast": [_vp, _i],
     "bonsai_runner_layer_ptr_count": [],
     "bonsai_runner_step_ptr_count": [],
     "bonsai_runner_decode_step": [_vp, _vp, _i, _i, _i, _vp],
 }
-_RES = {"bonsai_runner_create": _vp, "bonsai_runner_destroy": None, "bonsai_runner_set_comm": None, "bonsai_runner_set_nsplit": None}
+_RES = {"bonsai_runner_create": _vp, "bonsai_runner_destroy": None, "bonsai_runner_set_comm": None, "bonsai_runner_set_nsplit": None, "bonsai_runner_set_fast": None}
 _lib = None
 
 
@@ -112,13 +114,15 @@ class PlanarWeight:
 
 
 def bitgemv(w: PlanarWeight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
-            residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out = W x (f32 exact path).  ``epi``: store / residual add / SwiGLU over interleaved gate-up rows."""
+            residual: torch.Tensor | None = None, out: torch.Tensor | None = None, fast: bool = False) -> torch.Tensor:
+    """out = W x.  ``fast=False``: exact f32 path; ``fast=True``: packed-half path (f16 activations).
+    ``epi``: store / residual add / SwiGLU over interleaved gate-up rows."""
     _f32c(x)
     n_out = w.n // 2 if epi == EPI_SWIGLU else w.n
     if out is None:
         out = torch.empty(n_out, dtype=torch.float32, device=x.device)
-    check(lib().bonsai_bitgemv(w.codes.data_ptr(), w.scales.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual),
+    fn = lib().bonsai_bitgemv_h2 if fast else lib().bonsai_bitgemv
+    check(fn(w.codes.data_ptr(), w.scales.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual),
                                w.n, w.k, epi, stream()), "bitgemv")
     return out
 
@@ -147,11 +151,13 @@ def attn_decode(q, positions, block_table, nq, nkv, hd, kvt, page_size, kpool, v
     batch = q.shape[0]
     ws_acc = torch.empty((batch, nq, nsplit, hd), dtype=torch.float32, device=q.device)
     ws_ml = torch.empty((batch, nq, nsplit, 2), dtype=torch.float32, device=q.device)
+    counters = torch.zeros(batch * nkv, dtype=torch.int32, device=q.device)
     if out is None:
         out = torch.empty((batch, nq, hd), dtype=torch.float32, device=q.device)
     check(lib().bonsai_attn_decode(q.data_ptr(), positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], batch, nq, nkv, hd,
                                    kvt, page_size, kpool.data_ptr(), vpool.data_ptr(), ptr(kscale), ptr(vscale), nsplit,
-                                   ws_acc.data_ptr(), ws_ml.data_ptr(), out.data_ptr(), extra_len, stream()), "attn_decode")
+                                   ws_acc.data_ptr(), ws_ml.data_ptr(), counters.data_ptr(), out.data_ptr(), extra_len, stream()),
+          "attn_decode")
     return out
 
 
@@ -164,4 +170,122 @@ def sample(logits: torch.Tensor, temps=None, topks=None, topps=None, rng=None, p
     check(lib().bonsai_sample(logits.data_ptr(), batch, vocab, logits.stride(0), ptr(temps), ptr(topks), ptr(topps), ptr(rng),
                               out.data_ptr(), ptr(positions), int(advance and positions is not None), ptr(allow_mask),
                               0 if allow_mask is None else allow_mask.shape[1], stream()), "sample")
+    return out
+
+
+# ---- tensor-core decode path ------------------------------------------------------------------------
+_TC_SIG = {
+    "bonsai_act_prep_fp8": [_vp, _i, _vp, _f, _i, _i, _i, _i, _vp, _vp, _vp],
+    "bonsai_bitgemv_tc": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "bonsai_tc_tile": [_vp, _vp, _vp, _i, _i, _vp, _vp],
+}
+_tc_declared = False
+
+
+def _tc():
+    global _tc_declared
+    l = lib()
+    if not _tc_declared:
+        declare(_TC_SIG)
+        _tc_declared = True
+    return l
+
+
+def tc_columns(tokens: int, nterms: int) -> int:
+    """MMA column count (16 / 32 / 64) for ``tokens`` activations split into ``nterms`` fp8 terms."""
+    need = tokens * nterms
+    for n in (16, 32, 64):
+        if need <= n:
+            return n
+    raise ValueError(f"{tokens} tokens x {nterms} terms exceeds the 64 columns of the decode tensor-core kernel")
+
+
+class TcActivations:
+    """fp8-term operand of ``bitgemv_tc``: swizzled tiles [K/128][ncols][128 B] plus per-column factors."""
+
+    def __init__(self, k: int, ncols: int, device):
+        self.k, self.ncols = k, ncols
+        self.xq = torch.zeros((k // 128) * ncols * 128, dtype=torch.uint8, device=device)
+        self.colscale = torch.zeros(ncols, dtype=torch.float32, device=device)
+        self.tokens = 0
+        self.nterms = 0
+
+
+def act_prep_fp8(x: torch.Tensor, nterms: int = 3, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
+                 out: TcActivations | None = None) -> TcActivations:
+    """Splits rows of ``x`` ([T, K] f32, optionally RMS-normalised first) into e4m3 terms for the tensor cores."""
+    x2 = x if x.dim() == 2 else x.view(1, -1)
+    T, Kd = x2.shape
+    ncols = tc_columns(T, nterms)
+    if out is None:
+        out = TcActivations(Kd, ncols, x.device)
+    assert out.k == Kd and out.ncols >= T * nterms
+    check(_tc().bonsai_act_prep_fp8(x2.data_ptr(), x2.stride(0), ptr(norm_w), eps, T, Kd, nterms, out.ncols, out.xq.data_ptr(),
+                                    out.colscale.data_ptr(), stream()), "act_prep_fp8")
+    out.tokens, out.nterms = T, nterms
+    return out
+
+
+class TcWorkspace:
+    """Split-K scratch: partial sums, per-tile arrival counters and the error word of the tensor-core kernels."""
+
+    def __init__(self, device, max_partial_floats: int = 1 << 22, max_tiles: int = 4096):
+        self.partial = torch.empty(max_partial_floats, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(max_tiles, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def check(self) -> None:
+        s = int(self.status.item())
+        if s != 0:
+            self.status.zero_()
+            raise CudaKernelError(f"tensor-core kernel reported status {s} (a bounded wait expired)")
+
+
+def pick_ksplit(n_rows: int, k: int, ncols: int, sms: int = 148) -> int:
+    """K-split for the persistent tensor-core GEMV: the activation slab must fit in shared memory and the
+    busiest CTA column should carry as few (tile, group) steps as possible."""
+    tiles = (n_rows + 127) // 128
+    ngroups = k // 128
+    max_b_bytes = 88 * 1024
+    best, best_cost = None, None
+    for s in (1, 2, 3, 4, 6, 8, 12, 16):
+        if s > ngroups or s > sms:
+            continue
+        gps = -(-ngroups // s)
+        if gps * ncols * 128 > max_b_bytes:
+            continue
+        columns = min(sms // s, tiles)
+        steps = -(-tiles // columns) * gps
+        cost = steps + (3 if s > 1 else 0) * -(-tiles // columns)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    if best is None:
+        raise ValueError(f"no K-split fits: K={k}, columns={ncols}")
+    return best
+
+
+def bitgemv_tc(w: PlanarWeight, ws: TcWorkspace, act: TcActivations | None = None, x: torch.Tensor | None = None, nterms: int = 3,
+               norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE, residual: torch.Tensor | None = None,
+               out: torch.Tensor | None = None, ksplit: int | None = None, sms: int = 148) -> torch.Tensor:
+    """out[T, N] = epilogue(W x) on the tensor cores.
+
+    Either pass ``act`` (from :func:`act_prep_fp8`) or ``x`` ([T, K] f32 with T <= 4), in which case the fp8-term
+    operand - and the RMSNorm when ``norm_w`` is given - is built inside the kernel.
+    """
+    if act is not None:
+        T, nt, ncols = act.tokens, act.nterms, act.ncols
+        xq, cs, xp, xld = act.xq.data_ptr(), act.colscale.data_ptr(), None, 0
+    else:
+        x2 = x if x.dim() == 2 else x.view(1, -1)
+        T, nt = x2.shape[0], nterms
+        ncols = tc_columns(T, nt)
+        xq, cs, xp, xld = None, None, x2.data_ptr(), x2.stride(0)
+    n_out = w.n // 2 if epi == EPI_SWIGLU else w.n
+    if out is None:
+        out = torch.empty((T, n_out), dtype=torch.float32, device=w.codes.device)
+    ks = ksplit or pick_ksplit(w.n, w.k, ncols, sms)
+    assert ks * T * w.n <= ws.partial.numel() and (w.n + 127) // 128 <= ws.counters.numel()
+    check(_tc().bonsai_bitgemv_tc(w.codes.data_ptr(), w.scales.data_ptr(), xq, cs, xp, xld, ptr(norm_w), eps, out.data_ptr(),
+                                  ptr(residual), ws.partial.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr(), w.n, w.k, T,
+                                  nt, ncols, ks, epi, out.stride(0) if out.dim() == 2 else n_out, sms, stream()), "bitgemv_tc")
     return out

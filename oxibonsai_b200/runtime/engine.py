@@ -47,7 +47,7 @@ class InferenceEngine:
 
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
-                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True):
+                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("InferenceEngine needs a CUDA device; use oxibonsai_b200.core.Oracle for the CPU path")
         self.device = torch.device(device)
@@ -65,7 +65,9 @@ class InferenceEngine:
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
                                self.kvt, self.device)
-        self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len)
+        # exact = f32 activations end to end (the token-stream gate); default: exact only with an f32 KV cache
+        self.exact = (self.kvt == K.KV_F32) if exact is None else bool(exact)
+        self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact)
         self.load_seconds = time.perf_counter() - t0
         # pinned staging for the per-step host <-> device traffic
         self._tok_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
@@ -87,6 +89,7 @@ class InferenceEngine:
         self._set_sampling(0, SamplingPreset.GREEDY.params())
         self._upload(0, 0, 0)
         self.runner.step_eager(1, sample=True)
+        torch.cuda.synchronize(self.device)
         self._upload(0, 0, 1)
         self.runner.step(1, sample=True)
         torch.cuda.synchronize(self.device)
@@ -125,13 +128,17 @@ class InferenceEngine:
     def prefill(self, prompt: Sequence[int], slot: int = 0) -> None:
         """Runs the prompt through the model, leaving logits of the last prompt token in the runner."""
         n = len(prompt)
-        for i, tok in enumerate(prompt):
-            self._upload(slot, int(tok), i)
-            last = i == n - 1
-            if slot == 0:
-                self.runner.step_eager(1, sample=False, lm_head=last)
-            else:
-                raise NotImplementedError("token-by-token prefill is wired for slot 0; batched prefill uses the prefill kernels")
+        if slot != 0:
+            raise NotImplementedError("token-by-token prefill is wired for slot 0; batched prefill uses the prefill kernels")
+        # one upload for the whole prompt; per-token feeds are device-to-device and stream ordered, so
+        # no host buffer is rewritten while a copy that reads it is still queued
+        toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        pos = torch.arange(n, dtype=torch.int32, device=self.device)
+        r = self.runner
+        for i in range(n):
+            r.tokens[slot: slot + 1].copy_(toks[i: i + 1], non_blocking=True)
+            r.positions[slot: slot + 1].copy_(pos[i: i + 1], non_blocking=True)
+            r.step_eager(1, sample=False, lm_head=(i == n - 1))
 
     def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
                         stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None) -> Iterator[int]:
