@@ -363,9 +363,25 @@ __global__ void embed_f16_kernel(const __half* __restrict__ table, const int* __
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) h[i] = __half2float(row[i]);
 }
 
+// h[t][0..hidden) = f16 embedding row of tokens[t], one block per token.
+__global__ void embed_rows_f16_kernel(const __half* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ h,
+                                      int hidden, int vocab) {
+  int tok = tokens[blockIdx.x];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const __half* row = table + (size_t)tok * hidden;
+  float* o = h + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = __half2float(row[i]);
+}
+
 }  // namespace bonsai
 
 extern "C" {
+
+int bonsai_embed_rows_f16(const void* table, const int* tokens, float* h, int T, int hidden, int vocab, cudaStream_t stream) {
+  bonsai::embed_rows_f16_kernel<<<T, 256, 0, stream>>>((const __half*)table, tokens, h, hidden, vocab);
+  return bonsai::launch_status();
+}
+
 
 // out[N] (or out[N/2] for epi = 2 with gate/up rows interleaved) = W x.  x is f32[K]; when norm_w is
 // non-null x is first RMS-normalised with that weight.  K must be a multiple of 128 and <= 16384.

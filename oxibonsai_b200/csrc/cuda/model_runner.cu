@@ -28,6 +28,12 @@ int bonsai_bitgemv_h2(const void*, const void*, const float*, const float*, floa
 int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
                   const uint32_t*, int, cudaStream_t);
 int bonsai_allreduce_residual(void* comm, const float* partial, float* h, int n, int batch, cudaStream_t stream);
+int bonsai_bitgemm_prefill(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int, int,
+                           cudaStream_t);
+int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
+int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
+                        const float*, void*, int, cudaStream_t);
+int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
 }
 
 namespace bonsai {
@@ -130,6 +136,63 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   return 0;
 }
 
+enum PrefillPtr { PP_TOKENS = 0, PP_POSITIONS, PP_H, PP_XN, PP_QKV, PP_Q, PP_ATTN, PP_ACT, PP_STATUS, PP_COUNT };
+
+// One chunk of T prompt tokens of the sequence in `slot`, starting at position pos0: batched
+// embed -> per layer { norm -> QKV GEMM -> QK-norm+RoPE+KV append -> causal attention over the
+// paged cache -> O GEMM + residual -> norm -> gate/up GEMM + SwiGLU -> down GEMM + residual }.
+// With want_logits the last token's hidden state goes through the final norm and LM head into
+// the slot's logits row.
+static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int T, int pos0, int slot, int want_logits,
+                         cudaStream_t st) {
+  const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
+  const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
+  const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
+  if (r.ic[IC_TP_SIZE] > 1) return BONSAI_CUDA_BAD_ARG;  // tensor-parallel prefill runs through the decode path
+  const int sms = 148;
+  const int* tokens = P<int>(pp[PP_TOKENS]);
+  const int* positions = P<int>(pp[PP_POSITIONS]);
+  float* h = P<float>(pp[PP_H]);
+  void* xn = P<void>(pp[PP_XN]);
+  float* qkv = P<float>(pp[PP_QKV]);
+  float* q = P<float>(pp[PP_Q]);
+  void* attn = P<void>(pp[PP_ATTN]);
+  void* act = P<void>(pp[PP_ACT]);
+  int* status = P<int>(pp[PP_STATUS]);
+  const int xn_ld = hidden > qd ? hidden : qd;
+  const int* bt = P<int>(sp[SP_BLOCK_TABLE]) + (size_t)slot * r.ic[IC_MAX_PAGES];
+
+  RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, T, hidden, vocab, st));
+  for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
+    const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, T, hidden, xn, xn_ld, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
+                              hidden, T, 0, qkv_n, sms, st));
+    // every row of the chunk uses the same page list: a block-table stride of zero
+    RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
+                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, 0, q, T, nq, nkv, hd, r.ic[IC_KVT],
+                                  r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]),
+                                  P<float>(lp[LP_VSCALE]), st));
+    RC(bonsai_attn_prefill(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
+                           P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
+                              hidden, sms, st));
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
+                              hidden, T, 2, inter, sms, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+                              T, 1, hidden, sms, st));
+  }
+  if (want_logits) {
+    float* hs = P<float>(sp[SP_H]) + (size_t)slot * hidden;
+    if (cudaMemcpyAsync(hs, h + (size_t)(T - 1) * hidden, (size_t)hidden * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+      return BONSAI_CUDA_LAUNCH_FAILED;
+    RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, P<float>(sp[SP_LOGITS]) + (size_t)slot * vocab,
+                      lm_rows, hidden, st));
+  }
+  return 0;
+}
+
 }  // namespace bonsai
 
 extern "C" {
@@ -153,6 +216,12 @@ void bonsai_runner_set_nsplit(void* r, int nsplit) { static_cast<bonsai::Runner*
 void bonsai_runner_set_fast(void* r, int fast) { static_cast<bonsai::Runner*>(r)->ic[bonsai::IC_FAST] = fast; }
 int bonsai_runner_layer_ptr_count() { return bonsai::LP_COUNT; }
 int bonsai_runner_step_ptr_count() { return bonsai::SP_COUNT; }
+int bonsai_runner_prefill_ptr_count() { return bonsai::PP_COUNT; }
+
+int bonsai_runner_prefill_chunk(void* r, const uint64_t* step_ptrs, const uint64_t* prefill_ptrs, int T, int pos0, int slot,
+                                int want_logits, cudaStream_t stream) {
+  return bonsai::prefill_chunk(*static_cast<bonsai::Runner*>(r), step_ptrs, prefill_ptrs, T, pos0, slot, want_logits, stream);
+}
 
 int bonsai_runner_decode_step(void* r, const uint64_t* step_ptrs, int batch, int flags, int mask_words, cudaStream_t stream) {
   return bonsai::decode_step(*static_cast<bonsai::Runner*>(r), step_ptrs, batch, flags, mask_words, stream);

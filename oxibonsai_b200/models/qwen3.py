@@ -265,6 +265,46 @@ class Qwen3Runner:
         except Exception:
             pass
 
+    # ---- prefill (tcgen05 GEMMs + causal paged attention over a chunk of prompt tokens) ----
+    def _prefill_buffers(self, chunk: int):
+        if getattr(self, "_pf", None) is not None and self._pf["chunk"] >= chunk:
+            return self._pf
+        cfg, w, dev = self.cfg, self.w, self.device
+        hd, nq, nkv = cfg.head_dim, w.heads_local, w.kv_heads_local
+        qd = nq * hd
+        f32, f16, i32 = (dict(dtype=d, device=dev) for d in (torch.float32, torch.float16, torch.int32))
+        b = {"chunk": chunk,
+             "tokens": torch.zeros(chunk, **i32), "positions": torch.zeros(chunk, **i32),
+             "h": torch.zeros((chunk, cfg.hidden), **f32), "xn": torch.zeros((chunk, max(cfg.hidden, qd)), **f16),
+             "qkv": torch.zeros((chunk, (nq + 2 * nkv) * hd), **f32), "q": torch.zeros((chunk, nq, hd), **f32),
+             "attn": torch.zeros((chunk, qd), **f16), "act": torch.zeros((chunk, w.inter_local), **f16),
+             "status": torch.zeros(1, **i32)}
+        order = ["tokens", "positions", "h", "xn", "qkv", "q", "attn", "act", "status"]
+        assert len(order) == K._pf().bonsai_runner_prefill_ptr_count()
+        b["ptrs"] = (C.c_uint64 * len(order))(*[b[k].data_ptr() for k in order])
+        self._pf = b
+        return b
+
+    def prefill(self, tokens: torch.Tensor, slot: int, pos0: int = 0, chunk: int = 1024) -> None:
+        """Runs prompt ``tokens`` (int32 device tensor) of the sequence in ``slot`` starting at position ``pos0``;
+        leaves the logits of the last token in ``self.logits[slot]``."""
+        n = tokens.numel()
+        b = self._prefill_buffers(min(chunk, max(n, 1)))
+        lib = K._pf()
+        done = 0
+        while done < n:
+            T = min(b["chunk"], n - done)
+            b["tokens"][:T].copy_(tokens[done:done + T], non_blocking=True)
+            torch.arange(pos0 + done, pos0 + done + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
+            last = done + T == n
+            K.check(lib.bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0 + done, slot, int(last), K.stream()),
+                    "prefill_chunk")
+            done += T
+
+    def prefill_launches(self, n_tokens: int, chunk: int = 1024) -> int:
+        chunks = -(-n_tokens // chunk)
+        return chunks * (1 + 8 * self.cfg.layers) + 2
+
     def set_comm(self, comm_handle: int) -> None:
         K.lib().bonsai_runner_set_comm(self._native, comm_handle)
 

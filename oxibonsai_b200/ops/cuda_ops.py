@@ -289,3 +289,69 @@ def bitgemv_tc(w: PlanarWeight, ws: TcWorkspace, act: TcActivations | None = Non
                                   ptr(residual), ws.partial.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr(), w.n, w.k, T,
                                   nt, ncols, ks, epi, out.stride(0) if out.dim() == 2 else n_out, sms, stream()), "bitgemv_tc")
     return out
+
+
+# ---- prefill path -------------------------------------------------------------------------------------
+_PF_SIG = {
+    "bonsai_bitgemm_prefill": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _vp],
+    "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+    "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "bonsai_runner_prefill_ptr_count": [],
+    "bonsai_runner_prefill_chunk": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+}
+_pf_declared = False
+
+
+def _pf():
+    global _pf_declared
+    l = lib()
+    if not _pf_declared:
+        declare(_PF_SIG)
+        _pf_declared = True
+    return l
+
+
+def paired_k_index(k: int, device=None) -> torch.Tensor:
+    """Permutation ``perm`` with ``paired[..., perm[i]] = natural[..., i]`` (the K order of the prefill GEMM operand)."""
+    i = torch.arange(k, device=device)
+    j = i & 15
+    return (i & ~15) | (j & 8) | ((j & 3) * 2 + ((j >> 2) & 1))
+
+
+def norm_to_f16_paired(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """f32 [T, K] -> f16 [T, K] in paired-K order, optionally RMS-normalised first."""
+    T, Kd = x.shape
+    if out is None:
+        out = torch.empty((T, Kd), dtype=torch.float16, device=x.device)
+    check(_pf().bonsai_norm_to_f16_paired(x.data_ptr(), x.stride(0), ptr(norm_w), eps, T, Kd, out.data_ptr(), out.stride(0), stream()),
+          "norm_to_f16_paired")
+    return out
+
+
+def bitgemm_prefill(w: PlanarWeight, x_paired: torch.Tensor, epi: int = 0, residual: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None, status: torch.Tensor | None = None, sms: int = 148) -> torch.Tensor:
+    """out[T, N] = epilogue(W x) on tcgen05.  ``epi``: 0 f32 store, 1 f32 residual add, 2 f16 SwiGLU (paired-K), 3 f16 store."""
+    T = x_paired.shape[0]
+    assert x_paired.dtype == torch.float16 and x_paired.shape[1] == w.k
+    n_out = w.n // 2 if epi == 2 else w.n
+    if out is None:
+        out = torch.empty((T, n_out), dtype=torch.float32 if epi <= 1 else torch.float16, device=x_paired.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=x_paired.device)
+    f32p = out.data_ptr() if epi <= 1 else None
+    f16p = out.data_ptr() if epi >= 2 else None
+    check(_pf().bonsai_bitgemm_prefill(w.codes.data_ptr(), w.scales.data_ptr(), x_paired.data_ptr(), x_paired.stride(0), f32p, ptr(residual),
+                                       f16p, status.data_ptr(), w.n, w.k, T, epi, out.stride(0), sms, stream()), "bitgemm_prefill")
+    return out
+
+
+def attn_prefill(q: torch.Tensor, pos0: int, block_table_row: torch.Tensor, nq, nkv, hd, kvt, page_size, kpool, vpool, kscale=None,
+                 vscale=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of a T-token chunk (q f32 [T, nq, hd]) over the sequence's pages; returns f16 [T, nq*hd] (paired-K)."""
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty((T, nq * hd), dtype=torch.float16, device=q.device)
+    check(_pf().bonsai_attn_prefill(q.data_ptr(), T, pos0, block_table_row.data_ptr(), nq, nkv, hd, kvt, page_size, kpool.data_ptr(),
+                                    vpool.data_ptr(), ptr(kscale), ptr(vscale), out.data_ptr(), out.stride(0), stream()), "attn_prefill")
+    return out

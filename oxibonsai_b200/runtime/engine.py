@@ -74,6 +74,8 @@ class InferenceEngine:
         self._pos_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._out_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._slot_pages: dict[int, list[int]] = {}
+        self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
+        self.prefill_chunk = 1024
         self.last_stats = GenerationStats()
         if warmup:
             self.warmup()
@@ -125,16 +127,24 @@ class InferenceEngine:
         self.runner.positions[slot: slot + 1].copy_(self._pos_host[slot: slot + 1], non_blocking=True)
 
     # ---- generation -------------------------------------------------------------------------------
-    def prefill(self, prompt: Sequence[int], slot: int = 0) -> None:
-        """Runs the prompt through the model, leaving logits of the last prompt token in the runner."""
+    def prefill(self, prompt: Sequence[int], slot: int = 0, pos0: int = 0) -> None:
+        """Runs the prompt through the model, leaving logits of the last prompt token in the runner.
+
+        Prompts of at least ``prefill_min_tokens`` tokens go through the batched prefill kernels (tcgen05 GEMMs and
+        causal attention over the paged cache) in chunks; shorter ones, tensor-parallel ranks and the exact-f32 mode
+        are fed through the decode path one token at a time.
+        """
         n = len(prompt)
-        if slot != 0:
-            raise NotImplementedError("token-by-token prefill is wired for slot 0; batched prefill uses the prefill kernels")
-        # one upload for the whole prompt; per-token feeds are device-to-device and stream ordered, so
-        # no host buffer is rewritten while a copy that reads it is still queued
         toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-        pos = torch.arange(n, dtype=torch.int32, device=self.device)
         r = self.runner
+        if n >= self.prefill_min_tokens and not self.exact and self.weights.tp_size == 1:
+            r.prefill(toks, slot, pos0, self.prefill_chunk)
+            return
+        if slot != 0:
+            raise NotImplementedError("token-by-token prefill is wired for slot 0")
+        # per-token feeds are device-to-device and stream ordered, so no host buffer is rewritten while a copy
+        # that reads it is still queued
+        pos = torch.arange(pos0, pos0 + n, dtype=torch.int32, device=self.device)
         for i in range(n):
             r.tokens[slot: slot + 1].copy_(toks[i: i + 1], non_blocking=True)
             r.positions[slot: slot + 1].copy_(pos[i: i + 1], non_blocking=True)
