@@ -1,0 +1,114 @@
+// Tensor-parallel communication over NVLink peer memory (one process per GPU, symmetric buffers).
+//
+// The reference has no communication backend at all: its "NcclCollectives" and tensor-parallel
+// forward are CPU simulations over threads (crates/oxibonsai-model/src/multi_gpu.rs:159-238,
+// tensor_parallel.rs:338-386).  Here every rank maps every peer's symmetric buffer and kernels
+// exchange data with plain st.global / ld.global to peer addresses plus release/acquire flags:
+//
+//   * fused row-parallel GEMV -> all-reduce + residual (one-shot, push based): the GEMV epilogue
+//     stores each finished row tile into slot [my rank] of every peer's receive area, publishes
+//     an epoch flag per (rank, tile), waits for the same tile of every peer and sums the slots in
+//     rank order - every rank therefore computes bit-identical hidden states;
+//   * logits all-gather for the vocab-parallel LM head, and a two-shot in-place all-reduce for
+//     the prefill GEMM outputs, both bracketed by flag barriers.
+//
+// No TMA load, bulk copy or library call ever takes a peer address: remote data moves only
+// through ordinary loads and stores issued by these kernels.  Every wait is bounded; on expiry
+// the kernel records an error code in *status and carries on without the missing data, so a
+// rank that dies between steps cannot hang its peers' GPUs.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bonsai {
+
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpMaxTiles = 4096;
+constexpr uint32_t kTpSpinLimit = 1u << 22;   // x ~0.2 us per poll: about a second
+
+// Offsets inside every rank's symmetric buffer.
+struct TpLayout {
+  size_t off_tile_flags;   // int [2][kTpMaxRanks][kTpMaxTiles]
+  size_t off_bar_flags;    // int [kTpMaxRanks]
+  size_t off_recv;         // float [2][kTpMaxRanks][recv_elems]
+  size_t off_logits;       // float [max_batch][vocab]
+  size_t off_big;          // float [big_elems]  (prefill partial sums)
+  size_t recv_elems, big_elems, total_bytes;
+};
+
+struct TpComm {
+  int rank, size;
+  uint8_t* peer[kTpMaxRanks];   // peer[r] = rank r's symmetric buffer as mapped in this process
+  TpLayout lay;
+  int* epoch;      // device int: number of fused all-reduces completed (local memory)
+  int* done_ctr;   // device int: CTAs finished in the running fused kernel
+  int* bar_epoch;  // device int: number of flag barriers completed
+  int* status;     // device int: non-zero after a bounded wait expired
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_volatile(const int* p) {
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait until *flag >= want (epochs only grow).  Returns false on expiry.
+__device__ __forceinline__ bool tp_wait_flag(const int* flag, int want) {
+  for (uint32_t i = 0; i < kTpSpinLimit; ++i) {
+    if (ld_acquire_sys(flag) - want >= 0) return true;
+    __nanosleep(20);
+  }
+  return false;
+}
+
+__device__ __forceinline__ float* tp_recv_slot(const TpComm& c, int on_rank, int parity, int from_rank) {
+  return reinterpret_cast<float*>(c.peer[on_rank] + c.lay.off_recv) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.recv_elems;
+}
+__device__ __forceinline__ int* tp_tile_flag(const TpComm& c, int on_rank, int parity, int from_rank, int tile) {
+  return reinterpret_cast<int*>(c.peer[on_rank] + c.lay.off_tile_flags) + ((size_t)parity * kTpMaxRanks + from_rank) * kTpMaxTiles + tile;
+}
+
+// Second half of the fused epilogue, called by all threads of the CTA after the tile's rows have
+// been stored to every peer's slot [c.rank] (rows row0 .. row0+nrows-1, element offset elem0 + row):
+// publish the tile, wait for the peers' copies of it, then h[row] = residual[row] + sum_r slot[r][row].
+__device__ __forceinline__ void tp_tile_allreduce(const TpComm& c, int epoch, int tile, int row0, int nrows, int n_total,
+                                                  size_t elem0, const float* residual, float* out) {
+  const int parity = epoch & 1, want = epoch + 1;
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.size) {
+    st_release_sys(tp_tile_flag(c, threadIdx.x, parity, c.rank, tile), want);
+    if (!tp_wait_flag(tp_tile_flag(c, c.rank, parity, threadIdx.x, tile), want)) atomicExch(c.status, 2);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows; i += blockDim.x) {
+    const int row = row0 + i;
+    if (row >= n_total) break;
+    float v = residual ? residual[row] : 0.0f;
+    for (int r = 0; r < c.size; ++r) v += __ldcg(tp_recv_slot(c, c.rank, parity, r) + elem0 + row);
+    out[row] = v;
+  }
+}
+
+// Last CTA of the fused kernel bumps the epoch (every CTA has read it by then).
+__device__ __forceinline__ void tp_finish_kernel(const TpComm& c, int epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    int prev = atomicAdd(c.done_ctr, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *c.done_ctr = 0;
+      *c.epoch = epoch + 1;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace bonsai

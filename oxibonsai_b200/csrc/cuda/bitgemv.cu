@@ -13,19 +13,23 @@
 // the chunk partial sums of a row are reduced through shared memory in a fixed order, so the
 // result does not depend on the grid size.
 #include "common.cuh"
+#include "../comm/tp_comm.cuh"
 
 namespace bonsai {
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+// EPI_TP_ALLREDUCE: row-parallel partial sums are pushed to every tensor-parallel peer and reduced
+// with the residual inside this kernel (see comm/tp_comm.cuh).
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_TP_ALLREDUCE = 3 };
 
 template <int R>
 __global__ void __launch_bounds__(256) bitgemv_kernel(const uint4* __restrict__ codes, const __half* __restrict__ scales,
                                                      const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
                                                      float* __restrict__ out, const float* __restrict__ residual, int N, int K,
-                                                     int epi) {
+                                                     int epi, TpComm tp) {
   __shared__ float red[R][256];
   __shared__ float s32[32];
   const int t = threadIdx.x;
+  const int tp_epoch = epi == EPI_TP_ALLREDUCE ? ld_volatile(tp.epoch) : 0;
   const int cpr = K >> 6;        // 64-input chunks per row
   const int G = 256 / cpr;       // row groups handled side by side
   const int g = t / cpr, c = t - g * cpr;
@@ -111,11 +115,19 @@ __global__ void __launch_bounds__(256) bitgemv_kernel(const uint4* __restrict__ 
         for (int j = lane; j < cpr; j += 32) a += red[ii][gg * cpr + j];
         a = warp_sum(a) * kPow2_63;
         int row = tile * rows_per_tile + rr;
-        if (lane == 0 && row < N) out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+        if (lane == 0 && row < N) {
+          if (epi == EPI_TP_ALLREDUCE) {
+            for (int r = 0; r < tp.size; ++r) tp_recv_slot(tp, r, tp_epoch & 1, tp.rank)[row] = a;
+          } else {
+            out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+          }
+        }
       }
     }
+    if (epi == EPI_TP_ALLREDUCE) tp_tile_allreduce(tp, tp_epoch, tile, tile * rows_per_tile, rows_per_tile, N, 0, residual, out);
     __syncthreads();
   }
+  if (epi == EPI_TP_ALLREDUCE) tp_finish_kernel(tp, tp_epoch);
 }
 
 // Fast variant: activations held as half2 pairs, packed half-precision FMAs.  In the planar-SM word
@@ -129,7 +141,7 @@ template <int R>
 __global__ void __launch_bounds__(256, 2) bitgemv_h2_kernel(const uint4* __restrict__ codes, const __half* __restrict__ scales,
                                                            const float* __restrict__ x, const float* __restrict__ norm_w,
                                                            float eps, float* __restrict__ out, const float* __restrict__ residual,
-                                                           int N, int K, int epi) {
+                                                           int N, int K, int epi, TpComm tp) {
   __shared__ float red[R][256];
   __shared__ float s32[32];
   const int t = threadIdx.x;
@@ -157,6 +169,7 @@ __global__ void __launch_bounds__(256, 2) bitgemv_h2_kernel(const uint4* __restr
     }
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int tp_epoch = epi == EPI_TP_ALLREDUCE ? ld_volatile(tp.epoch) : 0;
 
   // activations: 64 floats -> 32 half2 in the pairing order of the packed words
   __half2 xh[32];
@@ -261,13 +274,21 @@ __global__ void __launch_bounds__(256, 2) bitgemv_h2_kernel(const uint4* __restr
         for (int j = lane; j < cpr; j += 32) a += red[ii][gg * cpr + j];
         a = warp_sum(a) * 128.0f;
         int row = tile * rows_per_tile + rr;
-        if (lane == 0 && row < N) out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+        if (lane == 0 && row < N) {
+          if (epi == EPI_TP_ALLREDUCE) {
+            for (int r = 0; r < tp.size; ++r) tp_recv_slot(tp, r, tp_epoch & 1, tp.rank)[row] = a;
+          } else {
+            out[row] = (epi == EPI_RESID) ? residual[row] + a : a;
+          }
+        }
       }
     }
+    if (epi == EPI_TP_ALLREDUCE) tp_tile_allreduce(tp, tp_epoch, tile, tile * rows_per_tile, rows_per_tile, N, 0, residual, out);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < R; ++i) { q[i] = qn[i]; d[i] = dn[i]; }
   }
+  if (epi == EPI_TP_ALLREDUCE) tp_finish_kernel(tp, tp_epoch);
 }
 
 // f16 row-major matrix [N][K] times f32 x, optional fused RMSNorm prologue.  Thread t owns the
@@ -394,11 +415,11 @@ int bonsai_bitgemv(const void* codes, const void* scales, const float* x, const 
   int tiles8 = (N + G * 8 - 1) / (G * 8);
   if (tiles8 >= 2 * 148) {
     int grid = tiles8 < 148 * 2 ? tiles8 : 148 * 2;
-    bitgemv_kernel<8><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi);
+    bitgemv_kernel<8><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi, TpComm{});
   } else {
     int tiles4 = (N + G * 4 - 1) / (G * 4);
     int grid = tiles4 < 148 * 3 ? tiles4 : 148 * 3;
-    bitgemv_kernel<4><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi);
+    bitgemv_kernel<4><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, norm_w, eps, out, residual, N, K, epi, TpComm{});
   }
   return launch_status();
 }
@@ -416,12 +437,39 @@ int bonsai_bitgemv_h2(const void* codes, const void* scales, const float* x, con
   if (tiles8 >= 2 * 148) {
     int grid = tiles8 < 148 * 2 ? tiles8 : 148 * 2;
     e = launch_pdl(bitgemv_h2_kernel<8>, dim3(grid), dim3(256), 0, stream, (const uint4*)codes, (const __half*)scales, x, norm_w, eps,
-                   out, residual, N, K, epi);
+                   out, residual, N, K, epi, TpComm{});
   } else {
     int tiles4 = (N + G * 4 - 1) / (G * 4);
     int grid = tiles4 < 148 * 2 ? tiles4 : 148 * 2;
     e = launch_pdl(bitgemv_h2_kernel<4>, dim3(grid), dim3(256), 0, stream, (const uint4*)codes, (const __half*)scales, x, norm_w, eps,
-                   out, residual, N, K, epi);
+                   out, residual, N, K, epi, TpComm{});
+  }
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
+// Fused row-parallel GEMV -> all-reduce + residual over the tensor-parallel group `comm`:
+// out[N] = residual[N] + sum over ranks of (W_rank x_rank).  Every rank must launch it with the same N
+// and the same tiling (same K shard size and `fast` flag).  fast != 0 selects the packed-half kernel.
+int bonsai_bitgemv_tp(const void* comm, const void* codes, const void* scales, const float* x, float eps, float* out,
+                      const float* residual, int N, int K, int fast, cudaStream_t stream) {
+  using namespace bonsai;
+  if (comm == nullptr || K % 128 != 0 || K < 128 || K > 16384 || N <= 0) return BONSAI_CUDA_BAD_ARG;
+  const TpComm tp = *static_cast<const TpComm*>(comm);
+  if ((size_t)N > tp.lay.recv_elems) return BONSAI_CUDA_BAD_ARG;
+  int cpr = K / 64, G = 256 / cpr;
+  int tiles4 = (N + G * 4 - 1) / (G * 4);
+  if (tiles4 > kTpMaxTiles) return BONSAI_CUDA_BAD_ARG;
+  // every CTA waits on its peers: keep the whole grid co-resident (two CTAs per SM at most)
+  int grid = tiles4 < 148 * 2 ? tiles4 : 148 * 2;
+  cudaError_t e = cudaSuccess;
+  if (fast) {
+    e = launch_pdl(bitgemv_h2_kernel<4>, dim3(grid), dim3(256), 0, stream, (const uint4*)codes, (const __half*)scales, x,
+                   (const float*)nullptr, eps, out, residual, N, K, (int)EPI_TP_ALLREDUCE, tp);
+  } else {
+    if (grid > 148) grid = 148;
+    bitgemv_kernel<4><<<grid, 256, 0, stream>>>((const uint4*)codes, (const __half*)scales, x, nullptr, eps, out, residual, N, K,
+                                                (int)EPI_TP_ALLREDUCE, tp);
+    e = cudaGetLastError();
   }
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }

@@ -27,7 +27,10 @@ int bonsai_attn_decode(const float*, const int*, const int*, int, int, int, int,
 int bonsai_bitgemv_h2(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
                   const uint32_t*, int, cudaStream_t);
-int bonsai_allreduce_residual(void* comm, const float* partial, float* h, int n, int batch, cudaStream_t stream);
+int bonsai_bitgemv_tp(const void*, const void*, const void*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
+int bonsai_tp_allgather_logits(void*, const float*, int, int, int, int, cudaStream_t);
+int bonsai_tp_allreduce_big_add(void*, float*, size_t, cudaStream_t);
+void* bonsai_tp_big_ptr(void*);
 int bonsai_bitgemm_prefill(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int, int,
                            cudaStream_t);
 int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
@@ -105,9 +108,8 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
                           h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, 1, st));
     } else {
       for (int b = 0; b < batch; ++b)
-        RC(gemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
-                          partial + (size_t)b * hidden, nullptr, hidden, qd, 0, st));
-      RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
+        RC(bonsai_bitgemv_tp(r.comm, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, r.eps,
+                             h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, r.ic[IC_FAST], st));
     }
     for (int b = 0; b < batch; ++b)
       RC(gemv(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), r.eps,
@@ -118,15 +120,25 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
                           h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, 1, st));
     } else {
       for (int b = 0; b < batch; ++b)
-        RC(gemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
-                          partial + (size_t)b * hidden, nullptr, hidden, inter, 0, st));
-      RC(bonsai_allreduce_residual(r.comm, partial, h, hidden, batch, st));
+        RC(bonsai_bitgemv_tp(r.comm, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, r.eps,
+                             h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, r.ic[IC_FAST], st));
     }
   }
   if (!(flags & 2)) {
-    for (int b = 0; b < batch; ++b)
-      RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), h + (size_t)b * hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps,
-                        logits + (size_t)b * vocab, lm_rows, hidden, st));
+    if (!tp) {
+      for (int b = 0; b < batch; ++b)
+        RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), h + (size_t)b * hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps,
+                          logits + (size_t)b * vocab, lm_rows, hidden, st));
+    } else {
+      // vocab-parallel head: local slice, then every rank pushes its slice into all logits areas
+      // (`logits` is this rank's area of the symmetric buffer)
+      const int rows_per_rank = (vocab + r.ic[IC_TP_SIZE] - 1) / r.ic[IC_TP_SIZE];
+      for (int b = 0; b < batch; ++b)
+        if (lm_rows > 0)
+          RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), h + (size_t)b * hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps,
+                            partial + (size_t)b * lm_rows, lm_rows, hidden, st));
+      RC(bonsai_tp_allgather_logits(r.comm, partial, batch, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
+    }
   }
   if (flags & 1) {
     RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),
@@ -148,7 +160,8 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
   const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
   const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
-  if (r.ic[IC_TP_SIZE] > 1) return BONSAI_CUDA_BAD_ARG;  // tensor-parallel prefill runs through the decode path
+  const bool tp = r.ic[IC_TP_SIZE] > 1;
+  float* big = tp ? static_cast<float*>(bonsai_tp_big_ptr(r.comm)) : nullptr;
   const int sms = 148;
   const int* tokens = P<int>(pp[PP_TOKENS]);
   const int* positions = P<int>(pp[PP_POSITIONS]);
@@ -175,20 +188,40 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
                                   P<float>(lp[LP_VSCALE]), st));
     RC(bonsai_attn_prefill(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
                            P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
-                              hidden, sms, st));
+    if (!tp) {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
+                                hidden, sms, st));
+    } else {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, status, hidden, qd, T,
+                                0, hidden, sms, st));
+      RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
+    }
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, st));
     RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
                               hidden, T, 2, inter, sms, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
-                              T, 1, hidden, sms, st));
+    if (!tp) {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+                                T, 1, hidden, sms, st));
+    } else {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, status, hidden,
+                                inter, T, 0, hidden, sms, st));
+      RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
+    }
   }
   if (want_logits) {
     float* hs = P<float>(sp[SP_H]) + (size_t)slot * hidden;
     if (cudaMemcpyAsync(hs, h + (size_t)(T - 1) * hidden, (size_t)hidden * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
       return BONSAI_CUDA_LAUNCH_FAILED;
-    RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, P<float>(sp[SP_LOGITS]) + (size_t)slot * vocab,
-                      lm_rows, hidden, st));
+    if (!tp) {
+      RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, P<float>(sp[SP_LOGITS]) + (size_t)slot * vocab,
+                        lm_rows, hidden, st));
+    } else {
+      if (slot != 0) return BONSAI_CUDA_BAD_ARG;
+      const int rows_per_rank = (vocab + r.ic[IC_TP_SIZE] - 1) / r.ic[IC_TP_SIZE];
+      float* partial = P<float>(sp[SP_PARTIAL]);
+      if (lm_rows > 0) RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, partial, lm_rows, hidden, st));
+      RC(bonsai_tp_allgather_logits(r.comm, partial, 1, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
+    }
   }
   return 0;
 }
@@ -196,9 +229,6 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
 }  // namespace bonsai
 
 extern "C" {
-
-// Weak default so the library links before the tensor-parallel communicator is built in.
-__attribute__((weak)) int bonsai_allreduce_residual(void*, const float*, float*, int, int, cudaStream_t) { return BONSAI_CUDA_BAD_ARG; }
 
 void* bonsai_runner_create(const int* icfg, float eps, const uint64_t* global_ptrs, const uint64_t* layer_ptrs) {
   using namespace bonsai;

@@ -195,7 +195,7 @@ class Qwen3Runner:
     """Owns the activation buffers and the native step runner for a fixed maximum batch."""
 
     def __init__(self, weights: Qwen3Weights, kv: PagedKvCache, max_batch: int, max_seq: int, nsplit: int | None = None,
-                 fast: bool = True):
+                 fast: bool = True, prefill_chunk: int = 1024):
         self.w, self.kv, self.max_batch, self.max_seq = weights, kv, max_batch, max_seq
         cfg, dev = weights.cfg, weights.device
         self.cfg, self.device = cfg, dev
@@ -216,8 +216,15 @@ class Qwen3Runner:
         self.q = torch.zeros((B, nq, hd), **f32)
         self.attn = torch.zeros((B, nq * hd), **f32)
         self.act = torch.zeros((B, weights.inter_local), **f32)
-        self.logits = torch.zeros((B, cfg.vocab), **f32)
-        self.partial = torch.zeros((B, cfg.hidden), **f32)
+        self.tp = None
+        if weights.tp_size > 1:
+            from ..parallel.tp import TpGroup
+            self.tp = TpGroup(weights.tp_rank, weights.tp_size, dev, cfg.hidden, cfg.vocab, B, prefill_chunk * cfg.hidden)
+            self.logits = self.tp.logits          # this rank's gathered-logits area of the symmetric buffer
+            self.partial = torch.zeros((B, max(1, weights.lm_head.shape[0])), **f32)   # local logits slice
+        else:
+            self.logits = torch.zeros((B, cfg.vocab), **f32)
+            self.partial = torch.zeros((B, cfg.hidden), **f32)
         self.ws_acc = torch.zeros((B, nq, self.nsplit, hd), **f32)
         self.ws_ml = torch.zeros((B, nq, self.nsplit, 2), **f32)
         self.temps = torch.zeros(B, **f32)
@@ -255,6 +262,8 @@ class Qwen3Runner:
               self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None, self.attn_counters]
         assert len(sp) == nsp
         self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
+        if self.tp is not None:
+            lib.bonsai_runner_set_comm(self._native, self.tp.handle)
         self.launches_per_step = None
 
     def __del__(self):
@@ -310,8 +319,8 @@ class Qwen3Runner:
 
     def kernel_launches(self, batch: int, sample: bool = True) -> int:
         """Number of kernel launches in one decode step (each is one of this library's kernels)."""
-        per_layer = 4 * batch + 2 + (2 if self.w.tp_size > 1 else 0)
-        return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0)
+        per_layer = 4 * batch + 2
+        return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0) + (2 if self.w.tp_size > 1 else 0)
 
     def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:
         flags = (1 if sample else 0) | (0 if lm_head else 2)

@@ -1,0 +1,114 @@
+"""Tensor-parallel group over NVLink peer memory: symmetric buffer set-up and the native communicator handle.
+
+The reference's tensor parallelism is a CPU simulation (``ShardedLinear``, ``tensor_parallel_forward``,
+``NcclCollectives``; crates/oxibonsai-model/src/tensor_parallel.rs:20-468, multi_gpu.rs:31-320).  Here one process
+per GPU joins a ``torch.distributed`` NCCL group (bootstrap, barriers), allocates one symmetric buffer with
+``torch.distributed._symmetric_memory`` and hands the peer addresses to the CUDA kernels of ``csrc/comm``,
+which move data with ordinary loads/stores to peer memory (never TMA, never a library kernel on a peer pointer).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import cuda_ops as K
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+_SIG = {
+    "bonsai_tp_layout": [_sz, _sz, _sz, _vp],
+    "bonsai_tp_create": [_i, _i, _vp, _sz, _sz, _sz, _vp],
+    "bonsai_tp_destroy": [_vp],
+    "bonsai_tp_barrier": [_vp, _vp],
+    "bonsai_tp_allgather_logits": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "bonsai_tp_logits_ptr": [_vp],
+    "bonsai_tp_big_ptr": [_vp],
+    "bonsai_tp_allreduce_big_add": [_vp, _vp, _sz, _vp],
+    "bonsai_bitgemv_tp": [_vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _i, _i, _i, _vp],
+}
+_RES = {"bonsai_tp_layout": _sz, "bonsai_tp_create": _vp, "bonsai_tp_destroy": None, "bonsai_tp_logits_ptr": _vp, "bonsai_tp_big_ptr": _vp}
+_declared = False
+
+
+def _lib():
+    global _declared
+    l = K.lib()
+    if not _declared:
+        K.declare(_SIG, _RES)
+        _declared = True
+    return l
+
+
+@dataclass(frozen=True)
+class ShardRange:
+    """Half-open ranges owned by one rank: rows for column-parallel matrices, 128-input blocks for row-parallel ones."""
+    heads: tuple[int, int]
+    kv_heads: tuple[int, int]
+    inter_blocks: tuple[int, int]
+    vocab_rows: tuple[int, int]
+
+
+def shard_plan(heads: int, kv_heads: int, inter: int, vocab: int, tp_size: int) -> list[ShardRange]:
+    """The standard transformer plan (q/k/v/gate/up column-parallel, o/down row-parallel, LM head vocab-parallel);
+    the intermediate dimension is split on 128-weight block boundaries, sizes differing by at most one block."""
+    if heads % tp_size or kv_heads % tp_size:
+        raise ValueError(f"tp_size {tp_size} must divide heads {heads} and kv_heads {kv_heads}")
+    nblk = inter // 128
+    base, extra = divmod(nblk, tp_size)
+    per = (vocab + tp_size - 1) // tp_size
+    out, b0 = [], 0
+    for r in range(tp_size):
+        nb = base + (1 if r < extra else 0)
+        h, kv = heads // tp_size, kv_heads // tp_size
+        out.append(ShardRange((r * h, (r + 1) * h), (r * kv, (r + 1) * kv), (b0, b0 + nb), (min(vocab, r * per), min(vocab, (r + 1) * per))))
+        b0 += nb
+    return out
+
+
+class TpGroup:
+    """Symmetric buffer + native communicator of one rank."""
+
+    def __init__(self, rank: int, size: int, device, hidden: int, vocab: int, max_batch: int, big_elems: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        if not dist.is_initialized():
+            raise RuntimeError("tensor parallelism needs torch.distributed initialised with the nccl backend")
+        lib = _lib()
+        self.rank, self.size = rank, size
+        self.recv_elems, self.logits_elems, self.big_elems = hidden, max_batch * vocab, big_elems
+        offs = (C.c_size_t * 5)()
+        total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
+        self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
+        self._hdl = symm.rendezvous(self.buffer, dist.group.WORLD)
+        self.buffer.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        ptrs = list(self._hdl.buffer_ptrs)
+        assert len(ptrs) == size
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        arr = (C.c_uint64 * size)(*ptrs)
+        self.handle = lib.bonsai_tp_create(rank, size, arr, self.recv_elems, self.logits_elems, self.big_elems, self.state.data_ptr())
+        if not self.handle:
+            raise RuntimeError("bonsai_tp_create failed")
+        lo = int(offs[3])
+        self.logits = self.buffer[lo: lo + self.logits_elems * 4].view(torch.float32).view(max_batch, vocab)
+        bo = int(offs[4])
+        self.big = self.buffer[bo: bo + self.big_elems * 4].view(torch.float32)
+
+    def barrier(self) -> None:
+        K.check(_lib().bonsai_tp_barrier(self.handle, K.stream()), "tp_barrier")
+
+    def status(self) -> int:
+        return int(self.state[3].item())
+
+    def check(self) -> None:
+        s = self.status()
+        if s:
+            raise K.CudaKernelError(f"tensor-parallel kernel reported status {s}: a peer did not answer within the wait limit")
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            _lib().bonsai_tp_destroy(self.handle)
+            self.handle = None

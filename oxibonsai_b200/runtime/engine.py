@@ -67,7 +67,9 @@ class InferenceEngine:
                                self.kvt, self.device)
         # exact = f32 activations end to end (the token-stream gate); default: exact only with an f32 KV cache
         self.exact = (self.kvt == K.KV_F32) if exact is None else bool(exact)
-        self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact)
+        self.prefill_chunk = 1024
+        self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact,
+                                  prefill_chunk=self.prefill_chunk)
         self.load_seconds = time.perf_counter() - t0
         # pinned staging for the per-step host <-> device traffic
         self._tok_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
@@ -75,7 +77,6 @@ class InferenceEngine:
         self._out_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._slot_pages: dict[int, list[int]] = {}
         self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
-        self.prefill_chunk = 1024
         self.last_stats = GenerationStats()
         if warmup:
             self.warmup()
@@ -137,7 +138,7 @@ class InferenceEngine:
         n = len(prompt)
         toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         r = self.runner
-        if n >= self.prefill_min_tokens and not self.exact and self.weights.tp_size == 1:
+        if n >= self.prefill_min_tokens and not self.exact:
             r.prefill(toks, slot, pos0, self.prefill_chunk)
             return
         if slot != 0:

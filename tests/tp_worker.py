@@ -1,0 +1,45 @@
+"""Worker of the multi-GPU tensor-parallel tests: run as one process per GPU under torch.distributed.run."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    path, mode = sys.argv[1], sys.argv[2]
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from oxibonsai_b200.core import GgufFile, Oracle
+    from oxibonsai_b200.runtime import EngineBuilder
+
+    prompt = [11, 257, 3, 999, 42, 7]
+    out = {"rank": rank}
+    if mode == "exact":
+        want, gaps = Oracle(GgufFile.open(path), 128).generate_greedy(prompt, 16)
+        eng = EngineBuilder().model_path(path).preset("greedy").max_seq_len(128).kv_cache("f32").device(f"cuda:{local}").tensor_parallel(rank, world).build()
+        got = eng.generate(prompt, 16)
+        out.update(ok=(got == want), got=got, want=want, status=eng.runner.tp.status())
+    elif mode == "fast":
+        eng = EngineBuilder().model_path(path).preset("greedy").max_seq_len(256).kv_cache("f16").device(f"cuda:{local}").tensor_parallel(rank, world).build()
+        g = torch.Generator().manual_seed(5)
+        long_prompt = torch.randint(0, 1000, (90,), generator=g).tolist()
+        a = eng.generate(long_prompt, 8)               # batched prefill (tcgen05 GEMMs + two-shot all-reduce)
+        eng.prefill_min_tokens = 10 ** 9
+        b = eng.generate(long_prompt, 8)               # token-by-token prefill through the fused GEMV all-reduce
+        toks = torch.tensor(a, device=f"cuda:{local}")
+        gathered = [torch.zeros_like(toks) for _ in range(world)]
+        dist.all_gather(gathered, toks)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        out.update(ok=(len(a) == 8 and same and sum(x == y for x, y in zip(a, b)) >= 6), a=a, b=b, same=same, status=eng.runner.tp.status())
+    dist.barrier()
+    print("TPRESULT " + json.dumps(out), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
