@@ -28,9 +28,7 @@
 namespace bonsai {
 
 constexpr int kPfStages = 4;
-constexpr int kPfTokTile = 256;
 constexpr int kPfABytes = 128 * 128;          // 128 rows x 64 f16
-constexpr int kPfBBytes = kPfTokTile * 128;   // 256 tokens x 64 f16
 constexpr int kPfThreads = 320;               // warps 0-3 expand, 4-7 epilogue, 8 = MMA, 9 = TMA
 
 // position of logical input k inside its 16-element block in the paired-K layout
@@ -47,6 +45,7 @@ struct PfParams {
   __half* out_f16;         // [T][out_ld]  (epi 2: SwiGLU, paired-K order; epi 3: plain f16 store)
   int* status;
   int n_rows, K, T, epi, out_ld;
+  int dense;               // 1: A is a dense f16 matrix fetched by TMA (natural K order), no expansion
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -56,7 +55,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                : "memory");
 }
 
-__global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __grid_constant__ CUtensorMap xmap, PfParams p) {
+// TOK = tokens per tile (MMA N): 256 for prompt chunks, 64 for batched decode / verification.
+template <int TOK>
+__global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                     const __grid_constant__ CUtensorMap amap, PfParams p) {
+  constexpr int kPfTokTile = TOK;
+  constexpr int kPfBBytes = TOK * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = base;
@@ -69,12 +73,12 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
   const int ntiles = row_tiles * tok_tiles;
 
   if (warp == 8) {
-    tc::tmem_alloc(&tmem_slot, 512);
+    tc::tmem_alloc(&tmem_slot, 2 * TOK);
     tc::tmem_relinquish();
   }
   if (t == 0) {
     for (int i = 0; i < kPfStages; ++i) {
-      tc::mbar_init(&full_bar[i], 5);   // 4 expander warps + the TMA issuer's expect_tx arrival
+      tc::mbar_init(&full_bar[i], p.dense ? 1 : 5);   // 4 expander warps + the TMA issuer's expect_tx arrival
       tc::mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -98,8 +102,9 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kPfStages;
           if (!tc::mbar_wait(&empty_bar[s], ((it / kPfStages) & 1) ^ 1)) { failed = true; break; }
-          tc::mbar_arrive_expect_tx(&full_bar[s], kPfBBytes);
+          tc::mbar_arrive_expect_tx(&full_bar[s], kPfBBytes + (p.dense ? kPfABytes : 0));
           tma_load_2d(sB + s * kPfBBytes, &xmap, kb * 64, tok0, &full_bar[s]);
+          if (p.dense) tma_load_2d(sA + s * kPfABytes, &amap, kb * 64, (tile % row_tiles) * 128, &full_bar[s]);
         }
       }
       if (failed) atomicExch(p.status, 1);
@@ -129,6 +134,8 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
     }
   } else if (warp < 4) {
     // ------------------------------- weight expanders (thread = weight row) ---------------------
+    if (p.dense) goto done;
+    {
     const int words_per_row = p.K >> 4, ngroups = p.K >> 7;
     int it = 0;
     for (int tile = blockIdx.x; tile < ntiles && !failed; tile += gridDim.x) {
@@ -169,6 +176,7 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
       }
     }
     if (failed && t == 0) atomicExch(p.status, 1);
+    }
   } else {
     // ------------------------------- epilogue (thread = weight row) ------------------------------
     const int a = t - 128;
@@ -209,15 +217,16 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
     }
     if (failed && a == 0) atomicExch(p.status, 1);
   }
+done:
   tc::tc_fence_before();
   __syncthreads();
-  if (warp == 8) tc::tmem_dealloc(taddr, 512);
+  if (warp == 8) tc::tmem_dealloc(taddr, 2 * TOK);
 }
 
 // One block per token: y = rmsnorm(x) * w (or a plain copy when w is null), written as f16 in the
 // paired-K order consumed by bitgemm_prefill.
 __global__ void norm_to_f16_paired_kernel(const float* __restrict__ x, int x_ld, const float* __restrict__ w, float eps, int K,
-                                          __half* __restrict__ out, int out_ld) {
+                                          __half* __restrict__ out, int out_ld, int natural) {
   __shared__ float s32[32];
   const int tok = blockIdx.x;
   const float* xr = x + (size_t)tok * x_ld;
@@ -230,46 +239,64 @@ __global__ void norm_to_f16_paired_kernel(const float* __restrict__ x, int x_ld,
   }
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
     float v = w ? w[k] * xr[k] * inv : xr[k];
-    out[(size_t)tok * out_ld + paired_k(k)] = __float2half_rn(v);
+    out[(size_t)tok * out_ld + (natural ? k : paired_k(k))] = __float2half_rn(v);
   }
 }
 
 }  // namespace bonsai
 
-extern "C" {
-
-// x_f16: activations [T][K] f16 in paired-K order (row stride x_ld elements, 16-byte aligned rows).
-// epi 0: out_f32 = W x; 1: out_f32 = residual + W x; 2: out_f16 = SwiGLU over interleaved gate/up rows
-// (paired-K order, out_ld = N/2 or more); 3: out_f16 = W x in natural order.
-int bonsai_bitgemm_prefill(const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32,
-                           const float* residual, void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld,
-                           int sms, cudaStream_t stream) {
-  using namespace bonsai;
-  if (K % 128 != 0 || n_rows < 1 || T < 1 || epi < 0 || epi > 3 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
-  if ((epi <= 1 && out_f32 == nullptr) || (epi == 1 && residual == nullptr) || (epi >= 2 && out_f16 == nullptr)) return BONSAI_CUDA_BAD_ARG;
-  CUtensorMap map;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
-  cuuint64_t strides[1] = {(cuuint64_t)x_ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)kPfTokTile};
+static bool make_map_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
+  cuuint32_t box[2] = {64, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult cr = cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x_f16), dims, strides, box, estr,
-                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (cr != CUDA_SUCCESS) return BONSAI_CUDA_BAD_ARG;
-  PfParams p{(const uint32_t*)codes, (const __half*)scales, out_f32, residual, (__half*)out_f16, status, n_rows, K, T, epi, out_ld};
-  const int ntiles = ((n_rows + 127) / 128) * ((T + kPfTokTile - 1) / kPfTokTile);
+  return cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int TOK>
+static int launch_prefill(const CUtensorMap& xmap, const CUtensorMap& amap, const bonsai::PfParams& p, int sms, cudaStream_t stream) {
+  using namespace bonsai;
+  const int ntiles = ((p.n_rows + 127) / 128) * ((p.T + TOK - 1) / TOK);
   int grid = ntiles < sms ? ntiles : sms;
-  size_t smem = 1024 + (size_t)kPfStages * (kPfABytes + kPfBBytes);
-  cudaError_t e = cudaFuncSetAttribute(bitgemm_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  size_t smem = 1024 + (size_t)kPfStages * (kPfABytes + TOK * 128);
+  cudaError_t e = cudaFuncSetAttribute(bitgemm_prefill_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
-  bitgemm_prefill_kernel<<<grid, kPfThreads, smem, stream>>>(map, p);
+  bitgemm_prefill_kernel<TOK><<<grid, kPfThreads, smem, stream>>>(xmap, amap, p);
   return launch_status();
 }
 
-int bonsai_norm_to_f16_paired(const float* x, int x_ld, const float* w, float eps, int T, int K, void* out, int out_ld,
+extern "C" {
+
+// x_f16: activations [T][K] f16 (row stride x_ld elements, 16-byte aligned rows), in paired-K order for packed
+// weights and natural order for dense ones.
+// epi 0: out_f32 = W x; 1: out_f32 = residual + W x; 2: out_f16 = SwiGLU over interleaved gate/up rows
+// (paired-K order, out_ld = N/2 or more); 3: out_f16 = W x in natural order.
+// dense_w != null: W is a dense f16 row-major [n_rows][K] matrix (codes / scales ignored), e.g. the LM head.
+int bonsai_bitgemm_prefill(const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32,
+                           const float* residual, void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld,
+                           int sms, const void* dense_w, cudaStream_t stream) {
+  using namespace bonsai;
+  if (K % 128 != 0 || n_rows < 1 || T < 1 || epi < 0 || epi > 3 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
+  if ((epi <= 1 && out_f32 == nullptr) || (epi == 1 && residual == nullptr) || (epi >= 2 && out_f16 == nullptr)) return BONSAI_CUDA_BAD_ARG;
+  const int tok = T <= 64 ? 64 : 256;
+  CUtensorMap xmap, amap;
+  if (!make_map_f16(&xmap, x_f16, K, T, x_ld, tok)) return BONSAI_CUDA_BAD_ARG;
+  if (dense_w != nullptr) {
+    if (!make_map_f16(&amap, dense_w, K, n_rows, K, 128)) return BONSAI_CUDA_BAD_ARG;
+  } else {
+    amap = xmap;
+  }
+  PfParams p{(const uint32_t*)codes, (const __half*)scales, out_f32, residual, (__half*)out_f16, status, n_rows, K, T, epi, out_ld,
+             dense_w != nullptr ? 1 : 0};
+  return tok == 64 ? launch_prefill<64>(xmap, amap, p, sms, stream) : launch_prefill<256>(xmap, amap, p, sms, stream);
+}
+
+int bonsai_norm_to_f16_paired(const float* x, int x_ld, const float* w, float eps, int T, int K, void* out, int out_ld, int natural,
                               cudaStream_t stream) {
   if (T < 1 || K % 16 != 0) return BONSAI_CUDA_BAD_ARG;
-  bonsai::norm_to_f16_paired_kernel<<<T, 256, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld);
+  bonsai::norm_to_f16_paired_kernel<<<T, 256, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural);
   return bonsai::launch_status();
 }
 

@@ -487,15 +487,15 @@ int bonsai_bitgemv_tc(const void* codes, const void* scales, const void* xq, con
   switch (ncols) {
     case 16:
       e = cudaFuncSetAttribute(bitgemv_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e == cudaSuccess) e = launch_pdl(bitgemv_tc_kernel<16>, grid, dim3(kTcThreads), smem, stream, p);
+      if (e == cudaSuccess) { bitgemv_tc_kernel<16><<<grid, kTcThreads, smem, stream>>>(p); e = cudaGetLastError(); }
       break;
     case 32:
       e = cudaFuncSetAttribute(bitgemv_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e == cudaSuccess) e = launch_pdl(bitgemv_tc_kernel<32>, grid, dim3(kTcThreads), smem, stream, p);
+      if (e == cudaSuccess) { bitgemv_tc_kernel<32><<<grid, kTcThreads, smem, stream>>>(p); e = cudaGetLastError(); }
       break;
     default:
       e = cudaFuncSetAttribute(bitgemv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e == cudaSuccess) e = launch_pdl(bitgemv_tc_kernel<64>, grid, dim3(kTcThreads), smem, stream, p);
+      if (e == cudaSuccess) { bitgemv_tc_kernel<64><<<grid, kTcThreads, smem, stream>>>(p); e = cudaGetLastError(); }
       break;
   }
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;

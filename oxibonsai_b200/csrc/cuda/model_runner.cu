@@ -32,8 +32,8 @@ int bonsai_tp_allgather_logits(void*, const float*, int, int, int, int, cudaStre
 int bonsai_tp_allreduce_big_add(void*, float*, size_t, cudaStream_t);
 void* bonsai_tp_big_ptr(void*);
 int bonsai_bitgemm_prefill(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int, int,
-                           cudaStream_t);
-int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
+                           const void*, cudaStream_t);
+int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, int, cudaStream_t);
 int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                         const float*, void*, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
@@ -50,7 +50,7 @@ enum GlobalPtr {
 };
 enum IntCfg {
   IC_HIDDEN = 0, IC_INTER_LOCAL, IC_LAYERS, IC_HEADS_LOCAL, IC_KV_HEADS_LOCAL, IC_HEAD_DIM, IC_VOCAB, IC_LM_ROWS_LOCAL,
-  IC_KVT, IC_PAGE_SIZE, IC_MAX_PAGES, IC_NSPLIT, IC_TP_SIZE, IC_TP_RANK, IC_FAST, IC_COUNT
+  IC_KVT, IC_PAGE_SIZE, IC_MAX_PAGES, IC_NSPLIT, IC_TP_SIZE, IC_TP_RANK, IC_FAST, IC_NSPLIT_BATCHED, IC_COUNT
 };
 enum StepPtr {
   SP_TOKENS = 0, SP_POSITIONS, SP_BLOCK_TABLE, SP_H, SP_QKV, SP_Q, SP_ATTN, SP_ACT, SP_LOGITS, SP_WS_ACC, SP_WS_ML,
@@ -178,9 +178,9 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, T, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, T, hidden, xn, xn_ld, st));
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
     RC(bonsai_bitgemm_prefill(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
-                              hidden, T, 0, qkv_n, sms, st));
+                              hidden, T, 0, qkv_n, sms, nullptr, st));
     // every row of the chunk uses the same page list: a block-table stride of zero
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
                                   P<float>(r.gp[GP_ROPE_SIN]), positions, bt, 0, q, T, nq, nkv, hd, r.ic[IC_KVT],
@@ -190,21 +190,21 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
                            P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, st));
     if (!tp) {
       RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
-                                hidden, sms, st));
+                                hidden, sms, nullptr, st));
     } else {
       RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, status, hidden, qd, T,
-                                0, hidden, sms, st));
+                                0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, st));
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
     RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
-                              hidden, T, 2, inter, sms, st));
+                              hidden, T, 2, inter, sms, nullptr, st));
     if (!tp) {
       RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
-                                T, 1, hidden, sms, st));
+                                T, 1, hidden, sms, nullptr, st));
     } else {
       RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, status, hidden,
-                                inter, T, 0, hidden, sms, st));
+                                inter, T, 0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
   }
@@ -222,6 +222,67 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
       if (lm_rows > 0) RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, partial, lm_rows, hidden, st));
       RC(bonsai_tp_allgather_logits(r.comm, partial, 1, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
     }
+  }
+  return 0;
+}
+
+// Batched decode step for `batch` live sequences (slots 0..batch-1): every linear layer is one
+// tcgen05 GEMM over all sequences (the packed weights are expanded once per step, not once per
+// sequence), attention stays the per-sequence split-KV kernel, and the LM head is a dense f16
+// tcgen05 GEMM.  The reference's continuous batching re-runs a full single-sequence generate per
+// request per step (crates/oxibonsai-runtime/src/continuous_batch.rs:283-293).
+static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp, int batch, int flags, int mask_words,
+                               cudaStream_t st) {
+  const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
+  const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
+  const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
+  if (r.ic[IC_TP_SIZE] > 1) return BONSAI_CUDA_BAD_ARG;
+  const int sms = 148;
+  int* tokens = P<int>(sp[SP_TOKENS]);
+  int* positions = P<int>(sp[SP_POSITIONS]);
+  const int* bt = P<int>(sp[SP_BLOCK_TABLE]);
+  float* h = P<float>(sp[SP_H]);
+  float* qkv = P<float>(sp[SP_QKV]);
+  float* q = P<float>(sp[SP_Q]);
+  float* attn = P<float>(sp[SP_ATTN]);
+  float* logits = P<float>(sp[SP_LOGITS]);
+  void* xn = P<void>(pp[PP_XN]);
+  void* attn16 = P<void>(pp[PP_ATTN]);
+  void* act = P<void>(pp[PP_ACT]);
+  int* status = P<int>(pp[PP_STATUS]);
+  const int xn_ld = hidden > qd ? hidden : qd;
+
+  RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, batch, hidden, vocab, st));
+  for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
+    const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
+                              hidden, batch, 0, qkv_n, sms, nullptr, st));
+    RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
+                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
+                                  r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
+                                  P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
+    RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
+                          P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
+                          r.ic[IC_NSPLIT_BATCHED], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
+    RC(bonsai_norm_to_f16_paired(attn, qd, nullptr, r.eps, batch, qd, attn16, qd, 0, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
+                              hidden, sms, nullptr, st));
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
+                              hidden, batch, 2, inter, sms, nullptr, st));
+    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+                              batch, 1, hidden, sms, nullptr, st));
+  }
+  if (!(flags & 2)) {
+    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps, batch, hidden, xn, xn_ld, 1, st));
+    RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, logits, nullptr, nullptr, status, lm_rows, hidden, batch, 0, vocab, sms,
+                              P<void>(r.gp[GP_LM_HEAD]), st));
+  }
+  if (flags & 1) {
+    RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),
+                     P<unsigned long long>(sp[SP_RNG]), P<int>(sp[SP_OUT_TOKENS]), positions, 1,
+                     P<uint32_t>(sp[SP_ALLOW_MASK]), mask_words, st));
   }
   return 0;
 }
@@ -247,6 +308,11 @@ void bonsai_runner_set_fast(void* r, int fast) { static_cast<bonsai::Runner*>(r)
 int bonsai_runner_layer_ptr_count() { return bonsai::LP_COUNT; }
 int bonsai_runner_step_ptr_count() { return bonsai::SP_COUNT; }
 int bonsai_runner_prefill_ptr_count() { return bonsai::PP_COUNT; }
+
+int bonsai_runner_decode_step_batched(void* r, const uint64_t* step_ptrs, const uint64_t* prefill_ptrs, int batch, int flags,
+                                      int mask_words, cudaStream_t stream) {
+  return bonsai::decode_step_batched(*static_cast<bonsai::Runner*>(r), step_ptrs, prefill_ptrs, batch, flags, mask_words, stream);
+}
 
 int bonsai_runner_prefill_chunk(void* r, const uint64_t* step_ptrs, const uint64_t* prefill_ptrs, int T, int pos0, int slot,
                                 int want_logits, cudaStream_t stream) {

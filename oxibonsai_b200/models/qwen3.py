@@ -243,8 +243,8 @@ class Qwen3Runner:
         lib = K.lib()
         w, kv, cfg = self.w, self.kv, self.cfg
         nlp, nsp = lib.bonsai_runner_layer_ptr_count(), lib.bonsai_runner_step_ptr_count()
-        icfg = (C.c_int * 15)(cfg.hidden, w.inter_local, cfg.layers, w.heads_local, w.kv_heads_local, cfg.head_dim, cfg.vocab,
-                              w.lm_head.shape[0], kv.kvt, kv.page_size, self.max_pages, self.nsplit, w.tp_size, w.tp_rank, int(self.fast))
+        icfg = (C.c_int * 16)(cfg.hidden, w.inter_local, cfg.layers, w.heads_local, w.kv_heads_local, cfg.head_dim, cfg.vocab,
+                              w.lm_head.shape[0], kv.kvt, kv.page_size, self.max_pages, self.nsplit, w.tp_size, w.tp_rank, int(self.fast), self.nsplit)
         gp = (C.c_uint64 * 5)(w.embd.data_ptr(), w.lm_head.data_ptr(), w.out_norm.data_ptr(), self.rope_cos.data_ptr(), self.rope_sin.data_ptr())
         lp = (C.c_uint64 * (nlp * cfg.layers))()
         for l, lw in enumerate(w.layers):
@@ -324,6 +324,12 @@ class Qwen3Runner:
 
     def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:
         flags = (1 if sample else 0) | (0 if lm_head else 2)
+        if batch >= 2 and self.fast and self.w.tp_size == 1:
+            # all sequences share one tcgen05 GEMM per linear layer
+            b = self._prefill_buffers(max(64, batch))
+            K.check(K._pf().bonsai_runner_decode_step_batched(self._native, self._step_ptrs, b["ptrs"], batch, flags, 0, K.stream()),
+                    "decode_step_batched")
+            return
         K.check(K.lib().bonsai_runner_decode_step(self._native, self._step_ptrs, batch, flags, 0, K.stream()), "decode_step")
 
     def step(self, batch: int, sample: bool = True) -> None:
@@ -331,6 +337,8 @@ class Qwen3Runner:
         key = (batch, int(sample))
         g = self._graphs.get(key)
         if g is None:
+            if batch >= 2 and self.fast and self.w.tp_size == 1:
+                self._prefill_buffers(max(64, batch))   # allocate outside the capture
             # capture without running: the capture itself executes nothing, so state is untouched
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream(self.device))

@@ -293,12 +293,13 @@ def bitgemv_tc(w: PlanarWeight, ws: TcWorkspace, act: TcActivations | None = Non
 
 # ---- prefill path -------------------------------------------------------------------------------------
 _PF_SIG = {
-    "bonsai_bitgemm_prefill": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _vp],
+    "bonsai_bitgemm_prefill": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _i, _vp],
     "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_runner_prefill_ptr_count": [],
     "bonsai_runner_prefill_chunk": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "bonsai_runner_decode_step_batched": [_vp, _vp, _vp, _i, _i, _i, _vp],
 }
 _pf_declared = False
 
@@ -319,13 +320,28 @@ def paired_k_index(k: int, device=None) -> torch.Tensor:
     return (i & ~15) | (j & 8) | ((j & 3) * 2 + ((j >> 2) & 1))
 
 
-def norm_to_f16_paired(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+def norm_to_f16_paired(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, out: torch.Tensor | None = None,
+                       natural: bool = False) -> torch.Tensor:
     """f32 [T, K] -> f16 [T, K] in paired-K order, optionally RMS-normalised first."""
     T, Kd = x.shape
     if out is None:
         out = torch.empty((T, Kd), dtype=torch.float16, device=x.device)
-    check(_pf().bonsai_norm_to_f16_paired(x.data_ptr(), x.stride(0), ptr(norm_w), eps, T, Kd, out.data_ptr(), out.stride(0), stream()),
+    check(_pf().bonsai_norm_to_f16_paired(x.data_ptr(), x.stride(0), ptr(norm_w), eps, T, Kd, out.data_ptr(), out.stride(0), int(natural), stream()),
           "norm_to_f16_paired")
+    return out
+
+
+def dense_gemm_f16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                   sms: int = 148) -> torch.Tensor:
+    """out[T, N] (f32) = x[T, K] @ w[N, K]^T for dense f16 operands (natural K order) on tcgen05; used for the LM head."""
+    T, n = x.shape[0], w.shape[0]
+    assert w.dtype == torch.float16 and x.dtype == torch.float16 and w.is_contiguous() and x.shape[1] == w.shape[1]
+    if out is None:
+        out = torch.empty((T, n), dtype=torch.float32, device=x.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    check(_pf().bonsai_bitgemm_prefill(None, None, x.data_ptr(), x.stride(0), out.data_ptr(), None, None, status.data_ptr(), n, w.shape[1],
+                                       T, 0, out.stride(0), sms, w.data_ptr(), stream()), "dense_gemm_f16")
     return out
 
 
@@ -342,7 +358,7 @@ def bitgemm_prefill(w: PlanarWeight, x_paired: torch.Tensor, epi: int = 0, resid
     f32p = out.data_ptr() if epi <= 1 else None
     f16p = out.data_ptr() if epi >= 2 else None
     check(_pf().bonsai_bitgemm_prefill(w.codes.data_ptr(), w.scales.data_ptr(), x_paired.data_ptr(), x_paired.stride(0), f32p, ptr(residual),
-                                       f16p, status.data_ptr(), w.n, w.k, T, epi, out.stride(0), sms, stream()), "bitgemm_prefill")
+                                       f16p, status.data_ptr(), w.n, w.k, T, epi, out.stride(0), sms, None, stream()), "bitgemm_prefill")
     return out
 
 

@@ -200,6 +200,59 @@ class InferenceEngine:
                  stop_at_eos: bool = True) -> list[int]:
         return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos))
 
+    def generate_batch(self, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams | None = None,
+                       stop_at_eos: bool = True) -> list[list[int]]:
+        """Generates for several prompts at once (true batched decode: one GEMM per linear layer for all of them).
+
+        The reference's ``batch_generate`` runs the prompts one after another with a cache reset in between
+        (crates/oxibonsai-runtime/src/batch_engine.rs:81-165).
+        """
+        B = len(prompts)
+        if B == 0:
+            return []
+        if B > self.max_batch:
+            raise ValueError(f"{B} prompts exceed max_batch {self.max_batch}")
+        p = (params or self.sampling).validate()
+        r = self.runner
+        from dataclasses import replace
+        try:
+            for s, prompt in enumerate(prompts):
+                n = len(prompt)
+                self._bind_slot(s, min(self.max_seq_len, n + max_tokens))
+                self._set_sampling(s, replace(p, seed=p.seed + s))
+                if s == 0 or (n >= self.prefill_min_tokens and not self.exact):
+                    self.prefill(prompt, s)
+                else:
+                    # short prompts of other slots: run them through slot 0's token path is not possible, use the chunk kernels
+                    toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+                    r.prefill(toks, s, 0, self.prefill_chunk)
+            lens = torch.tensor([len(q) for q in prompts], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            K.sample(r.logits[:B], r.temps[:B], r.topks[:B], r.topps[:B], r.rng[:B], out=r.tokens[:B])
+            r.positions[:B].copy_(lens)
+            out: list[list[int]] = [[] for _ in range(B)]
+            done = [False] * B
+            host = torch.zeros(B, dtype=torch.int32).pin_memory()
+            for step in range(max_tokens):
+                host.copy_(r.tokens[:B], non_blocking=True)
+                torch.cuda.synchronize(self.device)
+                for s in range(B):
+                    if done[s]:
+                        continue
+                    tok = int(host[s])
+                    if stop_at_eos and tok == EOS_TOKEN:
+                        done[s] = True
+                        continue
+                    out[s].append(tok)
+                    if len(prompts[s]) + len(out[s]) >= self.max_seq_len:
+                        done[s] = True
+                if all(done) or step == max_tokens - 1:
+                    break
+                r.step(B, sample=True)
+            return out
+        finally:
+            for s in range(B):
+                self._release_slot(s)
+
     def generate_seeded(self, prompt: Sequence[int], max_tokens: int, seed: int, params: SamplingParams | None = None) -> list[int]:
         from dataclasses import replace
         return self.generate(prompt, max_tokens, replace(params or self.sampling, seed=seed))

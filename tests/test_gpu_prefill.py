@@ -98,3 +98,16 @@ def test_attn_prefill_matches_reference(kvt, tol, nq, nkv, hd, T, pos0):
     sc_ = sc_.masked_fill(~mask[None], float("-inf"))
     ref = torch.einsum("nts,snd->tnd", torch.softmax(sc_, -1), vv)
     assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("rows,cols,T", [(151936, 2048, 3), (1000, 4096, 64), (300, 256, 200)])
+def test_dense_f16_gemm_on_tcgen05(rows, cols, T):
+    from oxibonsai_b200.ops import cuda_ops as K
+    g = torch.Generator().manual_seed(41)
+    w = (torch.randn(rows, cols, generator=g) * 0.02).half().to(DEV)
+    x = torch.randn(T, cols, generator=g).half().to(DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y = K.dense_gemm_f16(w, x, status=st)
+    ref = x.float() @ w.float().T
+    assert st.item() == 0
+    assert (y - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
