@@ -472,6 +472,7 @@ int bonsai_bitgemv_tc(const void* codes, const void* scales, const void* xq, con
   if (ksplit > ngroups) ksplit = ngroups;
   if (ksplit > 1 && (partial == nullptr || counters == nullptr)) return BONSAI_CUDA_BAD_ARG;
   const int gps = (ngroups + ksplit - 1) / ksplit;
+  ksplit = (ngroups + gps - 1) / gps;   // no empty K slab: every CTA of a tile must arrive at its counter
   const int ntiles = (n_rows + 127) / 128;
   int columns = sms / ksplit;
   if (columns < 1) columns = 1;

@@ -310,6 +310,18 @@ class Qwen3Runner:
                     "prefill_chunk")
             done += T
 
+    def verify_greedy(self, tokens: torch.Tensor, slot: int, pos0: int) -> torch.Tensor:
+        """Feeds ``tokens`` (int32 device tensor, at most one prefill chunk) at positions pos0.. and returns the model's
+        greedy next token after each of them (int32 [T]) - the batched verification pass of speculative decoding."""
+        T = tokens.numel()
+        b = self._prefill_buffers(max(64, T))
+        b["tokens"][:T].copy_(tokens, non_blocking=True)
+        torch.arange(pos0, pos0 + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
+        K.check(K._pf().bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0, slot, 0, K.stream()), "prefill_chunk")
+        xn = K.norm_to_f16_paired(b["h"][:T], self.w.out_norm, self.cfg.eps, natural=True)
+        logits = K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"])
+        return K.sample(logits)
+
     def prefill_launches(self, n_tokens: int, chunk: int = 1024) -> int:
         chunks = -(-n_tokens // chunk)
         return chunks * (1 + 8 * self.cfg.layers) + 2

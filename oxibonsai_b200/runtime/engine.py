@@ -253,6 +253,35 @@ class InferenceEngine:
             for s in range(B):
                 self._release_slot(s)
 
+    # ---- single-step primitives (speculative decoding, schedulers) -------------------------------
+    def open_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None) -> int:
+        """Binds ``slot``, prefills ``prompt`` and returns the first sampled token."""
+        self._bind_slot(slot, min(self.max_seq_len, max_total))
+        self._set_sampling(slot, params or self.sampling)
+        self.prefill(prompt, slot)
+        r = self.runner
+        K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
+                 out=r.tokens[slot: slot + 1])
+        self._out_host[:1].copy_(r.tokens[slot: slot + 1], non_blocking=True)
+        torch.cuda.synchronize(self.device)
+        return int(self._out_host[0])
+
+    def decode_one(self, token: int, pos: int) -> int:
+        """Feeds ``token`` at position ``pos`` of slot 0 and returns the next sampled token."""
+        self._upload(0, token, pos)
+        self.runner.step(1, sample=True)
+        self._out_host[:1].copy_(self.runner.tokens[:1], non_blocking=True)
+        torch.cuda.synchronize(self.device)
+        return int(self._out_host[0])
+
+    def verify_greedy(self, tokens: Sequence[int], pos0: int, slot: int = 0) -> list[int]:
+        """Greedy next-token choices of the model after each of ``tokens`` placed at positions pos0.. (one batched pass)."""
+        t = torch.tensor([int(x) for x in tokens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        return self.runner.verify_greedy(t, slot, pos0).tolist()
+
+    def close_sequence(self, slot: int = 0) -> None:
+        self._release_slot(slot)
+
     def generate_seeded(self, prompt: Sequence[int], max_tokens: int, seed: int, params: SamplingParams | None = None) -> list[int]:
         from dataclasses import replace
         return self.generate(prompt, max_tokens, replace(params or self.sampling, seed=seed))
