@@ -10,7 +10,7 @@ import torch.distributed as dist
 
 
 def main():
-    path, mode = sys.argv[1], sys.argv[2]
+    path, mode, out_dir = sys.argv[1], sys.argv[2], sys.argv[3]
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -37,7 +37,8 @@ def main():
         same = all(torch.equal(gathered[0], t) for t in gathered)
         out.update(ok=(len(a) == 8 and same and sum(x == y for x, y in zip(a, b)) >= 6), a=a, b=b, same=same, status=eng.runner.tp.status())
     dist.barrier()
-    print("TPRESULT " + json.dumps(out), flush=True)
+    with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
+        json.dump(out, f)
     dist.destroy_process_group()
 
 
