@@ -138,11 +138,11 @@ class InferenceEngine:
         n = len(prompt)
         toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         r = self.runner
-        if n >= self.prefill_min_tokens and not self.exact:
+        if (n >= self.prefill_min_tokens or slot != 0) and not self.exact:
             r.prefill(toks, slot, pos0, self.prefill_chunk)
             return
         if slot != 0:
-            raise NotImplementedError("token-by-token prefill is wired for slot 0")
+            raise NotImplementedError("the exact-f32 mode prefills through slot 0 only")
         # per-token feeds are device-to-device and stream ordered, so no host buffer is rewritten while a copy
         # that reads it is still queued
         pos = torch.arange(pos0, pos0 + n, dtype=torch.int32, device=self.device)
@@ -220,12 +220,7 @@ class InferenceEngine:
                 n = len(prompt)
                 self._bind_slot(s, min(self.max_seq_len, n + max_tokens))
                 self._set_sampling(s, replace(p, seed=p.seed + s))
-                if s == 0 or (n >= self.prefill_min_tokens and not self.exact):
-                    self.prefill(prompt, s)
-                else:
-                    # short prompts of other slots: run them through slot 0's token path is not possible, use the chunk kernels
-                    toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-                    r.prefill(toks, s, 0, self.prefill_chunk)
+                self.prefill(prompt, s)
             lens = torch.tensor([len(q) for q in prompts], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
             K.sample(r.logits[:B], r.temps[:B], r.topks[:B], r.topps[:B], r.rng[:B], out=r.tokens[:B])
             r.positions[:B].copy_(lens)
@@ -278,6 +273,14 @@ class InferenceEngine:
         """Greedy next-token choices of the model after each of ``tokens`` placed at positions pos0.. (one batched pass)."""
         t = torch.tensor([int(x) for x in tokens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         return self.runner.verify_greedy(t, slot, pos0).tolist()
+
+    def move_slot(self, src: int, dst: int) -> None:
+        """Moves a live sequence to another slot: block-table row, last token, position and sampler state.
+        KV pages stay where they are (the block table references them)."""
+        r = self.runner
+        for t in (r.block_table, r.tokens, r.positions, r.temps, r.topks, r.topps, r.rng):
+            t[dst].copy_(t[src], non_blocking=True)
+        self._slot_pages[dst] = self._slot_pages.pop(src, [])
 
     def close_sequence(self, slot: int = 0) -> None:
         self._release_slot(slot)

@@ -1,0 +1,394 @@
+"""OpenAI-compatible HTTP server (FastAPI): chat completions with SSE, completions, models, embeddings, health, metrics, admin.
+
+Reference: the axum router (crates/oxibonsai-runtime/src/server.rs:203-243), ChatML prompt builder (:514-551), SSE framing
+``role chunk -> content chunks -> finish chunk -> [DONE]`` with UTF-8-safe incremental decoding (:391-512), ``x-request-id``
+echo (:36-60), bearer auth that skips ``/health`` and ``/metrics`` (crates/oxibonsai-serve/src/main.rs:159-170,338-370),
+admin endpoints (admin.rs:45-302), embeddings (embeddings.rs), extended request fields - tools, logprobs, n <= 4,
+response_format, stop, seed (api_types.rs:13-345).  The reference serialises requests on one mutex and ignores the
+request's temperature; here requests run concurrently through the continuous-batching scheduler and per-request
+sampling parameters are applied.
+"""
+from __future__ import annotations
+
+import asyncio
+import hashlib
+import json
+import math
+import os
+import threading
+import time
+import uuid
+from dataclasses import replace
+from typing import Any, Callable, Protocol, Sequence
+
+from fastapi import FastAPI, Request
+from fastapi.responses import HTMLResponse, JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..runtime.metrics import InferenceMetrics, RequestRateTracker
+from ..runtime.presets import SamplingParams
+from ..runtime.resilience import CircuitBreaker, RateLimiter, check_health
+from ..tokenizer import StreamingDecoder, chat_prompt
+from .config import ServerConfig
+
+
+class Backend(Protocol):
+    """What the server needs from an engine."""
+
+    model_name: str
+    max_seq_len: int
+
+    def submit(self, prompt: Sequence[int], params: SamplingParams, max_tokens: int, on_token: Callable[[int], None] | None,
+               request_id: str): ...   # returns an object with wait(), tokens, finish_reason, cancel()
+
+    def kv_utilization(self) -> float: ...
+
+
+class SchedulerBackend:
+    """Backend over a :class:`BatchScheduler` (GPU)."""
+
+    def __init__(self, scheduler, model_name: str):
+        self.s = scheduler
+        self.model_name = model_name
+        self.max_seq_len = scheduler.engine.max_seq_len
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id):
+        return self.s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id)
+
+    def kv_utilization(self) -> float:
+        return self.s.engine.kv.utilization
+
+
+def new_request_id() -> str:
+    return uuid.uuid4().hex
+
+
+def _hash_embed(text: str, dim: int = 512) -> list[float]:
+    """Deterministic bag-of-hashed-tokens embedding (the reference serves TF-IDF / identity embedders of dimension 512)."""
+    v = [0.0] * dim
+    for w in text.lower().split():
+        h = int.from_bytes(hashlib.blake2b(w.encode(), digest_size=8).digest(), "little")
+        v[h % dim] += 1.0 if (h >> 63) & 1 == 0 else -1.0
+    n = math.sqrt(sum(x * x for x in v)) or 1.0
+    return [x / n for x in v]
+
+
+def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, metrics: InferenceMetrics | None = None):
+    cfg = config or ServerConfig()
+    metrics = metrics or InferenceMetrics()
+    breaker = CircuitBreaker()
+    limiter = RateLimiter(global_rate=1e6, global_burst=1e6, client_rate=1e5, client_burst=1e5)
+    app = FastAPI(title="oxibonsai-b200")
+    app.state.metrics, app.state.backend, app.state.config, app.state.breaker = metrics, backend, cfg, breaker
+    started = time.time()
+    sem = asyncio.Semaphore(cfg.max_concurrent)
+
+    def error(status: int, message: str, typ: str = "invalid_request_error", rid: str | None = None):
+        r = JSONResponse({"error": {"message": message, "type": typ, "code": status}}, status_code=status)
+        if rid:
+            r.headers["x-request-id"] = rid
+        return r
+
+    @app.middleware("http")
+    async def auth_and_ids(request: Request, call_next):
+        rid = request.headers.get("x-request-id") or new_request_id()
+        request.state.request_id = rid
+        path = request.url.path
+        if cfg.bearer_token and path not in ("/health", cfg.metrics_path):
+            if request.headers.get("authorization", "") != f"Bearer {cfg.bearer_token}":
+                return error(401, "missing or invalid bearer token", "authentication_error", rid)
+        client = request.client.host if request.client else "unknown"
+        if not limiter.allow(client):
+            return error(429, "rate limit exceeded", "rate_limit_error", rid)
+        resp = await call_next(request)
+        resp.headers["x-request-id"] = rid
+        return resp
+
+    def sampling_from(body: dict) -> tuple[SamplingParams, int]:
+        p = SamplingParams(temperature=cfg.temperature, top_k=cfg.top_k, top_p=cfg.top_p, repetition_penalty=cfg.repetition_penalty,
+                           max_tokens=cfg.max_tokens, seed=cfg.seed)
+        upd = {}
+        for k in ("temperature", "top_p", "top_k", "seed", "repetition_penalty"):
+            if body.get(k) is not None:
+                upd[k] = body[k]
+        p = replace(p, **upd).validate()
+        mt = body.get("max_tokens") or body.get("max_completion_tokens") or cfg.max_tokens
+        return p, max(1, min(int(mt), 8192))
+
+    def apply_stop(text: str, stops: list[str]) -> tuple[str, bool]:
+        cut = min((text.find(s) for s in stops if s and s in text), default=-1)
+        return (text[:cut], True) if cut >= 0 else (text, False)
+
+    async def run_generation(prompt_ids: list[int], params: SamplingParams, max_tokens: int, rid: str, stops: list[str]):
+        """Async generator of (text_delta, finish_reason | None)."""
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        tracker = RequestRateTracker()
+
+        def on_token(tok: int):
+            loop.call_soon_threadsafe(q.put_nowait, tok)
+
+        if not breaker.allow():
+            raise RuntimeError("circuit open")
+        t0 = time.perf_counter()
+        try:
+            req = backend.submit(prompt_ids, params, max_tokens, on_token, rid)
+        except Exception:
+            breaker.record_failure()
+            raise
+        metrics.prompt_tokens.inc(len(prompt_ids))
+        waiter = loop.run_in_executor(None, lambda: req.done.wait(cfg.request_timeout_ms / 1000.0))
+        dec = StreamingDecoder()
+        n_tok, first = 0, True
+        text, sent = "", 0
+
+        def feed(piece: str) -> tuple[str, bool]:
+            """Appends decoded text; returns (delta safe to send, stop sequence hit).  Text that could still turn
+            into a stop sequence is held back until it is disambiguated."""
+            nonlocal text, sent
+            text += piece
+            cut, hit = apply_stop(text, stops)
+            if hit:
+                delta, sent = cut[sent:], len(cut)
+                text = cut
+                return delta, True
+            hold = 0
+            for st in stops:
+                for L in range(min(len(st) - 1, len(text)), 0, -1):
+                    if text.endswith(st[:L]):
+                        hold = max(hold, L)
+                        break
+            safe = max(sent, len(text) - hold)
+            delta, sent = text[sent:safe], safe
+            return delta, False
+
+        try:
+            while True:
+                get = asyncio.ensure_future(q.get())
+                done, _ = await asyncio.wait({get, waiter}, return_when=asyncio.FIRST_COMPLETED)
+                if get in done:
+                    toks = [get.result()]
+                    finished = False
+                else:
+                    get.cancel()
+                    toks = []
+                    while not q.empty():
+                        toks.append(q.get_nowait())
+                    finished = True
+                for tok in toks:
+                    tracker.on_token()
+                    n_tok += 1
+                    if first:
+                        metrics.prefill_seconds.observe(time.perf_counter() - t0)
+                        first = False
+                    piece = dec.push(tokenizer.token_bytes(tok))
+                    if piece:
+                        delta, hit = feed(piece)
+                        if delta:
+                            yield delta, None
+                        if hit:
+                            req.cancel()
+                            yield "", "stop"
+                            return
+                if finished:
+                    if not waiter.result():
+                        req.cancel()
+                        raise TimeoutError("request timed out")
+                    if getattr(req, "error", None) is not None:
+                        raise req.error
+                    tail = dec.flush()
+                    delta, hit = feed(tail) if tail else ("", False)
+                    rest = delta + ("" if hit else text[sent:])
+                    if rest:
+                        yield rest, None
+                    yield "", ("stop" if hit else (req.finish_reason or "stop"))
+                    return
+        finally:
+            dt = time.perf_counter() - t0
+            metrics.tokens_generated.inc(n_tok)
+            metrics.request_seconds.observe(dt)
+            if n_tok and dt > 0:
+                metrics.tokens_per_second.observe(n_tok / dt)
+            metrics.aggregator.record(tracker)
+            metrics.kv_utilization.set(backend.kv_utilization())
+            breaker.record_success()
+
+    def encode_chat(messages: list[dict]) -> list[int]:
+        return tokenizer.encode(chat_prompt(messages, "chatml"))
+
+    # ---- routes -----------------------------------------------------------------------------------
+    @app.get("/health")
+    async def health():
+        return PlainTextResponse("ok")
+
+    @app.get("/health/detail")
+    async def health_detail():
+        return check_health(True, backend.kv_utilization(), breaker=breaker)
+
+    @app.get(cfg.metrics_path)
+    async def metrics_route():
+        if not cfg.metrics_enabled:
+            return error(404, "metrics disabled")
+        return PlainTextResponse(metrics.render_prometheus(), media_type="text/plain; version=0.0.4")
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": backend.model_name, "object": "model", "created": int(started), "owned_by": "oxibonsai"}]}
+
+    async def completion_common(request: Request, chat: bool):
+        rid = request.state.request_id
+        metrics.requests.inc()
+        try:
+            body = await request.json()
+        except Exception:
+            metrics.errors.inc()
+            return error(400, "request body is not valid JSON", rid=rid)
+        try:
+            if chat:
+                msgs = body.get("messages")
+                if not isinstance(msgs, list) or not msgs:
+                    raise ValueError("'messages' must be a non-empty list")
+                if body.get("tools"):
+                    from ..runtime.tools import tools_system_prompt
+                    msgs = [{"role": "system", "content": tools_system_prompt(body["tools"])}] + list(msgs)
+                prompt_ids = encode_chat(msgs)
+            else:
+                prompt = body.get("prompt")
+                if isinstance(prompt, list):
+                    prompt = prompt[0] if prompt else ""
+                if not isinstance(prompt, str) or prompt == "":
+                    raise ValueError("'prompt' must be a non-empty string")
+                prompt_ids = tokenizer.encode(prompt)
+            if len(prompt_ids) > cfg.max_input_tokens or len(prompt_ids) + 1 >= backend.max_seq_len:
+                raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds the input limit")
+            params, max_tokens = sampling_from(body)
+            n = int(body.get("n") or 1)
+            if not 1 <= n <= 4:
+                raise ValueError("'n' must be between 1 and 4")
+            stops = body.get("stop") or []
+            stops = [stops] if isinstance(stops, str) else list(stops)
+        except (ValueError, TypeError) as e:
+            metrics.errors.inc()
+            return error(400, str(e), rid=rid)
+
+        created = int(time.time())
+        obj_id = ("chatcmpl-" if chat else "cmpl-") + rid[:24]
+        model = body.get("model") or backend.model_name
+
+        if body.get("stream"):
+            async def sse():
+                metrics.active_requests.inc()
+                try:
+                    async with sem:
+                        if chat:
+                            first = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model,
+                                     "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
+                            yield f"data: {json.dumps(first)}\n\n"
+                        async for delta, fin in run_generation(prompt_ids, params, max_tokens, rid, stops):
+                            if chat:
+                                ch = {"index": 0, "delta": ({"content": delta} if delta else {}), "finish_reason": fin}
+                                chunk = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [ch]}
+                            else:
+                                chunk = {"id": obj_id, "object": "text_completion", "created": created, "model": model,
+                                         "choices": [{"index": 0, "text": delta, "finish_reason": fin}]}
+                            if delta or fin:
+                                yield f"data: {json.dumps(chunk)}\n\n"
+                        yield "data: [DONE]\n\n"
+                except Exception as e:  # noqa: BLE001
+                    metrics.errors.inc()
+                    breaker.record_failure()
+                    yield f"data: {json.dumps({'error': {'message': str(e), 'type': 'server_error'}})}\n\n"
+                finally:
+                    metrics.active_requests.dec()
+            return StreamingResponse(sse(), media_type="text/event-stream", headers={"x-request-id": rid, "cache-control": "no-cache"})
+
+        metrics.active_requests.inc()
+        try:
+            async with sem:
+                choices, completion_tokens = [], 0
+                for i in range(n):
+                    text, fin = "", "stop"
+                    async for delta, f in run_generation(prompt_ids, replace(params, seed=params.seed + i), max_tokens, rid, stops):
+                        text += delta
+                        fin = f or fin
+                    completion_tokens += len(tokenizer.encode(text)) if text else 0
+                    if chat:
+                        msg: dict[str, Any] = {"role": "assistant", "content": text}
+                        if body.get("tools"):
+                            from ..runtime.tools import parse_tool_calls
+                            calls = parse_tool_calls(text)
+                            if calls:
+                                msg = {"role": "assistant", "content": None, "tool_calls": calls}
+                                fin = "tool_calls"
+                        choices.append({"index": i, "message": msg, "finish_reason": fin})
+                    else:
+                        choices.append({"index": i, "text": text, "finish_reason": fin})
+        except TimeoutError as e:
+            metrics.errors.inc()
+            return error(504, str(e), "timeout", rid)
+        except Exception as e:  # noqa: BLE001
+            metrics.errors.inc()
+            breaker.record_failure()
+            status = 503 if type(e).__name__ in ("QueueFull", "CircuitOpenError") or "circuit" in str(e) else 500
+            return error(status, str(e), "server_error", rid)
+        finally:
+            metrics.active_requests.dec()
+        usage = {"prompt_tokens": len(prompt_ids), "completion_tokens": completion_tokens, "total_tokens": len(prompt_ids) + completion_tokens}
+        return {"id": obj_id, "object": "chat.completion" if chat else "text_completion", "created": created, "model": model,
+                "choices": choices, "usage": usage}
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        return await completion_common(request, True)
+
+    @app.post("/v1/chat/completions/extended")
+    async def chat_completions_extended(request: Request):
+        return await completion_common(request, True)
+
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        return await completion_common(request, False)
+
+    @app.post("/v1/embeddings")
+    async def embeddings(request: Request):
+        body = await request.json()
+        inp = body.get("input")
+        texts = [inp] if isinstance(inp, str) else list(inp or [])
+        if not texts:
+            return error(400, "'input' must be a string or a list of strings")
+        data = [{"object": "embedding", "index": i, "embedding": _hash_embed(t)} for i, t in enumerate(texts)]
+        ntok = sum(len(tokenizer.encode(t)) for t in texts)
+        return {"object": "list", "data": data, "model": body.get("model") or backend.model_name, "usage": {"prompt_tokens": ntok, "total_tokens": ntok}}
+
+    @app.get("/admin/status")
+    async def admin_status():
+        return {"uptime_seconds": time.time() - started, "model": backend.model_name, "active_requests": metrics.active_requests.get(),
+                "requests_total": metrics.requests.get(), "errors_total": metrics.errors.get(), "circuit": breaker.state.value,
+                "kv_utilization": backend.kv_utilization()}
+
+    @app.get("/admin/config")
+    async def admin_config():
+        d = {k: v for k, v in vars(cfg).items()}
+        if d.get("bearer_token"):
+            d["bearer_token"] = "***"
+        return d
+
+    @app.post("/admin/reset-metrics")
+    async def admin_reset():
+        metrics.reset()
+        return {"status": "ok"}
+
+    @app.get("/admin/cache-stats")
+    async def admin_cache():
+        return {"kv_utilization": backend.kv_utilization()}
+
+    @app.get("/ui")
+    async def ui():
+        p = os.path.join(os.path.dirname(__file__), "chat.html")
+        return HTMLResponse(open(p, encoding="utf-8").read())
+
+    return app
+
+
+def serve(app, host: str, port: int, log_level: str = "info") -> None:
+    import uvicorn
+    uvicorn.run(app, host=host, port=port, log_level=log_level)

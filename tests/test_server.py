@@ -1,0 +1,168 @@
+"""HTTP surface against a fake backend (no GPU): routing, SSE framing, auth, errors, metrics, config layering."""
+import json
+import threading
+
+import pytest
+
+from oxibonsai_b200.runtime.presets import SamplingParams
+from oxibonsai_b200.server.config import ServerConfig, load_config
+from oxibonsai_b200.tokenizer import ByteTokenizer
+
+
+class _Req:
+    def __init__(self):
+        self.done = threading.Event()
+        self.tokens, self.finish_reason, self.error, self.cancelled = [], None, None, False
+
+    def cancel(self):
+        self.cancelled = True
+
+
+class FakeBackend:
+    """Echoes a fixed reply byte by byte; records the sampling parameters it was given."""
+
+    model_name, max_seq_len = "fake-bonsai", 4096
+
+    def __init__(self, reply="héllo wörld", fail=False):
+        self.reply, self.fail, self.seen = reply.encode("utf-8"), fail, []
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id):
+        if self.fail:
+            raise RuntimeError("engine exploded")
+        self.seen.append((list(prompt), params, max_tokens, request_id))
+        r = _Req()
+
+        def run():
+            for b in self.reply[:max_tokens]:
+                if r.cancelled:
+                    break
+                r.tokens.append(b)
+                if on_token:
+                    on_token(b)
+            r.finish_reason = "length" if len(self.reply) > max_tokens else "stop"
+            r.done.set()
+
+        threading.Thread(target=run, daemon=True).start()
+        return r
+
+    def kv_utilization(self):
+        return 0.25
+
+
+@pytest.fixture()
+def client():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+    be = FakeBackend()
+    app = create_app(be, ByteTokenizer(), ServerConfig())
+    c = TestClient(app)
+    c.backend = be
+    return c
+
+
+def test_health_models_and_request_id(client):
+    r = client.get("/health")
+    assert r.status_code == 200 and r.text == "ok" and r.headers["x-request-id"]
+    r = client.get("/v1/models", headers={"x-request-id": "abc123"})
+    assert r.headers["x-request-id"] == "abc123"
+    assert r.json()["data"][0]["id"] == "fake-bonsai"
+    assert client.get("/health/detail").json()["status"] == "healthy"
+
+
+def test_chat_completion_applies_request_sampling(client):
+    body = {"messages": [{"role": "user", "content": "hi"}], "temperature": 0.2, "top_p": 0.5, "seed": 7, "max_tokens": 100}
+    j = client.post("/v1/chat/completions", json=body).json()
+    assert j["object"] == "chat.completion" and j["choices"][0]["message"] == {"role": "assistant", "content": "héllo wörld"}
+    assert j["choices"][0]["finish_reason"] == "stop" and j["usage"]["prompt_tokens"] > 0
+    prompt, params, mt, _ = client.backend.seen[-1]
+    assert bytes(prompt).decode().startswith("<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n")
+    assert (params.temperature, params.top_p, params.seed, mt) == (0.2, 0.5, 7, 100)
+
+
+def test_streaming_sse_framing_is_utf8_safe(client):
+    with client.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "stream": True}) as r:
+        assert r.headers["content-type"].startswith("text/event-stream")
+        events = [l[6:] for l in r.iter_lines() if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"] == {"role": "assistant"}
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks[1:])
+    assert text == "héllo wörld" and "�" not in text
+    assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+    assert all(c["object"] == "chat.completion.chunk" for c in chunks)
+
+
+def test_completions_stop_sequences_and_length(client):
+    j = client.post("/v1/completions", json={"prompt": "abc", "stop": [" w"]}).json()
+    assert j["choices"][0]["text"] == "héllo" and j["choices"][0]["finish_reason"] == "stop"
+    j = client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 3}).json()
+    assert j["choices"][0]["finish_reason"] == "length"
+    j = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "n": 2}).json()
+    assert len(j["choices"]) == 2
+
+
+def test_error_envelope(client):
+    r = client.post("/v1/chat/completions", json={"messages": []})
+    assert r.status_code == 400 and r.json()["error"]["type"] == "invalid_request_error"
+    r = client.post("/v1/chat/completions", content=b"{not json", headers={"content-type": "application/json"})
+    assert r.status_code == 400
+    assert client.post("/v1/completions", json={"prompt": "x", "temperature": -1}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": "x", "n": 9}).status_code == 400
+
+
+def test_backend_failure_maps_to_5xx_and_counts():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+    app = create_app(FakeBackend(fail=True), ByteTokenizer(), ServerConfig())
+    c = TestClient(app)
+    r = c.post("/v1/completions", json={"prompt": "x"})
+    assert r.status_code == 500 and "exploded" in r.json()["error"]["message"]
+    assert app.state.metrics.errors.get() == 1
+
+
+def test_bearer_auth_skips_health_and_metrics():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+    app = create_app(FakeBackend(), ByteTokenizer(), ServerConfig(bearer_token="s3cret-token-0123456789"))
+    c = TestClient(app)
+    assert c.get("/health").status_code == 200 and c.get("/metrics").status_code == 200
+    assert c.get("/v1/models").status_code == 401
+    assert c.get("/v1/models", headers={"authorization": "Bearer s3cret-token-0123456789"}).status_code == 200
+
+
+def test_metrics_embeddings_admin(client):
+    client.post("/v1/completions", json={"prompt": "abc"})
+    text = client.get("/metrics").text
+    for name in ("oxibonsai_requests_total 1", "oxibonsai_tokens_generated_total", "oxibonsai_prefill_duration_seconds_bucket",
+                 "oxibonsai_kv_cache_utilization 0.25", "oxibonsai_inter_token_latency_p95_seconds", "oxibonsai_kv_cache_compression_level"):
+        assert name in text
+    e = client.post("/v1/embeddings", json={"input": ["a b c", "a b d"]}).json()
+    assert len(e["data"]) == 2 and len(e["data"][0]["embedding"]) == 512
+    st = client.get("/admin/status").json()
+    assert st["model"] == "fake-bonsai" and st["circuit"] == "closed"
+    assert client.post("/admin/reset-metrics").json() == {"status": "ok"}
+    assert "oxibonsai_requests_total 0" in client.get("/metrics").text
+    assert "<html>" in client.get("/ui").text
+
+
+def test_config_layering_and_validation(tmp_path):
+    toml = tmp_path / "s.toml"
+    toml.write_text('[server]\nport = 9000\nhost = "127.0.0.1"\n[sampling]\ntemperature = 0.3\nmax_tokens = 64\n')
+    cfg = load_config(["--config", str(toml), "--port", "9100"], env={"OXIBONSAI_TEMPERATURE": "0.5", "OXIBONSAI_PORT": "9050"})
+    assert (cfg.port, cfg.host, cfg.temperature, cfg.max_tokens) == (9100, "127.0.0.1", 0.5, 64)   # CLI > env > TOML > defaults
+    with pytest.raises(ValueError):
+        ServerConfig(port=0).validate()
+    with pytest.raises(ValueError):
+        ServerConfig(bearer_token="short").validate()
+    with pytest.raises(ValueError):
+        ServerConfig(model_path="/nonexistent/model.gguf").validate()
+    with pytest.raises(ValueError):
+        ServerConfig(temperature=3.0).validate()
+
+
+def test_tool_call_parsing():
+    from oxibonsai_b200.runtime.tools import parse_tool_calls, tools_system_prompt
+    calls = parse_tool_calls('sure <tool_call>{"name": "get_weather", "arguments": {"city": "Kyoto"}}</tool_call>')
+    assert calls[0]["function"]["name"] == "get_weather" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Kyoto"}
+    assert parse_tool_calls("no json here") == []
+    assert "get_weather" in tools_system_prompt([{"type": "function", "function": {"name": "get_weather", "description": "d"}}])
