@@ -31,10 +31,10 @@ __global__ void tp_barrier_kernel(TpComm c) {
 
 // Vocab-parallel LM head: copy this rank's logits slice [batch][rows] into every rank's full
 // logits area at column row0.
-__global__ void tp_push_logits_kernel(TpComm c, const float* __restrict__ local, int batch, int rows, int row0, int vocab) {
+__global__ void tp_push_logits_kernel(TpComm c, const float* __restrict__ local, int slot0, int batch, int rows, int row0, int vocab) {
   const size_t total = (size_t)batch * rows;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int b = (int)(i / rows), r = (int)(i % rows);
+    const int b = slot0 + (int)(i / rows), r = (int)(i % rows);
     const float v = local[i];
     for (int p = 0; p < c.size; ++p) reinterpret_cast<float*>(c.peer[p] + c.lay.off_logits)[(size_t)b * vocab + row0 + r] = v;
   }
@@ -53,6 +53,47 @@ __global__ void tp_reduce_broadcast_kernel(TpComm c, size_t n) {
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
     for (int p = 0; p < c.size; ++p) reinterpret_cast<float4*>(c.peer[p] + c.lay.off_big)[i] = s;
+  }
+}
+
+// One-shot all-reduce fused with the residual add, for small tensors (a decode batch): every rank has
+// written its partial sums into its own big area at float4 offset off4.  One launch does the entry
+// barrier (CTA 0 tells the peers, every CTA waits for all of them), then h += sum over ranks in rank
+// order through peer loads, so all ranks hold bit-identical h.  There is no exit barrier: callers
+// alternate between the two halves of the big area, and a rank can only reach its next write of a
+// half after all peers have entered the all-reduce in between, i.e. finished reading that half.
+__global__ void tp_allreduce_oneshot_add_kernel(TpComm c, float* __restrict__ h, size_t n4, size_t off4) {
+  __shared__ int s_e;
+  if (threadIdx.x == 0) s_e = ld_volatile(c.bar_epoch);
+  __syncthreads();
+  const int want = s_e + 1;
+  if (threadIdx.x < c.size) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<int*>(c.peer[threadIdx.x] + c.lay.off_bar_flags) + c.rank, want);
+    }
+    const int* mine = reinterpret_cast<const int*>(c.peer[c.rank] + c.lay.off_bar_flags) + threadIdx.x;
+    if (!tp_wait_flag(mine, want)) atomicExch(c.status, 4);
+  }
+  __syncthreads();
+  float4* h4 = reinterpret_cast<float4*>(h);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    float4 s = h4[i];
+    for (int p = 0; p < c.size; ++p) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(c.peer[p] + c.lay.off_big) + off4 + i);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    h4[i] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(c.done_ctr, 1);
+    if (prev == (int)gridDim.x - 1) {   // every CTA has read bar_epoch by now
+      *c.done_ctr = 0;
+      *c.bar_epoch = want;
+      __threadfence();
+    }
   }
 }
 
@@ -112,16 +153,21 @@ int bonsai_tp_barrier(void* comm, cudaStream_t stream) {
 
 // Gathers [batch][rows] logits slices of all ranks into this rank's full logits area (and everyone else's).
 // On return of the second barrier the area holds [batch][vocab]; its address is bonsai_tp_logits_ptr().
-int bonsai_tp_allgather_logits(void* comm, const float* local, int batch, int rows, int row0, int vocab, cudaStream_t stream) {
+// `local` holds rows of logits slots slot0 .. slot0+batch-1.
+int bonsai_tp_allgather_logits_at(void* comm, const float* local, int slot0, int batch, int rows, int row0, int vocab,
+                                  cudaStream_t stream) {
   using namespace bonsai;
   TpComm& c = *static_cast<TpComm*>(comm);
   if (rows > 0) {
     int grid = (int)(((size_t)batch * rows + 255) / 256);
     if (grid > 296) grid = 296;
-    tp_push_logits_kernel<<<grid, 256, 0, stream>>>(c, local, batch, rows, row0, vocab);
+    tp_push_logits_kernel<<<grid, 256, 0, stream>>>(c, local, slot0, batch, rows, row0, vocab);
   }
   tp_barrier_kernel<<<1, 32, 0, stream>>>(c);
   return launch_status();
+}
+int bonsai_tp_allgather_logits(void* comm, const float* local, int batch, int rows, int row0, int vocab, cudaStream_t stream) {
+  return bonsai_tp_allgather_logits_at(comm, local, 0, batch, rows, row0, vocab, stream);
 }
 void* bonsai_tp_logits_ptr(void* comm) {
   bonsai::TpComm& c = *static_cast<bonsai::TpComm*>(comm);
@@ -142,6 +188,25 @@ int bonsai_tp_allreduce_big_add(void* comm, float* h, size_t n, cudaStream_t str
   tp_barrier_kernel<<<1, 32, 0, stream>>>(c);
   tp_add_kernel<<<296, 256, 0, stream>>>(h, reinterpret_cast<const float*>(c.peer[c.rank] + c.lay.off_big), n);
   return launch_status();
+}
+
+// h[n] += sum over ranks of the partial sums every rank wrote into half `half` (0 or 1) of its big area
+// (address: bonsai_tp_big_half_ptr).  One kernel; consecutive calls must alternate halves.
+int bonsai_tp_allreduce_oneshot_add(void* comm, float* h, size_t n, int half, cudaStream_t stream) {
+  using namespace bonsai;
+  TpComm& c = *static_cast<TpComm*>(comm);
+  const size_t half_elems = (c.lay.big_elems / 2) & ~(size_t)3;
+  if (n % 4 != 0 || n > half_elems || half < 0 || half > 1) return BONSAI_CUDA_BAD_ARG;
+  int grid = (int)((n / 4 + 255) / 256);
+  if (grid > 148) grid = 148;
+  if (grid < 1) grid = 1;
+  tp_allreduce_oneshot_add_kernel<<<grid, 256, 0, stream>>>(c, h, n / 4, (size_t)half * half_elems / 4);
+  return launch_status();
+}
+void* bonsai_tp_big_half_ptr(void* comm, int half) {
+  bonsai::TpComm& c = *static_cast<bonsai::TpComm*>(comm);
+  const size_t half_elems = (c.lay.big_elems / 2) & ~(size_t)3;
+  return c.peer[c.rank] + c.lay.off_big + (size_t)half * half_elems * sizeof(float);
 }
 
 }  // extern "C"

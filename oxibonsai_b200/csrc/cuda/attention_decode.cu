@@ -281,6 +281,239 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
   }
 }
 
+// ---- head_dim 128, compressed caches: half a warp per token --------------------------------------------
+// A 128-wide f16 row is 256 bytes = 16 lanes x 16 bytes, so the two halves of a warp walk two tokens
+// at once with full-width loads; kH128Unroll such pairs are requested before any is consumed (8
+// tokens x 2 rows in flight per warp).  Each half keeps its own online-softmax state, the halves are
+// folded with shuffles at the end, and from there on the warp / split merges are those of the
+// generic kernel above.  Q8 rows are 8-byte loads plus the row scale, Q4 rows 4-byte loads.
+constexpr int kH128Unroll = 4;
+
+template <int KVT>
+struct RawRow8 {
+  uint4 v;   // F16: 8 halves; Q8: x,y = 8 int8; Q4: x = 8 nibbles
+  float s;
+};
+
+template <int KVT>
+__device__ __forceinline__ void load_raw8(const uint8_t* base, const float* scales, size_t row, int sub, RawRow8<KVT>& r) {
+  if (KVT == KV_F16) {
+    r.v = *reinterpret_cast<const uint4*>(base + row * 256 + sub * 16);
+    r.s = 1.0f;
+  } else if (KVT == KV_Q8) {
+    const uint2 t = *reinterpret_cast<const uint2*>(base + row * 128 + sub * 8);
+    r.v = make_uint4(t.x, t.y, 0u, 0u);
+    r.s = scales[row];
+  } else {
+    r.v = make_uint4(*reinterpret_cast<const uint32_t*>(base + row * 64 + sub * 4), 0u, 0u, 0u);
+    r.s = scales[row];
+  }
+}
+
+template <int KVT>
+__device__ __forceinline__ void unpack8(const RawRow8<KVT>& r, float* out) {
+  if (KVT == KV_F16) {
+    const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      out[2 * j] = f.x;
+      out[2 * j + 1] = f.y;
+    }
+  } else if (KVT == KV_Q8) {
+    const uint32_t w[2] = {r.v.x, r.v.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = r.s * (float)(int)(int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = r.s * (float)((int)((r.v.x >> (4 * j)) & 15u) - 8);
+  }
+}
+
+template <int KVT, int G>
+__global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* __restrict__ q, const int* __restrict__ positions,
+                                                                 const int* __restrict__ block_table, int max_pages, KvPool pool,
+                                                                 int nq, float sm_scale, float* __restrict__ ws_acc,
+                                                                 float* __restrict__ ws_ml, int* __restrict__ counters,
+                                                                 float* __restrict__ out, int extra_len) {
+  extern __shared__ float sh[];  // [8 warps][G][hd + 2]
+  __shared__ int s_last;
+  constexpr int hd = 128;
+  const int nkv = pool.kv_heads;
+  const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, sub = lane & 15;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int len = positions[b] + 1 + extra_len;
+  const int chunk = (len + nsplit - 1) / nsplit;
+  const int t0 = split * chunk, t1 = min(len, t0 + chunk);
+
+  float qr[G][8], acc[G][8], m[G], l[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float4* qp = reinterpret_cast<const float4*>(q + ((size_t)b * nq + kvh * G + g) * hd + sub * 8);
+    const float4 a = qp[0], c = qp[1];
+    qr[g][0] = a.x * sm_scale; qr[g][1] = a.y * sm_scale; qr[g][2] = a.z * sm_scale; qr[g][3] = a.w * sm_scale;
+    qr[g][4] = c.x * sm_scale; qr[g][5] = c.y * sm_scale; qr[g][6] = c.z * sm_scale; qr[g][7] = c.w * sm_scale;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+  }
+  const int* bt = block_table + (size_t)b * max_pages;
+  constexpr int kTok = 2 * kH128Unroll;   // tokens per warp iteration
+  for (int tb = t0 + warp * kTok; tb < t1; tb += kAttnWarps * kTok) {
+    RawRow8<KVT> kr[kH128Unroll], vr[kH128Unroll];
+    bool valid[kH128Unroll];
+#pragma unroll
+    for (int u = 0; u < kH128Unroll; ++u) {
+      const int t = tb + 2 * u + half;
+      valid[u] = t < t1;
+      const int tt = valid[u] ? t : t0;
+      const int page = bt[tt / pool.page_size];
+      const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (tt % pool.page_size);
+      load_raw8<KVT>(pool.k, pool.k_scale, row, sub, kr[u]);
+      load_raw8<KVT>(pool.v, pool.v_scale, row, sub, vr[u]);
+    }
+    float s[kH128Unroll][G];
+#pragma unroll
+    for (int u = 0; u < kH128Unroll; ++u) {
+      float kf[8];
+      unpack8<KVT>(kr[u], kf);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaf(qr[g][j], kf[j], a);
+        s[u][g] = a;
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < kH128Unroll; ++u)
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
+    float p[kH128Unroll][G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mn = m[g];
+#pragma unroll
+      for (int u = 0; u < kH128Unroll; ++u)
+        if (valid[u]) mn = fmaxf(mn, s[u][g]);
+      const float r = expf(m[g] - mn);   // exp(-inf) = 0 before the first token; a half with no token yet keeps m = -inf
+      float ps = 0.0f;
+#pragma unroll
+      for (int u = 0; u < kH128Unroll; ++u) {
+        p[u][g] = valid[u] ? expf(s[u][g] - mn) : 0.0f;
+        ps += p[u][g];
+      }
+      const float rr = (mn == -INFINITY) ? 1.0f : r;
+      l[g] = l[g] * rr + ps;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] *= rr;
+      m[g] = mn;
+    }
+#pragma unroll
+    for (int u = 0; u < kH128Unroll; ++u) {
+      float vf[8];
+      unpack8<KVT>(vr[u], vf);
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(p[u][g], vf[j], acc[g][j]);
+    }
+  }
+  // fold the two halves of the warp (they saw different tokens)
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float mo = __shfl_xor_sync(0xffffffffu, m[g], 16), lo = __shfl_xor_sync(0xffffffffu, l[g], 16);
+    const float M = fmaxf(m[g], mo);
+    const float fa = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - M), fb = (mo == -INFINITY) ? 0.0f : expf(mo - M);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], 16);
+      acc[g][j] = fa * acc[g][j] + fb * ao;
+    }
+    l[g] = fa * l[g] + fb * lo;
+    m[g] = M;
+  }
+  // combine the warps (same scheme as the generic kernel)
+  const int stride = hd + 2;
+  if (half == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* dst = sh + ((size_t)warp * G + g) * stride;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[sub * 8 + j] = acc[g][j];
+      if (sub == 0) {
+        dst[hd] = m[g];
+        dst[hd + 1] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    int g = idx / hd, d = idx - g * hd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
+    float a = 0.0f, L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float* src = sh + ((size_t)w * G + g) * stride;
+      float f = (src[hd] == -INFINITY) ? 0.0f : expf(src[hd] - M);
+      a += f * src[d];
+      L += f * src[hd + 1];
+    }
+    size_t o = (((size_t)b * nq + kvh * G + g) * nsplit + split);
+    ws_acc[o * hd + d] = a;
+    if (d == 0) {
+      ws_ml[o * 2] = M;
+      ws_ml[o * 2 + 1] = L;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ctr = counters + (size_t)b * nkv + kvh;
+    int prev = atomicAdd(ctr, 1);
+    s_last = (prev == nsplit - 1);
+    if (s_last) *ctr = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    int g = idx / hd, d = idx - g * hd;
+    size_t hb = ((size_t)b * nq + kvh * G + g);
+    float M = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ws_ml + (hb * nsplit + sp) * 2));
+    float a = 0.0f, L = 0.0f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      float ms = __ldcg(ws_ml + (hb * nsplit + sp) * 2);
+      float f = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+      a += f * __ldcg(ws_acc + (hb * nsplit + sp) * hd + d);
+      L += f * __ldcg(ws_ml + (hb * nsplit + sp) * 2 + 1);
+    }
+    out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
+  }
+}
+
+template <int KVT>
+int launch_decode_h128(int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt, int max_pages,
+                       KvPool pool, int nq, float sc, float* wa, float* wm, int* ctr, float* out, int extra) {
+  cudaError_t e;
+  switch (G) {
+    case 1: e = launch_pdl(attn_decode_h128_kernel<KVT, 1>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    case 2: e = launch_pdl(attn_decode_h128_kernel<KVT, 2>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    case 4: e = launch_pdl(attn_decode_h128_kernel<KVT, 4>, grid, dim3(256), smem, st, q, pos, bt, max_pages, pool, nq, sc, wa, wm, ctr, out, extra); break;
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
 template <int KVT, int DPL>
 int launch_decode_g(int G, dim3 grid, size_t smem, cudaStream_t st, const float* q, const int* pos, const int* bt, int max_pages,
                     KvPool pool, int nq, float sc, float* wa, float* wm, int* ctr, float* out, int extra) {
@@ -340,6 +573,13 @@ int bonsai_attn_decode(const float* q, const int* positions, const int* block_ta
   size_t smem = (size_t)kAttnWarps * G * (hd + 2) * sizeof(float);
   if (smem > 48 * 1024) return BONSAI_CUDA_BAD_ARG;
   float sc = 1.0f / sqrtf((float)hd);
+  if (hd == 128 && kvt != KV_F32 && (G == 1 || G == 2 || G == 4)) {
+    switch (kvt) {
+      case KV_F16: return launch_decode_h128<KV_F16>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+      case KV_Q8: return launch_decode_h128<KV_Q8>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+      default: return launch_decode_h128<KV_Q4>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
+    }
+  }
   switch (kvt) {
     case KV_F32: return launch_decode_d<KV_F32>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
     case KV_F16: return launch_decode_d<KV_F16>(dpl, G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);

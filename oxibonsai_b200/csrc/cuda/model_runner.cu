@@ -25,12 +25,17 @@ int bonsai_qknorm_rope_kvstore(const float*, int, const float*, const float*, fl
 int bonsai_attn_decode(const float*, const int*, const int*, int, int, int, int, int, int, int, const void*, const void*,
                        const float*, const float*, int, float*, float*, int*, float*, int, cudaStream_t);
 int bonsai_bitgemv_h2(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
+int bonsai_bitgemv_warp(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
                   const uint32_t*, int, cudaStream_t);
 int bonsai_bitgemv_tp(const void*, const void*, const void*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_tp_allgather_logits(void*, const float*, int, int, int, int, cudaStream_t);
 int bonsai_tp_allreduce_big_add(void*, float*, size_t, cudaStream_t);
 void* bonsai_tp_big_ptr(void*);
+int bonsai_tp_allgather_logits_at(void*, const float*, int, int, int, int, int, cudaStream_t);
+int bonsai_tp_allreduce_oneshot_add(void*, float*, size_t, int, cudaStream_t);
+void* bonsai_tp_big_half_ptr(void*, int);
+int bonsai_tp_barrier(void*, cudaStream_t);
 int bonsai_bitgemm_prefill(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int, int,
                            const void*, cudaStream_t);
 int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, int, cudaStream_t);
@@ -76,7 +81,8 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
   const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
   const bool tp = r.ic[IC_TP_SIZE] > 1;
-  auto gemv = r.ic[IC_FAST] ? bonsai_bitgemv_h2 : bonsai_bitgemv;
+  // IC_FAST: 0 exact f32, 1 packed-half warp-per-row, 2 packed-half tile kernel
+  auto gemv = r.ic[IC_FAST] == 0 ? bonsai_bitgemv : (r.ic[IC_FAST] == 2 ? bonsai_bitgemv_h2 : bonsai_bitgemv_warp);
   int* tokens = P<int>(sp[SP_TOKENS]);
   int* positions = P<int>(sp[SP_POSITIONS]);
   const int* bt = P<int>(sp[SP_BLOCK_TABLE]);
@@ -216,11 +222,10 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
       RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, P<float>(sp[SP_LOGITS]) + (size_t)slot * vocab,
                         lm_rows, hidden, st));
     } else {
-      if (slot != 0) return BONSAI_CUDA_BAD_ARG;
       const int rows_per_rank = (vocab + r.ic[IC_TP_SIZE] - 1) / r.ic[IC_TP_SIZE];
-      float* partial = P<float>(sp[SP_PARTIAL]);
+      float* partial = P<float>(sp[SP_PARTIAL]) + (size_t)slot * lm_rows;
       if (lm_rows > 0) RC(bonsai_f16gemv(P<void>(r.gp[GP_LM_HEAD]), hs, P<float>(r.gp[GP_OUT_NORM]), r.eps, partial, lm_rows, hidden, st));
-      RC(bonsai_tp_allgather_logits(r.comm, partial, 1, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
+      RC(bonsai_tp_allgather_logits_at(r.comm, partial, slot, 1, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
     }
   }
   return 0;
@@ -231,12 +236,20 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
 // sequence), attention stays the per-sequence split-KV kernel, and the LM head is a dense f16
 // tcgen05 GEMM.  The reference's continuous batching re-runs a full single-sequence generate per
 // request per step (crates/oxibonsai-runtime/src/continuous_batch.rs:283-293).
+//
+// Tensor parallel: the row-parallel O and down GEMMs write partial sums into alternating halves of
+// the symmetric big area and one kernel per all-reduce (entry flag barrier + peer loads + residual
+// add) folds them into h; the vocab-parallel LM head writes [batch][local rows] and the slices are
+// pushed into every rank's logits area.  Every step issues an even number of all-reduces, so the
+// alternation of halves continues across replays of a captured step.
 static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp, int batch, int flags, int mask_words,
                                cudaStream_t st) {
   const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
   const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
   const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
-  if (r.ic[IC_TP_SIZE] > 1) return BONSAI_CUDA_BAD_ARG;
+  const bool tp = r.ic[IC_TP_SIZE] > 1;
+  float* big[2] = {tp ? static_cast<float*>(bonsai_tp_big_half_ptr(r.comm, 0)) : nullptr,
+                   tp ? static_cast<float*>(bonsai_tp_big_half_ptr(r.comm, 1)) : nullptr};
   const int sms = 148;
   int* tokens = P<int>(sp[SP_TOKENS]);
   int* positions = P<int>(sp[SP_POSITIONS]);
@@ -251,6 +264,10 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   void* act = P<void>(pp[PP_ACT]);
   int* status = P<int>(pp[PP_STATUS]);
   const int xn_ld = hidden > qd ? hidden : qd;
+  // about four CTAs per SM over all (sequence, kv head, split) triples, within the workspace's split count
+  int attn_splits = (4 * 148) / (nkv * batch);
+  if (attn_splits < 1) attn_splits = 1;
+  if (attn_splits > r.ic[IC_NSPLIT_BATCHED]) attn_splits = r.ic[IC_NSPLIT_BATCHED];
 
   RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, batch, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
@@ -264,20 +281,45 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
                                   P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
     RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
                           P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
-                          r.ic[IC_NSPLIT_BATCHED], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
+                          attn_splits, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
     RC(bonsai_norm_to_f16_paired(attn, qd, nullptr, r.eps, batch, qd, attn16, qd, 0, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
-                              hidden, sms, nullptr, st));
+    if (!tp) {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
+                                hidden, sms, nullptr, st));
+    } else {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, status, hidden, qd,
+                                batch, 0, hidden, sms, nullptr, st));
+      RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
+    }
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
     RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
                               hidden, batch, 2, inter, sms, nullptr, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
-                              batch, 1, hidden, sms, nullptr, st));
+    if (!tp) {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+                                batch, 1, hidden, sms, nullptr, st));
+    } else {
+      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, status, hidden,
+                                inter, batch, 0, hidden, sms, nullptr, st));
+      RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 1, st));
+    }
   }
   if (!(flags & 2)) {
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps, batch, hidden, xn, xn_ld, 1, st));
-    RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, logits, nullptr, nullptr, status, lm_rows, hidden, batch, 0, vocab, sms,
-                              P<void>(r.gp[GP_LM_HEAD]), st));
+    if (!tp) {
+      RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, logits, nullptr, nullptr, status, lm_rows, hidden, batch, 0, vocab, sms,
+                                P<void>(r.gp[GP_LM_HEAD]), st));
+    } else {
+      float* partial = P<float>(sp[SP_PARTIAL]);
+      const int rows_per_rank = (vocab + r.ic[IC_TP_SIZE] - 1) / r.ic[IC_TP_SIZE];
+      if (lm_rows > 0)
+        RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, partial, nullptr, nullptr, status, lm_rows, hidden, batch, 0, lm_rows, sms,
+                                  P<void>(r.gp[GP_LM_HEAD]), st));
+      RC(bonsai_tp_allgather_logits_at(r.comm, partial, 0, batch, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
+    }
+  } else if (tp) {
+    // no logits gather (and hence no barrier) in this step: close it so that a following prefill
+    // cannot overwrite the big area while a peer still reads it
+    RC(bonsai_tp_barrier(r.comm, st));
   }
   if (flags & 1) {
     RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),

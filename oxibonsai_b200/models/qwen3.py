@@ -203,7 +203,7 @@ class Qwen3Runner:
         nq, nkv = weights.heads_local, weights.kv_heads_local
         self.max_pages = (max_seq + kv.page_size - 1) // kv.page_size
         # enough splits to spread one sequence's heads over the GPU; empty splits cost almost nothing
-        self.nsplit = nsplit or max(1, min(32, 148 // max(1, nkv)))
+        self.nsplit = nsplit or max(1, min(64, 296 // max(1, nkv)))   # two CTAs per SM for one sequence
         self.fast = fast
         B = max_batch
         f32 = dict(dtype=torch.float32, device=dev)
@@ -336,7 +336,7 @@ class Qwen3Runner:
 
     def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:
         flags = (1 if sample else 0) | (0 if lm_head else 2)
-        if batch >= 2 and self.fast and self.w.tp_size == 1:
+        if batch >= 2 and self.fast:
             # all sequences share one tcgen05 GEMM per linear layer
             b = self._prefill_buffers(max(64, batch))
             K.check(K._pf().bonsai_runner_decode_step_batched(self._native, self._step_ptrs, b["ptrs"], batch, flags, 0, K.stream()),
@@ -349,7 +349,7 @@ class Qwen3Runner:
         key = (batch, int(sample))
         g = self._graphs.get(key)
         if g is None:
-            if batch >= 2 and self.fast and self.w.tp_size == 1:
+            if batch >= 2 and self.fast:
                 self._prefill_buffers(max(64, batch))   # allocate outside the capture
             # capture without running: the capture itself executes nothing, so state is untouched
             s = torch.cuda.Stream(device=self.device)

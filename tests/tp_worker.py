@@ -36,6 +36,22 @@ def main():
         dist.all_gather(gathered, toks)
         same = all(torch.equal(gathered[0], t) for t in gathered)
         out.update(ok=(len(a) == 8 and same and sum(x == y for x, y in zip(a, b)) >= 6), a=a, b=b, same=same, status=eng.runner.tp.status())
+    elif mode == "batched":
+        # four sequences decoded together: tcgen05 GEMMs + one-shot all-reduce kernels + vocab-parallel dense LM head
+        eng = (EngineBuilder().model_path(path).preset("greedy").max_seq_len(160).max_batch(4).kv_cache("f16").device(f"cuda:{local}")
+               .tensor_parallel(rank, world).build())
+        g = torch.Generator().manual_seed(9)
+        prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (20, 33, 17, 41)]
+        single = [eng.generate(p, 10) for p in prompts]
+        batch = eng.generate_batch(prompts, 10)
+        again = eng.generate_batch(prompts, 10)        # graph replay after the capture, halves keep alternating
+        toks = torch.tensor(batch, device=f"cuda:{local}")
+        gathered = [torch.zeros_like(toks) for _ in range(world)]
+        dist.all_gather(gathered, toks)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        agree = sum(x == y for a, b in zip(single, batch) for x, y in zip(a, b))
+        out.update(ok=(same and batch == again and agree >= 32 and all(len(b) == 10 for b in batch)), agree=agree, same=same,
+                   single=single, batch=batch, again=again, status=eng.runner.tp.status(), pf_status=int(eng.runner._pf["status"].item()))
     dist.barrier()
     with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
         json.dump(out, f)
