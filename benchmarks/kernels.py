@@ -97,9 +97,16 @@ def main() -> None:
             if a.case == "gemv":
                 x = torch.randn(k, device=dev)
 
+                if a.fast == "mma":
+                    fws = [K.FragWeight(w) for w in ws]
+                out = torch.empty(n, device=dev)
+
                 def fn():
                     it[0] += 1
-                    K.bitgemv(ws[it[0] % len(ws)], x, fast=(False if a.fast == "0" else a.fast))
+                    if a.fast == "mma":
+                        K.bitgemv_mma(fws[it[0] % len(ws)], x, out=out)
+                    else:
+                        K.bitgemv(ws[it[0] % len(ws)], x, out=out, fast=(False if a.fast == "0" else a.fast))
                 us = time_us(fn, a.iters, a.profile)
                 rows_out.append({"case": f"gemv/{name}", "n": n, "k": k, "us": round(us, 2), "GB/s": round(byts / us / 1e3, 1),
                                  f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})

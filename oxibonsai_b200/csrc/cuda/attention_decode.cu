@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     l[g] = 0.0f;
   }
   const int* bt = block_table + (size_t)b * max_pages;
+  const int pshift = 31 - __clz(pool.page_size), pmask = pool.page_size - 1;   // the launcher admits power-of-two pages only
   constexpr int kTok = 2 * kH128Unroll;   // tokens per warp iteration
   for (int tb = t0 + warp * kTok; tb < t1; tb += kAttnWarps * kTok) {
     RawRow8<KVT> kr[kH128Unroll], vr[kH128Unroll];
@@ -371,8 +372,8 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
       const int t = tb + 2 * u + half;
       valid[u] = t < t1;
       const int tt = valid[u] ? t : t0;
-      const int page = bt[tt / pool.page_size];
-      const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (tt % pool.page_size);
+      const int page = bt[tt >> pshift];
+      const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (tt & pmask);
       load_raw8<KVT>(pool.k, pool.k_scale, row, sub, kr[u]);
       load_raw8<KVT>(pool.v, pool.v_scale, row, sub, vr[u]);
     }
@@ -402,11 +403,11 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
 #pragma unroll
       for (int u = 0; u < kH128Unroll; ++u)
         if (valid[u]) mn = fmaxf(mn, s[u][g]);
-      const float r = expf(m[g] - mn);   // exp(-inf) = 0 before the first token; a half with no token yet keeps m = -inf
+      const float r = __expf(m[g] - mn);   // exp(-inf) = 0 before the first token; a half with no token yet keeps m = -inf
       float ps = 0.0f;
 #pragma unroll
       for (int u = 0; u < kH128Unroll; ++u) {
-        p[u][g] = valid[u] ? expf(s[u][g] - mn) : 0.0f;
+        p[u][g] = valid[u] ? __expf(s[u][g] - mn) : 0.0f;
         ps += p[u][g];
       }
       const float rr = (mn == -INFINITY) ? 1.0f : r;
@@ -430,7 +431,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
   for (int g = 0; g < G; ++g) {
     const float mo = __shfl_xor_sync(0xffffffffu, m[g], 16), lo = __shfl_xor_sync(0xffffffffu, l[g], 16);
     const float M = fmaxf(m[g], mo);
-    const float fa = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - M), fb = (mo == -INFINITY) ? 0.0f : expf(mo - M);
+    const float fa = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - M), fb = (mo == -INFINITY) ? 0.0f : __expf(mo - M);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], 16);
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) {
       const float* src = sh + ((size_t)w * G + g) * stride;
-      float f = (src[hd] == -INFINITY) ? 0.0f : expf(src[hd] - M);
+      float f = (src[hd] == -INFINITY) ? 0.0f : __expf(src[hd] - M);
       a += f * src[d];
       L += f * src[hd + 1];
     }
@@ -493,7 +494,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     float a = 0.0f, L = 0.0f;
     for (int sp = 0; sp < nsplit; ++sp) {
       float ms = __ldcg(ws_ml + (hb * nsplit + sp) * 2);
-      float f = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+      float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
       a += f * __ldcg(ws_acc + (hb * nsplit + sp) * hd + d);
       L += f * __ldcg(ws_ml + (hb * nsplit + sp) * 2 + 1);
     }
@@ -573,7 +574,7 @@ int bonsai_attn_decode(const float* q, const int* positions, const int* block_ta
   size_t smem = (size_t)kAttnWarps * G * (hd + 2) * sizeof(float);
   if (smem > 48 * 1024) return BONSAI_CUDA_BAD_ARG;
   float sc = 1.0f / sqrtf((float)hd);
-  if (hd == 128 && kvt != KV_F32 && (G == 1 || G == 2 || G == 4)) {
+  if (hd == 128 && kvt != KV_F32 && (G == 1 || G == 2 || G == 4) && (page_size & (page_size - 1)) == 0) {
     switch (kvt) {
       case KV_F16: return launch_decode_h128<KV_F16>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);
       case KV_Q8: return launch_decode_h128<KV_Q8>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);

@@ -114,6 +114,54 @@ class PlanarWeight:
         return out
 
 
+_MMA_SIG = {
+    "bonsai_frag_sizes": [_i, _i, _vp, _vp],
+    "bonsai_repack_frag": [_vp, _vp, _i, _i, _vp, _vp, _vp],
+    "bonsai_bitgemv_mma": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
+}
+_mma_declared = False
+
+
+def _mma():
+    global _mma_declared
+    l = lib()
+    if not _mma_declared:
+        declare(_MMA_SIG)
+        _mma_declared = True
+    return l
+
+
+class FragWeight:
+    """A packed matrix in the tensor-core fragment layout of the batch-1 decode GEMV (see csrc/cuda/bitgemv_mma.cu):
+    ``codes`` uint4 [N/16][K/128][32 lanes], ``scales`` half2 [N/16][K/128][8]."""
+
+    def __init__(self, planar: PlanarWeight):
+        self.n, self.k = planar.n, planar.k
+        cb, sb = C.c_size_t(), C.c_size_t()
+        _mma().bonsai_frag_sizes(self.n, self.k, C.byref(cb), C.byref(sb))
+        dev = planar.codes.device
+        self.codes = torch.empty(cb.value, dtype=torch.uint8, device=dev)
+        self.scales = torch.empty(sb.value, dtype=torch.uint8, device=dev)
+        check(_mma().bonsai_repack_frag(planar.codes.data_ptr(), planar.scales.data_ptr(), self.n, self.k, self.codes.data_ptr(),
+                                        self.scales.data_ptr(), stream()), "repack_frag")
+
+    @property
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel()
+
+
+def bitgemv_mma(w: FragWeight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
+                residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = W x through warp-level fp8 tensor-core MMAs on fragment-layout weights (activations as three e4m3 terms)."""
+    _f32c(x)
+    n_out = w.n // 2 if epi == EPI_SWIGLU else w.n
+    if out is None:
+        out = torch.empty(n_out, dtype=torch.float32, device=x.device)
+    check(_mma().bonsai_bitgemv_mma(w.codes.data_ptr(), w.scales.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual),
+                                    w.n, w.k, epi, stream()), "bitgemv_mma")
+    return out
+
+
 def bitgemv(w: PlanarWeight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
             residual: torch.Tensor | None = None, out: torch.Tensor | None = None, fast: bool | str = False) -> torch.Tensor:
     """out = W x.  ``fast=False``: exact f32 path; ``fast=True`` / ``"warp"``: packed-half warp-per-row kernel

@@ -74,6 +74,33 @@ def test_bitgemv_half_path_is_close_to_fp32(ty, rows, cols, kernel):
         assert torch.allclose(y.cpu().double(), want, rtol=2e-2, atol=2e-2 * want.abs().mean().item())
 
 
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+@pytest.mark.parametrize("rows,cols", [(6144, 4096), (4096, 12288), (512, 2560), (200, 128), (24576, 4096), (1001, 9728), (300, 6144),
+                                       (66, 16384), (5000, 2048)])
+def test_bitgemv_mma_fragment_path_is_close_to_fp32(ty, rows, cols):
+    from oxibonsai_b200.ops import cuda_ops as K
+    raw, wd = _random_quant(ty, rows, cols, 9)
+    pw = K.PlanarWeight(rows, cols, _dev()).fill_from_gguf(torch.from_numpy(raw).to(_dev()), ty, cols, 0, rows)
+    fw = K.FragWeight(pw)
+    g = torch.Generator().manual_seed(10)
+    x, nw, res = torch.randn(cols, generator=g), torch.rand(cols, generator=g) + 0.5, torch.randn(rows, generator=g)
+    x[::97] *= 6.0   # outliers stretch the e4m3 range
+    ref = wd.double() @ x.double()
+    y = K.bitgemv_mma(fw, x.to(_dev()))
+    # three e4m3 terms: 12 significant bits relative to the largest activation
+    assert (y.cpu().double() - ref).abs().max().item() <= 2e-3 * ref.abs().mean().item() * (cols / 128) ** 0.5 + 1e-4
+    xn = nw * x * torch.rsqrt((x * x).mean() + 1e-6)
+    refn = wd.double() @ xn.double()
+    y = K.bitgemv_mma(fw, x.to(_dev()), norm_w=nw.to(_dev()), eps=1e-6, epi=K.EPI_RESID, residual=res.to(_dev()))
+    assert torch.allclose(y.cpu().double(), refn + res.double(), rtol=5e-3, atol=5e-3 * refn.abs().mean().item())
+    if rows % 2 == 0:
+        y = K.bitgemv_mma(fw, xn.to(_dev()), epi=K.EPI_SWIGLU)
+        want = torch.nn.functional.silu(refn[0::2]) * refn[1::2]
+        assert torch.allclose(y.cpu().double(), want, rtol=2e-2, atol=2e-2 * want.abs().mean().item())
+    # a second call gives the same bits (no dependence on scheduling)
+    assert torch.equal(y, K.bitgemv_mma(fw, xn.to(_dev()), epi=K.EPI_SWIGLU)) if rows % 2 == 0 else True
+
+
 def test_bitgemv_fused_norm_residual_swiglu():
     from oxibonsai_b200.ops import cuda_ops as K
     rows, cols = 1024, 2048
