@@ -170,14 +170,29 @@ class PagedKvCache:
         else:
             self.k_scale = self.v_scale = None
         self.free_pages = list(range(num_pages - 1, -1, -1))
+        self.refcount = [0] * num_pages        # pages may be shared between sequences and the prefix cache
+        self.on_exhausted = None               # optional callback(n_missing) that may free pages (prefix-cache eviction)
 
     def alloc(self, n: int) -> list[int]:
+        if n > len(self.free_pages) and self.on_exhausted is not None:
+            self.on_exhausted(n - len(self.free_pages))
         if n > len(self.free_pages):
             raise MemoryError(f"KV cache exhausted: need {n} pages, {len(self.free_pages)} free")
-        return [self.free_pages.pop() for _ in range(n)]
+        pages = [self.free_pages.pop() for _ in range(n)]
+        for p in pages:
+            self.refcount[p] = 1
+        return pages
+
+    def retain(self, pages: list[int]) -> None:
+        for p in pages:
+            self.refcount[p] += 1
 
     def release(self, pages: list[int]) -> None:
-        self.free_pages.extend(reversed(pages))
+        for p in reversed(pages):
+            self.refcount[p] -= 1
+            if self.refcount[p] <= 0:
+                self.refcount[p] = 0
+                self.free_pages.append(p)
 
     @property
     def utilization(self) -> float:

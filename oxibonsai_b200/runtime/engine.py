@@ -77,6 +77,7 @@ class InferenceEngine:
         self._out_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._slot_pages: dict[int, list[int]] = {}
         self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
+        self.prefix_cache = None       # see enable_prefix_cache()
         self.last_stats = GenerationStats()
         if warmup:
             self.warmup()
@@ -127,6 +128,40 @@ class InferenceEngine:
         self.runner.tokens[slot: slot + 1].copy_(self._tok_host[slot: slot + 1], non_blocking=True)
         self.runner.positions[slot: slot + 1].copy_(self._pos_host[slot: slot + 1], non_blocking=True)
 
+    # ---- prefix cache ----------------------------------------------------------------------------
+    def enable_prefix_cache(self, max_pages: int | None = None):
+        """Shares the KV pages of repeated prompt prefixes between sequences (full pages only).  The cache may hold up to
+        ``max_pages`` pages (default: a quarter of the pool) and gives pages back when the pool runs dry."""
+        from .prefix_cache import PrefixCache
+        if self.exact:
+            raise ValueError("the exact-f32 mode prefills token by token and does not use the prefix cache")
+        self.prefix_cache = PrefixCache(self.kv.page_size, max_pages or max(1, self.kv.num_pages // 4), self.kv.retain, self.kv.release)
+        self.kv.on_exhausted = lambda missing: self.prefix_cache.evict(missing)
+        return self.prefix_cache
+
+    def _start_sequence(self, slot: int, prompt: Sequence[int], total: int) -> None:
+        """Binds pages for ``total`` tokens to ``slot`` and runs the prompt, reusing cached prefix pages when possible."""
+        shared: list[int] = []
+        pc = self.prefix_cache
+        if pc is not None and len(prompt) > 1:
+            shared = pc.lookup(prompt, max_tokens=len(prompt) - 1)   # the last prompt token is always recomputed
+            if shared:
+                self.kv.retain(shared)
+                self._release_slot(slot)
+                self._slot_pages[slot] = list(shared)
+        try:
+            self._bind_slot(slot, total)
+        except MemoryError:
+            self._release_slot(slot)
+            raise
+        if shared:
+            row = torch.tensor(self._slot_pages[slot], dtype=torch.int32)
+            self.runner.block_table[slot, : len(row)].copy_(row.to(self.device))
+        cached = len(shared) * self.kv.page_size
+        self.prefill(prompt[cached:], slot, cached)
+        if pc is not None:
+            pc.insert(prompt, self._slot_pages[slot])
+
     # ---- generation -------------------------------------------------------------------------------
     def prefill(self, prompt: Sequence[int], slot: int = 0, pos0: int = 0) -> None:
         """Runs the prompt through the model, leaving logits of the last prompt token in the runner.
@@ -161,12 +196,11 @@ class InferenceEngine:
         stats = GenerationStats(prompt_tokens=len(prompt))
         self.last_stats = stats
         total = min(self.max_seq_len, len(prompt) + max_new)
-        self._bind_slot(0, total)
         self._set_sampling(0, p)
         r = self.runner
         try:
             t0 = time.perf_counter()
-            self.prefill(prompt, 0)
+            self._start_sequence(0, prompt, total)
             # first token: sample from the prefill logits on the device
             K.sample(r.logits[:1], r.temps[:1], r.topks[:1], r.topps[:1], r.rng[:1], out=r.tokens[:1])
             self._out_host[:1].copy_(r.tokens[:1], non_blocking=True)
@@ -218,9 +252,8 @@ class InferenceEngine:
         try:
             for s, prompt in enumerate(prompts):
                 n = len(prompt)
-                self._bind_slot(s, min(self.max_seq_len, n + max_tokens))
                 self._set_sampling(s, replace(p, seed=p.seed + s))
-                self.prefill(prompt, s)
+                self._start_sequence(s, [int(t) for t in prompt], min(self.max_seq_len, n + max_tokens))
             lens = torch.tensor([len(q) for q in prompts], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
             K.sample(r.logits[:B], r.temps[:B], r.topks[:B], r.topps[:B], r.rng[:B], out=r.tokens[:B])
             r.positions[:B].copy_(lens)
@@ -251,9 +284,8 @@ class InferenceEngine:
     # ---- single-step primitives (speculative decoding, schedulers) -------------------------------
     def open_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None) -> int:
         """Binds ``slot``, prefills ``prompt`` and returns the first sampled token."""
-        self._bind_slot(slot, min(self.max_seq_len, max_total))
         self._set_sampling(slot, params or self.sampling)
-        self.prefill(prompt, slot)
+        self._start_sequence(slot, [int(t) for t in prompt], min(self.max_seq_len, max_total))
         r = self.runner
         K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
                  out=r.tokens[slot: slot + 1])

@@ -98,3 +98,22 @@ def test_http_server_end_to_end_on_device(tiny_gguf):
         assert "oxibonsai_tokens_generated_total 14" in m
     finally:
         sched.stop()
+
+
+def test_prefix_cache_reuses_pages_and_keeps_the_token_stream(tiny_gguf):
+    from oxibonsai_b200.runtime import EngineBuilder
+    eng = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(512).max_batch(2).kv_cache("f16").build()
+    g = torch.Generator().manual_seed(33)
+    base = torch.randint(0, 1000, (200,), generator=g).tolist()
+    want_a = eng.generate(base, 12)
+    want_b = eng.generate(base[:150] + [5, 6, 7], 12)
+    free0 = len(eng.kv.free_pages)
+    pc = eng.enable_prefix_cache()
+    assert eng.generate(base, 12) == want_a and pc.stats.hits == 0 and pc.size == 200 // eng.kv.page_size
+    assert eng.generate(base, 12) == want_a and pc.stats.hits == 1 and pc.stats.tokens_reused == (199 // eng.kv.page_size) * eng.kv.page_size
+    # a different continuation of a shared prefix reuses the common full pages
+    assert eng.generate(base[:150] + [5, 6, 7], 12) == want_b and pc.stats.hits == 2
+    # only the cache still holds pages; dropping it returns the pool to its initial state
+    assert len(eng.kv.free_pages) == free0 - pc.size
+    pc.clear()
+    assert len(eng.kv.free_pages) == free0 and all(c == 0 for c in eng.kv.refcount)
