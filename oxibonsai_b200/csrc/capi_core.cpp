@@ -7,6 +7,7 @@
 #include <string>
 
 #include "core/blocks.hpp"
+#include "core/kquants.hpp"
 #include "core/config.hpp"
 #include "core/gguf.hpp"
 #include "cpu/oracle.hpp"
@@ -214,6 +215,12 @@ int bonsai_dequant(uint32_t type, const uint8_t* src, uint64_t n_blocks, float* 
     case 8: dequant_q8_0(src, n_blocks, dst); return 0;
     case 43: dequant_fp8(src, n_blocks, dst, false); return 0;
     case 44: dequant_fp8(src, n_blocks, dst, true); return 0;
+    case 10: dequant_q2k(src, n_blocks, dst); return 0;
+    case 11: dequant_q3k(src, n_blocks, dst); return 0;
+    case 12: dequant_q4k(src, n_blocks, dst); return 0;
+    case 13: dequant_q5k(src, n_blocks, dst); return 0;
+    case 14: dequant_q6k(src, n_blocks, dst); return 0;
+    case 15: dequant_q8k(src, n_blocks, dst); return 0;
     case 1: for (uint64_t i = 0; i < n_blocks; ++i) dst[i] = f16_to_f32(ld_u16(src + 2 * i)); return 0;
     case 30: for (uint64_t i = 0; i < n_blocks; ++i) dst[i] = bf16_to_f32(ld_u16(src + 2 * i)); return 0;
     case 0: std::memcpy(dst, src, n_blocks * 4); return 0;
@@ -231,6 +238,12 @@ int bonsai_quant(uint32_t type, const float* src, uint64_t n_blocks, uint8_t* ds
     case 8: quant_q8_0(src, n_blocks, dst); return 0;
     case 43: quant_fp8(src, n_blocks, dst, false); return 0;
     case 44: quant_fp8(src, n_blocks, dst, true); return 0;
+    case 10: quant_q2k(src, n_blocks, dst); return 0;
+    case 11: quant_q3k(src, n_blocks, dst); return 0;
+    case 12: quant_q4k(src, n_blocks, dst); return 0;
+    case 13: quant_q5k(src, n_blocks, dst); return 0;
+    case 14: quant_q6k(src, n_blocks, dst); return 0;
+    case 15: quant_q8k(src, n_blocks, dst); return 0;
     case 1: for (uint64_t i = 0; i < n_blocks; ++i) st_u16(dst + 2 * i, f32_to_f16(src[i])); return 0;
     case 30: for (uint64_t i = 0; i < n_blocks; ++i) st_u16(dst + 2 * i, f32_to_bf16(src[i])); return 0;
     case 0: std::memcpy(dst, src, n_blocks * 4); return 0;
@@ -247,7 +260,8 @@ float bonsai_f16_to_f32(uint16_t v) { return f16_to_f32(v); }
 int bcpu_gemv(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, float* out) {
   BONSAI_TRY
   switch (type) {
-    case 0: case 1: case 30: case 2: case 8: case 35: case 41: case 42: case 43: case 44: break;
+    case 0: case 1: case 30: case 2: case 8: case 35: case 41: case 42: case 43: case 44:
+    case 10: case 11: case 12: case 13: case 14: case 15: break;
     default: fail(ErrorCode::UnsupportedQuantType, "cpu gemv: unsupported type " + std::to_string(type));
   }
   cpu_gemv(MatrixRef{data, type, rows, cols}, x, out);

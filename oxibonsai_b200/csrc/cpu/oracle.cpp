@@ -6,6 +6,7 @@
 #include <thread>
 
 #include "../core/blocks.hpp"
+#include "../core/kquants.hpp"
 
 namespace bonsai {
 
@@ -126,6 +127,12 @@ void cpu_gemv(const MatrixRef& w, const float* x, float* out) {
         case 8: s = row_dot_generic<32, 34>(row, cols / 32, x, [](const uint8_t* p, float* o) { dequant_q8_0(p, 1, o); }); break;
         case 43: s = row_dot_generic<32, 34>(row, cols / 32, x, [](const uint8_t* p, float* o) { dequant_fp8(p, 1, o, false); }); break;
         case 44: s = row_dot_generic<32, 34>(row, cols / 32, x, [](const uint8_t* p, float* o) { dequant_fp8(p, 1, o, true); }); break;
+        case 10: s = row_dot_generic<256, 84>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q2k(p, 1, o); }); break;
+        case 11: s = row_dot_generic<256, 110>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q3k(p, 1, o); }); break;
+        case 12: s = row_dot_generic<256, 144>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q4k(p, 1, o); }); break;
+        case 13: s = row_dot_generic<256, 176>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q5k(p, 1, o); }); break;
+        case 14: s = row_dot_generic<256, 210>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q6k(p, 1, o); }); break;
+        case 15: s = row_dot_generic<256, 292>(row, cols / 256, x, [](const uint8_t* p, float* o) { dequant_q8k(p, 1, o); }); break;
         default: fail(ErrorCode::UnsupportedQuantType, "cpu_gemv: unsupported type " + std::to_string(type));
       }
       out[r] = s;
@@ -150,6 +157,12 @@ void cpu_dequant_rows(const MatrixRef& w, uint64_t row0, uint64_t nrows, float* 
       case 8: dequant_q8_0(row, w.cols / 32, o); break;
       case 43: dequant_fp8(row, w.cols / 32, o, false); break;
       case 44: dequant_fp8(row, w.cols / 32, o, true); break;
+      case 10: dequant_q2k(row, w.cols / 256, o); break;
+      case 11: dequant_q3k(row, w.cols / 256, o); break;
+      case 12: dequant_q4k(row, w.cols / 256, o); break;
+      case 13: dequant_q5k(row, w.cols / 256, o); break;
+      case 14: dequant_q6k(row, w.cols / 256, o); break;
+      case 15: dequant_q8k(row, w.cols / 256, o); break;
       default: fail(ErrorCode::UnsupportedQuantType, "cpu_dequant_rows: unsupported type " + std::to_string(w.type));
     }
   }
