@@ -1,0 +1,426 @@
+"""Evaluation harness: perplexity, multiple-choice and generative benchmark evaluators, text-overlap metrics, QA metrics,
+calibration, bootstrap confidence intervals, streaming counters, throughput benchmark, reports and JSONL datasets.
+
+Reference: crates/oxibonsai-eval (perplexity.rs:39-94, throughput.rs:30-101, accuracy.rs, mmlu.rs, arc.rs, hellaswag.rs,
+winogrande.rs, boolq.rs, truthfulqa.rs, gsm8k.rs, bleu.rs, chrf.rs, meteor.rs, rouge.rs, qa.rs, calibration.rs,
+bootstrap.rs, streaming.rs, report.rs, dataset.rs).  Evaluators take plain callables - ``logprob_fn(context, continuation)
+-> float`` or ``generate_fn(prompt) -> str`` - so they run against the GPU engine, the CPU oracle or a stub.
+"""
+from __future__ import annotations
+
+import json
+import math
+import re
+import time
+from collections import Counter
+from dataclasses import dataclass, field
+from typing import Callable, Iterable, Sequence
+
+import numpy as np
+
+
+# ---- datasets ---------------------------------------------------------------------------------------------------------------
+def load_jsonl(path: str) -> list[dict]:
+    out = []
+    with open(path, encoding="utf-8") as f:
+        for n, line in enumerate(f, 1):
+            line = line.strip()
+            if line:
+                try:
+                    out.append(json.loads(line))
+                except json.JSONDecodeError as e:
+                    raise ValueError(f"{path}:{n}: {e}") from None
+    return out
+
+
+def save_jsonl(path: str, rows: Iterable[dict]) -> None:
+    with open(path, "w", encoding="utf-8") as f:
+        for r in rows:
+            f.write(json.dumps(r, ensure_ascii=False) + "\n")
+
+
+# ---- perplexity -----------------------------------------------------------------------------------------------------------------
+@dataclass
+class PerplexityResult:
+    perplexity: float
+    nll: float
+    tokens: int
+    bits_per_token: float
+
+
+class PerplexityEvaluator:
+    """``logits_fn(tokens) -> [len(tokens), vocab]`` next-token logits for every prefix position."""
+
+    def __init__(self, stride: int | None = None, max_len: int = 2048):
+        self.stride, self.max_len = stride, max_len
+
+    def evaluate(self, tokens: Sequence[int], logits_fn: Callable[[Sequence[int]], np.ndarray]) -> PerplexityResult:
+        toks = list(tokens)
+        stride = self.stride or self.max_len
+        nll, n, prev_end = 0.0, 0, 0
+        for start in range(0, max(1, len(toks) - 1), stride):
+            end = min(len(toks), start + self.max_len)
+            window = toks[start:end]
+            logits = np.asarray(logits_fn(window), dtype=np.float64)
+            lp = logits - logits.max(-1, keepdims=True)
+            lp = lp - np.log(np.exp(lp).sum(-1, keepdims=True))
+            first = max(prev_end - start, 1)           # positions already scored by the previous window are skipped
+            for i in range(first, len(window)):
+                nll -= lp[i - 1, window[i]]
+                n += 1
+            prev_end = end
+            if end == len(toks):
+                break
+        mean = nll / max(n, 1)
+        return PerplexityResult(math.exp(mean), nll, n, mean / math.log(2))
+
+
+# ---- multiple choice ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class McItem:
+    question: str
+    choices: list[str]
+    answer: int
+    subject: str = ""
+
+
+@dataclass
+class AccuracyResult:
+    correct: int
+    total: int
+    by_group: dict[str, tuple[int, int]] = field(default_factory=dict)
+    confidences: list[float] = field(default_factory=list)
+    outcomes: list[int] = field(default_factory=list)
+
+    @property
+    def accuracy(self) -> float:
+        return self.correct / self.total if self.total else 0.0
+
+    def group_accuracy(self) -> dict[str, float]:
+        return {k: c / t for k, (c, t) in self.by_group.items() if t}
+
+
+class MultipleChoiceEvaluator:
+    """Scores each choice with ``logprob_fn(context, continuation)``; optional length normalisation (per character)."""
+
+    letters = "ABCDEFGH"
+
+    def __init__(self, prompt_format: Callable[[McItem], str] | None = None, normalize: bool = False, letter_mode: bool = False):
+        self.fmt, self.normalize, self.letter_mode = prompt_format or (lambda it: it.question), normalize, letter_mode
+
+    def scores(self, item: McItem, logprob_fn) -> list[float]:
+        ctx = self.fmt(item)
+        if self.letter_mode:
+            ctx += "\n" + "\n".join(f"{self.letters[i]}. {c}" for i, c in enumerate(item.choices)) + "\nAnswer:"
+            return [logprob_fn(ctx, " " + self.letters[i]) for i in range(len(item.choices))]
+        return [logprob_fn(ctx, " " + c) / (max(1, len(c)) if self.normalize else 1) for c in item.choices]
+
+    def evaluate(self, items: Iterable[McItem], logprob_fn) -> AccuracyResult:
+        r = AccuracyResult(0, 0)
+        for it in items:
+            s = np.asarray(self.scores(it, logprob_fn), dtype=np.float64)
+            pred = int(np.argmax(s))
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            ok = int(pred == it.answer)
+            r.correct += ok
+            r.total += 1
+            c, t = r.by_group.get(it.subject, (0, 0))
+            r.by_group[it.subject] = (c + ok, t + 1)
+            r.confidences.append(float(p[pred]))
+            r.outcomes.append(ok)
+        return r
+
+
+def mmlu_item(row: dict) -> McItem:
+    a = row["answer"]
+    return McItem(row["question"], list(row["choices"]), a if isinstance(a, int) else "ABCD".index(a), row.get("subject", ""))
+
+
+def arc_item(row: dict) -> McItem:
+    ch = row["choices"]
+    labels, texts = (ch["label"], ch["text"]) if isinstance(ch, dict) else ([c["label"] for c in ch], [c["text"] for c in ch])
+    return McItem(row["question"], list(texts), labels.index(row["answerKey"]), row.get("category", ""))
+
+
+def hellaswag_item(row: dict) -> McItem:
+    return McItem(row.get("ctx") or (row["ctx_a"] + " " + row.get("ctx_b", "")), list(row["endings"]), int(row["label"]), row.get("activity_label", ""))
+
+
+def winogrande_item(row: dict) -> McItem:
+    s = row["sentence"]
+    return McItem(s.split("_")[0].rstrip(), [row["option1"] + s.split("_")[1], row["option2"] + s.split("_")[1]], int(row["answer"]) - 1)
+
+
+def boolq_item(row: dict) -> McItem:
+    return McItem(f"{row['passage']}\nQuestion: {row['question']}?\nAnswer:", ["no", "yes"], int(bool(row["answer"])))
+
+
+def truthfulqa_item(row: dict) -> McItem:
+    t = row["mc1_targets"]
+    return McItem(row["question"], list(t["choices"]), int(np.argmax(t["labels"])))
+
+
+def mmlu_evaluator() -> MultipleChoiceEvaluator:
+    return MultipleChoiceEvaluator(lambda it: f"The following is a multiple choice question about {it.subject.replace('_', ' ') or 'general knowledge'}.\n\n{it.question}", letter_mode=True)
+
+
+def hellaswag_evaluator() -> MultipleChoiceEvaluator:
+    return MultipleChoiceEvaluator(normalize=True)
+
+
+# ---- generative: GSM8K, QA ------------------------------------------------------------------------------------------------------------
+_NUM = re.compile(r"-?\d[\d,]*\.?\d*")
+
+
+def extract_final_number(text: str) -> str | None:
+    m = re.search(r"####\s*(-?[\d,]*\.?\d+)", text)
+    if m:
+        return m.group(1).replace(",", "")
+    nums = _NUM.findall(text)
+    return nums[-1].replace(",", "").rstrip(".") if nums else None
+
+
+class Gsm8kEvaluator:
+    def evaluate(self, rows: Iterable[dict], generate_fn: Callable[[str], str]) -> AccuracyResult:
+        r = AccuracyResult(0, 0)
+        for row in rows:
+            want = extract_final_number(row["answer"])
+            got = extract_final_number(generate_fn(f"Question: {row['question']}\nAnswer: Let's think step by step."))
+            ok = int(want is not None and got is not None and abs(float(want) - float(got)) < 1e-6)
+            r.correct += ok
+            r.total += 1
+            r.outcomes.append(ok)
+        return r
+
+
+def normalize_answer(s: str) -> str:
+    s = re.sub(r"\b(a|an|the)\b", " ", s.lower())
+    s = re.sub(r"[^\w\s]", "", s)
+    return " ".join(s.split())
+
+
+def exact_match(pred: str, golds: Sequence[str]) -> float:
+    return float(any(normalize_answer(pred) == normalize_answer(g) for g in golds))
+
+
+def qa_f1(pred: str, golds: Sequence[str]) -> float:
+    best = 0.0
+    p = normalize_answer(pred).split()
+    for g in golds:
+        t = normalize_answer(g).split()
+        common = sum((Counter(p) & Counter(t)).values())
+        if not p or not t:
+            best = max(best, float(p == t))
+            continue
+        if common:
+            pr, rc = common / len(p), common / len(t)
+            best = max(best, 2 * pr * rc / (pr + rc))
+    return best
+
+
+# ---- overlap metrics --------------------------------------------------------------------------------------------------------------------
+def _ngrams(seq: Sequence, n: int) -> Counter:
+    return Counter(tuple(seq[i:i + n]) for i in range(len(seq) - n + 1))
+
+
+def bleu(candidate: str, references: Sequence[str], max_n: int = 4, smooth: bool = True) -> float:
+    c = candidate.split()
+    refs = [r.split() for r in references]
+    if not c:
+        return 0.0
+    logs = 0.0
+    for n in range(1, max_n + 1):
+        cg = _ngrams(c, n)
+        best: Counter = Counter()
+        for r in refs:
+            for g, k in _ngrams(r, n).items():
+                best[g] = max(best[g], k)
+        match, total = sum(min(k, best[g]) for g, k in cg.items()), max(sum(cg.values()), 0)
+        if n == 1 and match == 0:
+            return 0.0
+        if smooth and n > 1:
+            match, total = match + 1, total + 1
+        if match == 0 or total == 0:
+            return 0.0
+        logs += math.log(match / total) / max_n
+    rl = min((abs(len(r) - len(c)), len(r)) for r in refs)[1]
+    bp = 1.0 if len(c) >= rl else math.exp(1 - rl / len(c))
+    return bp * math.exp(logs)
+
+
+def chrf(candidate: str, reference: str, max_n: int = 6, beta: float = 2.0) -> float:
+    c, r = candidate.replace(" ", ""), reference.replace(" ", "")
+    f = []
+    for n in range(1, max_n + 1):
+        cg, rg = _ngrams(c, n), _ngrams(r, n)
+        if not cg or not rg:
+            continue
+        m = sum((cg & rg).values())
+        p, rc = m / sum(cg.values()), m / sum(rg.values())
+        f.append((1 + beta ** 2) * p * rc / (beta ** 2 * p + rc) if p + rc > 0 else 0.0)
+    return sum(f) / len(f) if f else 0.0
+
+
+def _lcs(a: Sequence, b: Sequence) -> int:
+    dp = [0] * (len(b) + 1)
+    for x in a:
+        prev = 0
+        for j, y in enumerate(b, 1):
+            cur = dp[j]
+            dp[j] = prev + 1 if x == y else max(dp[j], dp[j - 1])
+            prev = cur
+    return dp[-1]
+
+
+def rouge(candidate: str, reference: str) -> dict[str, float]:
+    c, r = candidate.split(), reference.split()
+    out = {}
+    for n in (1, 2):
+        cg, rg = _ngrams(c, n), _ngrams(r, n)
+        m = sum((cg & rg).values())
+        p, rc = (m / sum(cg.values()) if cg else 0.0), (m / sum(rg.values()) if rg else 0.0)
+        out[f"rouge{n}"] = 2 * p * rc / (p + rc) if p + rc else 0.0
+    l = _lcs(c, r)
+    p, rc = (l / len(c) if c else 0.0), (l / len(r) if r else 0.0)
+    out["rougeL"] = 2 * p * rc / (p + rc) if p + rc else 0.0
+    return out
+
+
+def meteor(candidate: str, reference: str, alpha: float = 0.9, beta: float = 3.0, gamma: float = 0.5) -> float:
+    """Exact-match METEOR: harmonic mean weighted to recall, with a fragmentation penalty over matched chunks."""
+    c, r = candidate.split(), reference.split()
+    if not c or not r:
+        return 0.0
+    used, align = set(), []
+    for i, w in enumerate(c):
+        for j, v in enumerate(r):
+            if j not in used and w == v:
+                used.add(j)
+                align.append((i, j))
+                break
+    m = len(align)
+    if m == 0:
+        return 0.0
+    p, rc = m / len(c), m / len(r)
+    fmean = p * rc / (alpha * p + (1 - alpha) * rc)
+    chunks = 1 + sum(1 for (i0, j0), (i1, j1) in zip(align, align[1:]) if not (i1 == i0 + 1 and j1 == j0 + 1))
+    return fmean * (1 - gamma * (chunks / m) ** beta)
+
+
+# ---- calibration, bootstrap, streaming counters -------------------------------------------------------------------------------------------
+def expected_calibration_error(confidences: Sequence[float], outcomes: Sequence[int], n_bins: int = 10) -> float:
+    c, o = np.asarray(confidences, dtype=np.float64), np.asarray(outcomes, dtype=np.float64)
+    if c.size == 0:
+        return 0.0
+    bins = np.minimum((c * n_bins).astype(int), n_bins - 1)
+    ece = 0.0
+    for b in range(n_bins):
+        m = bins == b
+        if m.any():
+            ece += m.mean() * abs(o[m].mean() - c[m].mean())
+    return float(ece)
+
+
+def brier_score(probs: Sequence[float], outcomes: Sequence[int]) -> float:
+    p, o = np.asarray(probs, dtype=np.float64), np.asarray(outcomes, dtype=np.float64)
+    return float(((p - o) ** 2).mean()) if p.size else 0.0
+
+
+def negative_log_likelihood(probs_of_truth: Sequence[float]) -> float:
+    p = np.clip(np.asarray(probs_of_truth, dtype=np.float64), 1e-12, 1.0)
+    return float(-np.log(p).mean()) if p.size else 0.0
+
+
+def bootstrap_ci(values: Sequence[float], n_resamples: int = 1000, confidence: float = 0.95, seed: int = 0, statistic=np.mean) -> tuple[float, float, float]:
+    v = np.asarray(values, dtype=np.float64)
+    if v.size == 0:
+        return 0.0, 0.0, 0.0
+    rng = np.random.default_rng(seed)
+    stats = np.array([statistic(v[rng.integers(0, v.size, v.size)]) for _ in range(n_resamples)])
+    lo, hi = np.quantile(stats, [(1 - confidence) / 2, 1 - (1 - confidence) / 2])
+    return float(statistic(v)), float(lo), float(hi)
+
+
+class StreamingAccuracy:
+    """Running accuracy / mean / variance without keeping the samples (Welford)."""
+
+    def __init__(self):
+        self.n, self.mean, self._m2, self.correct = 0, 0.0, 0.0, 0
+
+    def update(self, value: float, correct: bool | None = None) -> None:
+        self.n += 1
+        d = value - self.mean
+        self.mean += d / self.n
+        self._m2 += d * (value - self.mean)
+        if correct:
+            self.correct += 1
+
+    @property
+    def variance(self) -> float:
+        return self._m2 / (self.n - 1) if self.n > 1 else 0.0
+
+    @property
+    def accuracy(self) -> float:
+        return self.correct / self.n if self.n else 0.0
+
+    def stderr(self) -> float:
+        return math.sqrt(self.variance / self.n) if self.n else 0.0
+
+
+# ---- throughput ------------------------------------------------------------------------------------------------------------------------------
+@dataclass
+class ThroughputResult:
+    tokens: int
+    seconds: float
+    latencies_ms: list[float]
+
+    @property
+    def tokens_per_second(self) -> float:
+        return self.tokens / self.seconds if self.seconds > 0 else 0.0
+
+    def percentile(self, q: float) -> float:
+        return float(np.percentile(self.latencies_ms, q)) if self.latencies_ms else 0.0
+
+    def summary(self) -> dict:
+        return {"tokens": self.tokens, "seconds": self.seconds, "tokens_per_second": self.tokens_per_second, "p50_ms": self.percentile(50),
+                "p95_ms": self.percentile(95), "p99_ms": self.percentile(99)}
+
+
+class ThroughputBenchmark:
+    def __init__(self, warmup: int = 1, runs: int = 3):
+        self.warmup, self.runs = warmup, runs
+
+    def run(self, generate_fn: Callable[[], int]) -> ThroughputResult:
+        """``generate_fn()`` performs one generation and returns the number of tokens it produced."""
+        for _ in range(self.warmup):
+            generate_fn()
+        toks, lat, t0 = 0, [], time.perf_counter()
+        for _ in range(self.runs):
+            t = time.perf_counter()
+            n = generate_fn()
+            dt = time.perf_counter() - t
+            toks += n
+            lat.append(dt * 1e3 / max(n, 1))
+        return ThroughputResult(toks, time.perf_counter() - t0, lat)
+
+
+# ---- reports -------------------------------------------------------------------------------------------------------------------------------------
+@dataclass
+class EvalReport:
+    model: str
+    results: dict[str, dict] = field(default_factory=dict)
+
+    def add(self, task: str, **metrics) -> "EvalReport":
+        self.results[task] = metrics
+        return self
+
+    def to_json(self) -> str:
+        return json.dumps({"model": self.model, "results": self.results}, indent=2)
+
+    def to_markdown(self) -> str:
+        out = f"# Evaluation report: {self.model}\n\n| Task | Metric | Value |\n|---|---|---|\n"
+        for task, m in self.results.items():
+            for k, v in m.items():
+                out += f"| {task} | {k} | {v:.4f} |\n" if isinstance(v, float) else f"| {task} | {k} | {v} |\n"
+        return out

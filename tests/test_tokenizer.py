@@ -1,0 +1,88 @@
+"""Tokenizers on CPU: byte-level BPE with the C++ merge engine, HF json loading, trainer, streaming decoder, chat
+templates, Unigram / WordPiece / char models, byte fallback and text serialisation."""
+import json
+
+import pytest
+
+from oxibonsai_b200 import tokenizer as T
+from oxibonsai_b200.tokenizer import extras as X
+
+CORPUS = ["the quick brown fox jumps over the lazy dog", "the quicker the better", "lazy dogs and quick foxes", "héllo wörld, the end"] * 4
+
+
+def test_bpe_train_encode_decode_roundtrip_and_merges_run_in_native_code():
+    tok = T.train_bpe(CORPUS, vocab_size=320, special_tokens=["<|im_start|>", "<|im_end|>"])
+    assert 256 < len(tok.vocab) <= 318 and tok.merges and tok.vocab_size == max(tok.special.values()) + 1
+    for text in CORPUS + ["unseen wörds ☃ too", ""]:
+        ids = tok.encode(text)
+        assert tok.decode(ids) == text
+    ids = tok.encode("the the the")
+    assert len(ids) < len("the the the")                                   # merges were applied
+    assert tok.encode("the") == tok.encode("the")                           # cache hit path gives the same ids
+    sp = tok.encode("<|im_start|>user\nhi<|im_end|>")
+    assert sp[0] == tok.special["<|im_start|>"] and sp[-1] == tok.special["<|im_end|>"]
+    assert tok.decode(sp, skip_special=True) == "user\nhi" and tok.encode("<|im_end|>", allow_special=False) != [tok.special["<|im_end|>"]]
+    assert b"".join(tok.token_bytes(i) for i in tok.encode("héllo")) == "héllo".encode()
+    assert tok.encode_batch(["a", "b"]) == [tok.encode("a"), tok.encode("b")]
+
+
+def test_hf_json_loading_and_text_serialisation(tmp_path):
+    tok = T.train_bpe(CORPUS, vocab_size=300, special_tokens=["<eos>"])
+    inv = {i: t for t, i in tok.vocab.items()}
+    j = {"model": {"type": "BPE", "vocab": tok.vocab, "merges": [f"{inv[a]} {inv[b]}" for a, b, _ in tok.merges]},
+         "added_tokens": [{"id": i, "content": t} for t, i in tok.special.items()]}
+    p = tmp_path / "tokenizer.json"
+    p.write_text(json.dumps(j))
+    again = T.BpeTokenizer.from_hf_json(str(p))
+    text = "the quick brown fox<eos>"
+    assert again.encode(text) == tok.encode(text) and isinstance(T.load_tokenizer(str(p)), T.BpeTokenizer)
+    assert isinstance(T.load_tokenizer(None), T.ByteTokenizer) and T.load_tokenizer(str(p), "bytes").vocab_size == 256
+    pairs = tmp_path / "pairs.json"
+    j["model"]["merges"] = [[inv[a], inv[b]] for a, b, _ in tok.merges]       # the list-of-pairs form of newer files
+    pairs.write_text(json.dumps(j))
+    assert T.BpeTokenizer.from_hf_json(str(pairs)).encode(text) == tok.encode(text)
+    j["model"]["type"] = "Unigram"
+    p.write_text(json.dumps(j))
+    with pytest.raises(ValueError):
+        T.BpeTokenizer.from_hf_json(str(p))
+    txt = tmp_path / "bpe.txt"
+    X.save_bpe_text(tok, str(txt))
+    assert X.load_bpe_text(str(txt)).encode(text) == tok.encode(text)
+
+
+def test_streaming_decoder_never_splits_utf8():
+    d = T.StreamingDecoder()
+    data = "añ☃😀z".encode()
+    out = [d.push(bytes([b])) for b in data]
+    assert "".join(out) + d.flush() == "añ☃😀z" and all("�" not in o for o in out)
+    assert out[1] == "" and out[2] == "ñ"
+    d2 = T.StreamingDecoder()
+    assert d2.push(b"\xe2\x98") == "" and d2.flush() == "�"
+
+
+def test_chat_templates():
+    msgs = [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}, {"role": "assistant", "content": "A"}, {"role": "user", "content": "Q"}]
+    assert T.chat_prompt(msgs, "chatml") == "<|im_start|>system\nS<|im_end|>\n<|im_start|>user\nU<|im_end|>\n<|im_start|>assistant\nA<|im_end|>\n<|im_start|>user\nQ<|im_end|>\n<|im_start|>assistant\n"
+    assert T.chat_prompt(msgs, "qwen") == T.chat_prompt(msgs, "chatml") and not T.chat_prompt(msgs, "chatml", add_generation_prompt=False).endswith("assistant\n")
+    l3 = T.chat_prompt(msgs, "llama3")
+    assert l3.startswith("<|begin_of_text|><|start_header_id|>system<|end_header_id|>\n\nS<|eot_id|>") and l3.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    assert T.chat_prompt(msgs, "mistral") == "<s>[INST] S\n\nU [/INST] A</s>[INST] Q [/INST]"
+    assert T.chat_prompt(msgs[1:2], "gemma") == "<bos><start_of_turn>user\nU<end_of_turn>\n<start_of_turn>model\n"
+    with pytest.raises(ValueError):
+        T.chat_prompt(msgs, "nope")
+
+
+def test_unigram_wordpiece_char_and_byte_fallback():
+    u = X.UnigramTokenizer([("<unk>", 0.0), ("▁", -2.0), ("▁the", -1.0), ("▁th", -3.0), ("e", -2.5), ("▁c", -3.0), ("a", -2.0), ("t", -2.0), ("at", -1.5), ("▁cat", -6.5)])
+    ids = u.encode(" the cat")
+    assert [u.pieces[i] for i in ids] == ["▁the", "▁c", "at"] and u.decode(ids) == " the cat"      # -1 -3 -1.5 beats -1 -6.5
+    assert u.encode("x") == [0] and u.token_bytes(2) == b" the"
+    w = X.WordPieceTokenizer(["[UNK]", "un", "##aff", "##able", "play", "##ing", ",", "aff"], lowercase=True)
+    assert [w.tokens[i] for i in w.encode("Unaffable, playing xyz")] == ["un", "##aff", "##able", ",", "play", "##ing", "[UNK]"]
+    assert w.decode(w.encode("unaffable playing")) == "unaffable playing"
+    c = X.CharTokenizer("hello")
+    assert c.decode(c.encode("hello")) == "hello" and c.encode("z") == [0] and c.vocab_size == 5
+    vocab = {"a": 1, "b": 2, **{X.byte_fallback_token(b): 10 + b for b in range(256)}}
+    ids = X.encode_with_byte_fallback("aé", vocab)
+    assert ids == [1, 10 + 0xC3, 10 + 0xA9] and X.decode_with_byte_fallback(ids, {v: k for k, v in vocab.items()}) == "aé"
+    assert X.parse_byte_fallback("<0x0A>") == 10 and X.parse_byte_fallback("<0xZZ>") is None and X.parse_byte_fallback("abc") is None
