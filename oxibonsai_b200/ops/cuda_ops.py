@@ -131,6 +131,40 @@ def _mma():
     return l
 
 
+_QG_SIG = {
+    "bonsai_quant_gemv": [_i, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp],
+    "bonsai_swiglu": [_vp, _vp, _vp, _i, _vp],
+}
+_qg_declared = False
+
+
+def _qg():
+    global _qg_declared
+    l = lib()
+    if not _qg_declared:
+        declare(_QG_SIG)
+        _qg_declared = True
+    return l
+
+
+def quant_gemv(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
+               residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n] = (residual) + W (rmsnorm(x)) for ``w`` = the raw GGUF bytes (uint8 CUDA tensor) of an [n, k] matrix of ``type_id`` blocks."""
+    assert w.is_cuda and w.dtype == torch.uint8
+    _f32c(x)
+    if out is None:
+        out = torch.empty(n, dtype=torch.float32, device=x.device)
+    check(_qg().bonsai_quant_gemv(type_id, w.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual), n, k, stream()), "quant_gemv")
+    return out
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty_like(gate)
+    check(_qg().bonsai_swiglu(_f32c(gate).data_ptr(), _f32c(up).data_ptr(), out.data_ptr(), gate.numel(), stream()), "swiglu")
+    return out
+
+
 class FragWeight:
     """A packed matrix in the tensor-core fragment layout of the batch-1 decode GEMV (see csrc/cuda/bitgemv_mma.cu):
     ``codes`` uint4 [N/16][K/128][32 lanes], ``scales`` half2 [N/16][K/128][8]."""

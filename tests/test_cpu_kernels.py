@@ -1,0 +1,73 @@
+"""CPU kernel tiers: reference tier bit-identical to the oracle, AVX2 tier close, float ops, dispatcher (CPU)."""
+import numpy as np
+import pytest
+
+from oxibonsai_b200.core import gguf as G
+from oxibonsai_b200.core.blocks import dequantize, quantize
+from oxibonsai_b200.core.oracle import cpu_gemv
+from oxibonsai_b200.ops import cpu_ops as CK
+
+
+@pytest.mark.parametrize("ty", [G.TQ2_0_G128, G.Q1_0_G128])
+def test_tiers_against_oracle(ty):
+    rng = np.random.default_rng(0)
+    rows, cols = 300, 512
+    w = rng.normal(size=(rows, cols)).astype(np.float32) * 0.05
+    q = quantize(ty, w)
+    x = rng.normal(size=cols).astype(np.float32)
+    oracle = cpu_gemv(ty, q, rows, cols, x)
+    ref = CK.gemv(ty, q, rows, cols, x, CK.KernelTier.REFERENCE, threads=3)
+    assert np.array_equal(ref, oracle)                                     # same summation order, any thread count
+    best = CK.detect_tier()
+    fast = CK.gemv(ty, q, rows, cols, x, best)
+    assert np.allclose(fast, oracle, rtol=1e-4, atol=1e-5)
+    xb = rng.normal(size=(5, cols)).astype(np.float32)
+    want = xb.astype(np.float64) @ dequantize(ty, q).reshape(rows, cols).astype(np.float64).T
+    assert np.allclose(CK.gemm(ty, q, rows, cols, xb), want, rtol=1e-4, atol=1e-4)
+
+
+def test_tier_control_and_errors():
+    best = CK.detect_tier()
+    assert CK.set_tier(CK.KernelTier.REFERENCE) == CK.KernelTier.REFERENCE and CK.set_tier(None) == best and CK.set_tier(99) == best
+    assert CK.tier_name(0) == "reference" and CK.tier_name(CK.KernelTier.GPU) == "gpu" and CK.KernelTier.AVX2.is_accelerated
+    q = quantize(G.TQ2_0_G128, np.zeros((2, 128), np.float32))
+    with pytest.raises(CK.UnsupportedOperation):
+        CK.gemv(G.Q4_0, q, 2, 128, np.zeros(128))
+    with pytest.raises(CK.NotBlockAligned):
+        CK.gemv(G.TQ2_0_G128, q, 2, 100, np.zeros(100))
+    with pytest.raises(CK.BufferTooSmall):
+        CK.gemv(G.TQ2_0_G128, q, 3, 128, np.zeros(128))
+    with pytest.raises(CK.DimensionMismatch):
+        CK.gemv(G.TQ2_0_G128, q, 2, 128, np.zeros(64))
+    assert issubclass(CK.GpuError, CK.KernelError)
+
+
+def test_float_ops():
+    rng = np.random.default_rng(1)
+    x, w = rng.normal(size=300).astype(np.float32), rng.uniform(0.5, 1.5, 300).astype(np.float32)
+    want = w * x / np.sqrt((x.astype(np.float64) ** 2).mean() + 1e-6)
+    assert np.allclose(CK.rms_norm(x, w, 1e-6, tier=0), want, rtol=1e-5) and np.allclose(CK.rms_norm(x, w, 1e-6, tier=1), want, rtol=1e-5)
+    assert np.allclose(CK.silu(x), x / (1 + np.exp(-x)), rtol=1e-5) and np.allclose(CK.swiglu(x, w), x / (1 + np.exp(-x)) * w, rtol=1e-5)
+    s = CK.softmax(x)
+    assert abs(s.sum() - 1) < 1e-5 and int(np.argmax(s)) == int(np.argmax(x))
+    from oxibonsai_b200.core.oracle import rope_table
+    cos, sin = rope_table(64, 8, 1e6)
+    v = rng.normal(size=(3, 64)).astype(np.float32)
+    r = CK.rope_apply(v, cos[5], sin[5])
+    assert np.allclose(np.linalg.norm(r, axis=1), np.linalg.norm(v, axis=1), rtol=1e-5)
+    assert np.allclose(r[:, :32], v[:, :32] * cos[5] - v[:, 32:] * sin[5], rtol=1e-5, atol=1e-6) and np.allclose(CK.rope_apply(v, cos[0], sin[0]), v)
+    b = CK.AlignedBuffer(100)
+    assert b.address % 64 == 0 and b.array.shape == (100,)
+    b.array[:] = 3.0
+    assert float(b.array.sum()) == 300.0
+
+
+def test_dispatcher_on_cpu():
+    d = CK.KernelDispatcher(tier=CK.detect_tier())
+    rng = np.random.default_rng(2)
+    w = rng.normal(size=(64, 256)).astype(np.float32)
+    q = quantize(G.Q1_0_G128, w)
+    x = rng.normal(size=256).astype(np.float32)
+    assert np.allclose(d.gemv(G.Q1_0_G128, q, 64, 256, x), cpu_gemv(G.Q1_0_G128, q, 64, 256, x), rtol=1e-4, atol=1e-5)
+    assert d.gemm(G.Q1_0_G128, q, 64, 256, x[None]).shape == (1, 64) and "threads=" in d.describe() and d.gpu_fallbacks == 0
+    assert CK.KernelDispatcher.auto_detect().tier in tuple(CK.KernelTier) and CK.GpuWeightHandle(3).id == 3
