@@ -40,6 +40,19 @@ class Oracle:
         check(self._lib.boracle_last_hidden(self._h, out.ctypes.data, out.size))
         return out
 
+    def keep_layer_hidden(self, on: bool = True) -> None:
+        """Keeps the residual stream after every layer of each forward (read it with :meth:`layer_hidden`)."""
+        self._lib.boracle_keep_layer_hidden.argtypes = [C.c_void_p, C.c_int]
+        self._lib.boracle_keep_layer_hidden(self._h, int(on))
+
+    def layer_hidden(self) -> np.ndarray:
+        out = np.empty((self.config.layers, self.config.hidden), dtype=np.float32)
+        self._lib.boracle_layer_hidden.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        self._lib.boracle_layer_hidden.restype = C.c_int
+        if self._lib.boracle_layer_hidden(self._h, out.ctypes.data, out.size) != 0:
+            raise RuntimeError("layer hidden states are not being kept; call keep_layer_hidden() before forward()")
+        return out
+
     def generate_greedy(self, prompt, max_new: int, stop_at_eos: bool = True):
         """Returns (token ids, per-step top-1 minus top-2 logit gaps)."""
         p = np.ascontiguousarray(prompt, dtype=np.uint32)

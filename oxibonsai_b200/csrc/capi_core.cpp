@@ -304,6 +304,13 @@ int boracle_last_hidden(void* h, float* out, uint64_t n) {
   std::memcpy(out, v.data(), v.size() * 4);
   return 0;
 }
+void boracle_keep_layer_hidden(void* h, int on) { static_cast<OracleModel*>(h)->keep_layer_hidden(on != 0); }
+int boracle_layer_hidden(void* h, float* out, uint64_t n) {
+  const std::vector<float>& v = static_cast<OracleModel*>(h)->layer_hidden();
+  if (v.empty() || n < v.size()) return -14;
+  std::memcpy(out, v.data(), v.size() * 4);
+  return 0;
+}
 // Returns the number of generated tokens (<= max_new) or a negative error code.
 int boracle_generate(void* h, const uint32_t* prompt, uint32_t n_prompt, uint32_t max_new, uint32_t* out, float* gaps,
                      int stop_at_eos) {

@@ -328,6 +328,7 @@ void OracleModel::forward(uint32_t token, uint32_t pos, float* logits) {
     cpu_swiglu(gate_.data(), up_.data(), act_.data(), c.inter);
     cpu_gemv(L.wdown, act_.data(), proj_.data());
     for (uint32_t i = 0; i < c.hidden; ++i) x_[i] += proj_[i];
+    if (!layer_hidden_.empty()) std::memcpy(&layer_hidden_[(size_t)l * c.hidden], x_.data(), (size_t)c.hidden * 4);
   }
   cpu_rmsnorm(x_.data(), out_norm_, normed_.data(), c.hidden, c.eps);
   if (logits) cpu_gemv(lm_head_, normed_.data(), logits);

@@ -52,6 +52,9 @@ class OracleModel {
                                         std::vector<float>* gaps, bool stop_at_eos = true);
   // Hidden state after the final norm of the last forward (for parity tests).
   const std::vector<float>& last_hidden() const { return normed_; }
+  // When enabled, the residual stream after every layer of the last forward is kept ([layers][hidden]).
+  void keep_layer_hidden(bool on) { layer_hidden_.assign(on ? (size_t)cfg_.layers * cfg_.hidden : 0, 0.0f); }
+  const std::vector<float>& layer_hidden() const { return layer_hidden_; }
 
  private:
   struct Layer {
@@ -68,6 +71,7 @@ class OracleModel {
   std::vector<Layer> layers_;
   std::vector<float> kcache_, vcache_;  // [layer][kv_head][max_seq][hd]
   std::vector<float> x_, normed_, q_, k_, v_, attn_, proj_, gate_, up_, act_;
+  std::vector<float> layer_hidden_;
   std::vector<std::vector<float>> owned_f32_;  // norm vectors converted from non-f32 storage
 
   const float* norm_vector(const GgufFile& f, const std::string& name, uint64_t n);

@@ -99,7 +99,7 @@ class GenericQwen3Engine:
     def _step_eager(self) -> None:
         c, eps = self.config, self.config.eps
         qd, kvd = c.heads * c.head_dim, c.kv_heads * c.head_dim
-        self.h.copy_(self.embd[self.token.long()[0]].float())
+        self.h.copy_(torch.index_select(self.embd, 0, self.token.long())[0].float())      # no host sync: capturable
         qkv = self.qkv[0]
         for l, w in enumerate(self.layers):
             w["q"](self.h, w["attn_norm"], eps, out=qkv[:qd])

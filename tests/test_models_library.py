@@ -348,3 +348,33 @@ def test_safetensors_to_gguf_conversion_roundtrip(tmp_path):
     assert g.metadata["llm.block_count"] == 2 and g.tensor_info("output.weight").type == G.TQ2_0_G128 and g.config().hidden == h
     with pytest.raises(ValueError):
         CV.convert_safetensors_to_gguf(str(d), out, quant="q9")
+
+
+def test_host_kv_caches_and_layer_stats(tiny_gguf):
+    from oxibonsai_b200.core import GgufFile, Oracle
+    from oxibonsai_b200.models import kv_cache as KV
+    rng = np.random.default_rng(0)
+    L, H, T, D = 2, 2, 8, 16
+    k, v = rng.normal(size=(H, D)).astype(np.float32), rng.normal(size=(H, D)).astype(np.float32)
+    for cls, tol in ((KV.KvCache, 0.0), (KV.KvCacheFp16, 2e-3), (KV.QuantizedKvCache, 0.02), (lambda *a: KV.Fp8KvCache(*a), 0.08),
+                     (lambda *a: KV.Fp8KvCache(*a, e5m2=True), 0.15)):
+        c = cls(L, H, T, D)
+        c.store(1, 3, k, v)
+        assert c.len == 4 and np.abs(c.keys(1, 0)[3] - k[0]).max() <= tol * np.abs(k[0]).max() + 1e-7
+        assert np.abs(c.values(1, 1, 4)[3] - v[1]).max() <= tol * np.abs(v[1]).max() + 1e-7 and c.nbytes > 0
+    d = KV.KvCache(L, H, T, D)
+    assert d.is_all_zero()
+    d.store(0, 0, k, v), d.store(0, 1, v, k)
+    kb, vb = d.extract_block(0, 2)
+    e = KV.KvCache(L, H, T, D)
+    e.inject_block(4, kb, vb)
+    assert e.len == 6 and np.array_equal(e.keys(0, 1)[5], v[1]) and not e.is_all_zero()
+    with pytest.raises(IndexError):
+        d.store(0, T, k, v)
+    q, s = KV.quantize_row_int8(k[0])
+    assert s == pytest.approx(np.abs(k[0]).max() / 127) and q.dtype == np.int8 and np.abs(q).max() == 127
+    p4, s4 = KV.quantize_row_int4(k[0])
+    assert p4.size == D // 2 and np.abs(KV.dequantize_row_int4(p4, s4) - k[0]).max() <= s4 / 2 + 1e-6
+    assert KV.QuantizedKvCache(L, H, T, D).compression_ratio() > 3
+    stats = KV.forward_with_stats(Oracle(GgufFile.open(tiny_gguf), 16), [1, 2, 3])
+    assert len(stats) == 2 and all(s.std > 0 and not s.has_nan for s in stats) and "layer   1" in stats[1].summary()
