@@ -386,7 +386,64 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         p = os.path.join(os.path.dirname(__file__), "chat.html")
         return HTMLResponse(open(p, encoding="utf-8").read())
 
+    # ---- retrieval endpoints (reference: crates/oxibonsai-runtime/src/rag_server.rs:484-492) ----
+    from ..rag import RagPipeline
+    app.state.rag = RagPipeline()
+
+    @app.post("/rag/index")
+    async def rag_index(request: Request):
+        body = await request.json()
+        docs = body.get("documents") or ([body["text"]] if "text" in body else [])
+        if not docs:
+            return error(400, "expected 'text' or 'documents'", "invalid_request_error", request.state.request_id)
+        n = sum(app.state.rag.index_document(d if isinstance(d, str) else d["text"], (body.get("metadata") if isinstance(d, str) else d.get("metadata")))
+                for d in docs)
+        return {"indexed_chunks": n, **app.state.rag.stats()}
+
+    @app.post("/rag/query")
+    async def rag_query(request: Request):
+        body = await request.json()
+        q = body.get("query")
+        if not q:
+            return error(400, "expected 'query'", "invalid_request_error", request.state.request_id)
+        hits = app.state.rag.query(q, body.get("top_k"))
+        out = {"hits": [{"text": h.text, "score": h.score, "metadata": h.metadata} for h in hits], "prompt": app.state.rag.build_prompt(q, body.get("top_k"))}
+        if body.get("generate"):
+            p, mt = sampling_from(body)
+            text, _, n_prompt, n_tok = await _collect(out["prompt"], p, mt, request.state.request_id)
+            out["answer"], out["usage"] = text, {"prompt_tokens": n_prompt, "completion_tokens": n_tok}
+        return out
+
+    @app.get("/rag/stats")
+    async def rag_stats():
+        return app.state.rag.stats()
+
+    async def _collect(prompt_text: str, p: SamplingParams, max_tokens: int, rid: str):
+        ids = tokenizer.encode(prompt_text)
+        parts, reason, n = [], "stop", 0
+        async for delta, fin in run_generation(ids, p, max_tokens, rid, []):
+            if delta:
+                parts.append(delta)
+                n += 1
+            if fin:
+                reason = fin
+        return "".join(parts), reason, len(ids), n
+
     return app
+
+
+def generate_json(engine_generate, tokenizer, request_json: str) -> str:
+    """String-in / string-out JSON API for embedding the engine in another host (the reference exposes the same shape
+    for its WASM build, crates/oxibonsai-runtime/src/wasm_api.rs:140): ``{"prompt": ..., "max_tokens": ...}`` ->
+    ``{"text": ..., "tokens": ..., "error": null}``."""
+    import json as _json
+    try:
+        req = _json.loads(request_json)
+        ids = tokenizer.encode(req["prompt"])
+        out = engine_generate(ids, int(req.get("max_tokens", 128)))
+        return _json.dumps({"text": tokenizer.decode(out), "tokens": len(out), "error": None})
+    except Exception as e:  # the caller gets a JSON error, never an exception
+        return _json.dumps({"text": "", "tokens": 0, "error": str(e)})
 
 
 def serve(app, host: str, port: int, log_level: str = "info") -> None:

@@ -160,6 +160,21 @@ def test_config_layering_and_validation(tmp_path):
         ServerConfig(temperature=3.0).validate()
 
 
+def test_rag_routes_and_json_api(client):
+    r = client.post("/rag/index", json={"documents": ["Bonsai trees need careful watering.", {"text": "Pines like full sun.", "metadata": {"k": 1}}]})
+    assert r.status_code == 200 and r.json()["documents"] == 2 and r.json()["indexed_chunks"] == 2
+    q = client.post("/rag/query", json={"query": "what do pines like?", "top_k": 1}).json()
+    assert q["hits"][0]["text"] == "Pines like full sun." and "Question: what do pines like?" in q["prompt"]
+    a = client.post("/rag/query", json={"query": "pines?", "generate": True, "max_tokens": 50}).json()
+    assert a["answer"] == "héllo wörld" and a["usage"]["completion_tokens"] > 0
+    assert client.get("/rag/stats").json()["chunks"] == 2 and client.post("/rag/query", json={}).status_code == 400
+    from oxibonsai_b200.server.app import generate_json
+    tok = ByteTokenizer()
+    out = json.loads(generate_json(lambda ids, n: ids[:n], tok, json.dumps({"prompt": "abcdef", "max_tokens": 3})))
+    assert out == {"text": "abc", "tokens": 3, "error": None}
+    assert json.loads(generate_json(lambda ids, n: ids, tok, "{broken"))["error"]
+
+
 def test_tool_call_parsing():
     from oxibonsai_b200.runtime.tools import parse_tool_calls, tools_system_prompt
     calls = parse_tool_calls('sure <tool_call>{"name": "get_weather", "arguments": {"city": "Kyoto"}}</tool_call>')
