@@ -210,6 +210,31 @@ def test_hash_ring_registry_coordinator_and_replica_pool():
     assert bad.pick(key) == "gpu1"                         # the failed replica is taken out of rotation
 
 
+def test_sse_formatter_token_stream_and_middleware_pieces():
+    from oxibonsai_b200.runtime import streaming as ST
+    f = ST.SseFormatter("rid", "m", created=1, include_usage=True)
+    first = f.first_chunk()
+    assert first.startswith("data: ") and first.endswith("\n\n") and json.loads(first[6:])["choices"][0]["delta"] == {"role": "assistant"}
+    tok = json.loads(f.token_chunk("héllo\nwörld")[6:])
+    assert tok["choices"][0]["delta"]["content"] == "héllo\nwörld" and tok["object"] == "chat.completion.chunk"
+    fin = json.loads(f.final_chunk("length", {"total_tokens": 3})[6:])
+    assert fin["choices"][0]["finish_reason"] == "length" and fin["usage"] == {"total_tokens": 3}
+    assert ST.SseFormatter.done_sentinel() == "data: [DONE]\n\n" and f.error_event("boom").startswith("event: error\ndata: ")
+    assert ST.SseFormatter.format_event("a\nb") == "data: a\ndata: b\n\n"
+    ts = ST.TokenStream()
+    assert ts.is_empty() and ts.push_token_bytes(b"\xc3") == "" and ts.push_token_bytes(b"\xa9x") == "éx" and ts.flush() == "" and ts.emitted == "éx"
+    st = ST.StreamStats(prompt_tokens=4)
+    st.on_token(), st.on_token(), st.finish()
+    assert st.to_usage_chunk() == {"prompt_tokens": 4, "completion_tokens": 2, "total_tokens": 6} and st.ttft() >= 0 and st.throughput() > 0
+    ctx = ST.RequestContext("r1", "POST", "/v1/completions")
+    assert ST.RequestLogger.format_request_line(ctx) == "--> POST /v1/completions [r1]" and "<-- 200 POST" in ST.RequestLogger.format_response_line(ctx, 200)
+    g = ST.RequestIdGen("t")
+    assert [g.next(), g.next()] == ["t-00000001", "t-00000002"]
+    c = ST.CorsConfig(allowed_origins=("https://a.example",))
+    assert c.is_origin_allowed("https://a.example") and not c.access_control_headers("https://evil.example")
+    assert ST.CorsConfig().access_control_headers("x")["access-control-allow-origin"] == "*"
+
+
 def test_async_engine_bounds_concurrency_and_streams():
     running, peak = [0], [0]
 
