@@ -28,6 +28,7 @@
 namespace bonsai {
 
 constexpr int kPfStages = 4;
+constexpr int kPfAhead = 8;                   // code vectors each expander thread keeps in flight
 constexpr int kPfABytes = 128 * 128;          // 128 rows x 64 f16
 constexpr int kPfThreads = 320;               // warps 0-3 expand, 4-7 epilogue, 8 = MMA, 9 = TMA
 
@@ -57,7 +58,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 
 // TOK = tokens per tile (MMA N): 256 for prompt chunks, 64 for batched decode / verification.
 template <int TOK>
-__global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __grid_constant__ CUtensorMap xmap,
+__global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                      const __grid_constant__ CUtensorMap amap, PfParams p) {
   constexpr int kPfTokTile = TOK;
   constexpr int kPfBBytes = TOK * 128;
@@ -143,14 +144,31 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
       const bool row_ok = row < p.n_rows;
       const uint4* wp = reinterpret_cast<const uint4*>(p.codes + (size_t)(row_ok ? row : 0) * words_per_row);
       const __half* sp = p.scales + (size_t)(row_ok ? row : 0) * ngroups;
-      uint4 nxt = row_ok ? __ldg(wp) : make_uint4(0, 0, 0, 0);
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const uint4 cur = nxt;
-        if (kb + 1 < kblocks && row_ok) nxt = __ldg(wp + kb + 1);
-        const __half dh = row_ok ? __hmul(sp[kb >> 1], __float2half(128.0f)) : __float2half(0.0f);
+      // a thread walks its own weight row, so its loads are a dependent chain of cache misses unless several
+      // are in flight: keep kPfAhead 16-byte code vectors (and their group scales) requested ahead of use
+      uint4 cbuf[kPfAhead];
+      __half sbuf[kPfAhead];
+#pragma unroll
+      for (int j = 0; j < kPfAhead; ++j) {
+        const bool ok = row_ok && j < kblocks;
+        cbuf[j] = ok ? __ldg(wp + j) : make_uint4(0, 0, 0, 0);
+        sbuf[j] = ok ? sp[j >> 1] : __float2half(0.0f);
+      }
+      for (int kb0 = 0; kb0 < kblocks && !failed; kb0 += kPfAhead) {
+#pragma unroll
+      for (int j = 0; j < kPfAhead; ++j) {
+        const int kb = kb0 + j;
+        if (kb < kblocks && !failed) {   // no break: the unrolled loop keeps cbuf / sbuf in registers
+        const uint4 cur = cbuf[j];
+        const __half dh = __hmul(sbuf[j], __float2half(128.0f));
+        if (row_ok && kb + kPfAhead < kblocks) {
+          cbuf[j] = __ldg(wp + kb + kPfAhead);
+          sbuf[j] = sp[(kb + kPfAhead) >> 1];
+        }
         const __half2 d2 = __half2half2(dh);
         const int s = it % kPfStages;
-        if (!tc::mbar_wait(&empty_bar[s], ((it / kPfStages) & 1) ^ 1)) { failed = true; break; }
+        if (!tc::mbar_wait(&empty_bar[s], ((it / kPfStages) & 1) ^ 1)) failed = true;
+        if (!failed) {
         uint8_t* stage = sA + s * kPfABytes;
         const uint32_t w4[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
@@ -173,6 +191,10 @@ __global__ void __launch_bounds__(kPfThreads) bitgemm_prefill_kernel(const __gri
         tc::fence_proxy_async();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&full_bar[s]);
+        ++it;
+        }
+        }
+      }
       }
     }
     if (failed && t == 0) atomicExch(p.status, 1);
