@@ -81,6 +81,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--shapes", default=",".join(SHAPES))
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--balanced", action="store_true", help="gemm: equal (tile, k) ranges per SM wherever possible")
+    ap.add_argument("--whole-tiles", action="store_true", help="gemm: whole tiles per CTA instead of equal (tile, k) ranges")
     a = ap.parse_args()
     from oxibonsai_b200.ops import cuda_ops as K
     dev = torch.device("cuda:0")
@@ -118,7 +120,7 @@ def main() -> None:
 
                 def fn():
                     it[0] += 1
-                    K.bitgemm_prefill(ws[it[0] % len(ws)], x, out=out, status=status)
+                    K.bitgemm_prefill(ws[it[0] % len(ws)], x, out=out, status=status, balanced=(False if a.whole_tiles else (True if a.balanced else "auto")))
                 us = time_us(fn, a.iters, a.profile)
                 fl = 2.0 * n * k * T
                 rows_out.append({"case": f"gemm/{name}", "n": n, "k": k, "tokens": T, "us": round(us, 2), "TFLOP/s": round(fl / us / 1e6, 1),

@@ -36,8 +36,8 @@ int bonsai_tp_allgather_logits_at(void*, const float*, int, int, int, int, int, 
 int bonsai_tp_allreduce_oneshot_add(void*, float*, size_t, int, cudaStream_t);
 void* bonsai_tp_big_half_ptr(void*, int);
 int bonsai_tp_barrier(void*, cudaStream_t);
-int bonsai_bitgemm_prefill(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int, int,
-                           const void*, cudaStream_t);
+int bonsai_bitgemm_prefill_ws(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int,
+                              int, const void*, void*, size_t, int, cudaStream_t);
 int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, int, cudaStream_t);
 int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                         const float*, void*, int, cudaStream_t);
@@ -68,6 +68,8 @@ struct Runner {
   uint64_t gp[GP_COUNT];
   std::vector<uint64_t> lp;  // [layers][LP_COUNT]
   void* comm = nullptr;      // tensor-parallel communicator (csrc/comm), null when tp_size == 1
+  void* gemm_ws = nullptr;   // set from the prefill pointer table at every call
+  size_t gemm_ws_bytes = 0;
 };
 
 template <typename T>
@@ -154,7 +156,18 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   return 0;
 }
 
-enum PrefillPtr { PP_TOKENS = 0, PP_POSITIONS, PP_H, PP_XN, PP_QKV, PP_Q, PP_ATTN, PP_ACT, PP_STATUS, PP_COUNT };
+enum PrefillPtr {
+  PP_TOKENS = 0, PP_POSITIONS, PP_H, PP_XN, PP_QKV, PP_Q, PP_ATTN, PP_ACT, PP_STATUS,
+  PP_GEMM_WS, PP_GEMM_WS_BYTES,   // workspace of the GEMM's balanced work distribution (pointer, size as a plain integer)
+  PP_COUNT
+};
+
+static inline int pf_gemm(Runner& r, const void* codes, const void* scales, const void* x, int x_ld, float* out_f32, const float* residual,
+                          void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld, int sms, const void* dense_w,
+                          cudaStream_t st) {
+  return bonsai_bitgemm_prefill_ws(codes, scales, x, x_ld, out_f32, residual, out_f16, status, n_rows, K, T, epi, out_ld, sms, dense_w,
+                                   r.gemm_ws, r.gemm_ws_bytes, 1, st);
+}
 
 // One chunk of T prompt tokens of the sequence in `slot`, starting at position pos0: batched
 // embed -> per layer { norm -> QKV GEMM -> QK-norm+RoPE+KV append -> causal attention over the
@@ -178,6 +191,8 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   void* attn = P<void>(pp[PP_ATTN]);
   void* act = P<void>(pp[PP_ACT]);
   int* status = P<int>(pp[PP_STATUS]);
+  r.gemm_ws = P<void>(pp[PP_GEMM_WS]);
+  r.gemm_ws_bytes = (size_t)pp[PP_GEMM_WS_BYTES];
   const int xn_ld = hidden > qd ? hidden : qd;
   const int* bt = P<int>(sp[SP_BLOCK_TABLE]) + (size_t)slot * r.ic[IC_MAX_PAGES];
 
@@ -185,7 +200,7 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
+    RC(pf_gemm(r, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
                               hidden, T, 0, qkv_n, sms, nullptr, st));
     // every row of the chunk uses the same page list: a block-table stride of zero
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
@@ -195,21 +210,21 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
     RC(bonsai_attn_prefill(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
                            P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, st));
     if (!tp) {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
+      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
                                 hidden, sms, nullptr, st));
     } else {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, status, hidden, qd, T,
+      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, status, hidden, qd, T,
                                 0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
+    RC(pf_gemm(r, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
                               hidden, T, 2, inter, sms, nullptr, st));
     if (!tp) {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
                                 T, 1, hidden, sms, nullptr, st));
     } else {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, status, hidden,
+      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, status, hidden,
                                 inter, T, 0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
@@ -263,6 +278,8 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   void* attn16 = P<void>(pp[PP_ATTN]);
   void* act = P<void>(pp[PP_ACT]);
   int* status = P<int>(pp[PP_STATUS]);
+  r.gemm_ws = P<void>(pp[PP_GEMM_WS]);
+  r.gemm_ws_bytes = (size_t)pp[PP_GEMM_WS_BYTES];
   const int xn_ld = hidden > qd ? hidden : qd;
   // about four CTAs per SM over all (sequence, kv head, split) triples, within the workspace's split count
   int attn_splits = (4 * 148) / (nkv * batch);
@@ -273,7 +290,7 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
+    RC(pf_gemm(r, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
                               hidden, batch, 0, qkv_n, sms, nullptr, st));
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
                                   P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
@@ -284,21 +301,21 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
                           attn_splits, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
     RC(bonsai_norm_to_f16_paired(attn, qd, nullptr, r.eps, batch, qd, attn16, qd, 0, st));
     if (!tp) {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
+      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
                                 hidden, sms, nullptr, st));
     } else {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, status, hidden, qd,
+      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, status, hidden, qd,
                                 batch, 0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
     }
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
-    RC(bonsai_bitgemm_prefill(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
+    RC(pf_gemm(r, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
                               hidden, batch, 2, inter, sms, nullptr, st));
     if (!tp) {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
+      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
                                 batch, 1, hidden, sms, nullptr, st));
     } else {
-      RC(bonsai_bitgemm_prefill(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, status, hidden,
+      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, status, hidden,
                                 inter, batch, 0, hidden, sms, nullptr, st));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 1, st));
     }
@@ -306,13 +323,13 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   if (!(flags & 2)) {
     RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(r.gp[GP_OUT_NORM]), r.eps, batch, hidden, xn, xn_ld, 1, st));
     if (!tp) {
-      RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, logits, nullptr, nullptr, status, lm_rows, hidden, batch, 0, vocab, sms,
+      RC(pf_gemm(r, nullptr, nullptr, xn, xn_ld, logits, nullptr, nullptr, status, lm_rows, hidden, batch, 0, vocab, sms,
                                 P<void>(r.gp[GP_LM_HEAD]), st));
     } else {
       float* partial = P<float>(sp[SP_PARTIAL]);
       const int rows_per_rank = (vocab + r.ic[IC_TP_SIZE] - 1) / r.ic[IC_TP_SIZE];
       if (lm_rows > 0)
-        RC(bonsai_bitgemm_prefill(nullptr, nullptr, xn, xn_ld, partial, nullptr, nullptr, status, lm_rows, hidden, batch, 0, lm_rows, sms,
+        RC(pf_gemm(r, nullptr, nullptr, xn, xn_ld, partial, nullptr, nullptr, status, lm_rows, hidden, batch, 0, lm_rows, sms,
                                   P<void>(r.gp[GP_LM_HEAD]), st));
       RC(bonsai_tp_allgather_logits_at(r.comm, partial, 0, batch, lm_rows, r.ic[IC_TP_RANK] * rows_per_rank, vocab, st));
     }

@@ -33,6 +33,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#ifdef BONSAI_MBAR_TEST_WAIT
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -40,6 +49,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait: returns false when the limit is hit.
@@ -47,6 +57,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
+}
+// Bounded wait that sleeps between polls.  A warp that re-polls a barrier back to back keeps the shared-memory pipe
+// busy; with a dozen producer warps doing so, every other barrier operation of the CTA (the MMA issuer's waits and
+// commits, the copy issuer's arrivals) queued behind the polls and a pipeline step took ~1000 cycles with no work in
+// it.  Producers that run several stages ahead lose nothing by waking up ~0.1 us late.
+template <int SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(SLEEP_NS);
+  }
+  return false;
+}
+
+// Warp-wide bounded wait in which only lane 0 polls (32 lanes polling one barrier word serialise in the shared-memory
+// pipe and slow every other warp's barrier, bulk-copy and MMA traffic); the shuffle broadcasts the outcome and orders
+// the other lanes' later accesses after the observation.  SLEEP_NS > 0 backs off between polls (for long waits).
+template <int SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int lane) {
+  int ok = 1;
+  if (lane == 0) {
+    ok = 0;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+      if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---- async proxy ------------------------------------------------------------------------------

@@ -302,10 +302,12 @@ class Qwen3Runner:
              "h": torch.zeros((chunk, cfg.hidden), **f32), "xn": torch.zeros((chunk, max(cfg.hidden, qd)), **f16),
              "qkv": torch.zeros((chunk, (nq + 2 * nkv) * hd), **f32), "q": torch.zeros((chunk, nq, hd), **f32),
              "attn": torch.zeros((chunk, qd), **f16), "act": torch.zeros((chunk, w.inter_local), **f16),
-             "status": torch.zeros(1, **i32)}
-        order = ["tokens", "positions", "h", "xn", "qkv", "q", "attn", "act", "status"]
-        assert len(order) == K._pf().bonsai_runner_prefill_ptr_count()
-        b["ptrs"] = (C.c_uint64 * len(order))(*[b[k].data_ptr() for k in order])
+             "status": torch.zeros(1, **i32), "gemm_ws": getattr(self, "_gemm_ws", None)}
+        if b["gemm_ws"] is None:
+            b["gemm_ws"] = self._gemm_ws = K.new_gemm_workspace(dev)
+        order = ["tokens", "positions", "h", "xn", "qkv", "q", "attn", "act", "status", "gemm_ws"]
+        assert len(order) + 1 == K._pf().bonsai_runner_prefill_ptr_count()
+        b["ptrs"] = (C.c_uint64 * (len(order) + 1))(*[b[k].data_ptr() for k in order], b["gemm_ws"].numel())
         self._pf = b
         return b
 

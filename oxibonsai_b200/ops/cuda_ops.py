@@ -378,6 +378,8 @@ def bitgemv_tc(w: PlanarWeight, ws: TcWorkspace, act: TcActivations | None = Non
 # ---- prefill path -------------------------------------------------------------------------------------
 _PF_SIG = {
     "bonsai_bitgemm_prefill": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "bonsai_bitgemm_prefill_ws": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, C.c_size_t, _i, _vp],
+    "bonsai_bitgemm_prefill_ws_bytes": [],
     "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _i, _vp],
     "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -415,8 +417,31 @@ def norm_to_f16_paired(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps:
     return out
 
 
+_GEMM_WS: dict = {}
+
+
+def gemm_workspace(device) -> torch.Tensor:
+    """Zero-filled workspace that lets the tcgen05 GEMM cut its work into equal ranges per SM.  One per device, for
+    launches on one stream at a time; an engine that runs GEMMs on its own stream allocates its own with
+    ``new_gemm_workspace``."""
+    key = torch.device(device).index or 0
+    if key not in _GEMM_WS:
+        _GEMM_WS[key] = new_gemm_workspace(device)
+    return _GEMM_WS[key]
+
+
+def _balance_mode(balanced) -> int:
+    return 1 if balanced == "auto" else (2 if balanced else 0)
+
+
+def new_gemm_workspace(device) -> torch.Tensor:
+    fn = _pf().bonsai_bitgemm_prefill_ws_bytes
+    fn.restype = C.c_size_t
+    return torch.zeros(int(fn()), dtype=torch.uint8, device=device)
+
+
 def dense_gemm_f16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                   sms: int = 148) -> torch.Tensor:
+                   sms: int = 148, balanced: bool | str = "auto") -> torch.Tensor:
     """out[T, N] (f32) = x[T, K] @ w[N, K]^T for dense f16 operands (natural K order) on tcgen05; used for the LM head."""
     T, n = x.shape[0], w.shape[0]
     assert w.dtype == torch.float16 and x.dtype == torch.float16 and w.is_contiguous() and x.shape[1] == w.shape[1]
@@ -424,14 +449,19 @@ def dense_gemm_f16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = 
         out = torch.empty((T, n), dtype=torch.float32, device=x.device)
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=x.device)
-    check(_pf().bonsai_bitgemm_prefill(None, None, x.data_ptr(), x.stride(0), out.data_ptr(), None, None, status.data_ptr(), n, w.shape[1],
-                                       T, 0, out.stride(0), sms, w.data_ptr(), stream()), "dense_gemm_f16")
+    ws = gemm_workspace(x.device) if balanced else None
+    check(_pf().bonsai_bitgemm_prefill_ws(None, None, x.data_ptr(), x.stride(0), out.data_ptr(), None, None, status.data_ptr(), n,
+                                          w.shape[1], T, 0, out.stride(0), sms, w.data_ptr(), ptr(ws), ws.numel() if balanced else 0,
+                                          _balance_mode(balanced), stream()), "dense_gemm_f16")
     return out
 
 
 def bitgemm_prefill(w: PlanarWeight, x_paired: torch.Tensor, epi: int = 0, residual: torch.Tensor | None = None,
-                    out: torch.Tensor | None = None, status: torch.Tensor | None = None, sms: int = 148) -> torch.Tensor:
-    """out[T, N] = epilogue(W x) on tcgen05.  ``epi``: 0 f32 store, 1 f32 residual add, 2 f16 SwiGLU (paired-K), 3 f16 store."""
+                    out: torch.Tensor | None = None, status: torch.Tensor | None = None, sms: int = 148,
+                    balanced: bool | str = "auto") -> torch.Tensor:
+    """out[T, N] = epilogue(W x) on tcgen05.  ``epi``: 0 f32 store, 1 f32 residual add, 2 f16 SwiGLU (paired-K), 3 f16 store.
+    ``balanced``: "auto" = equal (tile, k) ranges per SM where that is expected to pay, True = wherever the workspace
+    allows, False = whole tiles per CTA."""
     T = x_paired.shape[0]
     assert x_paired.dtype == torch.float16 and x_paired.shape[1] == w.k
     n_out = w.n // 2 if epi == 2 else w.n
@@ -441,8 +471,10 @@ def bitgemm_prefill(w: PlanarWeight, x_paired: torch.Tensor, epi: int = 0, resid
         status = torch.zeros(1, dtype=torch.int32, device=x_paired.device)
     f32p = out.data_ptr() if epi <= 1 else None
     f16p = out.data_ptr() if epi >= 2 else None
-    check(_pf().bonsai_bitgemm_prefill(w.codes.data_ptr(), w.scales.data_ptr(), x_paired.data_ptr(), x_paired.stride(0), f32p, ptr(residual),
-                                       f16p, status.data_ptr(), w.n, w.k, T, epi, out.stride(0), sms, None, stream()), "bitgemm_prefill")
+    ws = gemm_workspace(x_paired.device) if balanced else None
+    check(_pf().bonsai_bitgemm_prefill_ws(w.codes.data_ptr(), w.scales.data_ptr(), x_paired.data_ptr(), x_paired.stride(0), f32p,
+                                          ptr(residual), f16p, status.data_ptr(), w.n, w.k, T, epi, out.stride(0), sms, None, ptr(ws),
+                                          ws.numel() if balanced else 0, _balance_mode(balanced), stream()), "bitgemm_prefill")
     return out
 
 

@@ -29,7 +29,8 @@ def test_paired_k_layout_round_trip():
 
 
 @pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
-@pytest.mark.parametrize("rows,cols,T", [(256, 256, 64), (6144, 4096, 300), (1000, 2560, 256), (512, 12288, 513), (4096, 1024, 1)])
+@pytest.mark.parametrize("rows,cols,T", [(256, 256, 64), (6144, 4096, 300), (1000, 2560, 256), (512, 12288, 513), (4096, 1024, 1),
+                                         (128, 12288, 7), (4096, 12288, 64), (24576, 4096, 33), (200, 128, 5), (640, 384, 65)])
 def test_bitgemm_prefill_matches_fp32(ty, rows, cols, T):
     from oxibonsai_b200.ops import cuda_ops as K
     raw, wd = _random_quant(ty, rows, cols, 21)
@@ -55,6 +56,13 @@ def test_bitgemm_prefill_matches_fp32(ty, rows, cols, T):
         got = ys.cpu()[:, perm].double()
         assert (got - want).abs().max().item() <= 3e-3 * want.abs().max().item() + 1e-4
     assert st.item() == 0
+    # the balanced distribution sums partial tiles in a fixed order: repeatable bit for bit, and close to whole tiles
+    y1 = K.bitgemm_prefill(pw, xp, status=st, balanced=True)
+    y2 = K.bitgemm_prefill(pw, xp, status=st, balanced=True)
+    y0 = K.bitgemm_prefill(pw, xp, status=st, balanced=False)
+    assert torch.equal(y1, y2) and st.item() == 0
+    assert (y1 - y0).abs().max().item() <= 5e-5 * scale
+    assert int(K.gemm_workspace(DEV)[:65536].view(torch.int32).abs().sum().item()) == 0   # counters back to zero
 
 
 @pytest.mark.parametrize("kvt,tol", [(1, 4e-3), (0, 3e-3), (2, 3e-2)])
