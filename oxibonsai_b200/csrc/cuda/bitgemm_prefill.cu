@@ -129,8 +129,15 @@ __device__ __forceinline__ void pf_expand(uint8_t* stage, int r, const uint4& cu
   }
 }
 
+// residual input of one output element (epi 1), 0 otherwise.  Callers load a block of these before storing the block:
+// the output usually aliases the residual (h += W x), so inside a store loop the compiler has to order every load
+// after the previous store and the loop becomes a chain of exposed memory latencies.
+__device__ __forceinline__ float pf_residual(const PfParams& p, int tok, int row, bool row_ok) {
+  return p.epi == 1 && row_ok && tok < p.T ? p.residual[(size_t)tok * p.out_ld + row] : 0.0f;
+}
+
 // epilogue for one accumulator value; every lane of the warp calls it (epi 2 exchanges gate / up between lanes)
-__device__ __forceinline__ void pf_store(const PfParams& p, float v, int tok, int row, int a, bool row_ok) {
+__device__ __forceinline__ void pf_store(const PfParams& p, float v, float res, int tok, int row, int a, bool row_ok) {
   if (p.epi == 2) {
     float other = __shfl_xor_sync(0xffffffffu, v, 1);
     if (row_ok && tok < p.T && (a & 1) == 0)
@@ -138,7 +145,7 @@ __device__ __forceinline__ void pf_store(const PfParams& p, float v, int tok, in
   } else if (row_ok && tok < p.T) {
     const size_t o = (size_t)tok * p.out_ld + row;
     if (p.epi == 0) p.out_f32[o] = v;
-    else if (p.epi == 1) p.out_f32[o] = p.residual[o] + v;
+    else if (p.epi == 1) p.out_f32[o] = res + v;
     else p.out_f16[o] = __float2half_rn(v);
   }
 }
@@ -168,6 +175,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   __shared__ uint32_t tmem_slot;
   __shared__ int s_info[4];
   __shared__ int s_slots[kPfMaxCtas];
+  __shared__ uint64_t red_bar;   // completion of the bulk copies that bring partial tiles in for the final reduction
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int npairs = p.K >> 7;
   const int row_tiles = (p.n_rows + 127) >> 7, tok_tiles = (p.T + TOK - 1) / TOK;
@@ -191,6 +199,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
       tc::mbar_init(&accf_bar[i], NISS);
       tc::mbar_init(&acce_bar[i], 4);
     }
+    tc::mbar_init(&red_bar, 1);
     tc::mbar_fence_init();
   }
   tc::tc_fence_before();
@@ -341,13 +350,20 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
             for (int v = 0; v < NV; ++v) {
               const int it = 2 * qq + hh0 + v, s = it % S, bs = (it / GK) % NBS;
               const uint32_t par = (((it / GK) / NBS) & 1) ^ 1;
+              PF_CLK(c0);
               if (!failed && !tc::mbar_wait_sleep<kPfPollNs>(&empty_bar[bs], par)) failed = true;
               if (!failed) {
                 if (t == 0 && qq < 6) PF_STAMP(2 + qq);
+                PF_CLK(c1);
                 if (!PF_SKIP(4)) pf_expand(sA + s * kPfABytes, r, cur[v], d2);
+                PF_CLK(c2);
                 tc::fence_proxy_async();
                 __syncwarp();
+                PF_CLK(c3);
                 if (lane == 0) tc::mbar_arrive(&full_bar[bs]);
+#ifdef BONSAI_PF_TRACE
+                if (t == 0 && (qq == 8 || qq == 20)) { const int b = qq == 8 ? 44 : 50; PF_CLK(c4); PF_PUT(b, c0); PF_PUT(b + 1, c1 - c0); PF_PUT(b + 2, c2 - c1); PF_PUT(b + 3, c3 - c2); PF_PUT(b + 4, c4 - c3); }
+#endif
               }
             }
           }
@@ -360,6 +376,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
     const int a = t - kPfExpThreads;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     int seg = 0;
+    uint32_t red_phase = 0;
     for (int q = 0; q < n && !failed; ++seg) {
       const long long I = I0 + q;
       const int tile = (int)(I / npairs), pair_b = (int)(I - (long long)tile * npairs);
@@ -374,39 +391,39 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
       if (!tc::mbar_wait_warp<64>(&accf_bar[ab], (seg >> 1) & 1, lane)) { failed = true; break; }
       tc::tc_fence_after();
       if (a == 0 && seg < 2) PF_STAMP(28 + 4 * seg);
+      constexpr int CB = 16;   // columns per step: accumulator block + second operand block + residual block in registers
 #pragma unroll 1
-      for (int c0 = 0; c0 < TOK; c0 += 32) {
-        uint32_t rr[32];
+      for (int c0 = 0; c0 < TOK; c0 += CB) {
+        uint32_t rr[CB];
         if (NACC == 1) {
-          tc::tmem_ld32(taddr + lane_base + ab * kAccCols + c0, rr);
+          tc::tmem_ld16(taddr + lane_base + ab * kAccCols + c0, rr);
           tc::tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) rr[j] = 0u;
+          for (int j = 0; j < CB; ++j) rr[j] = 0u;
         }
 #pragma unroll
         for (int acc = 0; acc < (NACC == 1 ? 0 : NACC); ++acc) {
           // issuer `acc` wrote its accumulator only if one of its pairs (q % NACC == acc) lies in this segment
           if (len < NACC && ((acc - q) & (NACC - 1)) >= len) continue;
+          uint32_t r2[CB];
+          tc::tmem_ld16(taddr + lane_base + ab * kAccCols + acc * TOK + c0, r2);
+          tc::tmem_wait_ld();
 #pragma unroll
-          for (int hc = 0; hc < 32; hc += 16) {
-            uint32_t r2[16];
-            tc::tmem_ld16(taddr + lane_base + ab * kAccCols + acc * TOK + c0 + hc, r2);
-            tc::tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) rr[hc + j] = __float_as_uint(__uint_as_float(rr[hc + j]) + __uint_as_float(r2[j]));
-          }
+          for (int j = 0; j < CB; ++j) rr[j] = __float_as_uint(__uint_as_float(rr[j]) + __uint_as_float(r2[j]));
         }
         if (c0 >= ncols) continue;
         if (whole) {
+          float res[CB];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) pf_store(p, __uint_as_float(rr[j]), tok0 + c0 + j, row, a, row_ok);
+          for (int j = 0; j < CB; ++j) res[j] = pf_residual(p, tok0 + c0 + j, row, row_ok);
+#pragma unroll
+          for (int j = 0; j < CB; ++j) pf_store(p, __uint_as_float(rr[j]), res[j], tok0 + c0 + j, row, a, row_ok);
         } else {
-          float4* dst = reinterpret_cast<float4*>(part + a * TOK + c0);   // a slot is [128 rows][TOK columns]
+          // a slot is [TOK columns][128 rows]: a warp's store and the reducer's reads run along the rows
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(rr[4 * j]), __uint_as_float(rr[4 * j + 1]), __uint_as_float(rr[4 * j + 2]),
-                                 __uint_as_float(rr[4 * j + 3]));
+          for (int j = 0; j < CB; ++j)
+            if (c0 + j < ncols) part[(c0 + j) * 128 + a] = __uint_as_float(rr[j]);
         }
       }
       tc::tc_fence_before();
@@ -438,30 +455,62 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
           for (int i = a; i < nc; i += 128)
             s_slots[i] = 2 * (cf + i) + (pf_range_start(1, cf + i, grid, ntiles, npairs) >= (long long)tile * npairs ? 0 : 1);
           pf_epi_barrier();
-          for (int cb = 0; cb < ncols; cb += 16) {   // 16 columns of two contributors at a time: eight 16-byte loads in flight
-            float v[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-            for (int i = 0; i < nc; i += 2) {
-              const bool two = i + 1 < nc;
-              const float4* src0 = reinterpret_cast<const float4*>(p.ws_part + (size_t)s_slots[i] * (128 * TOK) + a * TOK + cb);
-              const float4* src1 = reinterpret_cast<const float4*>(p.ws_part + (size_t)s_slots[two ? i + 1 : i] * (128 * TOK) + a * TOK + cb);
-              float4 x0[4], x1[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x0[j] = __ldcg(src0 + j);
-                x1[j] = two ? __ldcg(src1 + j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (TOK == 64 && q + len == n) {
+            // The CTA's last segment: its producers and MMAs are done, so the 192 KB of stage memory are idle.  One
+            // thread pulls the partial tiles in with bulk copies (five 32 KB slots per round, the sixth holds the
+            // running sum between rounds) and every thread adds its row from shared memory, contributors in CTA order.
+            // Summing straight from global memory instead is a chain of exposed L2 latencies (measured 15 us here).
+            float* stage = reinterpret_cast<float*>(base);
+            float* carry = stage + 5 * (128 * TOK);
+            for (int i0 = 0; i0 < nc && !failed; i0 += 5) {
+              const int cnt = min(5, nc - i0);
+              if (a == 0) {
+                PF_STAMP(36);
+                asm volatile("fence.proxy.async.global;" ::: "memory");   // the partials were written through the generic proxy
+                PF_STAMP(37);
+                tc::mbar_arrive_expect_tx(&red_bar, (uint32_t)(cnt * ncols * 128 * sizeof(float)));
+                for (int i = 0; i < cnt; ++i)
+                  tc::bulk_g2s(stage + i * (128 * TOK), p.ws_part + (size_t)s_slots[i0 + i] * (128 * TOK),
+                               (uint32_t)(ncols * 128 * sizeof(float)), &red_bar);
               }
+              // every thread polls the same barrier with the same limit, so they agree on the outcome
+              if (a == 0) PF_STAMP(38);
+              const bool landed = tc::mbar_wait_sleep<32>(&red_bar, red_phase & 1);
+              if (a == 0) PF_STAMP(39);
+              ++red_phase;
+              const bool last = i0 + cnt >= nc;
+              for (int cb = 0; cb < ncols && landed; cb += 8) {
+                float v[8], res[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {   // contributor i, then i + 1: the CTA order
-                v[4 * j] = (v[4 * j] + x0[j].x) + x1[j].x;
-                v[4 * j + 1] = (v[4 * j + 1] + x0[j].y) + x1[j].y;
-                v[4 * j + 2] = (v[4 * j + 2] + x0[j].z) + x1[j].z;
-                v[4 * j + 3] = (v[4 * j + 3] + x0[j].w) + x1[j].w;
+                for (int j = 0; j < 8; ++j) res[j] = last ? pf_residual(p, tok0 + cb + j, row, row_ok) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const int c = cb + j < ncols ? cb + j : ncols - 1;
+                  // all five slots are read unconditionally (independent loads; a slot beyond cnt holds stale but
+                  // readable data) and the unused ones are dropped in the sum, which runs in CTA order
+                  float x[5];
+#pragma unroll
+                  for (int i = 0; i < 5; ++i) x[i] = stage[i * (128 * TOK) + c * 128 + a];
+                  v[j] = i0 == 0 ? 0.0f : carry[c * 128 + a];
+#pragma unroll
+                  for (int i = 0; i < 5; ++i) v[j] += i < cnt ? x[i] : 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (last) pf_store(p, v[j], res[j], tok0 + cb + j, row, a, row_ok && cb + j < ncols);
+                  else if (cb + j < ncols) carry[(cb + j) * 128 + a] = v[j];
+                }
               }
+              if (a == 0) PF_STAMP(40);
+              pf_epi_barrier();   // every thread has read the slots before the next round overwrites them
+              if (!landed) failed = true;
             }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) pf_store(p, v[j], tok0 + cb + j, row, a, row_ok);
+          } else {
+            for (int c = 0; c < ncols; ++c) {
+              float v = 0.0f;
+              for (int i = 0; i < nc; ++i) v += __ldcg(p.ws_part + (size_t)s_slots[i] * (128 * TOK) + c * 128 + a);
+              pf_store(p, v, pf_residual(p, tok0 + c, row, row_ok), tok0 + c, row, a, row_ok);
+            }
           }
           if (a == 0) p.ws_count[tile] = 0;
         }
@@ -524,12 +573,12 @@ static int launch_prefill(const CUtensorMap& xmap, const CUtensorMap& amap, bons
   // shared tile costs every contributor a few microseconds (partial store, fence, counter) and the last one a
   // reduction, so the balanced split is taken where measurements show it pays: few tiles with a long K extent (the
   // down projection of a decode batch: 32 tiles x 192 k-blocks), or so many tiles that partial tiles are a small
-  // fraction of the work (the LM head over a decode batch).  256-token partial tiles (128 KB each) cost more than the
+  // fraction of the work (the LM head over a decode batch), or at most 32 tokens (partial tiles are then small).  256-token partial tiles (128 KB each) cost more than the
   // imbalance they remove.  balance: 0 = never, 1 = by this rule, 2 = whenever possible.
   int grid = (int)(total < sms ? total : sms);
   const size_t need = (size_t)kPfCounterBytes + (size_t)2 * grid * 128 * TOK * sizeof(float);
   const bool can = ws != nullptr && ws_bytes >= need && ntiles * (long long)sizeof(int) <= kPfCounterBytes && ntiles % grid != 0;
-  const bool pays = TOK == 64 && ((ntiles < grid && (p.K >> 7) >= 64) || ntiles >= 4ll * grid);
+  const bool pays = TOK == 64 && ((ntiles < grid && (p.K >> 7) >= 64) || ntiles >= 4ll * grid || p.T <= 32);
   p.streamk = can && (balance == 2 || (balance == 1 && pays)) ? 1 : 0;
   if (!p.streamk) grid = (int)(ntiles < sms ? ntiles : sms);
   p.ws_count = static_cast<int*>(ws);
