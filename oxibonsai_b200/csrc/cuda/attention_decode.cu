@@ -268,18 +268,46 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
   for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
     int g = idx / hd, d = idx - g * hd;
     size_t hb = ((size_t)b * nq + kvh * G + g);
+    // eight splits per step with all loads issued before the first use: a loop that consumes each load at once is a
+    // chain of exposed L2 round trips (2 x nsplit of them)
+    const float2* ml = reinterpret_cast<const float2*>(ws_ml) + hb * nsplit;
+    const float* ac = ws_acc + hb * nsplit * hd + d;
     float M = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ws_ml + (hb * nsplit + sp) * 2));
+    for (int sp0 = 0; sp0 < nsplit; sp0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = sp0 + i < nsplit ? __ldcg(ml + sp0 + i).x : -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) M = fmaxf(M, x[i]);
+    }
     float a = 0.0f, L = 0.0f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      float ms = __ldcg(ws_ml + (hb * nsplit + sp) * 2);
-      float f = (ms == -INFINITY) ? 0.0f : expf(ms - M);
-      a += f * __ldcg(ws_acc + (hb * nsplit + sp) * hd + d);
-      L += f * __ldcg(ws_ml + (hb * nsplit + sp) * 2 + 1);
+    for (int sp0 = 0; sp0 < nsplit; sp0 += 8) {
+      float2 mlv[8];
+      float av[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool ok = sp0 + i < nsplit;
+        mlv[i] = ok ? __ldcg(ml + sp0 + i) : make_float2(-INFINITY, 0.0f);
+        av[i] = ok ? __ldcg(ac + (size_t)(sp0 + i) * hd) : 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float f = (mlv[i].x == -INFINITY) ? 0.0f : expf(mlv[i].x - M);
+        a += f * av[i];
+        L += f * mlv[i].y;
+      }
     }
     out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
   }
 }
+
+#ifdef BONSAI_ATTN_TRACE
+// Optional timeline for tuning: clock64() stamps of thread 0 of every CTA (16 slots each).
+__device__ long long* g_attn_trace = nullptr;
+#define AT_STAMP(slot) do { if (g_attn_trace != nullptr && threadIdx.x == 0) g_attn_trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define AT_STAMP(slot) do { } while (0)
+#endif
 
 // ---- head_dim 128, compressed caches: half a warp per token --------------------------------------------
 // A 128-wide f16 row is 256 bytes = 16 lanes x 16 bytes, so the two halves of a warp walk two tokens
@@ -343,8 +371,10 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
   const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, sub = lane & 15;
+  AT_STAMP(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  AT_STAMP(1);
   const int len = positions[b] + 1 + extra_len;
   const int chunk = (len + nsplit - 1) / nsplit;
   const int t0 = split * chunk, t1 = min(len, t0 + chunk);
@@ -426,6 +456,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
         for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(p[u][g], vf[j], acc[g][j]);
     }
   }
+  AT_STAMP(2);
   // fold the two halves of the warp (they saw different tokens)
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -455,6 +486,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     }
   }
   __syncthreads();
+  AT_STAMP(3);
   for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
     int g = idx / hd, d = idx - g * hd;
     float M = -INFINITY;
@@ -475,8 +507,10 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
       ws_ml[o * 2 + 1] = L;
     }
   }
+  AT_STAMP(4);
   __threadfence();
   __syncthreads();
+  AT_STAMP(5);
   if (threadIdx.x == 0) {
     int* ctr = counters + (size_t)b * nkv + kvh;
     int prev = atomicAdd(ctr, 1);
@@ -484,22 +518,69 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     if (s_last) *ctr = 0;
   }
   __syncthreads();
+  AT_STAMP(6);
   if (!s_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
-    int g = idx / hd, d = idx - g * hd;
-    size_t hb = ((size_t)b * nq + kvh * G + g);
-    float M = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ws_ml + (hb * nsplit + sp) * 2));
-    float a = 0.0f, L = 0.0f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      float ms = __ldcg(ws_ml + (hb * nsplit + sp) * 2);
-      float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
-      a += f * __ldcg(ws_acc + (hb * nsplit + sp) * hd + d);
-      L += f * __ldcg(ws_ml + (hb * nsplit + sp) * 2 + 1);
-    }
-    out[hb * hd + d] = L > 0.0f ? a / L : 0.0f;
+  // Merge of the splits by the last CTA of this (sequence, kv head).  Every dependent trip to L2 costs ~600 cycles
+  // here, so the (max, sum) pairs go to shared memory in one trip, one warp per query head turns them into weights
+  // f[sp] = exp(m_sp - M) / L, and each thread then sums its outputs over the splits with twenty loads in flight.
+  float* s_f = sh;                    // [G][nsplit] weights (the warp-merge staging area is free by now)
+  float* s_l = sh + G * nsplit;       // [G][nsplit] partial sums
+  const size_t hb0 = (size_t)b * nq + kvh * G;
+  for (int i = threadIdx.x; i < G * nsplit; i += blockDim.x) {
+    const float2 v = __ldcg(reinterpret_cast<const float2*>(ws_ml) + hb0 * nsplit + i);   // heads of a group are adjacent
+    s_f[i] = v.x;
+    s_l[i] = v.y;
   }
+  __syncthreads();
+  if (warp < G) {
+    float M = -INFINITY;
+    for (int sp = lane; sp < nsplit; sp += 32) M = fmaxf(M, s_f[warp * nsplit + sp]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.0f;
+    for (int sp = lane; sp < nsplit; sp += 32) {
+      const float ms = s_f[warp * nsplit + sp];
+      const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+      L += f * s_l[warp * nsplit + sp];
+      s_f[warp * nsplit + sp] = f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int sp = lane; sp < nsplit; sp += 32) s_f[warp * nsplit + sp] *= inv;
+  }
+  __syncthreads();
+  constexpr int NI = (G * hd + 255) / 256;   // outputs per thread
+  float a[NI];
+  const float* ac[NI];
+  const float* fw[NI];
+#pragma unroll
+  for (int k = 0; k < NI; ++k) {
+    const int idx = min(threadIdx.x + k * 256, G * hd - 1);
+    const int g = idx / hd, d = idx - g * hd;
+    ac[k] = ws_acc + (hb0 + g) * nsplit * hd + d;
+    fw[k] = s_f + g * nsplit;
+    a[k] = 0.0f;
+  }
+  constexpr int SB = 20 / NI;   // splits per step
+  for (int sp0 = 0; sp0 < nsplit; sp0 += SB) {
+    float av[NI][SB];
+#pragma unroll
+    for (int k = 0; k < NI; ++k)
+#pragma unroll
+      for (int i = 0; i < SB; ++i) av[k][i] = sp0 + i < nsplit ? __ldcg(ac[k] + (size_t)(sp0 + i) * hd) : 0.0f;
+#pragma unroll
+    for (int k = 0; k < NI; ++k)
+#pragma unroll
+      for (int i = 0; i < SB; ++i) a[k] += (sp0 + i < nsplit ? fw[k][sp0 + i] : 0.0f) * av[k][i];
+  }
+#pragma unroll
+  for (int k = 0; k < NI; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx < G * hd) out[hb0 * hd + idx] = a[k];
+  }
+  AT_STAMP(7);
 }
 
 template <int KVT>
@@ -543,6 +624,12 @@ int launch_decode_d(int dpl, int G, dim3 grid, size_t smem, cudaStream_t st, con
 }  // namespace bonsai
 
 extern "C" {
+
+#ifdef BONSAI_ATTN_TRACE
+int bonsai_attn_decode_trace(long long* buf) {
+  return cudaMemcpyToSymbol(bonsai::g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // qkv: f32 [batch][qkv_stride] holding q | k | v heads.  Writes normalised+rotated q to q_out
 // [batch][nq][hd] and appends k, v at positions[b] through block_table [batch][max_pages].
