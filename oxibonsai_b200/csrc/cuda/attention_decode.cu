@@ -373,6 +373,27 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
   const int half = lane >> 4, sub = lane & 15;
   AT_STAMP(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int* bt = block_table + (size_t)b * max_pages;
+  const int pshift = 31 - __clz(pool.page_size), pmask = pool.page_size - 1;   // the launcher admits power-of-two pages only
+  {
+    // Ask L2 for this CTA's K and V rows while the previous kernel is still running.  Rows of earlier tokens do not
+    // depend on it; the position and block-table entries read here may be one step old (they are re-read after the
+    // wait), which only shifts what gets prefetched.  With ~110 tokens per CTA the loop below is two load rounds, so
+    // without this it pays the DRAM latency twice, after the dependency wait.
+    constexpr int kRowBytes = KVT == KV_F16 ? 256 : (KVT == KV_Q8 ? 128 : 64);
+    constexpr int kLines = kRowBytes >= 128 ? kRowBytes / 128 : 1;
+    const int plen = positions[b] + 1 + extra_len;
+    const int pchunk = (plen + nsplit - 1) / nsplit;
+    const int p0 = split * pchunk, p1 = min(plen, p0 + pchunk);
+    for (int i = threadIdx.x; i < (p1 - p0) * 2 * kLines; i += blockDim.x) {
+      const int tok = p0 + i / (2 * kLines), which = (i / kLines) & 1, line = i % kLines;
+      const int page = bt[tok >> pshift];
+      if (page < 0) continue;
+      const size_t row = ((size_t)page * nkv + kvh) * pool.page_size + (tok & pmask);
+      const uint8_t* ptr = (which ? pool.v : pool.k) + row * kRowBytes + line * 128;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   AT_STAMP(1);
   const int len = positions[b] + 1 + extra_len;
@@ -391,8 +412,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     m[g] = -INFINITY;
     l[g] = 0.0f;
   }
-  const int* bt = block_table + (size_t)b * max_pages;
-  const int pshift = 31 - __clz(pool.page_size), pmask = pool.page_size - 1;   // the launcher admits power-of-two pages only
   constexpr int kTok = 2 * kH128Unroll;   // tokens per warp iteration
   for (int tb = t0 + warp * kTok; tb < t1; tb += kAttnWarps * kTok) {
     RawRow8<KVT> kr[kH128Unroll], vr[kH128Unroll];
@@ -621,9 +640,17 @@ int launch_decode_d(int dpl, int G, dim3 grid, size_t smem, cudaStream_t st, con
   }
 }
 
+int attn_decode_mma_f16(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
+                        int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc, float* ws_ml, int* counters,
+                        float* out, int extra_len, float sm_scale, cudaStream_t stream);
+static int g_attn_force_cuda_cores = 0;
+
 }  // namespace bonsai
 
 extern "C" {
+
+// 1: f16 caches with head_dim 128 use the CUDA-core kernel instead of the tensor-core one (comparisons, tests)
+void bonsai_attn_decode_force_cuda_cores(int on) { bonsai::g_attn_force_cuda_cores = on; }
 
 #ifdef BONSAI_ATTN_TRACE
 int bonsai_attn_decode_trace(long long* buf) {
@@ -661,6 +688,12 @@ int bonsai_attn_decode(const float* q, const int* positions, const int* block_ta
   size_t smem = (size_t)kAttnWarps * G * (hd + 2) * sizeof(float);
   if (smem > 48 * 1024) return BONSAI_CUDA_BAD_ARG;
   float sc = 1.0f / sqrtf((float)hd);
+  if (hd == 128 && kvt == KV_F16 && !g_attn_force_cuda_cores) {
+    // tensor-core path; it declines (BAD_ARG) shapes it does not cover and the CUDA-core kernels below take over
+    const int rc = attn_decode_mma_f16(q, positions, block_table, max_pages, batch, nq, nkv, page_size, kpool, vpool, nsplit, ws_acc,
+                                       ws_ml, counters, out, extra_len, sc, stream);
+    if (rc != BONSAI_CUDA_BAD_ARG) return rc;
+  }
   if (hd == 128 && kvt != KV_F32 && (G == 1 || G == 2 || G == 4) && (page_size & (page_size - 1)) == 0) {
     switch (kvt) {
       case KV_F16: return launch_decode_h128<KV_F16>(G, grid, smem, stream, q, positions, block_table, max_pages, pool, nq, sc, ws_acc, ws_ml, counters, out, extra_len);

@@ -1,0 +1,324 @@
+// Split-KV decode attention for head_dim 128 over f16 pages on the warp-level tensor-core path.
+//
+// The CUDA-core decode kernel (attention_decode.cu, half a warp per token) executes ~190 warp instructions per
+// (token, kv head): dot-product FMAs, 16-lane shuffle reductions and the online-softmax bookkeeping of every token.
+// With 16 warps resident per SM that instruction stream, not HBM, bounds it (6.3 M warp instructions for 4096 tokens x 8
+// kv heads; 0.39 of the measured copy bandwidth at 64 x 1024 tokens).  Here a warp handles 16 tokens at a time:
+//   S = Q K^T      m16n8k16 MMAs, the query heads of the group as rows 0..G-1 of the 16-row A operand (rest zero)
+//   P = softmax    on the accumulator fragments (a row lives in four lanes: two shuffles per reduction)
+//   O += P V       m16n8k16 MMAs, P re-used from registers as the A operand, V through ldmatrix.trans
+// K and V tiles (16 tokens x 256 bytes) come in through cp.async into padded shared-memory rows, double buffered per
+// warp.  That is ~10 warp instructions per (token, kv head).  The work decomposition, the workspace format and the
+// last-CTA merge over splits are those of the CUDA-core kernel, so the two are interchangeable behind
+// bonsai_attn_decode.  Reference behaviour: crates/oxibonsai-kernels/src/gpu_backend/cuda_attn_kernels.rs
+// (single-query attention over the cached K/V of one sequence), which walks one head per block on CUDA cores.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace bonsai {
+
+constexpr int kMmaWarps = 4;
+constexpr int kMmaTile = 16;                          // tokens per warp tile
+constexpr int kMmaRow = 272;                          // bytes per token row in shared memory: 256 + 16 (bank spread)
+constexpr int kMmaTileBytes = kMmaTile * kMmaRow;     // 4352
+constexpr int kMmaHd = 128;
+
+__device__ __forceinline__ uint32_t mma_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 16-byte asynchronous copy; src_bytes = 0 writes zeros without reading the source
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (16x8, f32) += A (16x16, f16, row) * B (16x8, f16, col)
+__device__ __forceinline__ void mma_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+struct MmaAttnParams {
+  const float* q;            // [batch][nq][128] f32
+  const int* positions;
+  const int* block_table;    // [batch][max_pages]
+  const uint8_t* k;          // this layer's pools, f16 rows of 256 bytes: [(page * nkv + kvh) * page_size + slot]
+  const uint8_t* v;
+  float* ws_acc;             // [batch][nq][nsplit][128]
+  float* ws_ml;              // [batch][nq][nsplit][2]
+  int* counters;             // [batch][nkv], zero between launches
+  float* out;                // [batch][nq][128]
+  int max_pages, nq, nkv, page_size, extra_len;
+  float sm_scale;
+};
+
+template <int G>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_decode_mma_kernel(MmaAttnParams p) {
+  constexpr int hd = kMmaHd;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  // [warp][buffer][K | V] tiles, then the warp-merge staging area [warp][G][hd + 2] floats
+  uint8_t* tiles = smem_raw;
+  float* sh = reinterpret_cast<float*>(smem_raw + kMmaWarps * 4 * kMmaTileBytes);
+  __shared__ int s_last;
+  const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = lane >> 2, cq = lane & 3;   // accumulator row (query head of the group) and column pair of this lane
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int len = p.positions[b] + 1 + p.extra_len;
+  int chunk = (len + nsplit - 1) / nsplit;
+  chunk = (chunk + kMmaTile - 1) & ~(kMmaTile - 1);   // tiles never straddle a split boundary or (page_size >= 16) a page
+  const int t0 = split * chunk, t1 = min(len, t0 + chunk);
+  const int ntiles = t1 > t0 ? (t1 - t0 + kMmaTile - 1) / kMmaTile : 0;
+  const int* bt = p.block_table + (size_t)b * p.max_pages;
+  const int pshift = 31 - __clz(p.page_size), pmask = p.page_size - 1;
+
+  // Q as A-operand fragments: rows 0..G-1 hold the group's query heads (scaled), rows G..15 are zero
+  uint32_t qa[8][2];   // per 16-wide k step: a0 (row, k lo pair) and a2 (row, k hi pair); a1 = a3 = 0 (rows 8..15)
+  {
+    const float* qp = p.q + ((size_t)b * p.nq + kvh * G + (row < G ? row : 0)) * hd;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const float2 lo = *reinterpret_cast<const float2*>(qp + ks * 16 + 2 * cq);
+      const float2 hi = *reinterpret_cast<const float2*>(qp + ks * 16 + 8 + 2 * cq);
+      qa[ks][0] = row < G ? pack_h2(lo.x * p.sm_scale, lo.y * p.sm_scale) : 0u;
+      qa[ks][1] = row < G ? pack_h2(hi.x * p.sm_scale, hi.y * p.sm_scale) : 0u;
+    }
+  }
+  float o[16][4];   // O accumulators: 16 column tiles of 8 dims; [.][0..1] = this lane's row, [.][2..3] = row + 8 (unused)
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+  float m = -INFINITY, l = 0.0f;   // running max of the row (same in the row's four lanes) and this lane's share of the sum
+
+  uint8_t* wt = tiles + (size_t)warp * 4 * kMmaTileBytes;
+  auto issue_tile = [&](int j, int buf) {   // tile j of the CTA -> K, V buffers `buf` of this warp
+    const int tb = t0 + j * kMmaTile;
+    const int page = bt[tb >> pshift];
+    const size_t rowbase = ((size_t)page * p.nkv + kvh) * p.page_size + (tb & pmask);
+    const uint32_t kd = mma_smem_u32(wt + (2 * buf) * kMmaTileBytes), vd = kd + kMmaTileBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = i * 32 + lane, r = c >> 4, c16 = c & 15;
+      // rows past the end of the sequence are zero-filled: their scores are masked, but 0 x (stale NaN in V) is NaN
+      const int nb = tb + r < t1 ? 16 : 0;
+      cp_async16(kd + r * kMmaRow + c16 * 16, p.k + (rowbase + r) * 256 + c16 * 16, nb);
+      cp_async16(vd + r * kMmaRow + c16 * 16, p.v + (rowbase + r) * 256 + c16 * 16, nb);
+    }
+  };
+  int buf = 0;
+  if (warp < ntiles) issue_tile(warp, 0);
+  cp_async_commit();
+  for (int j = warp; j < ntiles; j += kMmaWarps, buf ^= 1) {
+    if (j + kMmaWarps < ntiles) issue_tile(j + kMmaWarps, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const uint32_t kb = mma_smem_u32(wt + (2 * buf) * kMmaTileBytes), vb = kb + kMmaTileBytes;
+    // ---- S = Q K^T for 16 tokens: two 8-token column tiles --------------------------------------
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ks += 2) {
+        // matrices: (k lo, ks), (k hi, ks), (k lo, ks + 1), (k hi, ks + 1) of tokens nt*8 .. nt*8+7
+        const int mi = lane >> 3, r = lane & 7;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kb + (nt * 8 + r) * kMmaRow + ((ks + (mi >> 1)) * 16 + (mi & 1) * 8) * 2, b0, b1, b2, b3);
+        mma_16816(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+        mma_16816(s[nt], qa[ks + 1][0], 0u, qa[ks + 1][1], 0u, b2, b3);
+      }
+    }
+    // ---- online softmax on the row of this lane (tokens tb + nt*8 + 2*cq + {0,1}) ------------------
+    const int tb = t0 + j * kMmaTile;
+    float mx = m;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (tb + nt * 8 + 2 * cq + e >= t1) s[nt][e] = -INFINITY;
+        mx = fmaxf(mx, s[nt][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float resc = (mx == -INFINITY) ? 1.0f : __expf(m - mx);   // exp(-inf) = 0 before the first token
+    float pr[2][2], ps = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[nt][e] = (mx == -INFINITY) ? 0.0f : __expf(s[nt][e] - mx);
+        ps += pr[nt][e];
+      }
+    l = l * resc + ps;
+    m = mx;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      o[nt][0] *= resc;
+      o[nt][1] *= resc;
+    }
+    // ---- O += P V: P (16 x 16 tokens) straight from the score fragments ------------------------------
+    const uint32_t pa0 = pack_h2(pr[0][0], pr[0][1]), pa2 = pack_h2(pr[1][0], pr[1][1]);
+#pragma unroll
+    for (int nt = 0; nt < 16; nt += 2) {
+      // matrices: (tokens 0-7, dims nt), (tokens 8-15, dims nt), (tokens 0-7, dims nt + 1), (tokens 8-15, dims nt + 1)
+      const int mi = lane >> 3, r = lane & 7;
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vb + ((mi & 1) * 8 + r) * kMmaRow + ((nt + (mi >> 1)) * 8) * 2, b0, b1, b2, b3);
+      mma_16816(o[nt], pa0, 0u, pa2, 0u, b0, b1);
+      mma_16816(o[nt + 1], pa0, 0u, pa2, 0u, b2, b3);
+    }
+    __syncwarp();   // every lane is done with this buffer before the next iteration's copies overwrite it
+  }
+  cp_async_wait<0>();
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+  // ---- combine the warps of the CTA ----------------------------------------------------------------
+  const int stride = hd + 2;
+  if (row < G) {
+    float* dst = sh + ((size_t)warp * G + row) * stride;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      dst[nt * 8 + 2 * cq] = o[nt][0];
+      dst[nt * 8 + 2 * cq + 1] = o[nt][1];
+    }
+    if (cq == 0) {
+      dst[hd] = m;
+      dst[hd + 1] = l;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+    const int g = idx / hd, d = idx - g * hd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
+    float a = 0.0f, L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) {
+      const float* src = sh + ((size_t)w * G + g) * stride;
+      const float f = (src[hd] == -INFINITY) ? 0.0f : __expf(src[hd] - M);
+      a += f * src[d];
+      L += f * src[hd + 1];
+    }
+    const size_t oi = (((size_t)b * p.nq + kvh * G + g) * nsplit + split);
+    p.ws_acc[oi * hd + d] = a;
+    if (d == 0) {
+      p.ws_ml[oi * 2] = M;
+      p.ws_ml[oi * 2 + 1] = L;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ctr = p.counters + (size_t)b * p.nkv + kvh;
+    const int prev = atomicAdd(ctr, 1);
+    s_last = (prev == nsplit - 1);
+    if (s_last) *ctr = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // ---- merge of the splits by the last CTA of this (sequence, kv head): see attention_decode.cu -----
+  float* s_f = sh;
+  float* s_l = sh + G * nsplit;
+  const size_t hb0 = (size_t)b * p.nq + kvh * G;
+  for (int i = threadIdx.x; i < G * nsplit; i += blockDim.x) {
+    const float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml) + hb0 * nsplit + i);
+    s_f[i] = v.x;
+    s_l[i] = v.y;
+  }
+  __syncthreads();
+  for (int g = warp; g < G; g += kMmaWarps) {   // one warp per query head of the group
+    float M = -INFINITY;
+    for (int sp = lane; sp < nsplit; sp += 32) M = fmaxf(M, s_f[g * nsplit + sp]);
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+    float L = 0.0f;
+    for (int sp = lane; sp < nsplit; sp += 32) {
+      const float ms = s_f[g * nsplit + sp];
+      const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+      L += f * s_l[g * nsplit + sp];
+      s_f[g * nsplit + sp] = f;
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o2);
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    __syncwarp();
+    for (int sp = lane; sp < nsplit; sp += 32) s_f[g * nsplit + sp] *= inv;
+  }
+  __syncthreads();
+  constexpr int NI = (G * hd + kMmaWarps * 32 - 1) / (kMmaWarps * 32);   // outputs per thread
+  constexpr int SB = NI >= 4 ? 5 : 20 / NI;                             // splits per step: ~20 loads in flight
+  float a[NI];
+#pragma unroll
+  for (int k = 0; k < NI; ++k) a[k] = 0.0f;
+  for (int sp0 = 0; sp0 < nsplit; sp0 += SB) {
+    float av[NI][SB];
+#pragma unroll
+    for (int k = 0; k < NI; ++k) {
+      const int idx = min((int)threadIdx.x + k * kMmaWarps * 32, G * hd - 1);
+#pragma unroll
+      for (int i = 0; i < SB; ++i)
+        av[k][i] = sp0 + i < nsplit ? __ldcg(p.ws_acc + ((hb0 + idx / hd) * nsplit + sp0 + i) * hd + (idx % hd)) : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < NI; ++k) {
+      const int idx = min((int)threadIdx.x + k * kMmaWarps * 32, G * hd - 1);
+#pragma unroll
+      for (int i = 0; i < SB; ++i) a[k] += (sp0 + i < nsplit ? s_f[(idx / hd) * nsplit + sp0 + i] : 0.0f) * av[k][i];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NI; ++k) {
+    const int idx = threadIdx.x + k * kMmaWarps * 32;
+    if (idx < G * hd) p.out[hb0 * hd + idx] = a[k];
+  }
+}
+
+template <int G>
+static int launch_mma(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
+  const size_t smem = (size_t)kMmaWarps * 4 * kMmaTileBytes + (size_t)kMmaWarps * G * (kMmaHd + 2) * sizeof(float);
+  static bool configured[64] = {};   // per template instance and device: the attribute belongs to the function in a context
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return BONSAI_CUDA_LAUNCH_FAILED;
+    configured[dev] = true;
+  }
+  const cudaError_t e = launch_pdl(attn_decode_mma_kernel<G>, grid, dim3(kMmaWarps * 32), smem, st, p);
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
+// Returns BONSAI_CUDA_BAD_ARG for shapes it does not cover; the caller then uses the CUDA-core kernel.
+int attn_decode_mma_f16(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
+                        int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc, float* ws_ml, int* counters,
+                        float* out, int extra_len, float sm_scale, cudaStream_t stream) {
+  const int G = nq / nkv;
+  if (page_size < kMmaTile || (page_size & (page_size - 1)) != 0 || 2 * G * nsplit > kMmaWarps * G * (kMmaHd + 2)) return BONSAI_CUDA_BAD_ARG;
+  MmaAttnParams p{q, positions, block_table, (const uint8_t*)kpool, (const uint8_t*)vpool, ws_acc, ws_ml, counters, out,
+                  max_pages, nq, nkv, page_size, extra_len, sm_scale};
+  const dim3 grid(nkv, nsplit, batch);
+  switch (G) {
+    case 1: return launch_mma<1>(p, grid, stream);
+    case 2: return launch_mma<2>(p, grid, stream);
+    case 4: return launch_mma<4>(p, grid, stream);
+    case 8: return launch_mma<8>(p, grid, stream);
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+}
+
+}  // namespace bonsai

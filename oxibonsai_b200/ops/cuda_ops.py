@@ -26,6 +26,7 @@ _SIG = {
     "bonsai_embed_f16": [_vp, _vp, _vp, _i, _i, _vp],
     "bonsai_qknorm_rope_kvstore": [_vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "bonsai_attn_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp],
+    "bonsai_attn_decode_force_cuda_cores": [_i],
     "bonsai_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp],
     "bonsai_runner_create": [_vp, _f, _vp, _vp],
     "bonsai_runner_destroy": [_vp],

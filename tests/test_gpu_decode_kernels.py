@@ -214,3 +214,50 @@ def test_attention_batch_with_different_lengths():
         sc = torch.einsum("hd,htd->ht", q[b].cpu(), Kc.repeat_interleave(2, 0)) / hd ** 0.5
         ref = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.repeat_interleave(2, 0))
         assert torch.allclose(out[b], ref, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 8), (8, 4), (32, 8), (16, 2)])
+@pytest.mark.parametrize("page", [16, 64])
+def test_tensor_core_decode_attention_f16(nq, nkv, page):
+    """head_dim 128 over f16 pages runs on the mma.sync kernel: against a plain fp32 reference of the same op, with
+    ragged lengths, shuffled pages, a draft tail (extra_len) and NaN in every cache row a sequence does not own."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    hd, G = 128, nq // nkv
+    g = torch.Generator().manual_seed(31)
+    lens = [1, 15, 16, 17, 250, 333]
+    B = len(lens)
+    pps = (max(lens) + 3 + page - 1) // page
+    perm = torch.randperm(B * pps, generator=g)
+    bt = perm.view(B, pps).to(torch.int32).to(dev)
+    kf = torch.randn((B * pps, nkv, page, hd), generator=g)
+    vf = torch.randn((B * pps, nkv, page, hd), generator=g)
+    kpool = torch.full((B * pps, nkv, page, hd), float("nan"), dtype=torch.float16, device=dev)
+    vpool = torch.full_like(kpool, float("nan"))
+    q = torch.randn((B, nq, hd), generator=g).to(dev)
+    for extra in (0, 3):
+        pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
+        refs = []
+        for b, L in enumerate(lens):
+            n = L + extra
+            pages = bt[b].long().cpu()
+            Kc = kf[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :n].half()
+            Vc = vf[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :n].half()
+            for t in range(n):   # only the rows the sequence owns are real numbers
+                kpool[pages[t // page], :, t % page] = Kc[:, t].to(dev)
+                vpool[pages[t // page], :, t % page] = Vc[:, t].to(dev)
+            sc = torch.einsum("hd,htd->ht", q[b].cpu(), Kc.float().repeat_interleave(G, 0)) / hd ** 0.5
+            refs.append(torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.float().repeat_interleave(G, 0)))
+        ref = torch.stack(refs)
+        for nsplit in (1, 5, 37):
+            out = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit, extra_len=extra)
+            assert torch.isfinite(out).all()
+            # q and the softmax weights are rounded to f16 for the tensor cores: ~1e-3 relative on the scores
+            assert (out.cpu() - ref).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item()), (nsplit, extra)
+            if G <= 4:
+                K.lib().bonsai_attn_decode_force_cuda_cores(1)
+                try:
+                    out2 = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit, extra_len=extra)
+                finally:
+                    K.lib().bonsai_attn_decode_force_cuda_cores(0)
+                assert (out - out2).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item())
