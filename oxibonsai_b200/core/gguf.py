@@ -173,7 +173,7 @@ class GgufFile:
             nd, ty, off, nb = C.c_uint32(), C.c_uint32(), C.c_uint64(), C.c_uint64()
             for i in range(self._lib.bgguf_n_tensors(self._h)):
                 check(self._lib.bgguf_tensor_info(self._h, i, name, 512, dims, C.byref(nd), C.byref(ty), C.byref(off), C.byref(nb)))
-                out.append(TensorInfo(name.value.decode(), tuple(dims[d] for d in range(nd.value)), ty.value, off.value, nb.value))
+                out.append(TensorInfo(name.value.decode("utf-8", errors="replace"), tuple(dims[d] for d in range(nd.value)), ty.value, off.value, nb.value))
             self._tensors = out
         return self._tensors
 
