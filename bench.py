@@ -31,6 +31,7 @@ import time
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 PUBLISHED_BASELINE_TOK_S = 21.9  # Ternary-Bonsai-1.7B, native CUDA, RTX 3060 (reference README.md:287)
+TP_WATCHDOG_S = 420              # the tensor-parallel measurement may not hold the result line back longer than this
 
 
 def parse_args():
@@ -260,25 +261,17 @@ def main() -> None:
     st_tokens = torch.tensor([float(m["st_e2e_tokens"])], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(st_tokens)
+    st_tok_total = float(st_tokens.item())   # host copy now: the result line must not touch the device later
     del eng
     torch.cuda.empty_cache()
 
-    # ---------------- tensor parallel over all N GPUs ----------------
-    tp = None
-    if world > 1 and not args.no_tp:
-        t0 = time.time()
-        teng = (EngineBuilder().model_path(path).preset("greedy").max_seq_len(max_seq).max_batch(max(1, S)).kv_cache(args.kv)
-                .device(f"cuda:{local_rank}").tensor_parallel(rank, world).build())
-        print(f"[bench] rank {rank}: TP engine ready in {time.time() - t0:.1f}s", file=sys.stderr)
-        tm = measure(teng, args, cfg, prompt, S, barrier, dev, torch.Generator().manual_seed(7), e2e=True, sched_e2e=False, clocks_gpu=None)
-        t_dev, t_e2e, t_st = reduce_max([tm["dev_ms"], tm["e2e_s"], tm["st_ms"]])
-        tp = {"parallelism": f"tp{world}", "batch1_tokens_per_s": round(1000.0 * args.steps / t_dev, 2), "batch1_ms_per_token": round(t_dev / args.steps, 4),
-              "batch1_e2e_tokens_per_s": round(tm["e2e_steps"] / t_e2e, 2) if t_e2e == t_e2e and t_e2e > 0 else None,
-              "ttft_s": round(tm["ttft"], 3), "weights_bytes_per_step_per_gpu": teng.weights.packed_bytes,
-              "streams_tokens_per_s": None if S < 2 else round(S * args.steps / (t_st * 1e-3), 1),
-              "streams_ms_per_step": None if S < 2 else round(t_st / args.steps, 4), "status": int(teng.runner.tp.status())}
+    emitted: list = []
 
-    if rank == 0:
+    def emit(tp):
+        """Rank 0 prints the result line (once)."""
+        if rank != 0 or emitted:
+            return
+        emitted.append(True)
         ms_per_step = dev_ms / args.steps
         value = world * 1000.0 / ms_per_step                    # N replicas, each one token per step
         e2e_value = world * m["e2e_steps"] / e2e_s if e2e_s == e2e_s and e2e_s > 0 else None
@@ -307,13 +300,46 @@ def main() -> None:
                 "metric": f"aggregate decode tok/s, {n_total} concurrent streams" + (f" ({per_replica} per replica)" if world > 1 else ""),
                 "n_streams": n_total, "prompt_len": sp_len, "value": round(n_total * args.steps / (st_ms * 1e-3), 1),
                 "ms_per_step": round(st_ms / args.steps, 4), "unit": "tokens/s",
-                "e2e_value": None if not st_tokens.item() else round(st_tokens.item() / st_e2e_s, 1),
+                "e2e_value": None if not st_tok_total else round(st_tok_total / st_e2e_s, 1),
                 "e2e_h2d_bytes_per_step": 4 * n_total, "e2e_d2h_bytes_per_step": 4 * n_total},
             "tp": tp,
             "hbm_roofline_frac_of_measured" if peaks else "hbm_roofline_frac_of_fallback": round(bytes_step / (ms_per_step * 1e-3) / (hbm * 1e9), 4),
             "impl": "ours",
         }
         print(json.dumps(line))
+
+    # ---------------- tensor parallel over all N GPUs ----------------
+    # The replica numbers above are the headline; the TP engine is measured afterwards and must not be able to lose
+    # them.  An exception is reported under "tp"; a rank that never comes back from a collective is cut off by a
+    # watchdog, after which rank 0 prints the line without TP numbers and every rank leaves.
+    tp = None
+    if world > 1 and not args.no_tp:
+        import threading
+
+        def bail():
+            emit({"parallelism": f"tp{world}", "error": f"no answer within {TP_WATCHDOG_S} s"})
+            sys.stdout.flush()
+            os._exit(0)
+
+        dog = threading.Timer(TP_WATCHDOG_S, bail)
+        dog.daemon = True
+        dog.start()
+        try:
+            t0 = time.time()
+            teng = (EngineBuilder().model_path(path).preset("greedy").max_seq_len(max_seq).max_batch(max(1, S)).kv_cache(args.kv)
+                    .device(f"cuda:{local_rank}").tensor_parallel(rank, world).build())
+            print(f"[bench] rank {rank}: TP engine ready in {time.time() - t0:.1f}s", file=sys.stderr)
+            tm = measure(teng, args, cfg, prompt, S, barrier, dev, torch.Generator().manual_seed(7), e2e=True, sched_e2e=False, clocks_gpu=None)
+            t_dev, t_e2e, t_st = reduce_max([tm["dev_ms"], tm["e2e_s"], tm["st_ms"]])
+            tp = {"parallelism": f"tp{world}", "batch1_tokens_per_s": round(1000.0 * args.steps / t_dev, 2), "batch1_ms_per_token": round(t_dev / args.steps, 4),
+                  "batch1_e2e_tokens_per_s": round(tm["e2e_steps"] / t_e2e, 2) if t_e2e == t_e2e and t_e2e > 0 else None,
+                  "ttft_s": round(tm["ttft"], 3), "weights_bytes_per_step_per_gpu": teng.weights.packed_bytes,
+                  "streams_tokens_per_s": None if S < 2 else round(S * args.steps / (t_st * 1e-3), 1),
+                  "streams_ms_per_step": None if S < 2 else round(t_st / args.steps, 4), "status": int(teng.runner.tp.status())}
+        except Exception as e:   # noqa: BLE001 - reported in the result line
+            tp = {"parallelism": f"tp{world}", "error": f"{type(e).__name__}: {e}"[:300]}
+        dog.cancel()
+    emit(tp)
     if world > 1:
         dist.destroy_process_group()
 

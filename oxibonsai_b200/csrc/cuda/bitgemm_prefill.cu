@@ -6,14 +6,14 @@
 // fused_gate_up_swiglu_gemm_q1/_tq2; crates/oxibonsai-kernels/src/gpu_backend/cuda_prefill_kernels.rs:74-827)
 // walk the batch eight columns at a time on CUDA cores and re-read the weights for every chunk.
 // Here an output tile is 128 weight rows x TOK tokens (TOK = 256 for prompt chunks, 64 for decode batches):
-//   * A operand (weights): sixteen expander warps in four groups; a thread owns one weight row of the tile and
-//     one 32-byte load covers a pair of 64-input k-blocks of it.  Every two weights become a half2 with one
+//   * A operand (weights): sixteen expander warps in two groups of 256 threads; a thread owns one weight row of
+//     the tile and one 64-input k-block of a pair (one 16-byte load).  Every two weights become a half2 with one
 //     shift, one mask and one HMUL2 by the group scale (+-2^-7 * 128*d = +-d exactly, d being an f16), stored
-//     into the 128-byte-swizzled shared-memory stage.  Group g fills every fourth pair, so four pairs are being
-//     expanded at any time and each scheduler has four warps to hide the expansion's latencies behind;
+//     into the 128-byte-swizzled shared-memory stage.  The groups take alternate pairs of k-blocks;
 //   * B operand (activations): f16 tiles fetched by TMA (cp.async.bulk.tensor, no multicast);
-//   * tcgen05.mma kind::f16 accumulates in TMEM (128 lanes x TOK columns, double buffered so the epilogue of
-//     one segment overlaps the main loop of the next);
+//   * tcgen05.mma kind::f16 accumulates in TMEM (double buffered so the epilogue of one segment overlaps the main
+//     loop of the next); 64-token tiles spread the MMA and TMA issue over four warps each, one per pipeline slot,
+//     every MMA issuer with its own accumulator (the comments at the issuer loops give the measurements behind it);
 //   * epilogue warps read TMEM back and store f32 (plain / residual add) or f16 (SwiGLU / plain) outputs.
 //
 // Work distribution ("stream-K"): the (tile, k-block pair) index space is cut into one contiguous, equally long
