@@ -73,8 +73,10 @@ class ClockSampler:
     def _run(self):
         # one long-running nvidia-smi in loop mode (a row every 100 ms); reading the settings changes nothing on the GPU
         try:
-            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.gpu), "-lms", "100"],
-                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            cmd = ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"]
+            if self.gpu >= 0:
+                cmd += ["-i", str(self.gpu)]       # gpu < 0: every GPU of the node (rows carry the index)
+            self._proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             for line in self._proc.stdout:
                 if line.strip():
                     self.rows.append([c.strip() for c in line.split(",")])
@@ -87,7 +89,9 @@ class ClockSampler:
         self._proc = None
         self._t = threading.Thread(target=self._run, daemon=True)
         self._t.start()
-        time.sleep(0.25)          # the first row arrives before the timed region starts
+        t_end = time.time() + 10.0   # the first row arrives before the timed region starts (nvidia-smi can take seconds on 8 GPUs)
+        while not self.rows and time.time() < t_end:
+            time.sleep(0.05)
 
     def stop(self) -> dict:
         self._stop.set()
@@ -130,12 +134,12 @@ def measure(eng, args, cfg, prompt, n_streams: int, barrier, dev, gen, e2e: bool
     r.positions[:1].fill_(prompt_len)
     torch.cuda.synchronize(dev)
     out["ttft"] = time.time() - t0
+    clocks = ClockSampler(clocks_gpu) if clocks_gpu is not None else None
+    if clocks:
+        clocks.start()            # before the warm-up, so that waiting for its first row does not idle the GPU before the timed steps
     for _ in range(args.warmup):
         r.step(1, sample=True)
     barrier()
-    clocks = ClockSampler(clocks_gpu) if clocks_gpu is not None else None
-    if clocks:
-        clocks.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
@@ -255,7 +259,9 @@ def main() -> None:
     eng = (EngineBuilder().model_path(path).preset("greedy").max_seq_len(max_seq).max_batch(max(1, per_replica)).kv_cache(args.kv)
            .device(f"cuda:{local_rank}").build())
     print(f"[bench] rank {rank}: replica ready in {time.time() - t0:.1f}s; packed bytes/step {eng.weights.packed_bytes / 1e9:.3f} GB", file=sys.stderr)
-    m = measure(eng, args, cfg, prompt, per_replica, barrier, dev, g, e2e=True, sched_e2e=True, clocks_gpu=local_rank)
+    # rank 0 samples the clocks of every GPU of the job (one nvidia-smi for the node), the other ranks none
+    m = measure(eng, args, cfg, prompt, per_replica, barrier, dev, g, e2e=True, sched_e2e=True,
+                clocks_gpu=(0 if world == 1 else -1) if rank == 0 else None)
     bytes_step = eng.weights.packed_bytes
     dev_ms, e2e_s, st_ms, st_e2e_s = reduce_max([m["dev_ms"], m["e2e_s"], m["st_ms"], m["st_e2e_s"]])
     st_tokens = torch.tensor([float(m["st_e2e_tokens"])], dtype=torch.float64, device=dev)
