@@ -24,9 +24,11 @@ from typing import Any, Callable, Protocol, Sequence
 from fastapi import FastAPI, Request
 from fastapi.responses import HTMLResponse, JSONResponse, PlainTextResponse, StreamingResponse
 
+from ..runtime.kv_policy import KvCachePolicy
 from ..runtime.metrics import InferenceMetrics, RequestRateTracker
 from ..runtime.presets import SamplingParams
 from ..runtime.resilience import CircuitBreaker, RateLimiter, check_health
+from ..runtime.streaming import CorsConfig, RequestContext, RequestLogger
 from ..tokenizer import StreamingDecoder, chat_prompt
 from .config import ServerConfig
 
@@ -79,6 +81,11 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
     limiter = RateLimiter(global_rate=1e6, global_burst=1e6, client_rate=1e5, client_burst=1e5)
     app = FastAPI(title="oxibonsai-b200")
     app.state.metrics, app.state.backend, app.state.config, app.state.breaker = metrics, backend, cfg, breaker
+    # KV-pressure controller (FP16 -> Q8 -> Q4 with hysteresis): fed with the page utilisation after every request; its
+    # level is exported as a gauge and as the page format recommended for newly admitted sequences
+    kv_policy = app.state.kv_policy = KvCachePolicy()
+    cors = app.state.cors = CorsConfig()
+    http_log = RequestLogger()
     started = time.time()
     sem = asyncio.Semaphore(cfg.max_concurrent)
 
@@ -93,6 +100,15 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         rid = request.headers.get("x-request-id") or new_request_id()
         request.state.request_id = rid
         path = request.url.path
+        ctx = RequestContext(rid, request.method, path)
+        http_log.log_request(ctx)
+        origin = request.headers.get("origin")
+        if request.method == "OPTIONS" and origin:      # CORS preflight: answered here, never reaches a route
+            pre = PlainTextResponse("", status_code=204 if cors.is_origin_allowed(origin) else 403)
+            pre.headers.update(cors.access_control_headers(origin))
+            pre.headers["x-request-id"] = rid
+            http_log.log_response(ctx, pre.status_code)
+            return pre
         if cfg.bearer_token and path not in ("/health", cfg.metrics_path):
             if request.headers.get("authorization", "") != f"Bearer {cfg.bearer_token}":
                 return error(401, "missing or invalid bearer token", "authentication_error", rid)
@@ -101,6 +117,9 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             return error(429, "rate limit exceeded", "rate_limit_error", rid)
         resp = await call_next(request)
         resp.headers["x-request-id"] = rid
+        if origin:
+            resp.headers.update(cors.access_control_headers(origin))
+        http_log.log_response(ctx, resp.status_code)
         return resp
 
     def sampling_from(body: dict) -> tuple[SamplingParams, int]:
@@ -209,7 +228,10 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             if n_tok and dt > 0:
                 metrics.tokens_per_second.observe(n_tok / dt)
             metrics.aggregator.record(tracker)
-            metrics.kv_utilization.set(backend.kv_utilization())
+            util = backend.kv_utilization()
+            metrics.kv_utilization.set(util)
+            kv_policy.observe(util)
+            metrics.kv_level.set(kv_policy.metric_value())
             breaker.record_success()
 
     def encode_chat(messages: list[dict]) -> list[int]:
@@ -363,7 +385,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
     async def admin_status():
         return {"uptime_seconds": time.time() - started, "model": backend.model_name, "active_requests": metrics.active_requests.get(),
                 "requests_total": metrics.requests.get(), "errors_total": metrics.errors.get(), "circuit": breaker.state.value,
-                "kv_utilization": backend.kv_utilization()}
+                "kv_utilization": backend.kv_utilization(), "kv_level": kv_policy.level.name,
+                "kv_page_format_for_new_sequences": kv_policy.page_format()}
 
     @app.get("/admin/config")
     async def admin_config():

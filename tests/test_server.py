@@ -181,3 +181,21 @@ def test_tool_call_parsing():
     assert calls[0]["function"]["name"] == "get_weather" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Kyoto"}
     assert parse_tool_calls("no json here") == []
     assert "get_weather" in tools_system_prompt([{"type": "function", "function": {"name": "get_weather", "description": "d"}}])
+
+
+def test_cors_preflight_kv_policy_and_request_log(client, caplog):
+    import logging
+    with caplog.at_level(logging.INFO, logger="oxibonsai.http"):
+        r = client.options("/v1/chat/completions", headers={"origin": "https://app.example", "access-control-request-method": "POST"})
+        assert r.status_code == 204 and r.headers["access-control-allow-origin"] == "*" and "POST" in r.headers["access-control-allow-methods"]
+        r = client.post("/v1/completions", json={"prompt": "abc"}, headers={"origin": "https://app.example"})
+        assert r.headers["access-control-allow-origin"] == "*"
+    lines = [rec.getMessage() for rec in caplog.records]
+    assert any(l.startswith("--> POST /v1/completions") for l in lines) and any(l.startswith("<-- 200 POST /v1/completions") for l in lines)
+    # the fake backend reports 25 % page utilisation: the controller stays at FP16 and says so
+    st = client.get("/admin/status").json()
+    assert st["kv_level"] == "FP16" and st["kv_page_format_for_new_sequences"] == "f16"
+    assert "oxibonsai_kv_cache_compression_level 0" in client.get("/metrics").text
+    client.app.state.cors.allowed_origins = ("https://only.example",)
+    r = client.options("/v1/models", headers={"origin": "https://evil.example"})
+    assert r.status_code == 403 and "access-control-allow-origin" not in r.headers
