@@ -2,7 +2,7 @@
 """Kernel micro-benchmarks on Qwen3-8B-shaped matrices (the counterpart of the reference's ``benches/*.rs`` and its
 ``gemv_benchmark`` example, crates/oxibonsai-kernels/examples/).
 
-    python benchmarks/kernels.py gemv   [--fast 0|warp|tile]        packed-bit GEMV, batch 1
+    python benchmarks/kernels.py gemv   [--fast 0|warp|tile|hmma|mma]        packed-bit GEMV, batch 1
     python benchmarks/kernels.py gemm   [--tokens 64]         packed-bit tcgen05 GEMM (prefill / batched decode)
     python benchmarks/kernels.py lmhead [--tokens 64]         dense f16 tcgen05 GEMM of the LM head
     python benchmarks/kernels.py attn   [--ctx 4096 --batch 1 --kv f16]   split-KV decode attention
@@ -72,7 +72,7 @@ def weight_copies(K, rows, cols, dev, budget=400e6):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemv", "gemm", "lmhead", "attn"])
-    ap.add_argument("--fast", default="warp", help="0 (exact f32), warp or tile")
+    ap.add_argument("--fast", default="warp", help="0 (exact f32), warp, tile, hmma or mma")
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1)

@@ -26,6 +26,8 @@ int bonsai_attn_decode(const float*, const int*, const int*, int, int, int, int,
                        const float*, const float*, int, float*, float*, int*, float*, int, cudaStream_t);
 int bonsai_bitgemv_h2(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_bitgemv_warp(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
+int bonsai_bitgemv_hmma(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
+int bonsai_bitgemv_fast(const void*, const void*, const float*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
 int bonsai_sample(const float*, int, int, int, const float*, const int*, const float*, unsigned long long*, int*, int*, int,
                   const uint32_t*, int, cudaStream_t);
 int bonsai_bitgemv_tp(const void*, const void*, const void*, const float*, float, float*, const float*, int, int, int, cudaStream_t);
@@ -83,8 +85,11 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   const int hd = r.ic[IC_HEAD_DIM], vocab = r.ic[IC_VOCAB], lm_rows = r.ic[IC_LM_ROWS_LOCAL];
   const int qd = nq * hd, kvd = nkv * hd, qkv_n = qd + 2 * kvd;
   const bool tp = r.ic[IC_TP_SIZE] > 1;
-  // IC_FAST: 0 exact f32, 1 packed-half warp-per-row, 2 packed-half tile kernel
-  auto gemv = r.ic[IC_FAST] == 0 ? bonsai_bitgemv : (r.ic[IC_FAST] == 2 ? bonsai_bitgemv_h2 : bonsai_bitgemv_warp);
+  // IC_FAST: 0 exact f32, 1 packed-half (warp-per-row or tensor-core kernel by shape), 2 packed-half tile kernel,
+  // 3 warp-level tensor cores for every shape, 4 warp-per-row for every shape
+  auto gemv = r.ic[IC_FAST] == 0 ? bonsai_bitgemv
+              : (r.ic[IC_FAST] == 2 ? bonsai_bitgemv_h2
+                 : (r.ic[IC_FAST] == 3 ? bonsai_bitgemv_hmma : (r.ic[IC_FAST] == 4 ? bonsai_bitgemv_warp : bonsai_bitgemv_fast)));
   int* tokens = P<int>(sp[SP_TOKENS]);
   int* positions = P<int>(sp[SP_POSITIONS]);
   const int* bt = P<int>(sp[SP_BLOCK_TABLE]);

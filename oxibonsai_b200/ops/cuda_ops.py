@@ -22,6 +22,7 @@ _SIG = {
     "bonsai_bitgemv": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_bitgemv_h2": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_bitgemv_warp": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
+    "bonsai_bitgemv_hmma": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_f16gemv": [_vp, _vp, _vp, _f, _vp, _i, _i, _vp],
     "bonsai_embed_f16": [_vp, _vp, _vp, _i, _i, _vp],
     "bonsai_qknorm_rope_kvstore": [_vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
@@ -200,13 +201,15 @@ def bitgemv_mma(w: FragWeight, x: torch.Tensor, norm_w: torch.Tensor | None = No
 def bitgemv(w: PlanarWeight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
             residual: torch.Tensor | None = None, out: torch.Tensor | None = None, fast: bool | str = False) -> torch.Tensor:
     """out = W x.  ``fast=False``: exact f32 path; ``fast=True`` / ``"warp"``: packed-half warp-per-row kernel
-    (f16 activations); ``fast="tile"``: the packed-half tile kernel (the one the tensor-parallel epilogue builds on).
+    (f16 activations); ``fast="tile"``: the packed-half tile kernel (the one the tensor-parallel epilogue builds on);
+    ``fast="hmma"``: shift + mask expansion feeding ``mma.sync.m16n8k16`` (f16 activations, f32 accumulation).
     ``epi``: store / residual add / SwiGLU over interleaved gate-up rows."""
     _f32c(x)
     n_out = w.n // 2 if epi == EPI_SWIGLU else w.n
     if out is None:
         out = torch.empty(n_out, dtype=torch.float32, device=x.device)
-    fn = lib().bonsai_bitgemv if not fast else (lib().bonsai_bitgemv_h2 if fast == "tile" else lib().bonsai_bitgemv_warp)
+    fn = (lib().bonsai_bitgemv if not fast else lib().bonsai_bitgemv_h2 if fast == "tile" else lib().bonsai_bitgemv_hmma if fast == "hmma"
+          else lib().bonsai_bitgemv_warp)
     check(fn(w.codes.data_ptr(), w.scales.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual),
                                w.n, w.k, epi, stream()), "bitgemv")
     return out

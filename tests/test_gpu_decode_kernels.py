@@ -51,7 +51,7 @@ def test_bitgemv_matches_fp32_matmul(ty, rows, cols):
 
 
 @pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
-@pytest.mark.parametrize("kernel", ["warp", "tile"])
+@pytest.mark.parametrize("kernel", ["warp", "tile", "hmma"])
 @pytest.mark.parametrize("rows,cols", [(6144, 4096), (4096, 12288), (512, 2560), (200, 128), (24576, 4096), (1001, 9728), (300, 6144),
                                        (66, 16384), (5000, 2048)])
 def test_bitgemv_half_path_is_close_to_fp32(ty, rows, cols, kernel):
