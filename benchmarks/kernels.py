@@ -114,12 +114,16 @@ def main() -> None:
                                  f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})
             else:
                 T = a.tokens
-                x = K.norm_to_f16_paired(torch.randn(T, k, device=dev), None, 1e-6)
+                hm = a.fast == "hmma" and T <= 64            # decode-batch GEMM on mma.sync instead of tcgen05
+                x = (K.norm_to_f16_hmma if hm else K.norm_to_f16_paired)(torch.randn(T, k, device=dev), None, 1e-6)
                 out = torch.empty((T, n), device=dev)
                 status = torch.zeros(1, dtype=torch.int32, device=dev)
 
                 def fn():
                     it[0] += 1
+                    if hm:
+                        K.bitgemm_hmma(ws[it[0] % len(ws)], x, out=out)
+                        return
                     K.bitgemm_prefill(ws[it[0] % len(ws)], x, out=out, status=status, balanced=(False if a.whole_tiles else (True if a.balanced else "auto")))
                 us = time_us(fn, a.iters, a.profile)
                 fl = 2.0 * n * k * T

@@ -41,6 +41,8 @@ int bonsai_tp_barrier(void*, cudaStream_t);
 int bonsai_bitgemm_prefill_ws(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int,
                               int, const void*, void*, size_t, int, cudaStream_t);
 int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, int, cudaStream_t);
+int bonsai_norm_to_f16_hmma(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
+int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, const float*, void*, int, int, int, int, int, cudaStream_t);
 int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                         const float*, void*, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
@@ -286,6 +288,22 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   r.gemm_ws = P<void>(pp[PP_GEMM_WS]);
   r.gemm_ws_bytes = (size_t)pp[PP_GEMM_WS_BYTES];
   const int xn_ld = hidden > qd ? hidden : qd;
+  // Small batches run the packed GEMMs on mma.sync with register-expanded weights (bitgemm_hmma.cu, activations in
+  // hmma-K order); the tcgen05 kernel (paired-K order) takes over where it measured faster.  QKV / O / gate-up / down
+  // of the 8B model in us: 8 tokens 15.7 / 8.3 / 24.6 / 20.9 against 17.8 / 17.6 / 32.8 / 24.7, 32 tokens 23.9 / 12.7 /
+  // 40.2 / 33.3 against 21.8 / 25.0 / 38.4 / 30.7, 64 tokens 39.6 / 20.6 / 66.0 / 51.7 against 26.3 / 26.1 / 43.4 / 39.0:
+  // everything up to 32 sequences, and the O projection (few rows, short K) up to 64.
+  const bool hm_ok = r.ic[IC_FAST] != 5 && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
+  const bool hm_all = hm_ok && batch <= 32, hm_o = hm_ok && batch <= 64;
+  auto to_f16 = [&](bool hm, const float* src, int src_ld, const float* w, int K, void* dst, int dst_ld) {
+    return hm ? bonsai_norm_to_f16_hmma(src, src_ld, w, r.eps, batch, K, dst, dst_ld, st)
+              : bonsai_norm_to_f16_paired(src, src_ld, w, r.eps, batch, K, dst, dst_ld, 0, st);
+  };
+  auto gemm = [&](bool hm, const void* codes, const void* scales, const void* x, int x_ld, float* out_f32, const float* residual,
+                  void* out_f16, int n_rows, int K, int epi, int out_ld) {
+    return hm ? bonsai_bitgemm_hmma(codes, scales, x, x_ld, out_f32, residual, out_f16, n_rows, K, batch, epi, out_ld, st)
+              : pf_gemm(r, codes, scales, x, x_ld, out_f32, residual, out_f16, status, n_rows, K, batch, epi, out_ld, sms, nullptr, st);
+  };
   // about four CTAs per SM over all (sequence, kv head, split) triples, within the workspace's split count
   int attn_splits = (4 * 148) / (nkv * batch);
   if (attn_splits < 1) attn_splits = 1;
@@ -294,9 +312,8 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, batch, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
-    RC(pf_gemm(r, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
-                              hidden, batch, 0, qkv_n, sms, nullptr, st));
+    RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_ATTN_NORM]), hidden, xn, xn_ld));
+    RC(gemm(hm_all, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, qkv_n, hidden, 0, qkv_n));
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
                                   P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
                                   r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
@@ -304,24 +321,19 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
     RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
                           P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
                           attn_splits, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
-    RC(bonsai_norm_to_f16_paired(attn, qd, nullptr, r.eps, batch, qd, attn16, qd, 0, st));
+    RC(to_f16(hm_o, attn, qd, nullptr, qd, attn16, qd));
     if (!tp) {
-      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, status, hidden, qd, batch, 1,
-                                hidden, sms, nullptr, st));
+      RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, hidden, qd, 1, hidden));
     } else {
-      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, status, hidden, qd,
-                                batch, 0, hidden, sms, nullptr, st));
+      RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, hidden, qd, 0, hidden));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
     }
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, batch, hidden, xn, xn_ld, 0, st));
-    RC(pf_gemm(r, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
-                              hidden, batch, 2, inter, sms, nullptr, st));
+    RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_FFN_NORM]), hidden, xn, xn_ld));
+    RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
     if (!tp) {
-      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
-                                batch, 1, hidden, sms, nullptr, st));
+      RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
     } else {
-      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, status, hidden,
-                                inter, batch, 0, hidden, sms, nullptr, st));
+      RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, hidden, inter, 0, hidden));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 1, st));
     }
   }

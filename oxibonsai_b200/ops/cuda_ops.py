@@ -384,6 +384,8 @@ _PF_SIG = {
     "bonsai_bitgemm_prefill": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "bonsai_bitgemm_prefill_ws": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, C.c_size_t, _i, _vp],
     "bonsai_bitgemm_prefill_ws_bytes": [],
+    "bonsai_bitgemm_hmma": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "bonsai_norm_to_f16_hmma": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _vp],
     "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _i, _vp],
     "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -418,6 +420,42 @@ def norm_to_f16_paired(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps:
         out = torch.empty((T, Kd), dtype=torch.float16, device=x.device)
     check(_pf().bonsai_norm_to_f16_paired(x.data_ptr(), x.stride(0), ptr(norm_w), eps, T, Kd, out.data_ptr(), out.stride(0), int(natural), stream()),
           "norm_to_f16_paired")
+    return out
+
+
+def hmma_k_index(k: int, device=None) -> torch.Tensor:
+    """Permutation ``perm`` with ``hmma[..., perm[i]] = natural[..., i]``: the K order (inside every 128-input group) of the
+    activations of the decode-batch GEMM on ``mma.sync``."""
+    i = torch.arange(k, device=device)
+    r = i & 127
+    wq, e = r >> 4, r & 15
+    c, j, plane, p, h = wq >> 1, wq & 1, e >> 3, e & 3, (e >> 2) & 1
+    return (i & ~127) | ((j * 4 + p) * 16 + plane * 8 + 2 * c + h)
+
+
+def norm_to_f16_hmma(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """f32 [T, K] -> f16 [T, K] in hmma-K order, optionally RMS-normalised first."""
+    T, Kd = x.shape
+    if out is None:
+        out = torch.empty((T, Kd), dtype=torch.float16, device=x.device)
+    check(_pf().bonsai_norm_to_f16_hmma(x.data_ptr(), x.stride(0), ptr(norm_w), eps, T, Kd, out.data_ptr(), out.stride(0), stream()),
+          "norm_to_f16_hmma")
+    return out
+
+
+def bitgemm_hmma(w: PlanarWeight, x_hmma: torch.Tensor, epi: int = 0, residual: torch.Tensor | None = None,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[T, N] = epilogue(W x) for T <= 64 tokens on ``mma.sync`` with register-expanded weights.  ``epi``: 0 f32 store,
+    1 f32 residual add, 2 f16 SwiGLU over interleaved gate / up rows (hmma-K order)."""
+    T = x_hmma.shape[0]
+    assert x_hmma.dtype == torch.float16 and x_hmma.shape[1] == w.k and T <= 64
+    n_out = w.n // 2 if epi == 2 else w.n
+    if out is None:
+        out = torch.empty((T, n_out), dtype=torch.float32 if epi <= 1 else torch.float16, device=x_hmma.device)
+    f32p = out.data_ptr() if epi <= 1 else None
+    f16p = out.data_ptr() if epi == 2 else None
+    check(_pf().bonsai_bitgemm_hmma(w.codes.data_ptr(), w.scales.data_ptr(), x_hmma.data_ptr(), x_hmma.stride(0), f32p, ptr(residual), f16p,
+                                    w.n, w.k, T, epi, out.stride(0), stream()), "bitgemm_hmma")
     return out
 
 

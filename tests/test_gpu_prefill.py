@@ -119,3 +119,34 @@ def test_dense_f16_gemm_on_tcgen05(rows, cols, T):
     ref = x.float() @ w.float().T
     assert st.item() == 0
     assert (y - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+@pytest.mark.parametrize("rows,cols,T", [(6144, 4096, 64), (4096, 4096, 33), (24576, 4096, 64), (4096, 12288, 64), (512, 2560, 5), (200, 128, 1),
+                                         (1000, 384, 16), (256, 9728, 17)])
+def test_bitgemm_hmma_matches_fp32(ty, rows, cols, T):
+    """Decode-batch GEMM on mma.sync with register-expanded weights, against a plain fp32 matmul of the same operands."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    raw, wd = _random_quant(ty, rows, cols, 41)
+    pw = K.PlanarWeight(rows, cols, DEV).fill_from_gguf(torch.from_numpy(raw).to(DEV), ty, cols, 0, rows)
+    g = torch.Generator().manual_seed(42)
+    x = torch.randn(T, cols, generator=g)
+    xh = K.norm_to_f16_hmma(x.to(DEV))
+    perm = K.hmma_k_index(cols)
+    assert torch.equal(xh.cpu()[:, perm], x.half())           # the layout is a pure permutation
+    ref = x.half().double() @ wd.double().T
+    scale = ref.abs().max().item()
+    y = K.bitgemm_hmma(pw, xh)
+    assert (y.cpu().double() - ref).abs().max().item() <= 2e-4 * scale
+    res = torch.randn(T, rows, generator=g)
+    y = K.bitgemm_hmma(pw, xh, epi=1, residual=res.to(DEV))
+    assert (y.cpu().double() - (ref + res.double())).abs().max().item() <= 2e-4 * scale + 1e-5
+    nw = torch.rand(cols, generator=g) + 0.5
+    xn = nw * x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6)
+    xnh = K.norm_to_f16_hmma(x.to(DEV), nw.to(DEV), 1e-6)
+    assert torch.allclose(xnh.cpu()[:, perm].float(), xn, rtol=2e-3, atol=2e-3)
+    if rows % 256 == 0:
+        ys = K.bitgemm_hmma(pw, xh, epi=2)
+        want = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+        got = ys.cpu()[:, K.hmma_k_index(rows // 2)].double()
+        assert (got - want).abs().max().item() <= 3e-3 * want.abs().max().item() + 1e-4
