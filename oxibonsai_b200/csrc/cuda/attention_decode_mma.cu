@@ -18,7 +18,6 @@
 
 namespace bonsai {
 
-constexpr int kMmaWarps = 4;
 constexpr int kMmaTile = 16;                          // tokens per warp tile
 constexpr int kMmaRow = 272;                          // bytes per token row in shared memory: 256 + 16 (bank spread)
 constexpr int kMmaTileBytes = kMmaTile * kMmaRow;     // 4352
@@ -63,8 +62,12 @@ struct MmaAttnParams {
   float sm_scale;
 };
 
-template <int G>
-__global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_decode_mma_kernel(MmaAttnParams p) {
+// NW warps per CTA: 8 when the grid is about one CTA per SM (a single sequence: each warp then walks half as many
+// tiles; 479 vs 466 tok/s end to end), 4 with two CTAs per SM when many sequences fill the GPU (57 vs 63-70 us for
+// 64 x 1024 tokens).
+template <int G, int NW>
+__global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAttnParams p) {
+  constexpr int kMmaWarps = NW;
   constexpr int hd = kMmaHd;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   // [warp][buffer][K | V] tiles, then the warp-merge staging area [warp][G][hd + 2] floats
@@ -288,18 +291,19 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) attn_decode_mma_kernel(MmaA
   }
 }
 
-template <int G>
+template <int G, int NW>
 static int launch_mma(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int kMmaWarps = NW;
   const size_t smem = (size_t)kMmaWarps * 4 * kMmaTileBytes + (size_t)kMmaWarps * G * (kMmaHd + 2) * sizeof(float);
   static bool configured[64] = {};   // per template instance and device: the attribute belongs to the function in a context
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<G, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return BONSAI_CUDA_LAUNCH_FAILED;
     configured[dev] = true;
   }
-  const cudaError_t e = launch_pdl(attn_decode_mma_kernel<G>, grid, dim3(kMmaWarps * 32), smem, st, p);
+  const cudaError_t e = launch_pdl(attn_decode_mma_kernel<G, NW>, grid, dim3(kMmaWarps * 32), smem, st, p);
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
@@ -308,15 +312,16 @@ int attn_decode_mma_f16(const float* q, const int* positions, const int* block_t
                         int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc, float* ws_ml, int* counters,
                         float* out, int extra_len, float sm_scale, cudaStream_t stream) {
   const int G = nq / nkv;
-  if (page_size < kMmaTile || (page_size & (page_size - 1)) != 0 || 2 * G * nsplit > kMmaWarps * G * (kMmaHd + 2)) return BONSAI_CUDA_BAD_ARG;
+  if (page_size < kMmaTile || (page_size & (page_size - 1)) != 0 || 2 * G * nsplit > 4 * G * (kMmaHd + 2)) return BONSAI_CUDA_BAD_ARG;
   MmaAttnParams p{q, positions, block_table, (const uint8_t*)kpool, (const uint8_t*)vpool, ws_acc, ws_ml, counters, out,
                   max_pages, nq, nkv, page_size, extra_len, sm_scale};
   const dim3 grid(nkv, nsplit, batch);
+  const bool wide = (long long)nkv * nsplit * batch <= 296;   // about one CTA per SM: eight warps each
   switch (G) {
-    case 1: return launch_mma<1>(p, grid, stream);
-    case 2: return launch_mma<2>(p, grid, stream);
-    case 4: return launch_mma<4>(p, grid, stream);
-    case 8: return launch_mma<8>(p, grid, stream);
+    case 1: return wide ? launch_mma<1, 8>(p, grid, stream) : launch_mma<1, 4>(p, grid, stream);
+    case 2: return wide ? launch_mma<2, 8>(p, grid, stream) : launch_mma<2, 4>(p, grid, stream);
+    case 4: return wide ? launch_mma<4, 8>(p, grid, stream) : launch_mma<4, 4>(p, grid, stream);
+    case 8: return wide ? launch_mma<8, 8>(p, grid, stream) : launch_mma<8, 4>(p, grid, stream);
     default: return BONSAI_CUDA_BAD_ARG;
   }
 }
