@@ -60,7 +60,23 @@ struct MmaAttnParams {
   float* out;                // [batch][nq][128]
   int max_pages, nq, nkv, page_size, extra_len;
   float sm_scale;
+  // Fused mode (qkv != null, extra_len == 0): the kernel takes the raw projections of the new token
+  // ([batch][qkv_stride] f32: q heads | k heads | v heads), applies QK-RMSNorm and RoPE itself, and the CTA whose split
+  // holds the new position appends the K and V rows to the cache before it reads them.  One launch per layer less.
+  const float* qkv;
+  const float* q_norm;
+  const float* k_norm;
+  const float* rope_cos;     // [position][64]
+  const float* rope_sin;
+  int qkv_stride;
+  float eps;
 };
+
+__device__ __forceinline__ float mma_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
 // NW warps per CTA: 8 when the grid is about one CTA per SM (a single sequence: each warp then walks half as many
 // tiles; 479 vs 466 tok/s end to end), 4 with two CTAs per SM when many sequences fill the GPU (57 vs 63-70 us for
@@ -89,16 +105,52 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
 
   // Q as A-operand fragments: rows 0..G-1 hold the group's query heads (scaled), rows G..15 are zero
   uint32_t qa[8][2];   // per 16-wide k step: a0 (row, k lo pair) and a2 (row, k hi pair); a1 = a3 = 0 (rows 8..15)
+  const float* qp = p.q + ((size_t)b * p.nq + kvh * G + (row < G ? row : 0)) * hd;
+  float q_mul = p.sm_scale;
+  if (p.qkv != nullptr) {
+    // a warp per item: the G query heads, plus the new token's K and V rows in the CTA that owns position len - 1
+    float* qs = sh;                                          // [G][128] normalised, rotated, scaled queries
+    const int pos = len - 1;
+    const bool owner = pos >= t0 && pos < t1;
+    const float* raw = p.qkv + (size_t)b * p.qkv_stride;
+    for (int it = warp; it < G + (owner ? 2 : 0); it += kMmaWarps) {
+      const bool is_q = it < G, is_v = it == G + 1;
+      const float* src = raw + (size_t)(is_q ? kvh * G + it : (is_v ? p.nq + p.nkv + kvh : p.nq + kvh)) * hd;
+      float y0 = src[lane], y1 = src[lane + 32], y2 = src[lane + 64], y3 = src[lane + 96];
+      if (!is_v) {
+        const float inv = 1.0f / sqrtf(mma_warp_sum(y0 * y0 + y1 * y1 + y2 * y2 + y3 * y3) / (float)hd + p.eps);
+        const float* w = is_q ? p.q_norm : p.k_norm;
+        const float n0 = w[lane] * y0 * inv, n1 = w[lane + 32] * y1 * inv, n2 = w[lane + 64] * y2 * inv, n3 = w[lane + 96] * y3 * inv;
+        const float c0 = p.rope_cos[(size_t)pos * 64 + lane], s0 = p.rope_sin[(size_t)pos * 64 + lane];
+        const float c1 = p.rope_cos[(size_t)pos * 64 + lane + 32], s1 = p.rope_sin[(size_t)pos * 64 + lane + 32];
+        y0 = n0 * c0 - n2 * s0; y2 = n0 * s0 + n2 * c0;      // dims (lane, lane + 64)
+        y1 = n1 * c1 - n3 * s1; y3 = n1 * s1 + n3 * c1;      // dims (lane + 32, lane + 96)
+      }
+      if (is_q) {
+        float* dst = qs + it * hd;
+        dst[lane] = y0 * p.sm_scale; dst[lane + 32] = y1 * p.sm_scale; dst[lane + 64] = y2 * p.sm_scale; dst[lane + 96] = y3 * p.sm_scale;
+      } else {
+        const int page = bt[pos >> pshift];
+        const size_t crow = ((size_t)page * p.nkv + kvh) * p.page_size + (pos & pmask);
+        __half* dst = reinterpret_cast<__half*>(const_cast<uint8_t*>(is_v ? p.v : p.k)) + crow * hd;
+        dst[lane] = __float2half_rn(y0); dst[lane + 32] = __float2half_rn(y1); dst[lane + 64] = __float2half_rn(y2); dst[lane + 96] = __float2half_rn(y3);
+      }
+    }
+    if (owner) __threadfence();                              // the appended rows are read back through cp.async below
+    __syncthreads();
+    qp = qs + (row < G ? row : 0) * hd;
+    q_mul = 1.0f;
+  }
   {
-    const float* qp = p.q + ((size_t)b * p.nq + kvh * G + (row < G ? row : 0)) * hd;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       const float2 lo = *reinterpret_cast<const float2*>(qp + ks * 16 + 2 * cq);
       const float2 hi = *reinterpret_cast<const float2*>(qp + ks * 16 + 8 + 2 * cq);
-      qa[ks][0] = row < G ? pack_h2(lo.x * p.sm_scale, lo.y * p.sm_scale) : 0u;
-      qa[ks][1] = row < G ? pack_h2(hi.x * p.sm_scale, hi.y * p.sm_scale) : 0u;
+      qa[ks][0] = row < G ? pack_h2(lo.x * q_mul, lo.y * q_mul) : 0u;
+      qa[ks][1] = row < G ? pack_h2(hi.x * q_mul, hi.y * q_mul) : 0u;
     }
   }
+  if (p.qkv != nullptr) __syncthreads();                     // the staging area is reused for the warp merge later
   float o[16][4];   // O accumulators: 16 column tiles of 8 dims; [.][0..1] = this lane's row, [.][2..3] = row + 8 (unused)
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
@@ -307,14 +359,23 @@ static int launch_mma(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
-// Returns BONSAI_CUDA_BAD_ARG for shapes it does not cover; the caller then uses the CUDA-core kernel.
-int attn_decode_mma_f16(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
-                        int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc, float* ws_ml, int* counters,
-                        float* out, int extra_len, float sm_scale, cudaStream_t stream) {
+struct MmaFused {
+  const float* qkv = nullptr;
+  const float* q_norm = nullptr;
+  const float* k_norm = nullptr;
+  const float* rope_cos = nullptr;
+  const float* rope_sin = nullptr;
+  int qkv_stride = 0;
+  float eps = 0.0f;
+};
+
+static int attn_decode_mma_launch(const float* q, const MmaFused& f, const int* positions, const int* block_table, int max_pages, int batch,
+                                  int nq, int nkv, int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc,
+                                  float* ws_ml, int* counters, float* out, int extra_len, float sm_scale, cudaStream_t stream) {
   const int G = nq / nkv;
   if (page_size < kMmaTile || (page_size & (page_size - 1)) != 0 || 2 * G * nsplit > 4 * G * (kMmaHd + 2)) return BONSAI_CUDA_BAD_ARG;
   MmaAttnParams p{q, positions, block_table, (const uint8_t*)kpool, (const uint8_t*)vpool, ws_acc, ws_ml, counters, out,
-                  max_pages, nq, nkv, page_size, extra_len, sm_scale};
+                  max_pages, nq, nkv, page_size, extra_len, sm_scale, f.qkv, f.q_norm, f.k_norm, f.rope_cos, f.rope_sin, f.qkv_stride, f.eps};
   const dim3 grid(nkv, nsplit, batch);
   const bool wide = (long long)nkv * nsplit * batch <= 296;   // about one CTA per SM: eight warps each
   switch (G) {
@@ -326,4 +387,32 @@ int attn_decode_mma_f16(const float* q, const int* positions, const int* block_t
   }
 }
 
+// Returns BONSAI_CUDA_BAD_ARG for shapes it does not cover; the caller then uses the CUDA-core kernel.
+int attn_decode_mma_f16(const float* q, const int* positions, const int* block_table, int max_pages, int batch, int nq, int nkv,
+                        int page_size, const void* kpool, const void* vpool, int nsplit, float* ws_acc, float* ws_ml, int* counters,
+                        float* out, int extra_len, float sm_scale, cudaStream_t stream) {
+  return attn_decode_mma_launch(q, MmaFused{}, positions, block_table, max_pages, batch, nq, nkv, page_size, kpool, vpool, nsplit, ws_acc,
+                                ws_ml, counters, out, extra_len, sm_scale, stream);
+}
+
 }  // namespace bonsai
+
+extern "C" {
+
+// QK-RMSNorm + RoPE + KV append + split-KV attention of one new token per sequence in a single launch, for f16 pages
+// and head_dim 128.  qkv: f32 [batch][qkv_stride] raw projections (q heads | k heads | v heads); positions[b] is the
+// position of the new token, whose K and V rows are appended to the pools.  Returns BONSAI_CUDA_BAD_ARG for shapes it
+// does not cover (the caller then runs bonsai_qknorm_rope_kvstore + bonsai_attn_decode).
+int bonsai_attn_decode_qkv_f16(const float* qkv, int qkv_stride, const float* q_norm, const float* k_norm, float eps,
+                               const float* rope_cos, const float* rope_sin, const int* positions, const int* block_table,
+                               int max_pages, int batch, int nq, int nkv, int hd, int page_size, void* kpool, void* vpool, int nsplit,
+                               float* ws_acc, float* ws_ml, int* counters, float* out, cudaStream_t stream) {
+  using namespace bonsai;
+  if (hd != kMmaHd || nq % nkv != 0 || nsplit < 1 || batch <= 0 || counters == nullptr || qkv == nullptr) return BONSAI_CUDA_BAD_ARG;
+  MmaFused f;
+  f.qkv = qkv; f.q_norm = q_norm; f.k_norm = k_norm; f.rope_cos = rope_cos; f.rope_sin = rope_sin; f.qkv_stride = qkv_stride; f.eps = eps;
+  return attn_decode_mma_launch(nullptr, f, positions, block_table, max_pages, batch, nq, nkv, page_size, kpool, vpool, nsplit, ws_acc,
+                                ws_ml, counters, out, 0, 1.0f / sqrtf((float)hd), stream);
+}
+
+}  // extern "C"

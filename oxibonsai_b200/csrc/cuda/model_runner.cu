@@ -41,6 +41,8 @@ int bonsai_tp_barrier(void*, cudaStream_t);
 int bonsai_bitgemm_prefill_ws(const void*, const void*, const void*, int, float*, const float*, void*, int*, int, int, int, int, int,
                               int, const void*, void*, size_t, int, cudaStream_t);
 int bonsai_norm_to_f16_paired(const float*, int, const float*, float, int, int, void*, int, int, cudaStream_t);
+int bonsai_attn_decode_qkv_f16(const float*, int, const float*, const float*, float, const float*, const float*, const int*, const int*,
+                               int, int, int, int, int, int, void*, void*, int, float*, float*, int*, float*, cudaStream_t);
 int bonsai_norm_to_f16_hmma(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
 int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, const float*, void*, int, int, int, int, int, cudaStream_t);
 int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
@@ -81,6 +83,28 @@ static inline T* P(uint64_t v) { return reinterpret_cast<T*>(v); }
 
 #define RC(expr) do { int _rc = (expr); if (_rc != 0) return _rc; } while (0)
 
+// QK-norm + RoPE + KV append + decode attention of one new token per sequence: one fused launch for f16 pages with
+// head_dim 128 on the packed-half path, otherwise (other page formats, exact mode, shapes the fused kernel declines)
+// the two separate kernels.
+static int qkv_attention(Runner& r, const uint64_t* lp, const uint64_t* sp, const float* qkv, int qkv_n, float* q, float* attn,
+                         const int* positions, const int* bt, int batch, int nsplit, cudaStream_t st) {
+  const int nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL], hd = r.ic[IC_HEAD_DIM];
+  if (r.ic[IC_KVT] == 1 && hd == 128 && r.ic[IC_FAST] != 0) {
+    const int rc = bonsai_attn_decode_qkv_f16(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
+                                              P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd,
+                                              r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), nsplit,
+                                              P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, st);
+    if (rc != BONSAI_CUDA_BAD_ARG) return rc;   // bad argument = not a shape of the fused kernel
+  }
+  RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
+                                P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
+                                r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
+                                P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
+  return bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
+                            P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
+                            nsplit, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st);
+}
+
 // flags: bit 0 = run the sampler and advance positions, bit 1 = skip the LM head
 static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int mask_words, cudaStream_t st) {
   const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
@@ -110,13 +134,7 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
     for (int b = 0; b < batch; ++b)
       RC(gemv(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]),
                         r.eps, qkv + (size_t)b * qkv_n, nullptr, qkv_n, hidden, 0, st));
-    RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
-                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
-                                  r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
-                                  P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
-    RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
-                          P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
-                          r.ic[IC_NSPLIT], P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
+    RC(qkv_attention(r, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, r.ic[IC_NSPLIT], st));
     if (!tp) {
       for (int b = 0; b < batch; ++b)
         RC(gemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
@@ -314,13 +332,7 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_ATTN_NORM]), hidden, xn, xn_ld));
     RC(gemm(hm_all, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, qkv_n, hidden, 0, qkv_n));
-    RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
-                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
-                                  r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
-                                  P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
-    RC(bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
-                          P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
-                          attn_splits, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st));
+    RC(qkv_attention(r, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, attn_splits, st));
     RC(to_f16(hm_o, attn, qd, nullptr, qd, attn16, qd));
     if (!tp) {
       RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, hidden, qd, 1, hidden));

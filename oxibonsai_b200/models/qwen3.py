@@ -221,7 +221,8 @@ class Qwen3Runner:
         # KV splits of one sequence's decode attention: about 128 CTAs over (kv head, split).  More splits shorten every
         # CTA's stream but lengthen the merge in the last CTA: 16 splits measured 10.9 us at 4096 tokens (8 kv heads)
         # against 13.5 us for 37 and 12.4 us for 8, and 0.53 of the HBM bandwidth at 16384 tokens.
-        self.nsplit = nsplit or max(4, min(32, 128 // max(1, nkv)))
+        # With one or two local kv heads (tensor parallel) that rule would leave most SMs idle: up to 64 splits.
+        self.nsplit = nsplit or max(4, min(64, 128 // max(1, nkv)))
         self.fast = fast
         B = max_batch
         f32 = dict(dtype=torch.float32, device=dev)
@@ -351,7 +352,11 @@ class Qwen3Runner:
 
     def kernel_launches(self, batch: int, sample: bool = True) -> int:
         """Number of kernel launches in one decode step (each is one of this library's kernels)."""
-        per_layer = 4 * batch + 2
+        # four GEMVs per sequence, then QK-norm/RoPE/append + attention: one fused launch for f16 pages with head_dim 128
+        # on the packed-half path (page sizes are powers of two >= 16 there), two launches otherwise
+        fused = self.fast and self.kv.kvt == K.KV_F16 and self.cfg.head_dim == 128 and self.kv.page_size >= 16 \
+            and (self.kv.page_size & (self.kv.page_size - 1)) == 0
+        per_layer = 4 * batch + (1 if fused else 2)
         return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0) + (2 if self.w.tp_size > 1 else 0)
 
     def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:

@@ -28,6 +28,7 @@ _SIG = {
     "bonsai_qknorm_rope_kvstore": [_vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "bonsai_attn_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_attn_decode_force_cuda_cores": [_i],
+    "bonsai_attn_decode_qkv_f16": [_vp, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp],
     "bonsai_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp],
     "bonsai_runner_create": [_vp, _f, _vp, _vp],
     "bonsai_runner_destroy": [_vp],
@@ -246,6 +247,23 @@ def attn_decode(q, positions, block_table, nq, nkv, hd, kvt, page_size, kpool, v
                                    kvt, page_size, kpool.data_ptr(), vpool.data_ptr(), ptr(kscale), ptr(vscale), nsplit,
                                    ws_acc.data_ptr(), ws_ml.data_ptr(), counters.data_ptr(), out.data_ptr(), extra_len, stream()),
           "attn_decode")
+    return out
+
+
+def attn_decode_qkv(qkv, q_norm, k_norm, eps, rope_cos, rope_sin, positions, block_table, nq, nkv, hd, page_size, kpool, vpool,
+                    nsplit=8, out=None) -> torch.Tensor:
+    """QK-norm + RoPE + KV append + attention of one new token per sequence in one launch (f16 pages, head_dim 128).
+    Raises :class:`CudaKernelError` with the bad-argument code for shapes the fused kernel does not cover."""
+    batch = qkv.shape[0]
+    ws_acc = torch.empty((batch, nq, nsplit, hd), dtype=torch.float32, device=qkv.device)
+    ws_ml = torch.empty((batch, nq, nsplit, 2), dtype=torch.float32, device=qkv.device)
+    counters = torch.zeros(batch * nkv, dtype=torch.int32, device=qkv.device)
+    if out is None:
+        out = torch.empty((batch, nq, hd), dtype=torch.float32, device=qkv.device)
+    check(lib().bonsai_attn_decode_qkv_f16(qkv.data_ptr(), qkv.stride(0), q_norm.data_ptr(), k_norm.data_ptr(), eps, rope_cos.data_ptr(),
+                                           rope_sin.data_ptr(), positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], batch, nq,
+                                           nkv, hd, page_size, kpool.data_ptr(), vpool.data_ptr(), nsplit, ws_acc.data_ptr(), ws_ml.data_ptr(),
+                                           counters.data_ptr(), out.data_ptr(), stream()), "attn_decode_qkv")
     return out
 
 

@@ -261,3 +261,33 @@ def test_tensor_core_decode_attention_f16(nq, nkv, page):
                 finally:
                     K.lib().bonsai_attn_decode_force_cuda_cores(0)
                 assert (out - out2).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 2), (32, 8), (8, 8)])
+def test_fused_qknorm_rope_append_attention_matches_separate_kernels(nq, nkv):
+    """One launch (QK-norm + RoPE + KV append + attention) against the two separate kernels on a copy of the cache."""
+    from oxibonsai_b200.core.oracle import rope_table
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    hd, page, B, base, eps = 128, 16, 3, 1e6, 1e-6
+    g = torch.Generator().manual_seed(77)
+    lens = [1, 40, 129]                                     # context length including the new token
+    pps = 10
+    bt = torch.randperm(B * pps, generator=g).view(B, pps).to(torch.int32).to(dev)
+    kpool = torch.randn((B * pps, nkv, page, hd), generator=g).half().to(dev)
+    vpool = torch.randn((B * pps, nkv, page, hd), generator=g).half().to(dev)
+    k2, v2 = kpool.clone(), vpool.clone()
+    qn, kn = (torch.rand(hd, generator=g) + 0.5).to(dev), (torch.rand(hd, generator=g) + 0.5).to(dev)
+    cos, sin = rope_table(hd, 256, base)
+    cos, sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
+    qkv = torch.randn((B, (nq + 2 * nkv) * hd), generator=g).to(dev)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
+    q = torch.zeros((B, nq, hd), device=dev)
+    K.qknorm_rope_kvstore(qkv, qn, kn, eps, cos, sin, pos, bt, q, nq, nkv, hd, K.KV_F16, page, kpool, vpool)
+    for nsplit in (1, 4, 16):
+        want = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
+        ka, va = k2.clone(), v2.clone()
+        got = K.attn_decode_qkv(qkv, qn, kn, eps, cos, sin, pos, bt, nq, nkv, hd, page, ka, va, nsplit=nsplit)
+        # the same rows were appended (the sum of squares is reduced in another order: at most an f16 ulp apart)
+        assert torch.equal(va, vpool) and (ka.float() - kpool.float()).abs().max().item() <= 4e-3 * kpool.float().abs().max().item()
+        assert (got - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
