@@ -285,7 +285,9 @@ int bonsai_bitgemm_hmma(const void* codes, const void* scales, const void* x_f16
 
 int bonsai_norm_to_f16_hmma(const float* x, int x_ld, const float* w, float eps, int T, int K, void* out, int out_ld, cudaStream_t stream) {
   if (T < 1 || K % 128 != 0) return BONSAI_CUDA_BAD_ARG;
-  bonsai::norm_to_f16_hmma_kernel<<<T, 256, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld);
+  // one block per token: a block as wide as the row allows keeps the two passes short (few tokens = few blocks)
+  const int threads = K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256);
+  bonsai::norm_to_f16_hmma_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld);
   return bonsai::launch_status();
 }
 

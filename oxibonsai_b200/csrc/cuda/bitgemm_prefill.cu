@@ -642,7 +642,9 @@ int bonsai_bitgemm_prefill(const void* codes, const void* scales, const void* x_
 int bonsai_norm_to_f16_paired(const float* x, int x_ld, const float* w, float eps, int T, int K, void* out, int out_ld, int natural,
                               cudaStream_t stream) {
   if (T < 1 || K % 16 != 0) return BONSAI_CUDA_BAD_ARG;
-  bonsai::norm_to_f16_paired_kernel<<<T, 256, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural);
+  // one block per token; with few tokens (decode batches) a wide block keeps the two passes short
+  const int threads = T <= 128 ? (K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256)) : 256;
+  bonsai::norm_to_f16_paired_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural);
   return bonsai::launch_status();
 }
 
