@@ -214,9 +214,14 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p)
 
 // One block per token: y = rmsnorm(x) * w (or a plain copy when w is null) as f16 in hmma-K order.
 __global__ void norm_to_f16_hmma_kernel(const float* __restrict__ x, int x_ld, const float* __restrict__ w, float eps, int K,
-                                        __half* __restrict__ out, int out_ld) {
+                                        __half* __restrict__ out, int out_ld, int vec) {
   __shared__ float s32[32];
   const float* xr = x + (size_t)blockIdx.x * x_ld;
+  __half* orow = out + (size_t)blockIdx.x * out_ld;
+  if (vec) {
+    norm_row_to_f16(xr, w, eps, K, orow, s32, [](int k) { return hmma_k_pos(k); });
+    return;
+  }
   float inv = 1.0f;
   if (w != nullptr) {
     float ss = 0.0f;
@@ -224,8 +229,7 @@ __global__ void norm_to_f16_hmma_kernel(const float* __restrict__ x, int x_ld, c
     ss = block_sum(ss, s32);
     inv = 1.0f / sqrtf(ss / (float)K + eps);
   }
-  for (int k = threadIdx.x; k < K; k += blockDim.x)
-    out[(size_t)blockIdx.x * out_ld + hmma_k_pos(k)] = __float2half_rn(w ? w[k] * xr[k] * inv : xr[k]);
+  for (int k = threadIdx.x; k < K; k += blockDim.x) orow[hmma_k_pos(k)] = __float2half_rn(w ? w[k] * xr[k] * inv : xr[k]);
 }
 
 template <int NT>
@@ -287,7 +291,8 @@ int bonsai_norm_to_f16_hmma(const float* x, int x_ld, const float* w, float eps,
   if (T < 1 || K % 128 != 0) return BONSAI_CUDA_BAD_ARG;
   // one block per token: a block as wide as the row allows keeps the two passes short (few tokens = few blocks)
   const int threads = K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256);
-  bonsai::norm_to_f16_hmma_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld);
+  const int vec = (x_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);   // 16-byte loads
+  bonsai::norm_to_f16_hmma_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, vec);
   return bonsai::launch_status();
 }
 

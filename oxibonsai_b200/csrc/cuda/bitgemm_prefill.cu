@@ -530,10 +530,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
 // One block per token: y = rmsnorm(x) * w (or a plain copy when w is null), written as f16 in the
 // paired-K order consumed by bitgemm_prefill.
 __global__ void norm_to_f16_paired_kernel(const float* __restrict__ x, int x_ld, const float* __restrict__ w, float eps, int K,
-                                          __half* __restrict__ out, int out_ld, int natural) {
+                                          __half* __restrict__ out, int out_ld, int natural, int vec) {
   __shared__ float s32[32];
   const int tok = blockIdx.x;
   const float* xr = x + (size_t)tok * x_ld;
+  __half* orow = out + (size_t)tok * out_ld;
+  if (vec) {
+    if (natural) norm_row_to_f16(xr, w, eps, K, orow, s32, [](int k) { return k; });
+    else norm_row_to_f16(xr, w, eps, K, orow, s32, [](int k) { return paired_k(k); });
+    return;
+  }
   float inv = 1.0f;
   if (w != nullptr) {
     float ss = 0.0f;
@@ -543,7 +549,7 @@ __global__ void norm_to_f16_paired_kernel(const float* __restrict__ x, int x_ld,
   }
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
     float v = w ? w[k] * xr[k] * inv : xr[k];
-    out[(size_t)tok * out_ld + (natural ? k : paired_k(k))] = __float2half_rn(v);
+    orow[natural ? k : paired_k(k)] = __float2half_rn(v);
   }
 }
 
@@ -644,7 +650,8 @@ int bonsai_norm_to_f16_paired(const float* x, int x_ld, const float* w, float ep
   if (T < 1 || K % 16 != 0) return BONSAI_CUDA_BAD_ARG;
   // one block per token; with few tokens (decode batches) a wide block keeps the two passes short
   const int threads = T <= 128 ? (K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256)) : 256;
-  bonsai::norm_to_f16_paired_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural);
+  const int vec = (x_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);   // 16-byte loads
+  bonsai::norm_to_f16_paired_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural, vec);
   return bonsai::launch_status();
 }
 

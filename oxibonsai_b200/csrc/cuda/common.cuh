@@ -46,6 +46,50 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
   return t;
 }
 
+// One row: y = rmsnorm(x) * w (a plain copy when w is null), written as f16 at position pos(k) of the output row.
+// The row is read once with 16-byte loads and kept in registers between the sum of squares and the scaling (up to
+// 16 * blockDim.x elements; longer rows are read twice).  Needs 16-byte aligned rows and K % 4 == 0.
+template <class PosFn>
+__device__ __forceinline__ void norm_row_to_f16(const float* __restrict__ xr, const float* __restrict__ w, float eps, int K,
+                                                __half* __restrict__ orow, float* s32, PosFn pos) {
+  constexpr int kKeep = 4;
+  const int nch = K >> 2;
+  const float4* x4 = reinterpret_cast<const float4*>(xr);
+  float4 v[kKeep];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kKeep; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < nch ? x4[c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  for (int c = threadIdx.x + kKeep * blockDim.x; c < nch; c += blockDim.x) {
+    const float4 t = x4[c];
+    ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+  }
+  float inv = 1.0f;
+  if (w != nullptr) {
+    ss = block_sum(ss, s32);
+    inv = 1.0f / sqrtf(ss / (float)K + eps);
+  }
+  auto emit = [&](int c, float4 t) {
+    if (w != nullptr) {
+      const float4 ww = reinterpret_cast<const float4*>(w)[c];
+      t.x *= ww.x * inv; t.y *= ww.y * inv; t.z *= ww.z * inv; t.w *= ww.w * inv;
+    }
+    orow[pos(4 * c)] = __float2half_rn(t.x);
+    orow[pos(4 * c + 1)] = __float2half_rn(t.y);
+    orow[pos(4 * c + 2)] = __float2half_rn(t.z);
+    orow[pos(4 * c + 3)] = __float2half_rn(t.w);
+  };
+#pragma unroll
+  for (int i = 0; i < kKeep; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nch) emit(c, v[i]);
+  }
+  for (int c = threadIdx.x + kKeep * blockDim.x; c < nch; c += blockDim.x) emit(c, x4[c]);
+}
+
 // Dot of one packed word (16 ternary weights, scaled by 2^-63) with 16 floats.
 __device__ __forceinline__ float dot_word16(uint32_t w, const float* x) {
   float acc = 0.0f;
