@@ -336,32 +336,39 @@ __global__ void __launch_bounds__(256) f16gemv_kernel(const uint4* __restrict__ 
   }
   const int ntiles = (N + R - 1) / R;
   const int lane = t & 31, warp = t >> 5;
-  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    uint4 q[R][CH];
+  uint4 q[R][CH];
+  auto load_tile = [&](int tile) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       int row = tile * R + i;
 #pragma unroll
       for (int h = 0; h < CH; ++h) {
         int c = t + h * 256;
-        q[i][h] = (row < N && c < cpr) ? __ldg(w + (size_t)row * cpr + c) : make_uint4(0, 0, 0, 0);
+        q[i][h] = (tile < ntiles && row < N && c < cpr) ? __ldg(w + (size_t)row * cpr + c) : make_uint4(0, 0, 0, 0);
       }
     }
+  };
+  load_tile(blockIdx.x);
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    float acc[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      float acc = 0.0f;
+      float a = 0.0f;
 #pragma unroll
       for (int h = 0; h < CH; ++h) {
         const __half2* hp = reinterpret_cast<const __half2*>(&q[i][h]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 f = __half22float2(hp[j]);
-          acc = fmaf(f.x, xr[h][2 * j], acc);
-          acc = fmaf(f.y, xr[h][2 * j + 1], acc);
+          a = fmaf(f.x, xr[h][2 * j], a);
+          a = fmaf(f.y, xr[h][2 * j + 1], a);
         }
       }
-      red[i][t] = acc;
+      acc[i] = a;
     }
+    load_tile(tile + gridDim.x);   // the next tile's rows stream in while this one is reduced across the block
+#pragma unroll
+    for (int i = 0; i < R; ++i) red[i][t] = acc[i];
     __syncthreads();
     for (int rr = warp; rr < R; rr += 8) {
       float a = 0.0f;
