@@ -92,26 +92,7 @@ __global__ void __launch_bounds__(256, 2) bitgemv_warp_kernel(const uint4* __res
   // ---- activations: f32 -> (normalised) half2 pairs in shared memory ----
   {
     const int nwords = K >> 4;
-    float ss = 0.0f;
-    if (norm_w != nullptr) {
-      for (int i = t; i < (K >> 2); i += blockDim.x) {
-        const float4 v = reinterpret_cast<const float4*>(x)[i];
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-      }
-      ss = block_sum(ss, s32);
-    }
-    const float inv = norm_w != nullptr ? 1.0f / sqrtf(ss / (float)K + eps) : 1.0f;
-    for (int wd = t; wd < nwords; wd += blockDim.x) {
-      float xr[16];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float4 v = reinterpret_cast<const float4*>(x + (size_t)wd * 16)[j];
-        if (norm_w != nullptr) {
-          const float4 w = reinterpret_cast<const float4*>(norm_w + (size_t)wd * 16)[j];
-          v.x *= w.x * inv; v.y *= w.y * inv; v.z *= w.z * inv; v.w *= w.w * inv;
-        }
-        xr[4 * j] = v.x; xr[4 * j + 1] = v.y; xr[4 * j + 2] = v.z; xr[4 * j + 3] = v.w;
-      }
+    auto park = [&](int wd, const float* xr) {            // 16 activations of word wd -> paired half2, [step][quad][lane]
       __half2 h[8];
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
@@ -122,6 +103,54 @@ __global__ void __launch_bounds__(256, 2) bitgemv_warp_kernel(const uint4* __res
       uint4* dst = xs + ((size_t)step * 8 + w4 * 2) * 32 + owner;
       dst[0] = *reinterpret_cast<uint4*>(&h[0]);
       dst[32] = *reinterpret_cast<uint4*>(&h[4]);
+    };
+    if (norm_w != nullptr && nwords <= (int)blockDim.x) {
+      // one word per thread: x and the norm weights are requested together and x stays in registers across the
+      // block-wide sum, so the prologue is one memory round trip instead of three
+      float4 xv[4], wv[4];
+      const bool mine = t < nwords;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xv[j] = mine ? reinterpret_cast<const float4*>(x + (size_t)t * 16)[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        wv[j] = mine ? reinterpret_cast<const float4*>(norm_w + (size_t)t * 16)[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+      ss = block_sum(ss, s32);
+      const float inv = 1.0f / sqrtf(ss / (float)K + eps);
+      if (mine) {
+        float xr[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          xr[4 * j] = xv[j].x * wv[j].x * inv; xr[4 * j + 1] = xv[j].y * wv[j].y * inv;
+          xr[4 * j + 2] = xv[j].z * wv[j].z * inv; xr[4 * j + 3] = xv[j].w * wv[j].w * inv;
+        }
+        park(t, xr);
+      }
+    } else {
+      float ss = 0.0f;
+      if (norm_w != nullptr) {
+        for (int i = t; i < (K >> 2); i += blockDim.x) {
+          const float4 v = reinterpret_cast<const float4*>(x)[i];
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, s32);
+      }
+      const float inv = norm_w != nullptr ? 1.0f / sqrtf(ss / (float)K + eps) : 1.0f;
+      for (int wd = t; wd < nwords; wd += blockDim.x) {
+        float xr[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float4 v = reinterpret_cast<const float4*>(x + (size_t)wd * 16)[j];
+          if (norm_w != nullptr) {
+            const float4 w = reinterpret_cast<const float4*>(norm_w + (size_t)wd * 16)[j];
+            v.x *= w.x * inv; v.y *= w.y * inv; v.z *= w.z * inv; v.w *= w.w * inv;
+          }
+          xr[4 * j] = v.x; xr[4 * j + 1] = v.y; xr[4 * j + 2] = v.z; xr[4 * j + 3] = v.w;
+        }
+        park(wd, xr);
+      }
     }
   }
   __syncthreads();
