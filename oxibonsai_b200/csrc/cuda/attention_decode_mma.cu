@@ -103,6 +103,27 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   const int* bt = p.block_table + (size_t)b * p.max_pages;
   const int pshift = 31 - __clz(p.page_size), pmask = p.page_size - 1;
 
+  uint8_t* wt = tiles + (size_t)warp * 4 * kMmaTileBytes;
+  auto issue_tile = [&](int j, int buf) {   // tile j of the CTA -> K, V buffers `buf` of this warp
+    const int tb = t0 + j * kMmaTile;
+    const int page = bt[tb >> pshift];
+    const size_t rowbase = ((size_t)page * p.nkv + kvh) * p.page_size + (tb & pmask);
+    const uint32_t kd = mma_smem_u32(wt + (2 * buf) * kMmaTileBytes), vd = kd + kMmaTileBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = i * 32 + lane, r = c >> 4, c16 = c & 15;
+      // rows past the end of the sequence are zero-filled: their scores are masked, but 0 x (stale NaN in V) is NaN
+      const int nb = tb + r < t1 ? 16 : 0;
+      cp_async16(kd + r * kMmaRow + c16 * 16, p.k + (rowbase + r) * 256 + c16 * 16, nb);
+      cp_async16(vd + r * kMmaRow + c16 * 16, p.v + (rowbase + r) * 256 + c16 * 16, nb);
+    }
+  };
+  // The first tile of every warp is requested before the queries are prepared, so the two latencies overlap - unless
+  // it holds the position whose K and V rows are appended below.
+  const int first_tb = t0 + warp * kMmaTile;
+  const bool early = warp < ntiles && !(p.qkv != nullptr && len - 1 >= first_tb && len - 1 < first_tb + kMmaTile);
+  if (early) issue_tile(warp, 0);
+
   // Q as A-operand fragments: rows 0..G-1 hold the group's query heads (scaled), rows G..15 are zero
   uint32_t qa[8][2];   // per 16-wide k step: a0 (row, k lo pair) and a2 (row, k hi pair); a1 = a3 = 0 (rows 8..15)
   const float* qp = p.q + ((size_t)b * p.nq + kvh * G + (row < G ? row : 0)) * hd;
@@ -156,23 +177,8 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
   float m = -INFINITY, l = 0.0f;   // running max of the row (same in the row's four lanes) and this lane's share of the sum
 
-  uint8_t* wt = tiles + (size_t)warp * 4 * kMmaTileBytes;
-  auto issue_tile = [&](int j, int buf) {   // tile j of the CTA -> K, V buffers `buf` of this warp
-    const int tb = t0 + j * kMmaTile;
-    const int page = bt[tb >> pshift];
-    const size_t rowbase = ((size_t)page * p.nkv + kvh) * p.page_size + (tb & pmask);
-    const uint32_t kd = mma_smem_u32(wt + (2 * buf) * kMmaTileBytes), vd = kd + kMmaTileBytes;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = i * 32 + lane, r = c >> 4, c16 = c & 15;
-      // rows past the end of the sequence are zero-filled: their scores are masked, but 0 x (stale NaN in V) is NaN
-      const int nb = tb + r < t1 ? 16 : 0;
-      cp_async16(kd + r * kMmaRow + c16 * 16, p.k + (rowbase + r) * 256 + c16 * 16, nb);
-      cp_async16(vd + r * kMmaRow + c16 * 16, p.v + (rowbase + r) * 256 + c16 * 16, nb);
-    }
-  };
   int buf = 0;
-  if (warp < ntiles) issue_tile(warp, 0);
+  if (warp < ntiles && !early) issue_tile(warp, 0);
   cp_async_commit();
   for (int j = warp; j < ntiles; j += kMmaWarps, buf ^= 1) {
     if (j + kMmaWarps < ntiles) issue_tile(j + kMmaWarps, buf ^ 1);
