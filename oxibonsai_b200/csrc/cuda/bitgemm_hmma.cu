@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p)
 __global__ void norm_to_f16_hmma_kernel(const float* __restrict__ x, int x_ld, const float* __restrict__ w, float eps, int K,
                                         __half* __restrict__ out, int out_ld, int vec) {
   __shared__ float s32[32];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const float* xr = x + (size_t)blockIdx.x * x_ld;
   __half* orow = out + (size_t)blockIdx.x * out_ld;
   if (vec) {
@@ -292,8 +293,9 @@ int bonsai_norm_to_f16_hmma(const float* x, int x_ld, const float* w, float eps,
   // one block per token: a block as wide as the row allows keeps the two passes short (few tokens = few blocks)
   const int threads = K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256);
   const int vec = (x_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);   // 16-byte loads
-  bonsai::norm_to_f16_hmma_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, vec);
-  return bonsai::launch_status();
+  const cudaError_t e = bonsai::launch_pdl(bonsai::norm_to_f16_hmma_kernel, dim3(T), dim3(threads), 0, stream, x, x_ld, w, eps, K, (__half*)out,
+                                           out_ld, vec);
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 }  // extern "C"

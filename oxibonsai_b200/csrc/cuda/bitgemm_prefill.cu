@@ -186,6 +186,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   const int tile0 = (int)(I0 / npairs), pair0 = (int)(I0 - (long long)tile0 * npairs);
 
   if (t == 0) PF_STAMP(0);
+  // Programmatic dependent launch: this CTA may start while the previous kernel of the stream is still running.  Set-up,
+  // TMEM allocation and the expanders' first weight loads depend on nothing it writes; the warps that touch its outputs
+  // (activation copies, epilogue reads and writes, the work-split workspace) wait for it below.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (warp == kPfMmaWarp) {
     tc::tmem_alloc(&tmem_slot, 2 * kAccCols);
     tc::tmem_relinquish();
@@ -222,6 +226,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   // the epilogue adds the accumulators that were written.
   if (warp >= kPfTmaWarp && warp < kPfTmaWarp + NISS) {
     // ------------------------------- TMA issuers (activations; dense weights) -------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tw = warp - kPfTmaWarp;
     int tile = tile0, pair = pair0;
     for (int q = 0; q < n && !failed; ++q) {
@@ -373,6 +378,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
     }
   } else if (warp < kPfMmaWarp) {
     // ------------------------------- epilogue (thread = weight row) ------------------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int a = t - kPfExpThreads;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     int seg = 0;
@@ -532,6 +538,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
 __global__ void norm_to_f16_paired_kernel(const float* __restrict__ x, int x_ld, const float* __restrict__ w, float eps, int K,
                                           __half* __restrict__ out, int out_ld, int natural, int vec) {
   __shared__ float s32[32];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int tok = blockIdx.x;
   const float* xr = x + (size_t)tok * x_ld;
   __half* orow = out + (size_t)tok * out_ld;
@@ -592,8 +599,8 @@ static int launch_prefill(const CUtensorMap& xmap, const CUtensorMap& amap, bons
   size_t smem = 1024 + (size_t)S * (kPfABytes + TOK * 128);
   cudaError_t e = cudaFuncSetAttribute(bitgemm_prefill_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
-  bitgemm_prefill_kernel<TOK><<<grid, kPfThreads, smem, stream>>>(xmap, amap, p);
-  return launch_status();
+  e = launch_pdl(bitgemm_prefill_kernel<TOK>, dim3(grid), dim3(kPfThreads), smem, stream, xmap, amap, p);
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 extern "C" {
@@ -651,8 +658,9 @@ int bonsai_norm_to_f16_paired(const float* x, int x_ld, const float* w, float ep
   // one block per token; with few tokens (decode batches) a wide block keeps the two passes short
   const int threads = T <= 128 ? (K >= 4096 ? 1024 : (K >= 2048 ? 512 : 256)) : 256;
   const int vec = (x_ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);   // 16-byte loads
-  bonsai::norm_to_f16_paired_kernel<<<T, threads, 0, stream>>>(x, x_ld, w, eps, K, (__half*)out, out_ld, natural, vec);
-  return bonsai::launch_status();
+  const cudaError_t e = bonsai::launch_pdl(bonsai::norm_to_f16_paired_kernel, dim3(T), dim3(threads), 0, stream, x, x_ld, w, eps, K, (__half*)out,
+                                           out_ld, natural, vec);
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 }  // extern "C"
