@@ -7,8 +7,8 @@
 // parallel_tiled.rs (row-parallel GEMV, batch GEMM that decodes a weight block once for all batch
 // rows), aligned.rs / prefetch.rs (64-byte aligned buffers, prefetch hints).  The scalar bodies here
 // keep the reference's summation order (sequential inside a block, then `sum += d * block_sum`), so
-// tier 0 is bit-identical to the oracle in cpu/oracle.cpp; the AVX2 bodies reorder additions and are
-// the timed CPU baseline.  The serving path of this project is the GPU; these kernels exist for the
+// tier 0 is bit-identical to the oracle in cpu/oracle.cpp; the AVX2 and AVX-512 bodies reorder additions
+// and are the timed CPU baseline (the reference's simd_avx512.rs tier: 16-lane masks instead of a decode).  The serving path of this project is the GPU; these kernels exist for the
 // CPU fallback, for tests and for the CPU side of benchmarks.
 #include <immintrin.h>
 
@@ -115,12 +115,101 @@ __attribute__((target("avx2,fma"))) float dot_q1_avx2(const uint8_t* row, uint64
   return hsum256(total);
 }
 
+// ---- AVX-512 bodies ------------------------------------------------------------------------------
+// The weights never become numbers: sixteen 2-bit codes (or sixteen sign bits) turn into two mask registers and the
+// activations are added or subtracted under them, sixteen lanes per instruction.
+#define BONSAI_AVX512 __attribute__((target("avx512f,avx512bw,avx512vl,avx2,fma")))
+
+BONSAI_AVX512 float dot_tq2_avx512(const uint8_t* row, uint64_t nblk, const float* x) {
+  const __m512i shifts = _mm512_setr_epi32(0, 2, 4, 6, 8, 10, 12, 14, 16, 18, 20, 22, 24, 26, 28, 30);
+  const __m512i three = _mm512_set1_epi32(3), two = _mm512_set1_epi32(2);
+  __m512 total = _mm512_setzero_ps();
+  for (uint64_t b = 0; b < nblk; ++b, row += 34, x += 128) {
+    __m512 acc0 = _mm512_setzero_ps(), acc1 = _mm512_setzero_ps();
+    for (int c = 0; c < 8; c += 2) {
+      uint32_t w0, w1;
+      std::memcpy(&w0, row + 4 * c, 4);
+      std::memcpy(&w1, row + 4 * c + 4, 4);
+      const __m512i c0 = _mm512_and_si512(_mm512_srlv_epi32(_mm512_set1_epi32((int)w0), shifts), three);
+      const __m512i c1 = _mm512_and_si512(_mm512_srlv_epi32(_mm512_set1_epi32((int)w1), shifts), three);
+      const __m512 x0 = _mm512_loadu_ps(x + 16 * c), x1 = _mm512_loadu_ps(x + 16 * c + 16);
+      acc0 = _mm512_mask_add_ps(acc0, _mm512_cmpeq_epi32_mask(c0, two), acc0, x0);                    // code 2 = +1
+      acc0 = _mm512_mask_sub_ps(acc0, _mm512_cmpeq_epi32_mask(c0, _mm512_setzero_si512()), acc0, x0);  // code 0 = -1
+      acc1 = _mm512_mask_add_ps(acc1, _mm512_cmpeq_epi32_mask(c1, two), acc1, x1);
+      acc1 = _mm512_mask_sub_ps(acc1, _mm512_cmpeq_epi32_mask(c1, _mm512_setzero_si512()), acc1, x1);
+    }
+    total = _mm512_fmadd_ps(_mm512_add_ps(acc0, acc1), _mm512_set1_ps(f16_to_f32(ld_u16(row + 32))), total);
+  }
+  return _mm512_reduce_add_ps(total);
+}
+
+BONSAI_AVX512 float dot_q1_avx512(const uint8_t* row, uint64_t nblk, const float* x) {
+  __m512 total = _mm512_setzero_ps();
+  for (uint64_t b = 0; b < nblk; ++b, row += 18, x += 128) {
+    __m512 acc0 = _mm512_setzero_ps(), acc1 = _mm512_setzero_ps();
+    for (int c = 0; c < 8; c += 2) {
+      const __mmask16 m0 = (__mmask16)ld_u16(row + 2 + 2 * c), m1 = (__mmask16)ld_u16(row + 4 + 2 * c);
+      const __m512 x0 = _mm512_loadu_ps(x + 16 * c), x1 = _mm512_loadu_ps(x + 16 * c + 16);
+      acc0 = _mm512_mask_add_ps(acc0, m0, acc0, x0);   // bit set = +x
+      acc0 = _mm512_mask_sub_ps(acc0, (__mmask16)~m0, acc0, x0);
+      acc1 = _mm512_mask_add_ps(acc1, m1, acc1, x1);
+      acc1 = _mm512_mask_sub_ps(acc1, (__mmask16)~m1, acc1, x1);
+    }
+    total = _mm512_fmadd_ps(_mm512_add_ps(acc0, acc1), _mm512_set1_ps(f16_to_f32(ld_u16(row))), total);
+  }
+  return _mm512_reduce_add_ps(total);
+}
+
+BONSAI_AVX512 float dot_f32_avx512(const float* a, const float* b, uint64_t n) {
+  __m512 s0 = _mm512_setzero_ps(), s1 = _mm512_setzero_ps();
+  uint64_t i = 0;
+  for (; i + 32 <= n; i += 32) {
+    s0 = _mm512_fmadd_ps(_mm512_loadu_ps(a + i), _mm512_loadu_ps(b + i), s0);
+    s1 = _mm512_fmadd_ps(_mm512_loadu_ps(a + i + 16), _mm512_loadu_ps(b + i + 16), s1);
+  }
+  float s = _mm512_reduce_add_ps(_mm512_add_ps(s0, s1));
+  for (; i < n; ++i) s += a[i] * b[i];
+  return s;
+}
+
+__attribute__((target("avx2,fma"))) float dot_f32_avx2(const float* a, const float* b, uint64_t n) {
+  __m256 s0 = _mm256_setzero_ps(), s1 = _mm256_setzero_ps();
+  uint64_t i = 0;
+  for (; i + 16 <= n; i += 16) {
+    s0 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i), _mm256_loadu_ps(b + i), s0);
+    s1 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i + 8), _mm256_loadu_ps(b + i + 8), s1);
+  }
+  float s = hsum256(_mm256_add_ps(s0, s1));
+  for (; i < n; ++i) s += a[i] * b[i];
+  return s;
+}
+
+float dot_f32_ref(const float* a, const float* b, uint64_t n) {
+  float s = 0.0f;
+  for (uint64_t k = 0; k < n; ++k) s += a[k] * b[k];
+  return s;
+}
+
+BONSAI_AVX512 float sumsq_avx512(const float* x, uint64_t n) {
+  __m512 a = _mm512_setzero_ps();
+  uint64_t i = 0;
+  for (; i + 16 <= n; i += 16) {
+    const __m512 v = _mm512_loadu_ps(x + i);
+    a = _mm512_fmadd_ps(v, v, a);
+  }
+  float s = _mm512_reduce_add_ps(a);
+  for (; i < n; ++i) s += x[i] * x[i];
+  return s;
+}
+
 using RowDot = float (*)(const uint8_t*, uint64_t, const float*);
 RowDot pick(uint32_t type, int tier) {
-  if (type == 42) return tier >= kAvx2 ? dot_tq2_avx2 : dot_tq2_ref;
-  if (type == 41) return tier >= kAvx2 ? dot_q1_avx2 : dot_q1_ref;
+  if (type == 42) return tier >= kAvx512 ? dot_tq2_avx512 : (tier >= kAvx2 ? dot_tq2_avx2 : dot_tq2_ref);
+  if (type == 41) return tier >= kAvx512 ? dot_q1_avx512 : (tier >= kAvx2 ? dot_q1_avx2 : dot_q1_ref);
   return nullptr;
 }
+using VecDot = float (*)(const float*, const float*, uint64_t);
+VecDot pick_f32(int tier) { return tier >= kAvx512 ? dot_f32_avx512 : (tier >= kAvx2 ? dot_f32_avx2 : dot_f32_ref); }
 
 template <typename F>
 void parallel_rows(uint64_t n, int threads, F f) {
@@ -142,7 +231,7 @@ void parallel_rows(uint64_t n, int threads, F f) {
 
 extern "C" {
 
-// 0 reference, 1 AVX2+FMA, 2 AVX-512 capable (runs the AVX2 bodies).
+// 0 reference, 1 AVX2+FMA, 2 AVX-512 (F + BW + VL).
 int bcpu_detect_tier() { return bonsai::detect_tier(); }
 int bcpu_active_tier() { return bonsai::active_tier(); }
 // Forces a tier not above what the CPU supports; -1 returns to auto detection.  Returns the tier now active.
@@ -178,15 +267,13 @@ int bcpu_gemm_tiered(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t
   if (type != 41 && type != 42) return -7;
   const uint64_t rb = (cols / 128) * (type == 42 ? 34 : 18);
   if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
+  const VecDot vdot = pick_f32(active_tier());
   parallel_rows(rows, threads, [=](uint64_t lo, uint64_t hi) {
     std::vector<float> w(cols);
     for (uint64_t r = lo; r < hi; ++r) {
       if (type == 42) dequant_tq2(data + r * rb, cols / 128, w.data()); else dequant_q1(data + r * rb, cols / 128, w.data());
       for (uint64_t b = 0; b < batch; ++b) {
-        const float* xb = x + b * cols;
-        float s = 0.0f;
-        for (uint64_t k = 0; k < cols; ++k) s += w[k] * xb[k];
-        out[b * rows + r] = s;
+        out[b * rows + r] = vdot(w.data(), x + b * cols, cols);
       }
     }
   });
@@ -208,7 +295,10 @@ __attribute__((target("avx2,fma"))) static float sumsq_avx2(const float* x, uint
 
 void bcpu_rmsnorm_tiered(const float* x, const float* w, float* out, uint64_t n, float eps, int tier) {
   float ss = 0.0f;
-  if (tier >= 1 && bonsai::detect_tier() >= 1) ss = sumsq_avx2(x, n); else for (uint64_t i = 0; i < n; ++i) ss += x[i] * x[i];
+  const int have = std::min(tier, bonsai::detect_tier());
+  if (have >= 2) ss = bonsai::sumsq_avx512(x, n);
+  else if (have >= 1) ss = sumsq_avx2(x, n);
+  else for (uint64_t i = 0; i < n; ++i) ss += x[i] * x[i];
   const float inv = 1.0f / std::sqrt(ss / (float)n + eps);
   for (uint64_t i = 0; i < n; ++i) out[i] = w[i] * x[i] * inv;
 }
