@@ -116,6 +116,38 @@ static int launch_quant_gemv(const void* w, const float* x, const float* norm_w,
   return launch_status();
 }
 
+// Decodes an [N][K] matrix of blocks into row-major f16 for the dense tensor-core GEMM of the prompt path.  One thread
+// owns eight consecutive inputs and stores them as one 16-byte word.  With `paired` the eight values are written in the
+// K order of the GEMM's activation operand (inside every 16 inputs: position (j & 8) | ((j & 3) * 2 + ((j >> 2) & 1))
+// for input j), so the prompt path's normalisation and attention kernels can feed the GEMM without a transpose.
+template <typename D>
+__global__ void __launch_bounds__(256) quant_to_f16_kernel(const uint8_t* __restrict__ w, __half* __restrict__ out, int N, int K, int paired) {
+  const int nblk = K / D::kElems, per_row = K / 8;
+  const size_t row_bytes = (size_t)nblk * D::kBytes;
+  const size_t total = (size_t)N * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int row = (int)(idx / per_row), k0 = (int)(idx % per_row) * 8;
+    const uint8_t* bp = w + (size_t)row * row_bytes + (size_t)(k0 / D::kElems) * D::kBytes;
+    const int i0 = k0 % D::kElems;
+    __align__(16) __half v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int dst = paired ? ((j & 3) * 2 + ((j >> 2) & 1)) : j;
+      v[dst] = __float2half_rn(D::at(bp, i0 + j));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)row * K + k0) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+template <typename D>
+static int launch_quant_to_f16(const void* w, void* out, int N, int K, int paired, cudaStream_t st) {
+  if (K % D::kElems != 0 || K % 16 != 0) return BONSAI_CUDA_BAD_ARG;
+  const size_t total = (size_t)N * (K / 8);
+  int grid = (int)((total + 255) / 256 < (size_t)(148 * 16) ? (total + 255) / 256 : (size_t)(148 * 16));
+  quant_to_f16_kernel<D><<<grid, 256, 0, st>>>((const uint8_t*)w, (__half*)out, N, K, paired);
+  return launch_status();
+}
+
 __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out, int n) {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const float g = gate[i];
@@ -148,6 +180,30 @@ int bonsai_quant_gemv(int type, const void* w, const float* x, const float* norm
     case 35: return launch_quant_gemv<DecTq2_256>(w, x, norm_w, eps, out, residual, N, K, stream);
     case 43: return launch_quant_gemv<DecFp8<false>>(w, x, norm_w, eps, out, residual, N, K, stream);
     case 44: return launch_quant_gemv<DecFp8<true>>(w, x, norm_w, eps, out, residual, N, K, stream);
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+}
+
+// out f16 [N][K] = the decoded matrix (same type ids as bonsai_quant_gemv); `paired` selects the activation K order of
+// the tcgen05 GEMM instead of the natural one.  `out` must be 16-byte aligned.
+int bonsai_quant_to_f16(int type, const void* w, void* out, int N, int K, int paired, cudaStream_t stream) {
+  using namespace bonsai;
+  if (N <= 0 || K <= 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0) return BONSAI_CUDA_BAD_ARG;
+  switch (type) {
+    case 0: return launch_quant_to_f16<DecF32>(w, out, N, K, paired, stream);
+    case 1: return launch_quant_to_f16<DecF16>(w, out, N, K, paired, stream);
+    case 30: return launch_quant_to_f16<DecBF16>(w, out, N, K, paired, stream);
+    case 2: return launch_quant_to_f16<DecQ4_0>(w, out, N, K, paired, stream);
+    case 8: return launch_quant_to_f16<DecQ8_0>(w, out, N, K, paired, stream);
+    case 10: return launch_quant_to_f16<DecQ2K>(w, out, N, K, paired, stream);
+    case 11: return launch_quant_to_f16<DecQ3K>(w, out, N, K, paired, stream);
+    case 12: return launch_quant_to_f16<DecQ4K>(w, out, N, K, paired, stream);
+    case 13: return launch_quant_to_f16<DecQ5K>(w, out, N, K, paired, stream);
+    case 14: return launch_quant_to_f16<DecQ6K>(w, out, N, K, paired, stream);
+    case 15: return launch_quant_to_f16<DecQ8K>(w, out, N, K, paired, stream);
+    case 35: return launch_quant_to_f16<DecTq2_256>(w, out, N, K, paired, stream);
+    case 43: return launch_quant_to_f16<DecFp8<false>>(w, out, N, K, paired, stream);
+    case 44: return launch_quant_to_f16<DecFp8<true>>(w, out, N, K, paired, stream);
     default: return BONSAI_CUDA_BAD_ARG;
   }
 }

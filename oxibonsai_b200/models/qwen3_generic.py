@@ -5,8 +5,11 @@ decode GEMV (csrc/cuda/quant_gemv.cu).
 Reference: the per-format GPU forward paths (crates/oxibonsai-model/src/model/types/forward_cuda/q_std.rs, k_quant.rs,
 forward_cuda_fp8.rs) and their prefill variants (crates/oxibonsai-kernels/src/gpu_backend/cuda_q_std_prefill.rs,
 cuda_k_quant_prefill/*, cuda_fp8_prefill.rs).  A decode step is ~12 launches per layer issued from Python and captured
-once into a CUDA graph; the prompt runs through the same step token by token.  Attention, KV append, LM head and
-sampler are the kernels of the native engine.  The sub-2-bit formats (Q1_0_g128, TQ2_0_g128) should use
+once into a CUDA graph.  Prompts of at least ``prefill_min`` tokens run in chunks through the tensor cores: each weight
+matrix is decoded once per chunk into an f16 scratch matrix (csrc/cuda/quant_gemv.cu, bonsai_quant_to_f16) and multiplied
+by all the chunk's tokens with the dense tcgen05 GEMM, with the prompt-attention kernel of the native engine in between;
+shorter prompts go through the decode step token by token (all f32).  Attention, KV append, LM head and sampler are the
+kernels of the native engine.  The sub-2-bit formats (Q1_0_g128, TQ2_0_g128) should use
 ``oxibonsai_b200.runtime.InferenceEngine``, which is several times faster.
 """
 from __future__ import annotations
@@ -40,12 +43,14 @@ class _Linear:
 
 class GenericQwen3Engine:
     def __init__(self, model_path: str, max_seq_len: int = 2048, kv_dtype: str = "f16", device: str = "cuda:0", page_size: int = 64,
-                 sampling: SamplingParams | None = None):
+                 sampling: SamplingParams | None = None, prefill_min: int = 16, prefill_chunk: int = 512):
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.gguf = GgufFile.open(model_path)
         self.config = c = self.gguf.config()
         self.max_seq_len = max_seq_len
+        self.prefill_min, self.prefill_chunk = prefill_min, prefill_chunk
+        self._wscratch = None
         self.sampling = sampling or SamplingPreset.GREEDY.params()
         f, dev = self.gguf, self.device
         self.kvt = {"f32": K.KV_F32, "f16": K.KV_F16, "q8": K.KV_Q8, "q4": K.KV_Q4}[kv_dtype]
@@ -119,6 +124,52 @@ class GenericQwen3Engine:
         K.f16gemv(self.lm_head, self.h, self.out_norm, eps, out=self.logits[0])
         K.sample(self.logits, self.temps, self.topks, self.topps, self.rng, positions=self.pos, advance=True, out=self.out_token)
 
+    def prefill_supported(self) -> bool:
+        """The tensor-core prompt path needs every matrix width to be a multiple of 128 and a head size the prompt attention has."""
+        c = self.config
+        return c.hidden % 128 == 0 and c.inter % 128 == 0 and (c.heads * c.head_dim) % 128 == 0 and c.head_dim in (64, 128)
+
+    def prefill(self, tokens: torch.Tensor, pos0: int = 0) -> None:
+        """Runs ``tokens`` (int32 on the device) through every layer as chunks of up to ``prefill_chunk`` tokens, filling the KV
+        cache for positions pos0 .. pos0 + len - 1.  Nothing is sampled: the caller feeds the prompt's last token to ``step``."""
+        c, eps, dev = self.config, self.config.eps, self.device
+        qd, kvd = c.heads * c.head_dim, c.kv_heads * c.head_dim
+        if self._wscratch is None:
+            self._wscratch = torch.empty(max(c.hidden * c.inter, qd * c.hidden), dtype=torch.float16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        def mm(lin: _Linear, x16: torch.Tensor, out: torch.Tensor, residual: torch.Tensor | None = None) -> None:
+            w16 = K.quant_to_f16(lin.type, lin.data, lin.n, lin.k, out=self._wscratch[: lin.n * lin.k].view(lin.n, lin.k), paired=True)
+            K.dense_gemm_f16(w16, x16, out=out, residual=residual)
+
+        done = 0
+        while done < tokens.numel():
+            T = min(self.prefill_chunk, tokens.numel() - done)
+            p0 = pos0 + done
+            h = torch.index_select(self.embd, 0, tokens[done:done + T].long()).float()
+            positions = torch.arange(p0, p0 + T, dtype=torch.int32, device=dev)
+            bt = self.bt.expand(T, -1).contiguous()
+            qkv = torch.empty((T, qd + 2 * kvd), **f32)
+            q = torch.empty((T, c.heads, c.head_dim), **f32)
+            gate, up, act = (torch.empty((T, c.inter), **f32) for _ in range(3))
+            for l, w in enumerate(self.layers):
+                xn = K.norm_to_f16_paired(h, w["attn_norm"], eps)
+                mm(w["q"], xn, qkv[:, :qd])
+                mm(w["k"], xn, qkv[:, qd:qd + kvd])
+                mm(w["v"], xn, qkv[:, qd + kvd:])
+                ks = self.kscale[l] if self.kscale is not None else None
+                vs = self.vscale[l] if self.vscale is not None else None
+                K.qknorm_rope_kvstore(qkv, w["q_norm"], w["k_norm"], eps, self.cos, self.sin, positions, bt, q, c.heads, c.kv_heads, c.head_dim,
+                                      self.kvt, self.page, self.kpool[l], self.vpool[l], ks, vs)
+                a16 = K.attn_prefill(q, p0, self.bt[0], c.heads, c.kv_heads, c.head_dim, self.kvt, self.page, self.kpool[l], self.vpool[l], ks, vs)
+                mm(w["o"], a16, h, residual=h)
+                xn = K.norm_to_f16_paired(h, w["ffn_norm"], eps)
+                mm(w["gate"], xn, gate)
+                mm(w["up"], xn, up)
+                K.swiglu(gate, up, out=act)
+                mm(w["down"], K.norm_to_f16_paired(act, None, eps), h, residual=h)
+            done += T
+
     def step(self) -> None:
         """One token through the model (token and position are read from device buffers); replays a captured graph."""
         if self._graph is None:
@@ -153,7 +204,12 @@ class GenericQwen3Engine:
         self._set_sampling(p)
         toks = torch.tensor(prompt, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         self.pos.zero_()
-        for i in range(len(prompt)):
+        first = 0
+        if len(prompt) - 1 >= self.prefill_min and self.prefill_supported():
+            first = len(prompt) - 1                      # the last prompt token goes through the decode step, which samples
+            self.prefill(toks[:first])
+            self.pos.fill_(first)
+        for i in range(first, len(prompt)):
             self.token.copy_(toks[i:i + 1], non_blocking=True)
             self.step()
         for _ in range(max_tokens):

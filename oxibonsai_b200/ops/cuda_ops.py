@@ -137,6 +137,7 @@ def _mma():
 _QG_SIG = {
     "bonsai_quant_gemv": [_i, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp],
     "bonsai_swiglu": [_vp, _vp, _vp, _i, _vp],
+    "bonsai_quant_to_f16": [_i, _vp, _vp, _i, _i, _i, _vp],
 }
 _qg_declared = False
 
@@ -158,6 +159,17 @@ def quant_gemv(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, n
     if out is None:
         out = torch.empty(n, dtype=torch.float32, device=x.device)
     check(_qg().bonsai_quant_gemv(type_id, w.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual), n, k, stream()), "quant_gemv")
+    return out
+
+
+def quant_to_f16(type_id: int, w: torch.Tensor, n: int, k: int, out: torch.Tensor | None = None, paired: bool = True) -> torch.Tensor:
+    """Decodes the raw GGUF bytes of an [n, k] matrix into dense f16 [n, k]; ``paired`` writes the K order of the tcgen05 GEMM's
+    activation operand (``paired_k_index``) so that ``dense_gemm_f16`` can take paired-K activations."""
+    assert w.is_cuda and w.dtype == torch.uint8
+    if out is None:
+        out = torch.empty((n, k), dtype=torch.float16, device=w.device)
+    assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() >= n * k
+    check(_qg().bonsai_quant_to_f16(type_id, w.data_ptr(), out.data_ptr(), n, k, int(paired), stream()), "quant_to_f16")
     return out
 
 
@@ -501,8 +513,10 @@ def new_gemm_workspace(device) -> torch.Tensor:
 
 
 def dense_gemm_f16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                   sms: int = 148, balanced: bool | str = "auto") -> torch.Tensor:
-    """out[T, N] (f32) = x[T, K] @ w[N, K]^T for dense f16 operands (natural K order) on tcgen05; used for the LM head."""
+                   sms: int = 148, balanced: bool | str = "auto", residual: torch.Tensor | None = None) -> torch.Tensor:
+    """out[T, N] (f32) = (residual +) x[T, K] @ w[N, K]^T for dense f16 operands on tcgen05 (both in the same K order, natural
+    or paired); used for the LM head and for the prompt path of the block formats without a planar repack.  ``residual``
+    (f32 [T, N], same row stride as ``out``; may be ``out`` itself) is added in the epilogue."""
     T, n = x.shape[0], w.shape[0]
     assert w.dtype == torch.float16 and x.dtype == torch.float16 and w.is_contiguous() and x.shape[1] == w.shape[1]
     if out is None:
@@ -510,8 +524,10 @@ def dense_gemm_f16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = 
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=x.device)
     ws = gemm_workspace(x.device) if balanced else None
-    check(_pf().bonsai_bitgemm_prefill_ws(None, None, x.data_ptr(), x.stride(0), out.data_ptr(), None, None, status.data_ptr(), n,
-                                          w.shape[1], T, 0, out.stride(0), sms, w.data_ptr(), ptr(ws), ws.numel() if balanced else 0,
+    assert residual is None or residual.stride(0) == out.stride(0)
+    check(_pf().bonsai_bitgemm_prefill_ws(None, None, x.data_ptr(), x.stride(0), out.data_ptr(), ptr(residual), None, status.data_ptr(), n,
+                                          w.shape[1], T, 0 if residual is None else 1, out.stride(0), sms, w.data_ptr(), ptr(ws),
+                                          ws.numel() if balanced else 0,
                                           _balance_mode(balanced), stream()), "dense_gemm_f16")
     return out
 

@@ -56,3 +56,48 @@ def test_generic_engine_follows_the_cpu_oracle(fmt, tiny_gguf, tmp_path):
     assert len(got) == 12 and agree >= 10, (fmt, got, want)      # f32 everywhere; only the summation order differs from the CPU
     assert eng.generate(prompt, 12, stop_at_eos=False) == got     # graph replay is deterministic
     assert eng.kernel_launches_per_step() == 12 * 2 + 3
+
+
+@pytest.mark.parametrize("name,tid,tol", TYPES)
+def test_quant_to_f16_decodes_every_block_format(name, tid, tol):
+    from oxibonsai_b200.core.blocks import dequantize, quantize
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(5)
+    n, k = 37, 512
+    q = quantize(tid, rng.normal(size=(n, k)).astype(np.float32) * 0.05)
+    want = torch.from_numpy(dequantize(tid, q).reshape(n, k)).to(dev).half()      # the kernel rounds the same f32 value once
+    qd = torch.from_numpy(q).to(dev)
+    nat = K.quant_to_f16(tid, qd, n, k, paired=False)
+    assert torch.allclose(nat.float(), want.float(), rtol=2e-3, atol=1e-6), name      # one f16 ulp: the device may fuse d * q - m
+    paired = K.quant_to_f16(tid, qd, n, k, paired=True)
+    perm = K.paired_k_index(k, dev)
+    assert torch.equal(paired[:, perm], nat), name
+    # dense GEMM over paired-K operands with the residual epilogue against fp32 PyTorch
+    x = torch.randn(70, k, device=dev)
+    res = torch.randn(70, n, device=dev)
+    got = K.dense_gemm_f16(paired, K.norm_to_f16_paired(x, None), residual=res)
+    ref = res + x.half().float() @ nat.float().T
+    assert torch.allclose(got, ref, rtol=1e-3, atol=1e-3), name
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k"])
+def test_generic_engine_tensor_core_prompt_path_matches_token_by_token(fmt, tiny_gguf, tmp_path):
+    from oxibonsai_b200 import cli
+    from oxibonsai_b200.models.qwen3_generic import GenericQwen3Engine
+    path = str(tmp_path / f"tiny_{fmt}.gguf")
+    cli.requantize_gguf(tiny_gguf, path, fmt)
+    prompt = [int(t) for t in np.random.default_rng(9).integers(0, 1000, 90)]
+    slow = GenericQwen3Engine(path, max_seq_len=256, kv_dtype="f32", prefill_min=10**9)
+    fast = GenericQwen3Engine(path, max_seq_len=256, kv_dtype="f32", prefill_min=16, prefill_chunk=64)   # two chunks, the second ragged
+    assert fast.prefill_supported()
+    a = slow.generate(prompt, 1, stop_at_eos=False)
+    b = fast.generate(prompt, 1, stop_at_eos=False)
+    la, lb = slow.logits[0].float(), fast.logits[0].float()
+    assert torch.nn.functional.cosine_similarity(la, lb, dim=0).item() > 0.999, fmt     # f16 operands in the prompt path only
+    assert (la - lb).abs().max().item() <= 0.03 * la.abs().max().item(), fmt
+    n = len(prompt) - 1
+    ka = slow.kpool[:, : (n + 63) // 64].float()
+    kb = fast.kpool[:, : (n + 63) // 64].float()
+    assert torch.allclose(ka, kb, rtol=2e-2, atol=2e-2)
+    assert len(a) == 1 and len(b) == 1
