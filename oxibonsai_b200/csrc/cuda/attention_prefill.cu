@@ -24,6 +24,15 @@ __host__ __device__ inline int pf_paired_k(int k) {
   return (k & ~15) | hi | (p * 2 + q);
 }
 
+// position of logical input k in the K order of the mma.sync decode-batch GEMM (a permutation inside every 128 inputs;
+// the same map as hmma_k_pos in bitgemm_hmma.cu)
+__host__ __device__ inline int pf_hmma_k(int k) {
+  const int r = k & 127, wq = r >> 4, e = r & 15;
+  const int c = wq >> 1, j = wq & 1, plane = e >> 3, p = e & 3, h = (e >> 2) & 1;
+  return (k & ~127) | ((j * 4 + p) * 16 + plane * 8 + 2 * c + h);
+}
+__host__ __device__ inline int pf_out_k(int k, int order) { return order == 1 ? pf_hmma_k(k) : pf_paired_k(k); }
+
 struct PfKvPool {
   const uint8_t* k;
   const uint8_t* v;
@@ -90,7 +99,8 @@ __device__ __forceinline__ void stage_kv(__half* dst, const uint8_t* pool, const
 // grid (ceil(T/64), nq); block 128.  Query row i of the chunk sits at absolute position pos0 + i.
 template <int HD>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restrict__ q, int T, int pos0, const int* __restrict__ bt,
-                                                          PfKvPool kv, int nq, float sm_scale, __half* __restrict__ out, int out_ld) {
+                                                          PfKvPool kv, int nq, float sm_scale, __half* __restrict__ out, int out_ld,
+                                                          int k_order) {
   constexpr int LD = HD + 8;
   extern __shared__ __half smem_h[];
   __half* sQ = smem_h;             // [64][LD]
@@ -210,12 +220,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
     const int d = nt * 8 + (lane & 3) * 2;
     const int n0 = head * HD + d;
     if (row0 < T) {
-      out[(size_t)row0 * out_ld + pf_paired_k(n0)] = __float2half_rn(o[nt][0] * i0);
-      out[(size_t)row0 * out_ld + pf_paired_k(n0 + 1)] = __float2half_rn(o[nt][1] * i0);
+      out[(size_t)row0 * out_ld + pf_out_k(n0, k_order)] = __float2half_rn(o[nt][0] * i0);
+      out[(size_t)row0 * out_ld + pf_out_k(n0 + 1, k_order)] = __float2half_rn(o[nt][1] * i0);
     }
     if (row1 < T) {
-      out[(size_t)row1 * out_ld + pf_paired_k(n0)] = __float2half_rn(o[nt][2] * i1);
-      out[(size_t)row1 * out_ld + pf_paired_k(n0 + 1)] = __float2half_rn(o[nt][3] * i1);
+      out[(size_t)row1 * out_ld + pf_out_k(n0, k_order)] = __float2half_rn(o[nt][2] * i1);
+      out[(size_t)row1 * out_ld + pf_out_k(n0 + 1, k_order)] = __float2half_rn(o[nt][3] * i1);
     }
   }
 }
@@ -225,11 +235,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
 extern "C" {
 
 // q f32 [T][nq][hd]; block_table: the sequence's page list; the chunk's first token sits at pos0.
-// out f16 [T][out_ld] (paired-K order).
-int bonsai_attn_prefill(const float* q, int T, int pos0, const int* block_table, int nq, int nkv, int hd, int kvt, int page_size,
-                        const void* kpool, const void* vpool, const float* kscale, const float* vscale, void* out, int out_ld,
-                        cudaStream_t stream) {
+// out f16 [T][out_ld]; k_order 0 = paired-K (operand order of the tcgen05 GEMM), 1 = hmma-K (the mma.sync GEMM; needs
+// nq * hd to be a multiple of 128).
+int bonsai_attn_prefill_order(const float* q, int T, int pos0, const int* block_table, int nq, int nkv, int hd, int kvt, int page_size,
+                              const void* kpool, const void* vpool, const float* kscale, const float* vscale, void* out, int out_ld,
+                              int k_order, cudaStream_t stream) {
   using namespace bonsai;
+  if (k_order < 0 || k_order > 1 || (k_order == 1 && (nq * hd) % 128 != 0)) return BONSAI_CUDA_BAD_ARG;
   if (T < 1 || (hd != 64 && hd != 128) || nq % nkv != 0 || kvt < 0 || kvt > 3) return BONSAI_CUDA_BAD_ARG;
   PfKvPool kv{(const uint8_t*)kpool, (const uint8_t*)vpool, kscale, vscale, page_size, nkv, hd, kvt};
   dim3 grid((T + 63) / 64, nq);
@@ -239,13 +251,20 @@ int bonsai_attn_prefill(const float* q, int T, int pos0, const int* block_table,
   if (hd == 128) {
     e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
-    attn_prefill_kernel<128><<<grid, 128, smem, stream>>>(q, T, pos0, block_table, kv, nq, sc, (__half*)out, out_ld);
+    attn_prefill_kernel<128><<<grid, 128, smem, stream>>>(q, T, pos0, block_table, kv, nq, sc, (__half*)out, out_ld, k_order);
   } else {
     e = cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
-    attn_prefill_kernel<64><<<grid, 128, smem, stream>>>(q, T, pos0, block_table, kv, nq, sc, (__half*)out, out_ld);
+    attn_prefill_kernel<64><<<grid, 128, smem, stream>>>(q, T, pos0, block_table, kv, nq, sc, (__half*)out, out_ld, k_order);
   }
   return launch_status();
+}
+
+// out f16 [T][out_ld] in paired-K order.
+int bonsai_attn_prefill(const float* q, int T, int pos0, const int* block_table, int nq, int nkv, int hd, int kvt, int page_size,
+                        const void* kpool, const void* vpool, const float* kscale, const float* vscale, void* out, int out_ld,
+                        cudaStream_t stream) {
+  return bonsai_attn_prefill_order(q, T, pos0, block_table, nq, nkv, hd, kvt, page_size, kpool, vpool, kscale, vscale, out, out_ld, 0, stream);
 }
 
 }  // extern "C"

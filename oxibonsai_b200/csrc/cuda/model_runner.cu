@@ -45,8 +45,8 @@ int bonsai_attn_decode_qkv_f16(const float*, int, const float*, const float*, fl
                                int, int, int, int, int, int, void*, void*, int, float*, float*, int*, float*, cudaStream_t);
 int bonsai_norm_to_f16_hmma(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
 int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, const float*, void*, int, int, int, int, int, cudaStream_t);
-int bonsai_attn_prefill(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
-                        const float*, void*, int, cudaStream_t);
+int bonsai_attn_prefill_order(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
+                              const float*, void*, int, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
 }
 
@@ -183,9 +183,14 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
 
 enum PrefillPtr {
   PP_TOKENS = 0, PP_POSITIONS, PP_H, PP_XN, PP_QKV, PP_Q, PP_ATTN, PP_ACT, PP_STATUS,
+  PP_SM_ATTN, PP_SM_ACC, PP_SM_ML, PP_SM_CTR,   // small chunks: f32 attention output and split-KV workspace for kSmallChunk rows
   PP_GEMM_WS, PP_GEMM_WS_BYTES,   // workspace of the GEMM's balanced work distribution (pointer, size as a plain integer)
   PP_COUNT
 };
+
+// Chunks of at most this many tokens run like a decode batch (mma.sync GEMMs, split-KV attention); the small-chunk
+// workspace holds kSmallChunk rows of kSmallSplits splits.
+constexpr int kSmallChunk = 32, kSmallSplits = 8;
 
 static inline int pf_gemm(Runner& r, const void* codes, const void* scales, const void* x, int x_ld, float* out_f32, const float* residual,
                           void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld, int sms, const void* dense_w,
@@ -221,36 +226,57 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   const int xn_ld = hidden > qd ? hidden : qd;
   const int* bt = P<int>(sp[SP_BLOCK_TABLE]) + (size_t)slot * r.ic[IC_MAX_PAGES];
 
+  // Chunks of up to 32 tokens (speculative verification, short prompts) run like a decode batch: the packed GEMMs on
+  // mma.sync with register-expanded weights (activations in hmma-K order) and, once the chunk's K/V rows are appended,
+  // the split-KV decode attention with one "sequence" per token (all share the page list; token i sees positions
+  // <= pos0 + i), which spreads a long context over the GPU where the prompt kernel would run one CTA per head.
+  // Larger chunks use the tcgen05 GEMM (paired-K order) and the prompt attention kernel.
+  const bool hm = r.ic[IC_FAST] != 5 && T <= kSmallChunk && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
+  int sm_splits = (4 * 148) / (nkv * T);
+  if (sm_splits < 1) sm_splits = 1;
+  if (sm_splits > kSmallSplits) sm_splits = kSmallSplits;
+  auto to_f16 = [&](const float* w) {
+    return hm ? bonsai_norm_to_f16_hmma(h, hidden, w, r.eps, T, hidden, xn, xn_ld, st)
+              : bonsai_norm_to_f16_paired(h, hidden, w, r.eps, T, hidden, xn, xn_ld, 0, st);
+  };
+  auto gemm = [&](const void* codes, const void* scales, const void* x, int x_ld, float* out_f32, const float* residual, void* out_f16,
+                  int n_rows, int K, int epi, int out_ld) {
+    return hm ? bonsai_bitgemm_hmma(codes, scales, x, x_ld, out_f32, residual, out_f16, n_rows, K, T, epi, out_ld, st)
+              : pf_gemm(r, codes, scales, x, x_ld, out_f32, residual, out_f16, status, n_rows, K, T, epi, out_ld, sms, nullptr, st);
+  };
+
   RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, T, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_ATTN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
-    RC(pf_gemm(r, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, status, qkv_n,
-                              hidden, T, 0, qkv_n, sms, nullptr, st));
+    RC(to_f16(P<float>(lp[LP_ATTN_NORM])));
+    RC(gemm(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, qkv_n, hidden, 0, qkv_n));
     // every row of the chunk uses the same page list: a block-table stride of zero
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
                                   P<float>(r.gp[GP_ROPE_SIN]), positions, bt, 0, q, T, nq, nkv, hd, r.ic[IC_KVT],
                                   r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]),
                                   P<float>(lp[LP_VSCALE]), st));
-    RC(bonsai_attn_prefill(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
-                           P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, st));
-    if (!tp) {
-      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, status, hidden, qd, T, 1,
-                                hidden, sms, nullptr, st));
+    if (hm) {
+      float* attn32 = P<float>(pp[PP_SM_ATTN]);
+      RC(bonsai_attn_decode(q, positions, bt, 0, T, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]),
+                            P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), sm_splits, P<float>(pp[PP_SM_ACC]),
+                            P<float>(pp[PP_SM_ML]), P<int>(pp[PP_SM_CTR]), attn32, 0, st));
+      RC(bonsai_norm_to_f16_hmma(attn32, qd, nullptr, r.eps, T, qd, attn, qd, st));
     } else {
-      RC(pf_gemm(r, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, status, hidden, qd, T,
-                                0, hidden, sms, nullptr, st));
+      RC(bonsai_attn_prefill_order(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]),
+                                   P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, 0, st));
+    }
+    if (!tp) {
+      RC(gemm(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, hidden, qd, 1, hidden));
+    } else {
+      RC(gemm(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, hidden, qd, 0, hidden));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
-    RC(bonsai_norm_to_f16_paired(h, hidden, P<float>(lp[LP_FFN_NORM]), r.eps, T, hidden, xn, xn_ld, 0, st));
-    RC(pf_gemm(r, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, status, 2 * inter,
-                              hidden, T, 2, inter, sms, nullptr, st));
+    RC(to_f16(P<float>(lp[LP_FFN_NORM])));
+    RC(gemm(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
     if (!tp) {
-      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, status, hidden, inter,
-                                T, 1, hidden, sms, nullptr, st));
+      RC(gemm(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
     } else {
-      RC(pf_gemm(r, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, status, hidden,
-                                inter, T, 0, hidden, sms, nullptr, st));
+      RC(gemm(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, hidden, inter, 0, hidden));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
     }
   }
@@ -410,5 +436,8 @@ int bonsai_runner_prefill_chunk(void* r, const uint64_t* step_ptrs, const uint64
 int bonsai_runner_decode_step(void* r, const uint64_t* step_ptrs, int batch, int flags, int mask_words, cudaStream_t stream) {
   return bonsai::decode_step(*static_cast<bonsai::Runner*>(r), step_ptrs, batch, flags, mask_words, stream);
 }
+
+int bonsai_runner_small_chunk() { return bonsai::kSmallChunk; }
+int bonsai_runner_small_splits() { return bonsai::kSmallSplits; }
 
 }  // extern "C"

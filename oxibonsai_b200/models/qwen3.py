@@ -307,9 +307,13 @@ class Qwen3Runner:
              "qkv": torch.zeros((chunk, (nq + 2 * nkv) * hd), **f32), "q": torch.zeros((chunk, nq, hd), **f32),
              "attn": torch.zeros((chunk, qd), **f16), "act": torch.zeros((chunk, w.inter_local), **f16),
              "status": torch.zeros(1, **i32), "gemm_ws": getattr(self, "_gemm_ws", None)}
+        # chunks of up to `sm` tokens run like a decode batch: f32 attention rows and the split-KV workspace for them
+        sm, ss = K._pf().bonsai_runner_small_chunk(), K._pf().bonsai_runner_small_splits()
+        b.update({"sm_attn": torch.zeros((sm, qd), **f32), "sm_acc": torch.zeros((sm, nq, ss, hd), **f32),
+                  "sm_ml": torch.zeros((sm, nq, ss, 2), **f32), "sm_ctr": torch.zeros(sm * max(1, nkv), **i32)})
         if b["gemm_ws"] is None:
             b["gemm_ws"] = self._gemm_ws = K.new_gemm_workspace(dev)
-        order = ["tokens", "positions", "h", "xn", "qkv", "q", "attn", "act", "status", "gemm_ws"]
+        order = ["tokens", "positions", "h", "xn", "qkv", "q", "attn", "act", "status", "sm_attn", "sm_acc", "sm_ml", "sm_ctr", "gemm_ws"]
         assert len(order) + 1 == K._pf().bonsai_runner_prefill_ptr_count()
         b["ptrs"] = (C.c_uint64 * (len(order) + 1))(*[b[k].data_ptr() for k in order], b["gemm_ws"].numel())
         self._pf = b
@@ -344,8 +348,10 @@ class Qwen3Runner:
         return K.sample(logits)
 
     def prefill_launches(self, n_tokens: int, chunk: int = 1024) -> int:
-        chunks = -(-n_tokens // chunk)
-        return chunks * (1 + 8 * self.cfg.layers) + 2
+        full, tail = divmod(n_tokens, chunk)
+        small = K._pf().bonsai_runner_small_chunk()
+        per_chunk = lambda t: 1 + (9 if t <= small else 8) * self.cfg.layers     # small chunks convert the f32 attention rows separately
+        return full * per_chunk(chunk) + (per_chunk(tail) if tail else 0) + 2
 
     def set_comm(self, comm_handle: int) -> None:
         K.lib().bonsai_runner_set_comm(self._native, comm_handle)

@@ -420,6 +420,8 @@ _PF_SIG = {
     "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_runner_prefill_ptr_count": [],
+    "bonsai_runner_small_chunk": [],
+    "bonsai_runner_small_splits": [],
     "bonsai_runner_prefill_chunk": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "bonsai_runner_decode_step_batched": [_vp, _vp, _vp, _i, _i, _i, _vp],
 }
