@@ -418,6 +418,7 @@ _PF_SIG = {
     "bonsai_norm_to_f16_hmma": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _vp],
     "bonsai_norm_to_f16_paired": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _i, _vp],
     "bonsai_attn_prefill": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+    "bonsai_attn_prefill_order": [_vp, _i, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "bonsai_embed_rows_f16": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "bonsai_runner_prefill_ptr_count": [],
     "bonsai_runner_small_chunk": [],
@@ -557,11 +558,13 @@ def bitgemm_prefill(w: PlanarWeight, x_paired: torch.Tensor, epi: int = 0, resid
 
 
 def attn_prefill(q: torch.Tensor, pos0: int, block_table_row: torch.Tensor, nq, nkv, hd, kvt, page_size, kpool, vpool, kscale=None,
-                 vscale=None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal attention of a T-token chunk (q f32 [T, nq, hd]) over the sequence's pages; returns f16 [T, nq*hd] (paired-K)."""
+                 vscale=None, out: torch.Tensor | None = None, k_order: int = 0) -> torch.Tensor:
+    """Causal attention of a T-token chunk (q f32 [T, nq, hd]) over the sequence's pages; returns f16 [T, nq*hd] in paired-K
+    order (``k_order`` 0, the tcgen05 GEMM's operand order) or hmma-K order (1, the mma.sync GEMM's)."""
     T = q.shape[0]
     if out is None:
         out = torch.empty((T, nq * hd), dtype=torch.float16, device=q.device)
-    check(_pf().bonsai_attn_prefill(q.data_ptr(), T, pos0, block_table_row.data_ptr(), nq, nkv, hd, kvt, page_size, kpool.data_ptr(),
-                                    vpool.data_ptr(), ptr(kscale), ptr(vscale), out.data_ptr(), out.stride(0), stream()), "attn_prefill")
+    check(_pf().bonsai_attn_prefill_order(q.data_ptr(), T, pos0, block_table_row.data_ptr(), nq, nkv, hd, kvt, page_size, kpool.data_ptr(),
+                                          vpool.data_ptr(), ptr(kscale), ptr(vscale), out.data_ptr(), out.stride(0), k_order, stream()),
+          "attn_prefill")
     return out

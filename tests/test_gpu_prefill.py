@@ -106,6 +106,9 @@ def test_attn_prefill_matches_reference(kvt, tol, nq, nkv, hd, T, pos0):
     sc_ = sc_.masked_fill(~mask[None], float("-inf"))
     ref = torch.einsum("nts,snd->tnd", torch.softmax(sc_, -1), vv)
     assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    if (nq * hd) % 128 == 0:        # the same rows in the K order of the mma.sync GEMM
+        out_h = K.attn_prefill(q.to(DEV), pos0, bt, nq, nkv, hd, kvt, page, kpool, vpool, ksc, vsc, k_order=1)
+        assert torch.equal(out_h.cpu()[:, K.hmma_k_index(nq * hd)], out.cpu()[:, perm])
 
 
 @pytest.mark.parametrize("rows,cols,T", [(151936, 2048, 3), (1000, 4096, 64), (300, 256, 200)])
