@@ -57,11 +57,13 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
 
 // Stage rows [t0, t0+64) of one kv head into shared memory as f16 [64][HD + 8].
 template <int HD>
-__device__ __forceinline__ void stage_kv(__half* dst, const uint8_t* pool, const float* scales, const PfKvPool& kv, const int* bt,
-                                         int kvh, int t0, int t_end) {
+__device__ __forceinline__ void stage_kv(__half* __restrict__ dst, const uint8_t* __restrict__ pool, const float* __restrict__ scales,
+                                         const PfKvPool& kv, const int* __restrict__ bt, int kvh, int t0, int t_end) {
   constexpr int LD = HD + 8;
-  // 64 rows x HD/8 chunks of eight elements
-  for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += blockDim.x) {
+  // 64 rows x HD/8 chunks of eight elements; the block has 128 threads
+#pragma unroll 4
+  for (int i = 0; i < 64 * (HD / 8) / 128; ++i) {
+    const int idx = threadIdx.x + i * 128;
     const int r = idx / (HD / 8), c8 = (idx % (HD / 8)) * 8;
     const int t = t0 + r;
     __half h[8];
@@ -96,22 +98,59 @@ __device__ __forceinline__ void stage_kv(__half* dst, const uint8_t* pool, const
   }
 }
 
-// grid (ceil(T/64), nq); block 128.  Query row i of the chunk sits at absolute position pos0 + i.
+__device__ __forceinline__ void pf_cp_async16(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void pf_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void pf_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// f16 pages: rows [t0, t0+64) of one kv head go straight from the pool into shared memory with 16-byte asynchronous copies
+// (rows past t_end are zero-filled), all of a thread's copies in flight at once.
+template <int HD>
+__device__ __forceinline__ void stage_kv_async(__half* dst, const __half* pool, const PfKvPool& kv, const int* __restrict__ bt, int kvh,
+                                               int t0, int t_end) {
+  constexpr int LD = HD + 8;
+#pragma unroll
+  for (int i = 0; i < 64 * (HD / 8) / 128; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    const int r = idx / (HD / 8), c8 = (idx % (HD / 8)) * 8;
+    const int t = t0 + r;
+    const bool ok = t < t_end;
+    const int page = ok ? bt[t / kv.page_size] : 0;
+    const size_t row = ((size_t)page * kv.kv_heads + kvh) * kv.page_size + (ok ? t % kv.page_size : 0);
+    pf_cp_async16(dst + r * LD + c8, pool + row * HD + c8, ok ? 16 : 0);
+  }
+}
+
+__device__ __forceinline__ float pf_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// grid (nq, ceil(T/64)); block 128.  Query row i of the chunk sits at absolute position pos0 + i.
 template <int HD>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restrict__ q, int T, int pos0, const int* __restrict__ bt,
                                                           PfKvPool kv, int nq, float sm_scale, __half* __restrict__ out, int out_ld,
                                                           int k_order) {
   constexpr int LD = HD + 8;
-  extern __shared__ __half smem_h[];
-  __half* sQ = smem_h;             // [64][LD]
-  __half* sK = sQ + 64 * LD;       // [64][LD]
-  __half* sV = sK + 64 * LD;       // [64][LD]
-  const int qb = blockIdx.x, head = blockIdx.y;
+  extern __shared__ __align__(16) __half smem_h[];
+  // four regions of [64][LD]: K and V tiles of two stages.  The scaled queries are staged through region 0 and live in
+  // registers from then on, so the first K tile may overwrite them.
+  __half* sQ = smem_h;
+  auto stage_k = [&](int st) { return smem_h + (2 * st) * 64 * LD; };
+  auto stage_v = [&](int st) { return smem_h + (2 * st + 1) * 64 * LD; };
+  // blocks are dispatched in linear order: the query blocks with the most keys (the last ones) go first, the short ones
+  // fill the tail of the grid
+  const int qb = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int kvh = head / (nq / kv.kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = qb * 64;
 
-  // stage Q (scaled) as f16
+  // stage Q as f16, scaled by sm_scale * log2(e): the softmax below works in base 2 (one ex2 per score, no multiply)
+  sm_scale *= 1.4426950408889634f;
   for (int idx = threadIdx.x; idx < 64 * (HD / 4); idx += blockDim.x) {
     const int r = idx / (HD / 4), c4 = (idx % (HD / 4)) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -135,11 +174,27 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
   const int row0 = q0 + warp * 16 + (lane >> 2), row1 = row0 + 8;   // chunk-relative query rows of this thread
   const int kv_end = min(pos0 + q0 + 64, pos0 + T);                  // keys needed by this query block
 
-  for (int kb = 0; kb < kv_end; kb += 64) {
+  // Tile it + 1 is requested before tile it is used: asynchronous copies for f16 pages (they land while the MMAs of the
+  // current tile run), register staging with conversion for the other page formats.
+  auto fetch = [&](int kb, int st) {
+    if (kv.kvt == 1) {
+      stage_kv_async<HD>(stage_k(st), reinterpret_cast<const __half*>(kv.k), kv, bt, kvh, kb, kv_end);
+      stage_kv_async<HD>(stage_v(st), reinterpret_cast<const __half*>(kv.v), kv, bt, kvh, kb, kv_end);
+    } else {
+      stage_kv<HD>(stage_k(st), kv.k, kv.k_scale, kv, bt, kvh, kb, kv_end);
+      stage_kv<HD>(stage_v(st), kv.v, kv.v_scale, kv, bt, kvh, kb, kv_end);
+    }
+  };
+  __syncthreads();             // every warp has its query fragments: region 0 is free
+  fetch(0, 0);
+  pf_cp_commit();
+  for (int kb = 0, it = 0; kb < kv_end; kb += 64, ++it) {
+    if (kb + 64 < kv_end) fetch(kb + 64, (it + 1) & 1);   // that stage was released by the barrier that ended iteration it - 1
+    pf_cp_commit();
+    pf_cp_wait<1>();           // everything but the newest group: tile it has landed
     __syncthreads();
-    stage_kv<HD>(sK, kv.k, kv.k_scale, kv, bt, kvh, kb, kv_end);
-    stage_kv<HD>(sV, kv.v, kv.v_scale, kv, bt, kvh, kb, kv_end);
-    __syncthreads();
+    const __half* sK = stage_k(it & 1);
+    const __half* sV = stage_v(it & 1);
     // S = Q K^T : 16 x 64 per warp -> 8 n-tiles of 8 keys
     float s[8][4];
 #pragma unroll
@@ -156,17 +211,23 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
         mma16816(s[2 * np + 1], qf[ks], b2, b3);
       }
     }
-    // causal mask + online softmax (rows row0 and row1 of this thread)
+    // causal mask + online softmax (rows row0 and row1 of this thread).  Only tiles that reach past the first query row
+    // of this warp (the diagonal, and the zero-filled keys after the last one) need the mask.
     float mx0 = m0, mx1 = m1;
+    if (kb + 63 > pos0 + q0 + warp * 16) {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int qrow = (e < 2) ? row0 : row1;
+          const bool ok = key <= pos0 + qrow && qrow < T;
+          if (!ok) s[nt][e] = -INFINITY;
+        }
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = kb + nt * 8 + (lane & 3) * 2 + (e & 1);
-        const int qrow = (e < 2) ? row0 : row1;
-        const bool ok = key <= pos0 + qrow && qrow < T;
-        if (!ok) s[nt][e] = -INFINITY;
-      }
       mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
       mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
     }
@@ -174,13 +235,15 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float r0 = (mx0 == -INFINITY) ? 1.0f : __expf(m0 - mx0), r1 = (mx1 == -INFINITY) ? 1.0f : __expf(m1 - mx1);
+    // a row with nothing visible yet (rows past T) keeps max = -inf; subtracting 0 instead leaves every term ex2(-inf) = 0
+    const float e0 = (mx0 == -INFINITY) ? 0.0f : mx0, e1 = (mx1 == -INFINITY) ? 0.0f : mx1;
+    const float r0 = pf_ex2(m0 - e0), r1 = pf_ex2(m1 - e1);
     float ps0 = 0.0f, ps1 = 0.0f;
     uint32_t pf[8][2];   // P as f16 pairs: [n-tile][row0 pair, row1 pair]
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      float p0 = (mx0 == -INFINITY) ? 0.0f : __expf(s[nt][0] - mx0), p1 = (mx0 == -INFINITY) ? 0.0f : __expf(s[nt][1] - mx0);
-      float p2 = (mx1 == -INFINITY) ? 0.0f : __expf(s[nt][2] - mx1), p3 = (mx1 == -INFINITY) ? 0.0f : __expf(s[nt][3] - mx1);
+      const float p0 = pf_ex2(s[nt][0] - e0), p1 = pf_ex2(s[nt][1] - e0);
+      const float p2 = pf_ex2(s[nt][2] - e1), p3 = pf_ex2(s[nt][3] - e1);
       ps0 += p0 + p1;
       ps1 += p2 + p3;
       __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
@@ -208,7 +271,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
         mma16816(o[2 * np + 1], a, b2, b3);
       }
     }
+    __syncthreads();           // all warps are done with this stage before the next iteration refills it
   }
+  pf_cp_wait<0>();
   // the row sums are spread over the four lanes that share a row
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -244,9 +309,9 @@ int bonsai_attn_prefill_order(const float* q, int T, int pos0, const int* block_
   if (k_order < 0 || k_order > 1 || (k_order == 1 && (nq * hd) % 128 != 0)) return BONSAI_CUDA_BAD_ARG;
   if (T < 1 || (hd != 64 && hd != 128) || nq % nkv != 0 || kvt < 0 || kvt > 3) return BONSAI_CUDA_BAD_ARG;
   PfKvPool kv{(const uint8_t*)kpool, (const uint8_t*)vpool, kscale, vscale, page_size, nkv, hd, kvt};
-  dim3 grid((T + 63) / 64, nq);
+  dim3 grid(nq, (T + 63) / 64);
   const float sc = 1.0f / sqrtf((float)hd);
-  size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(__half);
+  size_t smem = (size_t)4 * 64 * (hd + 8) * sizeof(__half);
   cudaError_t e;
   if (hd == 128) {
     e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
