@@ -71,7 +71,7 @@ def weight_copies(K, rows, cols, dev, budget=400e6):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemv", "gemm", "lmhead", "attn"])
+    ap.add_argument("case", choices=["gemv", "gemm", "lmhead", "attn", "attn_prefill"])
     ap.add_argument("--fast", default="warp", help="0 (exact f32), warp, tile, hmma or mma")
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -144,7 +144,7 @@ def main() -> None:
         byts, fl = n * k * 2.0, 2.0 * n * k * T
         rows_out.append({"case": "lmhead", "tokens": T, "us": round(us, 2), "TFLOP/s": round(fl / us / 1e6, 1),
                          f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3), "status": int(status.item())})
-    else:
+    elif a.case == "attn":
         nq, nkv, hd, page = 32, 8, 128, 64
         kvt = {"f32": K.KV_F32, "f16": K.KV_F16, "q8": K.KV_Q8, "q4": K.KV_Q4}[a.kv]
         B, ctx = a.batch, a.ctx
@@ -177,6 +177,31 @@ def main() -> None:
         byts = 2.0 * B * ctx * nkv * hd * elt
         rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "nsplit": a.nsplit, "us": round(us, 2),
                          "GB/s": round(byts / us / 1e3, 1), f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})
+    elif a.case == "attn_prefill":
+        # one prompt chunk of --tokens queries whose first token sits at position --ctx (8B head layout, f16 / --kv pages)
+        nq, nkv, hd, page = 32, 8, 128, 64
+        kvt = {"f32": K.KV_F32, "f16": K.KV_F16, "q8": K.KV_Q8, "q4": K.KV_Q4}[a.kv]
+        T, pos0 = a.tokens, a.ctx
+        pps = (pos0 + T + page - 1) // page
+        row = hd // 2 if kvt == K.KV_Q4 else hd
+        kp = torch.empty((pps, nkv, page, row), dtype=K.KV_DTYPES[kvt], device=dev)
+        vp = torch.empty_like(kp)
+        if kp.dtype.is_floating_point:
+            kp.normal_()
+            vp.normal_()
+        else:
+            kp.random_(0, 127)
+            vp.random_(0, 127)
+        ks, vs = ((torch.rand((pps, nkv, page), device=dev) * 0.01, torch.rand((pps, nkv, page), device=dev) * 0.01) if kvt >= 2 else (None, None))
+        bt = torch.arange(pps, dtype=torch.int32, device=dev)
+        q = torch.randn((T, nq, hd), device=dev)
+        out = torch.empty((T, nq * hd), dtype=torch.float16, device=dev)
+
+        def fn():
+            K.attn_prefill(q, pos0, bt, nq, nkv, hd, kvt, page, kp, vp, ks, vs, out=out)
+        us = time_us(fn, a.iters, a.profile)
+        flops = 4.0 * T * (pos0 + (T + 1) / 2.0) * hd * nq            # QK^T and PV over the causal part
+        rows_out.append({"case": f"attn_prefill/{a.kv}", "tokens": T, "pos0": pos0, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1)})
     for r in rows_out:
         print(json.dumps(r))
 

@@ -132,7 +132,7 @@ __device__ __forceinline__ float pf_ex2(float x) {
 
 // grid (nq, ceil(T/64)); block 128.  Query row i of the chunk sits at absolute position pos0 + i.
 template <int HD>
-__global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restrict__ q, int T, int pos0, const int* __restrict__ bt,
+__global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const float* __restrict__ q, int T, int pos0, const int* __restrict__ bt,
                                                           PfKvPool kv, int nq, float sm_scale, __half* __restrict__ out, int out_ld,
                                                           int k_order) {
   constexpr int LD = HD + 8;
@@ -315,6 +315,9 @@ int bonsai_attn_prefill_order(const float* q, int T, int pos0, const int* block_
   cudaError_t e;
   if (hd == 128) {
     e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // three CTAs of 68 KB per SM need the largest shared-memory carve-out; the default picks a smaller one that fits two
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
     attn_prefill_kernel<128><<<grid, 128, smem, stream>>>(q, T, pos0, block_table, kv, nq, sc, (__half*)out, out_ld, k_order);
   } else {
