@@ -42,7 +42,8 @@ class SamplerBuilder:
 
 
 class EngineBuilder:
-    """Collects engine options; ``build()`` loads the checkpoint and returns an ``InferenceEngine``."""
+    """Collects engine options; ``build()`` loads the checkpoint and returns an ``InferenceEngine`` (Q1_0_g128 / TQ2_0_g128
+    weights) or a ``GenericFormatEngine`` (any other block format)."""
 
     def __init__(self):
         self._model_path: str | None = None
@@ -101,5 +102,5 @@ class EngineBuilder:
     def build(self):
         if not self._model_path:
             raise ValueError("EngineBuilder: model_path is required")
-        from .engine import InferenceEngine
-        return InferenceEngine(**self.options())
+        from .engine import load_engine
+        return load_engine(**self.options())     # the sub-2-bit runner, or the generic-format engine for other weight types

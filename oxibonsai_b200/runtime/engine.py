@@ -327,3 +327,100 @@ class InferenceEngine:
         return {"name": c.name, "arch": c.arch, "layers": c.layers, "hidden": c.hidden, "heads": c.heads, "kv_heads": c.kv_heads,
                 "head_dim": c.head_dim, "intermediate": c.inter, "vocab": c.vocab, "context": c.context,
                 "weight_bytes": self.weights.packed_bytes, "kv_bytes": self.kv.nbytes, "load_seconds": self.load_seconds}
+
+
+def layer_weight_type(gguf: GgufFile) -> int:
+    """GGUF type id of the first layer's attention projection (fused or split): what decides the GPU path of a checkpoint."""
+    for name in ("blk.0.attn_q.weight", "blk.0.attn_qkv.weight", "blk.0.ffn_down.weight"):
+        if gguf.has_tensor(name):
+            return gguf.tensor_info(name).type
+    raise ValueError("checkpoint has no blk.0 attention or FFN weights")
+
+
+class GenericFormatEngine:
+    """Engine for checkpoints whose layer weights are stored in a block format without a planar repack (Q4_0, Q8_0, FP8,
+    K-quants, 256-wide TQ2_0, F16 / BF16 / F32).
+
+    Reference counterpart: the same ``InferenceEngine`` serves every format through per-format forward paths
+    (crates/oxibonsai-model/src/model/types/forward_cuda/q_std.rs, k_quant.rs, forward_cuda_fp8.rs).  Here the
+    sub-2-bit formats have their own runner (``InferenceEngine``) and everything else goes through
+    ``models.qwen3_generic.GenericQwen3Engine``; this class gives it the single-stream part of the engine surface
+    (``generate`` / ``generate_stream`` / ``generate_seeded`` / ``model_info`` / ``last_stats``).  One request at a time:
+    calls are serialised by a lock, as the reference's server does around its engine."""
+
+    def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
+                 device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
+                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None):
+        import threading
+        from ..models.qwen3_generic import GenericQwen3Engine
+        if tp_size != 1:
+            raise NotImplementedError("tensor parallelism covers the Q1_0_g128 / TQ2_0_g128 runner only")
+        kv = {"fp32": "f32", "fp16": "f16", "int8": "q8", "int4": "q4"}.get(kv_dtype.lower(), kv_dtype.lower())
+        t0 = time.perf_counter()
+        self.sampling = (sampling or SamplingPreset.BALANCED.params()).validate()
+        self._eng = GenericQwen3Engine(str(model_path), max_seq_len=int(max_seq_len), kv_dtype=kv, device=str(device), page_size=page_size,
+                                       sampling=self.sampling)
+        self.load_seconds = time.perf_counter() - t0
+        self.model_path, self.device = str(model_path), self._eng.device
+        self.gguf, self.config = self._eng.gguf, self._eng.config
+        self.max_seq_len, self.max_batch = int(max_seq_len), 1
+        self.last_stats = GenerationStats()
+        self._lock = threading.Lock()
+        if warmup:
+            self.warmup()
+
+    def warmup(self) -> None:
+        """Captures the decode graph (one throw-away token) so that the first request does not pay for it."""
+        with self._lock:
+            self._eng.generate([0], 1, SamplingPreset.GREEDY.params(), stop_at_eos=False)
+
+    def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
+                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None) -> Iterator[int]:
+        p = (params or self.sampling).validate()
+        max_new = p.max_tokens if max_tokens is None else max_tokens
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            return
+        stats = GenerationStats(prompt_tokens=len(prompt))
+        self.last_stats = stats
+        max_new = max(0, min(max_new, self.max_seq_len - len(prompt)))
+        with self._lock:
+            t0 = time.perf_counter()
+            first = True
+            for tok in self._eng.generate_stream(prompt, max_new, p, stop_at_eos):
+                now = time.perf_counter()
+                if first:
+                    stats.prefill_seconds, t0, first = now - t0, now, False
+                stats.generated_tokens += 1
+                stats.token_times.append(now)
+                if on_token is not None:
+                    on_token(tok)
+                yield tok
+            stats.decode_seconds = time.perf_counter() - t0 if not first else 0.0
+
+    def generate(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
+                 stop_at_eos: bool = True) -> list[int]:
+        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos))
+
+    def generate_seeded(self, prompt: Sequence[int], max_tokens: int, seed: int, params: SamplingParams | None = None) -> list[int]:
+        from dataclasses import replace
+        return self.generate(prompt, max_tokens, replace(params or self.sampling, seed=seed))
+
+    def model_info(self) -> dict:
+        from ..core import gguf as G
+        from ..models.qwen3_generic import _Linear
+        c, e = self.config, self._eng
+        weight_bytes = sum(w.data.numel() for layer in e.layers for w in layer.values() if isinstance(w, _Linear))
+        return {"name": c.name, "arch": c.arch, "layers": c.layers, "hidden": c.hidden, "heads": c.heads, "kv_heads": c.kv_heads,
+                "head_dim": c.head_dim, "intermediate": c.inter, "vocab": c.vocab, "context": c.context, "weight_bytes": int(weight_bytes),
+                "kv_bytes": int(e.kpool.numel() * e.kpool.element_size() * 2), "load_seconds": self.load_seconds,
+                "weight_format": G.type_info(layer_weight_type(self.gguf))[0]}
+
+
+def load_engine(model_path: str, **options):
+    """``InferenceEngine`` for Q1_0_g128 / TQ2_0_g128 checkpoints, ``GenericFormatEngine`` for every other weight format."""
+    from ..core import gguf as G
+    with_type = layer_weight_type(GgufFile.open(str(model_path)))
+    if with_type in (G.TQ2_0_G128, G.Q1_0_G128):
+        return InferenceEngine(str(model_path), **options)
+    return GenericFormatEngine(str(model_path), **options)

@@ -26,7 +26,7 @@ def main(argv: list[str] | None = None) -> int:
     from ..runtime.presets import SamplingParams
     from ..runtime.scheduler import BatchScheduler
     from ..tokenizer import load_tokenizer
-    from .app import SchedulerBackend, create_app
+    from .app import SchedulerBackend, SerialBackend, create_app
     from .config import load_config
     cfg = load_config(sys.argv[1:] if argv is None else argv)
     if cfg.model_path is None:
@@ -41,16 +41,22 @@ def main(argv: list[str] | None = None) -> int:
                         max_tokens=cfg.max_tokens, seed=cfg.seed)
     engine = (EngineBuilder().model_path(cfg.model_path).sampler(sp).max_seq_len(cfg.max_seq_len).max_batch(cfg.max_concurrent)
               .kv_cache(cfg.kv_cache).build())
-    if not engine.exact:
-        engine.enable_prefix_cache()
-    sched = BatchScheduler(engine, queue_capacity=cfg.queue_capacity).start()
-    app = create_app(SchedulerBackend(sched, engine.config.name), tokenizer, cfg)
+    sched = None
+    if hasattr(engine, "open_sequence"):          # the sub-2-bit runner: continuous batching over its sequence slots
+        if not engine.exact:
+            engine.enable_prefix_cache()
+        sched = BatchScheduler(engine, queue_capacity=cfg.queue_capacity).start()
+        backend = SchedulerBackend(sched, engine.config.name)
+    else:                                         # generic block formats: one request at a time
+        backend = SerialBackend(engine, engine.config.name)
+    app = create_app(backend, tokenizer, cfg)
     print(banner(cfg, engine.model_info()), file=sys.stderr)
     import uvicorn
     try:
         uvicorn.run(app, host=cfg.host, port=cfg.port, log_level=cfg.log_level if cfg.log_level in ("debug", "info", "warning", "error") else "info")
     finally:
-        sched.stop()
+        if sched is not None:
+            sched.stop()
     return 0
 
 

@@ -60,6 +60,54 @@ class SchedulerBackend:
         return self.s.engine.kv.utilization
 
 
+class SerialBackend:
+    """Backend over an engine that serves one request at a time (``runtime.engine.GenericFormatEngine``, or anything with a
+    ``generate_stream(prompt, max_tokens, params, stop_at_eos)`` generator): every request gets a worker thread and the
+    engine's own lock serialises them, which is how the reference serves all requests (one engine behind a mutex,
+    crates/oxibonsai-runtime/src/server.rs).  Returns the scheduler's ``Request`` object, so the routes treat both backends alike."""
+
+    def __init__(self, engine, model_name: str):
+        self.engine = engine
+        self.model_name = model_name
+        self.max_seq_len = engine.max_seq_len
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id):
+        from ..runtime.scheduler import Request as Job
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + 1 > self.max_seq_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens does not fit max_seq_len {self.max_seq_len}")
+        r = Job(list(prompt), params.validate(), max_tokens, on_token=on_token, request_id=request_id, t_submit=time.perf_counter())
+
+        def run():
+            try:
+                for tok in self.engine.generate_stream(r.prompt, r.max_tokens, r.params, r.stop_at_eos):
+                    now = time.perf_counter()
+                    if r.t_first_token is None:
+                        r.t_first_token = now
+                    r.tokens.append(tok)
+                    r.token_times.append(now)
+                    if r.on_token is not None:
+                        r.on_token(tok)
+                    if r.cancelled:
+                        r.finish_reason = "cancelled"
+                        break
+                if r.finish_reason is None:
+                    r.finish_reason = "length" if len(r.tokens) >= r.max_tokens else "stop"
+            except Exception as e:          # surfaced by Request.wait()
+                r.error = e
+                r.finish_reason = "error"
+            finally:
+                r.t_done = time.perf_counter()
+                r.done.set()
+
+        threading.Thread(target=run, name=f"serial-{request_id[:8]}", daemon=True).start()
+        return r
+
+    def kv_utilization(self) -> float:
+        return 0.0
+
+
 def new_request_id() -> str:
     return uuid.uuid4().hex
 

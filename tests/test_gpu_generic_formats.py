@@ -101,3 +101,23 @@ def test_generic_engine_tensor_core_prompt_path_matches_token_by_token(fmt, tiny
     kb = fast.kpool[:, : (n + 63) // 64].float()
     assert torch.allclose(ka, kb, rtol=2e-2, atol=2e-2)
     assert len(a) == 1 and len(b) == 1
+
+
+def test_engine_builder_routes_checkpoints_by_weight_format(tiny_gguf, tmp_path):
+    from oxibonsai_b200 import cli
+    from oxibonsai_b200.models.qwen3_generic import GenericQwen3Engine
+    from oxibonsai_b200.runtime import EngineBuilder, SamplingPreset
+    from oxibonsai_b200.runtime.engine import GenericFormatEngine, InferenceEngine
+    path = str(tmp_path / "tiny_q8_0.gguf")
+    cli.requantize_gguf(tiny_gguf, path, "q8_0")
+    eng = EngineBuilder().model_path(path).preset("greedy").max_seq_len(128).kv_cache("f32").build()
+    assert isinstance(eng, GenericFormatEngine)
+    prompt = [11, 257, 3, 999, 42, 7, 100, 5]
+    got = eng.generate(prompt, 6, stop_at_eos=False)
+    want = GenericQwen3Engine(path, max_seq_len=128, kv_dtype="f32").generate(prompt, 6, SamplingPreset.GREEDY.params(), stop_at_eos=False)
+    assert got == want and len(got) == 6
+    assert eng.last_stats.prompt_tokens == 8 and eng.last_stats.generated_tokens == 6 and eng.last_stats.decode_tokens_per_second > 0
+    info = eng.model_info()
+    assert info["weight_format"].upper().startswith("Q8_0") and info["weight_bytes"] > 0 and info["layers"] == 2
+    assert eng.generate_seeded(prompt, 4, seed=7) == eng.generate_seeded(prompt, 4, seed=7)
+    assert isinstance(EngineBuilder().model_path(tiny_gguf).max_seq_len(64).build(), InferenceEngine)

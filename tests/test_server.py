@@ -199,3 +199,68 @@ def test_cors_preflight_kv_policy_and_request_log(client, caplog):
     client.app.state.cors.allowed_origins = ("https://only.example",)
     r = client.options("/v1/models", headers={"origin": "https://evil.example"})
     assert r.status_code == 403 and "access-control-allow-origin" not in r.headers
+
+
+class _OneAtATimeEngine:
+    """A ``generate_stream`` engine that fails if two requests ever overlap (what the serial backend has to prevent)."""
+
+    max_seq_len = 64
+
+    def __init__(self, reply=b"serial ok"):
+        self.reply, self.lock, self.busy, self.overlaps, self.calls = reply, threading.Lock(), 0, 0, []
+
+    def generate_stream(self, prompt, max_tokens, params, stop_at_eos=True):
+        with self.lock:
+            self.busy += 1
+            self.overlaps += self.busy > 1
+            self.calls.append((list(prompt), max_tokens, params.temperature))
+            try:
+                for b in self.reply[:max_tokens]:
+                    yield b
+            finally:
+                self.busy -= 1
+
+
+def test_serial_backend_serves_single_request_engines():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import SerialBackend, create_app
+    eng = _OneAtATimeEngine()
+    be = SerialBackend(eng, "generic-q8")
+    assert be.max_seq_len == 64 and be.kv_utilization() == 0.0
+    # direct: tokens, finish reasons, cancellation, argument checks
+    r = be.submit([1, 2, 3], SamplingParams(temperature=0.0), 4, None, "a" * 32)
+    assert bytes(r.wait(5)) == b"seri" and r.finish_reason == "length" and r.ttft is not None
+    r = be.submit([1], SamplingParams(), 50, None, "b" * 32)
+    assert bytes(r.wait(5)) == b"serial ok" and r.finish_reason == "stop"
+    seen, box, ready = [], {}, threading.Event()
+
+    def cancel_after_first(t):
+        seen.append(t)
+        ready.wait(5)                 # the request object exists only once submit() has returned
+        box["r"].cancel()
+    box["r"] = r = be.submit([1], SamplingParams(), 50, cancel_after_first, "c" * 32)
+    ready.set()
+    r.wait(5)
+    assert r.finish_reason == "cancelled" and len(seen) == 1
+    with pytest.raises(ValueError):
+        be.submit([], SamplingParams(), 4, None, "d" * 32)
+    with pytest.raises(ValueError):
+        be.submit(list(range(64)), SamplingParams(), 4, None, "e" * 32)
+    # an engine error reaches the waiter
+    class Broken(_OneAtATimeEngine):
+        def generate_stream(self, *a, **k):
+            raise RuntimeError("boom")
+            yield 0
+    bad = SerialBackend(Broken(), "x").submit([1], SamplingParams(), 4, None, "f" * 32)
+    with pytest.raises(RuntimeError):
+        bad.wait(5)
+    # through the HTTP routes, several requests at once: all answered, never two inside the engine
+    c = TestClient(create_app(be, ByteTokenizer(), ServerConfig()))
+    out = []
+    def ask():
+        out.append(c.post("/v1/completions", json={"prompt": "hi", "max_tokens": 32}).json()["choices"][0]["text"])
+    ts = [threading.Thread(target=ask) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert out == ["serial ok"] * 4 and eng.overlaps == 0
+    assert c.get("/v1/models").json()["data"][0]["id"] == "generic-q8"
