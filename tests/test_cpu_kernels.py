@@ -73,3 +73,30 @@ def test_dispatcher_on_cpu():
     assert np.allclose(d.gemv(G.Q1_0_G128, q, 64, 256, x), cpu_gemv(G.Q1_0_G128, q, 64, 256, x), rtol=1e-4, atol=1e-5)
     assert d.gemm(G.Q1_0_G128, q, 64, 256, x[None]).shape == (1, 64) and "threads=" in d.describe() and d.gpu_fallbacks == 0
     assert CK.KernelDispatcher.auto_detect().tier in tuple(CK.KernelTier) and CK.GpuWeightHandle(3).id == 3
+
+
+def test_vector_tiers_agree_with_the_reference_tier_on_random_shapes():
+    """Property test: every vector tier against tier 0 over random shapes, scales and sparsity (edge rows, all-zero blocks)."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=25, deadline=None)
+    @given(ty=st.sampled_from([G.TQ2_0_G128, G.Q1_0_G128]), rows=st.integers(1, 70), blocks=st.integers(1, 8),
+           scale=st.floats(1e-3, 10.0), zero_frac=st.floats(0.0, 1.0), seed=st.integers(0, 2**31 - 1))
+    def check(ty, rows, blocks, scale, zero_frac, seed):
+        rng = np.random.default_rng(seed)
+        cols = 128 * blocks
+        w = (rng.normal(size=(rows, cols)) * scale).astype(np.float32)
+        w[rng.random(size=w.shape) < zero_frac] = 0.0
+        q = quantize(ty, w)
+        x = rng.normal(size=cols).astype(np.float32)
+        ref = CK.gemv(ty, q, rows, cols, x, CK.KernelTier.REFERENCE, threads=1)
+        tol = 1e-4 * max(1.0, float(np.abs(ref).max()))
+        for tier in (CK.KernelTier.AVX2, CK.KernelTier.AVX512):
+            if tier <= CK.detect_tier():
+                assert np.abs(CK.gemv(ty, q, rows, cols, x, tier, threads=2) - ref).max() <= tol
+        xb = rng.normal(size=(3, cols)).astype(np.float32)
+        got = CK.gemm(ty, q, rows, cols, xb)
+        want = np.stack([CK.gemv(ty, q, rows, cols, xb[i], CK.KernelTier.REFERENCE, threads=1) for i in range(3)])
+        assert np.abs(got - want).max() <= 1e-4 * max(1.0, float(np.abs(want).max()))
+
+    check()
