@@ -152,7 +152,11 @@ def model_info(path: str) -> dict:
     cfg = f.config()
     v = validate_gguf(f)
     card = extract_model_card(f, os.path.getsize(path))
-    return {"path": path, "gguf_version": f.version, "tensors": len(f.tensors), "metadata_entries": len(f.metadata), "variant": v.variant.value,
+    from .core import gguf as G
+    # which GPU engine EngineBuilder would pick: decided by the storage format of the layer weights
+    lw = next((f.tensor_info(n).type for n in ("blk.0.attn_q.weight", "blk.0.attn_qkv.weight", "blk.0.ffn_down.weight") if f.has_tensor(n)), None)
+    gpu_engine = "none" if lw is None else ("sub-2-bit runner" if lw in (G.TQ2_0_G128, G.Q1_0_G128) else "generic-format engine")
+    return {"path": path, "gpu_engine": gpu_engine, "gguf_version": f.version, "tensors": len(f.tensors), "metadata_entries": len(f.metadata), "variant": v.variant.value,
             "architecture": card.architecture, "name": card.name, "quantization": card.quantization, "bits_per_weight": card.bits_per_weight,
             "estimated_parameters": card.estimated_param_count(), "file_size_bytes": os.path.getsize(path),
             "config": {"layers": cfg.layers, "hidden": cfg.hidden, "heads": cfg.heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
@@ -168,7 +172,7 @@ def cmd_info(args) -> int:
         from .core import GgufFile
         from .core.compat import extract_model_card
         print(extract_model_card(GgufFile.open(args.model), info["file_size_bytes"]).to_markdown())
-        print(f"variant: {info['variant']}\n{info['compat']}")
+        print(f"variant: {info['variant']}\nGPU engine: {info['gpu_engine']}\n{info['compat']}")
     return 0
 
 

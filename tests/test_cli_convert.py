@@ -31,6 +31,10 @@ def test_info_validate_quantize_commands(tiny_gguf, tmp_path, capsys):
     from oxibonsai_b200.core import GgufFile, gguf as G
     info = cli.model_info(tiny_gguf)
     assert info["valid"] and info["config"]["layers"] == 2 and info["quantization"] == "TQ2_0_g128" and info["variant"] == "Custom"
+    assert info["gpu_engine"] == "sub-2-bit runner"
+    q8 = str(tmp_path / "q8.gguf")
+    cli.requantize_gguf(tiny_gguf, q8, "q8_0")
+    assert cli.model_info(q8)["gpu_engine"] == "generic-format engine"
     assert cli.main(["info", "-m", tiny_gguf, "--json"]) == 0
     assert json.loads(capsys.readouterr().out)["tensors"] == info["tensors"]
     assert cli.main(["info", "-m", tiny_gguf]) == 0 and "Architecture Details" in capsys.readouterr().out
