@@ -2,7 +2,7 @@
 """Kernel micro-benchmarks on Qwen3-8B-shaped matrices (the counterpart of the reference's ``benches/*.rs`` and its
 ``gemv_benchmark`` example, crates/oxibonsai-kernels/examples/).
 
-    python benchmarks/kernels.py gemv   [--fast 0|warp|tile|hmma|mma]        packed-bit GEMV, batch 1
+    python benchmarks/kernels.py gemv   [--fast s16|0|warp|tile|hmma|mma]    packed-bit GEMV, batch 1 (s16 = the streamed kernel)
     python benchmarks/kernels.py gemm   [--tokens 64]         packed-bit tcgen05 GEMM (prefill / batched decode)
     python benchmarks/kernels.py lmhead [--tokens 64]         dense f16 tcgen05 GEMM of the LM head
     python benchmarks/kernels.py attn   [--ctx 4096 --batch 1 --kv f16]   split-KV decode attention
@@ -72,7 +72,7 @@ def weight_copies(K, rows, cols, dev, budget=400e6):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemv", "gemm", "lmhead", "attn", "attn_prefill"])
-    ap.add_argument("--fast", default="warp", help="0 (exact f32), warp, tile, hmma or mma")
+    ap.add_argument("--fast", default="s16", help="s16 (streamed tensor-core GEMV), 0 (exact f32), warp, tile, hmma or mma")
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1)
@@ -101,12 +101,16 @@ def main() -> None:
 
                 if a.fast == "mma":
                     fws = [K.FragWeight(w) for w in ws]
+                if a.fast == "s16":
+                    sws = [K.S16Weight(w) for w in ws]
                 out = torch.empty(n, device=dev)
 
                 def fn():
                     it[0] += 1
                     if a.fast == "mma":
                         K.bitgemv_mma(fws[it[0] % len(ws)], x, out=out)
+                    elif a.fast == "s16":
+                        K.bitgemv_s16(sws[it[0] % len(ws)], x, out=out)
                     else:
                         K.bitgemv(ws[it[0] % len(ws)], x, out=out, fast=(False if a.fast == "0" else a.fast))
                 us = time_us(fn, a.iters, a.profile)

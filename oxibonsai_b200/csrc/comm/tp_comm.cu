@@ -20,7 +20,7 @@ __global__ void tp_barrier_kernel(TpComm c) {
     int* theirs = reinterpret_cast<int*>(c.peer[threadIdx.x] + c.lay.off_bar_flags) + c.rank;
     st_release_sys(theirs, want);
     const int* mine = reinterpret_cast<const int*>(c.peer[c.rank] + c.lay.off_bar_flags) + threadIdx.x;
-    if (!tp_wait_flag(mine, want)) atomicExch(c.status, 3);
+    if (!tp_wait_flag(mine, want, c.spin_limit)) atomicExch(c.status, 3);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -73,7 +73,7 @@ __global__ void tp_allreduce_oneshot_add_kernel(TpComm c, float* __restrict__ h,
       st_release_sys(reinterpret_cast<int*>(c.peer[threadIdx.x] + c.lay.off_bar_flags) + c.rank, want);
     }
     const int* mine = reinterpret_cast<const int*>(c.peer[c.rank] + c.lay.off_bar_flags) + threadIdx.x;
-    if (!tp_wait_flag(mine, want)) atomicExch(c.status, 4);
+    if (!tp_wait_flag(mine, want, c.spin_limit)) atomicExch(c.status, 4);
   }
   __syncthreads();
   float4* h4 = reinterpret_cast<float4*>(h);
@@ -106,7 +106,7 @@ __global__ void tp_add_kernel(float* __restrict__ h, const float* __restrict__ a
 extern "C" {
 
 // Layout of the symmetric buffer for the given sizes; returns the number of bytes every rank must allocate.
-size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems, size_t* offsets /*[5]*/) {
+size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems, size_t* offsets /*[6]*/) {
   using namespace bonsai;
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   size_t o = 0;
@@ -115,6 +115,7 @@ size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems
   offsets[2] = o; o = up(o + sizeof(float) * 2 * kTpMaxRanks * recv_elems);
   offsets[3] = o; o = up(o + sizeof(float) * logits_elems);
   offsets[4] = o; o = up(o + sizeof(float) * big_elems);
+  offsets[5] = o; o = up(o + sizeof(unsigned long long) * 2 * kTpMaxRanks * recv_elems);
   return o;
 }
 
@@ -129,13 +130,15 @@ void* bonsai_tp_create(int rank, int size, const uint64_t* peer_ptrs, size_t rec
   c->rank = rank;
   c->size = size;
   for (int r = 0; r < size; ++r) c->peer[r] = reinterpret_cast<uint8_t*>(peer_ptrs[r]);
-  size_t off[5];
+  size_t off[6];
   c->lay.total_bytes = bonsai_tp_layout(recv_elems, logits_elems, big_elems, off);
   c->lay.off_tile_flags = off[0];
   c->lay.off_bar_flags = off[1];
   c->lay.off_recv = off[2];
   c->lay.off_logits = off[3];
   c->lay.off_big = off[4];
+  c->lay.off_ll = off[5];
+  c->spin_limit = kTpDefaultSpinLimit;
   c->lay.recv_elems = recv_elems;
   c->lay.big_elems = big_elems;
   c->epoch = state;
@@ -145,6 +148,10 @@ void* bonsai_tp_create(int rank, int size, const uint64_t* peer_ptrs, size_t rec
   return c;
 }
 void bonsai_tp_destroy(void* c) { delete static_cast<bonsai::TpComm*>(c); }
+// Redirects the status word (where expired waits are recorded) to another device int of the caller.
+void bonsai_tp_set_status_ptr(void* c, int* status) { static_cast<bonsai::TpComm*>(c)->status = status; }
+// Polls a wait on a peer may take before it gives up and records a status code (default: about a second).
+void bonsai_tp_set_spin_limit(void* c, unsigned int polls) { static_cast<bonsai::TpComm*>(c)->spin_limit = polls < 1 ? 1 : polls; }
 
 int bonsai_tp_barrier(void* comm, cudaStream_t stream) {
   bonsai::tp_barrier_kernel<<<1, 32, 0, stream>>>(*static_cast<bonsai::TpComm*>(comm));
@@ -152,7 +159,8 @@ int bonsai_tp_barrier(void* comm, cudaStream_t stream) {
 }
 
 // Gathers [batch][rows] logits slices of all ranks into this rank's full logits area (and everyone else's).
-// On return of the second barrier the area holds [batch][vocab]; its address is bonsai_tp_logits_ptr().
+// Once the flag barrier that follows the pushes has completed the area holds [batch][vocab]; its address is
+// bonsai_tp_logits_ptr().
 // `local` holds rows of logits slots slot0 .. slot0+batch-1.
 int bonsai_tp_allgather_logits_at(void* comm, const float* local, int slot0, int batch, int rows, int row0, int vocab,
                                   cudaStream_t stream) {

@@ -5,10 +5,12 @@
 // tensor_parallel.rs:338-386).  Here every rank maps every peer's symmetric buffer and kernels
 // exchange data with plain st.global / ld.global to peer addresses plus release/acquire flags:
 //
-//   * fused row-parallel GEMV -> all-reduce + residual (one-shot, push based): the GEMV epilogue
-//     stores each finished row tile into slot [my rank] of every peer's receive area, publishes
-//     an epoch flag per (rank, tile), waits for the same tile of every peer and sums the slots in
-//     rank order - every rank therefore computes bit-identical hidden states;
+//   * fused row-parallel GEMV -> all-reduce + residual (one-shot, push based), two protocols:
+//     flag-in-data (bitgemv_stream.cu): every finished row goes to slot [my rank] of every peer as
+//     one 8-byte {value, tag} store and the receiving thread polls the payload itself, so there is
+//     no fence and no separate flag round trip; tile flags (bitgemv.cu, the exact-f32 path): rows
+//     first, then an epoch flag per (rank, tile) behind a system fence.  Either way the slots are
+//     summed in rank order - every rank computes bit-identical hidden states;
 //   * logits all-gather for the vocab-parallel LM head, and a two-shot in-place all-reduce for
 //     the prefill GEMM outputs, both bracketed by flag barriers.
 //
@@ -24,7 +26,7 @@ namespace bonsai {
 
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpMaxTiles = 4096;
-constexpr uint32_t kTpSpinLimit = 1u << 22;   // x ~0.2 us per poll: about a second
+constexpr uint32_t kTpDefaultSpinLimit = 1u << 22;   // x ~0.2 us per poll: about a second
 
 // Offsets inside every rank's symmetric buffer.
 struct TpLayout {
@@ -33,6 +35,7 @@ struct TpLayout {
   size_t off_recv;         // float [2][kTpMaxRanks][recv_elems]
   size_t off_logits;       // float [max_batch][vocab]
   size_t off_big;          // float [big_elems]  (prefill partial sums)
+  size_t off_ll;           // u64 [2][kTpMaxRanks][recv_elems]  ({value, tag} slots of the flag-in-data exchange)
   size_t recv_elems, big_elems, total_bytes;
 };
 
@@ -44,6 +47,7 @@ struct TpComm {
   int* done_ctr;   // device int: CTAs finished in the running fused kernel
   int* bar_epoch;  // device int: number of flag barriers completed
   int* status;     // device int: non-zero after a bounded wait expired
+  uint32_t spin_limit;   // polls before a wait on a peer gives up (host-settable; tests use a small value)
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -59,8 +63,8 @@ __device__ __forceinline__ int ld_volatile(const int* p) {
 }
 
 // Bounded wait until *flag >= want (epochs only grow).  Returns false on expiry.
-__device__ __forceinline__ bool tp_wait_flag(const int* flag, int want) {
-  for (uint32_t i = 0; i < kTpSpinLimit; ++i) {
+__device__ __forceinline__ bool tp_wait_flag(const int* flag, int want, uint32_t spin_limit) {
+  for (uint32_t i = 0; i < spin_limit; ++i) {
     if (ld_acquire_sys(flag) - want >= 0) return true;
     __nanosleep(20);
   }
@@ -69,6 +73,9 @@ __device__ __forceinline__ bool tp_wait_flag(const int* flag, int want) {
 
 __device__ __forceinline__ float* tp_recv_slot(const TpComm& c, int on_rank, int parity, int from_rank) {
   return reinterpret_cast<float*>(c.peer[on_rank] + c.lay.off_recv) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.recv_elems;
+}
+__device__ __forceinline__ unsigned long long* tp_ll_slot(const TpComm& c, int on_rank, int parity, int from_rank) {
+  return reinterpret_cast<unsigned long long*>(c.peer[on_rank] + c.lay.off_ll) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.recv_elems;
 }
 __device__ __forceinline__ int* tp_tile_flag(const TpComm& c, int on_rank, int parity, int from_rank, int tile) {
   return reinterpret_cast<int*>(c.peer[on_rank] + c.lay.off_tile_flags) + ((size_t)parity * kTpMaxRanks + from_rank) * kTpMaxTiles + tile;
@@ -85,7 +92,7 @@ __device__ __forceinline__ void tp_tile_allreduce(const TpComm& c, int epoch, in
   __syncthreads();
   if (threadIdx.x < c.size) {
     st_release_sys(tp_tile_flag(c, threadIdx.x, parity, c.rank, tile), want);
-    if (!tp_wait_flag(tp_tile_flag(c, c.rank, parity, threadIdx.x, tile), want)) atomicExch(c.status, 2);
+    if (!tp_wait_flag(tp_tile_flag(c, c.rank, parity, threadIdx.x, tile), want, c.spin_limit)) atomicExch(c.status, 2);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < nrows; i += blockDim.x) {

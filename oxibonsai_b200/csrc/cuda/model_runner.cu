@@ -48,13 +48,16 @@ int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, cons
 int bonsai_attn_prefill_order(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                               const float*, void*, int, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
+int bonsai_bitgemv_s16(const void*, const float*, const float*, float, float*, const float*, int, int, int, const void*, int*, cudaStream_t);
 }
 
 namespace bonsai {
 
 enum LayerPtr {
   LP_QKV_CODES = 0, LP_QKV_SCALES, LP_O_CODES, LP_O_SCALES, LP_GU_CODES, LP_GU_SCALES, LP_DOWN_CODES, LP_DOWN_SCALES,
-  LP_ATTN_NORM, LP_FFN_NORM, LP_Q_NORM, LP_K_NORM, LP_KPOOL, LP_VPOOL, LP_KSCALE, LP_VSCALE, LP_COUNT
+  LP_ATTN_NORM, LP_FFN_NORM, LP_Q_NORM, LP_K_NORM, LP_KPOOL, LP_VPOOL, LP_KSCALE, LP_VSCALE,
+  LP_QKV_S16, LP_O_S16, LP_GU_S16, LP_DOWN_S16,   // the same four matrices in the streamed decode layout (0 = not built)
+  LP_COUNT
 };
 enum GlobalPtr {
   GP_EMBD = 0, GP_LM_HEAD, GP_OUT_NORM, GP_ROPE_COS, GP_ROPE_SIN, GP_COUNT
@@ -65,7 +68,9 @@ enum IntCfg {
 };
 enum StepPtr {
   SP_TOKENS = 0, SP_POSITIONS, SP_BLOCK_TABLE, SP_H, SP_QKV, SP_Q, SP_ATTN, SP_ACT, SP_LOGITS, SP_WS_ACC, SP_WS_ML,
-  SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_ATTN_COUNTERS, SP_COUNT
+  SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_ATTN_COUNTERS,
+  SP_STATUS,   // device int: non-zero after a bounded wait inside a kernel of the step expired
+  SP_COUNT
 };
 
 struct Runner {
@@ -127,35 +132,38 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   float* logits = P<float>(sp[SP_LOGITS]);
   float* partial = P<float>(sp[SP_PARTIAL]);
 
+  // One linear layer of one sequence.  The packed-half mode streams the matrix in its S16 form through the tensor-core
+  // GEMV (bitgemv_stream.cu) when that form was built and the shape fits; epi 3 = row-parallel sum over the
+  // tensor-parallel group + residual inside the same kernel.
+  int* status = P<int>(sp[SP_STATUS]);
+  auto linear = [&](const uint64_t* lp, int w_codes, int w_s16, const float* x, const float* norm_w, float* out, const float* residual,
+                    int n, int k, int epi) -> int {
+    if (r.ic[IC_FAST] == 1 && lp[w_s16] != 0) {
+      const int rc = bonsai_bitgemv_s16(P<void>(lp[w_s16]), x, norm_w, r.eps, out, residual, n, k, epi, r.comm, status, st);
+      if (rc != BONSAI_CUDA_BAD_ARG) return rc;   // bad argument = a shape the streamed kernel declines
+    }
+    if (epi == 3)
+      return bonsai_bitgemv_tp(r.comm, P<void>(lp[w_codes]), P<void>(lp[w_codes + 1]), x, r.eps, out, residual, n, k, r.ic[IC_FAST], st);
+    return gemv(P<void>(lp[w_codes]), P<void>(lp[w_codes + 1]), x, norm_w, r.eps, out, residual, n, k, epi, st);
+  };
+
   for (int b = 0; b < batch; ++b)
     RC(bonsai_embed_f16(P<void>(r.gp[GP_EMBD]), tokens + b, h + (size_t)b * hidden, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     for (int b = 0; b < batch; ++b)
-      RC(gemv(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]),
-                        r.eps, qkv + (size_t)b * qkv_n, nullptr, qkv_n, hidden, 0, st));
+      RC(linear(lp, LP_QKV_CODES, LP_QKV_S16, h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]), qkv + (size_t)b * qkv_n, nullptr,
+                qkv_n, hidden, 0));
     RC(qkv_attention(r, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, r.ic[IC_NSPLIT], st));
-    if (!tp) {
-      for (int b = 0; b < batch; ++b)
-        RC(gemv(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, nullptr, r.eps,
-                          h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, 1, st));
-    } else {
-      for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv_tp(r.comm, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn + (size_t)b * qd, r.eps,
-                             h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd, r.ic[IC_FAST], st));
-    }
     for (int b = 0; b < batch; ++b)
-      RC(gemv(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), r.eps,
-                        act + (size_t)b * inter, nullptr, 2 * inter, hidden, 2, st));
-    if (!tp) {
-      for (int b = 0; b < batch; ++b)
-        RC(gemv(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, nullptr, r.eps,
-                          h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, 1, st));
-    } else {
-      for (int b = 0; b < batch; ++b)
-        RC(bonsai_bitgemv_tp(r.comm, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act + (size_t)b * inter, r.eps,
-                             h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, inter, r.ic[IC_FAST], st));
-    }
+      RC(linear(lp, LP_O_CODES, LP_O_S16, attn + (size_t)b * qd, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd,
+                tp ? 3 : 1));
+    for (int b = 0; b < batch; ++b)
+      RC(linear(lp, LP_GU_CODES, LP_GU_S16, h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), act + (size_t)b * inter, nullptr,
+                2 * inter, hidden, 2));
+    for (int b = 0; b < batch; ++b)
+      RC(linear(lp, LP_DOWN_CODES, LP_DOWN_S16, act + (size_t)b * inter, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden,
+                inter, tp ? 3 : 1));
   }
   if (!(flags & 2)) {
     if (!tp) {

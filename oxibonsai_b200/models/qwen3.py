@@ -35,6 +35,11 @@ class LayerWeights:
     ffn_norm: torch.Tensor
     q_norm: torch.Tensor
     k_norm: torch.Tensor
+    # the same four matrices in the streamed decode layout (None when not built)
+    qkv_s16: "K.S16Weight | None" = None
+    o_s16: "K.S16Weight | None" = None
+    gate_up_s16: "K.S16Weight | None" = None
+    down_s16: "K.S16Weight | None" = None
 
 
 def _upload(arr: np.ndarray, device) -> torch.Tensor:
@@ -80,7 +85,9 @@ def _f16_matrix(f: GgufFile, name: str, device, row0: int = 0, nrows: int | None
 class Qwen3Weights:
     """Device-resident weights of one tensor-parallel rank."""
 
-    def __init__(self, f: GgufFile, device, tp_rank: int = 0, tp_size: int = 1):
+    def __init__(self, f: GgufFile, device, tp_rank: int = 0, tp_size: int = 1, decode_layout: bool = True):
+        """``decode_layout``: also build the S16 form of every layer matrix, which the batch-1 decode GEMV streams
+        (the planar form stays: the prompt and batched GEMMs read it)."""
         cfg = f.config()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -134,9 +141,12 @@ class Qwen3Weights:
             gu.fill_from_gguf(raws["ffn_up"], ty("ffn_up"), hidden, self.inter_blk0 * 128, self.inter_local, dst_row0=1, dst_row_stride=2)
             down = K.PlanarWeight(hidden, self.inter_local, dev)
             down.fill_from_gguf(raws["ffn_down"], ty("ffn_down"), cfg.inter, 0, hidden, blk0=self.inter_blk0, nblk=self.inter_local // 128)
-            self.layers.append(LayerWeights(qkv, o, gu, down,
-                                            _norm_vector(f, p + "attn_norm.weight", dev), _norm_vector(f, p + "ffn_norm.weight", dev),
-                                            _norm_vector(f, p + "attn_q_norm.weight", dev), _norm_vector(f, p + "attn_k_norm.weight", dev)))
+            lw = LayerWeights(qkv, o, gu, down,
+                              _norm_vector(f, p + "attn_norm.weight", dev), _norm_vector(f, p + "ffn_norm.weight", dev),
+                              _norm_vector(f, p + "attn_q_norm.weight", dev), _norm_vector(f, p + "attn_k_norm.weight", dev))
+            if decode_layout and dev.type == "cuda":
+                lw.qkv_s16, lw.o_s16, lw.gate_up_s16, lw.down_s16 = (K.S16Weight(m) for m in (qkv, o, gu, down))
+            self.layers.append(lw)
             del raws
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
@@ -227,7 +237,11 @@ class Qwen3Runner:
         B = max_batch
         f32 = dict(dtype=torch.float32, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
-        self.tokens = torch.zeros(B, **i32)
+        # [status word, token of slot 0, token of slot 1, ...]: one device-to-host copy brings the sampled tokens and the
+        # word in which a kernel records an expired bounded wait (copy pipeline, tensor-parallel peer)
+        self.ctl = torch.zeros(B + 1, **i32)
+        self.status = self.ctl[:1]
+        self.tokens = self.ctl[1:]
         self.positions = torch.zeros(B, **i32)
         self.block_table = torch.zeros((B, self.max_pages), **i32)
         self.h = torch.zeros((B, cfg.hidden), **f32)
@@ -272,18 +286,30 @@ class Qwen3Runner:
             vals = [lw.qkv.codes.data_ptr(), lw.qkv.scales.data_ptr(), lw.o.codes.data_ptr(), lw.o.scales.data_ptr(),
                     lw.gate_up.codes.data_ptr(), lw.gate_up.scales.data_ptr(), lw.down.codes.data_ptr(), lw.down.scales.data_ptr(),
                     lw.attn_norm.data_ptr(), lw.ffn_norm.data_ptr(), lw.q_norm.data_ptr(), lw.k_norm.data_ptr(),
-                    kv.k[l].data_ptr(), kv.v[l].data_ptr(), ks, vs]
+                    kv.k[l].data_ptr(), kv.v[l].data_ptr(), ks, vs,
+                    *[0 if m is None else m.data.data_ptr() for m in (lw.qkv_s16, lw.o_s16, lw.gate_up_s16, lw.down_s16)]]
             assert len(vals) == nlp
             for i, v in enumerate(vals):
                 lp[l * nlp + i] = v
         self._native = lib.bonsai_runner_create(icfg, cfg.eps, gp, lp)
         sp = [self.tokens, self.positions, self.block_table, self.h, self.qkv, self.q, self.attn, self.act, self.logits, self.ws_acc,
-              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None, self.attn_counters]
+              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None, self.attn_counters, self.status]
         assert len(sp) == nsp
         self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
         if self.tp is not None:
+            self.tp.use_status_word(self.status)     # peers that do not answer are reported in the same word
             lib.bonsai_runner_set_comm(self._native, self.tp.handle)
         self.launches_per_step = None
+
+    def check_status(self, value: int | None = None) -> None:
+        """Raises when a kernel of an earlier step recorded an expired wait (``value``: the status word as already read by
+        the caller, else it is read here)."""
+        v = int(self.status.item()) if value is None else int(value)
+        if v:
+            self.status.zero_()
+            what = {2: "a tensor-parallel peer did not deliver its partial sums", 3: "a tensor-parallel peer did not reach a barrier",
+                    4: "a tensor-parallel peer did not enter an all-reduce", 5: "the weight copy pipeline of a GEMV stalled"}.get(v, "a bounded wait expired")
+            raise K.CudaKernelError(f"decode step reported status {v}: {what}")
 
     def __del__(self):
         try:

@@ -117,6 +117,55 @@ class PlanarWeight:
         return out
 
 
+_S16_SIG = {
+    "bonsai_s16_bytes": [_i, _i],
+    "bonsai_repack_s16": [_vp, _vp, _i, _i, _vp, _vp],
+    "bonsai_bitgemv_s16": [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
+}
+_s16_declared = False
+EPI_TP = 3
+
+
+def _s16():
+    global _s16_declared
+    l = lib()
+    if not _s16_declared:
+        declare(_S16_SIG, {"bonsai_s16_bytes": C.c_size_t})
+        _s16_declared = True
+    return l
+
+
+class S16Weight:
+    """A packed matrix in the streamed decode layout (csrc/cuda/bitgemv_stream.cu): tiles of 16 rows, one 544-byte block per
+    (tile, 128-input group) holding the 2-bit codes in MMA-fragment order followed by the 16 group scales.  Built on the
+    device from a :class:`PlanarWeight`; ``oxibonsai_b200.ops.s16_layout`` restates the layout on the host."""
+
+    def __init__(self, planar: PlanarWeight):
+        self.n, self.k = planar.n, planar.k
+        nbytes = int(_s16().bonsai_s16_bytes(self.n, self.k))
+        self.data = torch.empty(nbytes, dtype=torch.uint8, device=planar.codes.device)
+        check(_s16().bonsai_repack_s16(planar.codes.data_ptr(), planar.scales.data_ptr(), self.n, self.k, self.data.data_ptr(), stream()),
+              "repack_s16")
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel()
+
+
+def bitgemv_s16(w: S16Weight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
+                residual: torch.Tensor | None = None, out: torch.Tensor | None = None, comm: int | None = None,
+                status: torch.Tensor | None = None) -> torch.Tensor:
+    """out = W x through the streamed tensor-core GEMV (f16 activations, f32 accumulation).  ``epi``: store / residual add /
+    SwiGLU over interleaved gate-up rows / ``EPI_TP`` (sum over the ranks of the communicator handle ``comm`` + residual)."""
+    _f32c(x)
+    n_out = w.n // 2 if epi == EPI_SWIGLU else w.n
+    if out is None:
+        out = torch.empty(n_out, dtype=torch.float32, device=x.device)
+    check(_s16().bonsai_bitgemv_s16(w.data.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual), w.n, w.k, epi,
+                                    comm, ptr(status), stream()), "bitgemv_s16")
+    return out
+
+
 _MMA_SIG = {
     "bonsai_frag_sizes": [_i, _i, _vp, _vp],
     "bonsai_repack_frag": [_vp, _vp, _i, _i, _vp, _vp, _vp],

@@ -18,6 +18,8 @@ from ..ops import cuda_ops as K
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 _SIG = {
     "bonsai_tp_layout": [_sz, _sz, _sz, _vp],
+    "bonsai_tp_set_spin_limit": [_vp, C.c_uint],
+    "bonsai_tp_set_status_ptr": [_vp, _vp],
     "bonsai_tp_create": [_i, _i, _vp, _sz, _sz, _sz, _vp],
     "bonsai_tp_destroy": [_vp],
     "bonsai_tp_barrier": [_vp, _vp],
@@ -27,7 +29,8 @@ _SIG = {
     "bonsai_tp_allreduce_big_add": [_vp, _vp, _sz, _vp],
     "bonsai_bitgemv_tp": [_vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _i, _i, _i, _vp],
 }
-_RES = {"bonsai_tp_layout": _sz, "bonsai_tp_create": _vp, "bonsai_tp_destroy": None, "bonsai_tp_logits_ptr": _vp, "bonsai_tp_big_ptr": _vp}
+_RES = {"bonsai_tp_layout": _sz, "bonsai_tp_create": _vp, "bonsai_tp_destroy": None, "bonsai_tp_set_spin_limit": None,
+        "bonsai_tp_set_status_ptr": None, "bonsai_tp_logits_ptr": _vp, "bonsai_tp_big_ptr": _vp}
 _declared = False
 
 
@@ -78,7 +81,7 @@ class TpGroup:
         lib = _lib()
         self.rank, self.size = rank, size
         self.recv_elems, self.logits_elems, self.big_elems = hidden, max_batch * vocab, big_elems
-        offs = (C.c_size_t * 5)()
+        offs = (C.c_size_t * 6)()
         total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self._hdl = symm.rendezvous(self.buffer, dist.group.WORLD)
@@ -100,8 +103,20 @@ class TpGroup:
     def barrier(self) -> None:
         K.check(_lib().bonsai_tp_barrier(self.handle, K.stream()), "tp_barrier")
 
+    def use_status_word(self, word: torch.Tensor) -> None:
+        """Makes the kernels record expired waits in ``word`` (a device int32 the owner reads with its results) instead
+        of the group's own word."""
+        assert word.is_cuda and word.dtype == torch.int32 and word.numel() == 1
+        self._status_word = word
+        _lib().bonsai_tp_set_status_ptr(self.handle, word.data_ptr())
+
+    def set_spin_limit(self, polls: int) -> None:
+        """Number of polls a wait on a peer may take before the kernel gives up and records a status code."""
+        _lib().bonsai_tp_set_spin_limit(self.handle, int(polls))
+
     def status(self) -> int:
-        return int(self.state[3].item())
+        word = getattr(self, "_status_word", None)
+        return int(word.item()) if word is not None else int(self.state[3].item())
 
     def check(self) -> None:
         s = self.status()

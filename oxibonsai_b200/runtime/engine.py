@@ -74,7 +74,7 @@ class InferenceEngine:
         # pinned staging for the per-step host <-> device traffic
         self._tok_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._pos_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
-        self._out_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
+        self._out_host = torch.zeros(self.max_batch + 1, dtype=torch.int32).pin_memory()   # [status word, tokens...]
         self._slot_pages: dict[int, list[int]] = {}
         self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
         self.prefix_cache = None       # see enable_prefix_cache()
@@ -128,6 +128,21 @@ class InferenceEngine:
         self.runner.tokens[slot: slot + 1].copy_(self._tok_host[slot: slot + 1], non_blocking=True)
         self.runner.positions[slot: slot + 1].copy_(self._pos_host[slot: slot + 1], non_blocking=True)
 
+    def _read_tokens(self, n: int = 1, slot0: int = 0) -> list[int]:
+        """Brings the sampled tokens of slots slot0..slot0+n-1 to the host together with the step's status word (one
+        device-to-host copy when slot0 == 0) and raises :class:`CudaKernelError` if a kernel recorded an expired wait -
+        tokens computed from missing data are never handed out."""
+        r = self.runner
+        if slot0 == 0:
+            self._out_host[: n + 1].copy_(r.ctl[: n + 1], non_blocking=True)
+        else:
+            self._out_host[:1].copy_(r.status, non_blocking=True)
+            self._out_host[1: n + 1].copy_(r.tokens[slot0: slot0 + n], non_blocking=True)
+        torch.cuda.synchronize(self.device)
+        if int(self._out_host[0]):
+            r.check_status(int(self._out_host[0]))
+        return self._out_host[1: n + 1].tolist()
+
     # ---- prefix cache ----------------------------------------------------------------------------
     def enable_prefix_cache(self, max_pages: int | None = None):
         """Shares the KV pages of repeated prompt prefixes between sequences (full pages only).  The cache may hold up to
@@ -167,8 +182,8 @@ class InferenceEngine:
         """Runs the prompt through the model, leaving logits of the last prompt token in the runner.
 
         Prompts of at least ``prefill_min_tokens`` tokens go through the batched prefill kernels (tcgen05 GEMMs and
-        causal attention over the paged cache) in chunks; shorter ones, tensor-parallel ranks and the exact-f32 mode
-        are fed through the decode path one token at a time.
+        causal attention over the paged cache) in chunks, on one GPU and on tensor-parallel ranks alike; shorter ones
+        and the exact-f32 mode are fed through the decode path one token at a time.
         """
         n = len(prompt)
         toks = torch.tensor([int(t) for t in prompt], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
@@ -203,12 +218,10 @@ class InferenceEngine:
             self._start_sequence(0, prompt, total)
             # first token: sample from the prefill logits on the device
             K.sample(r.logits[:1], r.temps[:1], r.topks[:1], r.topps[:1], r.rng[:1], out=r.tokens[:1])
-            self._out_host[:1].copy_(r.tokens[:1], non_blocking=True)
-            torch.cuda.synchronize(self.device)
+            tok = self._read_tokens(1)[0]
             stats.prefill_seconds = time.perf_counter() - t0
             pos = len(prompt)
             t_dec = time.perf_counter()
-            tok = int(self._out_host[0])
             for _ in range(max_new):
                 if stop_at_eos and tok == EOS_TOKEN:
                     break
@@ -222,9 +235,7 @@ class InferenceEngine:
                 # the reference runs a forward after every emitted token, including the last
                 self._upload(0, tok, pos)
                 r.step(1, sample=True)
-                self._out_host[:1].copy_(r.tokens[:1], non_blocking=True)
-                torch.cuda.synchronize(self.device)
-                tok = int(self._out_host[0])
+                tok = self._read_tokens(1)[0]
                 pos += 1
             stats.decode_seconds = time.perf_counter() - t_dec
         finally:
@@ -259,10 +270,8 @@ class InferenceEngine:
             r.positions[:B].copy_(lens)
             out: list[list[int]] = [[] for _ in range(B)]
             done = [False] * B
-            host = torch.zeros(B, dtype=torch.int32).pin_memory()
             for step in range(max_tokens):
-                host.copy_(r.tokens[:B], non_blocking=True)
-                torch.cuda.synchronize(self.device)
+                host = self._read_tokens(B)
                 for s in range(B):
                     if done[s]:
                         continue
@@ -289,17 +298,13 @@ class InferenceEngine:
         r = self.runner
         K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
                  out=r.tokens[slot: slot + 1])
-        self._out_host[:1].copy_(r.tokens[slot: slot + 1], non_blocking=True)
-        torch.cuda.synchronize(self.device)
-        return int(self._out_host[0])
+        return self._read_tokens(1, slot)[0]
 
     def decode_one(self, token: int, pos: int) -> int:
         """Feeds ``token`` at position ``pos`` of slot 0 and returns the next sampled token."""
         self._upload(0, token, pos)
         self.runner.step(1, sample=True)
-        self._out_host[:1].copy_(self.runner.tokens[:1], non_blocking=True)
-        torch.cuda.synchronize(self.device)
-        return int(self._out_host[0])
+        return self._read_tokens(1)[0]
 
     def verify_greedy(self, tokens: Sequence[int], pos0: int, slot: int = 0) -> list[int]:
         """Greedy next-token choices of the model after each of ``tokens`` placed at positions pos0.. (one batched pass)."""

@@ -238,11 +238,8 @@ class BatchScheduler:
         pos = torch.tensor(self._pos, dtype=torch.int32).pin_memory()
         r.positions[:B].copy_(pos, non_blocking=True)
         r.step(B, sample=True)
-        out = torch.empty(B, dtype=torch.int32).pin_memory()
-        out.copy_(r.tokens[:B], non_blocking=True)
-        torch.cuda.synchronize(eng.device)
+        toks = eng._read_tokens(B)      # tokens + the step's status word in one copy; raises on an expired wait
         self.steps += 1
-        toks = out.tolist()
         for s in range(B):
             self._pos[s] += 1
         # retire from the highest slot down so that moves never touch an unprocessed slot

@@ -101,6 +101,54 @@ def test_bitgemv_mma_fragment_path_is_close_to_fp32(ty, rows, cols):
     assert torch.equal(y, K.bitgemv_mma(fw, xn.to(_dev()), epi=K.EPI_SWIGLU)) if rows % 2 == 0 else True
 
 
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+def test_s16_device_repack_matches_host_layout(ty):
+    """The device repack into the streamed decode layout equals the numpy statement of that layout byte for byte."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    from oxibonsai_b200.ops import s16_layout as L
+    rows, cols = 200, 384      # a ragged last tile (200 = 12 * 16 + 8)
+    raw, wd = _random_quant(ty, rows, cols, 5)
+    pw = K.PlanarWeight(rows, cols, _dev()).fill_from_gguf(torch.from_numpy(raw).to(_dev()), ty, cols, 0, rows)
+    sw = K.S16Weight(pw)
+    scales = pw.scales.cpu().numpy()
+    dense = wd.numpy().reshape(rows, cols // 128, 128) / np.maximum(scales.astype(np.float32), 1e-30)[:, :, None]
+    tern = np.rint(dense).astype(np.int8).reshape(rows, cols)
+    want = L.pack(tern, scales)
+    assert sw.data.cpu().numpy().tobytes() == want.tobytes()
+
+
+@pytest.mark.parametrize("ty", [TQ2_0_G128, Q1_0_G128])
+@pytest.mark.parametrize("rows,cols", [(6144, 4096), (4096, 12288), (512, 2560), (200, 128), (24576, 4096), (1001, 9728), (300, 6144),
+                                       (66, 16384), (5000, 2048), (4096, 512), (4096, 1536), (16, 128)])
+def test_bitgemv_streamed_is_close_to_fp32(ty, rows, cols):
+    """Streamed tensor-core GEMV (S16 layout): f16 activations, exact products, f32 accumulation."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    raw, wd = _random_quant(ty, rows, cols, 9)
+    pw = K.PlanarWeight(rows, cols, _dev()).fill_from_gguf(torch.from_numpy(raw).to(_dev()), ty, cols, 0, rows)
+    sw = K.S16Weight(pw)
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    g = torch.Generator().manual_seed(10)
+    x, nw, res = torch.randn(cols, generator=g), torch.rand(cols, generator=g) + 0.5, torch.randn(rows, generator=g)
+    x[::97] *= 6.0
+    xh = x.half().double()                       # the kernel rounds the activations to f16 and nothing else
+    ref = wd.double() @ xh
+    y = K.bitgemv_s16(sw, x.to(_dev()), status=status)
+    assert (y.cpu().double() - ref).abs().max().item() <= 2e-4 * ref.abs().mean().item() * (cols / 128) ** 0.5 + 1e-5
+    # against the un-rounded activations: the f16 rounding of x is the only error of note
+    ref32 = wd.double() @ x.double()
+    assert (y.cpu().double() - ref32).abs().max().item() <= 2e-3 * ref32.abs().mean().item() * (cols / 128) ** 0.5 + 1e-4
+    xn = nw * x * torch.rsqrt((x * x).mean() + 1e-6)
+    refn = wd.double() @ xn.double()
+    y = K.bitgemv_s16(sw, x.to(_dev()), norm_w=nw.to(_dev()), eps=1e-6, epi=K.EPI_RESID, residual=res.to(_dev()), status=status)
+    assert torch.allclose(y.cpu().double(), refn + res.double(), rtol=5e-3, atol=5e-3 * refn.abs().mean().item())
+    if rows % 2 == 0:
+        y = K.bitgemv_s16(sw, xn.to(_dev()), epi=K.EPI_SWIGLU, status=status)
+        want = torch.nn.functional.silu(refn[0::2]) * refn[1::2]
+        assert torch.allclose(y.cpu().double(), want, rtol=2e-2, atol=2e-2 * want.abs().mean().item())
+        assert torch.equal(y, K.bitgemv_s16(sw, xn.to(_dev()), epi=K.EPI_SWIGLU, status=status))   # same bits on a second run
+    assert int(status.item()) == 0
+
+
 def test_bitgemv_fused_norm_residual_swiglu():
     from oxibonsai_b200.ops import cuda_ops as K
     rows, cols = 1024, 2048
