@@ -58,8 +58,8 @@ def time_us(fn, iters: int, profile: bool) -> float:
     return e0.elapsed_time(e1) / iters * 1000.0
 
 
-def weight_copies(K, rows, cols, dev, budget=400e6):
-    n = max(2, int(budget // (rows * cols // 4)))
+def weight_copies(K, rows, cols, dev, budget=400e6, copies=0):
+    n = copies if copies > 0 else max(2, int(budget // (rows * cols // 4)))
     out = []
     for _ in range(n):
         w = K.PlanarWeight(rows, cols, dev)
@@ -81,6 +81,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--shapes", default=",".join(SHAPES))
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--copies", type=int, default=0, help="gemv / gemm: weight copies to cycle through (default: enough to miss L2; 1 = L2-resident weights)")
     ap.add_argument("--balanced", action="store_true", help="gemm: equal (tile, k) ranges per SM wherever possible")
     ap.add_argument("--whole-tiles", action="store_true", help="gemm: whole tiles per CTA instead of equal (tile, k) ranges")
     a = ap.parse_args()
@@ -94,7 +95,7 @@ def main() -> None:
     if a.case in ("gemv", "gemm"):
         for name in a.shapes.split(","):
             n, k = SHAPES[name]
-            ws = weight_copies(K, n, k, dev)
+            ws = weight_copies(K, n, k, dev, copies=a.copies)
             byts = n * k / 4 + n * k / 64
             if a.case == "gemv":
                 x = torch.randn(k, device=dev)

@@ -31,7 +31,17 @@ def _load(kind: str) -> C.CDLL:
     path = _build.lib_path(kind)
     try:
         if _build.is_stale(kind):
-            _build.build(kind)
+            # Every rank of a torchrun job imports this module at the same time.  One process rebuilds; the others wait
+            # on the file lock and find the library fresh when they get it.
+            import fcntl
+            _build.LIB.mkdir(exist_ok=True)
+            with open(_build.LIB / f".{kind}.lock", "w") as lock:
+                fcntl.flock(lock, fcntl.LOCK_EX)
+                try:
+                    if _build.is_stale(kind):
+                        _build.build(kind)
+                finally:
+                    fcntl.flock(lock, fcntl.LOCK_UN)
     except Exception:
         if not path.exists():
             raise

@@ -24,7 +24,7 @@ bool tensor_type_traits(uint32_t id, TypeTraits* out) {
     case 6: t = {"Q5_0", 32, 22}; break;
     case 7: t = {"Q5_1", 32, 24}; break;
     case 8: t = {"Q8_0", 32, 34}; break;
-    case 9: t = {"Q8_1", 32, 36}; break;
+    case 9: t = {"Q8_1", 32, 40}; break;   // f32 scale + f32 sum + 32 bytes, as the reference sizes it (ggml itself uses two f16: 36)
     case 10: t = {"Q2_K", 256, 84}; break;
     case 11: t = {"Q3_K", 256, 110}; break;
     case 12: t = {"Q4_K", 256, 144}; break;

@@ -14,8 +14,10 @@
 // Limits (BONSAI_ATTN_STATIC_* below).  A call is rejected with BONSAI_CUDA_BAD_ARG and a message
 // in `err` when
 //     batch * nq * nsplit * hd  >  BONSAI_ATTN_STATIC_MAX_ACC_FLOATS   (1 Mi floats = 4 MiB), or
+//     batch * nq * nsplit * 2   >  BONSAI_ATTN_STATIC_MAX_ML_FLOATS    (32 Ki floats = 128 KiB), or
 //     batch * nkv               >  BONSAI_ATTN_STATIC_MAX_COUNTERS     (4096).
-// The max/sum area is sized for the accumulator limit at the smallest head dimension (64).
+// The max/sum area is sized for the accumulator limit at head dimension 64, the smallest the kernel
+// behind this entry accepts, so its limit only binds for head dimensions the kernel rejects anyway.
 //
 // Rules for callers:
 //  * The scratch array is shared by every call on a device.  Two calls whose kernels may overlap

@@ -6,8 +6,8 @@
 // quarter of the memory roofline.  Here
 //   * weights live in the "S16" layout: tiles of 16 output rows, one 544-byte block per (tile, 128-input group) =
 //     32 lanes x 16 bytes of 2-bit codes in MMA-fragment order + 16 f16 group scales.  A CTA owns a contiguous range
-//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a four-stage
-//     shared-memory ring with cp.async.bulk (17 KB per copy, 70 KB in flight per SM).  The copies are issued before
+//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a shared-memory
+//     ring with cp.async.bulk (by default four stages of 17 KB: 70 KB in flight per SM).  The copies are issued before
 //     griddepcontrol.wait: under programmatic dependent launch the next GEMV's weights stream in while the previous
 //     kernel is still running;
 //   * a code c = w + 1 in {0, 1, 2} sitting at bits p, p+1 of a 16-bit half becomes the f16 number 2^(10-p) + c with
@@ -39,11 +39,14 @@ enum { SEPI_STORE = 0, SEPI_RESID = 1, SEPI_SWIGLU = 2, SEPI_TP = 3 };
 constexpr int kS16Warps = 16;                                    // consumer warps; warp 16 is the copy producer
 constexpr int kS16Threads = (kS16Warps + 1) * 32;
 constexpr int kS16BlockBytes = 544;                              // 512 B codes + 32 B scales
-constexpr int kS16StageBlocks = 2 * kS16Warps;
-constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes; // 17408
-constexpr int kS16Stages = 4;
+constexpr int kS16MaxStages = 16;
 constexpr int kS16MaxTiles = 12;                                 // tiles per CTA (size of the partial-sum area)
-constexpr uint32_t kS16WaitLimit = 1u << 22;
+constexpr uint32_t kS16WaitLimit = 1u << 21;                     // polls (with a short sleep in between): about a second
+
+// Pipeline shape, settable through bonsai_s16_tune: blocks per warp per stage (1 or 2), ring stages, and the sleep
+// between two polls of a ring barrier.  Back-to-back polling by sixteen waiting warps saturates the shared-memory
+// pipe and delays the copy completions and the producer's own barrier traffic.
+static int g_s16_bpw = 2, g_s16_stages = 4, g_s16_sleep_ns = 32, g_s16_pdl = 1;
 
 // offset + 1 of MMA step mm (= code slot mm): slots reach mantissa position 6, 8 | 4, 6, 8 | 4, 6, 8
 __device__ __constant__ float kS16Off[8] = {17.0f, 5.0f, 65.0f, 17.0f, 5.0f, 65.0f, 17.0f, 5.0f};
@@ -59,16 +62,18 @@ __device__ __forceinline__ void s16_bar() { asm volatile("bar.sync 1, %0;" ::"n"
 
 // Bounded wait on a ring barrier: lane 0 polls, the outcome is broadcast.  Returns false on expiry or when another
 // warp has already given up (*abort set).
-__device__ __forceinline__ bool s16_wait(uint64_t* bar, uint32_t parity, int lane, volatile int* abort) {
-  int ok = 1;
-  if (lane == 0) {
-    ok = 0;
-    for (uint32_t i = 0; i < kS16WaitLimit; ++i) {
-      if (tc::mbar_try_wait(bar, parity)) { ok = 1; break; }
-      if (*abort) break;
-    }
-    if (!ok) *abort = 1;
+__device__ __forceinline__ bool s16_poll(uint64_t* bar, uint32_t parity, volatile int* abort, int sleep_ns) {
+  for (uint32_t i = 0; i < kS16WaitLimit; ++i) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort) break;
+    if (sleep_ns > 0) __nanosleep(sleep_ns);
   }
+  *abort = 1;
+  return false;
+}
+__device__ __forceinline__ bool s16_wait(uint64_t* bar, uint32_t parity, int lane, volatile int* abort, int sleep_ns) {
+  int ok = 1;
+  if (lane == 0) ok = s16_poll(bar, parity, abort, sleep_ns) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -132,18 +137,23 @@ struct S16Args {
   int* status;               // device int, set non-zero when a bounded wait expired (may be null)
   float eps;
   int N, K, epi;
+  int nstages, sleep_ns;     // ring depth and poll back-off
 };
 
+template <int BPW>
 __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, TpComm tp) {
+  constexpr int kS16StageBlocks = BPW * kS16Warps;
+  constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes;   // 8704 or 17408
   extern __shared__ __align__(128) uint8_t smem[];
   const int K = a.K, ng = K >> 7;
+  const int kS16Stages = a.nstages;
   uint8_t* ring = smem;
   __half* xs = reinterpret_cast<__half*>(smem + kS16Stages * kS16StageBytes);
   float* og = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + (size_t)K * 2);
   float* part = og + ((ng + 3) & ~3);                      // [kS16MaxTiles][kS16Warps][16]
   uint64_t* full = reinterpret_cast<uint64_t*>(part + kS16MaxTiles * kS16Warps * 16);
-  uint64_t* empty = full + kS16Stages;
-  float* s32 = reinterpret_cast<float*>(empty + kS16Stages);   // [32]
+  uint64_t* empty = full + kS16MaxStages;
+  float* s32 = reinterpret_cast<float*>(empty + kS16MaxStages);   // [32]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(s32 + 32);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,15 +180,7 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
     if (lane == 0) {
       for (int s = 0; s < nstage_total; ++s) {
         const int slot = s % kS16Stages;
-        if (s >= kS16Stages) {
-          bool ok = false;
-          const uint32_t parity = ((s / kS16Stages) - 1) & 1;
-          for (uint32_t i = 0; i < kS16WaitLimit; ++i) {
-            if (tc::mbar_try_wait(&empty[slot], parity)) { ok = true; break; }
-            if (*abort_flag) break;
-          }
-          if (!ok) { *abort_flag = 1; break; }
-        }
+        if (s >= kS16Stages && !s16_poll(&empty[slot], ((s / kS16Stages) - 1) & 1, abort_flag, a.sleep_ns)) break;
         const int b0 = s * kS16StageBlocks;
         const int nb = min(kS16StageBlocks, nb_total - b0);
         const uint32_t bytes = (uint32_t)nb * kS16BlockBytes;
@@ -197,10 +199,14 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
   }
 
   // ---- consumers ----
+  constexpr int NT = kS16Warps * 32;
+  for (int i = tid; i < kS16MaxTiles * kS16Warps * 16; i += NT) part[i] = 0.0f;   // nothing here depends on an earlier kernel
   asm volatile("griddepcontrol.wait;" ::: "memory");
   {
-    // activations: f32 -> (RMS-normalised) f16 in natural order, then the per-group offset sums
-    constexpr int NT = kS16Warps * 32;
+    // activations: f32 -> (RMS-normalised) f16 in natural order, and the per-group offset sums
+    //   og[g] = sum over the group's inputs of (offset + 1) * x,
+    // taken from the rounded values while they are written: thread tid + i * NT holds inputs 4c..4c+3 of chunk c, a
+    // warp's 32 chunks are one 128-input group, and lane l's four inputs all belong to MMA step 2 * (l / 8) + (l & 1)
     const int nch = K >> 2;
     const float4* x4 = reinterpret_cast<const float4*>(a.x);
     float4 keep[2];
@@ -224,7 +230,8 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
       tsum = warp_sum(tsum);
       inv = 1.0f / sqrtf(tsum / (float)K + a.eps);
     }
-    auto emit = [&](int c, float4 v) {
+    const float off = kS16Off[2 * (lane >> 3) + (lane & 1)];
+    auto emit = [&](int c, float4 v) {      // whole warps enter (K % 128 == 0): c / 32 is the warp's group
       if (a.norm_w != nullptr) {
         const float4 ww = reinterpret_cast<const float4*>(a.norm_w)[c];
         v.x *= ww.x * inv; v.y *= ww.y * inv; v.z *= ww.z * inv; v.w *= ww.w * inv;
@@ -234,6 +241,9 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
       u.x = *reinterpret_cast<const uint32_t*>(&h0);
       u.y = *reinterpret_cast<const uint32_t*>(&h1);
       reinterpret_cast<uint2*>(xs)[c] = u;
+      const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+      const float sg = warp_sum(off * ((f0.x + f0.y) + (f1.x + f1.y)));
+      if (lane == 0) og[c >> 5] = sg;
     };
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -241,22 +251,10 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
       if (c < nch) emit(c, keep[i]);
     }
     for (int c = tid + 2 * NT; c < nch; c += NT) emit(c, x4[c]);
-    for (int i = tid; i < kS16MaxTiles * kS16Warps * 16; i += NT) part[i] = 0.0f;
-    s16_bar();
-    // og[g] = sum over the group's inputs of (offset + 1) * x: lane l holds inputs 4l..4l+3, all of MMA step
-    // 2 * (l / 8) + (l & 1)
-    const float off = kS16Off[2 * (lane >> 3) + (lane & 1)];
-    for (int gi = warp; gi < ng; gi += kS16Warps) {
-      const uint2 u = reinterpret_cast<const uint2*>(xs + (size_t)gi * 128)[lane];
-      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-      const float s = warp_sum(off * ((f0.x + f0.y) + (f1.x + f1.y)));
-      if (lane == 0) og[gi] = s;
-    }
     s16_bar();
   }
 
-  // ---- main loop: two blocks per warp per stage ----
+  // ---- main loop: BPW consecutive blocks per warp per stage ----
   {
     int cur_tile = -1;
     float tot_lo = 0.0f, tot_hi = 0.0f;
@@ -271,19 +269,22 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
     };
     for (int s = 0; s < nstage_total; ++s) {
       const int slot = s % kS16Stages;
-      if (!s16_wait(&full[slot], (s / kS16Stages) & 1, lane, abort_flag)) break;
-      const uint8_t* st = ring + (size_t)slot * kS16StageBytes;
+      if (!s16_wait(&full[slot], (s / kS16Stages) & 1, lane, abort_flag, a.sleep_ns)) break;
+      const uint8_t* st = ring + (size_t)slot * kS16StageBytes + (size_t)(BPW * warp) * kS16BlockBytes;
+      const int idx0 = s * kS16StageBlocks + BPW * warp;
+      int tl = idx0 / ng, grp = idx0 - tl * ng;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int bi = 2 * warp + i;
-        const int idx = s * kS16StageBlocks + bi;
-        if (idx < nb_total) {
-          const int tl = idx / ng, grp = idx - tl * ng;
+      for (int i = 0; i < BPW; ++i) {
+        if (idx0 + i < nb_total) {
           if (tl != cur_tile) {
             flush();
             cur_tile = tl;
           }
-          s16_block(st + (size_t)bi * kS16BlockBytes, xs + (size_t)grp * 128, og[grp], lane, tot_lo, tot_hi);
+          s16_block(st + (size_t)i * kS16BlockBytes, xs + (size_t)grp * 128, og[grp], lane, tot_lo, tot_hi);
+        }
+        if (++grp == ng) {
+          grp = 0;
+          ++tl;
         }
       }
       __syncwarp();
@@ -416,10 +417,10 @@ __global__ void repack_s16_kernel(const uint32_t* __restrict__ codes, const __ha
   }
 }
 
-static inline size_t s16_smem_bytes(int K) {
+static inline size_t s16_smem_bytes(int K, int bpw, int stages) {
   const int ng = K / 128;
-  return (size_t)kS16Stages * kS16StageBytes + (size_t)K * 2 + (size_t)((ng + 3) & ~3) * 4 +
-         (size_t)kS16MaxTiles * kS16Warps * 16 * 4 + 2 * kS16Stages * 8 + 32 * 4 + 16;
+  return (size_t)stages * bpw * kS16Warps * kS16BlockBytes + (size_t)K * 2 + (size_t)((ng + 3) & ~3) * 4 +
+         (size_t)kS16MaxTiles * kS16Warps * 16 * 4 + 2 * kS16MaxStages * 8 + 32 * 4 + 16;
 }
 
 }  // namespace bonsai
@@ -436,6 +437,19 @@ int bonsai_repack_s16(const void* codes, const void* scales, int N, int K, void*
   const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   repack_s16_kernel<<<grid, 256, 0, stream>>>((const uint32_t*)codes, (const __half*)scales, N, K, (uint32_t*)out);
   return launch_status();
+}
+
+// Pipeline shape of bonsai_bitgemv_s16 for later launches of this process: blocks per warp per stage (1 or 2), ring
+// stages (2..16), nanoseconds of sleep between two polls of a ring barrier, and whether the kernel is launched with
+// programmatic dependent launch (its weight copies then start while the previous kernel still runs).  Returns 0, or
+// the bad-argument code.
+int bonsai_s16_tune(int blocks_per_warp, int stages, int sleep_ns, int pdl) {
+  if ((blocks_per_warp != 1 && blocks_per_warp != 2) || stages < 2 || stages > bonsai::kS16MaxStages || sleep_ns < 0) return BONSAI_CUDA_BAD_ARG;
+  bonsai::g_s16_pdl = pdl != 0;
+  bonsai::g_s16_bpw = blocks_per_warp;
+  bonsai::g_s16_stages = stages;
+  bonsai::g_s16_sleep_ns = sleep_ns;
+  return BONSAI_CUDA_OK;
 }
 
 // out = W x for an S16 matrix (see the head of this file): out[N] for epi 0 / 1 (1 adds residual[N]), out[N/2] for
@@ -461,12 +475,15 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
     tp = *static_cast<const TpComm*>(comm);
     if ((size_t)N > tp.lay.recv_elems) return BONSAI_CUDA_BAD_ARG;
   }
-  const size_t smem = s16_smem_bytes(K);
+  const int bpw = g_s16_bpw, stages = g_s16_stages;
+  const size_t smem = s16_smem_bytes(K, bpw, stages);
+  if (smem > 200 * 1024) return BONSAI_CUDA_BAD_ARG;
   static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(bitgemv_s16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(bitgemv_s16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(bitgemv_s16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
       return BONSAI_CUDA_LAUNCH_FAILED;
     attr_set[dev] = true;
   }
@@ -481,7 +498,17 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
   a.N = N;
   a.K = K;
   a.epi = epi;
-  cudaError_t e = launch_pdl(bitgemv_s16_kernel, dim3(grid), dim3(kS16Threads), smem, stream, a, tp);
+  a.nstages = stages;
+  a.sleep_ns = g_s16_sleep_ns;
+  cudaError_t e;
+  if (g_s16_pdl) {
+    e = bpw == 1 ? launch_pdl(bitgemv_s16_kernel<1>, dim3(grid), dim3(kS16Threads), smem, stream, a, tp)
+                 : launch_pdl(bitgemv_s16_kernel<2>, dim3(grid), dim3(kS16Threads), smem, stream, a, tp);
+  } else {
+    if (bpw == 1) bitgemv_s16_kernel<1><<<grid, kS16Threads, smem, stream>>>(a, tp);
+    else bitgemv_s16_kernel<2><<<grid, kS16Threads, smem, stream>>>(a, tp);
+    e = cudaGetLastError();
+  }
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 

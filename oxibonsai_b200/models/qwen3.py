@@ -220,7 +220,10 @@ class Qwen3Runner:
     """Owns the activation buffers and the native step runner for a fixed maximum batch."""
 
     def __init__(self, weights: Qwen3Weights, kv: PagedKvCache, max_batch: int, max_seq: int, nsplit: int | None = None,
-                 fast: bool = True, prefill_chunk: int = 1024):
+                 fast: bool = True, prefill_chunk: int = 1024, streamed_gemv_mask: int = 15):
+        """``streamed_gemv_mask``: which linear layers of the batch-1 step use the streamed S16 GEMV (bit 0 QKV, 1 attention
+        output, 2 gate/up, 3 down); the others stay on the planar-layout kernels."""
+        self.streamed_gemv_mask = streamed_gemv_mask
         self.w, self.kv, self.max_batch, self.max_seq = weights, kv, max_batch, max_seq
         cfg, dev = weights.cfg, weights.device
         self.cfg, self.device = cfg, dev
@@ -287,7 +290,8 @@ class Qwen3Runner:
                     lw.gate_up.codes.data_ptr(), lw.gate_up.scales.data_ptr(), lw.down.codes.data_ptr(), lw.down.scales.data_ptr(),
                     lw.attn_norm.data_ptr(), lw.ffn_norm.data_ptr(), lw.q_norm.data_ptr(), lw.k_norm.data_ptr(),
                     kv.k[l].data_ptr(), kv.v[l].data_ptr(), ks, vs,
-                    *[0 if m is None else m.data.data_ptr() for m in (lw.qkv_s16, lw.o_s16, lw.gate_up_s16, lw.down_s16)]]
+                    *[0 if m is None or not (self.streamed_gemv_mask >> i) & 1 else m.data.data_ptr()
+                      for i, m in enumerate((lw.qkv_s16, lw.o_s16, lw.gate_up_s16, lw.down_s16))]]
             assert len(vals) == nlp
             for i, v in enumerate(vals):
                 lp[l * nlp + i] = v

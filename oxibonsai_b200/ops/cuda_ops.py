@@ -121,6 +121,7 @@ _S16_SIG = {
     "bonsai_s16_bytes": [_i, _i],
     "bonsai_repack_s16": [_vp, _vp, _i, _i, _vp, _vp],
     "bonsai_bitgemv_s16": [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
+    "bonsai_s16_tune": [_i, _i, _i, _i],
 }
 _s16_declared = False
 EPI_TP = 3
@@ -133,6 +134,11 @@ def _s16():
         declare(_S16_SIG, {"bonsai_s16_bytes": C.c_size_t})
         _s16_declared = True
     return l
+
+
+def s16_tune(blocks_per_warp: int = 2, stages: int = 4, sleep_ns: int = 32, pdl: bool = True) -> None:
+    """Pipeline shape of the streamed GEMV for later launches (and graph captures) of this process."""
+    check(_s16().bonsai_s16_tune(blocks_per_warp, stages, sleep_ns, int(pdl)), "s16_tune")
 
 
 class S16Weight:

@@ -100,6 +100,30 @@ class TpGroup:
         bo = int(offs[4])
         self.big = self.buffer[bo: bo + self.big_elems * 4].view(torch.float32)
 
+    @classmethod
+    def loopback(cls, device, size: int = 2, hidden: int = 4096, vocab: int = 1024, max_batch: int = 1, big_elems: int = 4096,
+                 rank: int = 0) -> "TpGroup":
+        """A communicator of ``size`` ranks whose peers are plain buffers on this GPU that nothing ever writes: every wait on
+        a peer runs into its limit and the kernel reports it in the status word.  For testing the failure path of the
+        tensor-parallel kernels on one GPU without any fault (no process group, no symmetric memory)."""
+        lib = _lib()
+        self = cls.__new__(cls)
+        self.rank, self.size = rank, size
+        self.recv_elems, self.logits_elems, self.big_elems = hidden, max_batch * vocab, big_elems
+        offs = (C.c_size_t * 6)()
+        total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
+        self._peers = [torch.zeros(total, dtype=torch.uint8, device=device) for _ in range(size)]
+        self.buffer, self._hdl = self._peers[rank], None
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        arr = (C.c_uint64 * size)(*[t.data_ptr() for t in self._peers])
+        self.handle = lib.bonsai_tp_create(rank, size, arr, self.recv_elems, self.logits_elems, self.big_elems, self.state.data_ptr())
+        if not self.handle:
+            raise RuntimeError("bonsai_tp_create failed")
+        lo, bo = int(offs[3]), int(offs[4])
+        self.logits = self.buffer[lo: lo + self.logits_elems * 4].view(torch.float32).view(max_batch, vocab)
+        self.big = self.buffer[bo: bo + self.big_elems * 4].view(torch.float32)
+        return self
+
     def barrier(self) -> None:
         K.check(_lib().bonsai_tp_barrier(self.handle, K.stream()), "tp_barrier")
 

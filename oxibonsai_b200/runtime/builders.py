@@ -57,6 +57,7 @@ class EngineBuilder:
         self._page_size = 64
         self._kv_pages: int | None = None
         self._warmup = True
+        self._exact: bool | None = None
 
     def model_path(self, path: str) -> "EngineBuilder":
         self._model_path = str(path); return self
@@ -94,10 +95,15 @@ class EngineBuilder:
     def warmup(self, on: bool) -> "EngineBuilder":
         self._warmup = bool(on); return self
 
+    def exact(self, on: bool | None) -> "EngineBuilder":
+        """``True``: f32 activations end to end (the mode held to the CPU scalar path token for token); ``False``: f16
+        activations on the tensor-core kernels; ``None`` (default): exact only with an f32 KV cache."""
+        self._exact = on; return self
+
     def options(self) -> dict:
         return dict(model_path=self._model_path, max_seq_len=self._max_seq_len, max_batch=self._max_batch, kv_dtype=self._kv_dtype,
                     device=self._device, sampling=self._sampler.build(), page_size=self._page_size, kv_pages=self._kv_pages,
-                    tp_rank=self._tp_rank, tp_size=self._tp_size, warmup=self._warmup)
+                    tp_rank=self._tp_rank, tp_size=self._tp_size, warmup=self._warmup, exact=self._exact)
 
     def build(self):
         if not self._model_path:

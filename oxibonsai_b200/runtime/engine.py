@@ -61,12 +61,12 @@ class InferenceEngine:
         self.sampling = (sampling or SamplingPreset.BALANCED.params()).validate()
         self.kvt = KV_NAMES[kv_dtype.lower()]
         t0 = time.perf_counter()
-        self.weights = Qwen3Weights(self.gguf, self.device, tp_rank, tp_size)
+        # exact = f32 activations end to end (the token-stream gate); default: exact only with an f32 KV cache
+        self.exact = (self.kvt == K.KV_F32) if exact is None else bool(exact)
+        self.weights = Qwen3Weights(self.gguf, self.device, tp_rank, tp_size, decode_layout=not self.exact)
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
                                self.kvt, self.device)
-        # exact = f32 activations end to end (the token-stream gate); default: exact only with an f32 KV cache
-        self.exact = (self.kvt == K.KV_F32) if exact is None else bool(exact)
         self.prefill_chunk = 1024
         self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact,
                                   prefill_chunk=self.prefill_chunk)
@@ -299,6 +299,56 @@ class InferenceEngine:
         K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
                  out=r.tokens[slot: slot + 1])
         return self._read_tokens(1, slot)[0]
+
+    def begin_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None) -> int:
+        """First half of :meth:`open_sequence` for callers that prefill in pieces (the scheduler interleaves prompt chunks
+        with decode steps): binds pages for ``max_total`` tokens, attaches cached prefix pages and returns how many prompt
+        tokens those pages already cover.  Continue with :meth:`prefill` over ``prompt[covered:]`` in as many pieces as
+        wanted (``pos0`` = index of the piece's first token), then :meth:`finish_sequence`."""
+        self._set_sampling(slot, params or self.sampling)
+        prompt = [int(t) for t in prompt]
+        shared: list[int] = []
+        pc = self.prefix_cache
+        if pc is not None and len(prompt) > 1:
+            shared = pc.lookup(prompt, max_tokens=len(prompt) - 1)
+            if shared:
+                self.kv.retain(shared)
+                self._release_slot(slot)
+                self._slot_pages[slot] = list(shared)
+        try:
+            self._bind_slot(slot, min(self.max_seq_len, max_total))
+        except MemoryError:
+            self._release_slot(slot)
+            raise
+        if shared:
+            row = torch.tensor(self._slot_pages[slot], dtype=torch.int32)
+            self.runner.block_table[slot, : len(row)].copy_(row.to(self.device))
+        return len(shared) * self.kv.page_size
+
+    def finish_sequence(self, prompt: Sequence[int], slot: int = 0) -> int:
+        """Second half of :meth:`open_sequence`: the whole prompt has been prefilled into ``slot``; registers its pages with
+        the prefix cache and returns the first sampled token."""
+        if self.prefix_cache is not None:
+            self.prefix_cache.insert([int(t) for t in prompt], self._slot_pages[slot])
+        r = self.runner
+        K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
+                 out=r.tokens[slot: slot + 1])
+        return self._read_tokens(1, slot)[0]
+
+    def step_batch(self, positions: Sequence[int]) -> list[int]:
+        """One decode step of the live sequences in slots 0..len(positions)-1 (slot i feeds its last sampled token at
+        ``positions[i]``); returns the newly sampled token of every slot.  The positions go up from pinned memory and the
+        tokens come back with the step's status word in one copy."""
+        B = len(positions)
+        r = self.runner
+        self._pos_host[:B] = torch.tensor(list(positions), dtype=torch.int32)
+        r.positions[:B].copy_(self._pos_host[:B], non_blocking=True)
+        r.step(B, sample=True)
+        return self._read_tokens(B)
+
+    def bind_thread(self) -> None:
+        """Makes this engine's GPU the calling thread's current device (a scheduler thread calls it once)."""
+        torch.cuda.set_device(self.device)
 
     def decode_one(self, token: int, pos: int) -> int:
         """Feeds ``token`` at position ``pos`` of slot 0 and returns the next sampled token."""

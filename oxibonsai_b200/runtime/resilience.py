@@ -78,6 +78,8 @@ class CircuitBreaker:
 
     def record_failure(self) -> None:
         with self._lock:
+            if self.state == CircuitState.OPEN:
+                return                      # already open: a late failure must not restart the recovery timer
             if self.state == CircuitState.HALF_OPEN:
                 self._open()
             else:

@@ -3,10 +3,13 @@
 Reference: ``ContinuousBatchScheduler`` (crates/oxibonsai-runtime/src/continuous_batch.rs:28-380: priority queues, admission,
 per-step bookkeeping - but every step re-runs a whole single-sequence generate per request), ``BoundedQueue`` /
 ``InferenceQueue`` with back-pressure (request_queue.rs:52-357) and ``AsyncInferenceEngine`` (async_engine.rs:26-154).
-Here one decode step advances every live sequence through the batched tcgen05 path, prompts are prefilled into a
-free slot between steps, and finished sequences free their KV pages immediately.  Live sequences always occupy
-slots 0..n-1: when a sequence ends, the last live slot is moved into the hole (only its block-table row and
-sampler state move; KV pages are referenced, never copied).
+Here one decode step advances every live sequence through the batched tcgen05 path, and finished sequences free their KV
+pages immediately.  A new prompt is prefilled into the first free slot in chunks of ``prefill_chunk_tokens``, one chunk per
+scheduler iteration, with a decode step of the live batch after every chunk - so a 2048-token newcomer delays the tokens of
+the running streams by one chunk's time per step instead of the whole prompt's (the reference's ``ChunkedPrefill`` plans the
+chunks, crates/oxibonsai-model/src/chunked_prefill.rs:9-320, but runs them back to back).  Live sequences always occupy
+slots 0..n-1: when a sequence ends, the last live slot is moved into the hole (only its block-table row and sampler state
+move; KV pages are referenced, never copied).
 """
 from __future__ import annotations
 
@@ -18,6 +21,10 @@ from dataclasses import dataclass, field
 from typing import Callable, Sequence
 
 from .presets import SamplingParams
+
+
+class _Cancelled(Exception):
+    pass
 
 
 class QueueFull(RuntimeError):
@@ -96,9 +103,13 @@ class BoundedPriorityQueue:
 class BatchScheduler:
     """Owns an ``InferenceEngine`` (max_batch > 1) and serves requests with continuous batching."""
 
-    def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005):
+    def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
+                 prefill_chunk_tokens: int = 512):
         from ..core.oracle import EOS_TOKEN
         self.engine = engine
+        self.prefill_chunk_tokens = max(16, int(prefill_chunk_tokens))
+        self._pending: dict | None = None      # the request being prefilled: {"r", "slot", "done"} (slot >= len(live))
+        self.prefill_chunks = 0
         self.eos = EOS_TOKEN if eos_token is None else eos_token
         self.queue = BoundedPriorityQueue(queue_capacity)
         self.idle_sleep = idle_sleep
@@ -139,9 +150,8 @@ class BatchScheduler:
 
     # ---- loop ------------------------------------------------------------------------------------
     def _loop(self) -> None:
-        import torch
         eng = self.engine
-        torch.cuda.set_device(eng.device)
+        eng.bind_thread()
         while not self._stop.is_set():
             try:
                 admitted = self._admit()
@@ -155,41 +165,80 @@ class BatchScheduler:
                     r.error = e
                     r.done.set()
                 for s in range(len(self.live)):
-                    eng._release_slot(s)
+                    eng.close_sequence(s)
                 self.live, self._pos = [], []
+                if self._pending is not None:
+                    self._pending["r"].error = e
+                    self._pending["r"].done.set()
+                    eng.close_sequence(self._pending["slot"])
+                    self._pending = None
 
     def _admit(self) -> bool:
+        """Makes progress on admission: at most one prompt chunk per call.  Returns True when something was done."""
         eng = self.engine
-        any_new = False
-        while len(self.live) < eng.max_batch:
-            r = self.queue.get_nowait()
-            if r is None:
-                break
-            if r.cancelled:
-                r.finish_reason = "cancelled"
-                r.done.set()
-                continue
+        if self._pending is None:
+            if len(self.live) >= eng.max_batch:
+                return False
+            r = None
+            while r is None:
+                r = self.queue.get_nowait()
+                if r is None:
+                    return False
+                if r.cancelled:
+                    r.finish_reason = "cancelled"
+                    r.done.set()
+                    r = None
             slot = len(self.live)
             total = min(eng.max_seq_len, len(r.prompt) + r.max_tokens)
             try:
-                first = eng.open_sequence(r.prompt, total, slot, r.params)
+                covered = eng.begin_sequence(r.prompt, total, slot, r.params)
             except MemoryError:
                 # KV pool exhausted: put the request back and wait for a sequence to finish
-                eng._release_slot(slot)
+                eng.close_sequence(slot)
                 self.queue.put(r)
-                break
+                return False
             except Exception as e:
-                eng._release_slot(slot)
+                eng.close_sequence(slot)
                 r.error = e
                 r.done.set()
-                continue
-            self.prompt_tokens += len(r.prompt)
-            self.live.append(r)
-            self._pos.append(len(r.prompt))
-            any_new = True
-            if self._emit(slot, first):
-                self._retire(slot)
-        return any_new
+                return True
+            self._pending = {"r": r, "slot": slot, "done": covered}
+        p = self._pending
+        r, slot = p["r"], p["slot"]
+        try:
+            if r.cancelled:
+                raise _Cancelled()
+            n = len(r.prompt)
+            # short remainders go in one piece; never leave a tail shorter than the engine's batched-prefill threshold
+            end = n if n - p["done"] <= self.prefill_chunk_tokens + eng.prefill_min_tokens else p["done"] + self.prefill_chunk_tokens
+            eng.prefill(r.prompt[p["done"]:end], slot, p["done"])
+            self.prefill_chunks += 1
+            p["done"] = end
+            if end < n:
+                return True
+            first = eng.finish_sequence(r.prompt, slot)
+        except _Cancelled:
+            eng.close_sequence(slot)
+            r.finish_reason = "cancelled"
+            r.done.set()
+            self._pending = None
+            return True
+        except Exception as e:
+            eng.close_sequence(slot)
+            r.error = e
+            r.done.set()
+            self._pending = None
+            return True
+        self._pending = None
+        dst = len(self.live)
+        if slot != dst:                          # sequences retired while this one was prefilling: close the gap
+            eng.move_slot(slot, dst)
+        self.prompt_tokens += len(r.prompt)
+        self.live.append(r)
+        self._pos.append(len(r.prompt))
+        if self._emit(dst, first):
+            self._retire(dst)
+        return True
 
     def _emit(self, slot: int, tok: int) -> bool:
         """Delivers a sampled token; returns True when the sequence is finished."""
@@ -222,7 +271,7 @@ class BatchScheduler:
         r.t_done = time.perf_counter()
         r.done.set()
         last = len(self.live) - 1
-        eng._release_slot(slot)
+        eng.close_sequence(slot)
         if slot != last:
             eng.move_slot(last, slot)
             self.live[slot] = self.live[last]
@@ -231,14 +280,10 @@ class BatchScheduler:
         self._pos.pop()
 
     def _step(self) -> None:
-        import torch
-        eng, r = self.engine, self.engine.runner
+        eng = self.engine
         B = len(self.live)
         # the device holds each slot's last token; positions are set from the host's view
-        pos = torch.tensor(self._pos, dtype=torch.int32).pin_memory()
-        r.positions[:B].copy_(pos, non_blocking=True)
-        r.step(B, sample=True)
-        toks = eng._read_tokens(B)      # tokens + the step's status word in one copy; raises on an expired wait
+        toks = eng.step_batch(self._pos)      # raises when a kernel of the step recorded an expired wait
         self.steps += 1
         for s in range(B):
             self._pos[s] += 1

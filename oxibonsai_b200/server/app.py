@@ -27,7 +27,7 @@ from fastapi.responses import HTMLResponse, JSONResponse, PlainTextResponse, Str
 from ..runtime.kv_policy import KvCachePolicy
 from ..runtime.metrics import InferenceMetrics, RequestRateTracker
 from ..runtime.presets import SamplingParams
-from ..runtime.resilience import CircuitBreaker, RateLimiter, check_health
+from ..runtime.resilience import CircuitBreaker, CircuitOpenError, RateLimiter, check_health
 from ..runtime.streaming import CorsConfig, RequestContext, RequestLogger
 from ..tokenizer import StreamingDecoder, chat_prompt
 from .config import ServerConfig
@@ -194,8 +194,12 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         def on_token(tok: int):
             loop.call_soon_threadsafe(q.put_nowait, tok)
 
+        # Breaker accounting happens here and only here, once per request: a rejection by the open breaker touches
+        # nothing (it must not restart the recovery timer), a failed submit or a failed / timed-out generation counts one
+        # failure, a generation that ran to its end counts one success.
         if not breaker.allow():
-            raise RuntimeError("circuit open")
+            raise CircuitOpenError("circuit open")
+        completed = False
         t0 = time.perf_counter()
         try:
             req = backend.submit(prompt_ids, params, max_tokens, on_token, rid)
@@ -254,6 +258,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                             yield delta, None
                         if hit:
                             req.cancel()
+                            completed = True
                             yield "", "stop"
                             return
                 if finished:
@@ -267,8 +272,15 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                     rest = delta + ("" if hit else text[sent:])
                     if rest:
                         yield rest, None
+                    completed = True
                     yield "", ("stop" if hit else (req.finish_reason or "stop"))
                     return
+        except (GeneratorExit, asyncio.CancelledError):
+            completed = None          # the consumer went away: neither a success nor a failure of the engine
+            raise
+        except Exception:
+            breaker.record_failure()
+            raise
         finally:
             dt = time.perf_counter() - t0
             metrics.tokens_generated.inc(n_tok)
@@ -280,7 +292,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             metrics.kv_utilization.set(util)
             kv_policy.observe(util)
             metrics.kv_level.set(kv_policy.metric_value())
-            breaker.record_success()
+            if completed:
+                breaker.record_success()
 
     def encode_chat(messages: list[dict]) -> list[int]:
         return tokenizer.encode(chat_prompt(messages, "chatml"))
@@ -365,7 +378,6 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                         yield "data: [DONE]\n\n"
                 except Exception as e:  # noqa: BLE001
                     metrics.errors.inc()
-                    breaker.record_failure()
                     yield f"data: {json.dumps({'error': {'message': str(e), 'type': 'server_error'}})}\n\n"
                 finally:
                     metrics.active_requests.dec()
@@ -397,8 +409,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             return error(504, str(e), "timeout", rid)
         except Exception as e:  # noqa: BLE001
             metrics.errors.inc()
-            breaker.record_failure()
-            status = 503 if type(e).__name__ in ("QueueFull", "CircuitOpenError") or "circuit" in str(e) else 500
+            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ == "QueueFull" else 500
             return error(status, str(e), "server_error", rid)
         finally:
             metrics.active_requests.dec()

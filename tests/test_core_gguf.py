@@ -28,6 +28,7 @@ def test_type_table_matches_block_layouts():
     assert type_info(G.TQ2_0) == ("TQ2_0", 256, 66)
     assert type_info(G.Q4_0)[1:] == (32, 18) and type_info(G.Q8_0)[1:] == (32, 34)
     assert [type_info(t)[2] for t in (10, 11, 12, 13, 14, 15)] == [84, 110, 144, 176, 210, 292]
+    assert type_info(9) == ("Q8_1", 32, 40)      # sized as the reference sizes it (crates/oxibonsai-core/src/gguf/types.rs:96)
     assert data_size(TQ2_0_G128, 4096 * 4096) == 4096 * 32 * 34
     with pytest.raises(_native.NativeError):
         type_info(99)

@@ -1,0 +1,139 @@
+"""Continuous-batching scheduler against a fake engine (no GPU): chunked admission interleaved with decode steps, slot
+compaction while a prompt is still prefilling, error and cancellation paths."""
+import threading
+import time
+
+from oxibonsai_b200.runtime.presets import SamplingParams
+from oxibonsai_b200.runtime.scheduler import BatchScheduler
+
+
+class FakeEngine:
+    """Token i of a sequence is (sum of its prompt + i) % 1000; records every call so that orderings can be asserted."""
+
+    max_batch, max_seq_len, prefill_min_tokens = 4, 100000, 16
+
+    def __init__(self, step_delay=0.0):
+        self.log = []
+        self.slots = {}            # slot -> {"seed", "n", "prefilled"}
+        self.step_delay = step_delay
+        self.fail_next_step = False
+
+    def bind_thread(self):
+        pass
+
+    def begin_sequence(self, prompt, max_total, slot, params):
+        assert slot not in self.slots
+        self.slots[slot] = {"seed": sum(prompt), "n": 0, "prefilled": 0, "len": len(prompt)}
+        self.log.append(("begin", slot, len(prompt)))
+        return 0
+
+    def prefill(self, part, slot, pos0):
+        s = self.slots[slot]
+        assert pos0 == s["prefilled"]
+        s["prefilled"] += len(part)
+        self.log.append(("prefill", slot, pos0, len(part)))
+
+    def finish_sequence(self, prompt, slot):
+        s = self.slots[slot]
+        assert s["prefilled"] == len(prompt)
+        self.log.append(("finish", slot))
+        s["n"] = 1
+        return s["seed"] % 1000
+
+    def step_batch(self, positions):
+        if self.fail_next_step:
+            self.fail_next_step = False
+            raise RuntimeError("decode step reported status 2")
+        time.sleep(self.step_delay)
+        B = len(positions)
+        self.log.append(("step", B))
+        out = []
+        for b in range(B):
+            s = self.slots[b]
+            assert positions[b] == s["len"] + s["n"] - 1
+            out.append((s["seed"] + s["n"]) % 1000)
+            s["n"] += 1
+        return out
+
+    def move_slot(self, src, dst):
+        self.log.append(("move", src, dst))
+        self.slots[dst] = self.slots.pop(src)
+
+    def close_sequence(self, slot):
+        self.slots.pop(slot, None)
+
+
+def _expected(prompt, n):
+    return [(sum(prompt) + i) % 1000 for i in range(n)]
+
+
+def test_prompt_chunks_interleave_with_decode_steps():
+    eng = FakeEngine()
+    sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=64)
+    a = sched.submit(list(range(1, 21)), SamplingParams(), 40)
+    sched.start()
+    while not a.tokens:
+        time.sleep(0.001)
+    b = sched.submit(list(range(330)), SamplingParams(), 5)     # 330 tokens = 4 x 64 + 74: a tail of 10 would be shorter than the
+    #                                                             engine's batched-prefill threshold, so it joins the last chunk
+    assert b.wait(10) == _expected(list(range(330)), 5) and a.wait(10) == _expected(list(range(1, 21)), 40)
+    sched.stop()
+    chunks = [e for e in eng.log if e[0] == "prefill" and e[1] == 1]
+    assert [c[3] for c in chunks] == [64, 64, 64, 64, 74]
+    # between two chunks of the newcomer the running stream got a decode step
+    idx = [eng.log.index(c) for c in chunks]
+    for i0, i1 in zip(idx, idx[1:]):
+        assert ("step", 1) in eng.log[i0:i1]
+    assert sched.prefill_chunks >= 5
+
+
+def test_slot_gap_is_closed_when_a_stream_ends_during_a_prefill():
+    eng = FakeEngine()
+    sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=32)
+    a = sched.submit([5] * 20, SamplingParams(), 3)             # ends after three tokens ...
+    sched.start()
+    while not a.tokens:
+        time.sleep(0.001)
+    b = sched.submit([7] * 400, SamplingParams(), 6)            # ... while this one is still being prefilled into slot 1
+    assert a.wait(10) == _expected([5] * 20, 3)
+    assert b.wait(10) == _expected([7] * 400, 6)
+    sched.stop()
+    assert ("move", 1, 0) in eng.log and not eng.slots
+
+
+def test_failed_step_fails_live_and_pending_requests_and_the_loop_survives():
+    eng = FakeEngine(step_delay=0.002)
+    sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=32).start()
+    a = sched.submit([1] * 20, SamplingParams(), 1000)
+    while not a.tokens:
+        time.sleep(0.001)
+    b = sched.submit([2] * 4000, SamplingParams(), 4)
+    while not any(e[0] == "prefill" and e[1] == 1 for e in eng.log):
+        time.sleep(0.001)
+    eng.fail_next_step = True
+    for r in (a, b):
+        try:
+            r.wait(10)
+            raise AssertionError("expected the step failure to surface")
+        except RuntimeError as e:
+            assert "status 2" in str(e)
+    c = sched.submit([3] * 20, SamplingParams(), 4)
+    assert c.wait(10) == _expected([3] * 20, 4)
+    sched.stop()
+
+
+def test_cancel_while_prefilling_frees_the_slot():
+    eng = FakeEngine(step_delay=0.001)
+    sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=16).start()
+    a = sched.submit([1] * 20, SamplingParams(), 200)
+    while not a.tokens:
+        time.sleep(0.001)
+    b = sched.submit([2] * 5000, SamplingParams(), 4)
+    while not any(e[0] == "prefill" and e[1] == 1 for e in eng.log):
+        time.sleep(0.001)
+    b.cancel()
+    assert b.done.wait(10) and b.finish_reason == "cancelled"
+    a.cancel()
+    assert a.done.wait(10)
+    sched.stop()
+    assert not eng.slots

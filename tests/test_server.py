@@ -264,3 +264,59 @@ def test_serial_backend_serves_single_request_engines():
     [t.join() for t in ts]
     assert out == ["serial ok"] * 4 and eng.overlaps == 0
     assert c.get("/v1/models").json()["data"][0]["id"] == "generic-q8"
+
+
+class _FailingGeneration(FakeBackend):
+    """Accepts the request and then fails inside the generation (the engine raised while decoding)."""
+
+    def __init__(self):
+        super().__init__()
+        self.broken = True
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id):
+        if not self.broken:
+            return super().submit(prompt, params, max_tokens, on_token, request_id)
+        r = _Req()
+        r.error, r.finish_reason = RuntimeError("kernel reported status 2"), "error"
+        r.done.set()
+        return r
+
+
+def test_breaker_opens_on_generation_errors_and_recovers_under_steady_traffic():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.runtime.resilience import CircuitState
+    from oxibonsai_b200.server.app import create_app
+    be = _FailingGeneration()
+    app = create_app(be, ByteTokenizer(), ServerConfig())
+    br = app.state.breaker
+    now = [1000.0]
+    br._clock = lambda: now[0]
+    c = TestClient(app)
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4}
+    for i in range(br.config.failure_threshold):
+        assert br.state == CircuitState.CLOSED
+        assert c.post("/v1/chat/completions", json=body).status_code == 500
+        assert br.failures == i + 1 or br.state == CircuitState.OPEN      # failures accumulate: nothing zeroes them in between
+    assert br.state == CircuitState.OPEN
+    opened_at = br._opened_at
+    # rejected requests keep arriving: they are answered 503 and leave the breaker (and its recovery timer) alone
+    for _ in range(4):
+        now[0] += 5.0
+        assert c.post("/v1/chat/completions", json=body).status_code == 503
+    assert br.state == CircuitState.OPEN and br._opened_at == opened_at and br.total_rejected == 4
+    # after the recovery time the next request is let through as a probe; the engine is healthy again
+    now[0] = opened_at + br.config.recovery_seconds + 0.1
+    be.broken = False
+    assert c.post("/v1/chat/completions", json=body).status_code == 200
+    assert br.state == CircuitState.HALF_OPEN
+    assert c.post("/v1/chat/completions", json=body).status_code == 200
+    assert br.state == CircuitState.CLOSED and br.failures == 0
+
+
+def test_breaker_counts_a_failed_submit_once():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+    app = create_app(FakeBackend(fail=True), ByteTokenizer(), ServerConfig())
+    c = TestClient(app)
+    assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]}).status_code == 500
+    assert app.state.breaker.failures == 1
