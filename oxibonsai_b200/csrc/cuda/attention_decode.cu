@@ -301,14 +301,6 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
   }
 }
 
-#ifdef BONSAI_ATTN_TRACE
-// Optional timeline for tuning: clock64() stamps of thread 0 of every CTA (16 slots each).
-__device__ long long* g_attn_trace = nullptr;
-#define AT_STAMP(slot) do { if (g_attn_trace != nullptr && threadIdx.x == 0) g_attn_trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define AT_STAMP(slot) do { } while (0)
-#endif
-
 // ---- head_dim 128, compressed caches: half a warp per token --------------------------------------------
 // A 128-wide f16 row is 256 bytes = 16 lanes x 16 bytes, so the two halves of a warp walk two tokens
 // at once with full-width loads; kH128Unroll such pairs are requested before any is consumed (8
@@ -371,7 +363,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
   const int kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, sub = lane & 15;
-  AT_STAMP(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int* bt = block_table + (size_t)b * max_pages;
   const int pshift = 31 - __clz(pool.page_size), pmask = pool.page_size - 1;   // the launcher admits power-of-two pages only
@@ -395,7 +386,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     }
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  AT_STAMP(1);
   const int len = positions[b] + 1 + extra_len;
   const int chunk = (len + nsplit - 1) / nsplit;
   const int t0 = split * chunk, t1 = min(len, t0 + chunk);
@@ -475,7 +465,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
         for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(p[u][g], vf[j], acc[g][j]);
     }
   }
-  AT_STAMP(2);
   // fold the two halves of the warp (they saw different tokens)
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -505,7 +494,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     }
   }
   __syncthreads();
-  AT_STAMP(3);
   for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
     int g = idx / hd, d = idx - g * hd;
     float M = -INFINITY;
@@ -526,10 +514,8 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
       ws_ml[o * 2 + 1] = L;
     }
   }
-  AT_STAMP(4);
   __threadfence();
   __syncthreads();
-  AT_STAMP(5);
   if (threadIdx.x == 0) {
     int* ctr = counters + (size_t)b * nkv + kvh;
     int prev = atomicAdd(ctr, 1);
@@ -537,7 +523,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     if (s_last) *ctr = 0;
   }
   __syncthreads();
-  AT_STAMP(6);
   if (!s_last) return;
   __threadfence();
   // Merge of the splits by the last CTA of this (sequence, kv head).  Every dependent trip to L2 costs ~600 cycles
@@ -599,7 +584,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_h128_kernel(const float* _
     const int idx = threadIdx.x + k * 256;
     if (idx < G * hd) out[hb0 * hd + idx] = a[k];
   }
-  AT_STAMP(7);
 }
 
 template <int KVT>
@@ -651,12 +635,6 @@ extern "C" {
 
 // 1: f16 caches with head_dim 128 use the CUDA-core kernel instead of the tensor-core one (comparisons, tests)
 void bonsai_attn_decode_force_cuda_cores(int on) { bonsai::g_attn_force_cuda_cores = on; }
-
-#ifdef BONSAI_ATTN_TRACE
-int bonsai_attn_decode_trace(long long* buf) {
-  return cudaMemcpyToSymbol(bonsai::g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 // qkv: f32 [batch][qkv_stride] holding q | k | v heads.  Writes normalised+rotated q to q_out
 // [batch][nq][hd] and appends k, v at positions[b] through block_table [batch][max_pages].

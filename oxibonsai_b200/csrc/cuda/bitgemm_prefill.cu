@@ -67,21 +67,6 @@ struct PfParams {
   int* ws_count;           // [tiles] arrival counters, zero between launches
 };
 
-#ifdef BONSAI_PF_TRACE
-// Optional timeline for tuning: clock64() stamps per CTA (64 slots each) into a buffer set with bonsai_bitgemm_prefill_trace.
-__device__ long long* g_pf_trace = nullptr;
-#define PF_STAMP(slot) do { if (g_pf_trace != nullptr) g_pf_trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
-// timing experiments (results are wrong): 1 = no activation copies, 2 = no MMA instructions, 4 = no expansion
-__device__ int g_pf_skip = 0;
-#define PF_SKIP(bit) (g_pf_skip & (bit))
-#define PF_CLK(var) long long var = clock64()
-#define PF_PUT(slot, v) do { if (g_pf_trace != nullptr) g_pf_trace[blockIdx.x * 64 + (slot)] = (v); } while (0)
-#else
-#define PF_CLK(var) do { } while (0)
-#define PF_PUT(slot, v) do { } while (0)
-#define PF_SKIP(bit) 0
-#define PF_STAMP(slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -185,7 +170,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   const int n = (int)(pf_range_start(p.streamk, blockIdx.x + 1, grid, ntiles, npairs) - I0);   // pairs of this CTA
   const int tile0 = (int)(I0 / npairs), pair0 = (int)(I0 - (long long)tile0 * npairs);
 
-  if (t == 0) PF_STAMP(0);
   // Programmatic dependent launch: this CTA may start while the previous kernel of the stream is still running.  Set-up,
   // TMEM allocation and the expanders' first weight loads depend on nothing it writes; the warps that touch its outputs
   // (activation copies, epilogue reads and writes, the work-split workspace) wait for it below.
@@ -211,7 +195,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   tc::tc_fence_after();
   const uint32_t taddr = tmem_slot;
   bool failed = false;
-  if (t == 0) PF_STAMP(1);
 
   // Issuer warps run their loops with all 32 lanes (uniform control flow, every lane waits on the barriers) and elect
   // lane 0 only for the single-thread instructions.
@@ -236,16 +219,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
           const int it = 2 * q + g0, bs = (it / GK) % NBS;
           if (!__all_sync(0xffffffffu, tc::mbar_wait(&empty_bar[bs], (((it / GK) / NBS) & 1) ^ 1))) { failed = true; break; }
           if (lane == 0) {
-            if (PF_SKIP(1)) {
-              tc::mbar_arrive(&full_bar[bs]);
-            } else {
-              tc::mbar_arrive_expect_tx(&full_bar[bs], GK * (kPfBBytes + (p.dense ? kPfABytes : 0)));
+            tc::mbar_arrive_expect_tx(&full_bar[bs], GK * (kPfBBytes + (p.dense ? kPfABytes : 0)));
 #pragma unroll
-              for (int h = 0; h < GK; ++h) {
-                const int s = (it + h) % S, kb = 2 * pair + g0 + h;
-                tma_load_2d(sB + s * kPfBBytes, &xmap, kb * 64, tok0, &full_bar[bs]);
-                if (p.dense) tma_load_2d(sA + s * kPfABytes, &amap, kb * 64, row0, &full_bar[bs]);
-              }
+            for (int h = 0; h < GK; ++h) {
+              const int s = (it + h) % S, kb = 2 * pair + g0 + h;
+              tma_load_2d(sB + s * kPfBBytes, &xmap, kb * 64, tok0, &full_bar[bs]);
+              if (p.dense) tma_load_2d(sA + s * kPfABytes, &amap, kb * 64, row0, &full_bar[bs]);
             }
           }
           __syncwarp();
@@ -273,7 +252,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
           if (!__all_sync(0xffffffffu, tc::mbar_wait(&full_bar[bs], ((it / GK) / NBS) & 1))) { failed = true; break; }
           tc::tc_fence_after();
           if (lane == 0) {
-            if (it < 16) PF_STAMP(8 + it);
 #pragma unroll
             for (int h = 0; h < GK; ++h) {
               const int s = (it + h) % S;
@@ -295,7 +273,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
       if (pair == npairs - 1 || q == n - 1) {   // end of the segment: every issuer reports its MMAs of it done
         if (lane == 0) {
           tc::mma_commit(&accf_bar[ab]);
-          if (mw == 0) PF_STAMP(24 + (seg < 3 ? seg : 3));
         }
         __syncwarp();
         ++seg;
@@ -355,20 +332,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
             for (int v = 0; v < NV; ++v) {
               const int it = 2 * qq + hh0 + v, s = it % S, bs = (it / GK) % NBS;
               const uint32_t par = (((it / GK) / NBS) & 1) ^ 1;
-              PF_CLK(c0);
               if (!failed && !tc::mbar_wait_sleep<kPfPollNs>(&empty_bar[bs], par)) failed = true;
               if (!failed) {
-                if (t == 0 && qq < 6) PF_STAMP(2 + qq);
-                PF_CLK(c1);
-                if (!PF_SKIP(4)) pf_expand(sA + s * kPfABytes, r, cur[v], d2);
-                PF_CLK(c2);
+                pf_expand(sA + s * kPfABytes, r, cur[v], d2);
                 tc::fence_proxy_async();
                 __syncwarp();
-                PF_CLK(c3);
                 if (lane == 0) tc::mbar_arrive(&full_bar[bs]);
-#ifdef BONSAI_PF_TRACE
-                if (t == 0 && (qq == 8 || qq == 20)) { const int b = qq == 8 ? 44 : 50; PF_CLK(c4); PF_PUT(b, c0); PF_PUT(b + 1, c1 - c0); PF_PUT(b + 2, c2 - c1); PF_PUT(b + 3, c3 - c2); PF_PUT(b + 4, c4 - c3); }
-#endif
               }
             }
           }
@@ -396,7 +365,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
       float* part = p.ws_part + (size_t)(2 * blockIdx.x + (q == 0 ? 0 : 1)) * (128 * TOK);
       if (!tc::mbar_wait_warp<64>(&accf_bar[ab], (seg >> 1) & 1, lane)) { failed = true; break; }
       tc::tc_fence_after();
-      if (a == 0 && seg < 2) PF_STAMP(28 + 4 * seg);
       constexpr int CB = 16;   // columns per step: accumulator block + second operand block + residual block in registers
 #pragma unroll 1
       for (int c0 = 0; c0 < TOK; c0 += CB) {
@@ -435,7 +403,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&acce_bar[ab]);
-      if (a == 0 && seg < 2) PF_STAMP(29 + 4 * seg);
       if (!whole) {
         // the tile's K extent is shared with neighbouring CTAs: the last one to arrive sums the partials
         __threadfence();
@@ -454,7 +421,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
           s_info[2] = cl;
         }
         pf_epi_barrier();
-        if (a == 0 && seg < 2) PF_STAMP(30 + 4 * seg);
         if (s_info[0]) {
           const int cf = s_info[1], nc = s_info[2] - cf + 1;
           __threadfence();
@@ -471,18 +437,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
             for (int i0 = 0; i0 < nc && !failed; i0 += 5) {
               const int cnt = min(5, nc - i0);
               if (a == 0) {
-                PF_STAMP(36);
                 asm volatile("fence.proxy.async.global;" ::: "memory");   // the partials were written through the generic proxy
-                PF_STAMP(37);
                 tc::mbar_arrive_expect_tx(&red_bar, (uint32_t)(cnt * ncols * 128 * sizeof(float)));
                 for (int i = 0; i < cnt; ++i)
                   tc::bulk_g2s(stage + i * (128 * TOK), p.ws_part + (size_t)s_slots[i0 + i] * (128 * TOK),
                                (uint32_t)(ncols * 128 * sizeof(float)), &red_bar);
               }
               // every thread polls the same barrier with the same limit, so they agree on the outcome
-              if (a == 0) PF_STAMP(38);
               const bool landed = tc::mbar_wait_sleep<32>(&red_bar, red_phase & 1);
-              if (a == 0) PF_STAMP(39);
               ++red_phase;
               const bool last = i0 + cnt >= nc;
               for (int cb = 0; cb < ncols && landed; cb += 8) {
@@ -507,7 +469,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
                   else if (cb + j < ncols) carry[(cb + j) * 128 + a] = v[j];
                 }
               }
-              if (a == 0) PF_STAMP(40);
               pf_epi_barrier();   // every thread has read the slots before the next round overwrites them
               if (!landed) failed = true;
             }
@@ -520,7 +481,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
           }
           if (a == 0) p.ws_count[tile] = 0;
         }
-        if (a == 0 && seg < 2) PF_STAMP(31 + 4 * seg);
         pf_epi_barrier();   // s_info / s_slots are free for the next segment
       }
       q += len;
@@ -529,7 +489,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) bitgemm_prefill_kernel(const __
   }
   tc::tc_fence_before();
   __syncthreads();
-  if (t == 0) PF_STAMP(63);
   if (warp == kPfMmaWarp) tc::tmem_dealloc(taddr, 2 * kAccCols);
 }
 
@@ -604,13 +563,6 @@ static int launch_prefill(const CUtensorMap& xmap, const CUtensorMap& amap, bons
 }
 
 extern "C" {
-
-#ifdef BONSAI_PF_TRACE
-int bonsai_bitgemm_prefill_trace(long long* buf, int skip) {
-  if (cudaMemcpyToSymbol(bonsai::g_pf_skip, &skip, sizeof(skip)) != cudaSuccess) return BONSAI_CUDA_LAUNCH_FAILED;
-  return cudaMemcpyToSymbol(bonsai::g_pf_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : BONSAI_CUDA_LAUNCH_FAILED;
-}
-#endif
 
 // bytes of workspace that lets every shape this library launches use the balanced (stream-K) distribution
 size_t bonsai_bitgemm_prefill_ws_bytes() {

@@ -1,25 +1,28 @@
 // Batch-1 decode GEMV that streams packed weights through shared memory with bulk async copies and multiplies on
-// the warp-level f16 tensor cores with a one-instruction weight decode.
+// the warp-level integer tensor cores with a one-instruction decode of four weights.
 //
 // Why another GEMV: the planar-layout kernels (bitgemv_warp.cu, bitgemv_hmma.cu) spend ~2.5 thread instructions per
-// weight on shift + mask + FMA and hold their loads in registers, which leaves them issue- and latency-bound at a
-// quarter of the memory roofline.  Here
+// weight on shift + mask + FMA.  On this GPU the integer/logic pipe issues one warp instruction every two cycles, so
+// those kernels are bound by their decode instructions at a quarter of the memory roofline (measured: the same time
+// with the weights resident in L2).  Here
 //   * weights live in the "S16" layout: tiles of 16 output rows, one 544-byte block per (tile, 128-input group) =
 //     32 lanes x 16 bytes of 2-bit codes in MMA-fragment order + 16 f16 group scales.  A CTA owns a contiguous range
-//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a shared-memory
-//     ring with cp.async.bulk (by default four stages of 17 KB: 70 KB in flight per SM).  The copies are issued before
-//     griddepcontrol.wait: under programmatic dependent launch the next GEMV's weights stream in while the previous
-//     kernel is still running;
-//   * a code c = w + 1 in {0, 1, 2} sitting at bits p, p+1 of a 16-bit half becomes the f16 number 2^(10-p) + c with
-//     one LOP3: (word & mask) | magic, where magic is the exponent pattern of 2^(10-p) and the code lands in the
-//     mantissa.  Two codes (both halves of a word) per instruction, no sign handling, no conversion.  Three shifted
-//     views of a word (x << 6, x, x >> 6) bring its eight code slots to p in {4, 6, 8}, so the offsets are 64, 16, 4;
-//   * mma.sync.m16n8k16 multiplies the offset weights with the f16 activations and accumulates in f32; the offset
-//     part, sum_k (2^(10-p(k)) + 1) x_k, is the same for every row, is computed once per 128-input group in the
-//     prologue and subtracted before the group's f16 scale is applied in f32;
+//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a four-stage
+//     shared-memory ring with cp.async.bulk (17 KB per copy, 70 KB in flight per SM);
+//   * a code c = w + 1 in {0, 1, 2} occupies one 2-bit field of a byte; `word & (0x03030303 << 2j)` is the u8 vector
+//     (4^j c) of four weights: ONE logic instruction per four weights, no shift, no sign handling.  The 4^j is not
+//     undone on the weights: MMA step j of a group uses field j of every word, and the activations are laid out so
+//     that step j only reaches output columns 2j and 2j+1 of mma.sync.m16n8k32 (u8 x s8 -> s32) - every other column
+//     of its B operand is zero.  After the group's four steps, column 2j (+1) holds 4^j times the dot product of
+//     step j's 32 inputs, the lane that owns the column scales it by 4^-j in f32, and a quad reduction at the end of
+//     the tile adds the four partial sums;
+//   * activations are quantised per 128-input group to two int8 terms, x = s (q1 + q2 / 254), |q| <= 127 - sixteen
+//     bits relative to the group's largest value; the terms are the even and odd output columns.  Products and sums
+//     are exact integers; the +1 of the codes is removed by starting the accumulators at -4^j * sum(q) of the step;
 //   * sixteen consumer warps take two blocks each per stage, keep per-tile partial sums in registers and meet in
 //     shared memory once at the end; partials are added in warp order, so results do not depend on timing.
-// That is ~0.95 thread instructions per weight (0.5 LOP3, 0.125 shift, 0.125 MMA, the rest loads and bookkeeping).
+// Per (tile, group) block a thread issues 16 logic ops, 4 MMAs, 4 loads, 8 integer multiplies that build the
+// zero-padded B operands and a dozen f32 ops: ~0.8 instructions per weight.
 //
 // Epilogues: store, residual add, SwiGLU over interleaved gate/up rows, and the tensor-parallel one: every finished
 // row goes to all peers as one 8-byte {value, tag} store and the same thread polls its own slots for the peers'
@@ -39,41 +42,47 @@ enum { SEPI_STORE = 0, SEPI_RESID = 1, SEPI_SWIGLU = 2, SEPI_TP = 3 };
 constexpr int kS16Warps = 16;                                    // consumer warps; warp 16 is the copy producer
 constexpr int kS16Threads = (kS16Warps + 1) * 32;
 constexpr int kS16BlockBytes = 544;                              // 512 B codes + 32 B scales
-constexpr int kS16MaxStages = 16;
+constexpr int kS16Bpw = 2;                                       // blocks per warp per stage
+constexpr int kS16StageBlocks = kS16Bpw * kS16Warps;
+constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes; // 17408
+constexpr int kS16Stages = 4;                                    // power of two
 constexpr int kS16MaxTiles = 12;                                 // tiles per CTA (size of the partial-sum area)
-constexpr uint32_t kS16WaitLimit = 1u << 21;                     // polls (with a short sleep in between): about a second
+constexpr uint32_t kS16WaitLimit = 1u << 21;                     // polls with a short sleep in between: about a second
+constexpr float kS16Term2 = 254.0f;                              // x = s * (q1 + q2 / 254)
 
-// Pipeline shape, settable through bonsai_s16_tune: blocks per warp per stage (1 or 2), ring stages, and the sleep
-// between two polls of a ring barrier.  Back-to-back polling by sixteen waiting warps saturates the shared-memory
-// pipe and delays the copy completions and the producer's own barrier traffic.
-static int g_s16_bpw = 2, g_s16_stages = 4, g_s16_sleep_ns = 32, g_s16_pdl = 1;
+// Launched with programmatic dependent launch (the prologue of the next kernel overlaps the tail of this one) unless
+// switched off through bonsai_s16_tune.
+static int g_s16_pdl = 1;
 
-// offset + 1 of MMA step mm (= code slot mm): slots reach mantissa position 6, 8 | 4, 6, 8 | 4, 6, 8
-__device__ __constant__ float kS16Off[8] = {17.0f, 5.0f, 65.0f, 17.0f, 5.0f, 65.0f, 17.0f, 5.0f};
+__device__ __forceinline__ void s16_imma(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-__device__ __forceinline__ void s16_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// Integer multiply (runs on the FMA pipe, which this kernel leaves idle; the logic pipe is the scarce one).
+__device__ __forceinline__ uint32_t s16_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.lo.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
 // 512 consumer threads only (the producer warp never joins)
 __device__ __forceinline__ void s16_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kS16Warps * 32) : "memory"); }
 
-// Bounded wait on a ring barrier: lane 0 polls, the outcome is broadcast.  Returns false on expiry or when another
-// warp has already given up (*abort set).
-__device__ __forceinline__ bool s16_poll(uint64_t* bar, uint32_t parity, volatile int* abort, int sleep_ns) {
+// Bounded wait on a ring barrier.  Returns false on expiry or when another warp has already given up (*abort set).
+__device__ __forceinline__ bool s16_poll(uint64_t* bar, uint32_t parity, volatile int* abort) {
   for (uint32_t i = 0; i < kS16WaitLimit; ++i) {
     if (tc::mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u && *abort) break;
-    if (sleep_ns > 0) __nanosleep(sleep_ns);
+    __nanosleep(32);
   }
   *abort = 1;
   return false;
 }
-__device__ __forceinline__ bool s16_wait(uint64_t* bar, uint32_t parity, int lane, volatile int* abort, int sleep_ns) {
+__device__ __forceinline__ bool s16_wait(uint64_t* bar, uint32_t parity, int lane, volatile int* abort) {
   int ok = 1;
-  if (lane == 0) ok = s16_poll(bar, parity, abort, sleep_ns) ? 1 : 0;
+  if (lane == 0) ok = s16_poll(bar, parity, abort) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -86,46 +95,37 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
   return v;
 }
 
-// One (tile, group) block against the group's 128 activations.  Adds scale * (W x) of rows g and g + 8 to tot.
-__device__ __forceinline__ void s16_block(const uint8_t* __restrict__ blk, const __half* __restrict__ xg, float og, int lane,
-                                          float& tot_lo, float& tot_hi) {
-  const int g = lane >> 2, t = lane & 3;
+// Per (group, step) record of the activation side: the step's accumulator start values and f32 factor.
+struct __align__(16) S16Step {
+  int og0, og1;      // 4^j * sum of the step's q1 (q2) values: the part of the integer dot product that the +1 of the codes adds
+  float sx;          // group scale of the activations times 4^-j
+  float pad;
+};
+
+// One (tile, group) block.  xq_lane: the lane's eight int8 activations of step 0 of the group (term g & 1; step j is
+// 32 bytes further); st_lane: the S16Step record of the lane's accumulator columns (step t of the group).  sel[j] is 1
+// when this lane's B column belongs to step j, else 0.  Adds the lane's share (its step, both terms) of
+// scale * (W x) of rows g and g + 8 to tot.
+__device__ __forceinline__ void s16_block(const uint8_t* __restrict__ blk, const int8_t* __restrict__ xq_lane, const S16Step* __restrict__ st_lane,
+                                          int lane, const uint32_t (&sel)[4], float& tot_lo, float& tot_hi) {
+  const int g = lane >> 2;
   const uint4 cw = *reinterpret_cast<const uint4*>(blk + lane * 16);
   const uint32_t sc = *reinterpret_cast<const uint32_t*>(blk + 512 + 4 * g);
-  const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
-  uint32_t lo[4], hi[4];
+  const S16Step st = *st_lane;
+  int acc[4] = {-st.og0, -st.og1, -st.og0, -st.og1};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    lo[i] = w[i] << 6;
-    hi[i] = w[i] >> 6;
-  }
-  float accA[4] = {0.0f, 0.0f, 0.0f, 0.0f}, accB[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  const uint4* xv4 = reinterpret_cast<const uint4*>(xg + 8 * t);
-  constexpr uint32_t M4 = 0x00300030u, M6 = 0x00C000C0u, M8 = 0x03000300u;
-  constexpr uint32_t E4 = 0x54005400u, E6 = 0x4C004C00u, E8 = 0x44004400u;   // 64, 16, 4
-  {
-    const uint4 xv = xv4[0];    // inputs 8t .. 8t+7 of the group
-    s16_mma(accA, (lo[0] & M6) | E6, (lo[1] & M6) | E6, (lo[2] & M6) | E6, (lo[3] & M6) | E6, xv.x, xv.y);
-    s16_mma(accB, (lo[0] & M8) | E8, (lo[1] & M8) | E8, (lo[2] & M8) | E8, (lo[3] & M8) | E8, xv.z, xv.w);
-  }
-  {
-    const uint4 xv = xv4[4];    // 32 + 8t ..
-    s16_mma(accA, (w[0] & M4) | E4, (w[1] & M4) | E4, (w[2] & M4) | E4, (w[3] & M4) | E4, xv.x, xv.y);
-    s16_mma(accB, (w[0] & M6) | E6, (w[1] & M6) | E6, (w[2] & M6) | E6, (w[3] & M6) | E6, xv.z, xv.w);
-  }
-  {
-    const uint4 xv = xv4[8];    // 64 + 8t ..
-    s16_mma(accA, (w[0] & M8) | E8, (w[1] & M8) | E8, (w[2] & M8) | E8, (w[3] & M8) | E8, xv.x, xv.y);
-    s16_mma(accB, (hi[0] & M4) | E4, (hi[1] & M4) | E4, (hi[2] & M4) | E4, (hi[3] & M4) | E4, xv.z, xv.w);
-  }
-  {
-    const uint4 xv = xv4[12];   // 96 + 8t ..
-    s16_mma(accA, (hi[0] & M6) | E6, (hi[1] & M6) | E6, (hi[2] & M6) | E6, (hi[3] & M6) | E6, xv.x, xv.y);
-    s16_mma(accB, (hi[0] & M8) | E8, (hi[1] & M8) | E8, (hi[2] & M8) | E8, (hi[3] & M8) | E8, xv.z, xv.w);
+  for (int j = 0; j < 4; ++j) {
+    // B operand of step j: the lane's eight activations of that step if the lane's column belongs to step j, else zeros
+    const uint2 xb = *reinterpret_cast<const uint2*>(xq_lane + 32 * j);
+    const uint32_t m = 0x03030303u << (2 * j);
+    s16_imma(acc, cw.x & m, cw.y & m, cw.z & m, cw.w & m, s16_mul(xb.x, sel[j]), s16_mul(xb.y, sel[j]));
   }
   const __half2 s2 = *reinterpret_cast<const __half2*>(&sc);
-  tot_lo = fmaf(__low2float(s2), (accA[0] + accB[0]) - og, tot_lo);
-  tot_hi = fmaf(__high2float(s2), (accA[2] + accB[2]) - og, tot_hi);
+  // columns 2t and 2t+1 are the two terms of the lane's step: x = s (q1 + q2 / 254)
+  const float v_lo = fmaf((float)acc[1], 1.0f / kS16Term2, (float)acc[0]);
+  const float v_hi = fmaf((float)acc[3], 1.0f / kS16Term2, (float)acc[2]);
+  tot_lo = fmaf(__low2float(s2) * st.sx, v_lo, tot_lo);
+  tot_hi = fmaf(__high2float(s2) * st.sx, v_hi, tot_hi);
 }
 
 struct S16Args {
@@ -137,23 +137,19 @@ struct S16Args {
   int* status;               // device int, set non-zero when a bounded wait expired (may be null)
   float eps;
   int N, K, epi;
-  int nstages, sleep_ns;     // ring depth and poll back-off
 };
 
-template <int BPW>
-__global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, TpComm tp) {
-  constexpr int kS16StageBlocks = BPW * kS16Warps;
-  constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes;   // 8704 or 17408
+__global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, TpComm tp) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int K = a.K, ng = K >> 7;
-  const int kS16Stages = a.nstages;
+  const int term_stride = K + 32;                              // second term sits 32 bytes off a multiple of 128: no bank clash
   uint8_t* ring = smem;
-  __half* xs = reinterpret_cast<__half*>(smem + kS16Stages * kS16StageBytes);
-  float* og = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + (size_t)K * 2);
-  float* part = og + ((ng + 3) & ~3);                      // [kS16MaxTiles][kS16Warps][16]
+  int8_t* xq = reinterpret_cast<int8_t*>(smem + kS16Stages * kS16StageBytes);      // [2][K + 32]
+  S16Step* steps = reinterpret_cast<S16Step*>(xq + 2 * term_stride);                // [ng][4]
+  float* part = reinterpret_cast<float*>(steps + (size_t)ng * 4);                   // [kS16MaxTiles][kS16Warps][16]
   uint64_t* full = reinterpret_cast<uint64_t*>(part + kS16MaxTiles * kS16Warps * 16);
-  uint64_t* empty = full + kS16MaxStages;
-  float* s32 = reinterpret_cast<float*>(empty + kS16MaxStages);   // [32]
+  uint64_t* empty = full + kS16Stages;
+  float* s32 = reinterpret_cast<float*>(empty + kS16Stages);   // [32]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(s32 + 32);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -179,8 +175,8 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
     // ---- producer: one lane streams the CTA's byte range through the ring (weights depend on no earlier kernel) ----
     if (lane == 0) {
       for (int s = 0; s < nstage_total; ++s) {
-        const int slot = s % kS16Stages;
-        if (s >= kS16Stages && !s16_poll(&empty[slot], ((s / kS16Stages) - 1) & 1, abort_flag, a.sleep_ns)) break;
+        const int slot = s & (kS16Stages - 1);
+        if (s >= kS16Stages && !s16_poll(&empty[slot], ((s / kS16Stages) - 1) & 1, abort_flag)) break;
         const int b0 = s * kS16StageBlocks;
         const int nb = min(kS16StageBlocks, nb_total - b0);
         const uint32_t bytes = (uint32_t)nb * kS16BlockBytes;
@@ -203,10 +199,8 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
   for (int i = tid; i < kS16MaxTiles * kS16Warps * 16; i += NT) part[i] = 0.0f;   // nothing here depends on an earlier kernel
   asm volatile("griddepcontrol.wait;" ::: "memory");
   {
-    // activations: f32 -> (RMS-normalised) f16 in natural order, and the per-group offset sums
-    //   og[g] = sum over the group's inputs of (offset + 1) * x,
-    // taken from the rounded values while they are written: thread tid + i * NT holds inputs 4c..4c+3 of chunk c, a
-    // warp's 32 chunks are one 128-input group, and lane l's four inputs all belong to MMA step 2 * (l / 8) + (l & 1)
+    // Activations: f32 -> (RMS-normalised) -> two int8 terms per 128-input group.  Thread tid + i * NT holds the four
+    // inputs of chunk c; a warp's 32 chunks are one group and lanes 8j..8j+7 hold the 32 inputs of MMA step j.
     const int nch = K >> 2;
     const float4* x4 = reinterpret_cast<const float4*>(a.x);
     float4 keep[2];
@@ -230,20 +224,41 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
       tsum = warp_sum(tsum);
       inv = 1.0f / sqrtf(tsum / (float)K + a.eps);
     }
-    const float off = kS16Off[2 * (lane >> 3) + (lane & 1)];
     auto emit = [&](int c, float4 v) {      // whole warps enter (K % 128 == 0): c / 32 is the warp's group
       if (a.norm_w != nullptr) {
         const float4 ww = reinterpret_cast<const float4*>(a.norm_w)[c];
         v.x *= ww.x * inv; v.y *= ww.y * inv; v.z *= ww.z * inv; v.w *= ww.w * inv;
       }
-      const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
-      uint2 u;
-      u.x = *reinterpret_cast<const uint32_t*>(&h0);
-      u.y = *reinterpret_cast<const uint32_t*>(&h1);
-      reinterpret_cast<uint2*>(xs)[c] = u;
-      const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-      const float sg = warp_sum(off * ((f0.x + f0.y) + (f1.x + f1.y)));
-      if (lane == 0) og[c >> 5] = sg;
+      const float amax = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+      const float sx = amax > 0.0f ? amax * (1.0f / 127.0f) : 1.0f;
+      const float rs = 1.0f / sx;
+      const float f[4] = {v.x * rs, v.y * rs, v.z * rs, v.w * rs};
+      int q1[4], q2[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        q1[e] = max(-127, min(127, (int)rintf(f[e])));       // |f| <= 127 up to the rounding of the reciprocal
+        q2[e] = max(-127, min(127, (int)rintf((f[e] - (float)q1[e]) * kS16Term2)));
+      }
+      const uint32_t w1 = (uint32_t)(q1[0] & 255) | ((uint32_t)(q1[1] & 255) << 8) | ((uint32_t)(q1[2] & 255) << 16) | ((uint32_t)(q1[3] & 255) << 24);
+      const uint32_t w2 = (uint32_t)(q2[0] & 255) | ((uint32_t)(q2[1] & 255) << 8) | ((uint32_t)(q2[2] & 255) << 16) | ((uint32_t)(q2[3] & 255) << 24);
+      reinterpret_cast<uint32_t*>(xq)[c] = w1;
+      reinterpret_cast<uint32_t*>(xq + term_stride)[c] = w2;
+      // sums over the eight lanes of a step
+      int s1 = q1[0] + q1[1] + q1[2] + q1[3], s2 = q2[0] + q2[1] + q2[2] + q2[3];
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+      }
+      if ((lane & 7) == 0) {
+        const int j = lane >> 3;
+        S16Step r;
+        r.og0 = s1 * (1 << (2 * j));
+        r.og1 = s2 * (1 << (2 * j));
+        r.sx = sx * (1.0f / (float)(1 << (2 * j)));
+        r.pad = 0.0f;
+        steps[(size_t)(c >> 5) * 4 + j] = r;
+      }
     };
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -254,12 +269,22 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
     s16_bar();
   }
 
-  // ---- main loop: BPW consecutive blocks per warp per stage ----
+  // ---- main loop: two consecutive blocks per warp per stage ----
   {
+    const int g = lane >> 2, t = lane & 3;
+    // this lane supplies output column n = g = 2 * step + term of every B operand
+    const int my_step = g >> 1;
+    const uint32_t sel[4] = {my_step == 0 ? 1u : 0u, my_step == 1 ? 1u : 0u, my_step == 2 ? 1u : 0u, my_step == 3 ? 1u : 0u};
+    const int8_t* xq_lane = xq + (g & 1) * term_stride + 8 * t;        // + 128 * group + 32 * step
+    const S16Step* st_lane = steps + t;                                  // + 4 * group: the lane's accumulator columns belong to step t
     int cur_tile = -1;
     float tot_lo = 0.0f, tot_hi = 0.0f;
-    const int g = lane >> 2, t = lane & 3;
     auto flush = [&]() {
+      // the four lanes of a quad hold the four steps' shares of rows g and g + 8
+      tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 1);
+      tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 1);
+      tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 2);
+      tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 2);
       if (cur_tile >= 0 && t == 0) {
         float* p = part + ((size_t)cur_tile * kS16Warps + warp) * 16;
         p[g] += tot_lo;
@@ -267,28 +292,35 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
       }
       tot_lo = tot_hi = 0.0f;
     };
+    // (tile, group) of the warp's first block of the current stage, advanced by one stage's blocks per iteration
+    int tl = (kS16Bpw * warp) / ng, grp = (kS16Bpw * warp) - tl * ng;
     for (int s = 0; s < nstage_total; ++s) {
-      const int slot = s % kS16Stages;
-      if (!s16_wait(&full[slot], (s / kS16Stages) & 1, lane, abort_flag, a.sleep_ns)) break;
-      const uint8_t* st = ring + (size_t)slot * kS16StageBytes + (size_t)(BPW * warp) * kS16BlockBytes;
-      const int idx0 = s * kS16StageBlocks + BPW * warp;
-      int tl = idx0 / ng, grp = idx0 - tl * ng;
+      const int slot = s & (kS16Stages - 1);
+      if (!s16_wait(&full[slot], (s / kS16Stages) & 1, lane, abort_flag)) break;
+      const uint8_t* st = ring + (size_t)slot * kS16StageBytes + (size_t)(kS16Bpw * warp) * kS16BlockBytes;
+      const int idx0 = s * kS16StageBlocks + kS16Bpw * warp;
+      int tl_i = tl, grp_i = grp;
 #pragma unroll
-      for (int i = 0; i < BPW; ++i) {
+      for (int i = 0; i < kS16Bpw; ++i) {
         if (idx0 + i < nb_total) {
-          if (tl != cur_tile) {
+          if (tl_i != cur_tile) {       // warp-uniform
             flush();
-            cur_tile = tl;
+            cur_tile = tl_i;
           }
-          s16_block(st + (size_t)i * kS16BlockBytes, xs + (size_t)grp * 128, og[grp], lane, tot_lo, tot_hi);
+          s16_block(st + (size_t)i * kS16BlockBytes, xq_lane + (size_t)grp_i * 128, st_lane + (size_t)grp_i * 4, lane, sel, tot_lo, tot_hi);
         }
-        if (++grp == ng) {
-          grp = 0;
-          ++tl;
+        if (++grp_i == ng) {
+          grp_i = 0;
+          ++tl_i;
         }
       }
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&empty[slot]);
+      grp += kS16StageBlocks;
+      while (grp >= ng) {
+        grp -= ng;
+        ++tl;
+      }
     }
     flush();
   }
@@ -374,6 +406,8 @@ __global__ void __launch_bounds__(kS16Threads, 2) bitgemv_s16_kernel(S16Args a, 
 }
 
 // Planar-SM -> S16.  One thread per output 32-bit word (code words and scale pairs).
+// Code word i (0..3) of lane (g, t): rows g (i even) or g + 8 (i odd) of the tile; byte b, 2-bit field j = the code of
+// input 128 * group + 32 * j + 8 * t + (i >= 2 ? 4 : 0) + b.
 __global__ void repack_s16_kernel(const uint32_t* __restrict__ codes, const __half* __restrict__ scales, int N, int K,
                                   uint32_t* __restrict__ out) {
   const int ng = K >> 7, wpr = K >> 4;
@@ -390,20 +424,20 @@ __global__ void repack_s16_kernel(const uint32_t* __restrict__ codes, const __ha
       const int g = lane >> 2, t = lane & 3;
       const int row = tile * 16 + g + ((wi & 1) ? 8 : 0);
 #pragma unroll
-      for (int mm = 0; mm < 8; ++mm) {
+      for (int b = 0; b < 4; ++b) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int j = 0; j < 4; ++j) {
           uint32_t c = 1u;   // zero weight
           if (row < N) {
-            const int k = grp * 128 + 32 * (mm >> 1) + 8 * t + 4 * (mm & 1) + ((wi & 2) ? 2 : 0) + h;
+            const int k = grp * 128 + 32 * j + 8 * t + ((wi & 2) ? 4 : 0) + b;
             const uint32_t pw = codes[(size_t)row * wpr + (k >> 4)];
-            const int j = k & 15, i = j & 7;
+            const int jj = k & 15, i = jj & 7;
             const uint32_t nib = (pw >> (4 * i)) & 0xFu;
-            const uint32_t m = j < 8 ? (nib >> 1) & 1u : nib & 1u;
-            const uint32_t sgn = j < 8 ? (nib >> 3) & 1u : (nib >> 2) & 1u;
+            const uint32_t m = jj < 8 ? (nib >> 1) & 1u : nib & 1u;
+            const uint32_t sgn = jj < 8 ? (nib >> 3) & 1u : (nib >> 2) & 1u;
             c = m ? (sgn ? 0u : 2u) : 1u;
           }
-          o |= c << (2 * mm + 16 * h);
+          o |= c << (8 * b + 2 * j);
         }
       }
     } else {
@@ -417,10 +451,10 @@ __global__ void repack_s16_kernel(const uint32_t* __restrict__ codes, const __ha
   }
 }
 
-static inline size_t s16_smem_bytes(int K, int bpw, int stages) {
+static inline size_t s16_smem_bytes(int K) {
   const int ng = K / 128;
-  return (size_t)stages * bpw * kS16Warps * kS16BlockBytes + (size_t)K * 2 + (size_t)((ng + 3) & ~3) * 4 +
-         (size_t)kS16MaxTiles * kS16Warps * 16 * 4 + 2 * kS16MaxStages * 8 + 32 * 4 + 16;
+  return (size_t)kS16Stages * kS16StageBytes + 2 * (size_t)(K + 32) + (size_t)ng * 4 * sizeof(S16Step) +
+         (size_t)kS16MaxTiles * kS16Warps * 16 * 4 + 2 * kS16Stages * 8 + 32 * 4 + 16;
 }
 
 }  // namespace bonsai
@@ -439,16 +473,9 @@ int bonsai_repack_s16(const void* codes, const void* scales, int N, int K, void*
   return launch_status();
 }
 
-// Pipeline shape of bonsai_bitgemv_s16 for later launches of this process: blocks per warp per stage (1 or 2), ring
-// stages (2..16), nanoseconds of sleep between two polls of a ring barrier, and whether the kernel is launched with
-// programmatic dependent launch (its weight copies then start while the previous kernel still runs).  Returns 0, or
-// the bad-argument code.
-int bonsai_s16_tune(int blocks_per_warp, int stages, int sleep_ns, int pdl) {
-  if ((blocks_per_warp != 1 && blocks_per_warp != 2) || stages < 2 || stages > bonsai::kS16MaxStages || sleep_ns < 0) return BONSAI_CUDA_BAD_ARG;
+// Whether later launches of bonsai_bitgemv_s16 in this process use programmatic dependent launch (default: yes).
+int bonsai_s16_tune(int pdl) {
   bonsai::g_s16_pdl = pdl != 0;
-  bonsai::g_s16_bpw = blocks_per_warp;
-  bonsai::g_s16_stages = stages;
-  bonsai::g_s16_sleep_ns = sleep_ns;
   return BONSAI_CUDA_OK;
 }
 
@@ -475,15 +502,12 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
     tp = *static_cast<const TpComm*>(comm);
     if ((size_t)N > tp.lay.recv_elems) return BONSAI_CUDA_BAD_ARG;
   }
-  const int bpw = g_s16_bpw, stages = g_s16_stages;
-  const size_t smem = s16_smem_bytes(K, bpw, stages);
-  if (smem > 200 * 1024) return BONSAI_CUDA_BAD_ARG;
+  const size_t smem = s16_smem_bytes(K);
   static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(bitgemv_s16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(bitgemv_s16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(bitgemv_s16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
       return BONSAI_CUDA_LAUNCH_FAILED;
     attr_set[dev] = true;
   }
@@ -498,15 +522,11 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
   a.N = N;
   a.K = K;
   a.epi = epi;
-  a.nstages = stages;
-  a.sleep_ns = g_s16_sleep_ns;
   cudaError_t e;
   if (g_s16_pdl) {
-    e = bpw == 1 ? launch_pdl(bitgemv_s16_kernel<1>, dim3(grid), dim3(kS16Threads), smem, stream, a, tp)
-                 : launch_pdl(bitgemv_s16_kernel<2>, dim3(grid), dim3(kS16Threads), smem, stream, a, tp);
+    e = launch_pdl(bitgemv_s16_kernel, dim3(grid), dim3(kS16Threads), smem, stream, a, tp);
   } else {
-    if (bpw == 1) bitgemv_s16_kernel<1><<<grid, kS16Threads, smem, stream>>>(a, tp);
-    else bitgemv_s16_kernel<2><<<grid, kS16Threads, smem, stream>>>(a, tp);
+    bitgemv_s16_kernel<<<grid, kS16Threads, smem, stream>>>(a, tp);
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;

@@ -1,15 +1,13 @@
 // Single-tile tensor-core self-test: D[128][N] = A[128][K] * B[N][K]^T with one CTA, operands given
 // as row-major 128-byte rows that the kernel places into swizzled shared memory.  It exists to pin
-// down, on hardware, the operand encodings the production kernels rely on (f16/bf16, e2m1 x e4m3
-// under kind::f8f6f4, packed e2m1 under kind::mxf4 with unit block scales); the unit tests compare
-// it against a PyTorch fp32 matmul of the decoded operands.
+// down, on hardware, the operand encodings the production kernels rely on (f16 / bf16, and e2m1 x e4m3
+// under kind::f8f6f4); the unit tests compare it against a PyTorch fp32 matmul of the decoded operands.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
 namespace bonsai {
 
-// kind: 0 = f16, 1 = bf16, 2 = f8f6f4 (A e2m1, B e4m3), 3 = mxf4 (A, B packed e2m1, scales = 1.0),
-//       4 = f8f6f4 (A e4m3, B e4m3)
+// kind: 0 = f16, 1 = bf16, 2 = f8f6f4 (A e2m1, B e4m3)
 __global__ void __launch_bounds__(128) tc_tile_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B,
                                                      float* __restrict__ out, int N, int kind, int* __restrict__ status) {
   extern __shared__ uint8_t raw[];
@@ -41,21 +39,12 @@ __global__ void __launch_bounds__(128) tc_tile_kernel(const uint8_t* __restrict_
   tc::tc_fence_after();
   const uint32_t taddr = tmem_slot;
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  if (kind == 3) {
-    for (int j = 0; j < 128; ++j) tc::tmem_st1(taddr + lane_base + 256 + j, 0x7F7F7F7Fu);
-    tc::tmem_wait_st();
-    tc::tc_fence_before();
-    __syncthreads();
-    tc::tc_fence_after();
-  }
   if (t == 0) {
     uint64_t da = tc::smem_desc_sw128(tc::smem_u32(sA)), db = tc::smem_desc_sw128(tc::smem_u32(sB));
     for (uint32_t k = 0; k < 4; ++k) {
       if (kind == 0) tc::mma_f16(taddr, da + 2 * k, db + 2 * k, tc::idesc_f32acc(tc::FMT_F16, tc::FMT_F16, 128, N), k);
       else if (kind == 1) tc::mma_f16(taddr, da + 2 * k, db + 2 * k, tc::idesc_f32acc(tc::FMT_BF16, tc::FMT_BF16, 128, N), k);
-      else if (kind == 2) tc::mma_f8f6f4(taddr, da + 2 * k, db + 2 * k, tc::idesc_f32acc(tc::FMT_E2M1, tc::FMT_E4M3, 128, N), k);
-      else if (kind == 4) tc::mma_f8f6f4(taddr, da + 2 * k, db + 2 * k, tc::idesc_f32acc(tc::FMT_E4M3, tc::FMT_E4M3, 128, N), k);
-      else tc::mma_mxf4(taddr, da + 2 * k, db + 2 * k, tc::idesc_mxf4(128, N), k, taddr + 256, taddr + 384);
+      else tc::mma_f8f6f4(taddr, da + 2 * k, db + 2 * k, tc::idesc_f32acc(tc::FMT_E2M1, tc::FMT_E4M3, 128, N), k);
     }
     tc::mma_commit(&bar);
   }
@@ -80,7 +69,7 @@ __global__ void __launch_bounds__(128) tc_tile_kernel(const uint8_t* __restrict_
 }  // namespace bonsai
 
 extern "C" int bonsai_tc_tile(const void* A, const void* B, float* out, int N, int kind, int* status, cudaStream_t stream) {
-  if (N < 16 || N > 256 || N % 16 != 0 || kind < 0 || kind > 4) return BONSAI_CUDA_BAD_ARG;
+  if (N < 16 || N > 256 || N % 16 != 0 || kind < 0 || kind > 2) return BONSAI_CUDA_BAD_ARG;
   size_t smem = 1024 + 16384 + 32768;
   cudaFuncSetAttribute(bonsai::tc_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   bonsai::tc_tile_kernel<<<1, 128, smem, stream>>>((const uint8_t*)A, (const uint8_t*)B, out, N, kind, status);

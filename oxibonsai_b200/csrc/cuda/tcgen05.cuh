@@ -110,7 +110,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -137,10 +136,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
-}
-
 // ---- descriptors ------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address (>>4), leading byte
 // offset unused (1), stride byte offset 1024 (>>4 = 64) between 8-row atoms, descriptor version 1,
@@ -155,17 +150,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-enum : uint32_t { FMT_F16 = 0, FMT_BF16 = 1, FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_E2M1 = 5, FMT_MXF4_E2M1 = 1 };
+enum : uint32_t { FMT_F16 = 0, FMT_BF16 = 1, FMT_E4M3 = 0, FMT_E5M2 = 1, FMT_E2M1 = 5 };
 
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with f32 accumulation, K-major A and B.
 __host__ __device__ constexpr uint32_t idesc_f32acc(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N) {
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
-// Block-scaled (kind::mxf4, ue8m0 scales, K = 64 per instruction).
-__host__ __device__ constexpr uint32_t idesc_mxf4(uint32_t M, uint32_t N) {
-  return (FMT_MXF4_E2M1 << 7) | (FMT_MXF4_E2M1 << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
-}
-
 // D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.  Single-thread issue.
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -179,14 +169,6 @@ __device__ __forceinline__ void mma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uin
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
-                                         uint32_t sfa_tmem, uint32_t sfb_tmem) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
 // Arrives on `bar` once every previously issued tcgen05.mma of this thread has completed.

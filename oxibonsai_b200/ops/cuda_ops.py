@@ -121,7 +121,7 @@ _S16_SIG = {
     "bonsai_s16_bytes": [_i, _i],
     "bonsai_repack_s16": [_vp, _vp, _i, _i, _vp, _vp],
     "bonsai_bitgemv_s16": [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
-    "bonsai_s16_tune": [_i, _i, _i, _i],
+    "bonsai_s16_tune": [_i],
 }
 _s16_declared = False
 EPI_TP = 3
@@ -136,9 +136,9 @@ def _s16():
     return l
 
 
-def s16_tune(blocks_per_warp: int = 2, stages: int = 4, sleep_ns: int = 32, pdl: bool = True) -> None:
-    """Pipeline shape of the streamed GEMV for later launches (and graph captures) of this process."""
-    check(_s16().bonsai_s16_tune(blocks_per_warp, stages, sleep_ns, int(pdl)), "s16_tune")
+def s16_tune(pdl: bool = True) -> None:
+    """Whether later launches (and graph captures) of the streamed GEMV use programmatic dependent launch."""
+    check(_s16().bonsai_s16_tune(int(pdl)), "s16_tune")
 
 
 class S16Weight:
@@ -161,7 +161,7 @@ class S16Weight:
 def bitgemv_s16(w: S16Weight, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6, epi: int = EPI_STORE,
                 residual: torch.Tensor | None = None, out: torch.Tensor | None = None, comm: int | None = None,
                 status: torch.Tensor | None = None) -> torch.Tensor:
-    """out = W x through the streamed tensor-core GEMV (f16 activations, f32 accumulation).  ``epi``: store / residual add /
+    """out = W x through the streamed tensor-core GEMV (two-term int8 activations per 128-input group, exact integer sums).  ``epi``: store / residual add /
     SwiGLU over interleaved gate-up rows / ``EPI_TP`` (sum over the ranks of the communicator handle ``comm`` + residual)."""
     _f32c(x)
     n_out = w.n // 2 if epi == EPI_SWIGLU else w.n

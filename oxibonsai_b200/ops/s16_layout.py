@@ -2,25 +2,22 @@
 
 ``csrc/cuda/bitgemv_stream.cu`` reads a ternary / sign matrix as tiles of 16 output rows.  One 544-byte block covers a
 (tile, 128-input group) pair: 32 lanes x 16 bytes of 2-bit codes followed by 16 f16 group scales.  This module packs a
-dense matrix into that form, decodes it back and restates the kernel's arithmetic (offset decode, per-group offset sum,
-f32 accumulation) with numpy, so the layout and the bit tricks can be checked without a GPU and the device repack can be
-compared byte for byte.  Reference counterpart: the reference's array-of-blocks -> structure-of-arrays re-layout
-(crates/oxibonsai-kernels/src/gpu_backend/cuda_graph/cudagraph_reformat_tq2_blocks_to_soa_group.rs:16-74).
+dense matrix into that form, decodes it back and restates the kernel's arithmetic (two-term int8 activations, 4^j-scaled
+u8 weights per MMA step, integer sums, f32 scales) with numpy, so the layout and the bit tricks can be checked without a GPU
+and the device repack can be compared byte for byte.  Reference counterpart: the reference's array-of-blocks ->
+structure-of-arrays re-layout (crates/oxibonsai-kernels/src/gpu_backend/cuda_graph/cudagraph_reformat_tq2_blocks_to_soa_group.rs:16-74).
 """
 from __future__ import annotations
 
 import numpy as np
 
 BLOCK_BYTES = 544
-#: (shift applied to the word, mask, exponent pattern, offset) of code slot / MMA step 0..7
-SLOTS = [(+6, 0x00C000C0, 0x4C004C00, 16.0), (+6, 0x03000300, 0x44004400, 4.0),
-         (0, 0x00300030, 0x54005400, 64.0), (0, 0x00C000C0, 0x4C004C00, 16.0), (0, 0x03000300, 0x44004400, 4.0),
-         (-6, 0x00300030, 0x54005400, 64.0), (-6, 0x00C000C0, 0x4C004C00, 16.0), (-6, 0x03000300, 0x44004400, 4.0)]
+TERM2 = 254.0      # activations: x = s * (q1 + q2 / 254), |q| <= 127
 
 
-def input_of(group: int, step: int, t: int, word: int, half: int) -> int:
-    """Input index covered by MMA step ``step`` of lane-quad position ``t``, code word ``word`` (0..3), 16-bit half ``half``."""
-    return group * 128 + 32 * (step >> 1) + 8 * t + 4 * (step & 1) + (2 if word & 2 else 0) + half
+def input_of(group: int, step: int, t: int, word: int, byte: int) -> int:
+    """Input index held by 2-bit field ``step`` of byte ``byte`` of code word ``word`` (0..3) of lane-quad position ``t``."""
+    return group * 128 + 32 * step + 8 * t + (4 if word & 2 else 0) + byte
 
 
 def pack(weights: np.ndarray, scales: np.ndarray) -> np.ndarray:
@@ -34,21 +31,20 @@ def pack(weights: np.ndarray, scales: np.ndarray) -> np.ndarray:
     sp[:n] = scales
     codes = (wp.astype(np.int32) + 1).astype(np.uint32)          # c = w + 1
     out = np.zeros((ntiles, ng, BLOCK_BYTES // 4), dtype=np.uint32)
-    tiles = np.arange(ntiles)[:, None]
+    tiles = np.arange(ntiles)
     for grp in range(ng):
         for lane in range(32):
             g, t = lane >> 2, lane & 3
             for word in range(4):
-                rows = tiles[:, 0] * 16 + g + (8 if word & 1 else 0)
+                rows = tiles * 16 + g + (8 if word & 1 else 0)
                 acc = np.zeros(ntiles, dtype=np.uint32)
-                for step in range(8):
-                    for half in range(2):
-                        kk = input_of(grp, step, t, word, half)
-                        acc |= codes[rows, kk] << np.uint32(2 * step + 16 * half)
+                for byte in range(4):
+                    for step in range(4):
+                        acc |= codes[rows, input_of(grp, step, t, word, byte)] << np.uint32(8 * byte + 2 * step)
                 out[:, grp, lane * 4 + word] = acc
         for g in range(8):
-            lo = sp[tiles[:, 0] * 16 + g, grp].view(np.uint16).astype(np.uint32)
-            hi = sp[tiles[:, 0] * 16 + g + 8, grp].view(np.uint16).astype(np.uint32)
+            lo = sp[tiles * 16 + g, grp].view(np.uint16).astype(np.uint32)
+            hi = sp[tiles * 16 + g + 8, grp].view(np.uint16).astype(np.uint32)
             out[:, grp, 128 + g] = lo | (hi << np.uint32(16))
     return out.reshape(-1).view(np.uint8)
 
@@ -66,10 +62,10 @@ def unpack(blocks: np.ndarray, n: int, k: int) -> tuple[np.ndarray, np.ndarray]:
             for word in range(4):
                 rows = tiles * 16 + g + (8 if word & 1 else 0)
                 v = w32[:, grp, lane * 4 + word]
-                for step in range(8):
-                    for half in range(2):
-                        c = (v >> np.uint32(2 * step + 16 * half)) & np.uint32(3)
-                        weights[rows, input_of(grp, step, t, word, half)] = c.astype(np.int8) - 1
+                for byte in range(4):
+                    for step in range(4):
+                        c = (v >> np.uint32(8 * byte + 2 * step)) & np.uint32(3)
+                        weights[rows, input_of(grp, step, t, word, byte)] = c.astype(np.int8) - 1
         for g in range(8):
             v = w32[:, grp, 128 + g]
             scales[tiles * 16 + g, grp] = (v & np.uint32(0xFFFF)).astype(np.uint16).view(np.float16)
@@ -77,44 +73,52 @@ def unpack(blocks: np.ndarray, n: int, k: int) -> tuple[np.ndarray, np.ndarray]:
     return weights[:n], scales[:n]
 
 
-def decode_word(word: np.ndarray, step: int) -> np.ndarray:
-    """The kernel's one-instruction decode of code slot ``step``: returns the two f16 numbers (offset + code) held by the
-    halves of ``(shifted word & mask) | exponent`` as float32 [..., 2]."""
-    shift, mask, expo, _ = SLOTS[step]
-    w = word.astype(np.uint32)
-    v = (w << np.uint32(shift)) if shift > 0 else (w >> np.uint32(-shift)) if shift < 0 else w
-    v = (v & np.uint32(mask)) | np.uint32(expo)
-    halves = np.stack([(v & np.uint32(0xFFFF)).astype(np.uint16), (v >> np.uint32(16)).astype(np.uint16)], axis=-1)
-    return halves.view(np.float16).astype(np.float32)
+def quantize_activations(x: np.ndarray) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """Two int8 terms per 128-input group, as the kernel's prologue computes them: returns (q1, q2 int32 [K], s f32 [K/128])
+    with x ~ s[group] * (q1 + q2 / 254)."""
+    xg = x.astype(np.float32).reshape(-1, 128)
+    amax = np.abs(xg).max(axis=1)
+    s = np.where(amax > 0, amax * np.float32(1.0 / 127.0), np.float32(1.0)).astype(np.float32)
+    f = xg * (np.float32(1.0) / s)[:, None]
+    q1 = np.clip(np.rint(f), -127, 127).astype(np.int32)
+    q2 = np.clip(np.rint((f - q1.astype(np.float32)) * np.float32(TERM2)), -127, 127).astype(np.int32)
+    return q1.reshape(-1), q2.reshape(-1), s
+
+
+def step_operand(word: np.ndarray, step: int) -> np.ndarray:
+    """The kernel's one-instruction decode of MMA step ``step``: ``word & (0x03030303 << 2 * step)`` as four u8 values
+    (4^step * code) [..., 4]."""
+    v = word.astype(np.uint32) & np.uint32(0x03030303 << (2 * step))
+    return np.stack([(v >> np.uint32(8 * b)) & np.uint32(0xFF) for b in range(4)], axis=-1).astype(np.int64)
 
 
 def emulate_gemv(blocks: np.ndarray, n: int, k: int, x: np.ndarray) -> np.ndarray:
-    """W x as the kernel computes it: f16 activations, offset-coded weights, the per-group offset sum removed, group
-    scales applied in f32.  Returns float32 [N]."""
+    """W x as the kernel computes it: integer dot products of the 4^j-scaled codes with the two activation terms per MMA
+    step, minus the part the +1 of the codes adds, combined and scaled in f32.  Returns float32 [N]."""
     ntiles, ng = (n + 15) // 16, k // 128
     w32 = np.ascontiguousarray(blocks).view(np.uint32).reshape(ntiles, ng, BLOCK_BYTES // 4)
-    xh = x.astype(np.float16).astype(np.float32)
+    q1, q2, sx = quantize_activations(x)
     out = np.zeros(ntiles * 16, dtype=np.float32)
     tiles = np.arange(ntiles)
     for grp in range(ng):
-        og = np.float32(0.0)
-        acc = np.zeros(ntiles * 16, dtype=np.float32)
-        for step in range(8):
-            off1 = np.float32(SLOTS[step][3] + 1.0)
-            for t in range(4):
-                for word in range(4):
-                    ks = [input_of(grp, step, t, word, h) for h in range(2)]
-                    for g in range(8):
-                        rows = tiles * 16 + g + (8 if word & 1 else 0)
-                        dec = decode_word(w32[:, grp, (g * 4 + t) * 4 + word], step)       # [ntiles, 2] = offset + code
-                        acc[rows] += dec[:, 0] * xh[ks[0]] + dec[:, 1] * xh[ks[1]]
-                for word in (0, 2):                                                          # each input once for the offset sum
-                    for h in range(2):
-                        og += off1 * xh[input_of(grp, step, t, word, h)]
         sc = np.zeros(ntiles * 16, dtype=np.float32)
         for g in range(8):
             v = w32[:, grp, 128 + g]
             sc[tiles * 16 + g] = (v & np.uint32(0xFFFF)).astype(np.uint16).view(np.float16).astype(np.float32)
             sc[tiles * 16 + g + 8] = (v >> np.uint32(16)).astype(np.uint16).view(np.float16).astype(np.float32)
-        out += sc * (acc - og)
+        for step in range(4):
+            acc1 = np.zeros(ntiles * 16, dtype=np.int64)
+            acc2 = np.zeros(ntiles * 16, dtype=np.int64)
+            lo = grp * 128 + 32 * step
+            og1, og2 = int(q1[lo:lo + 32].sum()) << (2 * step), int(q2[lo:lo + 32].sum()) << (2 * step)
+            for lane in range(32):
+                g, t = lane >> 2, lane & 3
+                for word in range(4):
+                    rows = tiles * 16 + g + (8 if word & 1 else 0)
+                    a = step_operand(w32[:, grp, lane * 4 + word], step)            # [ntiles, 4] = 4^step * code
+                    ks = [input_of(grp, step, t, word, b) for b in range(4)]
+                    acc1[rows] += a @ q1[ks].astype(np.int64)
+                    acc2[rows] += a @ q2[ks].astype(np.int64)
+            v = (acc1 - og1).astype(np.float32) + (acc2 - og2).astype(np.float32) * np.float32(1.0 / TERM2)
+            out += sc * (sx[grp] * np.float32(1.0 / (1 << (2 * step)))) * v
     return out[:n]

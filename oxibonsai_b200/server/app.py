@@ -60,6 +60,32 @@ class SchedulerBackend:
         return self.s.engine.kv.utilization
 
 
+class ReplicaBackend:
+    """Backend over several :class:`BatchScheduler` s, one per GPU (data-parallel replicas of the whole model): a request goes
+    to the replica that its session key hashes to while that replica is healthy and not overloaded, else to the least loaded
+    one (``runtime.distributed.ReplicaPool``), so a conversation keeps hitting the replica that holds its prefix cache."""
+
+    def __init__(self, schedulers: list, model_name: str):
+        from ..runtime.distributed import ReplicaPool
+        self.schedulers = {f"gpu{i}": s for i, s in enumerate(schedulers)}
+        cap = max(1, schedulers[0].engine.max_batch)
+        self.pool = ReplicaPool(self.schedulers, capacity=cap)
+        self.model_name = model_name
+        self.max_seq_len = schedulers[0].engine.max_seq_len
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id, session_key: str | None = None):
+        nid, req = self.pool.submit(session_key or request_id, prompt, params, max_tokens, on_token=on_token, request_id=request_id)
+        req.replica = nid
+        threading.Thread(target=lambda: (req.done.wait(), self.pool.finished(nid)), name=f"replica-done-{request_id[:8]}", daemon=True).start()
+        return req
+
+    def kv_utilization(self) -> float:
+        return max(s.engine.kv.utilization for s in self.schedulers.values())
+
+    def replica_loads(self) -> dict:
+        return {k: {"live": s.active, "queued": len(s.queue)} for k, s in self.schedulers.items()}
+
+
 class SerialBackend:
     """Backend over an engine that serves one request at a time (``runtime.engine.GenericFormatEngine``, or anything with a
     ``generate_stream(prompt, max_tokens, params, stop_at_eos)`` generator): every request gets a worker thread and the

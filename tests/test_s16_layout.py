@@ -1,4 +1,4 @@
-"""Host statement of the streamed decode layout: packing, the one-instruction decode and the offset arithmetic."""
+"""Host statement of the streamed decode layout: packing, the one-instruction decode and the integer arithmetic."""
 import numpy as np
 
 from oxibonsai_b200.ops import s16_layout as L
@@ -20,30 +20,42 @@ def test_pack_round_trip_with_ragged_tile():
 
 
 def test_every_input_is_covered_once_per_row():
-    seen = set()
-    for step in range(8):
+    seen = []
+    for step in range(4):
         for t in range(4):
             for word in (0, 2):          # words 1 and 3 hold the same inputs for rows g + 8
-                for half in range(2):
-                    seen.add(L.input_of(0, step, t, word, half))
-    assert seen == set(range(128))
+                for byte in range(4):
+                    seen.append(L.input_of(0, step, t, word, byte))
+    assert sorted(seen) == list(range(128))
 
 
-def test_decode_is_offset_plus_code_for_every_slot():
-    for step in range(8):
-        for c_lo in range(3):
-            for c_hi in range(3):
-                word = np.array([(c_lo << (2 * step)) | (c_hi << (2 * step + 16)) | 0xFFFFFFFF & ~((3 << (2 * step)) | (3 << (2 * step + 16)))], dtype=np.uint32)
-                # every other slot is filled with ones: the mask must remove them
-                dec = L.decode_word(word, step)[0]
-                off = L.SLOTS[step][3]
-                assert dec[0] == off + c_lo and dec[1] == off + c_hi
+def test_step_operand_is_the_scaled_code_and_ignores_other_fields():
+    for step in range(4):
+        for codes in ((0, 1, 2, 1), (2, 2, 0, 0)):
+            word = 0xFFFFFFFF
+            for b, c in enumerate(codes):
+                word &= ~(3 << (8 * b + 2 * step))
+                word |= c << (8 * b + 2 * step)
+            got = L.step_operand(np.array([word], dtype=np.uint32), step)[0]
+            assert got.tolist() == [c << (2 * step) for c in codes] and max(got) <= 128
+
+
+def test_two_term_quantisation_is_sixteen_bits_of_the_group_maximum():
+    rng = np.random.default_rng(5)
+    x = (rng.normal(size=512) * np.repeat([0.01, 1.0, 30.0, 1e-4], 128)).astype(np.float32)
+    q1, q2, s = L.quantize_activations(x)
+    assert np.abs(q1).max() <= 127 and np.abs(q2).max() <= 127
+    back = np.repeat(s, 128) * (q1 + q2 / L.TERM2)
+    amax = np.repeat(np.abs(x.reshape(-1, 128)).max(axis=1), 128)
+    assert (np.abs(back - x) <= amax / (127 * 2 * L.TERM2) * 1.01 + 1e-12).all()
+    assert (L.quantize_activations(np.zeros(128, np.float32))[0] == 0).all()
 
 
 def test_emulated_kernel_arithmetic_matches_a_plain_product():
     w, s, rng = _random(50, 512, 3)
     x = rng.normal(size=512).astype(np.float32) * 3.0
+    x[::37] *= 8.0
     b = L.pack(w, s)
     y = L.emulate_gemv(b, 50, 512, x)
-    ref = (w.astype(np.float64) * np.repeat(s.astype(np.float64), 128, axis=1)) @ x.astype(np.float16).astype(np.float64)
-    assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max() + 1e-6
+    ref = (w.astype(np.float64) * np.repeat(s.astype(np.float64), 128, axis=1)) @ x.astype(np.float64)
+    assert np.abs(y - ref).max() <= 2e-4 * np.abs(ref).mean() * 2.0
