@@ -363,7 +363,7 @@ def main() -> None:
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": round(value / PUBLISHED_BASELINE_TOK_S, 2),
-        "dtype": "f16 activations, exact f16 x 2-bit products, f32 accumulation (mma.sync) and f32 residual stream; 2-bit weights as stored; f16 KV",
+        "dtype": "int8x2 activations per 128-input group (16 bits of the group maximum), exact integer products and sums (mma.sync u8 x s8 -> s32), f32 scales and residual stream; 2-bit weights as stored; f16 KV and f16 tensor-core attention",
         "data": "synthetic (seeded random-init GGUF, random prompt tokens)",
         "config": {"model": cfg.name, "global_batch": 1, "seq_len": prompt_len, "decode_tokens": args.steps, "kv_cache": args.kv,
                    "parallelism": "single GPU" if world == 1 else f"tp{world} (one stream over all GPUs; fused GEMV->all-reduce epilogues over NVLink peer memory)",

@@ -7,8 +7,8 @@
 // with the weights resident in L2).  Here
 //   * weights live in the "S16" layout: tiles of 16 output rows, one 544-byte block per (tile, 128-input group) =
 //     32 lanes x 16 bytes of 2-bit codes in MMA-fragment order + 16 f16 group scales.  A CTA owns a contiguous range
-//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a four-stage
-//     shared-memory ring with cp.async.bulk (17 KB per copy, 70 KB in flight per SM);
+//     of tiles, i.e. one contiguous byte range of the matrix, and a producer lane streams it into a three-stage
+//     shared-memory ring with cp.async.bulk (34 KB per copy, 104 KB in flight per SM);
 //   * a code c = w + 1 in {0, 1, 2} occupies one 2-bit field of a byte; `word & (0x03030303 << 2j)` is the u8 vector
 //     (4^j c) of four weights: ONE logic instruction per four weights, no shift, no sign handling.  The 4^j is not
 //     undone on the weights: MMA step j of a group uses field j of every word, and the activations are laid out so
@@ -19,8 +19,10 @@
 //   * activations are quantised per 128-input group to two int8 terms, x = s (q1 + q2 / 254), |q| <= 127 - sixteen
 //     bits relative to the group's largest value; the terms are the even and odd output columns.  Products and sums
 //     are exact integers; the +1 of the codes is removed by starting the accumulators at -4^j * sum(q) of the step;
-//   * sixteen consumer warps take two blocks each per stage, keep per-tile partial sums in registers and meet in
-//     shared memory once at the end; partials are added in warp order, so results do not depend on timing.
+//   * sixteen consumer warps take four consecutive blocks each per stage - four independent MMA chains, issued
+//     interleaved and without a branch in between when the blocks belong to one tile - keep per-tile partial sums
+//     in registers and meet in shared memory once at the end; partials are added in warp order, so results do not
+//     depend on timing.
 // Per (tile, group) block a thread issues 16 logic ops, 4 MMAs, 4 loads, 8 integer multiplies that build the
 // zero-padded B operands and a dozen f32 ops: ~0.8 instructions per weight.
 //
@@ -42,10 +44,10 @@ enum { SEPI_STORE = 0, SEPI_RESID = 1, SEPI_SWIGLU = 2, SEPI_TP = 3 };
 constexpr int kS16Warps = 16;                                    // consumer warps; warp 16 is the copy producer
 constexpr int kS16Threads = (kS16Warps + 1) * 32;
 constexpr int kS16BlockBytes = 544;                              // 512 B codes + 32 B scales
-constexpr int kS16Bpw = 2;                                       // blocks per warp per stage
+constexpr int kS16Bpw = 4;                                       // consecutive blocks per warp per stage
 constexpr int kS16StageBlocks = kS16Bpw * kS16Warps;
-constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes; // 17408
-constexpr int kS16Stages = 4;                                    // power of two
+constexpr int kS16StageBytes = kS16StageBlocks * kS16BlockBytes; // 34816
+constexpr int kS16Stages = 3;
 constexpr int kS16MaxTiles = 12;                                 // tiles per CTA (size of the partial-sum area)
 constexpr uint32_t kS16WaitLimit = 1u << 21;                     // polls with a short sleep in between: about a second
 constexpr float kS16Term2 = 254.0f;                              // x = s * (q1 + q2 / 254)
@@ -97,13 +99,13 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
 
 // Per (group, step) record of the activation side: the step's accumulator start values and f32 factor.
 struct __align__(16) S16Step {
-  int og0, og1;      // 4^j * sum of the step's q1 (q2) values: the part of the integer dot product that the +1 of the codes adds
+  int og0, og1;      // -4^j * sum of the step's q1 (q2) values: takes out what the +1 of the codes adds to the integer dot product
   float sx;          // group scale of the activations times 4^-j
   float pad;
 };
 
-// One (tile, group) block.  xq_lane: the lane's eight int8 activations of step 0 of the group (term g & 1; step j is
-// 32 bytes further); st_lane: the S16Step record of the lane's accumulator columns (step t of the group).  sel[j] is 1
+// One (tile, group) block.  xq_lane: the lane's eight int8 activations of its own step (g / 2) and term (g & 1) of the
+// group; st_lane: the S16Step record of the lane's accumulator columns (step t of the group).  sel[j] is 1
 // when this lane's B column belongs to step j, else 0.  Adds the lane's share (its step, both terms) of
 // scale * (W x) of rows g and g + 8 to tot.
 __device__ __forceinline__ void s16_block(const uint8_t* __restrict__ blk, const int8_t* __restrict__ xq_lane, const S16Step* __restrict__ st_lane,
@@ -112,11 +114,11 @@ __device__ __forceinline__ void s16_block(const uint8_t* __restrict__ blk, const
   const uint4 cw = *reinterpret_cast<const uint4*>(blk + lane * 16);
   const uint32_t sc = *reinterpret_cast<const uint32_t*>(blk + 512 + 4 * g);
   const S16Step st = *st_lane;
-  int acc[4] = {-st.og0, -st.og1, -st.og0, -st.og1};
+  int acc[4] = {st.og0, st.og1, st.og0, st.og1};
+  const uint2 xb = *reinterpret_cast<const uint2*>(xq_lane);            // the lane's eight activations of its own step
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    // B operand of step j: the lane's eight activations of that step if the lane's column belongs to step j, else zeros
-    const uint2 xb = *reinterpret_cast<const uint2*>(xq_lane + 32 * j);
+    // B operand of step j: those activations if the lane's column belongs to step j, else zeros
     const uint32_t m = 0x03030303u << (2 * j);
     s16_imma(acc, cw.x & m, cw.y & m, cw.z & m, cw.w & m, s16_mul(xb.x, sel[j]), s16_mul(xb.y, sel[j]));
   }
@@ -126,6 +128,44 @@ __device__ __forceinline__ void s16_block(const uint8_t* __restrict__ blk, const
   const float v_hi = fmaf((float)acc[3], 1.0f / kS16Term2, (float)acc[2]);
   tot_lo = fmaf(__low2float(s2) * st.sx, v_lo, tot_lo);
   tot_hi = fmaf(__high2float(s2) * st.sx, v_hi, tot_hi);
+}
+
+// NB consecutive blocks of one tile (groups grp .. grp + NB - 1), their MMA chains issued interleaved.
+template <int NB>
+__device__ __forceinline__ void s16_blocks(const uint8_t* __restrict__ blk, const int8_t* __restrict__ xq_lane, const S16Step* __restrict__ st_lane,
+                                           int lane, const uint32_t (&sel)[4], float& tot_lo, float& tot_hi) {
+  const int g = lane >> 2;
+  uint4 cw[NB];
+  uint2 xb[NB];
+  uint32_t sc[NB];
+  float sx[NB];
+  int acc[NB][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    cw[b] = *reinterpret_cast<const uint4*>(blk + b * kS16BlockBytes + lane * 16);
+    xb[b] = *reinterpret_cast<const uint2*>(xq_lane + 128 * b);
+    sc[b] = *reinterpret_cast<const uint32_t*>(blk + b * kS16BlockBytes + 512 + 4 * g);
+    const S16Step st = st_lane[4 * b];
+    acc[b][0] = acc[b][2] = st.og0;
+    acc[b][1] = acc[b][3] = st.og1;
+    sx[b] = st.sx;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t m = 0x03030303u << (2 * j);
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      s16_imma(acc[b], cw[b].x & m, cw[b].y & m, cw[b].z & m, cw[b].w & m, s16_mul(xb[b].x, sel[j]), s16_mul(xb[b].y, sel[j]));
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    const __half2 s2 = *reinterpret_cast<const __half2*>(&sc[b]);
+    const float v_lo = fmaf((float)acc[b][1], 1.0f / kS16Term2, (float)acc[b][0]);
+    const float v_hi = fmaf((float)acc[b][3], 1.0f / kS16Term2, (float)acc[b][2]);
+    tot_lo = fmaf(__low2float(s2) * sx[b], v_lo, tot_lo);
+    tot_hi = fmaf(__high2float(s2) * sx[b], v_hi, tot_hi);
+  }
 }
 
 struct S16Args {
@@ -174,9 +214,11 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
   if (warp == kS16Warps) {
     // ---- producer: one lane streams the CTA's byte range through the ring (weights depend on no earlier kernel) ----
     if (lane == 0) {
-      for (int s = 0; s < nstage_total; ++s) {
-        const int slot = s & (kS16Stages - 1);
-        if (s >= kS16Stages && !s16_poll(&empty[slot], ((s / kS16Stages) - 1) & 1, abort_flag)) break;
+      int slot = 0;
+      uint32_t phase = 1;      // parity of the use of a slot that must have been released: none for the first round
+      for (int s = 0; s < nstage_total; ++s, slot = slot + 1 == kS16Stages ? 0 : slot + 1) {
+        if (slot == 0) phase ^= 1u;
+        if (s >= kS16Stages && !s16_poll(&empty[slot], phase ^ 1u, abort_flag)) break;
         const int b0 = s * kS16StageBlocks;
         const int nb = min(kS16StageBlocks, nb_total - b0);
         const uint32_t bytes = (uint32_t)nb * kS16BlockBytes;
@@ -232,29 +274,36 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
       const float amax = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
       const float sx = amax > 0.0f ? amax * (1.0f / 127.0f) : 1.0f;
       const float rs = 1.0f / sx;
+      // Round with the 1.5 * 2^23 trick: (f + magic) holds rint(f) in its low mantissa bits (two's complement, so the low
+      // byte is the int8 value) and (f + magic) - magic is rint(f) as a float.  |f| <= 127 and |f - rint(f)| * 254 <= 127
+      // by construction, so nothing needs clamping.
+      constexpr float kMagic = 12582912.0f;
       const float f[4] = {v.x * rs, v.y * rs, v.z * rs, v.w * rs};
-      int q1[4], q2[4];
+      uint32_t w1 = 0, w2 = 0;
+      float fs1 = 0.0f, fs2 = 0.0f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        q1[e] = max(-127, min(127, (int)rintf(f[e])));       // |f| <= 127 up to the rounding of the reciprocal
-        q2[e] = max(-127, min(127, (int)rintf((f[e] - (float)q1[e]) * kS16Term2)));
+        const float m1 = f[e] + kMagic, r1 = m1 - kMagic;
+        const float m2 = (f[e] - r1) * kS16Term2 + kMagic, r2 = m2 - kMagic;
+        w1 |= (__float_as_uint(m1) & 255u) << (8 * e);
+        w2 |= (__float_as_uint(m2) & 255u) << (8 * e);
+        fs1 += r1;
+        fs2 += r2;
       }
-      const uint32_t w1 = (uint32_t)(q1[0] & 255) | ((uint32_t)(q1[1] & 255) << 8) | ((uint32_t)(q1[2] & 255) << 16) | ((uint32_t)(q1[3] & 255) << 24);
-      const uint32_t w2 = (uint32_t)(q2[0] & 255) | ((uint32_t)(q2[1] & 255) << 8) | ((uint32_t)(q2[2] & 255) << 16) | ((uint32_t)(q2[3] & 255) << 24);
       reinterpret_cast<uint32_t*>(xq)[c] = w1;
       reinterpret_cast<uint32_t*>(xq + term_stride)[c] = w2;
       // sums over the eight lanes of a step
-      int s1 = q1[0] + q1[1] + q1[2] + q1[3], s2 = q2[0] + q2[1] + q2[2] + q2[3];
 #pragma unroll
-      for (int o = 4; o > 0; o >>= 1) {
-        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+      for (int o = 4; o > 0; o >>= 1) {      // sums of small integers: exact in f32
+        fs1 += __shfl_xor_sync(0xffffffffu, fs1, o);
+        fs2 += __shfl_xor_sync(0xffffffffu, fs2, o);
       }
       if ((lane & 7) == 0) {
         const int j = lane >> 3;
+        const int s1 = (int)fs1, s2 = (int)fs2;
         S16Step r;
-        r.og0 = s1 * (1 << (2 * j));
-        r.og1 = s2 * (1 << (2 * j));
+        r.og0 = -s1 * (1 << (2 * j));
+        r.og1 = -s2 * (1 << (2 * j));
         r.sx = sx * (1.0f / (float)(1 << (2 * j)));
         r.pad = 0.0f;
         steps[(size_t)(c >> 5) * 4 + j] = r;
@@ -269,14 +318,15 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
     s16_bar();
   }
 
-  // ---- main loop: two consecutive blocks per warp per stage ----
+  // ---- main loop: kS16Bpw consecutive blocks per warp per stage ----
   {
     const int g = lane >> 2, t = lane & 3;
     // this lane supplies output column n = g = 2 * step + term of every B operand
     const int my_step = g >> 1;
     const uint32_t sel[4] = {my_step == 0 ? 1u : 0u, my_step == 1 ? 1u : 0u, my_step == 2 ? 1u : 0u, my_step == 3 ? 1u : 0u};
-    const int8_t* xq_lane = xq + (g & 1) * term_stride + 8 * t;        // + 128 * group + 32 * step
+    const int8_t* xq_lane = xq + (g & 1) * term_stride + 32 * my_step + 8 * t;   // + 128 * group
     const S16Step* st_lane = steps + t;                                  // + 4 * group: the lane's accumulator columns belong to step t
+    const bool aligned = (ng % kS16Bpw) == 0;                            // a warp's blocks of a stage then share their tile
     int cur_tile = -1;
     float tot_lo = 0.0f, tot_hi = 0.0f;
     auto flush = [&]() {
@@ -294,28 +344,38 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
     };
     // (tile, group) of the warp's first block of the current stage, advanced by one stage's blocks per iteration
     int tl = (kS16Bpw * warp) / ng, grp = (kS16Bpw * warp) - tl * ng;
+    int slot = 0;
+    uint32_t phase = 0;
     for (int s = 0; s < nstage_total; ++s) {
-      const int slot = s & (kS16Stages - 1);
-      if (!s16_wait(&full[slot], (s / kS16Stages) & 1, lane, abort_flag)) break;
+      if (!s16_wait(&full[slot], phase, lane, abort_flag)) break;
       const uint8_t* st = ring + (size_t)slot * kS16StageBytes + (size_t)(kS16Bpw * warp) * kS16BlockBytes;
-      const int idx0 = s * kS16StageBlocks + kS16Bpw * warp;
-      int tl_i = tl, grp_i = grp;
-#pragma unroll
-      for (int i = 0; i < kS16Bpw; ++i) {
-        if (idx0 + i < nb_total) {
-          if (tl_i != cur_tile) {       // warp-uniform
+      const int left = nb_total - (s * kS16StageBlocks + kS16Bpw * warp);   // blocks of the stream from the warp's first one on
+      if (aligned && left >= kS16Bpw) {
+        if (tl != cur_tile) {           // warp-uniform
+          flush();
+          cur_tile = tl;
+        }
+        s16_blocks<kS16Bpw>(st, xq_lane + (size_t)grp * 128, st_lane + (size_t)grp * 4, lane, sel, tot_lo, tot_hi);
+      } else {
+        int tl_i = tl, grp_i = grp;
+        for (int i = 0; i < kS16Bpw && i < left; ++i) {
+          if (tl_i != cur_tile) {
             flush();
             cur_tile = tl_i;
           }
           s16_block(st + (size_t)i * kS16BlockBytes, xq_lane + (size_t)grp_i * 128, st_lane + (size_t)grp_i * 4, lane, sel, tot_lo, tot_hi);
-        }
-        if (++grp_i == ng) {
-          grp_i = 0;
-          ++tl_i;
+          if (++grp_i == ng) {
+            grp_i = 0;
+            ++tl_i;
+          }
         }
       }
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&empty[slot]);
+      if (++slot == kS16Stages) {
+        slot = 0;
+        phase ^= 1u;
+      }
       grp += kS16StageBlocks;
       while (grp >= ng) {
         grp -= ng;
