@@ -138,7 +138,7 @@ def measure(eng, args, cfg, prompt, n_streams: int, barrier, dev, gen, e2e: bool
     prompt_len = len(prompt)
     total_steps = args.warmup + args.steps
     out = {"e2e_s": float("nan"), "e2e_steps": 0, "st_ms": float("nan"), "st_e2e_s": float("nan"), "st_e2e_tokens": 0, "clocks": None,
-           "ttfts": []}
+           "ttfts": [], "itl_p95": None}
     eng._bind_slot(0, prompt_len + 2 * total_steps + 16)
     eng._set_sampling(0, eng.sampling)
     barrier()
@@ -204,17 +204,21 @@ def measure(eng, args, cfg, prompt, n_streams: int, barrier, dev, gen, e2e: bool
             # and the S sampled tokens come back to the host
             from oxibonsai_b200.runtime.scheduler import BatchScheduler
             sched = BatchScheduler(eng, eos_token=-1)
-            n_out = args.warmup + args.steps
+            # Prompts are admitted one chunk per decode step, so the first streams are many tokens ahead when the last one
+            # starts: every stream gets enough tokens to be still running then, and the timed window is the stretch in
+            # which all S streams are live (from the last stream's first token to the first stream's last one).
+            n_out = args.warmup + args.steps + 3 * S
             reqs = [sched.submit(torch.randint(0, cfg.vocab, (sp_len,), generator=gen).tolist(), eng.sampling, n_out) for _ in range(S)]
             sched.start()
             for q_ in reqs:
                 q_.wait(timeout=1800)
             sched.stop()
-            t_start = max(q_.token_times[args.warmup - 1] for q_ in reqs)   # every stream is past its warm-up tokens
-            t_end = max(q_.token_times[-1] for q_ in reqs)
-            out["st_e2e_tokens"] = sum(sum(1 for x in q_.token_times if x > t_start) for q_ in reqs)
+            t_start = max(q_.token_times[0] for q_ in reqs)
+            t_end = min(q_.token_times[-1] for q_ in reqs)
+            out["st_e2e_tokens"] = sum(sum(1 for x in q_.token_times if t_start < x <= t_end) for q_ in reqs)
             out["st_e2e_s"] = t_end - t_start
             out["ttfts"] = sorted(q_.t_first_token - q_.t_submit for q_ in reqs if q_.t_first_token is not None)
+            out["itl_p95"] = sorted(b_ - a_ for q_ in reqs for a_, b_ in zip(q_.token_times, q_.token_times[1:]))[int(0.95 * sum(len(q_.token_times) - 1 for q_ in reqs))]
     return out
 
 
@@ -380,7 +384,9 @@ def main() -> None:
             "e2e_value": None if not m["st_e2e_tokens"] else round(m["st_e2e_tokens"] / st_e2e_s, 1),
             "e2e_h2d_bytes_per_step": 4 * S, "e2e_d2h_bytes_per_step": 4 * S + 4,
             "p50_ttft_s": None if not ttfts else round(ttfts[len(ttfts) // 2], 3),
-            "note": "TTFT of the scheduler run: all streams are submitted at once, so it includes queueing behind the other prompts"},
+            "p95_itl_s": None if m.get("itl_p95") is None else round(m["itl_p95"], 4),
+            "note": "scheduler run: all streams are submitted at once and admitted one 512-token prompt chunk per decode step, so TTFT "
+                    "includes queueing behind the other prompts; e2e_value counts the stretch in which all streams are live"},
         "hbm_roofline_frac_of_measured" if peaks else "hbm_roofline_frac_of_fallback": round(bytes_step / (ms_per_step * 1e-3) / (hbm * 1e9), 4),
     })
 

@@ -106,7 +106,10 @@ __global__ void tp_add_kernel(float* __restrict__ h, const float* __restrict__ a
 extern "C" {
 
 // Layout of the symmetric buffer for the given sizes; returns the number of bytes every rank must allocate.
-size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems, size_t* offsets /*[6]*/) {
+// {value, tag} slots for decode batches: up to 64 tokens of recv_elems rows each.
+size_t bonsai_tp_ll_big_elems(size_t recv_elems) { return 64 * recv_elems; }
+
+size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems, size_t* offsets /*[7]*/) {
   using namespace bonsai;
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   size_t o = 0;
@@ -116,6 +119,7 @@ size_t bonsai_tp_layout(size_t recv_elems, size_t logits_elems, size_t big_elems
   offsets[3] = o; o = up(o + sizeof(float) * logits_elems);
   offsets[4] = o; o = up(o + sizeof(float) * big_elems);
   offsets[5] = o; o = up(o + sizeof(unsigned long long) * 2 * kTpMaxRanks * recv_elems);
+  offsets[6] = o; o = up(o + sizeof(unsigned long long) * 2 * kTpMaxRanks * bonsai_tp_ll_big_elems(recv_elems));
   return o;
 }
 
@@ -130,7 +134,7 @@ void* bonsai_tp_create(int rank, int size, const uint64_t* peer_ptrs, size_t rec
   c->rank = rank;
   c->size = size;
   for (int r = 0; r < size; ++r) c->peer[r] = reinterpret_cast<uint8_t*>(peer_ptrs[r]);
-  size_t off[6];
+  size_t off[7];
   c->lay.total_bytes = bonsai_tp_layout(recv_elems, logits_elems, big_elems, off);
   c->lay.off_tile_flags = off[0];
   c->lay.off_bar_flags = off[1];
@@ -138,6 +142,8 @@ void* bonsai_tp_create(int rank, int size, const uint64_t* peer_ptrs, size_t rec
   c->lay.off_logits = off[3];
   c->lay.off_big = off[4];
   c->lay.off_ll = off[5];
+  c->lay.off_ll_big = off[6];
+  c->lay.ll_big_elems = bonsai_tp_ll_big_elems(recv_elems);
   c->spin_limit = kTpDefaultSpinLimit;
   c->lay.recv_elems = recv_elems;
   c->lay.big_elems = big_elems;

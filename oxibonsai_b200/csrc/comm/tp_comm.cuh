@@ -35,8 +35,9 @@ struct TpLayout {
   size_t off_recv;         // float [2][kTpMaxRanks][recv_elems]
   size_t off_logits;       // float [max_batch][vocab]
   size_t off_big;          // float [big_elems]  (prefill partial sums)
-  size_t off_ll;           // u64 [2][kTpMaxRanks][recv_elems]  ({value, tag} slots of the flag-in-data exchange)
-  size_t recv_elems, big_elems, total_bytes;
+  size_t off_ll;           // u64 [2][kTpMaxRanks][recv_elems]  ({value, tag} slots of the flag-in-data exchange, one token)
+  size_t off_ll_big;       // u64 [2][kTpMaxRanks][ll_big_elems]  (the same for decode batches: [token][row])
+  size_t recv_elems, big_elems, ll_big_elems, total_bytes;
 };
 
 struct TpComm {
@@ -76,6 +77,29 @@ __device__ __forceinline__ float* tp_recv_slot(const TpComm& c, int on_rank, int
 }
 __device__ __forceinline__ unsigned long long* tp_ll_slot(const TpComm& c, int on_rank, int parity, int from_rank) {
   return reinterpret_cast<unsigned long long*>(c.peer[on_rank] + c.lay.off_ll) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.recv_elems;
+}
+__device__ __forceinline__ unsigned long long* tp_ll_big_slot(const TpComm& c, int on_rank, int parity, int from_rank) {
+  return reinterpret_cast<unsigned long long*>(c.peer[on_rank] + c.lay.off_ll_big) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.ll_big_elems;
+}
+__device__ __forceinline__ void tp_st_msg(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long tp_ld_msg(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Polls a {value, tag} slot until the tag shows up.  `alive` goes false on expiry, after which later calls of the
+// thread poll only once (a silent peer costs one wait limit per thread, not one per value).
+__device__ __forceinline__ float tp_recv_msg(const TpComm& c, const unsigned long long* slot, uint32_t tag, bool& alive) {
+  const uint32_t limit = alive ? c.spin_limit : 1u;
+  for (uint32_t it = 0; it < limit; ++it) {
+    const unsigned long long m = tp_ld_msg(slot);
+    if ((uint32_t)(m >> 32) == tag) return __uint_as_float((uint32_t)m);
+  }
+  alive = false;
+  atomicExch(c.status, 2);
+  return 0.0f;
 }
 __device__ __forceinline__ int* tp_tile_flag(const TpComm& c, int on_rank, int parity, int from_rank, int tile) {
   return reinterpret_cast<int*>(c.peer[on_rank] + c.lay.off_tile_flags) + ((size_t)parity * kTpMaxRanks + from_rank) * kTpMaxTiles + tile;

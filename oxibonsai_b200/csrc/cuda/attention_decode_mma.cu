@@ -94,7 +94,11 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = lane >> 2, cq = lane & 3;   // accumulator row (query head of the group) and column pair of this lane
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Fused mode: the kernel before this one in the stream is the QKV projection, which writes nothing but the raw
+  // projections - positions, block table and the cached K/V rows of earlier tokens are older than it.  The wait
+  // therefore comes after the page lookups and the first K/V tile requests, just before the projections are read.
+  // Otherwise (the queries and the new K/V rows come from the kernel before) it comes first.
+  if (p.qkv == nullptr) asm volatile("griddepcontrol.wait;" ::: "memory");
   const int len = p.positions[b] + 1 + p.extra_len;
   int chunk = (len + nsplit - 1) / nsplit;
   chunk = (chunk + kMmaTile - 1) & ~(kMmaTile - 1);   // tiles never straddle a split boundary or (page_size >= 16) a page
@@ -123,6 +127,7 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   const int first_tb = t0 + warp * kMmaTile;
   const bool early = warp < ntiles && !(p.qkv != nullptr && len - 1 >= first_tb && len - 1 < first_tb + kMmaTile);
   if (early) issue_tile(warp, 0);
+  if (p.qkv != nullptr) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // Q as A-operand fragments: rows 0..G-1 hold the group's query heads (scaled), rows G..15 are zero
   uint32_t qa[8][2];   // per 16-wide k step: a0 (row, k lo pair) and a2 (row, k hi pair); a1 = a3 = 0 (rows 8..15)
@@ -296,6 +301,20 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   float* s_f = sh;
   float* s_l = sh + G * nsplit;
   const size_t hb0 = (size_t)b * p.nq + kvh * G;
+  constexpr int NI = (G * hd + kMmaWarps * 32 - 1) / (kMmaWarps * 32);   // outputs per thread
+  constexpr int SB = NI >= 4 ? 5 : 20 / NI;                             // splits per step: ~20 loads in flight
+  // The first SB splits' partial sums are requested together with the (max, sum) pairs: one trip to L2 instead of two.
+  float av[NI][SB];
+  auto load_acc = [&](int sp0) {
+#pragma unroll
+    for (int k = 0; k < NI; ++k) {
+      const int idx = min((int)threadIdx.x + k * kMmaWarps * 32, G * hd - 1);
+#pragma unroll
+      for (int i = 0; i < SB; ++i)
+        av[k][i] = sp0 + i < nsplit ? __ldcg(p.ws_acc + ((hb0 + idx / hd) * nsplit + sp0 + i) * hd + (idx % hd)) : 0.0f;
+    }
+  };
+  load_acc(0);
   for (int i = threadIdx.x; i < G * nsplit; i += blockDim.x) {
     const float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml) + hb0 * nsplit + i);
     s_f[i] = v.x;
@@ -321,20 +340,11 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
     for (int sp = lane; sp < nsplit; sp += 32) s_f[g * nsplit + sp] *= inv;
   }
   __syncthreads();
-  constexpr int NI = (G * hd + kMmaWarps * 32 - 1) / (kMmaWarps * 32);   // outputs per thread
-  constexpr int SB = NI >= 4 ? 5 : 20 / NI;                             // splits per step: ~20 loads in flight
   float a[NI];
 #pragma unroll
   for (int k = 0; k < NI; ++k) a[k] = 0.0f;
   for (int sp0 = 0; sp0 < nsplit; sp0 += SB) {
-    float av[NI][SB];
-#pragma unroll
-    for (int k = 0; k < NI; ++k) {
-      const int idx = min((int)threadIdx.x + k * kMmaWarps * 32, G * hd - 1);
-#pragma unroll
-      for (int i = 0; i < SB; ++i)
-        av[k][i] = sp0 + i < nsplit ? __ldcg(p.ws_acc + ((hb0 + idx / hd) * nsplit + sp0 + i) * hd + (idx % hd)) : 0.0f;
-    }
+    if (sp0 > 0) load_acc(sp0);
 #pragma unroll
     for (int k = 0; k < NI; ++k) {
       const int idx = min((int)threadIdx.x + k * kMmaWarps * 32, G * hd - 1);

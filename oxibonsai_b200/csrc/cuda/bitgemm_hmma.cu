@@ -19,6 +19,7 @@
 // (crates/oxibonsai-kernels/src/gpu_backend/cuda_prefill_kernels.rs:74-827).
 #include <cuda_fp16.h>
 
+#include "../comm/tp_comm.cuh"
 #include "common.cuh"
 
 namespace bonsai {
@@ -65,7 +66,7 @@ struct GhGroup {
 };
 
 template <int NT>   // n-tiles of 8 tokens (T <= 8 * NT)
-__global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p) {
+__global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p, TpComm tp) {
   extern __shared__ __align__(16) uint8_t gh_smem[];   // [2 stages][KW chunks][64 tokens][272 bytes]; later the k-warp partial sums
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -181,16 +182,41 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p)
   // ---- epilogue: lane holds (row g | g + 8) x (tokens nt * 8 + 2c, + 1) -------------------------------
   // The residual usually aliases the output (h += W x): inside a store loop every load would have to wait for the
   // previous store, a chain of exposed memory latencies, so the residuals are loaded as a block first.
+  // epi 3 (row-parallel shard of a tensor-parallel group): every value goes to all peers as one 8-byte {value, tag}
+  // store into slot [parity][my rank][token][row] before the residuals are even requested, and is summed with the
+  // peers' values in rank order below - the all-reduce and the residual add are this epilogue.
+  int tp_epoch = 0;
+  if (p.epi == 3) {
+    tp_epoch = ld_volatile(tp.epoch);
+    const unsigned long long tag_hi = (unsigned long long)((uint32_t)tp_epoch + 1u) << 32;
+    const int parity = tp_epoch & 1;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int tok = nt * 8 + 2 * c + e;
+        if (tok >= p.T) continue;
+        const size_t i_lo = (size_t)tok * p.n_rows + r_lo, i_hi = (size_t)tok * p.n_rows + r_hi;
+        const unsigned long long m_lo = tag_hi | __float_as_uint(tot[nt][e] * 128.0f), m_hi = tag_hi | __float_as_uint(tot[nt][2 + e] * 128.0f);
+        for (int q = 0; q < tp.size; ++q) {
+          if (q == tp.rank) continue;
+          unsigned long long* dst = tp_ll_big_slot(tp, q, parity, tp.rank);
+          if (ok_lo) tp_st_msg(dst + i_lo, m_lo);
+          if (ok_hi) tp_st_msg(dst + i_hi, m_hi);
+        }
+      }
+  }
   float res[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int tok = nt * 8 + 2 * c + e;
-      const bool rd = p.epi == 1 && tok < p.T;
+      const bool rd = (p.epi == 1 || (p.epi == 3 && p.residual != nullptr)) && tok < p.T;
       res[nt][e] = rd && ok_lo ? p.residual[(size_t)tok * p.out_ld + r_lo] : 0.0f;
       res[nt][2 + e] = rd && ok_hi ? p.residual[(size_t)tok * p.out_ld + r_hi] : 0.0f;
     }
+  bool tp_alive = true;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -204,9 +230,36 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p)
           if (r_lo + 1 < p.n_rows) p.out_f16[(size_t)tok * p.out_ld + hmma_k_pos(r_lo >> 1)] = __float2half_rn(v_lo / (1.0f + __expf(-v_lo)) * up_lo);
           if (r_hi + 1 < p.n_rows) p.out_f16[(size_t)tok * p.out_ld + hmma_k_pos(r_hi >> 1)] = __float2half_rn(v_hi / (1.0f + __expf(-v_hi)) * up_hi);
         }
+      } else if (p.epi == 3) {
+        if (tok < p.T) {
+          const uint32_t tag = (uint32_t)tp_epoch + 1u;
+          const int parity = tp_epoch & 1;
+          const size_t i_lo = (size_t)tok * p.n_rows + r_lo, i_hi = (size_t)tok * p.n_rows + r_hi;
+          float s_lo = res[nt][e], s_hi = res[nt][2 + e];
+          for (int q = 0; q < tp.size; ++q) {   // rank order: every rank adds the same numbers in the same order
+            const unsigned long long* src = tp_ll_big_slot(tp, tp.rank, parity, q);
+            if (ok_lo) s_lo += q == tp.rank ? v_lo : tp_recv_msg(tp, src + i_lo, tag, tp_alive);
+            if (ok_hi) s_hi += q == tp.rank ? v_hi : tp_recv_msg(tp, src + i_hi, tag, tp_alive);
+          }
+          if (ok_lo) p.out_f32[(size_t)tok * p.out_ld + r_lo] = s_lo;
+          if (ok_hi) p.out_f32[(size_t)tok * p.out_ld + r_hi] = s_hi;
+        }
       } else if (tok < p.T) {
         if (ok_lo) p.out_f32[(size_t)tok * p.out_ld + r_lo] = res[nt][e] + v_lo;
         if (ok_hi) p.out_f32[(size_t)tok * p.out_ld + r_hi] = res[nt][2 + e] + v_hi;
+      }
+    }
+  }
+  if (p.epi == 3) {
+    // the last row-warp of the grid to finish moves the exchange counter on (every one has read it by then)
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      const int prev = atomicAdd(tp.done_ctr, 1);
+      if (prev == (int)gridDim.x * RW - 1) {
+        *tp.done_ctr = 0;
+        *tp.epoch = tp_epoch + 1;
+        __threadfence();
       }
     }
   }
@@ -234,7 +287,7 @@ __global__ void norm_to_f16_hmma_kernel(const float* __restrict__ x, int x_ld, c
 }
 
 template <int NT>
-static int launch_gh(const GhParams& p, int grid, size_t smem, cudaStream_t st) {
+static int launch_gh(const GhParams& p, const TpComm& tp, int grid, size_t smem, cudaStream_t st) {
   static bool configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
@@ -243,7 +296,7 @@ static int launch_gh(const GhParams& p, int grid, size_t smem, cudaStream_t st) 
       return BONSAI_CUDA_LAUNCH_FAILED;
     configured[dev] = true;
   }
-  const cudaError_t e = launch_pdl(bitgemm_hmma_kernel<NT>, dim3(grid), dim3(kGhWarps * 32), smem, st, p);
+  const cudaError_t e = launch_pdl(bitgemm_hmma_kernel<NT>, dim3(grid), dim3(kGhWarps * 32), smem, st, p, tp);
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
@@ -254,11 +307,12 @@ extern "C" {
 // x_f16: activations [T][x_ld] f16 in hmma-K order (bonsai_norm_to_f16_hmma, or epi 2 of this kernel), T <= 64,
 // K % 128 == 0.  epi 0: out_f32 = W x; 1: out_f32 = residual + W x; 2: out_f16 = SwiGLU over interleaved gate / up rows
 // in hmma-K order (out_ld >= N / 2, N / 2 a multiple of 128 for a following GEMM).
-int bonsai_bitgemm_hmma(const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32, const float* residual,
-                        void* out_f16, int n_rows, int K, int T, int epi, int out_ld, cudaStream_t stream) {
+static int bitgemm_hmma_launch(const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32, const float* residual,
+                               void* out_f16, int n_rows, int K, int T, int epi, int out_ld, const bonsai::TpComm& tp, cudaStream_t stream) {
   using namespace bonsai;
-  if (K % 128 != 0 || K < 128 || n_rows < 1 || T < 1 || T > kGhMaxTok || epi < 0 || epi > 2 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
-  if ((epi <= 1 && out_f32 == nullptr) || (epi == 1 && residual == nullptr) || (epi == 2 && (out_f16 == nullptr || (n_rows & 1)))) return BONSAI_CUDA_BAD_ARG;
+  if (K % 128 != 0 || K < 128 || n_rows < 1 || T < 1 || T > kGhMaxTok || epi < 0 || epi > 3 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
+  if (epi == 3 && (out_f32 == nullptr || (size_t)T * n_rows > tp.lay.ll_big_elems)) return BONSAI_CUDA_BAD_ARG;
+  if (((epi <= 1 || epi == 3) && out_f32 == nullptr) || (epi == 1 && residual == nullptr) || (epi == 2 && (out_f16 == nullptr || (n_rows & 1)))) return BONSAI_CUDA_BAD_ARG;
   const int tiles16 = (n_rows + 15) / 16, ng = K / 128;
   // k-warps per CTA: the fewest waves of (steps per k-warp + fixed cost), CTAs per SM bounded by the stage memory
   int best_kw = 1;
@@ -283,9 +337,26 @@ int bonsai_bitgemm_hmma(const void* codes, const void* scales, const void* x_f16
   GhParams p{(const uint32_t*)codes, (const __half*)scales, (const __half*)x_f16, out_f32, residual, (__half*)out_f16,
              n_rows, K, T, epi, x_ld, out_ld, KW};
   const int nt = (T + 7) / 8;
-  if (nt <= 2) return launch_gh<2>(p, grid, smem, stream);
-  if (nt <= 4) return launch_gh<4>(p, grid, smem, stream);
-  return launch_gh<8>(p, grid, smem, stream);
+  if (epi == 3 && grid > 148) return BONSAI_CUDA_BAD_ARG;   // its CTAs wait on peers: all of them must be resident (one per SM at 130 registers)
+  if (nt <= 2) return launch_gh<2>(p, tp, grid, smem, stream);
+  if (nt <= 4) return launch_gh<4>(p, tp, grid, smem, stream);
+  return launch_gh<8>(p, tp, grid, smem, stream);
+}
+
+int bonsai_bitgemm_hmma(const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32, const float* residual,
+                        void* out_f16, int n_rows, int K, int T, int epi, int out_ld, cudaStream_t stream) {
+  if (epi == 3) return BONSAI_CUDA_BAD_ARG;
+  return bitgemm_hmma_launch(codes, scales, x_f16, x_ld, out_f32, residual, out_f16, n_rows, K, T, epi, out_ld, bonsai::TpComm{}, stream);
+}
+
+// Row-parallel shard of a tensor-parallel group: out_f32[T][out_ld] = residual + sum over the ranks of `comm` of their
+// W x, the exchange being part of the GEMM's epilogue ({value, tag} stores into the peers' memory).  Every rank
+// launches the same call on its K shard; T * n_rows <= 64 * hidden.  residual may be null or alias out_f32.
+int bonsai_bitgemm_hmma_tp(const void* comm, const void* codes, const void* scales, const void* x_f16, int x_ld, float* out_f32,
+                           const float* residual, int n_rows, int K, int T, int out_ld, cudaStream_t stream) {
+  if (comm == nullptr) return BONSAI_CUDA_BAD_ARG;
+  return bitgemm_hmma_launch(codes, scales, x_f16, x_ld, out_f32, residual, nullptr, n_rows, K, T, 3, out_ld,
+                             *static_cast<const bonsai::TpComm*>(comm), stream);
 }
 
 int bonsai_norm_to_f16_hmma(const float* x, int x_ld, const float* w, float eps, int T, int K, void* out, int out_ld, cudaStream_t stream) {

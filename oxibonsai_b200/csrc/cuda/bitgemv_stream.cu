@@ -88,15 +88,6 @@ __device__ __forceinline__ bool s16_wait(uint64_t* bar, uint32_t parity, int lan
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // Per (group, step) record of the activation side: the step's accumulator start values and f32 factor.
 struct __align__(16) S16Step {
   int og0, og1;      // -4^j * sum of the step's q1 (q2) values: takes out what the +1 of the codes adds to the integer dot product
@@ -425,28 +416,10 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
       const int parity = tp_epoch & 1;
       const unsigned long long msg = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
       for (int p = 0; p < tp.size; ++p)
-        if (p != tp.rank) st_relaxed_sys_u64(tp_ll_slot(tp, p, parity, tp.rank) + row, msg);
+        if (p != tp.rank) tp_st_msg(tp_ll_slot(tp, p, parity, tp.rank) + row, msg);
       float sum = a.residual != nullptr ? a.residual[row] : 0.0f;
-      for (int s = 0; s < tp.size; ++s) {
-        float pv = v;
-        if (s != tp.rank) {
-          const unsigned long long* src = tp_ll_slot(tp, tp.rank, parity, s) + row;
-          bool got = false;
-          for (uint32_t it = 0; it < tp.spin_limit; ++it) {
-            const unsigned long long m = ld_relaxed_sys_u64(src);
-            if ((uint32_t)(m >> 32) == tag) {
-              pv = __uint_as_float((uint32_t)m);
-              got = true;
-              break;
-            }
-          }
-          if (!got) {
-            atomicExch(tp.status, 2);
-            pv = 0.0f;
-          }
-        }
-        sum += pv;
-      }
+      bool alive = true;
+      for (int s = 0; s < tp.size; ++s) sum += s == tp.rank ? v : tp_recv_msg(tp, tp_ll_slot(tp, tp.rank, parity, s) + row, tag, alive);
       a.out[row] = sum;
     }
   }

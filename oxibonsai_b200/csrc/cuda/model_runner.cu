@@ -45,6 +45,7 @@ int bonsai_attn_decode_qkv_f16(const float*, int, const float*, const float*, fl
                                int, int, int, int, int, int, void*, void*, int, float*, float*, int*, float*, cudaStream_t);
 int bonsai_norm_to_f16_hmma(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
 int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, const float*, void*, int, int, int, int, int, cudaStream_t);
+int bonsai_bitgemm_hmma_tp(const void*, const void*, const void*, const void*, int, float*, const float*, int, int, int, int, cudaStream_t);
 int bonsai_attn_prefill_order(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                               const float*, void*, int, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
@@ -346,7 +347,10 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   // 40.2 / 33.3 against 21.8 / 25.0 / 38.4 / 30.7, 64 tokens 39.6 / 20.6 / 66.0 / 51.7 against 26.3 / 26.1 / 43.4 / 39.0:
   // everything up to 32 sequences, and the O projection (few rows, short K) up to 64.
   const bool hm_ok = r.ic[IC_FAST] != 5 && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
-  const bool hm_all = hm_ok && batch <= 32, hm_o = hm_ok && batch <= 64;
+  // Tensor parallel: every GEMM of a decode batch (<= 64 sequences) runs on the mma.sync kernel - the K and row ranges of
+  // a rank are short - and the two row-parallel ones carry the all-reduce + residual add in their epilogue.
+  const bool tp_fused = tp && hm_ok && batch <= 64;
+  const bool hm_all = hm_ok && (batch <= 32 || tp_fused), hm_o = hm_ok && batch <= 64;
   auto to_f16 = [&](bool hm, const float* src, int src_ld, const float* w, int K, void* dst, int dst_ld) {
     return hm ? bonsai_norm_to_f16_hmma(src, src_ld, w, r.eps, batch, K, dst, dst_ld, st)
               : bonsai_norm_to_f16_paired(src, src_ld, w, r.eps, batch, K, dst, dst_ld, 0, st);
@@ -370,6 +374,8 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
     RC(to_f16(hm_o, attn, qd, nullptr, qd, attn16, qd));
     if (!tp) {
       RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, hidden, qd, 1, hidden));
+    } else if (tp_fused) {
+      RC(bonsai_bitgemm_hmma_tp(r.comm, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, hidden, qd, batch, hidden, st));
     } else {
       RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, big[0], nullptr, nullptr, hidden, qd, 0, hidden));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
@@ -378,6 +384,8 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
     RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
     if (!tp) {
       RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
+    } else if (tp_fused) {
+      RC(bonsai_bitgemm_hmma_tp(r.comm, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, hidden, inter, batch, hidden, st));
     } else {
       RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big[1], nullptr, nullptr, hidden, inter, 0, hidden));
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 1, st));

@@ -109,7 +109,14 @@ __device__ float block_sum_f(float v, float* sh) {
   return t;
 }
 
-// grid = batch, block = 1024
+// Greedy rows of small batches are scanned by kArgmaxBlocks CTAs each (a 152k-entry row is 608 KB: one CTA needs ~10
+// dependent trips to L2 for it); the CTAs leave their candidates here and the last one to arrive picks the winner.
+constexpr int kArgmaxBlocks = 32, kArgmaxRows = 64;
+struct ArgmaxCand { float v; int i; };
+__device__ ArgmaxCand g_argmax_cand[kArgmaxRows][kArgmaxBlocks];
+__device__ int g_argmax_count[kArgmaxRows];   // zero between launches
+
+// grid = (batch, 1 or kArgmaxBlocks), block = 1024
 __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __restrict__ logits, int vocab, int stride,
                                                              const float* __restrict__ temps, const int* __restrict__ topks,
                                                              const float* __restrict__ topps,
@@ -125,6 +132,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __res
   __shared__ int s_pick;
 
   const int b = blockIdx.x, t = threadIdx.x;
+  const int nby = gridDim.y, by = blockIdx.y;
   const float* lg = logits + (size_t)b * stride;
   const uint32_t* am = allow_mask ? allow_mask + (size_t)b * mask_words : nullptr;
   const float T = temps ? temps[b] : 0.0f;
@@ -133,6 +141,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __res
   auto allowed = [&](int i) -> bool { return am == nullptr || ((am[i >> 5] >> (i & 31)) & 1u); };
 
   int result = 0;
+  if (by > 0 && !(T < 1e-6f)) return;      // only the greedy scan is split over several CTAs
   if (T < 1e-6f) {
     // ---- greedy: last maximal index ----
     // Threads stride through the row with 16-byte loads (a warp reads 512 contiguous bytes); a thread that walks its
@@ -145,15 +154,17 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __res
     };
     const int nv4 = ((stride & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) ? vocab >> 2 : 0;
     const float4* lg4 = reinterpret_cast<const float4*>(lg);
+    const int per4 = (nv4 + nby - 1) / nby, lo4 = by * per4, hi4 = min(nv4, lo4 + per4);
 #pragma unroll 4
-    for (int i4 = t; i4 < nv4; i4 += kSampThreads) {
+    for (int i4 = lo4 + t; i4 < hi4; i4 += kSampThreads) {
       const float4 v = lg4[i4];
       consider(v.x, 4 * i4);
       consider(v.y, 4 * i4 + 1);
       consider(v.z, 4 * i4 + 2);
       consider(v.w, 4 * i4 + 3);
     }
-    for (int i = 4 * nv4 + t; i < vocab; i += kSampThreads) consider(lg[i], i);
+    if (by == nby - 1)
+      for (int i = 4 * nv4 + t; i < vocab; i += kSampThreads) consider(lg[i], i);
     s_val[t] = bv;
     s_idx[t] = bi;
     __syncthreads();
@@ -163,6 +174,36 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const float* __res
         int oi = s_idx[t + o];
         // equal values: the larger index wins (last maximal index overall)
         if (oi >= 0 && (s_idx[t] < 0 || ov > s_val[t] || (ov == s_val[t] && oi > s_idx[t]))) { s_val[t] = ov; s_idx[t] = oi; }
+      }
+      __syncthreads();
+    }
+    if (nby > 1) {
+      // leave this CTA's candidate; the last CTA of the row to arrive reduces them (ties: the larger index)
+      if (t == 0) {
+        g_argmax_cand[b][by] = ArgmaxCand{s_val[0], s_idx[0]};
+        __threadfence();
+        const int prev = atomicAdd(&g_argmax_count[b], 1);
+        s_pick = prev == nby - 1;
+        if (s_pick) g_argmax_count[b] = 0;
+      }
+      __syncthreads();
+      if (!s_pick) return;
+      __threadfence();
+      if (t < 32) {
+        float v = -INFINITY;
+        int i = -1;
+        for (int c = t; c < nby; c += 32) {
+          const float cv = __ldcg(&g_argmax_cand[b][c].v);
+          const int ci = __ldcg(&g_argmax_cand[b][c].i);
+          if (ci >= 0 && (i < 0 || cv > v || (cv == v && ci > i))) { v = cv; i = ci; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+          if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi > i))) { v = ov; i = oi; }
+        }
+        if (t == 0) s_idx[0] = i;
       }
       __syncthreads();
     }
@@ -409,7 +450,9 @@ int bonsai_sample(const float* logits, int batch, int vocab, int stride, const f
                   const uint32_t* allow_mask, int mask_words, cudaStream_t stream) {
   if (batch <= 0 || vocab <= 0 || stride < vocab) return BONSAI_CUDA_BAD_ARG;
   if (temps != nullptr && rng == nullptr) return BONSAI_CUDA_BAD_ARG;
-  bonsai::sample_kernel<<<batch, bonsai::kSampThreads, 0, stream>>>(logits, vocab, stride, temps, topks, topps, rng, out_tokens,
+  // a few rows: split every greedy row's scan over kArgmaxBlocks CTAs (their meeting place is a fixed-size device array)
+  const int nby = (batch <= 4 && batch <= bonsai::kArgmaxRows && vocab >= 32768) ? bonsai::kArgmaxBlocks : 1;
+  bonsai::sample_kernel<<<dim3(batch, nby), bonsai::kSampThreads, 0, stream>>>(logits, vocab, stride, temps, topks, topps, rng, out_tokens,
                                                                     positions, advance, allow_mask, mask_words);
   return bonsai::launch_status();
 }

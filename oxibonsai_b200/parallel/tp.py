@@ -81,7 +81,7 @@ class TpGroup:
         lib = _lib()
         self.rank, self.size = rank, size
         self.recv_elems, self.logits_elems, self.big_elems = hidden, max_batch * vocab, big_elems
-        offs = (C.c_size_t * 6)()
+        offs = (C.c_size_t * 7)()
         total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self._hdl = symm.rendezvous(self.buffer, dist.group.WORLD)
@@ -110,7 +110,7 @@ class TpGroup:
         self = cls.__new__(cls)
         self.rank, self.size = rank, size
         self.recv_elems, self.logits_elems, self.big_elems = hidden, max_batch * vocab, big_elems
-        offs = (C.c_size_t * 6)()
+        offs = (C.c_size_t * 7)()
         total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
         self._peers = [torch.zeros(total, dtype=torch.uint8, device=device) for _ in range(size)]
         self.buffer, self._hdl = self._peers[rank], None
