@@ -30,13 +30,6 @@ constexpr int kGhRow = 272;                       // bytes per token row of a ch
 constexpr int kGhChunk = kGhMaxTok * kGhRow;      // 17408 bytes: one 128-input chunk of 64 tokens
 constexpr int kGhDepth = 3;                       // weight groups in flight per warp
 
-// position of logical input k inside its 128-input group in the hmma-K order
-__host__ __device__ inline int hmma_k_pos(int k) {
-  const int r = k & 127, wq = r >> 4, e = r & 15;
-  const int c = wq >> 1, j = wq & 1, plane = e >> 3, p = e & 3, h = (e >> 2) & 1;
-  return (k & ~127) | ((j * 4 + p) * 16 + plane * 8 + 2 * c + h);
-}
-
 __device__ __forceinline__ uint32_t gh_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void gh_cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

@@ -168,6 +168,8 @@ struct S16Args {
   int* status;               // device int, set non-zero when a bounded wait expired (may be null)
   float eps;
   int N, K, epi;
+  const uint8_t* next_w;     // weights the following kernel will stream (may be null): requested into L2 from here
+  unsigned long long next_bytes;
 };
 
 __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, TpComm tp) {
@@ -205,6 +207,12 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
   if (warp == kS16Warps) {
     // ---- producer: one lane streams the CTA's byte range through the ring (weights depend on no earlier kernel) ----
     if (lane == 0) {
+      // slice of the next kernel's weights that this CTA requests into L2 (16-byte units)
+      const unsigned long long pf_units = a.next_w != nullptr ? a.next_bytes / 16 : 0;
+      const unsigned long long pf_lo = pf_units * blockIdx.x / gridDim.x, pf_hi = pf_units * (blockIdx.x + 1) / gridDim.x;
+      const uint8_t* pf_ptr = a.next_w + pf_lo * 16;
+      unsigned long long pf_left = (pf_hi - pf_lo) * 16;
+      const unsigned long long pf_piece = 32768;
       int slot = 0;
       uint32_t phase = 1;      // parity of the use of a slot that must have been released: none for the first round
       for (int s = 0; s < nstage_total; ++s, slot = slot + 1 == kS16Stages ? 0 : slot + 1) {
@@ -215,6 +223,20 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
         const uint32_t bytes = (uint32_t)nb * kS16BlockBytes;
         tc::mbar_arrive_expect_tx(&full[slot], bytes);
         tc::bulk_g2s(ring + (size_t)slot * kS16StageBytes, wbase + (size_t)b0 * kS16BlockBytes, bytes, &full[slot]);
+        // This kernel is bound by instruction issue, not by HBM: the idle bandwidth brings the next kernel's weights
+        // into L2, a slice per CTA and a piece per stage, so that its first stage does not start with a trip to DRAM.
+        if (pf_left > 0) {
+          const unsigned long long n = pf_left < pf_piece ? pf_left : pf_piece;
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr), "r"((uint32_t)n) : "memory");
+          pf_ptr += n;
+          pf_left -= n;
+        }
+      }
+      while (pf_left > 0) {
+        const unsigned long long n = pf_left < pf_piece ? pf_left : pf_piece;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr), "r"((uint32_t)n) : "memory");
+        pf_ptr += n;
+        pf_left -= n;
       }
       // The consumers wait for every stage that was issued, so all copies have landed when they finish.  After an
       // abort they no longer do: give outstanding copies a bounded time to land before this CTA's memory is released.
@@ -517,8 +539,9 @@ int bonsai_s16_tune(int pdl) {
 // their W x (every rank launches the same call on its shard; residual may be null).  x is f32[K], RMS-normalised with
 // norm_w first when that is non-null.  K % 128 == 0, 128 <= K <= 16384, at most 12 row tiles per CTA.  `status`
 // (device int, may be null) is set to 5 if a bounded wait on the copy pipeline expired.
-int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, float eps, float* out, const float* residual,
-                       int N, int K, int epi, const void* comm, int* status, cudaStream_t stream) {
+static int bitgemv_s16_launch(const void* w16, const float* x, const float* norm_w, float eps, float* out, const float* residual,
+                              int N, int K, int epi, const void* comm, int* status, const void* next_w, size_t next_bytes,
+                              cudaStream_t stream) {
   using namespace bonsai;
   if (K % 128 != 0 || K < 128 || K > 16384 || N <= 0 || epi < 0 || epi > 3) return BONSAI_CUDA_BAD_ARG;
   if (epi == SEPI_RESID && residual == nullptr) return BONSAI_CUDA_BAD_ARG;
@@ -555,6 +578,8 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
   a.N = N;
   a.K = K;
   a.epi = epi;
+  a.next_w = static_cast<const uint8_t*>(next_w);
+  a.next_bytes = next_w != nullptr ? next_bytes : 0;
   cudaError_t e;
   if (g_s16_pdl) {
     e = launch_pdl(bitgemv_s16_kernel, dim3(grid), dim3(kS16Threads), smem, stream, a, tp);
@@ -563,6 +588,20 @@ int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, flo
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
+int bonsai_bitgemv_s16(const void* w16, const float* x, const float* norm_w, float eps, float* out, const float* residual,
+                       int N, int K, int epi, const void* comm, int* status, cudaStream_t stream) {
+  return bitgemv_s16_launch(w16, x, norm_w, eps, out, residual, N, K, epi, comm, status, nullptr, 0, stream);
+}
+
+// The same, and while it runs the kernel requests `next_bytes` bytes at `next_w` (16-byte aligned; the weights of the
+// GEMV that follows in the stream) into L2.
+int bonsai_bitgemv_s16_pf(const void* w16, const float* x, const float* norm_w, float eps, float* out, const float* residual,
+                          int N, int K, int epi, const void* comm, int* status, const void* next_w, size_t next_bytes,
+                          cudaStream_t stream) {
+  if (next_w != nullptr && (reinterpret_cast<uintptr_t>(next_w) & 15) != 0) return BONSAI_CUDA_BAD_ARG;
+  return bitgemv_s16_launch(w16, x, norm_w, eps, out, residual, N, K, epi, comm, status, next_w, next_bytes, stream);
 }
 
 }  // extern "C"

@@ -103,6 +103,13 @@ __device__ __forceinline__ float dot_word16(uint32_t w, const float* x) {
   return acc;
 }
 
+// position of logical input k inside its 128-input group in the hmma-K order
+__host__ __device__ inline int hmma_k_pos(int k) {
+  const int r = k & 127, wq = r >> 4, e = r & 15;
+  const int c = wq >> 1, j = wq & 1, plane = e >> 3, p = e & 3, h = (e >> 2) & 1;
+  return (k & ~127) | ((j * 4 + p) * 16 + plane * 8 + 2 * c + h);
+}
+
 // Launch with programmatic dependent launch enabled: the kernel may start while its predecessor in
 // the stream is still running and must execute griddepcontrol.wait before touching anything the
 // predecessor writes (or writing anything it reads).

@@ -49,7 +49,9 @@ int bonsai_bitgemm_hmma_tp(const void*, const void*, const void*, const void*, i
 int bonsai_attn_prefill_order(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                               const float*, void*, int, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
-int bonsai_bitgemv_s16(const void*, const float*, const float*, float, float*, const float*, int, int, int, const void*, int*, cudaStream_t);
+int bonsai_bitgemv_s16_pf(const void*, const float*, const float*, float, float*, const float*, int, int, int, const void*, int*, const void*,
+                          size_t, cudaStream_t);
+size_t bonsai_s16_bytes(int, int);
 }
 
 namespace bonsai {
@@ -74,7 +76,15 @@ enum StepPtr {
   SP_COUNT
 };
 
+// K / V pools of one layer in one page format.
+struct KvPoolPtrs { uint64_t k = 0, v = 0, ks = 0, vs = 0; };
+
 struct Runner {
+  // Page formats beside the default one (ic[IC_KVT]): pools[kvt][layer], empty when that format has no pool.  slot_fmt[s] is
+  // the page format of the sequence in slot s (slots beyond its size use the default): a KV-pressure policy admits new
+  // sequences in a denser format while the old ones keep theirs, so one decode batch can mix formats.
+  std::vector<KvPoolPtrs> pools[4];
+  std::vector<int> slot_fmt;
   int ic[IC_COUNT];
   float eps;
   uint64_t gp[GP_COUNT];
@@ -89,26 +99,55 @@ static inline T* P(uint64_t v) { return reinterpret_cast<T*>(v); }
 
 #define RC(expr) do { int _rc = (expr); if (_rc != 0) return _rc; } while (0)
 
+static inline int slot_format(const Runner& r, int slot) {
+  return slot < (int)r.slot_fmt.size() ? r.slot_fmt[slot] : r.ic[IC_KVT];
+}
+static inline KvPoolPtrs layer_pool(const Runner& r, const uint64_t* lp, int layer, int kvt) {
+  if (kvt != r.ic[IC_KVT] && !r.pools[kvt].empty()) return r.pools[kvt][layer];
+  KvPoolPtrs p;
+  p.k = lp[LP_KPOOL]; p.v = lp[LP_VPOOL]; p.ks = lp[LP_KSCALE]; p.vs = lp[LP_VSCALE];
+  return p;
+}
+
 // QK-norm + RoPE + KV append + decode attention of one new token per sequence: one fused launch for f16 pages with
 // head_dim 128 on the packed-half path, otherwise (other page formats, exact mode, shapes the fused kernel declines)
-// the two separate kernels.
-static int qkv_attention(Runner& r, const uint64_t* lp, const uint64_t* sp, const float* qkv, int qkv_n, float* q, float* attn,
-                         const int* positions, const int* bt, int batch, int nsplit, cudaStream_t st) {
-  const int nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL], hd = r.ic[IC_HEAD_DIM];
-  if (r.ic[IC_KVT] == 1 && hd == 128 && r.ic[IC_FAST] != 0) {
+// the two separate kernels.  Slots b0 .. b0+n-1 of the step buffers, all in page format kvt.
+static int qkv_attention_run(Runner& r, const uint64_t* lp, const uint64_t* sp, const KvPoolPtrs& pool, int kvt, const float* qkv, int qkv_n,
+                             float* q, float* attn, const int* positions, const int* bt, int b0, int n, int nsplit, cudaStream_t st) {
+  const int nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL], hd = r.ic[IC_HEAD_DIM], mp = r.ic[IC_MAX_PAGES];
+  qkv += (size_t)b0 * qkv_n;
+  q += (size_t)b0 * nq * hd;
+  attn += (size_t)b0 * nq * hd;
+  positions += b0;
+  bt += (size_t)b0 * mp;
+  float* ws_acc = P<float>(sp[SP_WS_ACC]) + (size_t)b0 * nq * nsplit * hd;
+  float* ws_ml = P<float>(sp[SP_WS_ML]) + (size_t)b0 * nq * nsplit * 2;
+  int* counters = P<int>(sp[SP_ATTN_COUNTERS]) + (size_t)b0 * nkv;
+  if (kvt == 1 && hd == 128 && r.ic[IC_FAST] != 0) {
     const int rc = bonsai_attn_decode_qkv_f16(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
-                                              P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd,
-                                              r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), nsplit,
-                                              P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, st);
+                                              P<float>(r.gp[GP_ROPE_SIN]), positions, bt, mp, n, nq, nkv, hd, r.ic[IC_PAGE_SIZE],
+                                              P<void>(pool.k), P<void>(pool.v), nsplit, ws_acc, ws_ml, counters, attn, st);
     if (rc != BONSAI_CUDA_BAD_ARG) return rc;   // bad argument = not a shape of the fused kernel
   }
   RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
-                                P<float>(r.gp[GP_ROPE_SIN]), positions, bt, r.ic[IC_MAX_PAGES], q, batch, nq, nkv, hd,
-                                r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]),
-                                P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), st));
-  return bonsai_attn_decode(q, positions, bt, r.ic[IC_MAX_PAGES], batch, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE],
-                            P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]),
-                            nsplit, P<float>(sp[SP_WS_ACC]), P<float>(sp[SP_WS_ML]), P<int>(sp[SP_ATTN_COUNTERS]), attn, 0, st);
+                                P<float>(r.gp[GP_ROPE_SIN]), positions, bt, mp, q, n, nq, nkv, hd, kvt, r.ic[IC_PAGE_SIZE], P<void>(pool.k),
+                                P<void>(pool.v), P<float>(pool.ks), P<float>(pool.vs), st));
+  return bonsai_attn_decode(q, positions, bt, mp, n, nq, nkv, hd, kvt, r.ic[IC_PAGE_SIZE], P<void>(pool.k), P<void>(pool.v),
+                            P<float>(pool.ks), P<float>(pool.vs), nsplit, ws_acc, ws_ml, counters, attn, 0, st);
+}
+
+// The same for slots 0 .. batch-1: one launch (pair) per run of consecutive slots that share a page format.
+static int qkv_attention(Runner& r, int layer, const uint64_t* lp, const uint64_t* sp, const float* qkv, int qkv_n, float* q, float* attn,
+                         const int* positions, const int* bt, int batch, int nsplit, cudaStream_t st) {
+  int b0 = 0;
+  while (b0 < batch) {
+    const int kvt = slot_format(r, b0);
+    int b1 = b0 + 1;
+    while (b1 < batch && slot_format(r, b1) == kvt) ++b1;
+    RC(qkv_attention_run(r, lp, sp, layer_pool(r, lp, layer, kvt), kvt, qkv, qkv_n, q, attn, positions, bt, b0, b1 - b0, nsplit, st));
+    b0 = b1;
+  }
+  return 0;
 }
 
 // flags: bit 0 = run the sampler and advance positions, bit 1 = skip the LM head
@@ -137,10 +176,12 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   // GEMV (bitgemv_stream.cu) when that form was built and the shape fits; epi 3 = row-parallel sum over the
   // tensor-parallel group + residual inside the same kernel.
   int* status = P<int>(sp[SP_STATUS]);
+  // (next, next_n, next_k): the S16 matrix of the GEMV that follows in the stream, which this one requests into L2.
   auto linear = [&](const uint64_t* lp, int w_codes, int w_s16, const float* x, const float* norm_w, float* out, const float* residual,
-                    int n, int k, int epi) -> int {
+                    int n, int k, int epi, uint64_t next, int next_n, int next_k) -> int {
     if (r.ic[IC_FAST] == 1 && lp[w_s16] != 0) {
-      const int rc = bonsai_bitgemv_s16(P<void>(lp[w_s16]), x, norm_w, r.eps, out, residual, n, k, epi, r.comm, status, st);
+      const int rc = bonsai_bitgemv_s16_pf(P<void>(lp[w_s16]), x, norm_w, r.eps, out, residual, n, k, epi, r.comm, status, P<void>(next),
+                                           next != 0 ? bonsai_s16_bytes(next_n, next_k) : 0, st);
       if (rc != BONSAI_CUDA_BAD_ARG) return rc;   // bad argument = a shape the streamed kernel declines
     }
     if (epi == 3)
@@ -152,19 +193,20 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
     RC(bonsai_embed_f16(P<void>(r.gp[GP_EMBD]), tokens + b, h + (size_t)b * hidden, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
+    const uint64_t next_qkv = l + 1 < r.ic[IC_LAYERS] ? r.lp[(size_t)(l + 1) * LP_COUNT + LP_QKV_S16] : 0;
     for (int b = 0; b < batch; ++b)
       RC(linear(lp, LP_QKV_CODES, LP_QKV_S16, h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]), qkv + (size_t)b * qkv_n, nullptr,
-                qkv_n, hidden, 0));
-    RC(qkv_attention(r, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, r.ic[IC_NSPLIT], st));
+                qkv_n, hidden, 0, lp[LP_O_S16], hidden, qd));
+    RC(qkv_attention(r, l, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, r.ic[IC_NSPLIT], st));
     for (int b = 0; b < batch; ++b)
       RC(linear(lp, LP_O_CODES, LP_O_S16, attn + (size_t)b * qd, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd,
-                tp ? 3 : 1));
+                tp ? 3 : 1, lp[LP_GU_S16], 2 * inter, hidden));
     for (int b = 0; b < batch; ++b)
       RC(linear(lp, LP_GU_CODES, LP_GU_S16, h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), act + (size_t)b * inter, nullptr,
-                2 * inter, hidden, 2));
+                2 * inter, hidden, 2, lp[LP_DOWN_S16], hidden, inter));
     for (int b = 0; b < batch; ++b)
       RC(linear(lp, LP_DOWN_CODES, LP_DOWN_S16, act + (size_t)b * inter, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden,
-                inter, tp ? 3 : 1));
+                inter, tp ? 3 : 1, next_qkv, qkv_n, hidden));
   }
   if (!(flags & 2)) {
     if (!tp) {
@@ -254,25 +296,27 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
               : pf_gemm(r, codes, scales, x, x_ld, out_f32, residual, out_f16, status, n_rows, K, T, epi, out_ld, sms, nullptr, st);
   };
 
+  const int kvt = slot_format(r, slot);                   // page format of this sequence
   RC(bonsai_embed_rows_f16(P<void>(r.gp[GP_EMBD]), tokens, h, T, hidden, vocab, st));
   for (int l = 0; l < r.ic[IC_LAYERS]; ++l) {
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
+    const KvPoolPtrs pool = layer_pool(r, lp, l, kvt);
     RC(to_f16(P<float>(lp[LP_ATTN_NORM])));
     RC(gemm(P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, qkv_n, hidden, 0, qkv_n));
     // every row of the chunk uses the same page list: a block-table stride of zero
     RC(bonsai_qknorm_rope_kvstore(qkv, qkv_n, P<float>(lp[LP_Q_NORM]), P<float>(lp[LP_K_NORM]), r.eps, P<float>(r.gp[GP_ROPE_COS]),
-                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, 0, q, T, nq, nkv, hd, r.ic[IC_KVT],
-                                  r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]), P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]),
-                                  P<float>(lp[LP_VSCALE]), st));
+                                  P<float>(r.gp[GP_ROPE_SIN]), positions, bt, 0, q, T, nq, nkv, hd, kvt,
+                                  r.ic[IC_PAGE_SIZE], P<void>(pool.k), P<void>(pool.v), P<float>(pool.ks),
+                                  P<float>(pool.vs), st));
     if (hm) {
       float* attn32 = P<float>(pp[PP_SM_ATTN]);
-      RC(bonsai_attn_decode(q, positions, bt, 0, T, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]),
-                            P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), sm_splits, P<float>(pp[PP_SM_ACC]),
+      RC(bonsai_attn_decode(q, positions, bt, 0, T, nq, nkv, hd, kvt, r.ic[IC_PAGE_SIZE], P<void>(pool.k),
+                            P<void>(pool.v), P<float>(pool.ks), P<float>(pool.vs), sm_splits, P<float>(pp[PP_SM_ACC]),
                             P<float>(pp[PP_SM_ML]), P<int>(pp[PP_SM_CTR]), attn32, 0, st));
       RC(bonsai_norm_to_f16_hmma(attn32, qd, nullptr, r.eps, T, qd, attn, qd, st));
     } else {
-      RC(bonsai_attn_prefill_order(q, T, pos0, bt, nq, nkv, hd, r.ic[IC_KVT], r.ic[IC_PAGE_SIZE], P<void>(lp[LP_KPOOL]),
-                                   P<void>(lp[LP_VPOOL]), P<float>(lp[LP_KSCALE]), P<float>(lp[LP_VSCALE]), attn, qd, 0, st));
+      RC(bonsai_attn_prefill_order(q, T, pos0, bt, nq, nkv, hd, kvt, r.ic[IC_PAGE_SIZE], P<void>(pool.k),
+                                   P<void>(pool.v), P<float>(pool.ks), P<float>(pool.vs), attn, qd, 0, st));
     }
     if (!tp) {
       RC(gemm(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, hidden, qd, 1, hidden));
@@ -312,11 +356,12 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
 // tcgen05 GEMM.  The reference's continuous batching re-runs a full single-sequence generate per
 // request per step (crates/oxibonsai-runtime/src/continuous_batch.rs:283-293).
 //
-// Tensor parallel: the row-parallel O and down GEMMs write partial sums into alternating halves of
-// the symmetric big area and one kernel per all-reduce (entry flag barrier + peer loads + residual
-// add) folds them into h; the vocab-parallel LM head writes [batch][local rows] and the slices are
-// pushed into every rank's logits area.  Every step issues an even number of all-reduces, so the
-// alternation of halves continues across replays of a captured step.
+// Tensor parallel: up to 64 sequences, the row-parallel O and down GEMMs run on the mma.sync kernel and their epilogue
+// is the all-reduce + residual add ({value, tag} stores into the peers' memory, summed in rank order).  Larger batches
+// write partial sums into alternating halves of the symmetric big area and one kernel per all-reduce (entry flag
+// barrier + peer loads + residual add) folds them into h; every step issues an even number of those, so the
+// alternation of halves continues across replays of a captured step.  The vocab-parallel LM head writes
+// [batch][local rows] and the slices are pushed into every rank's logits area.
 static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp, int batch, int flags, int mask_words,
                                cudaStream_t st) {
   const int hidden = r.ic[IC_HIDDEN], inter = r.ic[IC_INTER_LOCAL], nq = r.ic[IC_HEADS_LOCAL], nkv = r.ic[IC_KV_HEADS_LOCAL];
@@ -349,8 +394,10 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   const bool hm_ok = r.ic[IC_FAST] != 5 && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
   // Tensor parallel: every GEMM of a decode batch (<= 64 sequences) runs on the mma.sync kernel - the K and row ranges of
   // a rank are short - and the two row-parallel ones carry the all-reduce + residual add in their epilogue.
+  // Between 33 and 64 sequences the column-parallel GEMMs stay on tcgen05 and the gate/up epilogue writes the K order the
+  // mma.sync down projection reads.
   const bool tp_fused = tp && hm_ok && batch <= 64;
-  const bool hm_all = hm_ok && (batch <= 32 || tp_fused), hm_o = hm_ok && batch <= 64;
+  const bool hm_all = hm_ok && batch <= 32, hm_o = hm_ok && batch <= 64;
   auto to_f16 = [&](bool hm, const float* src, int src_ld, const float* w, int K, void* dst, int dst_ld) {
     return hm ? bonsai_norm_to_f16_hmma(src, src_ld, w, r.eps, batch, K, dst, dst_ld, st)
               : bonsai_norm_to_f16_paired(src, src_ld, w, r.eps, batch, K, dst, dst_ld, 0, st);
@@ -370,7 +417,7 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
     const uint64_t* lp = &r.lp[(size_t)l * LP_COUNT];
     RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_ATTN_NORM]), hidden, xn, xn_ld));
     RC(gemm(hm_all, P<void>(lp[LP_QKV_CODES]), P<void>(lp[LP_QKV_SCALES]), xn, xn_ld, qkv, nullptr, nullptr, qkv_n, hidden, 0, qkv_n));
-    RC(qkv_attention(r, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, attn_splits, st));
+    RC(qkv_attention(r, l, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, attn_splits, st));
     RC(to_f16(hm_o, attn, qd, nullptr, qd, attn16, qd));
     if (!tp) {
       RC(gemm(hm_o, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn16, qd, h, h, nullptr, hidden, qd, 1, hidden));
@@ -381,7 +428,8 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
     }
     RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_FFN_NORM]), hidden, xn, xn_ld));
-    RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
+    RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden,
+            tp_fused && !hm_all ? 4 : 2, inter));
     if (!tp) {
       RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
     } else if (tp_fused) {
@@ -429,6 +477,25 @@ void* bonsai_runner_create(const int* icfg, float eps, const uint64_t* global_pt
   for (int i = 0; i < GP_COUNT; ++i) r->gp[i] = global_ptrs[i];
   r->lp.assign(layer_ptrs, layer_ptrs + (size_t)icfg[IC_LAYERS] * LP_COUNT);
   return r;
+}
+
+// Registers the K / V pools of `layer` in page format kvt (0 f32, 1 f16, 2 int8, 3 int4) beside the runner's default format.
+int bonsai_runner_set_pool(void* rp, int kvt, int layer, const void* k, const void* v, const void* ks, const void* vs) {
+  bonsai::Runner& r = *static_cast<bonsai::Runner*>(rp);
+  if (kvt < 0 || kvt > 3 || layer < 0 || layer >= r.ic[bonsai::IC_LAYERS]) return BONSAI_CUDA_BAD_ARG;
+  if (r.pools[kvt].empty()) r.pools[kvt].resize(r.ic[bonsai::IC_LAYERS]);
+  bonsai::KvPoolPtrs p;
+  p.k = (uint64_t)k; p.v = (uint64_t)v; p.ks = (uint64_t)ks; p.vs = (uint64_t)vs;
+  r.pools[kvt][layer] = p;
+  return 0;
+}
+// Page format of the sequences in slots 0 .. n-1 for the launches that follow (and the graphs captured from them).
+int bonsai_runner_set_slot_formats(void* rp, const int* fmts, int n) {
+  bonsai::Runner& r = *static_cast<bonsai::Runner*>(rp);
+  for (int i = 0; i < n; ++i)
+    if (fmts[i] < 0 || fmts[i] > 3 || (fmts[i] != r.ic[bonsai::IC_KVT] && r.pools[fmts[i]].empty())) return BONSAI_CUDA_BAD_ARG;
+  r.slot_fmt.assign(fmts, fmts + n);
+  return 0;
 }
 
 void bonsai_runner_destroy(void* r) { delete static_cast<bonsai::Runner*>(r); }

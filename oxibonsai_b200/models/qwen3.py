@@ -272,7 +272,9 @@ class Qwen3Runner:
         cos, sin = rope_table(hd, max_seq, cfg.rope_base)
         self.rope_cos = torch.from_numpy(cos).to(dev)
         self.rope_sin = torch.from_numpy(sin).to(dev)
-        self._graphs: dict[tuple[int, int], torch.cuda.CUDAGraph] = {}
+        self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.kv_pools: dict[int, PagedKvCache] = {kv.kvt: kv}      # page pools by format; kv is the default one
+        self.slot_formats: list[int] = [kv.kvt] * B                # page format of the sequence in every slot
         self._build_native()
 
     def _build_native(self) -> None:
@@ -304,6 +306,29 @@ class Qwen3Runner:
             self.tp.use_status_word(self.status)     # peers that do not answer are reported in the same word
             lib.bonsai_runner_set_comm(self._native, self.tp.handle)
         self.launches_per_step = None
+
+    def add_kv_pool(self, kv: PagedKvCache) -> None:
+        """Registers a page pool in another format (same page size): sequences whose slot format is ``kv.kvt`` append to and
+        attend over it.  The default pool keeps serving every other slot."""
+        assert kv.page_size == self.kv.page_size and kv.kvt not in self.kv_pools
+        lib = K.lib()
+        for l in range(self.cfg.layers):
+            ks = kv.k_scale[l].data_ptr() if kv.k_scale is not None else None
+            vs = kv.v_scale[l].data_ptr() if kv.v_scale is not None else None
+            K.check(lib.bonsai_runner_set_pool(self._native, kv.kvt, l, kv.k[l].data_ptr(), kv.v[l].data_ptr(), ks, vs), "runner_set_pool")
+        self.kv_pools[kv.kvt] = kv
+
+    def set_slot_format(self, slot: int, kvt: int) -> None:
+        """Page format of the sequence that occupies ``slot`` from now on (its pool must have been registered)."""
+        if kvt not in self.kv_pools:
+            raise ValueError(f"no KV pool in page format {kvt}")
+        if self.slot_formats[slot] != kvt:
+            self.slot_formats[slot] = kvt
+            self._push_slot_formats()
+
+    def _push_slot_formats(self) -> None:
+        arr = (C.c_int * len(self.slot_formats))(*self.slot_formats)
+        K.check(K.lib().bonsai_runner_set_slot_formats(self._native, arr, len(self.slot_formats)), "runner_set_slot_formats")
 
     def check_status(self, value: int | None = None) -> None:
         """Raises when a kernel of an earlier step recorded an expired wait (``value``: the status word as already read by
@@ -407,7 +432,8 @@ class Qwen3Runner:
 
     def step(self, batch: int, sample: bool = True) -> None:
         """One decode step for the first ``batch`` slots, replayed from a CUDA graph after the first call."""
-        key = (batch, int(sample))
+        # the page formats of the live slots are baked into the launches of a captured step
+        key = (batch, int(sample), tuple(self.slot_formats[:batch]) if len(self.kv_pools) > 1 else ())
         g = self._graphs.get(key)
         if g is None:
             if batch >= 2 and self.fast:

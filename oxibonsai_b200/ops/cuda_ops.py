@@ -34,6 +34,8 @@ _SIG = {
     "bonsai_runner_destroy": [_vp],
     "bonsai_runner_set_comm": [_vp, _vp],
     "bonsai_runner_set_nsplit": [_vp, _i],
+    "bonsai_runner_set_pool": [_vp, _i, _i, _vp, _vp, _vp, _vp],
+    "bonsai_runner_set_slot_formats": [_vp, _vp, _i],
     "bonsai_runner_set_fast": [_vp, _i],
     "bonsai_runner_layer_ptr_count": [],
     "bonsai_runner_step_ptr_count": [],

@@ -76,6 +76,7 @@ class InferenceEngine:
         self._pos_host = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
         self._out_host = torch.zeros(self.max_batch + 1, dtype=torch.int32).pin_memory()   # [status word, tokens...]
         self._slot_pages: dict[int, list[int]] = {}
+        self._slot_fmt: dict[int, int] = {}       # page format of a bound slot when it is not the default one
         self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
         self.prefix_cache = None       # see enable_prefix_cache()
         self.last_stats = GenerationStats()
@@ -100,19 +101,48 @@ class InferenceEngine:
         self._release_slot(0)
 
     # ---- slot / page management -----------------------------------------------------------------
+    def _pool_of(self, slot: int) -> PagedKvCache:
+        return self.runner.kv_pools[self._slot_fmt.get(slot, self.kvt)]
+
     def _bind_slot(self, slot: int, n_tokens: int) -> None:
         if n_tokens > self.max_seq_len:
             raise ValueError(f"sequence of {n_tokens} tokens exceeds max_seq_len {self.max_seq_len}")
         need = (n_tokens + self.kv.page_size - 1) // self.kv.page_size
         have = self._slot_pages.setdefault(slot, [])
         if need > len(have):
-            have.extend(self.kv.alloc(need - len(have)))
+            have.extend(self._pool_of(slot).alloc(need - len(have)))
             row = torch.tensor(have, dtype=torch.int32)
             self.runner.block_table[slot, : len(have)].copy_(row.to(self.device))
 
     def _release_slot(self, slot: int) -> None:
         pages = self._slot_pages.pop(slot, [])
-        self.kv.release(pages)
+        self._pool_of(slot).release(pages)
+        if self._slot_fmt.pop(slot, None) is not None:
+            self.runner.set_slot_format(slot, self.kvt)
+
+    # ---- KV page formats ---------------------------------------------------------------------------
+    def enable_kv_formats(self, formats: Sequence[str] = ("q8", "q4"), pages: int | None = None) -> list[str]:
+        """Adds page pools in further formats (``f16`` / ``q8`` / ``q4``; each ``pages`` pages, default: as many as the
+        default pool) so that new sequences can be admitted in a denser format while running ones keep theirs - what a
+        :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy` level change then means.  Returns the formats now
+        available.  Not offered in the exact-f32 mode or under tensor parallelism of the prefix cache's shared pages."""
+        for name in formats:
+            kvt = KV_NAMES[name.lower()]
+            if kvt in self.runner.kv_pools:
+                continue
+            pool = PagedKvCache(self.config, self.weights.kv_heads_local, pages or self.kv.num_pages, self.kv.page_size, kvt, self.device)
+            self.runner.add_kv_pool(pool)
+        return self.kv_formats()
+
+    def kv_formats(self) -> list[str]:
+        names = {K.KV_F32: "f32", K.KV_F16: "f16", K.KV_Q8: "q8", K.KV_Q4: "q4"}
+        return [names[k] for k in sorted(self.runner.kv_pools)]
+
+    def kv_utilization(self) -> float:
+        """Bytes of KV pages in use over bytes of all pools (the pressure a KV-cache policy observes)."""
+        pools = self.runner.kv_pools.values()
+        used = sum(p.utilization * p.nbytes for p in pools)
+        return used / max(1, sum(p.nbytes for p in pools))
 
     def _set_sampling(self, slot: int, p: SamplingParams) -> None:
         r = self.runner
@@ -300,15 +330,23 @@ class InferenceEngine:
                  out=r.tokens[slot: slot + 1])
         return self._read_tokens(1, slot)[0]
 
-    def begin_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None) -> int:
+    def begin_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None,
+                       kv_format: str | None = None) -> int:
         """First half of :meth:`open_sequence` for callers that prefill in pieces (the scheduler interleaves prompt chunks
         with decode steps): binds pages for ``max_total`` tokens, attaches cached prefix pages and returns how many prompt
         tokens those pages already cover.  Continue with :meth:`prefill` over ``prompt[covered:]`` in as many pieces as
         wanted (``pos0`` = index of the piece's first token), then :meth:`finish_sequence`."""
         self._set_sampling(slot, params or self.sampling)
         prompt = [int(t) for t in prompt]
+        kvt = self.kvt if kv_format is None else KV_NAMES[kv_format.lower()]
+        if kvt not in self.runner.kv_pools:
+            kvt = self.kvt                          # no pool in that format: the default one
+        self._release_slot(slot)
+        if kvt != self.kvt:
+            self._slot_fmt[slot] = kvt
+            self.runner.set_slot_format(slot, kvt)
         shared: list[int] = []
-        pc = self.prefix_cache
+        pc = self.prefix_cache if kvt == self.kvt else None      # cached pages live in the default pool
         if pc is not None and len(prompt) > 1:
             shared = pc.lookup(prompt, max_tokens=len(prompt) - 1)
             if shared:
@@ -328,7 +366,7 @@ class InferenceEngine:
     def finish_sequence(self, prompt: Sequence[int], slot: int = 0) -> int:
         """Second half of :meth:`open_sequence`: the whole prompt has been prefilled into ``slot``; registers its pages with
         the prefix cache and returns the first sampled token."""
-        if self.prefix_cache is not None:
+        if self.prefix_cache is not None and slot not in self._slot_fmt:
             self.prefix_cache.insert([int(t) for t in prompt], self._slot_pages[slot])
         r = self.runner
         K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
@@ -368,6 +406,13 @@ class InferenceEngine:
         for t in (r.block_table, r.tokens, r.positions, r.temps, r.topks, r.topps, r.rng):
             t[dst].copy_(t[src], non_blocking=True)
         self._slot_pages[dst] = self._slot_pages.pop(src, [])
+        fmt = self._slot_fmt.pop(src, None)
+        if fmt is not None:
+            self._slot_fmt[dst] = fmt
+            r.set_slot_format(src, self.kvt)
+        elif dst in self._slot_fmt:
+            del self._slot_fmt[dst]
+        r.set_slot_format(dst, fmt if fmt is not None else self.kvt)
 
     def close_sequence(self, slot: int = 0) -> None:
         self._release_slot(slot)

@@ -57,6 +57,7 @@ class Request:
     token_times: list[float] = field(default_factory=list)
     done: threading.Event = field(default_factory=threading.Event)
     cancelled: bool = False
+    kv_format: str | None = None           # page format the sequence was admitted in (set when a KV policy is active)
 
     def wait(self, timeout: float | None = None) -> list[int]:
         if not self.done.wait(timeout):
@@ -104,7 +105,11 @@ class BatchScheduler:
     """Owns an ``InferenceEngine`` (max_batch > 1) and serves requests with continuous batching."""
 
     def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
-                 prefill_chunk_tokens: int = 512):
+                 prefill_chunk_tokens: int = 512, kv_policy=None):
+        """``kv_policy``: a :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy`; when given, the scheduler feeds it the
+        engine's KV utilisation after every admission and retirement, and every newly admitted sequence gets its pages in the
+        format of the policy's current level (FP16 / Q8 / Q4, as far as the engine has pools for them)."""
+        self.kv_policy = kv_policy
         from ..core.oracle import EOS_TOKEN
         self.engine = engine
         self.prefill_chunk_tokens = max(16, int(prefill_chunk_tokens))
@@ -191,7 +196,12 @@ class BatchScheduler:
             slot = len(self.live)
             total = min(eng.max_seq_len, len(r.prompt) + r.max_tokens)
             try:
-                covered = eng.begin_sequence(r.prompt, total, slot, r.params)
+                if self.kv_policy is not None:
+                    r.kv_format = self.kv_policy.page_format()
+                    covered = eng.begin_sequence(r.prompt, total, slot, r.params, r.kv_format)
+                    self.kv_policy.observe(eng.kv_utilization())
+                else:
+                    covered = eng.begin_sequence(r.prompt, total, slot, r.params)
             except MemoryError:
                 # KV pool exhausted: put the request back and wait for a sequence to finish
                 eng.close_sequence(slot)
@@ -272,6 +282,8 @@ class BatchScheduler:
         r.done.set()
         last = len(self.live) - 1
         eng.close_sequence(slot)
+        if self.kv_policy is not None:
+            self.kv_policy.observe(eng.kv_utilization())
         if slot != last:
             eng.move_slot(last, slot)
             self.live[slot] = self.live[last]

@@ -12,7 +12,8 @@ from __future__ import annotations
 
 from typing import Any, Callable
 
-MIRRORED = ("begin_sequence", "prefill", "finish_sequence", "step_batch", "move_slot", "close_sequence", "enable_prefix_cache")
+MIRRORED = ("begin_sequence", "prefill", "finish_sequence", "step_batch", "move_slot", "close_sequence", "enable_prefix_cache",
+            "enable_kv_formats")
 SHUTDOWN = "__shutdown__"
 
 

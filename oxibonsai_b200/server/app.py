@@ -57,7 +57,8 @@ class SchedulerBackend:
         return self.s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id)
 
     def kv_utilization(self) -> float:
-        return self.s.engine.kv.utilization
+        e = self.s.engine
+        return e.kv_utilization() if hasattr(e, "kv_utilization") else e.kv.utilization
 
 
 class ReplicaBackend:
@@ -80,7 +81,7 @@ class ReplicaBackend:
         return req
 
     def kv_utilization(self) -> float:
-        return max(s.engine.kv.utilization for s in self.schedulers.values())
+        return max(s.engine.kv_utilization() for s in self.schedulers.values())
 
     def replica_loads(self) -> dict:
         return {k: {"live": s.active, "queued": len(s.queue)} for k, s in self.schedulers.items()}
@@ -148,7 +149,8 @@ def _hash_embed(text: str, dim: int = 512) -> list[float]:
     return [x / n for x in v]
 
 
-def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, metrics: InferenceMetrics | None = None):
+def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, metrics: InferenceMetrics | None = None,
+               kv_policy: KvCachePolicy | None = None):
     cfg = config or ServerConfig()
     metrics = metrics or InferenceMetrics()
     breaker = CircuitBreaker()
@@ -157,7 +159,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
     app.state.metrics, app.state.backend, app.state.config, app.state.breaker = metrics, backend, cfg, breaker
     # KV-pressure controller (FP16 -> Q8 -> Q4 with hysteresis): fed with the page utilisation after every request; its
     # level is exported as a gauge and as the page format recommended for newly admitted sequences
-    kv_policy = app.state.kv_policy = KvCachePolicy()
+    kv_policy = app.state.kv_policy = kv_policy or KvCachePolicy()
     cors = app.state.cors = CorsConfig()
     http_log = RequestLogger()
     started = time.time()

@@ -40,6 +40,7 @@ class ServerConfig:
     tensor_parallel: int = 1          # > 1: launch with torchrun, one process per GPU; rank 0 serves HTTP, the others follow its commands
     replicas: int = 1                 # > 1: one engine + scheduler per GPU (cuda:0 .. cuda:N-1) in this process, requests routed between them
     prefill_chunk_tokens: int = 512   # prompt tokens prefilled between two decode steps of the running streams
+    kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
 
     def validate(self, check_paths: bool = True) -> "ServerConfig":
@@ -60,6 +61,8 @@ class ServerConfig:
             errs.append("tensor_parallel and replicas must be positive")
         if self.tensor_parallel > 1 and self.replicas > 1:
             errs.append("tensor_parallel and replicas cannot be combined in one server")
+        if self.kv_policy not in ("off", "adaptive", "aggressive"):
+            errs.append("kv_policy must be one of off, adaptive, aggressive")
         if self.kv_cache.lower() not in ("f32", "f16", "q8", "q4"):
             errs.append("kv_cache must be one of f32, f16, q8, q4")
         if check_paths:
@@ -78,7 +81,7 @@ _TOML_MAP = {
     ("sampling", "temperature"): "temperature", ("sampling", "top_k"): "top_k", ("sampling", "top_p"): "top_p",
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
-    ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas",
+    ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "kv_policy"): "kv_policy",
     ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",

@@ -117,3 +117,39 @@ def test_prefix_cache_reuses_pages_and_keeps_the_token_stream(tiny_gguf):
     assert len(eng.kv.free_pages) == free0 - pc.size
     pc.clear()
     assert len(eng.kv.free_pages) == free0 and all(c == 0 for c in eng.kv.refcount)
+
+
+def test_sequences_in_different_kv_page_formats_share_a_decode_batch(tiny_gguf):
+    """A KV-policy level change alters the storage of the sequences admitted after it: one engine, three page pools, three
+    live sequences in f16 / int8 / int4 pages decoded together.  Each stream equals what a single-format engine produces for
+    that prompt (same kernels, same format), and the pages come out of the pool of the sequence's format."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    from oxibonsai_b200.runtime import EngineBuilder
+    from oxibonsai_b200.runtime.kv_policy import KvCachePolicy, KvPolicyConfig
+    from oxibonsai_b200.runtime.scheduler import BatchScheduler
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 33, 51)]
+    want = {}
+    for fmt, p in zip(("f16", "q8", "q4"), prompts):
+        e = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(128).max_batch(1).kv_cache(fmt).build()
+        want[fmt] = e.generate(p, 12, stop_at_eos=False)
+        del e
+    eng = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(128).max_batch(4).kv_cache("f16").build()
+    assert eng.enable_kv_formats(("q8", "q4")) == ["f16", "q8", "q4"]
+    free0 = {k: len(p.free_pages) for k, p in eng.runner.kv_pools.items()}
+
+    class Scripted(KvCachePolicy):
+        """Hands out the formats in a fixed order, whatever the pressure."""
+        order = ["f16", "q8", "q4"]
+
+        def page_format(self):
+            return self.order[min(self.observations, 2)]
+
+    sched = BatchScheduler(eng, eos_token=-1, kv_policy=Scripted(KvPolicyConfig())).start()
+    reqs = [sched.submit(p, eng.sampling, 12) for p in prompts]
+    outs = [r.wait(60) for r in reqs]
+    sched.stop()
+    assert [r.kv_format for r in reqs] == ["f16", "q8", "q4"]
+    assert outs == [want["f16"], want["q8"], want["q4"]]
+    assert {k: len(p.free_pages) for k, p in eng.runner.kv_pools.items()} == free0      # every pool got its pages back
+    assert eng.runner.slot_formats == [K.KV_F16] * 4

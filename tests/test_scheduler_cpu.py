@@ -137,3 +137,39 @@ def test_cancel_while_prefilling_frees_the_slot():
     assert a.done.wait(10)
     sched.stop()
     assert not eng.slots
+
+
+def test_policy_level_sets_the_page_format_of_the_next_sequence():
+    """The scheduler asks the KV policy for a format at every admission and feeds it the engine's utilisation: once the
+    pressure crosses the policy's thresholds, sequences admitted from then on get Q8 and then Q4 pages."""
+    from oxibonsai_b200.runtime.kv_policy import KvCachePolicy, KvPolicyConfig
+
+    class Eng(FakeEngine):
+        util = 0.1
+        formats = []
+
+        def begin_sequence(self, prompt, max_total, slot, params, kv_format=None):
+            self.formats.append(kv_format)
+            return super().begin_sequence(prompt, max_total, slot, params)
+
+        def kv_utilization(self):
+            return self.util
+
+    eng = Eng()
+    pol = KvCachePolicy(KvPolicyConfig(alpha=1.0))
+    sched = BatchScheduler(eng, eos_token=-1, kv_policy=pol).start()
+    a = sched.submit([1] * 20, SamplingParams(), 2)
+    a.wait(10)
+    eng.util = 0.85                                   # moderate pressure is observed when the next one is admitted ...
+    b = sched.submit([2] * 20, SamplingParams(), 2)
+    b.wait(10)
+    c = sched.submit([3] * 20, SamplingParams(), 2)   # ... so this one is the first to get the denser format
+    c.wait(10)
+    eng.util = 0.97
+    d = sched.submit([4] * 20, SamplingParams(), 2)
+    d.wait(10)
+    e = sched.submit([5] * 20, SamplingParams(), 2)
+    e.wait(10)
+    sched.stop()
+    assert eng.formats == ["f16", "f16", "q8", "q8", "q4"] and [r.kv_format for r in (a, c, e)] == ["f16", "q8", "q4"]
+    assert pol.upgrades == 2
