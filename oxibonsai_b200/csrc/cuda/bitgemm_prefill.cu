@@ -58,7 +58,7 @@ struct PfParams {
   const __half* scales;
   float* out_f32;          // [T][out_ld]  (epi 0, 1)
   const float* residual;   // [T][out_ld]  (epi 1)
-  __half* out_f16;         // [T][out_ld]  (epi 2: SwiGLU, paired-K order; epi 3: plain f16 store; epi 4: SwiGLU, hmma-K order)
+  __half* out_f16;         // [T][out_ld]  (epi 2: SwiGLU, paired-K order; epi 3: plain f16 store)
   int* status;
   int n_rows, K, T, epi, out_ld;
   int dense;               // 1: A is a dense f16 matrix fetched by TMA (natural K order), no expansion
@@ -123,10 +123,10 @@ __device__ __forceinline__ float pf_residual(const PfParams& p, int tok, int row
 
 // epilogue for one accumulator value; every lane of the warp calls it (epi 2 exchanges gate / up between lanes)
 __device__ __forceinline__ void pf_store(const PfParams& p, float v, float res, int tok, int row, int a, bool row_ok) {
-  if (p.epi == 2 || p.epi == 4) {
+  if (p.epi == 2) {
     float other = __shfl_xor_sync(0xffffffffu, v, 1);
     if (row_ok && tok < p.T && (a & 1) == 0)
-      p.out_f16[(size_t)tok * p.out_ld + (p.epi == 2 ? paired_k(row >> 1) : hmma_k_pos(row >> 1))] = __float2half_rn(v / (1.0f + __expf(-v)) * other);
+      p.out_f16[(size_t)tok * p.out_ld + paired_k(row >> 1)] = __float2half_rn(v / (1.0f + __expf(-v)) * other);
   } else if (row_ok && tok < p.T) {
     const size_t o = (size_t)tok * p.out_ld + row;
     if (p.epi == 0) p.out_f32[o] = v;
@@ -572,8 +572,7 @@ size_t bonsai_bitgemm_prefill_ws_bytes() {
 // x_f16: activations [T][K] f16 (row stride x_ld elements, 16-byte aligned rows), in paired-K order for packed
 // weights and natural order for dense ones.
 // epi 0: out_f32 = W x; 1: out_f32 = residual + W x; 2: out_f16 = SwiGLU over interleaved gate/up rows
-// (paired-K order, out_ld = N/2 or more); 3: out_f16 = W x in natural order; 4: as 2 but in the K order of the mma.sync
-// decode-batch GEMM (hmma-K), for a following bonsai_bitgemm_hmma.
+// (paired-K order, out_ld = N/2 or more); 3: out_f16 = W x in natural order.
 // dense_w != null: W is a dense f16 row-major [n_rows][K] matrix (codes / scales ignored), e.g. the LM head.
 // ws / ws_bytes: optional workspace (zero-filled once by the caller, left zeroed by every launch; one launch at a
 // time may use it) for the balanced work distribution; null = whole tiles per CTA.  balance: 0 = whole tiles, 1 = balanced
@@ -582,7 +581,7 @@ int bonsai_bitgemm_prefill_ws(const void* codes, const void* scales, const void*
                               const float* residual, void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld,
                               int sms, const void* dense_w, void* ws, size_t ws_bytes, int balance, cudaStream_t stream) {
   using namespace bonsai;
-  if (K % 128 != 0 || n_rows < 1 || T < 1 || epi < 0 || epi > 4 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
+  if (K % 128 != 0 || n_rows < 1 || T < 1 || epi < 0 || epi > 3 || x_ld % 8 != 0) return BONSAI_CUDA_BAD_ARG;
   if ((epi <= 1 && out_f32 == nullptr) || (epi == 1 && residual == nullptr) || (epi >= 2 && out_f16 == nullptr)) return BONSAI_CUDA_BAD_ARG;
   const int tok = T <= 64 ? 64 : 256;
   CUtensorMap xmap, amap;

@@ -227,7 +227,7 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   if (flags & 1) {
     RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),
                      P<unsigned long long>(sp[SP_RNG]), P<int>(sp[SP_OUT_TOKENS]), positions, 1,
-                     P<uint32_t>(sp[SP_ALLOW_MASK]), mask_words, st));
+                     mask_words > 0 ? P<uint32_t>(sp[SP_ALLOW_MASK]) : nullptr, mask_words, st));
   }
   return 0;
 }
@@ -356,7 +356,7 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
 // tcgen05 GEMM.  The reference's continuous batching re-runs a full single-sequence generate per
 // request per step (crates/oxibonsai-runtime/src/continuous_batch.rs:283-293).
 //
-// Tensor parallel: up to 64 sequences, the row-parallel O and down GEMMs run on the mma.sync kernel and their epilogue
+// Tensor parallel: up to 16 sequences, the row-parallel O and down GEMMs run on the mma.sync kernel and their epilogue
 // is the all-reduce + residual add ({value, tag} stores into the peers' memory, summed in rank order).  Larger batches
 // write partial sums into alternating halves of the symmetric big area and one kernel per all-reduce (entry flag
 // barrier + peer loads + residual add) folds them into h; every step issues an even number of those, so the
@@ -392,11 +392,11 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   // 40.2 / 33.3 against 21.8 / 25.0 / 38.4 / 30.7, 64 tokens 39.6 / 20.6 / 66.0 / 51.7 against 26.3 / 26.1 / 43.4 / 39.0:
   // everything up to 32 sequences, and the O projection (few rows, short K) up to 64.
   const bool hm_ok = r.ic[IC_FAST] != 5 && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
-  // Tensor parallel: every GEMM of a decode batch (<= 64 sequences) runs on the mma.sync kernel - the K and row ranges of
-  // a rank are short - and the two row-parallel ones carry the all-reduce + residual add in their epilogue.
-  // Between 33 and 64 sequences the column-parallel GEMMs stay on tcgen05 and the gate/up epilogue writes the K order the
-  // mma.sync down projection reads.
-  const bool tp_fused = tp && hm_ok && batch <= 64;
+  // Tensor parallel, up to 16 sequences: the two row-parallel GEMMs carry the all-reduce + residual add in their epilogue
+  // ({value, tag} messages).  That doubles the bytes on the wire, which is right while the exchange is latency-bound;
+  // measured at 64 sequences (2 MB per peer per exchange) it lost to partial sums + the one-shot all-reduce kernel
+  // (TP = 2: 7.3 against 6.2 ms per step), so larger batches keep that path.
+  const bool tp_fused = tp && hm_ok && batch <= 16;
   const bool hm_all = hm_ok && batch <= 32, hm_o = hm_ok && batch <= 64;
   auto to_f16 = [&](bool hm, const float* src, int src_ld, const float* w, int K, void* dst, int dst_ld) {
     return hm ? bonsai_norm_to_f16_hmma(src, src_ld, w, r.eps, batch, K, dst, dst_ld, st)
@@ -428,8 +428,7 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
       RC(bonsai_tp_allreduce_oneshot_add(r.comm, h, (size_t)batch * hidden, 0, st));
     }
     RC(to_f16(hm_all, h, hidden, P<float>(lp[LP_FFN_NORM]), hidden, xn, xn_ld));
-    RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden,
-            tp_fused && !hm_all ? 4 : 2, inter));
+    RC(gemm(hm_all, P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
     if (!tp) {
       RC(gemm(hm_all, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
     } else if (tp_fused) {
@@ -460,7 +459,7 @@ static int decode_step_batched(Runner& r, const uint64_t* sp, const uint64_t* pp
   if (flags & 1) {
     RC(bonsai_sample(logits, batch, vocab, vocab, P<float>(sp[SP_TEMPS]), P<int>(sp[SP_TOPKS]), P<float>(sp[SP_TOPPS]),
                      P<unsigned long long>(sp[SP_RNG]), P<int>(sp[SP_OUT_TOKENS]), positions, 1,
-                     P<uint32_t>(sp[SP_ALLOW_MASK]), mask_words, st));
+                     mask_words > 0 ? P<uint32_t>(sp[SP_ALLOW_MASK]) : nullptr, mask_words, st));
   }
   return 0;
 }

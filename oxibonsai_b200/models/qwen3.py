@@ -268,6 +268,9 @@ class Qwen3Runner:
         self.topps = torch.ones(B, **f32)
         self.rng = torch.full((B,), 42, dtype=torch.int64, device=dev)
         self.out_tokens = torch.zeros(B, **i32)
+        # per-slot vocabulary masks of constrained decoding (bit set = token allowed), read by the sampler of a masked step
+        self.mask_words = (cfg.vocab + 31) // 32
+        self.allow_mask = torch.full((B, self.mask_words), -1, **i32)
         self.attn_counters = torch.zeros(B * max(1, nkv), **i32)
         cos, sin = rope_table(hd, max_seq, cfg.rope_base)
         self.rope_cos = torch.from_numpy(cos).to(dev)
@@ -299,7 +302,7 @@ class Qwen3Runner:
                 lp[l * nlp + i] = v
         self._native = lib.bonsai_runner_create(icfg, cfg.eps, gp, lp)
         sp = [self.tokens, self.positions, self.block_table, self.h, self.qkv, self.q, self.attn, self.act, self.logits, self.ws_acc,
-              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, None, self.attn_counters, self.status]
+              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, self.allow_mask, self.attn_counters, self.status]
         assert len(sp) == nsp
         self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
         if self.tp is not None:
@@ -420,20 +423,21 @@ class Qwen3Runner:
         per_layer = 4 * batch + (1 if fused else 2)
         return batch + per_layer * self.cfg.layers + batch + (1 if sample else 0) + (2 if self.w.tp_size > 1 else 0)
 
-    def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True) -> None:
+    def step_eager(self, batch: int, sample: bool = True, lm_head: bool = True, masked: bool = False) -> None:
         flags = (1 if sample else 0) | (0 if lm_head else 2)
+        mw = self.mask_words if masked else 0      # masked: the sampler only picks tokens whose bit is set in ``allow_mask[slot]``
         if batch >= 2 and self.fast:
             # all sequences share one tcgen05 GEMM per linear layer
             b = self._prefill_buffers(max(64, batch))
-            K.check(K._pf().bonsai_runner_decode_step_batched(self._native, self._step_ptrs, b["ptrs"], batch, flags, 0, K.stream()),
+            K.check(K._pf().bonsai_runner_decode_step_batched(self._native, self._step_ptrs, b["ptrs"], batch, flags, mw, K.stream()),
                     "decode_step_batched")
             return
-        K.check(K.lib().bonsai_runner_decode_step(self._native, self._step_ptrs, batch, flags, 0, K.stream()), "decode_step")
+        K.check(K.lib().bonsai_runner_decode_step(self._native, self._step_ptrs, batch, flags, mw, K.stream()), "decode_step")
 
-    def step(self, batch: int, sample: bool = True) -> None:
+    def step(self, batch: int, sample: bool = True, masked: bool = False) -> None:
         """One decode step for the first ``batch`` slots, replayed from a CUDA graph after the first call."""
         # the page formats of the live slots are baked into the launches of a captured step
-        key = (batch, int(sample), tuple(self.slot_formats[:batch]) if len(self.kv_pools) > 1 else ())
+        key = (batch, int(sample), tuple(self.slot_formats[:batch]) if len(self.kv_pools) > 1 else (), masked)
         g = self._graphs.get(key)
         if g is None:
             if batch >= 2 and self.fast:
@@ -444,7 +448,7 @@ class Qwen3Runner:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.stream(s):
                 with torch.cuda.graph(g, stream=s):
-                    self.step_eager(batch, sample)
+                    self.step_eager(batch, sample, masked=masked)
             torch.cuda.current_stream(self.device).wait_stream(s)
             self._graphs[key] = g
         g.replay()

@@ -77,6 +77,7 @@ class InferenceEngine:
         self._out_host = torch.zeros(self.max_batch + 1, dtype=torch.int32).pin_memory()   # [status word, tokens...]
         self._slot_pages: dict[int, list[int]] = {}
         self._slot_fmt: dict[int, int] = {}       # page format of a bound slot when it is not the default one
+        self._masked: set[int] = set()            # slots whose vocabulary mask is not "every token"
         self.prefill_min_tokens = 16   # the reference also switches to batch prefill above 16 tokens
         self.prefix_cache = None       # see enable_prefix_cache()
         self.last_stats = GenerationStats()
@@ -117,6 +118,8 @@ class InferenceEngine:
     def _release_slot(self, slot: int) -> None:
         pages = self._slot_pages.pop(slot, [])
         self._pool_of(slot).release(pages)
+        if slot in self._masked:
+            self.set_mask(slot, None)
         if self._slot_fmt.pop(slot, None) is not None:
             self.runner.set_slot_format(slot, self.kvt)
 
@@ -231,8 +234,38 @@ class InferenceEngine:
             r.positions[slot: slot + 1].copy_(pos[i: i + 1], non_blocking=True)
             r.step_eager(1, sample=False, lm_head=(i == n - 1))
 
+    # ---- constrained decoding and log-probabilities -------------------------------------------------
+    def set_mask(self, slot: int, mask) -> None:
+        """Vocabulary mask of ``slot`` for the masked steps that follow: a packed uint32 array (bit set = token allowed, as
+        ``TokenConstraint.allowed_mask`` returns it), or ``None`` for "every token"."""
+        r = self.runner
+        if mask is None:
+            if slot in self._masked:
+                r.allow_mask[slot].fill_(-1)
+                self._masked.discard(slot)
+            return
+        self._masked.add(slot)
+        import numpy as np
+        m = np.zeros(r.mask_words, dtype=np.uint32)
+        src = np.asarray(mask, dtype=np.uint32)[: r.mask_words]
+        m[: src.size] = src
+        r.allow_mask[slot].copy_(torch.from_numpy(m.view(np.int32)).pin_memory(), non_blocking=True)
+
+    def token_logprobs(self, slot: int, token: int, top_n: int = 0) -> tuple[float, list[tuple[int, float]]]:
+        """Log-probability of ``token`` under the logits that the last step (or prefill) left for ``slot``, and the ``top_n``
+        most likely tokens with theirs (natural log, temperature 1)."""
+        lp = torch.log_softmax(self.runner.logits[slot, : self.config.vocab].float(), dim=-1)
+        top = []
+        if top_n > 0:
+            v, i = torch.topk(lp, min(top_n, lp.numel()))
+            top = list(zip(i.tolist(), v.tolist()))
+        return float(lp[int(token)]), top
+
     def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
-                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None) -> Iterator[int]:
+                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None, constraint=None) -> Iterator[int]:
+        """``constraint``: a :class:`~oxibonsai_b200.runtime.constrained.TokenConstraint`; its vocabulary mask goes to the
+        device before every step and the sampler kernel only picks allowed tokens; generation ends when the constraint is
+        complete (reference: ``ConstrainedSampler``, crates/oxibonsai-runtime/src/constrained_decoding/sampler.rs:19-94)."""
         p = (params or self.sampling).validate()
         max_new = p.max_tokens if max_tokens is None else max_tokens
         prompt = [int(t) for t in prompt]
@@ -246,8 +279,13 @@ class InferenceEngine:
         try:
             t0 = time.perf_counter()
             self._start_sequence(0, prompt, total)
+            masked = constraint is not None
+            if masked:
+                constraint.reset()
+                self.set_mask(0, constraint.allowed_mask())
             # first token: sample from the prefill logits on the device
-            K.sample(r.logits[:1], r.temps[:1], r.topks[:1], r.topps[:1], r.rng[:1], out=r.tokens[:1])
+            K.sample(r.logits[:1], r.temps[:1], r.topks[:1], r.topps[:1], r.rng[:1], out=r.tokens[:1],
+                     allow_mask=r.allow_mask[:1] if masked else None)
             tok = self._read_tokens(1)[0]
             stats.prefill_seconds = time.perf_counter() - t0
             pos = len(prompt)
@@ -260,20 +298,27 @@ class InferenceEngine:
                 if on_token is not None:
                     on_token(tok)
                 yield tok
+                if masked:
+                    constraint.advance(tok)
+                    if constraint.is_complete():
+                        break
+                    self.set_mask(0, constraint.allowed_mask())
                 if pos >= self.max_seq_len:
                     break
                 # the reference runs a forward after every emitted token, including the last
                 self._upload(0, tok, pos)
-                r.step(1, sample=True)
+                r.step(1, sample=True, masked=masked)
                 tok = self._read_tokens(1)[0]
                 pos += 1
             stats.decode_seconds = time.perf_counter() - t_dec
         finally:
+            if constraint is not None:
+                self.set_mask(0, None)
             self._release_slot(0)
 
     def generate(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
-                 stop_at_eos: bool = True) -> list[int]:
-        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos))
+                 stop_at_eos: bool = True, constraint=None) -> list[int]:
+        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos, constraint=constraint))
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams | None = None,
                        stop_at_eos: bool = True) -> list[list[int]]:
@@ -363,25 +408,30 @@ class InferenceEngine:
             self.runner.block_table[slot, : len(row)].copy_(row.to(self.device))
         return len(shared) * self.kv.page_size
 
-    def finish_sequence(self, prompt: Sequence[int], slot: int = 0) -> int:
+    def finish_sequence(self, prompt: Sequence[int], slot: int = 0, mask=None) -> int:
         """Second half of :meth:`open_sequence`: the whole prompt has been prefilled into ``slot``; registers its pages with
-        the prefix cache and returns the first sampled token."""
+        the prefix cache and returns the first sampled token (restricted to ``mask`` when one is given)."""
         if self.prefix_cache is not None and slot not in self._slot_fmt:
             self.prefix_cache.insert([int(t) for t in prompt], self._slot_pages[slot])
         r = self.runner
+        if mask is not None:
+            self.set_mask(slot, mask)
         K.sample(r.logits[slot: slot + 1], r.temps[slot: slot + 1], r.topks[slot: slot + 1], r.topps[slot: slot + 1], r.rng[slot: slot + 1],
-                 out=r.tokens[slot: slot + 1])
+                 out=r.tokens[slot: slot + 1], allow_mask=r.allow_mask[slot: slot + 1] if mask is not None else None)
         return self._read_tokens(1, slot)[0]
 
-    def step_batch(self, positions: Sequence[int]) -> list[int]:
+    def step_batch(self, positions: Sequence[int], masks: dict | None = None) -> list[int]:
         """One decode step of the live sequences in slots 0..len(positions)-1 (slot i feeds its last sampled token at
         ``positions[i]``); returns the newly sampled token of every slot.  The positions go up from pinned memory and the
-        tokens come back with the step's status word in one copy."""
+        tokens come back with the step's status word in one copy.  ``masks``: {slot: packed vocabulary mask} for the
+        constrained sequences of the batch (the others may pick any token)."""
         B = len(positions)
         r = self.runner
         self._pos_host[:B] = torch.tensor(list(positions), dtype=torch.int32)
         r.positions[:B].copy_(self._pos_host[:B], non_blocking=True)
-        r.step(B, sample=True)
+        for slot, m in (masks or {}).items():
+            self.set_mask(slot, m)
+        r.step(B, sample=True, masked=bool(masks))
         return self._read_tokens(B)
 
     def bind_thread(self) -> None:
@@ -403,8 +453,14 @@ class InferenceEngine:
         """Moves a live sequence to another slot: block-table row, last token, position and sampler state.
         KV pages stay where they are (the block table references them)."""
         r = self.runner
-        for t in (r.block_table, r.tokens, r.positions, r.temps, r.topks, r.topps, r.rng):
+        for t in (r.block_table, r.tokens, r.positions, r.temps, r.topks, r.topps, r.rng, r.allow_mask):
             t[dst].copy_(t[src], non_blocking=True)
+        if src in self._masked:
+            self._masked.discard(src)
+            self._masked.add(dst)
+            r.allow_mask[src].fill_(-1)
+        else:
+            self._masked.discard(dst)
         self._slot_pages[dst] = self._slot_pages.pop(src, [])
         fmt = self._slot_fmt.pop(src, None)
         if fmt is not None:
@@ -474,8 +530,38 @@ class GenericFormatEngine:
         with self._lock:
             self._eng.generate([0], 1, SamplingPreset.GREEDY.params(), stop_at_eos=False)
 
+    # ---- constrained decoding and log-probabilities -------------------------------------------------
+    def set_mask(self, slot: int, mask) -> None:
+        """Vocabulary mask of ``slot`` for the masked steps that follow: a packed uint32 array (bit set = token allowed, as
+        ``TokenConstraint.allowed_mask`` returns it), or ``None`` for "every token"."""
+        r = self.runner
+        if mask is None:
+            if slot in self._masked:
+                r.allow_mask[slot].fill_(-1)
+                self._masked.discard(slot)
+            return
+        self._masked.add(slot)
+        import numpy as np
+        m = np.zeros(r.mask_words, dtype=np.uint32)
+        src = np.asarray(mask, dtype=np.uint32)[: r.mask_words]
+        m[: src.size] = src
+        r.allow_mask[slot].copy_(torch.from_numpy(m.view(np.int32)).pin_memory(), non_blocking=True)
+
+    def token_logprobs(self, slot: int, token: int, top_n: int = 0) -> tuple[float, list[tuple[int, float]]]:
+        """Log-probability of ``token`` under the logits that the last step (or prefill) left for ``slot``, and the ``top_n``
+        most likely tokens with theirs (natural log, temperature 1)."""
+        lp = torch.log_softmax(self.runner.logits[slot, : self.config.vocab].float(), dim=-1)
+        top = []
+        if top_n > 0:
+            v, i = torch.topk(lp, min(top_n, lp.numel()))
+            top = list(zip(i.tolist(), v.tolist()))
+        return float(lp[int(token)]), top
+
     def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
-                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None) -> Iterator[int]:
+                        stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None, constraint=None) -> Iterator[int]:
+        """``constraint``: a :class:`~oxibonsai_b200.runtime.constrained.TokenConstraint`; its vocabulary mask goes to the
+        device before every step and the sampler kernel only picks allowed tokens; generation ends when the constraint is
+        complete (reference: ``ConstrainedSampler``, crates/oxibonsai-runtime/src/constrained_decoding/sampler.rs:19-94)."""
         p = (params or self.sampling).validate()
         max_new = p.max_tokens if max_tokens is None else max_tokens
         prompt = [int(t) for t in prompt]

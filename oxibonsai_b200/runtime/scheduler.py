@@ -58,6 +58,9 @@ class Request:
     done: threading.Event = field(default_factory=threading.Event)
     cancelled: bool = False
     kv_format: str | None = None           # page format the sequence was admitted in (set when a KV policy is active)
+    constraint: object | None = None       # TokenConstraint: the sampler only picks tokens it allows; ends the request when complete
+    logprobs: int | None = None            # not None: record the log-probability of every token and of the top `logprobs` ones
+    token_logprobs: list = field(default_factory=list)   # [(logprob, [(token, logprob), ...]), ...] when `logprobs` is set
 
     def wait(self, timeout: float | None = None) -> list[int]:
         if not self.done.wait(timeout):
@@ -226,7 +229,11 @@ class BatchScheduler:
             p["done"] = end
             if end < n:
                 return True
-            first = eng.finish_sequence(r.prompt, slot)
+            if r.constraint is not None:
+                r.constraint.reset()
+                first = eng.finish_sequence(r.prompt, slot, r.constraint.allowed_mask())
+            else:
+                first = eng.finish_sequence(r.prompt, slot)
         except _Cancelled:
             eng.close_sequence(slot)
             r.finish_reason = "cancelled"
@@ -240,6 +247,8 @@ class BatchScheduler:
             self._pending = None
             return True
         self._pending = None
+        if r.logprobs is not None:               # from the prefill logits, which stay with the prefill slot
+            r.token_logprobs.append(eng.token_logprobs(slot, first, r.logprobs))
         dst = len(self.live)
         if slot != dst:                          # sequences retired while this one was prefilling: close the gap
             eng.move_slot(slot, dst)
@@ -262,6 +271,12 @@ class BatchScheduler:
             return True
         r.tokens.append(tok)
         r.token_times.append(now)
+        if r.logprobs is not None and len(r.token_logprobs) < len(r.tokens):   # (the first token's was taken at admission)
+            r.token_logprobs.append(self.engine.token_logprobs(slot, tok, r.logprobs))
+        if r.constraint is not None:
+            r.constraint.advance(tok)
+            if r.constraint.is_complete():
+                r.finish_reason = "stop"
         if r.t_first_token is None:
             r.t_first_token = now
         self.tokens_generated += 1
@@ -270,6 +285,8 @@ class BatchScheduler:
                 r.on_token(tok)
             except Exception:
                 r.cancelled = True
+        if r.finish_reason == "stop":
+            return True
         if len(r.tokens) >= r.max_tokens or self._pos[slot] + 1 >= self.engine.max_seq_len:
             r.finish_reason = "length"
             return True
@@ -295,7 +312,9 @@ class BatchScheduler:
         eng = self.engine
         B = len(self.live)
         # the device holds each slot's last token; positions are set from the host's view
-        toks = eng.step_batch(self._pos)      # raises when a kernel of the step recorded an expired wait
+        masks = {s: r.constraint.allowed_mask() for s, r in enumerate(self.live) if r.constraint is not None}
+        # raises when a kernel of the step recorded an expired wait
+        toks = eng.step_batch(self._pos, masks) if masks else eng.step_batch(self._pos)
         self.steps += 1
         for s in range(B):
             self._pos[s] += 1

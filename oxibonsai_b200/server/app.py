@@ -3,8 +3,9 @@
 Reference: the axum router (crates/oxibonsai-runtime/src/server.rs:203-243), ChatML prompt builder (:514-551), SSE framing
 ``role chunk -> content chunks -> finish chunk -> [DONE]`` with UTF-8-safe incremental decoding (:391-512), ``x-request-id``
 echo (:36-60), bearer auth that skips ``/health`` and ``/metrics`` (crates/oxibonsai-serve/src/main.rs:159-170,338-370),
-admin endpoints (admin.rs:45-302), embeddings (embeddings.rs), extended request fields - tools, logprobs, n <= 4,
-response_format, stop, seed (api_types.rs:13-345).  The reference serialises requests on one mutex and ignores the
+admin endpoints (admin.rs:45-302), embeddings (embeddings.rs), extended request fields - tools, logprobs / top_logprobs
+(per-token log-probabilities from the step's logits), n <= 4, response_format (json_object / json_schema: a grammar
+constraint whose vocabulary mask the GPU sampler applies at every step), stop, seed (api_types.rs:13-345).  The reference serialises requests on one mutex and ignores the
 request's temperature; here requests run concurrently through the continuous-batching scheduler and per-request
 sampling parameters are applied.
 """
@@ -53,8 +54,9 @@ class SchedulerBackend:
         self.model_name = model_name
         self.max_seq_len = scheduler.engine.max_seq_len
 
-    def submit(self, prompt, params, max_tokens, on_token, request_id):
-        return self.s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id)
+    def submit(self, prompt, params, max_tokens, on_token, request_id, **extra):
+        # extra: constraint (TokenConstraint) and logprobs (int) of the request, when it asked for them
+        return self.s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id, **extra)
 
     def kv_utilization(self) -> float:
         e = self.s.engine
@@ -74,8 +76,8 @@ class ReplicaBackend:
         self.model_name = model_name
         self.max_seq_len = schedulers[0].engine.max_seq_len
 
-    def submit(self, prompt, params, max_tokens, on_token, request_id, session_key: str | None = None):
-        nid, req = self.pool.submit(session_key or request_id, prompt, params, max_tokens, on_token=on_token, request_id=request_id)
+    def submit(self, prompt, params, max_tokens, on_token, request_id, session_key: str | None = None, **extra):
+        nid, req = self.pool.submit(session_key or request_id, prompt, params, max_tokens, on_token=on_token, request_id=request_id, **extra)
         req.replica = nid
         threading.Thread(target=lambda: (req.done.wait(), self.pool.finished(nid)), name=f"replica-done-{request_id[:8]}", daemon=True).start()
         return req
@@ -213,8 +215,46 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         cut = min((text.find(s) for s in stops if s and s in text), default=-1)
         return (text[:cut], True) if cut >= 0 else (text, False)
 
-    async def run_generation(prompt_ids: list[int], params: SamplingParams, max_tokens: int, rid: str, stops: list[str]):
-        """Async generator of (text_delta, finish_reason | None)."""
+    _table: list = []
+
+    def token_table():
+        """Byte strings of the vocabulary for the constraint engines (built once, on the first constrained request)."""
+        if not _table:
+            from ..runtime.constrained import TokenTable
+            _table.append(TokenTable.from_tokenizer(tokenizer))
+        return _table[0]
+
+    def constraint_from(body: dict):
+        """``response_format`` of the request as a token constraint: ``{"type": "json_object"}`` -> any JSON value,
+        ``{"type": "json_schema", "json_schema": {"schema": {...}}}`` -> JSON of that shape; None for plain text."""
+        rf = body.get("response_format")
+        if not isinstance(rf, dict) or rf.get("type") in (None, "text"):
+            return None
+        from ..runtime.constrained import json_constraint, json_schema_constraint
+        eos = getattr(tokenizer, "eos_token_id", None)
+        if rf["type"] == "json_object":
+            return json_constraint(token_table(), eos)
+        if rf["type"] == "json_schema":
+            spec = rf.get("json_schema") or {}
+            schema = spec.get("schema", spec)
+            return json_schema_constraint(token_table(), schema, eos)
+        raise ValueError(f"unsupported response_format type {rf['type']!r}")
+
+    def logprobs_from(body: dict, chat: bool):
+        """Number of alternatives to report per token, or None: chat uses ``logprobs: true`` + ``top_logprobs: n``,
+        completions ``logprobs: n``."""
+        lp = body.get("logprobs")
+        if lp is None or lp is False:
+            return None
+        n = int(body.get("top_logprobs") or 0) if chat else (0 if lp is True else int(lp))
+        if not 0 <= n <= 20:
+            raise ValueError("'top_logprobs' must be between 0 and 20")
+        return n
+
+    async def run_generation(prompt_ids: list[int], params: SamplingParams, max_tokens: int, rid: str, stops: list[str],
+                             extra: dict | None = None, sink: dict | None = None):
+        """Async generator of (text_delta, finish_reason | None).  ``extra``: constraint / logprobs of the request, handed to
+        the backend; ``sink``: receives the backend's request object under "req" (for the recorded log-probabilities)."""
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
         tracker = RequestRateTracker()
@@ -230,7 +270,9 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         completed = False
         t0 = time.perf_counter()
         try:
-            req = backend.submit(prompt_ids, params, max_tokens, on_token, rid)
+            req = backend.submit(prompt_ids, params, max_tokens, on_token, rid, **(extra or {}))
+            if sink is not None:
+                sink["req"] = req
         except Exception:
             breaker.record_failure()
             raise
@@ -377,6 +419,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                 raise ValueError("'n' must be between 1 and 4")
             stops = body.get("stop") or []
             stops = [stops] if isinstance(stops, str) else list(stops)
+            top_lp = logprobs_from(body, chat)
+            constraint_from(body)          # validated here (a 400 for a bad schema); built again per choice below: it is stateful
         except (ValueError, TypeError) as e:
             metrics.errors.inc()
             return error(400, str(e), rid=rid)
@@ -384,6 +428,25 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         created = int(time.time())
         obj_id = ("chatcmpl-" if chat else "cmpl-") + rid[:24]
         model = body.get("model") or backend.model_name
+
+        def extras() -> dict:
+            ex: dict[str, Any] = {}
+            c = constraint_from(body)
+            if c is not None:
+                ex["constraint"] = c
+            if top_lp is not None:
+                ex["logprobs"] = top_lp
+            return ex
+
+        def logprobs_json(req) -> dict | None:
+            """OpenAI shape: one entry per generated token with its log-probability and the requested alternatives."""
+            if top_lp is None or req is None:
+                return None
+            piece = lambda t: tokenizer.token_bytes(t).decode("utf-8", errors="replace")
+            content = [{"token": piece(tok), "logprob": lp, "bytes": list(tokenizer.token_bytes(tok)),
+                        "top_logprobs": [{"token": piece(t), "logprob": l} for t, l in top]}
+                       for tok, (lp, top) in zip(req.tokens, getattr(req, "token_logprobs", []))]
+            return {"content": content}
 
         if body.get("stream"):
             async def sse():
@@ -394,7 +457,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                             first = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model,
                                      "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
                             yield f"data: {json.dumps(first)}\n\n"
-                        async for delta, fin in run_generation(prompt_ids, params, max_tokens, rid, stops):
+                        async for delta, fin in run_generation(prompt_ids, params, max_tokens, rid, stops, extras()):
                             if chat:
                                 ch = {"index": 0, "delta": ({"content": delta} if delta else {}), "finish_reason": fin}
                                 chunk = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [ch]}
@@ -417,9 +480,11 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                 choices, completion_tokens = [], 0
                 for i in range(n):
                     text, fin = "", "stop"
-                    async for delta, f in run_generation(prompt_ids, replace(params, seed=params.seed + i), max_tokens, rid, stops):
+                    sink: dict = {}
+                    async for delta, f in run_generation(prompt_ids, replace(params, seed=params.seed + i), max_tokens, rid, stops, extras(), sink):
                         text += delta
                         fin = f or fin
+                    lpj = logprobs_json(sink.get("req"))
                     completion_tokens += len(tokenizer.encode(text)) if text else 0
                     if chat:
                         msg: dict[str, Any] = {"role": "assistant", "content": text}
@@ -429,9 +494,9 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                             if calls:
                                 msg = {"role": "assistant", "content": None, "tool_calls": calls}
                                 fin = "tool_calls"
-                        choices.append({"index": i, "message": msg, "finish_reason": fin})
+                        choices.append({"index": i, "message": msg, "finish_reason": fin, **({"logprobs": lpj} if lpj else {})})
                     else:
-                        choices.append({"index": i, "text": text, "finish_reason": fin})
+                        choices.append({"index": i, "text": text, "finish_reason": fin, **({"logprobs": lpj} if lpj else {})})
         except TimeoutError as e:
             metrics.errors.inc()
             return error(504, str(e), "timeout", rid)

@@ -88,9 +88,9 @@ def test_prompt_chunks_interleave_with_decode_steps():
 
 
 def test_slot_gap_is_closed_when_a_stream_ends_during_a_prefill():
-    eng = FakeEngine()
+    eng = FakeEngine(step_delay=0.02)
     sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=32)
-    a = sched.submit([5] * 20, SamplingParams(), 3)             # ends after three tokens ...
+    a = sched.submit([5] * 20, SamplingParams(), 3)             # ends after three tokens (two slow decode steps) ...
     sched.start()
     while not a.tokens:
         time.sleep(0.001)
@@ -173,3 +173,61 @@ def test_policy_level_sets_the_page_format_of_the_next_sequence():
     sched.stop()
     assert eng.formats == ["f16", "f16", "q8", "q8", "q4"] and [r.kv_format for r in (a, c, e)] == ["f16", "q8", "q4"]
     assert pol.upgrades == 2
+
+
+def test_constrained_request_sends_masks_and_ends_when_the_constraint_is_complete():
+    import numpy as np
+
+    class Exactly(object):
+        """Allows exactly the token sequence ``seq``; complete after the last one."""
+
+        def __init__(self, seq):
+            self.seq, self.i = seq, 0
+
+        def reset(self):
+            self.i = 0
+
+        def allowed_mask(self):
+            m = np.zeros(32, dtype=np.uint32)
+            t = self.seq[self.i]
+            m[t >> 5] |= np.uint32(1 << (t & 31))
+            return m
+
+        def advance(self, tok):
+            self.i += 1
+            return True
+
+        def is_complete(self):
+            return self.i >= len(self.seq)
+
+    class Eng(FakeEngine):
+        seen_masks = []
+
+        def finish_sequence(self, prompt, slot, mask=None):
+            super().finish_sequence(prompt, slot)
+            return self._pick(slot, mask)
+
+        def step_batch(self, positions, masks=None):
+            out = super().step_batch(positions)
+            for s, m in (masks or {}).items():
+                out[s] = self._pick(s, m)
+            return out
+
+        def _pick(self, slot, mask):
+            if mask is None:
+                return self.slots[slot]["seed"] % 1000
+            self.seen_masks.append(mask.copy())
+            return int(np.flatnonzero(np.unpackbits(mask.view(np.uint8), bitorder="little"))[0])
+
+        def token_logprobs(self, slot, tok, n):
+            return (-1.0, [(tok, -1.0)][:n])
+
+    eng = Eng()
+    sched = BatchScheduler(eng, eos_token=-1).start()
+    free = sched.submit([9] * 20, SamplingParams(), 6)
+    tied = sched.submit([1] * 20, SamplingParams(), 50, constraint=Exactly([7, 300, 12]), logprobs=1)
+    assert tied.wait(10) == [7, 300, 12] and tied.finish_reason == "stop"
+    assert len(tied.token_logprobs) == 3 and tied.token_logprobs[0] == (-1.0, [(7, -1.0)])
+    assert len(free.wait(10)) == 6
+    sched.stop()
+    assert len(eng.seen_masks) == 3

@@ -320,3 +320,43 @@ def test_breaker_counts_a_failed_submit_once():
     c = TestClient(app)
     assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]}).status_code == 500
     assert app.state.breaker.failures == 1
+
+
+class _ExtrasBackend(FakeBackend):
+    """Records the constraint / logprobs a request carried and answers with recorded log-probabilities."""
+
+    def submit(self, prompt, params, max_tokens, on_token, request_id, **extra):
+        self.extra = extra
+        r = super().submit(prompt, params, max_tokens, on_token, request_id)
+        r.done.wait(5)
+        n = extra.get("logprobs")
+        r.token_logprobs = [(-0.5 - i, [(65 + i, -0.5 - i), (66 + i, -2.0)][: n or 0]) for i in range(len(r.tokens))] if n is not None else []
+        return r
+
+
+def _client_with(backend):
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+    return TestClient(create_app(backend, ByteTokenizer(), ServerConfig()))
+
+
+def test_response_format_becomes_a_token_constraint_and_logprobs_are_returned():
+    from oxibonsai_b200.runtime.constrained import GrammarConstraint
+    be = _ExtrasBackend(reply="{}")
+    c = _client_with(be)
+    body = {"messages": [{"role": "user", "content": "json please"}], "response_format": {"type": "json_object"},
+            "logprobs": True, "top_logprobs": 2, "max_tokens": 8}
+    j = c.post("/v1/chat/completions", json=body).json()
+    assert isinstance(be.extra["constraint"], GrammarConstraint) and be.extra["logprobs"] == 2
+    mask = be.extra["constraint"].allowed_mask()            # a JSON value may start with '{' but not with '}'
+    assert (mask[ord("{") >> 5] >> (ord("{") & 31)) & 1 and not (mask[ord("}") >> 5] >> (ord("}") & 31)) & 1
+    lp = j["choices"][0]["logprobs"]["content"]
+    assert [e["token"] for e in lp] == ["{", "}"] and lp[0]["logprob"] == -0.5 and len(lp[0]["top_logprobs"]) == 2
+    # a schema is compiled too; plain text carries neither field
+    body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 4,
+            "response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"]}}}}
+    assert c.post("/v1/chat/completions", json=body).status_code == 200 and isinstance(be.extra["constraint"], GrammarConstraint)
+    j = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 4}).json()
+    assert be.extra == {} and "logprobs" not in j["choices"][0]
+    assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "yaml"}}).status_code == 400
+    assert c.post("/v1/completions", json={"prompt": "x", "logprobs": 3, "max_tokens": 4}).json()["choices"][0]["logprobs"]["content"]
