@@ -402,8 +402,19 @@ class Qwen3Runner:
         torch.arange(pos0, pos0 + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
         K.check(K._pf().bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0, slot, 0, K.stream()), "prefill_chunk")
         xn = K.norm_to_f16_paired(b["h"][:T], self.w.out_norm, self.cfg.eps, natural=True)
-        logits = K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"])
-        return K.sample(logits)
+        if self.tp is None:
+            logits = K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"])
+            return K.sample(logits)
+        # vocab-parallel head: every rank computes its slice for the T positions and pushes it into all ranks' logits areas
+        if T > self.max_batch:
+            raise ValueError(f"tensor-parallel verification of {T} tokens needs max_batch >= {T} (the gathered logits use the batch rows)")
+        rows = self.w.lm_head.shape[0]
+        local = K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"]) if rows else torch.empty((T, 0), dtype=torch.float32, device=self.device)
+        from ..parallel import tp as _tp
+        rows_per_rank = (self.cfg.vocab + self.w.tp_size - 1) // self.w.tp_size
+        K.check(_tp._lib().bonsai_tp_allgather_logits(self.tp.handle, local.data_ptr() if rows else None, T, rows, self.w.tp_rank * rows_per_rank,
+                                                      self.cfg.vocab, K.stream()), "tp_allgather_logits")
+        return K.sample(self.logits[:T])
 
     def prefill_launches(self, n_tokens: int, chunk: int = 1024) -> int:
         full, tail = divmod(n_tokens, chunk)

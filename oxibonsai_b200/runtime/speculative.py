@@ -98,6 +98,8 @@ class SpeculativeStats:
     accepted: int = 0
     emitted: int = 0
     target_passes: int = 0
+    prefill_seconds: float = 0.0     # both prompts into the caches (GPU decoder only)
+    decode_seconds: float = 0.0      # everything after that
     history: list[int] = field(default_factory=list)
 
     @property
@@ -198,9 +200,13 @@ class GpuSpeculativeDecoder:
         greedy = SamplingPreset.GREEDY.params()
         total = len(prompt) + max_tokens + self.lookahead.config.max_lookahead + 2
         out: list[int] = []
+        import time
+        t0 = time.perf_counter()
         try:
             last = self.target.open_sequence(prompt, total, 0, greedy)
             self.draft.open_sequence(prompt, total, 0, greedy)
+            self.stats.prefill_seconds = time.perf_counter() - t0      # both prompts are in the caches (open_sequence synchronises)
+            t0 = time.perf_counter()
             pos = len(prompt)            # position at which `last` will be fed
             draft_pos = pos              # the draft cache holds positions < draft_pos
             while len(out) < max_tokens:
@@ -241,5 +247,6 @@ class GpuSpeculativeDecoder:
                 last = nxt
             return out
         finally:
+            self.stats.decode_seconds = time.perf_counter() - t0
             self.target.close_sequence(0)
             self.draft.close_sequence(0)

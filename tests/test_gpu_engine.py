@@ -87,3 +87,25 @@ def test_batched_decode_matches_single_sequence_decode(tiny_gguf):
     agree = sum(x == y for a, b in zip(single, batch) for x, y in zip(a, b))
     assert agree >= 24, (single, batch)   # f16 GEMM activations vs packed-half GEMV: near-ties may flip late tokens
     assert eng.runner._pf["status"].item() == 0
+
+
+def test_constraint_masks_reach_the_gpu_sampler(tiny_gguf):
+    """Constrained decoding through the engine: the constraint's vocabulary mask is uploaded before every step and the
+    sampler kernel only picks allowed tokens; a sequence constraint forces its tokens and ends the generation."""
+    from oxibonsai_b200.runtime import EngineBuilder
+    from oxibonsai_b200.runtime.constrained import AllowListConstraint, SequenceConstraint, TokenTable
+    from oxibonsai_b200.runtime.presets import SamplingParams
+    eng = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(96).build()
+    table = TokenTable([bytes([i % 251, i // 251]) for i in range(1000)])
+    free = eng.generate([3, 1, 4, 1, 5], 10, stop_at_eos=False)
+    allowed = {7, 300, 999, 512}
+    got = eng.generate([3, 1, 4, 1, 5], 10, stop_at_eos=False, constraint=AllowListConstraint(table, allowed))
+    assert len(got) == 10 and set(got) <= allowed
+    hot = eng.generate([3, 1, 4, 1, 5], 10, SamplingParams(temperature=0.9, top_k=40, top_p=0.95, seed=3), stop_at_eos=False,
+                       constraint=AllowListConstraint(table, allowed))
+    assert len(hot) == 10 and set(hot) <= allowed
+    forced = eng.generate([3, 1, 4, 1, 5], 10, stop_at_eos=False, constraint=SequenceConstraint(table, [11, 22, 33]))
+    assert forced == [11, 22, 33]
+    assert eng.generate([3, 1, 4, 1, 5], 10, stop_at_eos=False) == free          # the mask does not outlive its request
+    lp, top = eng.token_logprobs(0, free[-1], 3)
+    assert lp <= 0.0 and len(top) == 3 and top[0][1] >= top[1][1] >= top[2][1]

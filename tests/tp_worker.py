@@ -52,6 +52,18 @@ def main():
         agree = sum(x == y for a, b in zip(single, batch) for x, y in zip(a, b))
         out.update(ok=(same and batch == again and agree >= 32 and all(len(b) == 10 for b in batch)), agree=agree, same=same,
                    single=single, batch=batch, again=again, status=eng.runner.tp.status(), pf_status=int(eng.runner._pf["status"].item()))
+    elif mode == "speculative":
+        # exact mode on both sides: the batched verification (vocab-parallel head gathered for every verified position)
+        # picks the target's own greedy tokens, and a draft with the same weights is accepted every time
+        from oxibonsai_b200.runtime.speculative import GpuSpeculativeDecoder
+        mk = lambda nb: (EngineBuilder().model_path(path).preset("greedy").max_seq_len(128).max_batch(nb).kv_cache("f32").device(f"cuda:{local}")
+                         .tensor_parallel(rank, world).build())
+        target, draft = mk(9), mk(1)
+        want = target.generate(prompt, 20)
+        dec = GpuSpeculativeDecoder(target, draft)
+        got = dec.generate(prompt, 20)
+        out.update(ok=(got[:len(want)] == want[:len(got)] and len(got) >= len(want) - 1 and dec.stats.acceptance_rate > 0.9),
+                   got=got, want=want, acceptance=dec.stats.acceptance_rate, status=target.runner.tp.status() | draft.runner.tp.status())
     dist.barrier()
     with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
         json.dump(out, f)
