@@ -178,6 +178,66 @@ def repack_cache_key(model_path: str, tp_rank: int, tp_size: int, layout: str = 
     return h.hexdigest()
 
 
+REPACK_MAGIC = b"OXRP"
+_REPACK_ALIGN = 4096
+
+
+def save_repacked(path: str, tensors: dict, meta: dict | None = None) -> None:
+    """Writes named tensors (torch, any device) as one file: ``"OXRP" | u32 version=1 | u64 header_len | header JSON`` and
+    the raw bytes of every tensor at a 4096-byte aligned offset.  The header lists name, dtype, shape, offset and byte
+    count, plus ``meta``.  The file is written under a temporary name and renamed, so a reader never sees a partial one."""
+    import torch
+    entries, off = [], 0
+    flat = {}
+    for name, t in tensors.items():
+        c = t.detach().contiguous().cpu()
+        flat[name] = c
+        nbytes = c.numel() * c.element_size()
+        entries.append({"name": name, "dtype": str(c.dtype).replace("torch.", ""), "shape": list(c.shape), "offset": off, "nbytes": nbytes})
+        off += -(-nbytes // _REPACK_ALIGN) * _REPACK_ALIGN
+    header = json.dumps({"meta": meta or {}, "tensors": entries}).encode("utf-8")
+    base = -(-(16 + len(header)) // _REPACK_ALIGN) * _REPACK_ALIGN
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "wb") as f:
+        f.write(REPACK_MAGIC + struct.pack("<IQ", 1, len(header)) + header)
+        for e in entries:
+            f.seek(base + e["offset"])
+            if e["nbytes"]:
+                f.write(flat[e["name"]].reshape(-1).view(torch.uint8).numpy().tobytes())
+        f.truncate(base + off)
+    os.replace(tmp, path)
+
+
+def load_repacked(path: str, device="cpu") -> tuple[dict, dict]:
+    """Reads a file written by :func:`save_repacked`; returns ``(tensors, meta)`` with the tensors on ``device`` (uploaded
+    from the page cache through pinned staging copies when it is a CUDA device)."""
+    import torch
+    size = os.path.getsize(path)
+    with open(path, "rb") as f:
+        if _read(f, 4) != REPACK_MAGIC:
+            raise CheckpointError("not a repacked-weight cache")
+        version, hlen = struct.unpack("<IQ", _read(f, 12))
+        if version != 1 or hlen > size:
+            raise CheckpointError("unsupported or damaged repacked-weight cache")
+        header = json.loads(_read(f, hlen).decode("utf-8"))
+    base = -(-(16 + hlen) // _REPACK_ALIGN) * _REPACK_ALIGN
+    mm = np.memmap(path, dtype=np.uint8, mode="r")
+    dev = torch.device(device)
+    out = {}
+    for e in header["tensors"]:
+        lo = base + e["offset"]
+        if lo + e["nbytes"] > size:
+            raise CheckpointError(f"tensor {e['name']!r} exceeds the file size")
+        if e["nbytes"] == 0:
+            out[e["name"]] = torch.empty(e["shape"], dtype=getattr(torch, e["dtype"]), device=dev)
+            continue
+        raw = torch.from_numpy(np.array(mm[lo: lo + e["nbytes"]], copy=True))
+        if dev.type == "cuda":
+            raw = raw.pin_memory().to(dev, non_blocking=True)
+        out[e["name"]] = raw.view(getattr(torch, e["dtype"])).reshape(e["shape"])
+    return out, header.get("meta", {})
+
+
 def tie_weights(tensors: dict[str, np.ndarray], embed: str = "token_embd.weight", head: str = "output.weight") -> dict[str, np.ndarray]:
     """Makes the LM head an alias of the embedding table (shared storage)."""
     if embed not in tensors:

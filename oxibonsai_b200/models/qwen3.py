@@ -11,6 +11,8 @@ device so one CUDA graph covers embed -> layers -> LM head -> sampler.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from dataclasses import dataclass
 
@@ -21,6 +23,7 @@ from ..core import gguf as G
 from ..core.gguf import GgufFile, Qwen3Config
 from ..core.oracle import rope_table
 from ..ops import cuda_ops as K
+from ..ops import nvtx
 
 _QUANT_TYPES = (G.TQ2_0_G128, G.Q1_0_G128)
 
@@ -85,9 +88,18 @@ def _f16_matrix(f: GgufFile, name: str, device, row0: int = 0, nrows: int | None
 class Qwen3Weights:
     """Device-resident weights of one tensor-parallel rank."""
 
-    def __init__(self, f: GgufFile, device, tp_rank: int = 0, tp_size: int = 1, decode_layout: bool = True):
+    REPACK_LAYOUT = "planar-sm+s16-v1"
+
+    def __init__(self, f: GgufFile, device, tp_rank: int = 0, tp_size: int = 1, decode_layout: bool = True,
+                 cache_dir: str | None = None, source_path: str | None = None):
         """``decode_layout``: also build the S16 form of every layer matrix, which the batch-1 decode GEMV streams
-        (the planar form stays: the prompt and batched GEMMs read it)."""
+        (the planar form stays: the prompt and batched GEMMs read it).
+
+        ``cache_dir`` (with ``source_path``, the GGUF file ``f`` was opened from): directory of the repacked-weight cache.
+        The device layouts of this rank's shard are written there once, under a key made of the file's identity, the
+        layout version and the tensor-parallel coordinates; a later start reads them back instead of decoding and
+        repacking the GGUF tensors (the counterpart of the reference's quantised-tensor disk cache,
+        crates/oxibonsai-model/src/disk_cache.rs:7-19,277)."""
         cfg = f.config()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -107,6 +119,14 @@ class Qwen3Weights:
         hd, hidden = cfg.head_dim, cfg.hidden
         qd_l, kvd_l = self.heads_local * hd, self.kv_heads_local * hd
         dev = self.device
+        self.from_cache = False
+        cache_file = None
+        if cache_dir and source_path:
+            from .checkpoint import repack_cache_key
+            layout = self.REPACK_LAYOUT if decode_layout else self.REPACK_LAYOUT.split("+")[0]
+            cache_file = os.path.join(cache_dir, repack_cache_key(source_path, tp_rank, tp_size, layout) + ".oxrp")
+            if os.path.exists(cache_file) and self._load_cache(cache_file, decode_layout):
+                return
 
         self.embd = _f16_matrix(f, "token_embd.weight", dev)
         head_name = "output.weight" if f.has_tensor("output.weight") else "token_embd.weight"
@@ -150,6 +170,57 @@ class Qwen3Weights:
             del raws
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
+        if cache_file is not None:
+            self._save_cache(cache_file)
+
+    _LAYER_MATS = ("qkv", "o", "gate_up", "down")
+    _LAYER_VECS = ("attn_norm", "ffn_norm", "q_norm", "k_norm")
+
+    def _save_cache(self, path: str) -> None:
+        from .checkpoint import save_repacked
+        t = {"embd": self.embd, "out_norm": self.out_norm}
+        if self.lm_head is not self.embd:
+            t["lm_head"] = self.lm_head
+        for l, lw in enumerate(self.layers):
+            for m in self._LAYER_MATS:
+                pw = getattr(lw, m)
+                t[f"{l}.{m}.codes"], t[f"{l}.{m}.scales"] = pw.codes, pw.scales
+                s16 = getattr(lw, m + "_s16")
+                if s16 is not None:
+                    t[f"{l}.{m}.s16"] = s16.data
+            for v in self._LAYER_VECS:
+                t[f"{l}.{v}"] = getattr(lw, v)
+        os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+        try:
+            save_repacked(path, t, {"layers": len(self.layers), "weight_type": int(self.weight_type), "lm_row0": int(self.lm_row0),
+                                    "tp": f"{self.tp_rank}/{self.tp_size}"})
+        except OSError:
+            pass          # a read-only or full cache directory costs the next start its shortcut, nothing else
+
+    def _load_cache(self, path: str, decode_layout: bool) -> bool:
+        from .checkpoint import CheckpointError, load_repacked
+        try:
+            t, meta = load_repacked(path, self.device)
+        except (CheckpointError, OSError, ValueError, KeyError):
+            return False
+        if int(meta.get("layers", -1)) != self.cfg.layers:
+            return False
+        self.embd, self.out_norm = t["embd"], t["out_norm"]
+        self.lm_head = t.get("lm_head", self.embd)
+        self.lm_row0 = int(meta.get("lm_row0", 0))
+        self.weight_type = int(meta["weight_type"])
+        self.layers = []
+        for l in range(self.cfg.layers):
+            mats = [K.PlanarWeight.from_tensors(t[f"{l}.{m}.codes"], t[f"{l}.{m}.scales"]) for m in self._LAYER_MATS]
+            lw = LayerWeights(*mats, *(t[f"{l}.{v}"] for v in self._LAYER_VECS))
+            if decode_layout and self.device.type == "cuda":
+                for m, pw in zip(self._LAYER_MATS, mats):
+                    setattr(lw, m + "_s16", K.S16Weight.from_tensor(pw.n, pw.k, t[f"{l}.{m}.s16"]))
+            self.layers.append(lw)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self.from_cache = True
+        return True
 
     @property
     def packed_bytes(self) -> int:
@@ -389,8 +460,10 @@ class Qwen3Runner:
             b["tokens"][:T].copy_(tokens[done:done + T], non_blocking=True)
             torch.arange(pos0 + done, pos0 + done + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
             last = done + T == n
+            mark = nvtx.push(f"prefill_chunk[slot={slot},pos={pos0 + done},T={T}]")
             K.check(lib.bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0 + done, slot, int(last), K.stream()),
                     "prefill_chunk")
+            nvtx.pop(mark)
             done += T
 
     def verify_greedy(self, tokens: torch.Tensor, slot: int, pos0: int) -> torch.Tensor:
@@ -398,6 +471,10 @@ class Qwen3Runner:
         greedy next token after each of them (int32 [T]) - the batched verification pass of speculative decoding."""
         T = tokens.numel()
         b = self._prefill_buffers(max(64, T))
+        with nvtx.range(f"verify[slot={slot},pos={pos0},T={T}]"):
+            return self._verify_greedy(tokens, slot, pos0, T, b)
+
+    def _verify_greedy(self, tokens: torch.Tensor, slot: int, pos0: int, T: int, b: dict) -> torch.Tensor:
         b["tokens"][:T].copy_(tokens, non_blocking=True)
         torch.arange(pos0, pos0 + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
         K.check(K._pf().bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0, slot, 0, K.stream()), "prefill_chunk")
@@ -462,4 +539,6 @@ class Qwen3Runner:
                     self.step_eager(batch, sample, masked=masked)
             torch.cuda.current_stream(self.device).wait_stream(s)
             self._graphs[key] = g
+        mark = nvtx.push(f"decode_step[batch={batch}]")
         g.replay()
+        nvtx.pop(mark)

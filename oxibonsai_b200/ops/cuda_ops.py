@@ -98,6 +98,15 @@ class PlanarWeight:
         self.codes = torch.empty((n, k // 16), dtype=torch.int32, device=device)
         self.scales = torch.empty((n, k // 128), dtype=torch.float16, device=device)
 
+    @classmethod
+    def from_tensors(cls, codes: torch.Tensor, scales: torch.Tensor) -> "PlanarWeight":
+        """Wraps tensors that already hold the layout (the repacked-weight cache)."""
+        self = cls.__new__(cls)
+        self.n, self.k = codes.shape[0], codes.shape[1] * 16
+        assert codes.dtype == torch.int32 and scales.dtype == torch.float16 and tuple(scales.shape) == (self.n, self.k // 128)
+        self.codes, self.scales = codes, scales
+        return self
+
     @property
     def nbytes(self) -> int:
         return self.codes.numel() * 4 + self.scales.numel() * 2
@@ -154,6 +163,14 @@ class S16Weight:
         self.data = torch.empty(nbytes, dtype=torch.uint8, device=planar.codes.device)
         check(_s16().bonsai_repack_s16(planar.codes.data_ptr(), planar.scales.data_ptr(), self.n, self.k, self.data.data_ptr(), stream()),
               "repack_s16")
+
+    @classmethod
+    def from_tensor(cls, n: int, k: int, data: torch.Tensor) -> "S16Weight":
+        """Wraps bytes that already hold the layout (the repacked-weight cache)."""
+        self = cls.__new__(cls)
+        self.n, self.k, self.data = n, k, data
+        assert data.dtype == torch.uint8
+        return self
 
     @property
     def nbytes(self) -> int:

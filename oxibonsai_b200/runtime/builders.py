@@ -58,6 +58,7 @@ class EngineBuilder:
         self._kv_pages: int | None = None
         self._warmup = True
         self._exact: bool | None = None
+        self._repack_cache: str | None = None
 
     def model_path(self, path: str) -> "EngineBuilder":
         self._model_path = str(path); return self
@@ -100,10 +101,15 @@ class EngineBuilder:
         activations on the tensor-core kernels; ``None`` (default): exact only with an f32 KV cache."""
         self._exact = on; return self
 
+    def repack_cache(self, directory: str | None) -> "EngineBuilder":
+        """Directory in which the device layouts of the weights are kept between starts (None = no cache)."""
+        self._repack_cache = directory; return self
+
     def options(self) -> dict:
         return dict(model_path=self._model_path, max_seq_len=self._max_seq_len, max_batch=self._max_batch, kv_dtype=self._kv_dtype,
                     device=self._device, sampling=self._sampler.build(), page_size=self._page_size, kv_pages=self._kv_pages,
-                    tp_rank=self._tp_rank, tp_size=self._tp_size, warmup=self._warmup, exact=self._exact)
+                    tp_rank=self._tp_rank, tp_size=self._tp_size, warmup=self._warmup, exact=self._exact,
+                    repack_cache=self._repack_cache)
 
     def build(self):
         if not self._model_path:

@@ -8,6 +8,8 @@ uploads (token, position) from pinned memory, replays one CUDA graph and reads b
 """
 from __future__ import annotations
 
+import os
+
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Iterator, Sequence
@@ -47,7 +49,8 @@ class InferenceEngine:
 
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
-                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None):
+                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None,
+                 repack_cache: str | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("InferenceEngine needs a CUDA device; use oxibonsai_b200.core.Oracle for the CPU path")
         self.device = torch.device(device)
@@ -63,7 +66,10 @@ class InferenceEngine:
         t0 = time.perf_counter()
         # exact = f32 activations end to end (the token-stream gate); default: exact only with an f32 KV cache
         self.exact = (self.kvt == K.KV_F32) if exact is None else bool(exact)
-        self.weights = Qwen3Weights(self.gguf, self.device, tp_rank, tp_size, decode_layout=not self.exact)
+        # directory of the repacked-weight cache (None = decode and repack the GGUF tensors on every start)
+        self.repack_cache = repack_cache if repack_cache is not None else os.environ.get("OXIBONSAI_REPACK_CACHE") or None
+        self.weights = Qwen3Weights(self.gguf, self.device, tp_rank, tp_size, decode_layout=not self.exact,
+                                    cache_dir=self.repack_cache, source_path=self.model_path)
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
                                self.kvt, self.device)
@@ -482,7 +488,8 @@ class InferenceEngine:
         c = self.config
         return {"name": c.name, "arch": c.arch, "layers": c.layers, "hidden": c.hidden, "heads": c.heads, "kv_heads": c.kv_heads,
                 "head_dim": c.head_dim, "intermediate": c.inter, "vocab": c.vocab, "context": c.context,
-                "weight_bytes": self.weights.packed_bytes, "kv_bytes": self.kv.nbytes, "load_seconds": self.load_seconds}
+                "weight_bytes": self.weights.packed_bytes, "kv_bytes": self.kv.nbytes, "load_seconds": self.load_seconds,
+                "weights_from_repack_cache": self.weights.from_cache}
 
 
 def layer_weight_type(gguf: GgufFile) -> int:
@@ -506,7 +513,8 @@ class GenericFormatEngine:
 
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
-                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None):
+                 kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None,
+                 repack_cache: str | None = None):      # the generic formats are used as stored: nothing to cache
         import threading
         from ..models.qwen3_generic import GenericQwen3Engine
         if tp_size != 1:

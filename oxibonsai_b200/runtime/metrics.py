@@ -138,6 +138,7 @@ class RequestRateAggregator:
         self.tps: deque[float] = deque(maxlen=window)
         self.waits: deque[float] = deque(maxlen=window)
         self.tbts: deque[float] = deque(maxlen=window * 8)
+        self.completed = 0
         self._lock = threading.Lock()
 
     def record(self, tr: RequestRateTracker) -> None:
@@ -146,13 +147,15 @@ class RequestRateAggregator:
                 self.tps.append(tr.ewma_tps)
             self.waits.append(tr.queue_wait)
             self.tbts.extend(tr.tbt)
+            self.completed += 1
 
     def snapshot(self) -> dict:
         with self._lock:
             def pct(v, q):
                 v = sorted(v)
                 return v[min(len(v) - 1, int(q * len(v)))] if v else 0.0
-            return {"tokens_per_second": sum(self.tps) / len(self.tps) if self.tps else 0.0,
+            return {"completed_requests": self.completed,
+                    "tokens_per_second": sum(self.tps) / len(self.tps) if self.tps else 0.0,
                     "itl_p50": pct(self.tbts, 0.5), "itl_p95": pct(self.tbts, 0.95),
                     "queue_wait": sum(self.waits) / len(self.waits) if self.waits else 0.0}
 

@@ -556,6 +556,19 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
     async def admin_cache():
         return {"kv_utilization": backend.kv_utilization()}
 
+    @app.get("/admin/workload-stats")
+    async def admin_workload():
+        """Sliding-window request telemetry and the KV-cache policy state in one document (admin.rs:223-260)."""
+        snap = metrics.aggregator.snapshot()
+        lvl = kv_policy.level
+        return {"request_rate": {"completed_requests": snap["completed_requests"], "mean_tokens_per_second": snap["tokens_per_second"],
+                                 "tbt_p50_seconds": snap["itl_p50"], "tbt_p95_seconds": snap["itl_p95"],
+                                 "mean_queue_wait_seconds": snap["queue_wait"]},
+                "kv_cache": {"level": lvl.name.lower(), "memory_factor": lvl.bytes_per_element / 2.0, "pressure_ewma": kv_policy.smoothed_pressure,
+                             "samples": kv_policy.observations, "upgrades": kv_policy.upgrades, "downgrades": kv_policy.downgrades,
+                             "page_format_for_new_sequences": kv_policy.page_format()},
+                "status": "ok"}
+
     @app.get("/ui")
     async def ui():
         p = os.path.join(os.path.dirname(__file__), "chat.html")

@@ -109,3 +109,16 @@ def test_constraint_masks_reach_the_gpu_sampler(tiny_gguf):
     assert eng.generate([3, 1, 4, 1, 5], 10, stop_at_eos=False) == free          # the mask does not outlive its request
     lp, top = eng.token_logprobs(0, free[-1], 3)
     assert lp <= 0.0 and len(top) == 3 and top[0][1] >= top[1][1] >= top[2][1]
+
+
+def test_repacked_weight_cache_gives_the_same_engine(tiny_gguf, tmp_path):
+    from oxibonsai_b200.runtime import EngineBuilder
+    prompt = [5, 9, 200, 31, 77]
+    mk = lambda: EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(96).kv_cache("f16").repack_cache(str(tmp_path)).build()
+    first = mk()
+    assert not first.weights.from_cache and len(list(tmp_path.iterdir())) == 1
+    want = first.generate(prompt, 12)
+    second = mk()
+    assert second.weights.from_cache and second.model_info()["weights_from_repack_cache"]
+    assert second.generate(prompt, 12) == want
+    assert second.weights.packed_bytes == first.weights.packed_bytes

@@ -378,3 +378,30 @@ def test_host_kv_caches_and_layer_stats(tiny_gguf):
     assert KV.QuantizedKvCache(L, H, T, D).compression_ratio() > 3
     stats = KV.forward_with_stats(Oracle(GgufFile.open(tiny_gguf), 16), [1, 2, 3])
     assert len(stats) == 2 and all(s.std > 0 and not s.has_nan for s in stats) and "layer   1" in stats[1].summary()
+
+
+def test_repacked_weight_cache_file_roundtrip(tmp_path):
+    import torch
+    from oxibonsai_b200.models import checkpoint as CK
+    t = {"a.codes": torch.arange(24, dtype=torch.int32).reshape(2, 12), "a.scales": torch.linspace(0, 1, 6).to(torch.float16).reshape(2, 3),
+         "bytes": torch.arange(5000, dtype=torch.int64).to(torch.uint8), "empty": torch.zeros((0, 4), dtype=torch.float32),
+         "norm": torch.randn(7)}
+    path = str(tmp_path / "w.oxrp")
+    CK.save_repacked(path, t, {"layers": 3})
+    got, meta = CK.load_repacked(path)
+    assert meta == {"layers": 3} and set(got) == set(t)
+    for k in t:
+        assert got[k].dtype == t[k].dtype and got[k].shape == t[k].shape and torch.equal(got[k], t[k])
+    # damaged files are refused, not half-read
+    with open(path, "r+b") as f:
+        f.write(b"XXXX")
+    with pytest.raises(CK.CheckpointError):
+        CK.load_repacked(path)
+
+
+def test_nvtx_ranges_are_off_by_default_and_nest():
+    from oxibonsai_b200.ops import nvtx
+    assert not nvtx.enabled() and nvtx.push("x") is False
+    nvtx.pop(False)
+    with nvtx.range("nothing happens on CPU when off"):
+        pass

@@ -140,6 +140,9 @@ def test_metrics_embeddings_admin(client):
     assert len(e["data"]) == 2 and len(e["data"][0]["embedding"]) == 512
     st = client.get("/admin/status").json()
     assert st["model"] == "fake-bonsai" and st["circuit"] == "closed"
+    ws = client.get("/admin/workload-stats").json()
+    assert ws["status"] == "ok" and ws["request_rate"]["completed_requests"] == 1 and ws["request_rate"]["tbt_p95_seconds"] >= 0.0
+    assert ws["kv_cache"]["level"] == "fp16" and ws["kv_cache"]["memory_factor"] == 1.0 and ws["kv_cache"]["samples"] == 1
     assert client.post("/admin/reset-metrics").json() == {"status": "ok"}
     assert "oxibonsai_requests_total 0" in client.get("/metrics").text
     assert "<html>" in client.get("/ui").text
