@@ -47,18 +47,32 @@ async def one_stream(session, url: str, prompt: str, max_tokens: int, seed: int)
             "top_p": 0.9, "seed": seed}
     t0 = time.perf_counter()
     times: list[float] = []
-    async with session.post(url, json=body) as resp:
-        async for raw in resp.content:
-            line = raw.decode("utf-8", errors="replace").strip()
-            if not line.startswith("data:") or line.endswith("[DONE]"):
-                continue
-            try:
-                ch = json.loads(line[5:])["choices"][0]
-            except Exception:
-                continue
-            if (ch.get("delta") or {}).get("content"):
-                times.append(time.perf_counter())
-    return {"t0": t0, "times": times}
+    out = {"t0": t0, "times": times, "status": None, "finish": None, "error": None}
+    try:
+        async with session.post(url, json=body) as resp:
+            out["status"] = resp.status
+            if resp.status != 200:
+                out["error"] = (await resp.text())[:300]
+                return out
+            async for raw in resp.content:
+                line = raw.decode("utf-8", errors="replace").strip()
+                if not line.startswith("data:") or line.endswith("[DONE]"):
+                    continue
+                try:
+                    j = json.loads(line[5:])
+                    if "error" in j:
+                        out["error"] = json.dumps(j["error"])[:300]
+                        continue
+                    ch = j["choices"][0]
+                except Exception:
+                    continue
+                if (ch.get("delta") or {}).get("content"):
+                    times.append(time.perf_counter())
+                if ch.get("finish_reason"):
+                    out["finish"] = ch["finish_reason"]
+    except Exception as e:  # noqa: BLE001 - a failed stream is part of the result
+        out["error"] = f"{type(e).__name__}: {e}"[:300]
+    return out
 
 
 async def drive(url: str, prompts: list[str], max_tokens: int) -> list[dict]:
@@ -120,9 +134,16 @@ def main() -> None:
         prompts = ["".join(rnd.choice("abcdefghijklmnopqrstuvwxyz ") for _ in range(max(1, rnd.randint(a.prompt_min, a.prompt_max) - 30))) for _ in range(a.streams)]
         url = f"http://127.0.0.1:{port}/v1/chat/completions"
         asyncio.run(drive(url, prompts[:2], 8))                       # warm-up: graph capture, tokenizer tables
+        def server_tokens() -> float:
+            for line in urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode().splitlines():
+                if line.startswith("oxibonsai_tokens_generated_total"):
+                    return float(line.split()[-1])
+            return 0.0
+        n0 = server_tokens()
         t0 = time.perf_counter()
         res = asyncio.run(drive(url, prompts, a.max_tokens))
         wall = time.perf_counter() - t0
+        generated = server_tokens() - n0          # the server's own count: every sampled token, whatever text it decodes to
     finally:
         server.terminate()          # this exact child process (torchrun forwards the signal to its ranks)
         try:
@@ -133,14 +154,21 @@ def main() -> None:
     ttft = sorted(r["times"][0] - r["t0"] for r in res if r["times"])
     itl = sorted(b - x for r in res for x, b in zip(r["times"], r["times"][1:]))
     # all streams live: from the last first-token to the first last-token
-    lo, hi = max(r["times"][0] for r in res if r["times"]), min(r["times"][-1] for r in res if r["times"])
+    live = [r for r in res if r["times"]]
+    lo, hi = (max(r["times"][0] for r in live), min(r["times"][-1] for r in live)) if live else (0.0, 0.0)
+    finishes: dict = {}
+    for r in res:
+        finishes[str(r["finish"])] = finishes.get(str(r["finish"]), 0) + 1
+    errors = [r["error"] for r in res if r["error"]]
     steady = sum(1 for r in res for x in r["times"] if lo < x <= hi)
     pct = lambda v, q: None if not v else round(v[min(len(v) - 1, int(q * len(v)))], 4)
     print(json.dumps({
         "metric": f"aggregate decode tok/s over {a.streams} concurrent SSE streams", "model": SHAPES[a.model]["name"], "kv_cache": a.kv,
         "parallelism": f"tp{a.tensor_parallel}" if a.tensor_parallel > 1 else f"{a.replicas} replica(s)",
         "prompt_tokens": [a.prompt_min, a.prompt_max], "max_tokens": a.max_tokens, "preset": "balanced (T 0.7, top-k 40, top-p 0.9)",
-        "content_chunks": chunks, "wall_s": round(wall, 3), "tokens_per_s_overall": round(chunks / wall, 1),
+        "streams_ok": sum(1 for r in res if r["status"] == 200 and not r["error"]), "finish_reasons": finishes, "errors": errors[:3],
+        "generated_tokens_server_count": int(generated), "content_chunks": chunks, "wall_s": round(wall, 3),
+        "tokens_per_s_overall": round(generated / wall, 1), "chunks_per_s_overall": round(chunks / wall, 1),
         "tokens_per_s_all_streams_live": None if hi <= lo else round(steady / (hi - lo), 1),
         "p50_ttft_s": pct(ttft, 0.5), "p95_ttft_s": pct(ttft, 0.95), "p50_itl_s": pct(itl, 0.5), "p95_itl_s": pct(itl, 0.95),
         "note": "a content chunk is one SSE delta: usually one token (the byte tokenizer may hold back incomplete UTF-8)"}))

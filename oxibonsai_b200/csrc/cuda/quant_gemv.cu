@@ -116,6 +116,85 @@ static int launch_quant_gemv(const void* w, const float* x, const float* norm_w,
   return launch_status();
 }
 
+// The same product for NB activation rows at once (a decode batch): every weight element is decoded once and multiplied into
+// NB accumulators.  x: [B][x_ld], out / residual: [B][out_ld]; rows b >= B of the NB-wide template are computed on row B - 1's
+// input and not stored.
+template <typename D, int NB>
+__global__ void __launch_bounds__(256) quant_gemv_batched_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_ld,
+                                                                const float* __restrict__ norm_w, float eps, float* __restrict__ out,
+                                                                const float* __restrict__ residual, int out_ld, int N, int K, int B) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nblk = K / D::kElems;
+  const size_t row_bytes = (size_t)nblk * D::kBytes;
+  const float* xs[NB];
+  float inv[NB];
+#pragma unroll
+  for (int t = 0; t < NB; ++t) {
+    xs[t] = x + (size_t)(t < B ? t : B - 1) * x_ld;
+    inv[t] = 1.0f;
+    if (norm_w != nullptr) {
+      float ss = 0.0f;
+      for (int k = lane; k < K; k += 32) ss += xs[t][k] * xs[t][k];
+      inv[t] = 1.0f / sqrtf(warp_sum(ss) / (float)K + eps);
+    }
+  }
+  for (int row = blockIdx.x * 8 + warp; row < N; row += gridDim.x * 8) {
+    const uint8_t* rp = w + (size_t)row * row_bytes;
+    float acc[NB];
+#pragma unroll
+    for (int t = 0; t < NB; ++t) acc[t] = 0.0f;
+    if (D::kElems == 32) {
+      for (int b = lane; b < nblk; b += 32) {
+        const uint8_t* p = rp + (size_t)b * D::kBytes;
+#pragma unroll 4
+        for (int i = 0; i < 32; ++i) {
+          const int k = b * 32 + i;
+          const float wv = D::at(p, i) * (norm_w ? norm_w[k] : 1.0f);
+#pragma unroll
+          for (int t = 0; t < NB; ++t) acc[t] = fmaf(wv, xs[t][k], acc[t]);
+        }
+      }
+    } else {
+      for (int b = 0; b < nblk; ++b) {
+        const uint8_t* p = rp + (size_t)b * D::kBytes;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = lane * 8 + j, k = b * 256 + i;
+          const float wv = D::at(p, i) * (norm_w ? norm_w[k] : 1.0f);
+#pragma unroll
+          for (int t = 0; t < NB; ++t) acc[t] = fmaf(wv, xs[t][k], acc[t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NB; ++t) {
+      const float v = warp_sum(acc[t]) * inv[t];
+      if (lane == 0 && t < B) out[(size_t)t * out_ld + row] = (residual ? residual[(size_t)t * out_ld + row] : 0.0f) + v;
+    }
+  }
+}
+
+template <typename D>
+static int launch_quant_gemv_batched(const void* w, const float* x, int x_ld, const float* norm_w, float eps, float* out, const float* residual,
+                                     int out_ld, int N, int K, int B, cudaStream_t st) {
+  if (K % D::kElems != 0) return BONSAI_CUDA_BAD_ARG;
+  int grid = (N + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  const uint8_t* wp = (const uint8_t*)w;
+  // groups of up to eight rows: the weights of a later group come from L2 when the matrix fits there
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    const int nb = B - b0 < 8 ? B - b0 : 8;
+    const float* xb = x + (size_t)b0 * x_ld;
+    float* ob = out + (size_t)b0 * out_ld;
+    const float* rb = residual ? residual + (size_t)b0 * out_ld : nullptr;
+    if (nb == 1) quant_gemv_kernel<D><<<grid, 256, 0, st>>>(wp, xb, norm_w, eps, ob, rb, N, K);
+    else if (nb == 2) quant_gemv_batched_kernel<D, 2><<<grid, 256, 0, st>>>(wp, xb, x_ld, norm_w, eps, ob, rb, out_ld, N, K, nb);
+    else if (nb <= 4) quant_gemv_batched_kernel<D, 4><<<grid, 256, 0, st>>>(wp, xb, x_ld, norm_w, eps, ob, rb, out_ld, N, K, nb);
+    else quant_gemv_batched_kernel<D, 8><<<grid, 256, 0, st>>>(wp, xb, x_ld, norm_w, eps, ob, rb, out_ld, N, K, nb);
+  }
+  return launch_status();
+}
+
 // Decodes an [N][K] matrix of blocks into row-major f16 for the dense tensor-core GEMM of the prompt path.  One thread
 // owns eight consecutive inputs and stores them as one 16-byte word.  With `paired` the eight values are written in the
 // K order of the GEMM's activation operand (inside every 16 inputs: position (j & 8) | ((j & 3) * 2 + ((j >> 2) & 1))
@@ -146,6 +225,16 @@ static int launch_quant_to_f16(const void* w, void* out, int N, int K, int paire
   int grid = (int)((total + 255) / 256 < (size_t)(148 * 16) ? (total + 255) / 256 : (size_t)(148 * 16));
   quant_to_f16_kernel<D><<<grid, 256, 0, st>>>((const uint8_t*)w, (__half*)out, N, K, paired);
   return launch_status();
+}
+
+// out[t][i] = silu(gu[t][i]) * gu[t][inter + i]: the activation after a fused gate || up projection of T rows
+__global__ void swiglu_rows_kernel(const float* __restrict__ gu, int gu_ld, float* __restrict__ out, int out_ld, int inter, int T) {
+  const size_t total = (size_t)T * inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / inter), i = (int)(idx % inter);
+    const float g = gu[(size_t)t * gu_ld + i];
+    out[(size_t)t * out_ld + i] = g / (1.0f + __expf(-g)) * gu[(size_t)t * gu_ld + inter + i];
+  }
 }
 
 __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out, int n) {
@@ -182,6 +271,40 @@ int bonsai_quant_gemv(int type, const void* w, const float* x, const float* norm
     case 44: return launch_quant_gemv<DecFp8<true>>(w, x, norm_w, eps, out, residual, N, K, stream);
     default: return BONSAI_CUDA_BAD_ARG;
   }
+}
+
+// The same for B activation rows (a decode batch): x [B][x_ld], out and residual [B][out_ld].
+int bonsai_quant_gemv_batched(int type, const void* w, const float* x, int x_ld, const float* norm_w, float eps, float* out,
+                              const float* residual, int out_ld, int N, int K, int B, cudaStream_t stream) {
+  using namespace bonsai;
+  if (N <= 0 || K <= 0 || B <= 0 || x_ld < K || out_ld < N) return BONSAI_CUDA_BAD_ARG;
+#define BONSAI_QGB(D) return launch_quant_gemv_batched<D>(w, x, x_ld, norm_w, eps, out, residual, out_ld, N, K, B, stream)
+  switch (type) {
+    case 0: BONSAI_QGB(DecF32);
+    case 1: BONSAI_QGB(DecF16);
+    case 30: BONSAI_QGB(DecBF16);
+    case 2: BONSAI_QGB(DecQ4_0);
+    case 8: BONSAI_QGB(DecQ8_0);
+    case 10: BONSAI_QGB(DecQ2K);
+    case 11: BONSAI_QGB(DecQ3K);
+    case 12: BONSAI_QGB(DecQ4K);
+    case 13: BONSAI_QGB(DecQ5K);
+    case 14: BONSAI_QGB(DecQ6K);
+    case 15: BONSAI_QGB(DecQ8K);
+    case 35: BONSAI_QGB(DecTq2_256);
+    case 43: BONSAI_QGB(DecFp8<false>);
+    case 44: BONSAI_QGB(DecFp8<true>);
+    default: return BONSAI_CUDA_BAD_ARG;
+  }
+#undef BONSAI_QGB
+}
+
+int bonsai_swiglu_rows(const float* gu, int gu_ld, float* out, int out_ld, int inter, int T, cudaStream_t stream) {
+  if (inter <= 0 || T <= 0 || gu_ld < 2 * inter || out_ld < inter) return BONSAI_CUDA_BAD_ARG;
+  const size_t total = (size_t)T * inter;
+  int grid = (int)((total + 255) / 256 < (size_t)(148 * 8) ? (total + 255) / 256 : (size_t)(148 * 8));
+  bonsai::swiglu_rows_kernel<<<grid, 256, 0, stream>>>(gu, gu_ld, out, out_ld, inter, T);
+  return bonsai::launch_status();
 }
 
 // out f16 [N][K] = the decoded matrix (same type ids as bonsai_quant_gemv); `paired` selects the activation K order of

@@ -211,6 +211,8 @@ def _mma():
 _QG_SIG = {
     "bonsai_quant_gemv": [_i, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp],
     "bonsai_swiglu": [_vp, _vp, _vp, _i, _vp],
+    "bonsai_quant_gemv_batched": [_i, _vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp],
+    "bonsai_swiglu_rows": [_vp, _i, _vp, _i, _i, _i, _vp],
     "bonsai_quant_to_f16": [_i, _vp, _vp, _i, _i, _i, _vp],
 }
 _qg_declared = False
@@ -233,6 +235,29 @@ def quant_gemv(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, n
     if out is None:
         out = torch.empty(n, dtype=torch.float32, device=x.device)
     check(_qg().bonsai_quant_gemv(type_id, w.data_ptr(), x.data_ptr(), ptr(norm_w), eps, out.data_ptr(), ptr(residual), n, k, stream()), "quant_gemv")
+    return out
+
+
+def quant_gemv_batched(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
+                       residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """:func:`quant_gemv` for a batch: ``x`` [B, k] f32 (row stride >= k), ``out`` and ``residual`` [B, n] with one common row stride."""
+    assert w.is_cuda and w.dtype == torch.uint8 and x.dim() == 2 and x.dtype == torch.float32 and x.stride(1) == 1
+    B = x.shape[0]
+    if out is None:
+        out = torch.empty((B, n), dtype=torch.float32, device=x.device)
+    assert out.stride(1) == 1 and (residual is None or (residual.stride(1) == 1 and residual.stride(0) == out.stride(0)))
+    check(_qg().bonsai_quant_gemv_batched(type_id, w.data_ptr(), x.data_ptr(), x.stride(0), ptr(norm_w), eps, out.data_ptr(), ptr(residual),
+                                          out.stride(0), n, k, B, stream()), "quant_gemv_batched")
+    return out
+
+
+def swiglu_rows(gu: torch.Tensor, inter: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = silu(gu[t, :inter]) * gu[t, inter:2*inter] for every row of ``gu`` (f32, the output of a fused gate || up projection)."""
+    assert gu.dim() == 2 and gu.dtype == torch.float32 and gu.stride(1) == 1
+    T = gu.shape[0]
+    if out is None:
+        out = torch.empty((T, inter), dtype=torch.float32, device=gu.device)
+    check(_qg().bonsai_swiglu_rows(gu.data_ptr(), gu.stride(0), out.data_ptr(), out.stride(0), inter, T, stream()), "swiglu_rows")
     return out
 
 

@@ -98,7 +98,14 @@ class TokenConstraint:
         return True
 
     def is_complete(self) -> bool:
+        """Whether the output so far is a valid place to stop (a terminal state)."""
         return True
+
+    def finished(self) -> bool:
+        """Whether the generation has to end here: the constraint's language admits no useful continuation.  Engines and
+        the scheduler end a constrained sequence on this, on EOS and on the token limit; an always-terminal constraint
+        (an allow-list, a length window) never asks for the end itself."""
+        return False
 
     def reset(self) -> None:
         pass
@@ -123,7 +130,8 @@ class AllowListConstraint(TokenConstraint):
 
 
 class SequenceConstraint(TokenConstraint):
-    """Forces an exact token sequence, then lets anything through."""
+    """Forces an exact token sequence; the generation ends after its last token (a caller that keeps sampling past it gets
+    every token allowed)."""
     name = "sequence"
 
     def __init__(self, table: TokenTable, sequence: Sequence[int]):
@@ -140,6 +148,9 @@ class SequenceConstraint(TokenConstraint):
         return True
 
     def is_complete(self) -> bool:
+        return self.pos >= len(self.seq)
+
+    def finished(self) -> bool:
         return self.pos >= len(self.seq)
 
     def reset(self) -> None:
@@ -220,6 +231,17 @@ class DfaConstraint(TokenConstraint):
     def is_complete(self) -> bool:
         return self.state >= 0 and bool(self.dfa.accepting[self.state])
 
+    def finished(self) -> bool:
+        """Dead state, or an accepting state that no token other than EOS can leave."""
+        if self.state < 0:
+            return True
+        if not self.dfa.accepting[self.state]:
+            return False
+        mask = self._entry(self.state)[0].copy()
+        if self.eos is not None and 0 <= self.eos < self.table.n:
+            mask[self.eos >> 5] &= ~np.uint32(1 << (self.eos & 31))
+        return not mask.any()
+
     def reset(self) -> None:
         self.state = 0
 
@@ -279,6 +301,10 @@ class GrammarConstraint(TokenConstraint):
     def is_complete(self) -> bool:
         return self.rec.is_complete()
 
+    def finished(self) -> bool:
+        """The first complete sentence ends the generation (a JSON value is returned as soon as it closes)."""
+        return self.rec.is_complete()
+
     def reset(self) -> None:
         self.rec.reset()
         self.text = bytearray()
@@ -314,6 +340,9 @@ class AllOf(TokenConstraint):
 
     def is_complete(self) -> bool:
         return all(c.is_complete() for c in self.cs)
+
+    def finished(self) -> bool:
+        return any(c.finished() for c in self.cs) and self.is_complete()
 
     def reset(self) -> None:
         for c in self.cs:

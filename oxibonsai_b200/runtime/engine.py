@@ -306,7 +306,7 @@ class InferenceEngine:
                 yield tok
                 if masked:
                     constraint.advance(tok)
-                    if constraint.is_complete():
+                    if constraint.finished():
                         break
                     self.set_mask(0, constraint.allowed_mask())
                 if pos >= self.max_seq_len:

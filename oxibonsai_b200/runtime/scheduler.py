@@ -275,7 +275,7 @@ class BatchScheduler:
             r.token_logprobs.append(self.engine.token_logprobs(slot, tok, r.logprobs))
         if r.constraint is not None:
             r.constraint.advance(tok)
-            if r.constraint.is_complete():
+            if r.constraint.finished():
                 r.finish_reason = "stop"
         if r.t_first_token is None:
             r.t_first_token = now

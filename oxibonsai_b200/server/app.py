@@ -165,7 +165,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
     cors = app.state.cors = CorsConfig()
     http_log = RequestLogger()
     started = time.time()
-    sem = asyncio.Semaphore(cfg.max_concurrent)
+    sem = asyncio.Semaphore(cfg.max_concurrent * max(1, getattr(cfg, "replicas", 1)))      # max_concurrent is per engine
 
     def error(status: int, message: str, typ: str = "invalid_request_error", rid: str | None = None):
         r = JSONResponse({"error": {"message": message, "type": typ, "code": status}}, status_code=status)

@@ -261,3 +261,24 @@ def test_simple_constraints_and_intersection():
     s = ConstrainedSampler(AllOf(AllowListConstraint(t, [1]), AllowListConstraint(t, [2])), lambda x: 0, t.n)
     with pytest.raises(ConstraintViolation):
         s.sample(np.zeros(t.n))
+
+
+def test_finished_is_asked_for_by_bounded_constraints_only():
+    """``is_complete`` says a stop is valid, ``finished`` says the generation has to end: engines end a sequence on the
+    latter, so an always-terminal constraint (allow-list, length window) must never report it."""
+    from oxibonsai_b200.runtime.constrained import AllOf, AllowListConstraint, DfaConstraint, LengthConstraint, NoConstraint, SequenceConstraint
+    t = _table()
+    assert not NoConstraint().finished()
+    al = AllowListConstraint(t, [1, 5])
+    assert al.is_complete() and not al.finished() and al.advance(5) and not al.finished()
+    ln = LengthConstraint(t, eos_token=264, min_tokens=0, max_tokens=2)
+    assert ln.is_complete() and not ln.finished()
+    sq = SequenceConstraint(t, [7, 8])
+    assert not sq.finished() and sq.advance(7) and not sq.finished() and sq.advance(8) and sq.finished()
+    # "true" can be followed by ", true": accepting but extendable; "(ab)" has nothing after its match
+    ext = DfaConstraint.from_regex(t, r"(true|false)(, (true|false))*", eos_token=264)
+    assert ext.advance(256) and ext.is_complete() and not ext.finished()
+    end = DfaConstraint.from_regex(t, r"ab", eos_token=264)
+    assert not end.finished() and end.advance(263) and end.is_complete() and end.finished()
+    both = AllOf(AllowListConstraint(t, [7, 8]), SequenceConstraint(t, [7]))
+    assert not both.finished() and both.advance(7) and both.finished()

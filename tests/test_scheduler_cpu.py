@@ -200,6 +200,9 @@ def test_constrained_request_sends_masks_and_ends_when_the_constraint_is_complet
         def is_complete(self):
             return self.i >= len(self.seq)
 
+        def finished(self):
+            return self.i >= len(self.seq)
+
     class Eng(FakeEngine):
         seen_masks = []
 
