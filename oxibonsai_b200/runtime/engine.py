@@ -501,15 +501,16 @@ def layer_weight_type(gguf: GgufFile) -> int:
 
 
 class GenericFormatEngine:
-    """Engine for checkpoints whose layer weights are stored in a block format without a planar repack (Q4_0, Q8_0, FP8,
+    """Engine for checkpoints whose layer weights are in a block format without a planar repack (Q4_0, Q8_0, FP8, the
     K-quants, 256-wide TQ2_0, F16 / BF16 / F32).
 
     Reference counterpart: the same ``InferenceEngine`` serves every format through per-format forward paths
     (crates/oxibonsai-model/src/model/types/forward_cuda/q_std.rs, k_quant.rs, forward_cuda_fp8.rs).  Here the
     sub-2-bit formats have their own runner (``InferenceEngine``) and everything else goes through
-    ``models.qwen3_generic.GenericQwen3Engine``; this class gives it the single-stream part of the engine surface
-    (``generate`` / ``generate_stream`` / ``generate_seeded`` / ``model_info`` / ``last_stats``).  One request at a time:
-    calls are serialised by a lock, as the reference's server does around its engine."""
+    ``models.qwen3_generic.GenericQwen3Engine``; this class gives it the engine surface: ``generate`` / ``generate_stream`` /
+    ``generate_seeded`` / ``model_info`` / ``last_stats`` for one stream (serialised by a lock), and the sequence-slot
+    interface (``begin_sequence`` ... ``step_batch``) through which the continuous-batching scheduler decodes up to
+    ``max_batch`` sequences together."""
 
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
@@ -523,11 +524,13 @@ class GenericFormatEngine:
         t0 = time.perf_counter()
         self.sampling = (sampling or SamplingPreset.BALANCED.params()).validate()
         self._eng = GenericQwen3Engine(str(model_path), max_seq_len=int(max_seq_len), kv_dtype=kv, device=str(device), page_size=page_size,
-                                       sampling=self.sampling)
+                                       sampling=self.sampling, max_batch=int(max_batch))
         self.load_seconds = time.perf_counter() - t0
         self.model_path, self.device = str(model_path), self._eng.device
         self.gguf, self.config = self._eng.gguf, self._eng.config
-        self.max_seq_len, self.max_batch = int(max_seq_len), 1
+        self.max_seq_len, self.max_batch = int(max_seq_len), self._eng.max_batch
+        self.prefill_min_tokens = self._eng.prefill_min_tokens
+        self.exact = False
         self.last_stats = GenerationStats()
         self._lock = threading.Lock()
         if warmup:
@@ -538,38 +541,41 @@ class GenericFormatEngine:
         with self._lock:
             self._eng.generate([0], 1, SamplingPreset.GREEDY.params(), stop_at_eos=False)
 
-    # ---- constrained decoding and log-probabilities -------------------------------------------------
+    # ---- sequence slots (the scheduler's interface; see InferenceEngine for the contract) -----------------------------------------
+    def bind_thread(self) -> None:
+        torch.cuda.set_device(self.device)
+
+    def begin_sequence(self, prompt: Sequence[int], max_total: int, slot: int = 0, params: SamplingParams | None = None,
+                       kv_format: str | None = None) -> int:
+        return self._eng.begin_sequence(prompt, max_total, slot, params or self.sampling, kv_format)
+
+    def prefill(self, prompt: Sequence[int], slot: int = 0, pos0: int = 0) -> None:
+        self._eng.prefill_slot(prompt, slot, pos0)
+
+    def finish_sequence(self, prompt: Sequence[int], slot: int = 0, mask=None) -> int:
+        return self._eng.finish_sequence(prompt, slot, mask)
+
+    def step_batch(self, positions: Sequence[int], masks: dict | None = None) -> list[int]:
+        return self._eng.step_batch(positions, masks)
+
+    def move_slot(self, src: int, dst: int) -> None:
+        self._eng.move_slot(src, dst)
+
+    def close_sequence(self, slot: int = 0) -> None:
+        self._eng.close_sequence(slot)
+
+    def kv_utilization(self) -> float:
+        return self._eng.kv_utilization()
+
     def set_mask(self, slot: int, mask) -> None:
-        """Vocabulary mask of ``slot`` for the masked steps that follow: a packed uint32 array (bit set = token allowed, as
-        ``TokenConstraint.allowed_mask`` returns it), or ``None`` for "every token"."""
-        r = self.runner
-        if mask is None:
-            if slot in self._masked:
-                r.allow_mask[slot].fill_(-1)
-                self._masked.discard(slot)
-            return
-        self._masked.add(slot)
-        import numpy as np
-        m = np.zeros(r.mask_words, dtype=np.uint32)
-        src = np.asarray(mask, dtype=np.uint32)[: r.mask_words]
-        m[: src.size] = src
-        r.allow_mask[slot].copy_(torch.from_numpy(m.view(np.int32)).pin_memory(), non_blocking=True)
+        self._eng.set_mask(slot, mask)
 
     def token_logprobs(self, slot: int, token: int, top_n: int = 0) -> tuple[float, list[tuple[int, float]]]:
-        """Log-probability of ``token`` under the logits that the last step (or prefill) left for ``slot``, and the ``top_n``
-        most likely tokens with theirs (natural log, temperature 1)."""
-        lp = torch.log_softmax(self.runner.logits[slot, : self.config.vocab].float(), dim=-1)
-        top = []
-        if top_n > 0:
-            v, i = torch.topk(lp, min(top_n, lp.numel()))
-            top = list(zip(i.tolist(), v.tolist()))
-        return float(lp[int(token)]), top
+        return self._eng.token_logprobs(slot, token, top_n)
 
+    # ---- one stream ------------------------------------------------------------------------------------------------------------
     def generate_stream(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
                         stop_at_eos: bool = True, on_token: Callable[[int], None] | None = None, constraint=None) -> Iterator[int]:
-        """``constraint``: a :class:`~oxibonsai_b200.runtime.constrained.TokenConstraint`; its vocabulary mask goes to the
-        device before every step and the sampler kernel only picks allowed tokens; generation ends when the constraint is
-        complete (reference: ``ConstrainedSampler``, crates/oxibonsai-runtime/src/constrained_decoding/sampler.rs:19-94)."""
         p = (params or self.sampling).validate()
         max_new = p.max_tokens if max_tokens is None else max_tokens
         prompt = [int(t) for t in prompt]
@@ -581,7 +587,7 @@ class GenericFormatEngine:
         with self._lock:
             t0 = time.perf_counter()
             first = True
-            for tok in self._eng.generate_stream(prompt, max_new, p, stop_at_eos):
+            for tok in self._eng.generate_stream(prompt, max_new, p, stop_at_eos, constraint):
                 now = time.perf_counter()
                 if first:
                     stats.prefill_seconds, t0, first = now - t0, now, False
@@ -593,8 +599,8 @@ class GenericFormatEngine:
             stats.decode_seconds = time.perf_counter() - t0 if not first else 0.0
 
     def generate(self, prompt: Sequence[int], max_tokens: int | None = None, params: SamplingParams | None = None,
-                 stop_at_eos: bool = True) -> list[int]:
-        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos))
+                 stop_at_eos: bool = True, constraint=None) -> list[int]:
+        return list(self.generate_stream(prompt, max_tokens, params, stop_at_eos, constraint=constraint))
 
     def generate_seeded(self, prompt: Sequence[int], max_tokens: int, seed: int, params: SamplingParams | None = None) -> list[int]:
         from dataclasses import replace
@@ -608,7 +614,7 @@ class GenericFormatEngine:
         return {"name": c.name, "arch": c.arch, "layers": c.layers, "hidden": c.hidden, "heads": c.heads, "kv_heads": c.kv_heads,
                 "head_dim": c.head_dim, "intermediate": c.inter, "vocab": c.vocab, "context": c.context, "weight_bytes": int(weight_bytes),
                 "kv_bytes": int(e.kpool.numel() * e.kpool.element_size() * 2), "load_seconds": self.load_seconds,
-                "weight_format": G.type_info(layer_weight_type(self.gguf))[0]}
+                "weight_format": G.type_info(layer_weight_type(self.gguf))[0], "max_batch": self.max_batch}
 
 
 def load_engine(model_path: str, **options):

@@ -71,16 +71,16 @@ def main(argv: list[str] | None = None) -> int:
     if cfg.kv_policy != "off" and hasattr(engine, "enable_kv_formats"):
         from ..runtime.kv_policy import KvCachePolicy
         policy = KvCachePolicy.aggressive() if cfg.kv_policy == "aggressive" else KvCachePolicy()
-    if hasattr(engine, "open_sequence"):          # the sub-2-bit runner: continuous batching over its sequence slots
+    if hasattr(engine, "step_batch"):             # continuous batching over the engine's sequence slots
         for e in engines:
-            if not e.exact:
+            if not e.exact and hasattr(e, "enable_prefix_cache"):
                 e.enable_prefix_cache()
                 if policy is not None:
                     e.enable_kv_formats(("f16", "q8", "q4"))      # the levels of the policy that the engine does not have yet
             scheds.append(BatchScheduler(e, queue_capacity=cfg.queue_capacity, prefill_chunk_tokens=cfg.prefill_chunk_tokens,
                                          kv_policy=policy).start())
         backend = SchedulerBackend(scheds[0], engine.config.name) if len(scheds) == 1 else ReplicaBackend(scheds, engine.config.name)
-    else:                                         # generic block formats: one request at a time
+    else:                                         # an engine without sequence slots: one request at a time
         backend = SerialBackend(engine, engine.config.name)
     app = create_app(backend, tokenizer, cfg, kv_policy=policy)
     print(banner(cfg, engine.model_info()), file=sys.stderr)
