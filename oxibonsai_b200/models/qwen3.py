@@ -469,19 +469,23 @@ class Qwen3Runner:
     def verify_greedy(self, tokens: torch.Tensor, slot: int, pos0: int) -> torch.Tensor:
         """Feeds ``tokens`` (int32 device tensor, at most one prefill chunk) at positions pos0.. and returns the model's
         greedy next token after each of them (int32 [T]) - the batched verification pass of speculative decoding."""
+        return K.sample(self.verify_logits(tokens, slot, pos0))
+
+    def verify_logits(self, tokens: torch.Tensor, slot: int, pos0: int) -> torch.Tensor:
+        """The same pass, returning the logits after each of ``tokens`` (f32 [T, vocab]; the tensor is reused by the next
+        call) for the rejection test of sampled speculative decoding."""
         T = tokens.numel()
         b = self._prefill_buffers(max(64, T))
         with nvtx.range(f"verify[slot={slot},pos={pos0},T={T}]"):
-            return self._verify_greedy(tokens, slot, pos0, T, b)
+            return self._verify_logits(tokens, slot, pos0, T, b)
 
-    def _verify_greedy(self, tokens: torch.Tensor, slot: int, pos0: int, T: int, b: dict) -> torch.Tensor:
+    def _verify_logits(self, tokens: torch.Tensor, slot: int, pos0: int, T: int, b: dict) -> torch.Tensor:
         b["tokens"][:T].copy_(tokens, non_blocking=True)
         torch.arange(pos0, pos0 + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
         K.check(K._pf().bonsai_runner_prefill_chunk(self._native, self._step_ptrs, b["ptrs"], T, pos0, slot, 0, K.stream()), "prefill_chunk")
         xn = K.norm_to_f16_paired(b["h"][:T], self.w.out_norm, self.cfg.eps, natural=True)
         if self.tp is None:
-            logits = K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"])
-            return K.sample(logits)
+            return K.dense_gemm_f16(self.w.lm_head, xn, status=b["status"])
         # vocab-parallel head: every rank computes its slice for the T positions and pushes it into all ranks' logits areas
         if T > self.max_batch:
             raise ValueError(f"tensor-parallel verification of {T} tokens needs max_batch >= {T} (the gathered logits use the batch rows)")
@@ -491,7 +495,7 @@ class Qwen3Runner:
         rows_per_rank = (self.cfg.vocab + self.w.tp_size - 1) // self.w.tp_size
         K.check(_tp._lib().bonsai_tp_allgather_logits(self.tp.handle, local.data_ptr() if rows else None, T, rows, self.w.tp_rank * rows_per_rank,
                                                       self.cfg.vocab, K.stream()), "tp_allgather_logits")
-        return K.sample(self.logits[:T])
+        return self.logits[:T]
 
     def prefill_launches(self, n_tokens: int, chunk: int = 1024) -> int:
         full, tail = divmod(n_tokens, chunk)

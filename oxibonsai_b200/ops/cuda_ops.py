@@ -390,6 +390,36 @@ def sample(logits: torch.Tensor, temps=None, topks=None, topps=None, rng=None, p
     return out
 
 
+_spec_declared = False
+
+
+def spec_verify(target_logits: torch.Tensor, draft_logits: torch.Tensor | None, draft_tokens: torch.Tensor | None, temperature: float,
+                uniforms: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rejection test of k drafted tokens on the device.  ``target_logits`` f32 [k+1, vocab] (row i: the target at the
+    position of draft i; row k: after the last draft), ``draft_logits`` f32 [k, vocab] (the distributions the drafts were
+    drawn from), ``draft_tokens`` int32 [k], ``uniforms`` f32 [2*(k+1)] in [0, 1).  Returns int32 [2]: the number of accepted
+    drafts and the token that follows them (the replacement drawn from max(0, p - q) at the first rejection, or a sample
+    of the last row when all were accepted).  Both distributions are softmax(logits / temperature)."""
+    global _spec_declared
+    l = lib()
+    if not _spec_declared:
+        declare({"bonsai_spec_verify": [_vp, _i, _vp, _i, _vp, _i, _i, _f, _vp, _vp, _vp, _vp]})
+        _spec_declared = True
+    k = target_logits.shape[0] - 1
+    vocab = target_logits.shape[1]
+    assert target_logits.dtype == torch.float32 and target_logits.stride(1) == 1 and uniforms.dtype == torch.float32 and uniforms.numel() >= 2 * (k + 1)
+    if k > 0:
+        assert draft_logits.dtype == torch.float32 and draft_logits.stride(1) == 1 and draft_logits.shape[0] >= k and draft_logits.shape[1] >= vocab
+        assert draft_tokens.dtype == torch.int32 and draft_tokens.numel() >= k
+    if out is None:
+        out = torch.empty(2, dtype=torch.int32, device=target_logits.device)
+    scratch = torch.empty(16 * (k + 1), dtype=torch.uint8, device=target_logits.device)
+    check(l.bonsai_spec_verify(target_logits.data_ptr(), target_logits.stride(0), ptr(draft_logits), draft_logits.stride(0) if k > 0 else 0,
+                               ptr(draft_tokens), k, vocab, float(temperature), uniforms.data_ptr(), scratch.data_ptr(), out.data_ptr(), stream()),
+          "spec_verify")
+    return out
+
+
 # ---- tensor-core decode path ------------------------------------------------------------------------
 _TC_SIG = {
     "bonsai_act_prep_fp8": [_vp, _i, _vp, _f, _i, _i, _i, _i, _vp, _vp, _vp],

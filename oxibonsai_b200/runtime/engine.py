@@ -455,6 +455,20 @@ class InferenceEngine:
         t = torch.tensor([int(x) for x in tokens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
         return self.runner.verify_greedy(t, slot, pos0).tolist()
 
+    def verify_sampled(self, tokens: Sequence[int], pos0: int, draft_logits: torch.Tensor, temperature: float,
+                       uniforms: Sequence[float], slot: int = 0) -> tuple[int, int]:
+        """Rejection test of the drafted tokens ``tokens[1:]`` on the device: ``tokens`` (the last emitted token followed by the
+        drafts) go through the model at positions pos0.. in one batched pass, and the logits of every position are compared
+        with ``draft_logits`` (f32 [k, vocab], the distributions the drafts were drawn from) at ``temperature``.  Returns
+        (number of accepted drafts, the token that follows them); only these two integers come back to the host."""
+        t = torch.tensor([int(x) for x in tokens], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        u = torch.tensor([float(x) for x in uniforms], dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        logits = self.runner.verify_logits(t, slot, pos0)
+        out = K.spec_verify(logits, draft_logits, t[1:], temperature, u)
+        n, nxt = out.tolist()
+        self.runner.check_status()
+        return int(n), int(nxt)
+
     def move_slot(self, src: int, dst: int) -> None:
         """Moves a live sequence to another slot: block-table row, last token, position and sampler state.
         KV pages stay where they are (the block table references them)."""

@@ -187,6 +187,12 @@ class GpuSpeculativeDecoder:
     ``[last, d1..dk]`` in one pass through the prefill kernels, the longest agreeing prefix is kept and the target's
     own token follows it.  Rolling back a rejection costs nothing: the paged caches are indexed by position, so the
     next round simply overwrites the stale entries.  Greedy verification reproduces the target's greedy stream exactly.
+
+    With a ``temperature`` the draft samples its proposals from softmax(logits / T) and the target accepts each with
+    probability min(1, p / q), replacing the first rejected one by a draw from max(0, p - q): the rejection test runs on the
+    device over the logits of both models (csrc/cuda/spec_verify.cu) and the output is distributed as the target's own
+    sampling at that temperature.  Top-k / top-p filters are not applied in this mode (both distributions would need the
+    same support).  On tensor-parallel engines every rank draws the same uniforms from ``seed``.
     """
 
     def __init__(self, target, draft, lookahead: AdaptiveLookahead | None = None, eos_token: int | None = None):
@@ -195,16 +201,26 @@ class GpuSpeculativeDecoder:
         self.eos = eos_token
         self.stats = SpeculativeStats()
 
-    def generate(self, prompt: Sequence[int], max_tokens: int) -> list[int]:
-        from .presets import SamplingPreset
+    def generate(self, prompt: Sequence[int], max_tokens: int, temperature: float | None = None, seed: int = 0) -> list[int]:
+        from .presets import SamplingParams, SamplingPreset
+        import random
+        sampled = temperature is not None and temperature > 1e-6
         greedy = SamplingPreset.GREEDY.params()
+        t_params = SamplingParams(temperature=float(temperature), top_k=0, top_p=1.0, seed=seed) if sampled else greedy
+        d_params = SamplingParams(temperature=float(temperature), top_k=0, top_p=1.0, seed=seed + 1) if sampled else greedy
+        rnd = random.Random(seed)
         total = len(prompt) + max_tokens + self.lookahead.config.max_lookahead + 2
         out: list[int] = []
         import time
+        import torch
+        draft_logits = None
+        if sampled:
+            kmax = self.lookahead.config.max_lookahead
+            draft_logits = torch.empty((kmax, self.draft.config.vocab), dtype=torch.float32, device=self.draft.device)
         t0 = time.perf_counter()
         try:
-            last = self.target.open_sequence(prompt, total, 0, greedy)
-            self.draft.open_sequence(prompt, total, 0, greedy)
+            last = self.target.open_sequence(prompt, total, 0, t_params)
+            self.draft.open_sequence(prompt, total, 0, d_params)
             self.stats.prefill_seconds = time.perf_counter() - t0      # both prompts are in the caches (open_sequence synchronises)
             t0 = time.perf_counter()
             pos = len(prompt)            # position at which `last` will be fed
@@ -223,9 +239,15 @@ class GpuSpeculativeDecoder:
                 for i in range(k):
                     tok = self.draft.decode_one(tok, pos + i)
                     drafts.append(tok)
+                    if sampled:      # the distribution this proposal was drawn from
+                        draft_logits[i].copy_(self.draft.runner.logits[0, : draft_logits.shape[1]], non_blocking=True)
                 draft_pos = pos + k
-                choice = self.target.verify_greedy([last] + drafts, pos)
-                n, nxt = greedy_accept(drafts, choice)
+                if sampled:
+                    n, nxt = self.target.verify_sampled([last] + drafts, pos, draft_logits, float(temperature),
+                                                        [rnd.random() for _ in range(2 * (k + 1))])
+                else:
+                    choice = self.target.verify_greedy([last] + drafts, pos)
+                    n, nxt = greedy_accept(drafts, choice)
                 self.stats.steps += 1
                 self.stats.target_passes += 1
                 self.stats.drafted += k

@@ -78,6 +78,71 @@ def test_gpu_speculative_decoding_reproduces_greedy_stream(tiny_gguf, tiny_q1_gg
     assert dec2.stats.acceptance_rate < 0.5
 
 
+def _spec_verify_reference(target, draft, tokens, temperature, uniforms):
+    """fp32 PyTorch statement of the rejection test: returns (accepted, next token, cdf margin of the drawn token)."""
+    import torch
+    k = tokens.numel()
+    p = torch.softmax(target.double() / temperature, dim=-1)
+    q = torch.softmax(draft.double() / temperature, dim=-1) if k else None
+    n = 0
+    while n < k:
+        d = int(tokens[n])
+        if uniforms[2 * n] <= min(1.0, float(p[n, d] / q[n, d])):
+            n += 1
+        else:
+            break
+    res = torch.clamp(p[n] - q[n], min=0.0) if n < k else p[n]
+    cdf = torch.cumsum(res, 0)
+    want = uniforms[2 * n + 1] * float(cdf[-1])
+    tok = int(torch.searchsorted(cdf, torch.tensor(want, dtype=cdf.dtype)).clamp(max=res.numel() - 1))
+    return n, tok, cdf, want
+
+
+@pytest.mark.parametrize("k", [0, 1, 4, 8])
+def test_spec_verify_kernel_matches_fp32_reference(k):
+    import torch
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = torch.device("cuda:0")
+    vocab = 5003
+    g = torch.Generator().manual_seed(100 + k)
+    for trial in range(6):
+        target = torch.randn(k + 1, vocab, generator=g) * 3.0
+        # a draft close to the target so that some proposals are accepted and some are not
+        draft = target[:k] + torch.randn(k, vocab, generator=g) * (0.3 + 0.5 * trial)
+        temperature = 0.8
+        q = torch.softmax(draft / temperature, dim=-1)
+        toks = torch.multinomial(q, 1, generator=g).view(-1).to(torch.int32) if k else torch.zeros(0, dtype=torch.int32)
+        u = torch.rand(2 * (k + 1), generator=g)
+        out = K.spec_verify(target.to(dev), draft.to(dev) if k else None, toks.to(dev) if k else None, temperature, u.to(dev)).tolist()
+        n, tok, cdf, want = _spec_verify_reference(target, draft, toks, temperature, u.tolist())
+        # a uniform that falls within float rounding of an acceptance threshold or a CDF step may legitimately go either way
+        p = torch.softmax(target.double() / temperature, dim=-1)
+        near = any(abs(float(u[2 * i]) - min(1.0, float(p[i, int(toks[i])] / q.double()[i, int(toks[i])]))) < 1e-4 for i in range(k))
+        if out[0] != n:
+            assert near, (k, trial, out, n)
+            continue
+        if out[1] != tok:
+            lo = float(cdf[out[1] - 1]) if out[1] > 0 else 0.0
+            assert lo - 1e-5 <= want <= float(cdf[out[1]]) + 1e-5, (k, trial, out, tok)
+
+
+def test_gpu_speculative_sampling_accepts_everything_from_an_identical_draft(tiny_gguf, tiny_q1_gguf):
+    from oxibonsai_b200.runtime.speculative import GpuSpeculativeDecoder
+    prompt = list(range(5, 30))
+    target, twin, other = _engine(tiny_gguf, kv="f16"), _engine(tiny_gguf, kv="f16"), _engine(tiny_q1_gguf, kv="f16")
+    vocab = target.config.vocab
+    dec = GpuSpeculativeDecoder(target, twin)
+    got = dec.generate(prompt, 24, temperature=0.9, seed=5)
+    assert len(got) == 24 and all(0 <= t < vocab for t in got)
+    # p and q differ only by the numerics of the prompt kernels against the decode kernels: nearly every proposal passes
+    assert dec.stats.acceptance_rate > 0.8 and dec.stats.tokens_per_target_pass > 2.0
+    assert dec.generate(prompt, 24, temperature=0.9, seed=5) == got          # same seed, same stream
+    dec2 = GpuSpeculativeDecoder(target, other)
+    got2 = dec2.generate(prompt, 24, temperature=0.9, seed=5)
+    assert len(got2) == 24 and all(0 <= t < vocab for t in got2)
+    assert dec2.stats.acceptance_rate < dec.stats.acceptance_rate
+
+
 def test_http_server_end_to_end_on_device(tiny_gguf):
     from fastapi.testclient import TestClient
     from oxibonsai_b200.runtime.scheduler import BatchScheduler
