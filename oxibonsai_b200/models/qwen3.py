@@ -535,13 +535,7 @@ class Qwen3Runner:
             if batch >= 2 and self.fast:
                 self._prefill_buffers(max(64, batch))   # allocate outside the capture
             # capture without running: the capture itself executes nothing, so state is untouched
-            s = torch.cuda.Stream(device=self.device)
-            s.wait_stream(torch.cuda.current_stream(self.device))
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(s):
-                with torch.cuda.graph(g, stream=s):
-                    self.step_eager(batch, sample, masked=masked)
-            torch.cuda.current_stream(self.device).wait_stream(s)
+            g = K.capture_graph(self.device, lambda: self.step_eager(batch, sample, masked=masked))
             self._graphs[key] = g
         mark = nvtx.push(f"decode_step[batch={batch}]")
         g.replay()

@@ -269,13 +269,7 @@ class GenericQwen3Engine:
                 self.pos[:1].copy_(pos0)
                 self.rng[:1].copy_(rng0)
                 torch.cuda.synchronize(self.device)
-            s = torch.cuda.Stream(device=self.device)
-            s.wait_stream(torch.cuda.current_stream(self.device))
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(s):
-                with torch.cuda.graph(g, stream=s):
-                    self._forward(0, batch, True, masked)
-            torch.cuda.current_stream(self.device).wait_stream(s)
+            g = K.capture_graph(self.device, lambda: self._forward(0, batch, True, masked))
             self._graphs[key] = g
         g.replay()
 

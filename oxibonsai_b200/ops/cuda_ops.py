@@ -390,6 +390,24 @@ def sample(logits: torch.Tensor, temps=None, topks=None, topps=None, rng=None, p
     return out
 
 
+_capture_lock = __import__("threading").Lock()
+
+
+def capture_graph(device, fn) -> "torch.cuda.CUDAGraph":
+    """Captures the launches of ``fn()`` on a side stream into a CUDA graph.  One capture at a time per process, and in
+    thread-local capture mode: engines of several GPUs live in one process (replica serving), and another engine's thread
+    must be free to allocate, copy and synchronise while this one records."""
+    with _capture_lock:
+        s = torch.cuda.Stream(device=device)
+        s.wait_stream(torch.cuda.current_stream(device))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
+                fn()
+        torch.cuda.current_stream(device).wait_stream(s)
+    return g
+
+
 _spec_declared = False
 
 

@@ -68,12 +68,6 @@ class NcclTpDecoder:
             self.r.positions[:1].sub_(1)           # ... and take the step back: the replay below redoes it
             self.r.tokens[:1].copy_(tok0)
             torch.cuda.synchronize(self.r.device)
-            s = torch.cuda.Stream(device=self.r.device)
-            s.wait_stream(torch.cuda.current_stream(self.r.device))
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(s):
-                with torch.cuda.graph(g, stream=s):
-                    self.step_eager()
-            torch.cuda.current_stream(self.r.device).wait_stream(s)
+            g = K.capture_graph(self.r.device, self.step_eager)
             self._graph = g
         self._graph.replay()

@@ -137,6 +137,9 @@ class SerialBackend:
         return 0.0
 
 
+_END = object()      # queue sentinel: the request is done (or timed out)
+
+
 def new_request_id() -> str:
     return uuid.uuid4().hex
 
@@ -302,19 +305,21 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             delta, sent = text[sent:safe], safe
             return delta, False
 
+        # the end of the request arrives through the same queue as its tokens (after them: both are queued on the loop in
+        # order), so the hot loop is one ``await q.get()`` per wake-up and drains whatever else is already there
+        waiter.add_done_callback(lambda _f: q.put_nowait(_END))
         try:
             while True:
-                get = asyncio.ensure_future(q.get())
-                done, _ = await asyncio.wait({get, waiter}, return_when=asyncio.FIRST_COMPLETED)
-                if get in done:
-                    toks = [get.result()]
-                    finished = False
-                else:
-                    get.cancel()
-                    toks = []
-                    while not q.empty():
-                        toks.append(q.get_nowait())
-                    finished = True
+                item = await q.get()
+                toks, finished = [], False
+                while True:
+                    if item is _END:
+                        finished = True
+                        break
+                    toks.append(item)
+                    if q.empty():
+                        break
+                    item = q.get_nowait()
                 for tok in toks:
                     tracker.on_token()
                     n_tok += 1
@@ -457,15 +462,17 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                             first = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model,
                                      "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
                             yield f"data: {json.dumps(first)}\n\n"
+                        # the fixed part of every chunk is serialised once; per token only the text is encoded
+                        head_json = (f'data: {{"id": {json.dumps(obj_id)}, "object": "{"chat.completion.chunk" if chat else "text_completion"}", '
+                                     f'"created": {created}, "model": {json.dumps(model)}, "choices": [{{"index": 0, ')
                         async for delta, fin in run_generation(prompt_ids, params, max_tokens, rid, stops, extras()):
+                            if not (delta or fin):
+                                continue
                             if chat:
-                                ch = {"index": 0, "delta": ({"content": delta} if delta else {}), "finish_reason": fin}
-                                chunk = {"id": obj_id, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [ch]}
+                                body_json = f'"delta": {{"content": {json.dumps(delta)}}}' if delta else '"delta": {}'
                             else:
-                                chunk = {"id": obj_id, "object": "text_completion", "created": created, "model": model,
-                                         "choices": [{"index": 0, "text": delta, "finish_reason": fin}]}
-                            if delta or fin:
-                                yield f"data: {json.dumps(chunk)}\n\n"
+                                body_json = f'"text": {json.dumps(delta)}'
+                            yield f'{head_json}{body_json}, "finish_reason": {json.dumps(fin)}}}]}}\n\n'
                         yield "data: [DONE]\n\n"
                 except Exception as e:  # noqa: BLE001
                     metrics.errors.inc()
