@@ -36,7 +36,12 @@ __global__ void tp_push_logits_kernel(TpComm c, const float* __restrict__ local,
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int b = slot0 + (int)(i / rows), r = (int)(i % rows);
     const float v = local[i];
-    for (int p = 0; p < c.size; ++p) reinterpret_cast<float*>(c.peer[p] + c.lay.off_logits)[(size_t)b * vocab + row0 + r] = v;
+    const size_t at = (size_t)b * vocab + row0 + r;
+    if (c.mc != nullptr) {
+      tp_mc_st_f32(reinterpret_cast<float*>(c.mc + c.lay.off_logits) + at, v);
+    } else {
+      for (int p = 0; p < c.size; ++p) reinterpret_cast<float*>(c.peer[p] + c.lay.off_logits)[at] = v;
+    }
   }
 }
 
@@ -47,6 +52,11 @@ __global__ void tp_reduce_broadcast_kernel(TpComm c, size_t n) {
   const size_t per = (n / 4 + c.size - 1) / c.size;   // float4 units per rank
   const size_t lo = (size_t)c.rank * per, hi = min(n / 4, lo + per);
   for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
+    if (c.mc != nullptr) {   // the switch adds the ranks' values and replicates the result
+      float4* at = reinterpret_cast<float4*>(c.mc + c.lay.off_big) + i;
+      tp_mc_st_f4(at, tp_mc_ld_reduce_f4(at));
+      continue;
+    }
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < c.size; ++p) {
       const float4 v = __ldcg(reinterpret_cast<const float4*>(c.peer[p] + c.lay.off_big) + i);
@@ -79,9 +89,14 @@ __global__ void tp_allreduce_oneshot_add_kernel(TpComm c, float* __restrict__ h,
   float4* h4 = reinterpret_cast<float4*>(h);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
     float4 s = h4[i];
-    for (int p = 0; p < c.size; ++p) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(c.peer[p] + c.lay.off_big) + off4 + i);
+    if (c.mc != nullptr) {
+      const float4 v = tp_mc_ld_reduce_f4(reinterpret_cast<const float4*>(c.mc + c.lay.off_big) + off4 + i);
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    } else {
+      for (int p = 0; p < c.size; ++p) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(c.peer[p] + c.lay.off_big) + off4 + i);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
     }
     h4[i] = s;
   }
@@ -217,6 +232,12 @@ int bonsai_tp_allreduce_oneshot_add(void* comm, float* h, size_t n, int half, cu
   tp_allreduce_oneshot_add_kernel<<<grid, 256, 0, stream>>>(c, h, n / 4, (size_t)half * half_elems / 4);
   return launch_status();
 }
+// Multicast mapping of the symmetric buffer (0 = none): switches the stores of the fused epilogues and of the logits
+// gather to multimem.st and the sums of the all-reduce kernels to multimem.ld_reduce.
+void bonsai_tp_set_multicast(void* comm, uint64_t mc_ptr) {
+  static_cast<bonsai::TpComm*>(comm)->mc = reinterpret_cast<uint8_t*>(mc_ptr);
+}
+int bonsai_tp_has_multicast(void* comm) { return static_cast<bonsai::TpComm*>(comm)->mc != nullptr ? 1 : 0; }
 void* bonsai_tp_big_half_ptr(void* comm, int half) {
   bonsai::TpComm& c = *static_cast<bonsai::TpComm*>(comm);
   const size_t half_elems = (c.lay.big_elems / 2) & ~(size_t)3;

@@ -49,6 +49,10 @@ struct TpComm {
   int* bar_epoch;  // device int: number of flag barriers completed
   int* status;     // device int: non-zero after a bounded wait expired
   uint32_t spin_limit;   // polls before a wait on a peer gives up (host-settable; tests use a small value)
+  // Multicast mapping of the symmetric buffer (same layout; null when the fabric offers none or the path is switched
+  // off): a multimem store through it lands in every rank's buffer, a multimem load-reduce returns the sum over all
+  // ranks' buffers, both done by the NVLink switch.
+  uint8_t* mc;
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -83,6 +87,29 @@ __device__ __forceinline__ unsigned long long* tp_ll_big_slot(const TpComm& c, i
 }
 __device__ __forceinline__ void tp_st_msg(unsigned long long* p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// One {value, tag} message to the same slot of every rank's buffer (mc_slot: the slot's address in the multicast mapping).
+__device__ __forceinline__ void tp_mc_st_msg(unsigned long long* mc_slot, unsigned long long v) {
+  asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(mc_slot), "l"(v) : "memory");
+}
+__device__ __forceinline__ void tp_mc_st_f32(float* mc_p, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void tp_mc_st_f4(float4* mc_p, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// Sum over all ranks of the float4 at this offset of their buffers, added inside the switch.
+__device__ __forceinline__ float4 tp_mc_ld_reduce_f4(const float4* mc_p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc_p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long* tp_ll_slot_mc(const TpComm& c, int parity, int from_rank) {
+  return reinterpret_cast<unsigned long long*>(c.mc + c.lay.off_ll) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.recv_elems;
+}
+__device__ __forceinline__ unsigned long long* tp_ll_big_slot_mc(const TpComm& c, int parity, int from_rank) {
+  return reinterpret_cast<unsigned long long*>(c.mc + c.lay.off_ll_big) + ((size_t)parity * kTpMaxRanks + from_rank) * c.lay.ll_big_elems;
 }
 __device__ __forceinline__ unsigned long long tp_ld_msg(const unsigned long long* p) {
   unsigned long long v;

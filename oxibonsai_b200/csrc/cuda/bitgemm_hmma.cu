@@ -191,11 +191,17 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p,
         if (tok >= p.T) continue;
         const size_t i_lo = (size_t)tok * p.n_rows + r_lo, i_hi = (size_t)tok * p.n_rows + r_hi;
         const unsigned long long m_lo = tag_hi | __float_as_uint(tot[nt][e] * 128.0f), m_hi = tag_hi | __float_as_uint(tot[nt][2 + e] * 128.0f);
-        for (int q = 0; q < tp.size; ++q) {
-          if (q == tp.rank) continue;
-          unsigned long long* dst = tp_ll_big_slot(tp, q, parity, tp.rank);
-          if (ok_lo) tp_st_msg(dst + i_lo, m_lo);
-          if (ok_hi) tp_st_msg(dst + i_hi, m_hi);
+        if (tp.mc != nullptr) {   // one multicast store per message: the switch replicates it into every rank's slot
+          unsigned long long* dst = tp_ll_big_slot_mc(tp, parity, tp.rank);
+          if (ok_lo) tp_mc_st_msg(dst + i_lo, m_lo);
+          if (ok_hi) tp_mc_st_msg(dst + i_hi, m_hi);
+        } else {
+          for (int q = 0; q < tp.size; ++q) {
+            if (q == tp.rank) continue;
+            unsigned long long* dst = tp_ll_big_slot(tp, q, parity, tp.rank);
+            if (ok_lo) tp_st_msg(dst + i_lo, m_lo);
+            if (ok_hi) tp_st_msg(dst + i_hi, m_hi);
+          }
         }
       }
   }

@@ -437,8 +437,12 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
       const uint32_t tag = (uint32_t)tp_epoch + 1u;
       const int parity = tp_epoch & 1;
       const unsigned long long msg = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
-      for (int p = 0; p < tp.size; ++p)
-        if (p != tp.rank) tp_st_msg(tp_ll_slot(tp, p, parity, tp.rank) + row, msg);
+      if (tp.mc != nullptr) {   // one multicast store: the switch replicates it into every rank's slot
+        tp_mc_st_msg(tp_ll_slot_mc(tp, parity, tp.rank) + row, msg);
+      } else {
+        for (int p = 0; p < tp.size; ++p)
+          if (p != tp.rank) tp_st_msg(tp_ll_slot(tp, p, parity, tp.rank) + row, msg);
+      }
       float sum = a.residual != nullptr ? a.residual[row] : 0.0f;
       bool alive = true;
       for (int s = 0; s < tp.size; ++s) sum += s == tp.rank ? v : tp_recv_msg(tp, tp_ll_slot(tp, tp.rank, parity, s) + row, tag, alive);

@@ -4,9 +4,12 @@ The reference's tensor parallelism is a CPU simulation (``ShardedLinear``, ``ten
 ``NcclCollectives``; crates/oxibonsai-model/src/tensor_parallel.rs:20-468, multi_gpu.rs:31-320).  Here one process
 per GPU joins a ``torch.distributed`` NCCL group (bootstrap, barriers), allocates one symmetric buffer with
 ``torch.distributed._symmetric_memory`` and hands the peer addresses to the CUDA kernels of ``csrc/comm``,
-which move data with ordinary loads/stores to peer memory (never TMA, never a library kernel on a peer pointer).
+which move data with ordinary loads/stores to peer memory, or with multimem stores and load-reduces through the NVLink
+switch where the buffer has a multicast mapping (never TMA, never a library kernel on a peer pointer).
 """
 from __future__ import annotations
+
+import os
 
 import ctypes as C
 from dataclasses import dataclass
@@ -24,12 +27,13 @@ _SIG = {
     "bonsai_tp_destroy": [_vp],
     "bonsai_tp_barrier": [_vp, _vp],
     "bonsai_tp_allgather_logits": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "bonsai_tp_set_multicast": [_vp, C.c_uint64],
     "bonsai_tp_logits_ptr": [_vp],
     "bonsai_tp_big_ptr": [_vp],
     "bonsai_tp_allreduce_big_add": [_vp, _vp, _sz, _vp],
     "bonsai_bitgemv_tp": [_vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _i, _i, _i, _vp],
 }
-_RES = {"bonsai_tp_layout": _sz, "bonsai_tp_create": _vp, "bonsai_tp_destroy": None, "bonsai_tp_set_spin_limit": None,
+_RES = {"bonsai_tp_layout": _sz, "bonsai_tp_create": _vp, "bonsai_tp_destroy": None, "bonsai_tp_set_spin_limit": None, "bonsai_tp_set_multicast": None,
         "bonsai_tp_set_status_ptr": None, "bonsai_tp_logits_ptr": _vp, "bonsai_tp_big_ptr": _vp}
 _declared = False
 
@@ -99,6 +103,21 @@ class TpGroup:
         self.logits = self.buffer[lo: lo + self.logits_elems * 4].view(torch.float32).view(max_batch, vocab)
         bo = int(offs[4])
         self.big = self.buffer[bo: bo + self.big_elems * 4].view(torch.float32)
+        # NVLink-switch multicast (multimem.st / multimem.ld_reduce) when the fabric maps the buffer that way;
+        # OXIBONSAI_TP_MULTIMEM=0 keeps every exchange on plain peer loads and stores
+        self.multicast = False
+        mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+        if mc and os.environ.get("OXIBONSAI_TP_MULTIMEM", "1") != "0":
+            self.set_multicast(True)
+
+    def set_multicast(self, on: bool) -> bool:
+        """Switches the exchanges between multimem instructions and plain peer accesses; returns whether multicast is on
+        afterwards (it stays off where the symmetric buffer has no multicast mapping).  Collective: every rank must make the
+        same choice before the next step."""
+        mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0) if self._hdl is not None else 0
+        self.multicast = bool(on and mc)
+        _lib().bonsai_tp_set_multicast(self.handle, mc if self.multicast else 0)
+        return self.multicast
 
     @classmethod
     def loopback(cls, device, size: int = 2, hidden: int = 4096, vocab: int = 1024, max_batch: int = 1, big_elems: int = 4096,
@@ -114,6 +133,7 @@ class TpGroup:
         total = lib.bonsai_tp_layout(self.recv_elems, self.logits_elems, self.big_elems, offs)
         self._peers = [torch.zeros(total, dtype=torch.uint8, device=device) for _ in range(size)]
         self.buffer, self._hdl = self._peers[rank], None
+        self.multicast = False
         self.state = torch.zeros(4, dtype=torch.int32, device=device)
         arr = (C.c_uint64 * size)(*[t.data_ptr() for t in self._peers])
         self.handle = lib.bonsai_tp_create(rank, size, arr, self.recv_elems, self.logits_elems, self.big_elems, self.state.data_ptr())

@@ -26,7 +26,7 @@ def _run(path, mode, nproc, out_dir):
     return res
 
 
-@pytest.mark.parametrize("mode", ["exact", "fast", "batched", "speculative"])
+@pytest.mark.parametrize("mode", ["exact", "fast", "batched", "speculative", "multimem"])
 def test_tensor_parallel_two_gpus(mode, tiny_gguf, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

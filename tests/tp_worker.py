@@ -64,6 +64,50 @@ def main():
         got = dec.generate(prompt, 20)
         out.update(ok=(got[:len(want)] == want[:len(got)] and len(got) >= len(want) - 1 and dec.stats.acceptance_rate > 0.9),
                    got=got, want=want, acceptance=dec.stats.acceptance_rate, status=target.runner.tp.status() | draft.runner.tp.status())
+    elif mode == "multimem":
+        # the exchanges through the NVLink switch (multimem.st / multimem.ld_reduce) against the plain peer accesses and
+        # against NCCL; reported as skipped where the symmetric buffer has no multicast mapping
+        import ctypes as C
+        from oxibonsai_b200.ops import cuda_ops as K
+        from oxibonsai_b200.parallel import tp as TP
+        eng = (EngineBuilder().model_path(path).preset("greedy").max_seq_len(256).max_batch(4).kv_cache("f16").device(f"cuda:{local}")
+               .tensor_parallel(rank, world).build())
+        tp = eng.runner.tp
+        if not tp.multicast:
+            out.update(ok=True, skipped="no multicast mapping on this fabric", status=tp.status())
+        else:
+            lib = TP._lib()
+            K.declare({"bonsai_tp_allreduce_oneshot_add": [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p],
+                       "bonsai_tp_big_half_ptr": [C.c_void_p, C.c_int]}, {"bonsai_tp_big_half_ptr": C.c_void_p})
+            dev = torch.device("cuda", local)
+            n = 4096 * 6
+            g = torch.Generator(device=dev).manual_seed(100 + rank)
+            checks = {}
+            for mc in (True, False):
+                tp.set_multicast(mc)
+                for half in (0, 1):
+                    part = torch.randn(n, device=dev, generator=g)
+                    base = lib.bonsai_tp_big_half_ptr(tp.handle, half) - tp.big.data_ptr()
+                    tp.big[base // 4: base // 4 + n].copy_(part)
+                    h = torch.full((n,), 0.5, device=dev)
+                    K.check(lib.bonsai_tp_allreduce_oneshot_add(tp.handle, h.data_ptr(), n, half, K.stream()), "oneshot")
+                    ref = part.clone()
+                    dist.all_reduce(ref)
+                    checks[f"oneshot mc={mc} half={half}"] = bool(torch.allclose(h, ref + 0.5, rtol=1e-5, atol=1e-5))
+                part = torch.randn(n, device=dev, generator=g)
+                tp.big[:n].copy_(part)
+                h = torch.zeros(n, device=dev)
+                K.check(lib.bonsai_tp_allreduce_big_add(tp.handle, h.data_ptr(), n, K.stream()), "twoshot")
+                ref = part.clone()
+                dist.all_reduce(ref)
+                checks[f"twoshot mc={mc}"] = bool(torch.allclose(h, ref, rtol=1e-5, atol=1e-5))
+            long_prompt = torch.randint(0, 1000, (90,), generator=torch.Generator().manual_seed(5)).tolist()
+            tp.set_multicast(True)
+            a = eng.generate(long_prompt, 8)         # prompt: two-shot all-reduce through the switch; decode: multicast {value, tag} stores
+            tp.set_multicast(False)
+            b = eng.generate(long_prompt, 8)
+            out.update(ok=all(checks.values()) and len(a) == 8 and sum(x == y for x, y in zip(a, b)) >= 6, checks=checks, a=a, b=b,
+                       status=tp.status())
     dist.barrier()
     with open(os.path.join(out_dir, f"rank{rank}.json"), "w") as f:
         json.dump(out, f)
