@@ -296,6 +296,9 @@ class Qwen3Runner:
         output, 2 gate/up, 3 down); the others stay on the planar-layout kernels."""
         self.streamed_gemv_mask = streamed_gemv_mask
         self.w, self.kv, self.max_batch, self.max_seq = weights, kv, max_batch, max_seq
+        # rows of the prompt / decode-batch activation buffers: allocated once at this size, because the captured decode
+        # graphs hold their addresses (a later, larger allocation would leave those graphs pointing at freed memory)
+        self.prefill_capacity = max(int(prefill_chunk), 64, int(max_batch))
         cfg, dev = weights.cfg, weights.device
         self.cfg, self.device = cfg, dev
         hd = cfg.head_dim
@@ -424,8 +427,13 @@ class Qwen3Runner:
 
     # ---- prefill (tcgen05 GEMMs + causal paged attention over a chunk of prompt tokens) ----
     def _prefill_buffers(self, chunk: int):
-        if getattr(self, "_pf", None) is not None and self._pf["chunk"] >= chunk:
+        """The activation buffers of the prompt path and of batched decode steps (``chunk``: rows the caller needs).  One
+        allocation for the runner's lifetime, ``prefill_capacity`` rows: the addresses are part of every captured graph."""
+        if chunk > self.prefill_capacity:
+            raise ValueError(f"{chunk} rows exceed the runner's activation buffers ({self.prefill_capacity} rows)")
+        if getattr(self, "_pf", None) is not None:
             return self._pf
+        chunk = self.prefill_capacity
         cfg, w, dev = self.cfg, self.w, self.device
         hd, nq, nkv = cfg.head_dim, w.heads_local, w.kv_heads_local
         qd = nq * hd
@@ -452,11 +460,12 @@ class Qwen3Runner:
         """Runs prompt ``tokens`` (int32 device tensor) of the sequence in ``slot`` starting at position ``pos0``;
         leaves the logits of the last token in ``self.logits[slot]``."""
         n = tokens.numel()
+        chunk = max(1, min(chunk, self.prefill_capacity))
         b = self._prefill_buffers(min(chunk, max(n, 1)))
         lib = K._pf()
         done = 0
         while done < n:
-            T = min(b["chunk"], n - done)
+            T = min(chunk, n - done)
             b["tokens"][:T].copy_(tokens[done:done + T], non_blocking=True)
             torch.arange(pos0 + done, pos0 + done + T, dtype=torch.int32, device=self.device, out=b["positions"][:T])
             last = done + T == n

@@ -209,6 +209,10 @@ class GpuSpeculativeDecoder:
         t_params = SamplingParams(temperature=float(temperature), top_k=0, top_p=1.0, seed=seed) if sampled else greedy
         d_params = SamplingParams(temperature=float(temperature), top_k=0, top_p=1.0, seed=seed + 1) if sampled else greedy
         rnd = random.Random(seed)
+        # every call starts from the same decoder state: the draft length adapts within a generation, and ``stats``
+        # describes the last one
+        self.lookahead.reset()
+        self.stats = SpeculativeStats()
         total = len(prompt) + max_tokens + self.lookahead.config.max_lookahead + 2
         out: list[int] = []
         import time
