@@ -346,7 +346,8 @@ def main() -> None:
         b = b.tensor_parallel(rank, world)
     eng = b.build()
     bytes_step = eng.weights.packed_bytes
-    print(f"[bench] rank {rank}: engine (tp{world}) ready in {time.time() - t0:.1f}s; packed bytes/step/GPU {bytes_step / 1e9:.3f} GB", file=sys.stderr)
+    print(f"[bench] rank {rank}: engine (tp{world}) ready in {time.time() - t0:.1f}s; packed bytes/step/GPU {bytes_step / 1e9:.3f} GB; "
+          f"switch multicast {getattr(getattr(eng.runner, 'tp', None), 'multicast', None)}", file=sys.stderr)
     # rank 0 samples the clocks of every GPU of the job (one nvidia-smi for the node), the other ranks none
     m = measure(eng, args, cfg, prompt, S, barrier, dev, torch.Generator().manual_seed(7), e2e=True, sched_e2e=(world == 1),
                 clocks_gpu=(0 if world == 1 else -1) if rank == 0 else None)
@@ -371,7 +372,8 @@ def main() -> None:
         "data": "synthetic (seeded random-init GGUF, random prompt tokens)",
         "config": {"model": cfg.name, "global_batch": 1, "seq_len": prompt_len, "decode_tokens": args.steps, "kv_cache": args.kv,
                    "parallelism": "single GPU" if world == 1 else f"tp{world} (one stream over all GPUs; fused GEMV->all-reduce epilogues over NVLink peer memory)",
-                   "l2": "inputs larger than L2 (each step streams the packed weights + LM head)", "weights_bytes_per_step_per_gpu": bytes_step},
+                   "l2": "inputs larger than L2 (each step streams the packed weights + LM head)", "weights_bytes_per_step_per_gpu": bytes_step,
+                   "nvlink_switch_multicast": bool(world > 1 and getattr(eng.runner.tp, "multicast", False))},
         "clocks": m["clocks"],
         "e2e": {"value": None if e2e_value is None else round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 8 * world,
                 "d2h_bytes_per_step": 8 * world, "ttft_s": round(ttft, 3)},

@@ -320,22 +320,25 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                     if q.empty():
                         break
                     item = q.get_nowait()
+                # tokens that piled up while this coroutine waited for its turn go out as one delta: under load the number of
+                # SSE events per stream falls instead of the event loop falling further behind
+                piece = ""
                 for tok in toks:
                     tracker.on_token()
                     n_tok += 1
                     if first:
                         metrics.prefill_seconds.observe(time.perf_counter() - t0)
                         first = False
-                    piece = dec.push(tokenizer.token_bytes(tok))
-                    if piece:
-                        delta, hit = feed(piece)
-                        if delta:
-                            yield delta, None
-                        if hit:
-                            req.cancel()
-                            completed = True
-                            yield "", "stop"
-                            return
+                    piece += dec.push(tokenizer.token_bytes(tok))
+                if piece:
+                    delta, hit = feed(piece)
+                    if delta:
+                        yield delta, None
+                    if hit:
+                        req.cancel()
+                        completed = True
+                        yield "", "stop"
+                        return
                 if finished:
                     if not waiter.result():
                         req.cancel()
