@@ -5,8 +5,8 @@ per GPU, only rank 0 runs the HTTP front and the continuous-batching scheduler; 
 open a sequence, prefill a prompt chunk, take a decode step of B sequences, move or close a slot - is broadcast as a small
 command before rank 0 executes it, and every other rank executes the same call on its own engine.  All ranks hold the same
 host-side state (page tables, prefix cache, sampler seeds) because they apply the same commands in the same order, so the
-tensor-parallel kernels of a step always meet their peers.  Commands travel over a CPU (gloo) process group as pickled
-tuples; a decode step costs one broadcast of the live positions.
+tensor-parallel kernels of a step always meet their peers.  Commands travel over a CPU (gloo) process group; a decode
+step costs one broadcast of a small tensor holding the live positions, other commands follow as pickled tuples.
 """
 from __future__ import annotations
 
@@ -18,18 +18,40 @@ SHUTDOWN = "__shutdown__"
 
 
 class CommandChannel:
-    """Broadcast of (op, args) tuples from rank ``src`` over a ``torch.distributed`` group (gloo: CPU objects)."""
+    """Broadcast of (op, args) from rank ``src`` over a ``torch.distributed`` group (gloo: CPU tensors and objects).
+
+    Every command starts with one broadcast of a fixed int64 header.  The hot command - a decode step without vocabulary
+    masks - travels inside it (``[STEP, B, positions...]``), so a step costs one small tensor broadcast and no pickling;
+    any other command announces itself as ``OBJECT`` and follows as a pickled tuple."""
+
+    OBJECT, STEP = 0, 1
+    MAX_INLINE = 1022            # positions that fit into the header
 
     def __init__(self, group=None, src: int = 0):
+        import torch
         import torch.distributed as dist
-        self._dist, self.group, self.src = dist, group, src
+        self._torch, self._dist, self.group, self.src = torch, dist, group, src
         self.rank = dist.get_rank()
+        self._hdr = torch.zeros(self.MAX_INLINE + 2, dtype=torch.int64)
 
     def send(self, op: str, args: tuple = ()) -> None:
         assert self.rank == self.src
+        h = self._hdr
+        if op == "step_batch" and len(args) == 1 and len(args[0]) <= self.MAX_INLINE:
+            pos = args[0]
+            h[0], h[1] = self.STEP, len(pos)
+            h[2:2 + len(pos)] = self._torch.as_tensor(list(pos), dtype=self._torch.int64)
+            self._dist.broadcast(h, src=self.src, group=self.group)
+            return
+        h[0] = self.OBJECT
+        self._dist.broadcast(h, src=self.src, group=self.group)
         self._dist.broadcast_object_list([(op, tuple(args))], src=self.src, group=self.group)
 
     def recv(self) -> tuple[str, tuple]:
+        h = self._hdr
+        self._dist.broadcast(h, src=self.src, group=self.group)
+        if int(h[0]) == self.STEP:
+            return "step_batch", (h[2:2 + int(h[1])].tolist(),)
         box: list[Any] = [None]
         self._dist.broadcast_object_list(box, src=self.src, group=self.group)
         return box[0]
