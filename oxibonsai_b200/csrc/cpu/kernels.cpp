@@ -202,11 +202,87 @@ BONSAI_AVX512 float sumsq_avx512(const float* x, uint64_t n) {
   return s;
 }
 
+// ---- FP8 rows (blocks of 32: 32 codes + f16 scale; GGUF types 43 = E4M3, 44 = E5M2) -----------------------------
+// The reference's FP8 tiers decode through a 256-entry table (crates/oxibonsai-kernels/src/fp8_lut.rs, simd_fp8_avx2.rs,
+// simd_fp8_avx512.rs); here the table feeds vector gathers: eight (AVX2) or sixteen (AVX-512) codes become floats with
+// one gather and meet the activations in one fused multiply-add.
+alignas(64) float g_fp8_lut[2][256];
+std::atomic<bool> g_fp8_lut_ready{false};
+void init_fp8_lut() {
+  if (g_fp8_lut_ready.load(std::memory_order_acquire)) return;
+  for (int q = 0; q < 256; ++q) {
+    g_fp8_lut[0][q] = fp8_e4m3_decode((uint8_t)q);
+    g_fp8_lut[1][q] = fp8_e5m2_decode((uint8_t)q);
+    // NaN codes contribute nothing to a dot product here (the scalar body skips them the same way)
+    if (g_fp8_lut[0][q] != g_fp8_lut[0][q]) g_fp8_lut[0][q] = 0.0f;
+    if (g_fp8_lut[1][q] != g_fp8_lut[1][q] || std::isinf(g_fp8_lut[1][q])) g_fp8_lut[1][q] = 0.0f;
+  }
+  g_fp8_lut_ready.store(true, std::memory_order_release);
+}
+template <int FMT>
+float dot_fp8_ref(const uint8_t* row, uint64_t nblk32, const float* x) {
+  const float* lut = g_fp8_lut[FMT];
+  float sum = 0.0f;
+  for (uint64_t b = 0; b < nblk32; ++b, row += kFp8Bytes, x += 32) {
+    float bs = 0.0f;
+    for (int i = 0; i < 32; ++i) bs += lut[row[i]] * x[i];
+    sum += f16_to_f32(ld_u16(row + 32)) * bs;
+  }
+  return sum;
+}
+template <int FMT>
+__attribute__((target("avx2,fma"))) float dot_fp8_avx2(const uint8_t* row, uint64_t nblk32, const float* x) {
+  const float* lut = g_fp8_lut[FMT];
+  __m256 acc = _mm256_setzero_ps();
+  for (uint64_t b = 0; b < nblk32; ++b, row += kFp8Bytes, x += 32) {
+    __m256 bs = _mm256_setzero_ps();
+    for (int i = 0; i < 32; i += 8) {
+      const __m256i idx = _mm256_cvtepu8_epi32(_mm_loadl_epi64(reinterpret_cast<const __m128i*>(row + i)));
+      bs = _mm256_fmadd_ps(_mm256_i32gather_ps(lut, idx, 4), _mm256_loadu_ps(x + i), bs);
+    }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(f16_to_f32(ld_u16(row + 32))), bs, acc);
+  }
+  return hsum256(acc);
+}
+template <int FMT>
+__attribute__((target("avx512f,avx512bw,avx512vl"))) float dot_fp8_avx512(const uint8_t* row, uint64_t nblk32, const float* x) {
+  const float* lut = g_fp8_lut[FMT];
+  __m512 acc = _mm512_setzero_ps();
+  for (uint64_t b = 0; b < nblk32; ++b, row += kFp8Bytes, x += 32) {
+    __m512 bs = _mm512_setzero_ps();
+    for (int i = 0; i < 32; i += 16) {
+      const __m512i idx = _mm512_cvtepu8_epi32(_mm_loadu_si128(reinterpret_cast<const __m128i*>(row + i)));
+      bs = _mm512_fmadd_ps(_mm512_i32gather_ps(idx, lut, 4), _mm512_loadu_ps(x + i), bs);
+    }
+    acc = _mm512_fmadd_ps(_mm512_set1_ps(f16_to_f32(ld_u16(row + 32))), bs, acc);
+  }
+  return _mm512_reduce_add_ps(acc);
+}
+
 using RowDot = float (*)(const uint8_t*, uint64_t, const float*);
 RowDot pick(uint32_t type, int tier) {
   if (type == 42) return tier >= kAvx512 ? dot_tq2_avx512 : (tier >= kAvx2 ? dot_tq2_avx2 : dot_tq2_ref);
   if (type == 41) return tier >= kAvx512 ? dot_q1_avx512 : (tier >= kAvx2 ? dot_q1_avx2 : dot_q1_ref);
+  if (type == 43 || type == 44) {
+    init_fp8_lut();
+    if (type == 43) return tier >= kAvx512 ? dot_fp8_avx512<0> : (tier >= kAvx2 ? dot_fp8_avx2<0> : dot_fp8_ref<0>);
+    return tier >= kAvx512 ? dot_fp8_avx512<1> : (tier >= kAvx2 ? dot_fp8_avx2<1> : dot_fp8_ref<1>);
+  }
   return nullptr;
+}
+// elements and bytes of one block of a row format the tiers know
+bool row_format(uint32_t type, uint64_t* elems, uint64_t* bytes) {
+  switch (type) {
+    case 41: *elems = kQ1Block; *bytes = kQ1Bytes; return true;
+    case 42: *elems = kTq2Block; *bytes = kTq2Bytes; return true;
+    case 43: case 44: *elems = kFp8Block; *bytes = kFp8Bytes; return true;
+    default: return false;
+  }
+}
+void dequant_row(uint32_t type, const uint8_t* src, uint64_t nblk, float* dst) {
+  if (type == 42) dequant_tq2(src, nblk, dst);
+  else if (type == 41) dequant_q1(src, nblk, dst);
+  else dequant_fp8(src, nblk, dst, type == 44);
 }
 using VecDot = float (*)(const float*, const float*, uint64_t);
 VecDot pick_f32(int tier) { return tier >= kAvx512 ? dot_f32_avx512 : (tier >= kAvx2 ? dot_f32_avx2 : dot_f32_ref); }
@@ -245,15 +321,17 @@ const char* bcpu_tier_name(int tier) { return tier == 0 ? "reference" : (tier ==
 // out[rows] = W x for Q1_0_g128 (41) / TQ2_0_g128 (42) rows; tier < 0 uses the active tier; threads <= 0 = all cores.
 int bcpu_gemv_tiered(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, float* out, int tier, int threads) {
   using namespace bonsai;
-  if (cols % 128 != 0) return -12;
+  uint64_t be = 0, bb = 0;
+  if (!row_format(type, &be, &bb)) return -7;
+  if (cols % be != 0) return -12;
   RowDot dot = pick(type, tier < 0 ? active_tier() : std::min(tier, detect_tier()));
   if (dot == nullptr) return -7;
-  const uint64_t rb = (cols / 128) * (type == 42 ? 34 : 18);
+  const uint64_t nblk = cols / be, rb = nblk * bb;
   if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
   parallel_rows(rows, threads, [=](uint64_t lo, uint64_t hi) {
     for (uint64_t r = lo; r < hi; ++r) {
       if (r + 1 < hi) __builtin_prefetch(data + (r + 1) * rb);
-      out[r] = dot(data + r * rb, cols / 128, x);
+      out[r] = dot(data + r * rb, nblk, x);
     }
   });
   return 0;
@@ -263,15 +341,16 @@ int bcpu_gemv_tiered(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t
 // (the batch GEMM of the prefill path on CPU).
 int bcpu_gemm_tiered(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, uint64_t batch, float* out, int threads) {
   using namespace bonsai;
-  if (cols % 128 != 0) return -12;
-  if (type != 41 && type != 42) return -7;
-  const uint64_t rb = (cols / 128) * (type == 42 ? 34 : 18);
+  uint64_t be = 0, bb = 0;
+  if (!row_format(type, &be, &bb)) return -7;
+  if (cols % be != 0) return -12;
+  const uint64_t nblk = cols / be, rb = nblk * bb;
   if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
   const VecDot vdot = pick_f32(active_tier());
   parallel_rows(rows, threads, [=](uint64_t lo, uint64_t hi) {
     std::vector<float> w(cols);
     for (uint64_t r = lo; r < hi; ++r) {
-      if (type == 42) dequant_tq2(data + r * rb, cols / 128, w.data()); else dequant_q1(data + r * rb, cols / 128, w.data());
+      dequant_row(type, data + r * rb, nblk, w.data());
       for (uint64_t b = 0; b < batch; ++b) {
         out[b * rows + r] = vdot(w.data(), x + b * cols, cols);
       }
@@ -341,5 +420,149 @@ void* bcpu_aligned_alloc(uint64_t bytes) {
   return posix_memalign(&p, 64, ((bytes + 63) / 64) * 64) == 0 ? p : nullptr;
 }
 void bcpu_aligned_free(void* p) { std::free(p); }
+
+// ---- cache-aware tiling, adaptive strategy, block packing, prefetch (reference: tiled.rs, parallel_tiled.rs, packing.rs,
+// prefetch.rs of crates/oxibonsai-kernels) -------------------------------------------------------------------------------------
+
+// Bytes a GEMV over `rows` rows touches: packed weights + input + output.
+uint64_t bcpu_working_set_bytes(uint32_t type, uint64_t rows, uint64_t cols) {
+  uint64_t be = 0, bb = 0;
+  if (!bonsai::row_format(type, &be, &bb) || cols % be != 0) return 0;
+  return rows * (cols / be) * bb + cols * 4 + rows * 4;
+}
+// Rows per tile so that a tile's weights and the input vector stay in `cache_bytes` (0 = 32 KB, an L1 data cache), clamped
+// to [4, 256].
+uint64_t bcpu_optimal_tile_rows(uint32_t type, uint64_t cols, uint64_t cache_bytes) {
+  uint64_t be = 0, bb = 0;
+  if (!bonsai::row_format(type, &be, &bb) || cols % be != 0 || cols == 0) return 0;
+  if (cache_bytes == 0) cache_bytes = 32 * 1024;
+  const uint64_t row_bytes = (cols / be) * bb, input = cols * 4;
+  const uint64_t room = cache_bytes > input ? cache_bytes - input : 0;
+  return std::min<uint64_t>(256, std::max<uint64_t>(4, room / row_bytes));
+}
+// 0 = direct (one thread, no tiling), 1 = parallel rows, 2 = parallel tiles.
+int bcpu_select_strategy(uint64_t rows, uint64_t cols, uint64_t batch) {
+  (void)cols;
+  if (rows * std::max<uint64_t>(1, batch) <= 32) return 0;
+  if (rows <= 256 && batch <= 1) return 1;
+  return 2;
+}
+// Prefetch hints over a byte range, one per cache line.  locality 0 (streamed once) .. 3 (keep in all levels).
+void bcpu_prefetch_range(const void* ptr, uint64_t bytes, int locality, int write) {
+  const char* p = static_cast<const char*>(ptr);
+  for (uint64_t off = 0; off < bytes; off += 64) {
+    if (write) {
+      switch (locality) { case 0: __builtin_prefetch(p + off, 1, 0); break; case 1: __builtin_prefetch(p + off, 1, 1); break;
+                          case 2: __builtin_prefetch(p + off, 1, 2); break; default: __builtin_prefetch(p + off, 1, 3); }
+    } else {
+      switch (locality) { case 0: __builtin_prefetch(p + off, 0, 0); break; case 1: __builtin_prefetch(p + off, 0, 1); break;
+                          case 2: __builtin_prefetch(p + off, 0, 2); break; default: __builtin_prefetch(p + off, 0, 3); }
+    }
+  }
+}
+// Tile-interleaved block order for a GEMV that walks a tile of rows block column by block column: inside every tile of
+// `tile` rows the blocks are stored [block 0 of every row, block 1 of every row, ...].  `unpack` is the inverse.
+int bcpu_pack_rows_tiled(const uint8_t* src, uint64_t rows, uint64_t blocks_per_row, uint64_t block_bytes, uint64_t tile, uint8_t* dst, int unpack) {
+  if (tile == 0 || block_bytes == 0) return -12;
+  uint64_t at = 0;   // running block index in the tiled order
+  for (uint64_t r0 = 0; r0 < rows; r0 += tile) {
+    const uint64_t tr = std::min(tile, rows - r0);
+    for (uint64_t b = 0; b < blocks_per_row; ++b)
+      for (uint64_t r = 0; r < tr; ++r, ++at) {
+        const uint64_t plain = ((r0 + r) * blocks_per_row + b) * block_bytes, tiled = at * block_bytes;
+        if (unpack) std::memcpy(dst + plain, src + tiled, block_bytes);
+        else std::memcpy(dst + tiled, src + plain, block_bytes);
+      }
+  }
+  return 0;
+}
+
+// out[rows] = W x with the rows cut into tiles (tile_rows = 0: bcpu_optimal_tile_rows): threads take tiles from a shared
+// counter and ask for the next tile's weights while they work on the current one.
+int bcpu_gemv_tiled(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, float* out, uint64_t tile_rows, int threads) {
+  using namespace bonsai;
+  uint64_t be = 0, bb = 0;
+  if (!row_format(type, &be, &bb)) return -7;
+  if (cols % be != 0) return -12;
+  RowDot dot = pick(type, active_tier());
+  if (tile_rows == 0) tile_rows = bcpu_optimal_tile_rows(type, cols, 0);
+  const uint64_t nblk = cols / be, rb = nblk * bb, ntiles = (rows + tile_rows - 1) / tile_rows;
+  if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
+  threads = (int)std::min<uint64_t>(threads, ntiles);
+  std::atomic<uint64_t> next{0};
+  auto work = [&] {
+    for (;;) {
+      const uint64_t t = next.fetch_add(1);
+      if (t >= ntiles) return;
+      const uint64_t lo = t * tile_rows, hi = std::min(rows, lo + tile_rows);
+      if (hi < rows) bcpu_prefetch_range(data + hi * rb, std::min<uint64_t>(rb * tile_rows, 4096), 1, 0);
+      for (uint64_t r = lo; r < hi; ++r) out[r] = dot(data + r * rb, nblk, x);
+    }
+  };
+  if (threads <= 1) {
+    work();
+  } else {
+    std::vector<std::thread> pool;
+    for (int i = 0; i < threads; ++i) pool.emplace_back(work);
+    for (auto& th : pool) th.join();
+  }
+  return 0;
+}
+
+// out[batch][rows] = X W^T, tiled both ways: a tile of weight rows is decoded to f32 once (it then sits in L2) and is
+// multiplied with the batch in groups of tile_batch rows, so that the decoded tile is reused from cache by every group.
+int bcpu_gemm_tiled(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, uint64_t batch, float* out,
+                    uint64_t tile_rows, uint64_t tile_batch, int threads) {
+  using namespace bonsai;
+  uint64_t be = 0, bb = 0;
+  if (!row_format(type, &be, &bb)) return -7;
+  if (cols % be != 0) return -12;
+  if (tile_rows == 0) tile_rows = std::max<uint64_t>(4, std::min<uint64_t>(64, (256 * 1024) / (cols * 4)));   // decoded tile within ~256 KB
+  if (tile_batch == 0) tile_batch = 8;
+  const uint64_t nblk = cols / be, rb = nblk * bb, ntiles = (rows + tile_rows - 1) / tile_rows;
+  if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
+  threads = (int)std::min<uint64_t>(threads, ntiles);
+  const VecDot vdot = pick_f32(active_tier());
+  std::atomic<uint64_t> next{0};
+  auto work = [&] {
+    std::vector<float> w(tile_rows * cols);
+    for (;;) {
+      const uint64_t t = next.fetch_add(1);
+      if (t >= ntiles) return;
+      const uint64_t lo = t * tile_rows, hi = std::min(rows, lo + tile_rows);
+      for (uint64_t r = lo; r < hi; ++r) dequant_row(type, data + r * rb, nblk, w.data() + (r - lo) * cols);
+      for (uint64_t b0 = 0; b0 < batch; b0 += tile_batch) {
+        const uint64_t b1 = std::min(batch, b0 + tile_batch);
+        for (uint64_t r = lo; r < hi; ++r)
+          for (uint64_t b = b0; b < b1; ++b) out[b * rows + r] = vdot(w.data() + (r - lo) * cols, x + b * cols, cols);
+      }
+    }
+  };
+  if (threads <= 1) {
+    work();
+  } else {
+    std::vector<std::thread> pool;
+    for (int i = 0; i < threads; ++i) pool.emplace_back(work);
+    for (auto& th : pool) th.join();
+  }
+  return 0;
+}
+
+// Picks direct / parallel-row / parallel-tiled by problem size (bcpu_select_strategy) and runs it; returns the strategy
+// (>= 0) or a negative error.
+int bcpu_gemv_adaptive(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, float* out) {
+  const int st = bcpu_select_strategy(rows, cols, 1);
+  const int rc = st == 0 ? bcpu_gemv_tiered(type, data, rows, cols, x, out, -1, 1)
+               : st == 1 ? bcpu_gemv_tiered(type, data, rows, cols, x, out, -1, 0)
+                         : bcpu_gemv_tiled(type, data, rows, cols, x, out, 0, 0);
+  return rc < 0 ? rc : st;
+}
+int bcpu_gemm_adaptive(uint32_t type, const uint8_t* data, uint64_t rows, uint64_t cols, const float* x, uint64_t batch, float* out) {
+  const int st = bcpu_select_strategy(rows, cols, batch);
+  const int rc = st == 0 ? bcpu_gemm_tiered(type, data, rows, cols, x, batch, out, 1)
+               : st == 1 ? bcpu_gemm_tiered(type, data, rows, cols, x, batch, out, 0)
+                         : bcpu_gemm_tiled(type, data, rows, cols, x, batch, out, 0, 0, 0);
+  return rc < 0 ? rc : st;
+}
 
 }  // extern "C"

@@ -66,7 +66,12 @@ def _lib():
             "bcpu_gemv_tiered": (i, [u32, vp, u64, u64, vp, vp, i, i]), "bcpu_gemm_tiered": (i, [u32, vp, u64, u64, vp, u64, vp, i]),
             "bcpu_rmsnorm_tiered": (None, [vp, vp, vp, u64, f, i]), "bcpu_silu": (None, [vp, vp, u64]), "bcpu_swiglu_tiered": (None, [vp, vp, vp, u64]),
             "bcpu_softmax": (None, [vp, vp, u64]), "bcpu_rope_apply": (None, [vp, u64, u64, vp, vp]),
-            "bcpu_aligned_alloc": (vp, [u64]), "bcpu_aligned_free": (None, [vp])})
+            "bcpu_aligned_alloc": (vp, [u64]), "bcpu_aligned_free": (None, [vp]),
+            "bcpu_working_set_bytes": (u64, [u32, u64, u64]), "bcpu_optimal_tile_rows": (u64, [u32, u64, u64]),
+            "bcpu_select_strategy": (i, [u64, u64, u64]), "bcpu_prefetch_range": (None, [vp, u64, i, i]),
+            "bcpu_pack_rows_tiled": (i, [vp, u64, u64, u64, u64, vp, i]),
+            "bcpu_gemv_tiled": (i, [u32, vp, u64, u64, vp, vp, u64, i]), "bcpu_gemm_tiled": (i, [u32, vp, u64, u64, vp, u64, vp, u64, u64, i]),
+            "bcpu_gemv_adaptive": (i, [u32, vp, u64, u64, vp, vp]), "bcpu_gemm_adaptive": (i, [u32, vp, u64, u64, vp, u64, vp])})
         lib._declared.add("bcpu_gemv_tiered")
     return lib
 
@@ -87,13 +92,18 @@ def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
+# (elements, bytes) of one block of the row formats the CPU tiers read
+_ROW_FORMATS = {G.Q1_0_G128: (128, 18), G.TQ2_0_G128: (128, 34), G.F8_E4M3: (32, 34), G.F8_E5M2: (32, 34)}
+
+
 def _check_matrix(type_id: int, data: np.ndarray, rows: int, cols: int) -> np.ndarray:
-    if type_id not in (G.Q1_0_G128, G.TQ2_0_G128):
-        raise UnsupportedOperation(f"tiered CPU kernels cover Q1_0_g128 and TQ2_0_g128, not type {type_id}")
-    if cols % 128:
-        raise NotBlockAligned(f"row length {cols} is not a multiple of 128")
+    if type_id not in _ROW_FORMATS:
+        raise UnsupportedOperation(f"tiered CPU kernels cover Q1_0_g128, TQ2_0_g128 and the FP8 blocks, not type {type_id}")
+    elems, nbytes = _ROW_FORMATS[type_id]
+    if cols % elems:
+        raise NotBlockAligned(f"row length {cols} is not a multiple of {elems}")
     raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
-    need = rows * (cols // 128) * (34 if type_id == G.TQ2_0_G128 else 18)
+    need = rows * (cols // elems) * nbytes
     if raw.size < need:
         raise BufferTooSmall(f"matrix needs {need} bytes, got {raw.size}")
     return raw
@@ -120,6 +130,100 @@ def gemm(type_id: int, data, rows: int, cols: int, x, threads: int = 0) -> np.nd
     if rc != 0:
         raise KernelError(f"cpu gemm failed with code {rc}")
     return out
+
+
+class Strategy(IntEnum):
+    """How the adaptive entry points run a product (reference: ``AdaptiveStrategy``, parallel_tiled.rs:259-281)."""
+    DIRECT = 0
+    PARALLEL_ROWS = 1
+    PARALLEL_TILED = 2
+
+
+def select_strategy(rows: int, cols: int, batch: int = 1) -> Strategy:
+    return Strategy(_lib().bcpu_select_strategy(rows, cols, batch))
+
+
+def working_set_bytes(type_id: int, rows: int, cols: int) -> int:
+    """Packed weights + input + output of a GEMV (0 for an unknown format or a ragged row)."""
+    return int(_lib().bcpu_working_set_bytes(type_id, rows, cols))
+
+
+def fits_in_cache(type_id: int, rows: int, cols: int, cache_bytes: int = 32 * 1024) -> bool:
+    ws = working_set_bytes(type_id, rows, cols)
+    return 0 < ws <= cache_bytes
+
+
+def optimal_tile_rows(type_id: int, cols: int, cache_bytes: int = 0) -> int:
+    """Rows per tile whose weights stay in ``cache_bytes`` beside the input vector (default: a 32 KB L1), within [4, 256]."""
+    return int(_lib().bcpu_optimal_tile_rows(type_id, cols, cache_bytes))
+
+
+def prefetch_range(array: np.ndarray, locality: int = 3, write: bool = False) -> None:
+    """Prefetch hints for every cache line of ``array`` (locality 0 = streamed once .. 3 = keep in all cache levels)."""
+    a = np.ascontiguousarray(array)
+    _lib().bcpu_prefetch_range(a.ctypes.data, a.nbytes, int(locality), int(write))
+
+
+def pack_rows_tiled(type_id: int, data, rows: int, cols: int, tile: int = 32, unpack: bool = False) -> np.ndarray:
+    """Block order for a GEMV that walks ``tile`` rows block column by block column: inside every tile, block 0 of every row,
+    then block 1 of every row, ...  ``unpack=True`` inverts it (reference: ``pack_blocks_for_gemv`` / ``unpack_blocks_from_gemv``,
+    packing.rs:122-215)."""
+    raw = _check_matrix(type_id, data, rows, cols)
+    elems, nbytes = _ROW_FORMATS[type_id]
+    n = rows * (cols // elems) * nbytes
+    out = np.empty(n, dtype=np.uint8)
+    rc = _lib().bcpu_pack_rows_tiled(raw.ctypes.data, rows, cols // elems, nbytes, tile, out.ctypes.data, int(unpack))
+    if rc != 0:
+        raise KernelError(f"pack_rows_tiled failed with code {rc}")
+    return out
+
+
+def gemv_tiled(type_id: int, data, rows: int, cols: int, x, tile_rows: int = 0, threads: int = 0) -> np.ndarray:
+    """GEMV over row tiles sized for the cache (``tile_rows`` 0 = :func:`optimal_tile_rows`), tiles handed to threads from a
+    shared counter with the next tile prefetched (reference: ``gemv_tiled_par``, ``gemv_parallel_tiled``)."""
+    raw, xv = _check_matrix(type_id, data, rows, cols), _f32(x)
+    if xv.size != cols:
+        raise DimensionMismatch(f"x has {xv.size} elements, expected {cols}")
+    out = np.empty(rows, dtype=np.float32)
+    rc = _lib().bcpu_gemv_tiled(type_id, raw.ctypes.data, rows, cols, xv.ctypes.data, out.ctypes.data, tile_rows, threads)
+    if rc != 0:
+        raise KernelError(f"cpu tiled gemv failed with code {rc}")
+    return out
+
+
+def gemm_tiled(type_id: int, data, rows: int, cols: int, x, tile_rows: int = 0, tile_batch: int = 0, threads: int = 0) -> np.ndarray:
+    """Batch GEMM tiled over weight rows (decoded once per tile) and over the batch (reference: ``gemm_tiled_par``)."""
+    raw, xv = _check_matrix(type_id, data, rows, cols), _f32(x)
+    if xv.ndim != 2 or xv.shape[1] != cols:
+        raise DimensionMismatch(f"x has shape {xv.shape}, expected [batch, {cols}]")
+    out = np.empty((xv.shape[0], rows), dtype=np.float32)
+    rc = _lib().bcpu_gemm_tiled(type_id, raw.ctypes.data, rows, cols, xv.ctypes.data, xv.shape[0], out.ctypes.data, tile_rows, tile_batch, threads)
+    if rc != 0:
+        raise KernelError(f"cpu tiled gemm failed with code {rc}")
+    return out
+
+
+def gemv_adaptive(type_id: int, data, rows: int, cols: int, x) -> tuple[np.ndarray, Strategy]:
+    """GEMV by the strategy :func:`select_strategy` picks for the shape; returns the result and the strategy used."""
+    raw, xv = _check_matrix(type_id, data, rows, cols), _f32(x)
+    if xv.size != cols:
+        raise DimensionMismatch(f"x has {xv.size} elements, expected {cols}")
+    out = np.empty(rows, dtype=np.float32)
+    rc = _lib().bcpu_gemv_adaptive(type_id, raw.ctypes.data, rows, cols, xv.ctypes.data, out.ctypes.data)
+    if rc < 0:
+        raise KernelError(f"cpu adaptive gemv failed with code {rc}")
+    return out, Strategy(rc)
+
+
+def gemm_adaptive(type_id: int, data, rows: int, cols: int, x) -> tuple[np.ndarray, Strategy]:
+    raw, xv = _check_matrix(type_id, data, rows, cols), _f32(x)
+    if xv.ndim != 2 or xv.shape[1] != cols:
+        raise DimensionMismatch(f"x has shape {xv.shape}, expected [batch, {cols}]")
+    out = np.empty((xv.shape[0], rows), dtype=np.float32)
+    rc = _lib().bcpu_gemm_adaptive(type_id, raw.ctypes.data, rows, cols, xv.ctypes.data, xv.shape[0], out.ctypes.data)
+    if rc < 0:
+        raise KernelError(f"cpu adaptive gemm failed with code {rc}")
+    return out, Strategy(rc)
 
 
 def rms_norm(x, w, eps: float = 1e-6, tier: int = 1) -> np.ndarray:

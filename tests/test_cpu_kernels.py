@@ -100,3 +100,67 @@ def test_vector_tiers_agree_with_the_reference_tier_on_random_shapes():
         assert np.abs(got - want).max() <= 1e-4 * max(1.0, float(np.abs(want).max()))
 
     check()
+
+
+@pytest.mark.parametrize("ty", [G.F8_E4M3, G.F8_E5M2])
+def test_fp8_rows_on_every_tier(ty):
+    """FP8 blocks (32 codes + f16 scale): the scalar body and the table-gather vector bodies agree with the decoded matrix."""
+    rng = np.random.default_rng(2)
+    rows, cols = 130, 224                                   # 7 blocks per row: not a multiple of 128
+    q = quantize(ty, rng.normal(size=(rows, cols)).astype(np.float32) * 0.05)
+    wd = dequantize(ty, q).reshape(rows, cols).astype(np.float64)
+    x = rng.normal(size=cols).astype(np.float32)
+    want = wd @ x.astype(np.float64)
+    best = CK.detect_tier()
+    for tier in (CK.KernelTier.REFERENCE, CK.KernelTier.AVX2, CK.KernelTier.AVX512):
+        if tier <= best:
+            assert np.allclose(CK.gemv(ty, q, rows, cols, x, tier, threads=2), want, rtol=1e-4, atol=1e-5), tier
+    xb = rng.normal(size=(3, cols)).astype(np.float32)
+    assert np.allclose(CK.gemm(ty, q, rows, cols, xb), xb.astype(np.float64) @ wd.T, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("ty", [G.TQ2_0_G128, G.Q1_0_G128, G.F8_E4M3])
+def test_tiled_and_adaptive_products_match_the_plain_ones(ty):
+    rng = np.random.default_rng(6)
+    rows, cols = 523, 384
+    q = quantize(ty, rng.normal(size=(rows, cols)).astype(np.float32) * 0.05)
+    x = rng.normal(size=cols).astype(np.float32)
+    plain = CK.gemv(ty, q, rows, cols, x, threads=1)
+    for tile, threads in ((0, 0), (7, 3), (600, 2), (1, 1)):
+        assert np.array_equal(CK.gemv_tiled(ty, q, rows, cols, x, tile_rows=tile, threads=threads), plain), (tile, threads)
+    xb = rng.normal(size=(11, cols)).astype(np.float32)
+    plain_mm = CK.gemm(ty, q, rows, cols, xb, threads=1)
+    for tr, tb, threads in ((0, 0, 0), (5, 3, 2), (64, 16, 4)):
+        assert np.array_equal(CK.gemm_tiled(ty, q, rows, cols, xb, tile_rows=tr, tile_batch=tb, threads=threads), plain_mm), (tr, tb)
+    y, st = CK.gemv_adaptive(ty, q, rows, cols, x)
+    assert st == CK.Strategy.PARALLEL_TILED and np.array_equal(y, plain)
+    y, st = CK.gemv_adaptive(ty, q[: 20 * (cols // (128 if ty != G.F8_E4M3 else 32)) * (34 if ty != G.Q1_0_G128 else 18)], 20, cols, x)
+    assert st == CK.Strategy.DIRECT and np.array_equal(y, plain[:20])
+    ym, st = CK.gemm_adaptive(ty, q, rows, cols, xb)
+    assert st == CK.Strategy.PARALLEL_TILED and np.array_equal(ym, plain_mm)
+
+
+def test_strategy_tiles_packing_and_prefetch_helpers():
+    assert CK.select_strategy(16, 4096) == CK.Strategy.DIRECT
+    assert CK.select_strategy(200, 4096) == CK.Strategy.PARALLEL_ROWS
+    assert CK.select_strategy(200, 4096, batch=8) == CK.Strategy.PARALLEL_TILED
+    assert CK.select_strategy(4096, 4096) == CK.Strategy.PARALLEL_TILED
+    # working set: packed rows + f32 input + f32 output
+    assert CK.working_set_bytes(G.TQ2_0_G128, 10, 256) == 10 * 2 * 34 + 256 * 4 + 10 * 4
+    assert CK.working_set_bytes(G.Q4_0, 10, 256) == 0 and CK.working_set_bytes(G.TQ2_0_G128, 10, 100) == 0
+    assert CK.fits_in_cache(G.Q1_0_G128, 64, 1024) and not CK.fits_in_cache(G.Q1_0_G128, 4096, 4096)
+    t = CK.optimal_tile_rows(G.Q1_0_G128, 4096)                   # (32 KB - 16 KB input) / 576 bytes per row
+    assert t == (32 * 1024 - 4096 * 4) // (32 * 18)
+    assert CK.optimal_tile_rows(G.TQ2_0_G128, 16384) == 4 and CK.optimal_tile_rows(G.Q1_0_G128, 128, 1 << 20) == 256
+    # tile packing: a permutation of the blocks with an exact inverse; a ragged last tile is handled
+    rng = np.random.default_rng(1)
+    rows, cols = 70, 512
+    q = quantize(G.TQ2_0_G128, rng.normal(size=(rows, cols)).astype(np.float32))
+    packed = CK.pack_rows_tiled(G.TQ2_0_G128, q, rows, cols, tile=32)
+    assert packed.shape == q.reshape(-1).shape and not np.array_equal(packed, q.reshape(-1))
+    blocks, pblocks = q.reshape(rows, 4, 34), packed.reshape(-1, 34)
+    assert np.array_equal(pblocks[0], blocks[0, 0]) and np.array_equal(pblocks[1], blocks[1, 0]) and np.array_equal(pblocks[32], blocks[0, 1])
+    assert np.array_equal(pblocks[2 * 32 * 4 + 6], blocks[64, 1])            # last tile has 6 rows: block 1 starts after 6 entries
+    assert np.array_equal(CK.pack_rows_tiled(G.TQ2_0_G128, packed, rows, cols, tile=32, unpack=True), q.reshape(-1))
+    CK.prefetch_range(q, locality=1)
+    CK.prefetch_range(np.zeros(1000, np.float32), locality=3, write=True)     # hints only: nothing observable, must not fault
