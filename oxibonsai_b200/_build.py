@@ -141,6 +141,40 @@ def build(kind: str, force: bool = False, verbose: bool = False) -> Path:
     return so
 
 
+def build_sanitized(out_dir: str | os.PathLike) -> Path:
+    """Builds the host library with AddressSanitizer and UndefinedBehaviorSanitizer into ``out_dir`` (the regular library is
+    left alone) and returns its path.  Load it through ``OXIBONSAI_HOST_LIB=<path>`` in a process started with the sanitizer
+    runtimes preloaded (``sanitizer_runtimes()``); ``tests/test_host_sanitizers.py`` runs the codecs, the GGUF reader and
+    writer, the CPU kernels and the tokenizer / constraint helpers that way."""
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    flags = [f for f in HOST_FLAGS if f not in ("-shared", "-O2")] + ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+                                                                     "-fno-sanitize-recover=undefined"]
+    objs = []
+    for src in _sources("host"):
+        obj = out / (src.relative_to(CSRC).as_posix().replace("/", "__") + ".o")
+        cmd = ["g++", *flags, f"-I{CSRC}", "-c", str(src), "-o", str(obj)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"sanitized build failed: {' '.join(cmd)}\n{proc.stderr}")
+        objs.append(str(obj))
+    so = out / "libbonsai_host_san.so"
+    proc = subprocess.run(["g++", "-shared", "-pthread", "-fsanitize=address,undefined", *objs, "-o", str(so)], capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"sanitized link failed:\n{proc.stderr}")
+    return so
+
+
+def sanitizer_runtimes() -> list[str]:
+    """Paths of libasan / libubsan of the host compiler, for ``LD_PRELOAD`` (empty when the compiler has none)."""
+    libs = []
+    for name in ("libasan.so", "libubsan.so"):
+        p = subprocess.run(["gcc", f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip()
+        if p and os.path.isabs(p) and os.path.exists(p):
+            libs.append(os.path.realpath(p))
+    return libs
+
+
 def build_all(force: bool = False, verbose: bool = False) -> dict[str, Path]:
     return {k: build(k, force=force, verbose=verbose) for k in ("host", "cuda")}
 

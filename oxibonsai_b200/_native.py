@@ -28,6 +28,10 @@ class NativeError(RuntimeError):
 
 
 def _load(kind: str) -> C.CDLL:
+    import os
+    override = os.environ.get("OXIBONSAI_HOST_LIB") if kind == "host" else None
+    if override:            # an instrumented build of the host library (see _build.build_sanitized)
+        return C.CDLL(override, mode=C.RTLD_GLOBAL)
     path = _build.lib_path(kind)
     try:
         if _build.is_stale(kind):
