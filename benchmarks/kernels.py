@@ -78,6 +78,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--kv", default="f16")
     ap.add_argument("--nsplit", type=int, default=16)
+    ap.add_argument("--heads", type=int, default=32, help="attn: query heads (a tensor-parallel rank of the 8B model has 32 / N)")
+    ap.add_argument("--kv-heads", type=int, default=8, help="attn: KV heads (8 / N on a tensor-parallel rank)")
     ap.add_argument("--iters", type=int, default=40)
     ap.add_argument("--shapes", default=",".join(SHAPES))
     ap.add_argument("--profile", action="store_true")
@@ -150,7 +152,7 @@ def main() -> None:
         rows_out.append({"case": "lmhead", "tokens": T, "us": round(us, 2), "TFLOP/s": round(fl / us / 1e6, 1),
                          f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3), "status": int(status.item())})
     elif a.case == "attn":
-        nq, nkv, hd, page = 32, 8, 128, 64
+        nq, nkv, hd, page = a.heads, a.kv_heads, 128, 64
         kvt = {"f32": K.KV_F32, "f16": K.KV_F16, "q8": K.KV_Q8, "q4": K.KV_Q4}[a.kv]
         B, ctx = a.batch, a.ctx
         pps = (ctx + page - 1) // page
@@ -180,7 +182,7 @@ def main() -> None:
         us = time_us(fn, a.iters, a.profile)
         elt = {K.KV_F32: 4, K.KV_F16: 2, K.KV_Q8: 1, K.KV_Q4: 0.5}[kvt]
         byts = 2.0 * B * ctx * nkv * hd * elt
-        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "nsplit": a.nsplit, "us": round(us, 2),
+        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "heads": f"{nq}/{nkv}", "nsplit": a.nsplit, "us": round(us, 2),
                          "GB/s": round(byts / us / 1e3, 1), f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})
     elif a.case == "attn_prefill":
         # one prompt chunk of --tokens queries whose first token sits at position --ctx (8B head layout, f16 / --kv pages)
