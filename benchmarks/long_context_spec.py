@@ -47,6 +47,7 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=32768)
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--max-lookahead", type=int, default=8)
+    ap.add_argument("--no-self-draft", action="store_true", help="skip the arm in which a copy of the target drafts")
     ap.add_argument("--model-dir", default=os.environ.get("BONSAI_BENCH_DIR", "/tmp/oxibonsai_b200_bench"))
     a = ap.parse_args()
 
@@ -146,8 +147,12 @@ def main() -> None:
         "speculative": spec,
         "data": "synthetic (seeded random-init GGUFs of both shapes, random prompt tokens): unrelated models agree only by chance",
     }
-    if world == 1 or a.target.startswith("tiny"):
-        # ceiling of the mechanism: a second engine over the target's own checkpoint drafts, every proposal is accepted
+    if not a.no_self_draft:
+        # ceiling of the mechanism: a second engine over the target's own checkpoint drafts, so nearly every proposal is
+        # accepted (the draft runs the decode kernels, the verification the prompt kernels); it costs as much as the target,
+        # so this arm shows tokens per verification pass, not a speed-up
+        del draft
+        torch.cuda.empty_cache()
         twin = build(a.target, 1)
         res["self_draft"] = spec_run(twin)
     if rank == 0:

@@ -283,6 +283,10 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   // <= pos0 + i), which spreads a long context over the GPU where the prompt kernel would run one CTA per head.
   // Larger chunks use the tcgen05 GEMM (paired-K order) and the prompt attention kernel.
   const bool hm = r.ic[IC_FAST] != 5 && T <= kSmallChunk && hidden % 128 == 0 && qd % 128 == 0 && inter % 128 == 0;
+  // Tensor parallel, up to 16 tokens (a speculative verification pass): the row-parallel GEMMs exchange their partial sums
+  // in the epilogue, as in the batched decode step, instead of GEMM + two-shot all-reduce (three more launches and two flag
+  // barriers per exchange).
+  const bool tp_fused = tp && hm && T <= 16;
   int sm_splits = (4 * 148) / (nkv * T);
   if (sm_splits < 1) sm_splits = 1;
   if (sm_splits > kSmallSplits) sm_splits = kSmallSplits;
@@ -320,6 +324,8 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
     }
     if (!tp) {
       RC(gemm(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, nullptr, hidden, qd, 1, hidden));
+    } else if (tp_fused) {
+      RC(bonsai_bitgemm_hmma_tp(r.comm, P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, h, h, hidden, qd, T, hidden, st));
     } else {
       RC(gemm(P<void>(lp[LP_O_CODES]), P<void>(lp[LP_O_SCALES]), attn, qd, big, nullptr, nullptr, hidden, qd, 0, hidden));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
@@ -328,6 +334,8 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
     RC(gemm(P<void>(lp[LP_GU_CODES]), P<void>(lp[LP_GU_SCALES]), xn, xn_ld, nullptr, nullptr, act, 2 * inter, hidden, 2, inter));
     if (!tp) {
       RC(gemm(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, nullptr, hidden, inter, 1, hidden));
+    } else if (tp_fused) {
+      RC(bonsai_bitgemm_hmma_tp(r.comm, P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, h, h, hidden, inter, T, hidden, st));
     } else {
       RC(gemm(P<void>(lp[LP_DOWN_CODES]), P<void>(lp[LP_DOWN_SCALES]), act, inter, big, nullptr, nullptr, hidden, inter, 0, hidden));
       RC(bonsai_tp_allreduce_big_add(r.comm, h, (size_t)T * hidden, st));
