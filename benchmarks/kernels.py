@@ -78,6 +78,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--kv", default="f16")
     ap.add_argument("--nsplit", type=int, default=16)
+    ap.add_argument("--no-cluster", action="store_true", help="attn: merge the KV splits through global memory instead of a thread-block cluster")
     ap.add_argument("--heads", type=int, default=32, help="attn: query heads (a tensor-parallel rank of the 8B model has 32 / N)")
     ap.add_argument("--kv-heads", type=int, default=8, help="attn: KV heads (8 / N on a tensor-parallel rank)")
     ap.add_argument("--iters", type=int, default=40)
@@ -174,6 +175,7 @@ def main() -> None:
         pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
         q = torch.randn((B, nq, hd), device=dev)
         out = torch.empty_like(q)
+        K.attn_decode_cluster_mode(1 if a.no_cluster else 0)
 
         def fn():
             it[0] += 1
@@ -182,7 +184,7 @@ def main() -> None:
         us = time_us(fn, a.iters, a.profile)
         elt = {K.KV_F32: 4, K.KV_F16: 2, K.KV_Q8: 1, K.KV_Q4: 0.5}[kvt]
         byts = 2.0 * B * ctx * nkv * hd * elt
-        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "heads": f"{nq}/{nkv}", "nsplit": a.nsplit, "us": round(us, 2),
+        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "heads": f"{nq}/{nkv}", "nsplit": a.nsplit, "cluster_merge": not a.no_cluster, "us": round(us, 2),
                          "GB/s": round(byts / us / 1e3, 1), f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})
     elif a.case == "attn_prefill":
         # one prompt chunk of --tokens queries whose first token sits at position --ctx (8B head layout, f16 / --kv pages)

@@ -14,6 +14,8 @@
 // (single-query attention over the cached K/V of one sequence), which walks one head per block on CUDA cores.
 #include <cuda_fp16.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace bonsai {
@@ -81,7 +83,9 @@ __device__ __forceinline__ float mma_warp_sum(float v) {
 // NW warps per CTA: 8 when the grid is about one CTA per SM (a single sequence: each warp then walks half as many
 // tiles; 479 vs 466 tok/s end to end), 4 with two CTAs per SM when many sequences fill the GPU (57 vs 63-70 us for
 // 64 x 1024 tokens).
-template <int G, int NW>
+// CL: the splits of one (sequence, kv head) form a thread-block cluster (cluster dimension = the grid's y extent) and meet
+// in the shared memory of the cluster's first CTA instead of in global memory.
+template <int G, int NW, bool CL>
 __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAttnParams p) {
   constexpr int kMmaWarps = NW;
   constexpr int hd = kMmaHd;
@@ -94,6 +98,9 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = lane >> 2, cq = lane & 3;   // accumulator row (query head of the group) and column pair of this lane
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Distributed shared memory may only be touched once every CTA of the cluster runs: all threads arrive here and wait
+  // just before the remote writes, by which time the barrier has long completed.
+  if constexpr (CL) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   // Fused mode: the kernel before this one in the stream is the QKV projection, which writes nothing but the raw
   // projections - positions, block table and the cached K/V rows of earlier tokens are older than it.  The wait
   // therefore comes after the page lookups and the first K/V tile requests, just before the projections are read.
@@ -266,6 +273,70 @@ __global__ void __launch_bounds__(NW * 32, 8 / NW) attn_decode_mma_kernel(MmaAtt
     }
   }
   __syncthreads();
+  if constexpr (CL) {
+    // ---- the splits meet in the first CTA's shared memory --------------------------------------------------------------
+    // Every CTA of the cluster writes its (partial sum, max, sum) rows into slot [its rank] of the merge area of CTA 0
+    // through distributed shared memory, the cluster barrier (release / acquire) orders the writes before CTA 0's reads,
+    // and CTA 0 folds the slots.  Every thread of every CTA passes the same two barrier phases on every path (there is
+    // no early exit before them).  No global workspace, fence, counter or reload.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank();                 // = split: the cluster spans the grid's y extent
+    float* merge = sh + (size_t)kMmaWarps * G * stride;         // [nsplit][G][hd + 2], used in CTA 0 only
+    float* lead = cluster.map_shared_rank(merge, 0);
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // the arrival at the top of the kernel: every CTA runs
+    for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+      const int g = idx / hd, d = idx - g * hd;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) M = fmaxf(M, sh[((size_t)w * G + g) * stride + hd]);
+      float a = 0.0f, L = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float* src = sh + ((size_t)w * G + g) * stride;
+        const float f = (src[hd] == -INFINITY) ? 0.0f : __expf(src[hd] - M);
+        a += f * src[d];
+        L += f * src[hd + 1];
+      }
+      float* dst = lead + ((size_t)rank * G + g) * stride;
+      dst[d] = a;
+      if (d == 0) {
+        dst[hd] = M;
+        dst[hd + 1] = L;
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank != 0) return;
+    float* s_f = sh;                                            // [G][nsplit] normalised weights of the splits
+    for (int g = warp; g < G; g += kMmaWarps) {
+      float M = -INFINITY;
+      for (int sp = lane; sp < nsplit; sp += 32) M = fmaxf(M, merge[((size_t)sp * G + g) * stride + hd]);
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+      float L = 0.0f;
+      for (int sp = lane; sp < nsplit; sp += 32) {
+        const float ms = merge[((size_t)sp * G + g) * stride + hd];
+        const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+        L += f * merge[((size_t)sp * G + g) * stride + hd + 1];
+        s_f[g * nsplit + sp] = f;
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o2);
+      const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+      __syncwarp();
+      for (int sp = lane; sp < nsplit; sp += 32) s_f[g * nsplit + sp] *= inv;
+    }
+    __syncthreads();
+    const size_t hb = (size_t)b * p.nq + kvh * G;
+    for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+      const int g = idx / hd, d = idx - g * hd;
+      float a = 0.0f;
+      for (int sp = 0; sp < nsplit; ++sp) a += s_f[g * nsplit + sp] * merge[((size_t)sp * G + g) * stride + d];
+      p.out[hb * hd + idx] = a;
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
     const int g = idx / hd, d = idx - g * hd;
     float M = -INFINITY;
@@ -367,11 +438,59 @@ static int launch_mma(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel<G, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<G, NW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return BONSAI_CUDA_LAUNCH_FAILED;
     configured[dev] = true;
   }
-  const cudaError_t e = launch_pdl(attn_decode_mma_kernel<G, NW>, grid, dim3(kMmaWarps * 32), smem, st, p);
+  const cudaError_t e = launch_pdl(attn_decode_mma_kernel<G, NW, false>, grid, dim3(kMmaWarps * 32), smem, st, p);
+  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
+}
+
+// 0 = let the launcher decide, 1 = never use the cluster merge, 2 = use it wherever it can be launched
+static int g_cluster_mode = 0;
+
+// The cluster form: the grid's y extent (the splits) is the cluster dimension, 2 to 16 CTAs (more than 8 needs the
+// non-portable opt-in).  Returns BONSAI_CUDA_BAD_ARG when the device cannot hold one such cluster, and the caller
+// launches the plain form instead.
+template <int G>
+static int launch_mma_cluster(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int NW = 8;
+  const int nsplit = (int)grid.y;
+  const size_t smem = (size_t)NW * 4 * kMmaTileBytes + (size_t)NW * G * (kMmaHd + 2) * sizeof(float) +
+                      (size_t)nsplit * G * (kMmaHd + 2) * sizeof(float);
+  if (smem > 227 * 1024) return BONSAI_CUDA_BAD_ARG;
+  auto kernel = attn_decode_mma_kernel<G, NW, true>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(NW * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)nsplit;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  // per (device, cluster size): attributes set; the number of clusters the device holds at once (-1 = none / refused)
+  static int fits[64][17] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
+  if (fits[dev][nsplit] == 0) {
+    bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+    if (ok && nsplit > 8) ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    int n = 0;
+    cudaLaunchConfig_t probe = cfg;
+    probe.numAttrs = 1;                 // the occupancy query takes the cluster dimension only
+    if (ok) ok = cudaOccupancyMaxActiveClusters(&n, kernel, &probe) == cudaSuccess && n >= 1;
+    if (!ok) (void)cudaGetLastError();  // a refused attribute or query must not poison the next launch check
+    fits[dev][nsplit] = ok ? n : -1;
+  }
+  // a second wave of clusters would cost more than the merge through global memory that this form saves
+  if (fits[dev][nsplit] < (int)(grid.x * grid.z)) return BONSAI_CUDA_BAD_ARG;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
@@ -394,6 +513,20 @@ static int attn_decode_mma_launch(const float* q, const MmaFused& f, const int* 
                   max_pages, nq, nkv, page_size, extra_len, sm_scale, f.qkv, f.q_norm, f.k_norm, f.rope_cos, f.rope_sin, f.qkv_stride, f.eps};
   const dim3 grid(nkv, nsplit, batch);
   const bool wide = (long long)nkv * nsplit * batch <= 296;   // about one CTA per SM: eight warps each
+  // Few CTAs (one sequence, or a handful): the splits of a (sequence, kv head) run as one cluster and merge through
+  // distributed shared memory, which takes the global round trip (partial store, fence, counter, reload) out of a
+  // kernel that is all latency at this size.
+  if (g_cluster_mode != 1 && wide && (nsplit == 2 || nsplit == 4 || nsplit == 8 || nsplit == 16)) {
+    int rc = BONSAI_CUDA_BAD_ARG;
+    switch (G) {
+      case 1: rc = launch_mma_cluster<1>(p, grid, stream); break;
+      case 2: rc = launch_mma_cluster<2>(p, grid, stream); break;
+      case 4: rc = launch_mma_cluster<4>(p, grid, stream); break;
+      case 8: rc = launch_mma_cluster<8>(p, grid, stream); break;
+      default: break;
+    }
+    if (rc != BONSAI_CUDA_BAD_ARG) return rc;
+  }
   switch (G) {
     case 1: return wide ? launch_mma<1, 8>(p, grid, stream) : launch_mma<1, 4>(p, grid, stream);
     case 2: return wide ? launch_mma<2, 8>(p, grid, stream) : launch_mma<2, 4>(p, grid, stream);
@@ -414,6 +547,9 @@ int attn_decode_mma_f16(const float* q, const int* positions, const int* block_t
 }  // namespace bonsai
 
 extern "C" {
+
+// 0 = cluster merge where the launcher finds it fits (default), 1 = never, 2 = same as 0 (kept for symmetry of the A/B switch).
+void bonsai_attn_decode_cluster_mode(int mode) { bonsai::g_cluster_mode = mode; }
 
 // QK-RMSNorm + RoPE + KV append + split-KV attention of one new token per sequence in a single launch, for f16 pages
 // and head_dim 128.  qkv: f32 [batch][qkv_stride] raw projections (q heads | k heads | v heads); positions[b] is the

@@ -390,6 +390,16 @@ def sample(logits: torch.Tensor, temps=None, topks=None, topps=None, rng=None, p
     return out
 
 
+def attn_decode_cluster_mode(mode: int) -> None:
+    """Decode attention for a few sequences merges its KV splits inside a thread-block cluster (distributed shared memory)
+    where the device holds all clusters at once; ``mode`` 1 switches that off (partials through global memory, merged by the
+    last CTA), 0 restores the default.  Takes effect for launches and graph captures that follow."""
+    l = lib()
+    l.bonsai_attn_decode_cluster_mode.argtypes = [C.c_int]
+    l.bonsai_attn_decode_cluster_mode.restype = None
+    l.bonsai_attn_decode_cluster_mode(int(mode))
+
+
 _capture_lock = __import__("threading").Lock()
 
 

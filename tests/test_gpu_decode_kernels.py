@@ -337,3 +337,39 @@ def test_fused_qknorm_rope_append_attention_matches_separate_kernels(nq, nkv):
         # the same rows were appended (the sum of squares is reduced in another order: at most an f16 ulp apart)
         assert torch.equal(va, vpool) and (ka.float() - kpool.float()).abs().max().item() <= 4e-3 * kpool.float().abs().max().item()
         assert (got - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("nq,nkv", [(32, 8), (8, 2), (4, 1), (4, 4)])
+@pytest.mark.parametrize("nsplit", [2, 8, 16])
+def test_cluster_merge_of_decode_attention_matches_the_global_merge(nq, nkv, nsplit):
+    """One or two sequences: the KV splits of a (sequence, kv head) run as one thread-block cluster and meet in the first
+    CTA's shared memory.  Against the same kernel with the merge through global memory, and against fp32 PyTorch; lengths
+    that leave most splits empty are included."""
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = _dev()
+    hd, page, G = 128, 64, nq // nkv
+    g = torch.Generator().manual_seed(5)
+    for lens in ([1], [100], [4096], [777, 3000]):
+        B = len(lens)
+        pps = (max(lens) + page - 1) // page
+        bt = torch.randperm(B * pps, generator=g).view(B, pps).to(torch.int32).to(dev)
+        kpool = torch.randn((B * pps, nkv, page, hd), generator=g).half().to(dev)
+        vpool = torch.randn((B * pps, nkv, page, hd), generator=g).half().to(dev)
+        q = torch.randn((B, nq, hd), generator=g).to(dev)
+        pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
+        try:
+            K.attn_decode_cluster_mode(1)
+            plain = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
+        finally:
+            K.attn_decode_cluster_mode(0)
+        got = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
+        again = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
+        assert torch.isfinite(got).all() and torch.equal(got, again)
+        assert (got - plain).abs().max().item() <= 1e-5 * max(1.0, plain.abs().max().item()), (lens, nsplit)
+        for b, L in enumerate(lens):
+            pages = bt[b].long()
+            Kc = kpool[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :L].float()
+            Vc = vpool[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :L].float()
+            sc = torch.einsum("hd,htd->ht", q[b], Kc.repeat_interleave(G, 0)) / hd ** 0.5
+            ref = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.repeat_interleave(G, 0))
+            assert (got[b] - ref).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item()), (lens, nsplit, b)
