@@ -184,7 +184,7 @@ def main() -> None:
         us = time_us(fn, a.iters, a.profile)
         elt = {K.KV_F32: 4, K.KV_F16: 2, K.KV_Q8: 1, K.KV_Q4: 0.5}[kvt]
         byts = 2.0 * B * ctx * nkv * hd * elt
-        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "heads": f"{nq}/{nkv}", "nsplit": a.nsplit, "cluster_merge": not a.no_cluster, "us": round(us, 2),
+        rows_out.append({"case": f"attn_decode/{a.kv}", "batch": B, "ctx": ctx, "heads": f"{nq}/{nkv}", "nsplit": a.nsplit, "launch_form": K.attn_decode_last_form(), "us": round(us, 2),
                          "GB/s": round(byts / us / 1e3, 1), f"hbm_frac_{tag.replace(' ', '_')}": round(byts / (us * 1e-6) / hbm, 3)})
     elif a.case == "attn_prefill":
         # one prompt chunk of --tokens queries whose first token sits at position --ctx (8B head layout, f16 / --kv pages)

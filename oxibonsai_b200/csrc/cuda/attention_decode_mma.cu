@@ -448,13 +448,14 @@ static int launch_mma(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
 
 // 0 = let the launcher decide, 1 = never use the cluster merge, 2 = use it wherever it can be launched
 static int g_cluster_mode = 0;
+// form of the last launch: 0 = splits merged through global memory, 8 / 4 = cluster merge with that many warps per CTA
+static int g_last_form = 0;
 
 // The cluster form: the grid's y extent (the splits) is the cluster dimension, 2 to 16 CTAs (more than 8 needs the
 // non-portable opt-in).  Returns BONSAI_CUDA_BAD_ARG when the device cannot hold one such cluster, and the caller
 // launches the plain form instead.
-template <int G>
+template <int G, int NW>
 static int launch_mma_cluster(const MmaAttnParams& p, dim3 grid, cudaStream_t st) {
-  constexpr int NW = 8;
   const int nsplit = (int)grid.y;
   const size_t smem = (size_t)NW * 4 * kMmaTileBytes + (size_t)NW * G * (kMmaHd + 2) * sizeof(float) +
                       (size_t)nsplit * G * (kMmaHd + 2) * sizeof(float);
@@ -491,6 +492,7 @@ static int launch_mma_cluster(const MmaAttnParams& p, dim3 grid, cudaStream_t st
   // a second wave of clusters would cost more than the merge through global memory that this form saves
   if (fits[dev][nsplit] < (int)(grid.x * grid.z)) return BONSAI_CUDA_BAD_ARG;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
+  if (e == cudaSuccess) g_last_form = NW;
   return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
@@ -517,16 +519,19 @@ static int attn_decode_mma_launch(const float* q, const MmaFused& f, const int* 
   // distributed shared memory, which takes the global round trip (partial store, fence, counter, reload) out of a
   // kernel that is all latency at this size.
   if (g_cluster_mode != 1 && wide && (nsplit == 2 || nsplit == 4 || nsplit == 8 || nsplit == 16)) {
+    // eight warps per CTA (one CTA per SM: a cluster of 16 then needs 16 SMs of one GPC); where the device cannot hold
+    // all clusters of the grid that way, four warps per CTA (two CTAs per SM, half the tile buffers)
     int rc = BONSAI_CUDA_BAD_ARG;
     switch (G) {
-      case 1: rc = launch_mma_cluster<1>(p, grid, stream); break;
-      case 2: rc = launch_mma_cluster<2>(p, grid, stream); break;
-      case 4: rc = launch_mma_cluster<4>(p, grid, stream); break;
-      case 8: rc = launch_mma_cluster<8>(p, grid, stream); break;
+      case 1: rc = launch_mma_cluster<1, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<1, 4>(p, grid, stream); break;
+      case 2: rc = launch_mma_cluster<2, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<2, 4>(p, grid, stream); break;
+      case 4: rc = launch_mma_cluster<4, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<4, 4>(p, grid, stream); break;
+      case 8: rc = launch_mma_cluster<8, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<8, 4>(p, grid, stream); break;
       default: break;
     }
     if (rc != BONSAI_CUDA_BAD_ARG) return rc;
   }
+  g_last_form = 0;
   switch (G) {
     case 1: return wide ? launch_mma<1, 8>(p, grid, stream) : launch_mma<1, 4>(p, grid, stream);
     case 2: return wide ? launch_mma<2, 8>(p, grid, stream) : launch_mma<2, 4>(p, grid, stream);
@@ -550,6 +555,7 @@ extern "C" {
 
 // 0 = cluster merge where the launcher finds it fits (default), 1 = never, 2 = same as 0 (kept for symmetry of the A/B switch).
 void bonsai_attn_decode_cluster_mode(int mode) { bonsai::g_cluster_mode = mode; }
+int bonsai_attn_decode_last_form() { return bonsai::g_last_form; }
 
 // QK-RMSNorm + RoPE + KV append + split-KV attention of one new token per sequence in a single launch, for f16 pages
 // and head_dim 128.  qkv: f32 [batch][qkv_stride] raw projections (q heads | k heads | v heads); positions[b] is the

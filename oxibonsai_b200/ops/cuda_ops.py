@@ -400,6 +400,12 @@ def attn_decode_cluster_mode(mode: int) -> None:
     l.bonsai_attn_decode_cluster_mode(int(mode))
 
 
+def attn_decode_last_form() -> int:
+    """How the last tensor-core decode attention was launched: 0 = splits merged through global memory, 8 or 4 = cluster
+    merge with that many warps per CTA."""
+    return int(lib().bonsai_attn_decode_last_form())
+
+
 _capture_lock = __import__("threading").Lock()
 
 
