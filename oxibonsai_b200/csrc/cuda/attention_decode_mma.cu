@@ -519,14 +519,15 @@ static int attn_decode_mma_launch(const float* q, const MmaFused& f, const int* 
   // distributed shared memory, which takes the global round trip (partial store, fence, counter, reload) out of a
   // kernel that is all latency at this size.
   if (g_cluster_mode != 1 && wide && (nsplit == 2 || nsplit == 4 || nsplit == 8 || nsplit == 16)) {
-    // eight warps per CTA (one CTA per SM: a cluster of 16 then needs 16 SMs of one GPC); where the device cannot hold
-    // all clusters of the grid that way, four warps per CTA (two CTAs per SM, half the tile buffers)
+    // Eight warps per CTA, one CTA per SM: a cluster of 16 needs 16 SMs of one GPC, so eight such clusters (one sequence,
+    // eight kv heads) do not all fit and that shape keeps the global merge unless it is launched with 8 splits.  A
+    // four-warp form at two CTAs per SM does fit but measured slower inside a decode step (1.633 against 1.613 ms).
     int rc = BONSAI_CUDA_BAD_ARG;
     switch (G) {
-      case 1: rc = launch_mma_cluster<1, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<1, 4>(p, grid, stream); break;
-      case 2: rc = launch_mma_cluster<2, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<2, 4>(p, grid, stream); break;
-      case 4: rc = launch_mma_cluster<4, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<4, 4>(p, grid, stream); break;
-      case 8: rc = launch_mma_cluster<8, 8>(p, grid, stream); if (rc == BONSAI_CUDA_BAD_ARG) rc = launch_mma_cluster<8, 4>(p, grid, stream); break;
+      case 1: rc = launch_mma_cluster<1, 8>(p, grid, stream); break;
+      case 2: rc = launch_mma_cluster<2, 8>(p, grid, stream); break;
+      case 4: rc = launch_mma_cluster<4, 8>(p, grid, stream); break;
+      case 8: rc = launch_mma_cluster<8, 8>(p, grid, stream); break;
       default: break;
     }
     if (rc != BONSAI_CUDA_BAD_ARG) return rc;

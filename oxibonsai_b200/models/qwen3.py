@@ -313,6 +313,11 @@ class Qwen3Runner:
         # 11.0 / 10.1 / 9.9 us against 15.7 / 10.5 / 9.9 us for 32 splits), and 16 splits fit one thread-block cluster, whose
         # CTAs merge through distributed shared memory.
         self.nsplit = nsplit or (16 if max_seq <= 8192 else max(4, min(64, 128 // max(1, nkv))))
+        if os.environ.get("OXIBONSAI_ATTN_CLUSTER", "1") == "0":       # A/B switch: merge the KV splits through global memory
+            K.attn_decode_cluster_mode(1)
+        self.nsplit_override = os.environ.get("OXIBONSAI_ATTN_SPLITS")
+        if nsplit is None and self.nsplit_override:
+            self.nsplit = max(1, int(self.nsplit_override))
         self.fast = fast
         B = max_batch
         f32 = dict(dtype=torch.float32, device=dev)

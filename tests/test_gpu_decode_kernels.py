@@ -365,7 +365,7 @@ def test_cluster_merge_of_decode_attention_matches_the_global_merge(nq, nkv, nsp
         got = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
         again = K.attn_decode(q, pos, bt, nq, nkv, hd, K.KV_F16, page, kpool, vpool, nsplit=nsplit)
         assert torch.isfinite(got).all() and torch.equal(got, again)
-        assert (got - plain).abs().max().item() <= 1e-5 * max(1.0, plain.abs().max().item()), (lens, nsplit)
+        assert (got - plain).abs().max().item() <= 1e-4 * max(1.0, plain.abs().max().item()), (lens, nsplit)
         for b, L in enumerate(lens):
             pages = bt[b].long()
             Kc = kpool[pages].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :L].float()
