@@ -241,7 +241,7 @@ enum PrefillPtr {
 
 // Chunks of at most this many tokens run like a decode batch (mma.sync GEMMs, split-KV attention); the small-chunk
 // workspace holds kSmallChunk rows of kSmallSplits splits.
-constexpr int kSmallChunk = 32, kSmallSplits = 8;
+constexpr int kSmallChunk = 32, kSmallSplits = 16;
 
 static inline int pf_gemm(Runner& r, const void* codes, const void* scales, const void* x, int x_ld, float* out_f32, const float* residual,
                           void* out_f16, int* status, int n_rows, int K, int T, int epi, int out_ld, int sms, const void* dense_w,
@@ -290,6 +290,7 @@ static int prefill_chunk(Runner& r, const uint64_t* sp, const uint64_t* pp, int 
   int sm_splits = (4 * 148) / (nkv * T);
   if (sm_splits < 1) sm_splits = 1;
   if (sm_splits > kSmallSplits) sm_splits = kSmallSplits;
+  while (sm_splits & (sm_splits - 1)) sm_splits &= sm_splits - 1;   // a power of two: 2 to 16 splits can run as one cluster
   auto to_f16 = [&](const float* w) {
     return hm ? bonsai_norm_to_f16_hmma(h, hidden, w, r.eps, T, hidden, xn, xn_ld, st)
               : bonsai_norm_to_f16_paired(h, hidden, w, r.eps, T, hidden, xn, xn_ld, 0, st);
