@@ -464,350 +464,6 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
   }
 }
 
-// ---- several dependent GEMVs in one launch ---------------------------------------------------------------------------
-// The attention-output, gate/up and down projections of a layer depend on one another through the whole hidden state,
-// so as separate kernels each pays a drain, a launch and a refill of the copy pipeline (about 4 us of a ~5-10 us
-// kernel).  Here they are phases of one kernel: every CTA works through its tile range of every phase, the producer
-// lane streams the phases' weights back to back (weights depend on nothing, so the ring never drains), and between
-// phases the CTAs meet at a counter in global memory - they are all resident (at most one CTA per SM, at most 148 CTAs).
-// Every wait on the counter is bounded; an expired wait sets the abort flag, the CTA still counts itself in at the
-// remaining barriers so that the counter ends at zero, and the status word tells the host.
-constexpr int kS16MaxPhases = 3;
-struct S16Phase {
-  const uint8_t* w;
-  const float* x;
-  const float* norm_w;
-  float* out;
-  const float* residual;
-  int N, K, epi;
-};
-struct S16Chain {
-  S16Phase ph[kS16MaxPhases];
-  int nphases;
-  float eps;
-  int* status;
-  int* counter;              // device int, zero between launches
-  uint32_t spin_limit;       // polls of the counter before a CTA gives up
-  int kmax;                  // largest K of the phases (shared-memory layout)
-  const uint8_t* next_w;
-  unsigned long long next_bytes;
-};
-
-__device__ __forceinline__ int s16_ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_chain_kernel(S16Chain c, TpComm tp) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int kmax = c.kmax;
-  uint8_t* ring = smem;
-  int8_t* xq = reinterpret_cast<int8_t*>(smem + kS16Stages * kS16StageBytes);          // [2][K + 32] of the running phase
-  S16Step* steps = reinterpret_cast<S16Step*>(xq + 2 * (kmax + 32));                     // [ng][4]
-  float* part = reinterpret_cast<float*>(steps + (size_t)(kmax >> 7) * 4);               // [kS16MaxTiles][kS16Warps][16]
-  uint64_t* full = reinterpret_cast<uint64_t*>(part + kS16MaxTiles * kS16Warps * 16);
-  uint64_t* empty = full + kS16Stages;
-  float* s32 = reinterpret_cast<float*>(empty + kS16Stages);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(s32 + 32);
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    for (int s = 0; s < kS16Stages; ++s) {
-      tc::mbar_init(&full[s], 1);
-      tc::mbar_init(&empty[s], kS16Warps);
-    }
-    *abort_flag = 0;
-    tc::mbar_fence_init();
-  }
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  __syncthreads();
-
-  if (warp == kS16Warps) {
-    // ---- producer: the phases' byte ranges of this CTA, back to back through the ring ----
-    if (lane == 0) {
-      const unsigned long long pf_units = c.next_w != nullptr ? c.next_bytes / 16 : 0;
-      const unsigned long long pf_lo = pf_units * blockIdx.x / gridDim.x, pf_hi = pf_units * (blockIdx.x + 1) / gridDim.x;
-      const uint8_t* pf_ptr = c.next_w + pf_lo * 16;
-      unsigned long long pf_left = (pf_hi - pf_lo) * 16;
-      const unsigned long long pf_piece = 32768;
-      int slot = 0, gs = 0;
-      uint32_t par = 1;
-      bool ok = true;
-      for (int p = 0; p < c.nphases && ok; ++p) {
-        const S16Phase& a = c.ph[p];
-        const int ng = a.K >> 7, ntiles = (a.N + 15) >> 4;
-        const int tile_lo = (int)(((long long)blockIdx.x * ntiles) / gridDim.x);
-        const int tile_hi = (int)(((long long)(blockIdx.x + 1) * ntiles) / gridDim.x);
-        const int nb_total = (tile_hi - tile_lo) * ng;
-        const int nstage_total = (nb_total + kS16StageBlocks - 1) / kS16StageBlocks;
-        const uint8_t* wbase = a.w + (size_t)tile_lo * ng * kS16BlockBytes;
-        for (int s = 0; s < nstage_total; ++s, ++gs, slot = slot + 1 == kS16Stages ? 0 : slot + 1) {
-          if (slot == 0) par ^= 1u;
-          if (gs >= kS16Stages && !s16_poll(&empty[slot], par ^ 1u, abort_flag)) { ok = false; break; }
-          const int b0 = s * kS16StageBlocks;
-          const int nb = min(kS16StageBlocks, nb_total - b0);
-          const uint32_t bytes = (uint32_t)nb * kS16BlockBytes;
-          tc::mbar_arrive_expect_tx(&full[slot], bytes);
-          tc::bulk_g2s(ring + (size_t)slot * kS16StageBytes, wbase + (size_t)b0 * kS16BlockBytes, bytes, &full[slot]);
-          if (pf_left > 0) {
-            const unsigned long long n = pf_left < pf_piece ? pf_left : pf_piece;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr), "r"((uint32_t)n) : "memory");
-            pf_ptr += n;
-            pf_left -= n;
-          }
-        }
-      }
-      while (pf_left > 0) {
-        const unsigned long long n = pf_left < pf_piece ? pf_left : pf_piece;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr), "r"((uint32_t)n) : "memory");
-        pf_ptr += n;
-        pf_left -= n;
-      }
-      if (*abort_flag) {   // copies that nobody waits for any more: a bounded time to land before the CTA's memory goes
-        for (int sl = 0; sl < kS16Stages; ++sl)
-          for (uint32_t i = 0; i < (1u << 16); ++i)
-            if (tc::mbar_try_wait(&full[sl], 0) || tc::mbar_try_wait(&full[sl], 1)) break;
-      }
-    }
-    return;
-  }
-
-  // ---- consumers ----
-  constexpr int NT = kS16Warps * 32;
-  bool any_tp = false;
-  for (int p = 0; p < c.nphases; ++p) any_tp |= c.ph[p].epi == SEPI_TP;
-  int n_tp_done = 0;
-  int slot = 0;
-  uint32_t par = 0;
-  int bad = 0;                           // status code of this thread's expired waits (5 ring, 6 grid barrier)
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int tp_e0 = any_tp ? ld_volatile(tp.epoch) : 0;
-  for (int p = 0; p < c.nphases; ++p) {
-    const S16Phase a = c.ph[p];
-    const int K = a.K, ng = K >> 7, term_stride = K + 32;
-    const int ntiles = (a.N + 15) >> 4;
-    const int tile_lo = (int)(((long long)blockIdx.x * ntiles) / gridDim.x);
-    const int tile_hi = (int)(((long long)(blockIdx.x + 1) * ntiles) / gridDim.x);
-    const int nb_total = (tile_hi - tile_lo) * ng;
-    const int nstage_total = (nb_total + kS16StageBlocks - 1) / kS16StageBlocks;
-    for (int i = tid; i < kS16MaxTiles * kS16Warps * 16; i += NT) part[i] = 0.0f;
-    if (nb_total > 0) {
-      // activations of the phase: written by other CTAs in the phase before (p > 0), so they are read past L1
-      const int nch = K >> 2;
-      const float4* x4 = reinterpret_cast<const float4*>(a.x);
-      float4 keep[2];                                // the first two chunks of a thread stay in registers (all of K = 4096)
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int ch = tid + i * NT;
-        keep[i] = ch < nch ? __ldcg(x4 + ch) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      }
-      float inv = 1.0f;
-      if (a.norm_w != nullptr) {
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) ss += keep[i].x * keep[i].x + keep[i].y * keep[i].y + keep[i].z * keep[i].z + keep[i].w * keep[i].w;
-        for (int ch = tid + 2 * NT; ch < nch; ch += NT) {
-          const float4 v = __ldcg(x4 + ch);
-          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) s32[warp] = ss;
-        s16_bar();
-        float tsum = lane < kS16Warps ? s32[lane] : 0.0f;
-        tsum = warp_sum(tsum);
-        inv = 1.0f / sqrtf(tsum / (float)K + c.eps);
-      }
-      for (int ch = tid, it = 0; ch < nch; ch += NT, ++it) {   // whole warps enter (K % 128 == 0): ch / 32 is the warp's group
-        float4 v = it == 0 ? keep[0] : (it == 1 ? keep[1] : __ldcg(x4 + ch));
-        if (a.norm_w != nullptr) {
-          const float4 ww = reinterpret_cast<const float4*>(a.norm_w)[ch];
-          v.x *= ww.x * inv; v.y *= ww.y * inv; v.z *= ww.z * inv; v.w *= ww.w * inv;
-        }
-        const float amax = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        const float sx = amax > 0.0f ? amax * (1.0f / 127.0f) : 1.0f;
-        const float rs = 1.0f / sx;
-        constexpr float kMagic = 12582912.0f;        // see bitgemv_s16_kernel: rint through the low mantissa bits
-        const float f[4] = {v.x * rs, v.y * rs, v.z * rs, v.w * rs};
-        uint32_t w1 = 0, w2 = 0;
-        float fs1 = 0.0f, fs2 = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float m1 = f[e] + kMagic, r1 = m1 - kMagic;
-          const float m2 = (f[e] - r1) * kS16Term2 + kMagic, r2 = m2 - kMagic;
-          w1 |= (__float_as_uint(m1) & 255u) << (8 * e);
-          w2 |= (__float_as_uint(m2) & 255u) << (8 * e);
-          fs1 += r1;
-          fs2 += r2;
-        }
-        reinterpret_cast<uint32_t*>(xq)[ch] = w1;
-        reinterpret_cast<uint32_t*>(xq + term_stride)[ch] = w2;
-#pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-          fs1 += __shfl_xor_sync(0xffffffffu, fs1, o);
-          fs2 += __shfl_xor_sync(0xffffffffu, fs2, o);
-        }
-        if ((lane & 7) == 0) {
-          const int j = lane >> 3;
-          S16Step r;
-          r.og0 = -(int)fs1 * (1 << (2 * j));
-          r.og1 = -(int)fs2 * (1 << (2 * j));
-          r.sx = sx * (1.0f / (float)(1 << (2 * j)));
-          r.pad = 0.0f;
-          steps[(size_t)(ch >> 5) * 4 + j] = r;
-        }
-      }
-    }
-    s16_bar();
-
-    // ---- main loop of the phase: the ring slot and parity carry on from the phase before ----
-    {
-      const int g = lane >> 2, t = lane & 3;
-      const int my_step = g >> 1;
-      const uint32_t sel[4] = {my_step == 0 ? 1u : 0u, my_step == 1 ? 1u : 0u, my_step == 2 ? 1u : 0u, my_step == 3 ? 1u : 0u};
-      const int8_t* xq_lane = xq + (g & 1) * term_stride + 32 * my_step + 8 * t;
-      const S16Step* st_lane = steps + t;
-      const bool aligned = (ng % kS16Bpw) == 0;
-      int cur_tile = -1;
-      float tot_lo = 0.0f, tot_hi = 0.0f;
-      auto flush = [&]() {
-        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 1);
-        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 1);
-        tot_lo += __shfl_xor_sync(0xffffffffu, tot_lo, 2);
-        tot_hi += __shfl_xor_sync(0xffffffffu, tot_hi, 2);
-        if (cur_tile >= 0 && t == 0) {
-          float* pp = part + ((size_t)cur_tile * kS16Warps + warp) * 16;
-          pp[g] += tot_lo;
-          pp[g + 8] += tot_hi;
-        }
-        tot_lo = tot_hi = 0.0f;
-      };
-      int tl = (kS16Bpw * warp) / ng, grp = (kS16Bpw * warp) - tl * ng;
-      for (int s = 0; s < nstage_total; ++s) {
-        if (!s16_wait(&full[slot], par, lane, abort_flag)) { bad = 5; break; }
-        const uint8_t* st = ring + (size_t)slot * kS16StageBytes + (size_t)(kS16Bpw * warp) * kS16BlockBytes;
-        const int left = nb_total - (s * kS16StageBlocks + kS16Bpw * warp);
-        if (aligned && left >= kS16Bpw) {
-          if (tl != cur_tile) {
-            flush();
-            cur_tile = tl;
-          }
-          s16_blocks<kS16Bpw>(st, xq_lane + (size_t)grp * 128, st_lane + (size_t)grp * 4, lane, sel, tot_lo, tot_hi);
-        } else {
-          int tl_i = tl, grp_i = grp;
-          for (int i = 0; i < kS16Bpw && i < left; ++i) {
-            if (tl_i != cur_tile) {
-              flush();
-              cur_tile = tl_i;
-            }
-            s16_block(st + (size_t)i * kS16BlockBytes, xq_lane + (size_t)grp_i * 128, st_lane + (size_t)grp_i * 4, lane, sel, tot_lo, tot_hi);
-            if (++grp_i == ng) {
-              grp_i = 0;
-              ++tl_i;
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&empty[slot]);
-        if (++slot == kS16Stages) {
-          slot = 0;
-          par ^= 1u;
-        }
-        grp += kS16StageBlocks;
-        while (grp >= ng) {
-          grp -= ng;
-          ++tl;
-        }
-      }
-      flush();
-    }
-    s16_bar();
-    const bool aborted = *abort_flag != 0;
-
-    // ---- reduce over warps (fixed order) and epilogue of the phase ----
-    const int rows_local = (tile_hi - tile_lo) * 16;
-    const int row_base = tile_lo * 16;
-    if (!aborted && a.epi == SEPI_SWIGLU) {
-      for (int pi = tid; pi < rows_local / 2; pi += NT) {
-        const int r0 = 2 * pi, tl = r0 >> 4, rr = r0 & 15;
-        float gate = 0.0f, up = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kS16Warps; ++w) {
-          gate += part[((size_t)tl * kS16Warps + w) * 16 + rr];
-          up += part[((size_t)tl * kS16Warps + w) * 16 + rr + 1];
-        }
-        const int row = row_base + r0;
-        if (row + 1 < a.N) a.out[row >> 1] = gate / (1.0f + __expf(-gate)) * up;
-      }
-    } else if (!aborted) {
-      const int tp_epoch = tp_e0 + n_tp_done;
-      for (int i = tid; i < rows_local; i += NT) {
-        const int tl = i >> 4, rr = i & 15;
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kS16Warps; ++w) v += part[((size_t)tl * kS16Warps + w) * 16 + rr];
-        const int row = row_base + i;
-        if (row >= a.N) continue;
-        if (a.epi == SEPI_STORE) {
-          a.out[row] = v;
-        } else if (a.epi == SEPI_RESID) {
-          a.out[row] = __ldcg(a.residual + row) + v;
-        } else {
-          const uint32_t tag = (uint32_t)tp_epoch + 1u;
-          const int parity = tp_epoch & 1;
-          const unsigned long long msg = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
-          if (tp.mc != nullptr) {
-            tp_mc_st_msg(tp_ll_slot_mc(tp, parity, tp.rank) + row, msg);
-          } else {
-            for (int q = 0; q < tp.size; ++q)
-              if (q != tp.rank) tp_st_msg(tp_ll_slot(tp, q, parity, tp.rank) + row, msg);
-          }
-          float sum = a.residual != nullptr ? __ldcg(a.residual + row) : 0.0f;
-          bool alive = true;
-          for (int sr = 0; sr < tp.size; ++sr) sum += sr == tp.rank ? v : tp_recv_msg(tp, tp_ll_slot(tp, tp.rank, parity, sr) + row, tag, alive);
-          a.out[row] = sum;
-        }
-      }
-    }
-    if (a.epi == SEPI_TP) ++n_tp_done;
-
-    // ---- all CTAs meet before the next phase reads what this one wrote ----
-    if (p + 1 < c.nphases) {
-      s16_bar();                                   // this CTA's stores of the phase are issued
-      if (tid == 0) {
-        __threadfence();
-        atomicAdd(c.counter, 1);
-        if (!*abort_flag) {
-          const int target = (p + 1) * (int)gridDim.x;
-          bool met = false;
-          for (uint32_t i = 0; i < c.spin_limit; ++i) {
-            if (s16_ld_acquire_gpu(c.counter) >= target) { met = true; break; }
-            __nanosleep(20);
-          }
-          if (!met) {
-            *abort_flag = 1;
-            bad = 6;
-          }
-          __threadfence();
-        }
-      }
-      s16_bar();
-    }
-  }
-  // ---- count out: the last CTA of the grid zeroes the counter and moves the exchange counter on ----
-  s16_bar();
-  if (bad != 0 && c.status != nullptr) atomicExch(c.status, bad);
-  if (tid == 0) {
-    __threadfence();
-    const int prev = atomicAdd(c.counter, 1);
-    if (prev == c.nphases * (int)gridDim.x - 1) {
-      *c.counter = 0;
-      if (any_tp) *tp.epoch = tp_e0 + n_tp_done;
-      __threadfence();
-    }
-  }
-}
-
 // Planar-SM -> S16.  One thread per output 32-bit word (code words and scale pairs).
 // Code word i (0..3) of lane (g, t): rows g (i even) or g + 8 (i odd) of the tile; byte b, 2-bit field j = the code of
 // input 128 * group + 32 * j + 8 * t + (i >= 2 ? 4 : 0) + b.
@@ -950,69 +606,6 @@ int bonsai_bitgemv_s16_pf(const void* w16, const float* x, const float* norm_w, 
                           cudaStream_t stream) {
   if (next_w != nullptr && (reinterpret_cast<uintptr_t>(next_w) & 15) != 0) return BONSAI_CUDA_BAD_ARG;
   return bitgemv_s16_launch(w16, x, norm_w, eps, out, residual, N, K, epi, comm, status, next_w, next_bytes, stream);
-}
-
-// Up to three dependent GEMVs in one launch (see bitgemv_s16_chain_kernel): phase i computes out[i] from x[i] with the
-// epilogue epi[i] exactly as bonsai_bitgemv_s16 would; x[i] may be what an earlier phase wrote.  `counter` is a device
-// int that is zero before the first launch (the kernel leaves it at zero); `spin_limit` bounds every wait on it
-// (0 = the default, about a second).  Returns BONSAI_CUDA_BAD_ARG for shapes it declines (the caller then launches the
-// phases as separate kernels): more than 12 row tiles per CTA in some phase, or K outside 128..16384.
-int bonsai_bitgemv_s16_chain(int nphases, const void* const* w16, const float* const* x, const float* const* norm_w, float eps,
-                             float* const* out, const float* const* residual, const int* N, const int* K, const int* epi,
-                             const void* comm, int* counter, unsigned spin_limit, int* status, const void* next_w, size_t next_bytes,
-                             cudaStream_t stream) {
-  using namespace bonsai;
-  if (nphases < 1 || nphases > kS16MaxPhases || counter == nullptr) return BONSAI_CUDA_BAD_ARG;
-  if (next_w != nullptr && (reinterpret_cast<uintptr_t>(next_w) & 15) != 0) return BONSAI_CUDA_BAD_ARG;
-  S16Chain c{};
-  int kmax = 0, max_tiles = 0;
-  bool any_tp = false;
-  for (int i = 0; i < nphases; ++i) {
-    if (K[i] % 128 != 0 || K[i] < 128 || K[i] > 16384 || N[i] <= 0 || epi[i] < 0 || epi[i] > 3) return BONSAI_CUDA_BAD_ARG;
-    if (epi[i] == SEPI_RESID && residual[i] == nullptr) return BONSAI_CUDA_BAD_ARG;
-    if (epi[i] == SEPI_SWIGLU && (N[i] & 1)) return BONSAI_CUDA_BAD_ARG;
-    if (epi[i] == SEPI_TP && comm == nullptr) return BONSAI_CUDA_BAD_ARG;
-    any_tp |= epi[i] == SEPI_TP;
-    kmax = K[i] > kmax ? K[i] : kmax;
-    const int nt = (N[i] + 15) / 16;
-    max_tiles = nt > max_tiles ? nt : max_tiles;
-    c.ph[i] = S16Phase{static_cast<const uint8_t*>(w16[i]), x[i], norm_w[i], out[i], residual[i], N[i], K[i], epi[i]};
-  }
-  // every CTA must be resident while the others wait for it: one CTA per SM
-  const int grid = max_tiles < 148 ? max_tiles : 148;
-  for (int i = 0; i < nphases; ++i)
-    if (((N[i] + 15) / 16 + grid - 1) / grid > kS16MaxTiles) return BONSAI_CUDA_BAD_ARG;
-  TpComm tp{};
-  if (any_tp) {
-    tp = *static_cast<const TpComm*>(comm);
-    for (int i = 0; i < nphases; ++i)
-      if (epi[i] == SEPI_TP && (size_t)N[i] > tp.lay.recv_elems) return BONSAI_CUDA_BAD_ARG;
-  }
-  const size_t smem = s16_smem_bytes(kmax);
-  static bool attr_set[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BONSAI_CUDA_LAUNCH_FAILED;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(bitgemv_s16_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
-      return BONSAI_CUDA_LAUNCH_FAILED;
-    attr_set[dev] = true;
-  }
-  c.nphases = nphases;
-  c.eps = eps;
-  c.status = status;
-  c.counter = counter;
-  c.spin_limit = spin_limit != 0 ? spin_limit : (1u << 24);
-  c.kmax = kmax;
-  c.next_w = static_cast<const uint8_t*>(next_w);
-  c.next_bytes = next_w != nullptr ? next_bytes : 0;
-  cudaError_t e;
-  if (g_s16_pdl) {
-    e = launch_pdl(bitgemv_s16_chain_kernel, dim3(grid), dim3(kS16Threads), smem, stream, c, tp);
-  } else {
-    bitgemv_s16_chain_kernel<<<grid, kS16Threads, smem, stream>>>(c, tp);
-    e = cudaGetLastError();
-  }
-  return e == cudaSuccess ? BONSAI_CUDA_OK : BONSAI_CUDA_LAUNCH_FAILED;
 }
 
 }  // extern "C"

@@ -46,8 +46,6 @@ int bonsai_attn_decode_qkv_f16(const float*, int, const float*, const float*, fl
 int bonsai_norm_to_f16_hmma(const float*, int, const float*, float, int, int, void*, int, cudaStream_t);
 int bonsai_bitgemm_hmma(const void*, const void*, const void*, int, float*, const float*, void*, int, int, int, int, int, cudaStream_t);
 int bonsai_bitgemm_hmma_tp(const void*, const void*, const void*, const void*, int, float*, const float*, int, int, int, int, cudaStream_t);
-int bonsai_bitgemv_s16_chain(int, const void* const*, const float* const*, const float* const*, float, float* const*, const float* const*,
-                             const int*, const int*, const int*, const void*, int*, unsigned, int*, const void*, size_t, cudaStream_t);
 int bonsai_attn_prefill_order(const float*, int, int, const int*, int, int, int, int, int, const void*, const void*, const float*,
                               const float*, void*, int, int, cudaStream_t);
 int bonsai_embed_rows_f16(const void*, const int*, float*, int, int, int, cudaStream_t);
@@ -75,7 +73,6 @@ enum StepPtr {
   SP_TOKENS = 0, SP_POSITIONS, SP_BLOCK_TABLE, SP_H, SP_QKV, SP_Q, SP_ATTN, SP_ACT, SP_LOGITS, SP_WS_ACC, SP_WS_ML,
   SP_TEMPS, SP_TOPKS, SP_TOPPS, SP_RNG, SP_OUT_TOKENS, SP_PARTIAL, SP_ALLOW_MASK, SP_ATTN_COUNTERS,
   SP_STATUS,   // device int: non-zero after a bounded wait inside a kernel of the step expired
-  SP_CHAIN_CTR,   // device int, zero between launches: where the CTAs of the fused O / gate-up / down kernel meet (0 = not fused)
   SP_COUNT
 };
 
@@ -179,7 +176,6 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
   // GEMV (bitgemv_stream.cu) when that form was built and the shape fits; epi 3 = row-parallel sum over the
   // tensor-parallel group + residual inside the same kernel.
   int* status = P<int>(sp[SP_STATUS]);
-  int* chain_ctr = P<int>(sp[SP_CHAIN_CTR]);
   // (next, next_n, next_k): the S16 matrix of the GEMV that follows in the stream, which this one requests into L2.
   auto linear = [&](const uint64_t* lp, int w_codes, int w_s16, const float* x, const float* norm_w, float* out, const float* residual,
                     int n, int k, int epi, uint64_t next, int next_n, int next_k) -> int {
@@ -202,37 +198,15 @@ static int decode_step(Runner& r, const uint64_t* sp, int batch, int flags, int 
       RC(linear(lp, LP_QKV_CODES, LP_QKV_S16, h + (size_t)b * hidden, P<float>(lp[LP_ATTN_NORM]), qkv + (size_t)b * qkv_n, nullptr,
                 qkv_n, hidden, 0, lp[LP_O_S16], hidden, qd));
     RC(qkv_attention(r, l, lp, sp, qkv, qkv_n, q, attn, positions, bt, batch, r.ic[IC_NSPLIT], st));
-    // The three projections after the attention as phases of one kernel (bitgemv_s16_chain_kernel) where all are in the
-    // streamed layout and the shapes fit; otherwise, or when the kernel declines, one kernel each.
-    bool chained = false;
-    if (chain_ctr != nullptr && r.ic[IC_FAST] == 1 && lp[LP_O_S16] != 0 && lp[LP_GU_S16] != 0 && lp[LP_DOWN_S16] != 0) {
-      chained = true;
-      for (int b = 0; b < batch && chained; ++b) {
-        float* hb = h + (size_t)b * hidden;
-        float* ab = act + (size_t)b * inter;
-        const void* w3[3] = {P<void>(lp[LP_O_S16]), P<void>(lp[LP_GU_S16]), P<void>(lp[LP_DOWN_S16])};
-        const float* x3[3] = {attn + (size_t)b * qd, hb, ab};
-        const float* n3[3] = {nullptr, P<float>(lp[LP_FFN_NORM]), nullptr};
-        float* o3[3] = {hb, ab, hb};
-        const float* r3[3] = {hb, nullptr, hb};
-        const int N3[3] = {hidden, 2 * inter, hidden}, K3[3] = {qd, hidden, inter}, e3[3] = {tp ? 3 : 1, 2, tp ? 3 : 1};
-        const int rc = bonsai_bitgemv_s16_chain(3, w3, x3, n3, r.eps, o3, r3, N3, K3, e3, r.comm, chain_ctr, 0, status, P<void>(next_qkv),
-                                                next_qkv != 0 ? bonsai_s16_bytes(qkv_n, hidden) : 0, st);
-        if (rc == BONSAI_CUDA_BAD_ARG && b == 0) chained = false;   // a shape the fused kernel declines
-        else RC(rc);
-      }
-    }
-    if (!chained) {
-      for (int b = 0; b < batch; ++b)
-        RC(linear(lp, LP_O_CODES, LP_O_S16, attn + (size_t)b * qd, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd,
-                  tp ? 3 : 1, lp[LP_GU_S16], 2 * inter, hidden));
-      for (int b = 0; b < batch; ++b)
-        RC(linear(lp, LP_GU_CODES, LP_GU_S16, h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), act + (size_t)b * inter, nullptr,
-                  2 * inter, hidden, 2, lp[LP_DOWN_S16], hidden, inter));
-      for (int b = 0; b < batch; ++b)
-        RC(linear(lp, LP_DOWN_CODES, LP_DOWN_S16, act + (size_t)b * inter, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden,
-                  inter, tp ? 3 : 1, next_qkv, qkv_n, hidden));
-    }
+    for (int b = 0; b < batch; ++b)
+      RC(linear(lp, LP_O_CODES, LP_O_S16, attn + (size_t)b * qd, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden, qd,
+                tp ? 3 : 1, lp[LP_GU_S16], 2 * inter, hidden));
+    for (int b = 0; b < batch; ++b)
+      RC(linear(lp, LP_GU_CODES, LP_GU_S16, h + (size_t)b * hidden, P<float>(lp[LP_FFN_NORM]), act + (size_t)b * inter, nullptr,
+                2 * inter, hidden, 2, lp[LP_DOWN_S16], hidden, inter));
+    for (int b = 0; b < batch; ++b)
+      RC(linear(lp, LP_DOWN_CODES, LP_DOWN_S16, act + (size_t)b * inter, nullptr, h + (size_t)b * hidden, h + (size_t)b * hidden, hidden,
+                inter, tp ? 3 : 1, next_qkv, qkv_n, hidden));
   }
   if (!(flags & 2)) {
     if (!tp) {

@@ -383,12 +383,8 @@ class Qwen3Runner:
             for i, v in enumerate(vals):
                 lp[l * nlp + i] = v
         self._native = lib.bonsai_runner_create(icfg, cfg.eps, gp, lp)
-        # where the CTAs of the fused attention-output / gate-up / down kernel meet; OXIBONSAI_GEMV_CHAIN=0 keeps one kernel
-        # per projection (the A/B switch of that fusion)
-        self.chain_counter = torch.zeros(1, dtype=torch.int32, device=self.device) if os.environ.get("OXIBONSAI_GEMV_CHAIN", "1") != "0" else None
         sp = [self.tokens, self.positions, self.block_table, self.h, self.qkv, self.q, self.attn, self.act, self.logits, self.ws_acc,
-              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, self.allow_mask, self.attn_counters, self.status,
-              self.chain_counter]
+              self.ws_ml, self.temps, self.topks, self.topps, self.rng, self.tokens, self.partial, self.allow_mask, self.attn_counters, self.status]
         assert len(sp) == nsp
         self._step_ptrs = (C.c_uint64 * nsp)(*[0 if t is None else t.data_ptr() for t in sp])
         if self.tp is not None:

@@ -133,7 +133,6 @@ _S16_SIG = {
     "bonsai_repack_s16": [_vp, _vp, _i, _i, _vp, _vp],
     "bonsai_bitgemv_s16": [_vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
     "bonsai_s16_tune": [_i],
-    "bonsai_bitgemv_s16_chain": [_i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint, _vp, _vp, C.c_size_t, _vp],
 }
 _s16_declared = False
 EPI_TP = 3
@@ -226,27 +225,6 @@ def _qg():
         declare(_QG_SIG)
         _qg_declared = True
     return l
-
-
-def bitgemv_s16_chain(phases: list[dict], counter: torch.Tensor, eps: float = 1e-6, comm: int | None = None,
-                      status: torch.Tensor | None = None, spin_limit: int = 0) -> None:
-    """Up to three dependent streamed GEMVs in one launch.  Every phase is a dict with ``w`` (:class:`S16Weight`), ``x``,
-    ``out`` and optionally ``norm_w``, ``residual``, ``epi`` (as :func:`bitgemv_s16`); a later phase may read what an earlier
-    one wrote.  ``counter``: int32[1] device tensor, zero before the first use (the kernel leaves it at zero): where the CTAs
-    meet between phases.  Raises ``ValueError`` for shapes the fused kernel declines."""
-    n = len(phases)
-    assert 1 <= n <= 3 and counter.dtype == torch.int32 and counter.is_cuda
-    vps = lambda vals: (C.c_void_p * n)(*vals)
-    ints = lambda vals: (C.c_int * n)(*vals)
-    epis = [int(p.get("epi", EPI_STORE)) for p in phases]
-    rc = _s16().bonsai_bitgemv_s16_chain(
-        n, vps([p["w"].data.data_ptr() for p in phases]), vps([_f32c(p["x"]).data_ptr() for p in phases]),
-        vps([ptr(p.get("norm_w")) for p in phases]), eps, vps([p["out"].data_ptr() for p in phases]),
-        vps([ptr(p.get("residual")) for p in phases]), ints([p["w"].n for p in phases]), ints([p["w"].k for p in phases]), ints(epis),
-        comm, counter.data_ptr(), int(spin_limit), ptr(status), None, 0, stream())
-    if rc == -13:
-        raise ValueError("bitgemv_s16_chain declines these shapes")
-    check(rc, "bitgemv_s16_chain")
 
 
 def quant_gemv(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6,

@@ -373,45 +373,3 @@ def test_cluster_merge_of_decode_attention_matches_the_global_merge(nq, nkv, nsp
             sc = torch.einsum("hd,htd->ht", q[b], Kc.repeat_interleave(G, 0)) / hd ** 0.5
             ref = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), Vc.repeat_interleave(G, 0))
             assert (got[b] - ref).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item()), (lens, nsplit, b)
-
-
-@pytest.mark.parametrize("hidden,qd,inter", [(4096, 4096, 12288), (2560, 4096, 9728), (512, 512, 1024), (4096, 512, 1536)])
-def test_chained_gemvs_equal_the_separate_kernels(hidden, qd, inter):
-    """Attention-output -> gate/up (fused RMSNorm, SwiGLU) -> down as three phases of one launch: the same bits as three
-    launches of the streamed GEMV, on repeated launches (the meeting counter returns to zero), for the 8B and 4B shapes, a
-    tiny one (fewer tiles than SMs) and the shard shapes of a tensor-parallel rank."""
-    from oxibonsai_b200.ops import cuda_ops as K
-    dev = _dev()
-    mats = []
-    for seed, (rows, cols) in enumerate([(hidden, qd), (2 * inter, hidden), (hidden, inter)]):
-        raw, _ = _random_quant(TQ2_0_G128, rows, cols, 20 + seed)
-        pw = K.PlanarWeight(rows, cols, dev).fill_from_gguf(torch.from_numpy(raw).to(dev), TQ2_0_G128, cols, 0, rows)
-        mats.append(K.S16Weight(pw))
-    o_w, gu_w, down_w = mats
-    g = torch.Generator().manual_seed(2)
-    attn, h0, nw = torch.randn(qd, generator=g).to(dev), torch.randn(hidden, generator=g).to(dev), (torch.rand(hidden, generator=g) + 0.5).to(dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    # three launches
-    h = h0.clone()
-    K.bitgemv_s16(o_w, attn, epi=K.EPI_RESID, residual=h, out=h, status=status)
-    act = K.bitgemv_s16(gu_w, h, norm_w=nw, eps=1e-6, epi=K.EPI_SWIGLU, status=status)
-    K.bitgemv_s16(down_w, act, epi=K.EPI_RESID, residual=h, out=h, status=status)
-    want_h, want_act = h.clone(), act.clone()
-    # one launch, three times over
-    counter = torch.zeros(1, dtype=torch.int32, device=dev)
-    for _ in range(3):
-        h2, act2 = h0.clone(), torch.zeros(inter, device=dev)
-        K.bitgemv_s16_chain([dict(w=o_w, x=attn, out=h2, residual=h2, epi=K.EPI_RESID),
-                             dict(w=gu_w, x=h2, norm_w=nw, out=act2, epi=K.EPI_SWIGLU),
-                             dict(w=down_w, x=act2, out=h2, residual=h2, epi=K.EPI_RESID)], counter, eps=1e-6, status=status)
-        if min(hidden, 2 * inter) // 16 >= 148:        # the same tile ranges per CTA as the separate launches: the same bits
-            assert torch.equal(act2, want_act) and torch.equal(h2, want_h)
-        else:                                          # fewer tiles than SMs: another split of a tile's groups over the warps
-            assert torch.allclose(act2, want_act, rtol=1e-4, atol=1e-5) and torch.allclose(h2, want_h, rtol=1e-4, atol=1e-4)
-        assert int(counter.item()) == 0 and int(status.item()) == 0
-    # a phase with more than 12 row tiles per CTA is declined on the host
-    if hidden == 512:
-        raw, _ = _random_quant(TQ2_0_G128, 148 * 16 * 13, 128, 1)
-        big = K.S16Weight(K.PlanarWeight(148 * 16 * 13, 128, dev).fill_from_gguf(torch.from_numpy(raw).to(dev), TQ2_0_G128, 128, 0, 148 * 16 * 13))
-        with pytest.raises(ValueError):
-            K.bitgemv_s16_chain([dict(w=big, x=torch.zeros(128, device=dev), out=torch.zeros(148 * 16 * 13, device=dev))], counter)
