@@ -128,6 +128,33 @@ __device__ __forceinline__ float tp_recv_msg(const TpComm& c, const unsigned lon
   atomicExch(c.status, 2);
   return 0.0f;
 }
+// The same for all peers at once: acc + sum over ranks (in rank order) of their value for this element, `own` being this
+// rank's.  slot_of(r) is the address of rank r's {value, tag} slot in this rank's buffer.  Every round requests all
+// outstanding slots before it looks at any of them, so the round trips to L2 overlap instead of queueing up behind one
+// another (seven peers: one latency per round, not seven); the values are added only when all have arrived, in rank
+// order, so every rank adds the same numbers in the same order.
+template <class SlotFn>
+__device__ __forceinline__ float tp_recv_sum(const TpComm& c, SlotFn slot_of, uint32_t tag, float own, float acc, bool& alive) {
+  unsigned long long m[kTpMaxRanks];
+  uint32_t pending = ((1u << c.size) - 1u) & ~(1u << c.rank);
+  const uint32_t limit = alive ? c.spin_limit : 1u;
+  for (uint32_t it = 0; it < limit && pending != 0u; ++it) {
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)
+      if ((pending >> r) & 1u) m[r] = tp_ld_msg(slot_of(r));
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)
+      if (((pending >> r) & 1u) && (uint32_t)(m[r] >> 32) == tag) pending &= ~(1u << r);
+  }
+  if (pending != 0u) {
+    alive = false;
+    atomicExch(c.status, 2);
+  }
+#pragma unroll
+  for (int r = 0; r < kTpMaxRanks; ++r)
+    if (r < c.size) acc += r == c.rank ? own : (((pending >> r) & 1u) ? 0.0f : __uint_as_float((uint32_t)m[r]));
+  return acc;
+}
 __device__ __forceinline__ int* tp_tile_flag(const TpComm& c, int on_rank, int parity, int from_rank, int tile) {
   return reinterpret_cast<int*>(c.peer[on_rank] + c.lay.off_tile_flags) + ((size_t)parity * kTpMaxRanks + from_rank) * kTpMaxTiles + tile;
 }

@@ -234,14 +234,13 @@ __global__ void __launch_bounds__(kGhWarps * 32) bitgemm_hmma_kernel(GhParams p,
           const uint32_t tag = (uint32_t)tp_epoch + 1u;
           const int parity = tp_epoch & 1;
           const size_t i_lo = (size_t)tok * p.n_rows + r_lo, i_hi = (size_t)tok * p.n_rows + r_hi;
-          float s_lo = res[nt][e], s_hi = res[nt][2 + e];
-          for (int q = 0; q < tp.size; ++q) {   // rank order: every rank adds the same numbers in the same order
-            const unsigned long long* src = tp_ll_big_slot(tp, tp.rank, parity, q);
-            if (ok_lo) s_lo += q == tp.rank ? v_lo : tp_recv_msg(tp, src + i_lo, tag, tp_alive);
-            if (ok_hi) s_hi += q == tp.rank ? v_hi : tp_recv_msg(tp, src + i_hi, tag, tp_alive);
-          }
-          if (ok_lo) p.out_f32[(size_t)tok * p.out_ld + r_lo] = s_lo;
-          if (ok_hi) p.out_f32[(size_t)tok * p.out_ld + r_hi] = s_hi;
+          // all peers' slots of an element are requested together and added in rank order once they are all there
+          if (ok_lo)
+            p.out_f32[(size_t)tok * p.out_ld + r_lo] =
+                tp_recv_sum(tp, [&](int q) { return tp_ll_big_slot(tp, tp.rank, parity, q) + i_lo; }, tag, v_lo, res[nt][e], tp_alive);
+          if (ok_hi)
+            p.out_f32[(size_t)tok * p.out_ld + r_hi] =
+                tp_recv_sum(tp, [&](int q) { return tp_ll_big_slot(tp, tp.rank, parity, q) + i_hi; }, tag, v_hi, res[nt][2 + e], tp_alive);
         }
       } else if (tok < p.T) {
         if (ok_lo) p.out_f32[(size_t)tok * p.out_ld + r_lo] = res[nt][e] + v_lo;

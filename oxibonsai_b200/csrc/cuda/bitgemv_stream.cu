@@ -443,10 +443,9 @@ __global__ void __launch_bounds__(kS16Threads, 1) bitgemv_s16_kernel(S16Args a, 
         for (int p = 0; p < tp.size; ++p)
           if (p != tp.rank) tp_st_msg(tp_ll_slot(tp, p, parity, tp.rank) + row, msg);
       }
-      float sum = a.residual != nullptr ? a.residual[row] : 0.0f;
+      const float res = a.residual != nullptr ? a.residual[row] : 0.0f;
       bool alive = true;
-      for (int s = 0; s < tp.size; ++s) sum += s == tp.rank ? v : tp_recv_msg(tp, tp_ll_slot(tp, tp.rank, parity, s) + row, tag, alive);
-      a.out[row] = sum;
+      a.out[row] = tp_recv_sum(tp, [&](int s) { return tp_ll_slot(tp, tp.rank, parity, s) + row; }, tag, v, res, alive);
     }
   }
   if (a.epi == SEPI_TP) {
