@@ -11,7 +11,7 @@ GPU runner in place of the plain one (``Qwen3Runner`` takes its cos/sin tables a
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 

@@ -8,8 +8,7 @@ On a GPU engine ``logits_fn`` is backed by ``InferenceEngine`` slots: the engine
 from __future__ import annotations
 
 import heapq
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Sequence
 
 import numpy as np

@@ -13,7 +13,7 @@ import asyncio
 import bisect
 import threading
 from dataclasses import dataclass, field
-from typing import Any, Callable, Iterator, Sequence
+from typing import Any, Callable, Iterator
 
 
 def fnv1a_hash(data: bytes | str) -> int:

@@ -8,7 +8,7 @@ multi-byte tokens without disturbing the main state.
 """
 from __future__ import annotations
 
-from .ast import Grammar, NonTerm, Term
+from .ast import Grammar, Term
 
 
 class EarleyRecognizer:

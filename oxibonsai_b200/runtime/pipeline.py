@@ -9,7 +9,7 @@ the new token each step (the pipeline always extends the token list by one).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 from typing import Callable, Sequence
 
