@@ -59,6 +59,7 @@ class EngineBuilder:
         self._warmup = True
         self._exact: bool | None = None
         self._repack_cache: str | None = None
+        self._prefill_chunk: int | None = None
 
     def model_path(self, path: str) -> "EngineBuilder":
         self._model_path = str(path); return self
@@ -105,11 +106,15 @@ class EngineBuilder:
         """Directory in which the device layouts of the weights are kept between starts (None = no cache)."""
         self._repack_cache = directory; return self
 
+    def prefill_chunk(self, tokens: int | None) -> "EngineBuilder":
+        """Tokens per prompt chunk of the batched prefill path (a multiple of 64; default 1024)."""
+        self._prefill_chunk = None if tokens is None else int(tokens); return self
+
     def options(self) -> dict:
         return dict(model_path=self._model_path, max_seq_len=self._max_seq_len, max_batch=self._max_batch, kv_dtype=self._kv_dtype,
                     device=self._device, sampling=self._sampler.build(), page_size=self._page_size, kv_pages=self._kv_pages,
                     tp_rank=self._tp_rank, tp_size=self._tp_size, warmup=self._warmup, exact=self._exact,
-                    repack_cache=self._repack_cache)
+                    repack_cache=self._repack_cache, prefill_chunk=self._prefill_chunk)
 
     def build(self):
         if not self._model_path:

@@ -50,7 +50,7 @@ class InferenceEngine:
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
                  kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None,
-                 repack_cache: str | None = None):
+                 repack_cache: str | None = None, prefill_chunk: int | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("InferenceEngine needs a CUDA device; use oxibonsai_b200.core.Oracle for the CPU path")
         self.device = torch.device(device)
@@ -73,7 +73,10 @@ class InferenceEngine:
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
                                self.kvt, self.device)
-        self.prefill_chunk = 1024
+        # tokens per prompt chunk of the batched prefill path (the activation buffers are sized for it)
+        self.prefill_chunk = int(prefill_chunk or os.environ.get("OXIBONSAI_PREFILL_CHUNK") or 1024)
+        if self.prefill_chunk < 64 or self.prefill_chunk % 64:
+            raise ValueError("prefill_chunk must be a multiple of 64")
         self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact,
                                   prefill_chunk=self.prefill_chunk)
         self.load_seconds = time.perf_counter() - t0
@@ -529,7 +532,7 @@ class GenericFormatEngine:
     def __init__(self, model_path: str, max_seq_len: int = 4096, max_batch: int = 1, kv_dtype: str = "f16",
                  device: str | torch.device = "cuda:0", sampling: SamplingParams | None = None, page_size: int = 64,
                  kv_pages: int | None = None, tp_rank: int = 0, tp_size: int = 1, warmup: bool = True, exact: bool | None = None,
-                 repack_cache: str | None = None):      # the generic formats are used as stored: nothing to cache
+                 repack_cache: str | None = None, prefill_chunk: int | None = None):      # the generic formats are used as stored: nothing to cache
         import threading
         from ..models.qwen3_generic import GenericQwen3Engine
         if tp_size != 1:
