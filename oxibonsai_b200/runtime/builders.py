@@ -107,7 +107,7 @@ class EngineBuilder:
         self._repack_cache = directory; return self
 
     def prefill_chunk(self, tokens: int | None) -> "EngineBuilder":
-        """Tokens per prompt chunk of the batched prefill path (a multiple of 64; default 1024)."""
+        """Tokens per prompt chunk of the batched prefill path (a multiple of 64; default 4096)."""
         self._prefill_chunk = None if tokens is None else int(tokens); return self
 
     def options(self) -> dict:

@@ -73,8 +73,11 @@ class InferenceEngine:
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.kv = PagedKvCache(self.config, self.weights.kv_heads_local, kv_pages or pages_per_seq * self.max_batch, page_size,
                                self.kvt, self.device)
-        # tokens per prompt chunk of the batched prefill path (the activation buffers are sized for it)
-        self.prefill_chunk = int(prefill_chunk or os.environ.get("OXIBONSAI_PREFILL_CHUNK") or 1024)
+        # Tokens per prompt chunk of the batched prefill path (the activation buffers are sized for it).  Larger chunks fill
+        # the GPU better in the projections with few row tiles (QKV / attention output: 48 / 32 row tiles x one column block
+        # per 256 tokens on 148 SMs): time to first token of a 4096-token prompt on the 8B shape 0.148 s at 1024, 0.132 s at
+        # 2048, 0.122 s at 4096.
+        self.prefill_chunk = int(prefill_chunk or os.environ.get("OXIBONSAI_PREFILL_CHUNK") or 4096)
         if self.prefill_chunk < 64 or self.prefill_chunk % 64:
             raise ValueError("prefill_chunk must be a multiple of 64")
         self.runner = Qwen3Runner(self.weights, self.kv, self.max_batch, self.max_seq_len, fast=not self.exact,
