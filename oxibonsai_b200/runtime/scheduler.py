@@ -108,7 +108,7 @@ class BatchScheduler:
     """Owns an ``InferenceEngine`` (max_batch > 1) and serves requests with continuous batching."""
 
     def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
-                 prefill_chunk_tokens: int = 512, kv_policy=None):
+                 prefill_chunk_tokens: int = 512, kv_policy=None, prefill_chunk_boost: int = 1):
         """``kv_policy``: a :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy`; when given, the scheduler feeds it the
         engine's KV utilisation after every admission and retirement, and every newly admitted sequence gets its pages in the
         format of the policy's current level (FP16 / Q8 / Q4, as far as the engine has pools for them)."""
@@ -116,6 +116,9 @@ class BatchScheduler:
         from ..core.oracle import EOS_TOKEN
         self.engine = engine
         self.prefill_chunk_tokens = max(16, int(prefill_chunk_tokens))
+        # While fewer than a quarter of the slots decode, prompt chunks are ``prefill_chunk_boost`` times as long: few streams
+        # wait behind the chunk then, and long chunks fill the GPU better (1 = always the same chunk length).
+        self.prefill_chunk_boost = max(1, int(prefill_chunk_boost))
         self._pending: dict | None = None      # the request being prefilled: {"r", "slot", "done"} (slot >= len(live))
         self.prefill_chunks = 0
         self.eos = EOS_TOKEN if eos_token is None else eos_token
@@ -223,7 +226,8 @@ class BatchScheduler:
                 raise _Cancelled()
             n = len(r.prompt)
             # short remainders go in one piece; never leave a tail shorter than the engine's batched-prefill threshold
-            end = n if n - p["done"] <= self.prefill_chunk_tokens + eng.prefill_min_tokens else p["done"] + self.prefill_chunk_tokens
+            chunk = self.prefill_chunk_tokens * (self.prefill_chunk_boost if 4 * len(self.live) < eng.max_batch else 1)
+            end = n if n - p["done"] <= chunk + eng.prefill_min_tokens else p["done"] + chunk
             eng.prefill(r.prompt[p["done"]:end], slot, p["done"])
             self.prefill_chunks += 1
             p["done"] = end

@@ -40,6 +40,7 @@ class ServerConfig:
     tensor_parallel: int = 1          # > 1: launch with torchrun, one process per GPU; rank 0 serves HTTP, the others follow its commands
     replicas: int = 1                 # > 1: one engine + scheduler per GPU (cuda:0 .. cuda:N-1) in this process, requests routed between them
     prefill_chunk_tokens: int = 512   # prompt tokens prefilled between two decode steps of the running streams
+    prefill_chunk_boost: int = 1      # chunks this many times as long while fewer than a quarter of the slots decode
     kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
 
@@ -82,7 +83,7 @@ _TOML_MAP = {
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
     ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "kv_policy"): "kv_policy",
-    ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens",
+    ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",
 }

@@ -234,3 +234,13 @@ def test_constrained_request_sends_masks_and_ends_when_the_constraint_is_complet
     assert len(free.wait(10)) == 6
     sched.stop()
     assert len(eng.seen_masks) == 3
+
+
+def test_prompt_chunks_are_longer_while_few_streams_decode():
+    eng = FakeEngine()                                         # four slots: "few" means none is decoding
+    sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=64, prefill_chunk_boost=4)
+    a = sched.submit(list(range(600)), SamplingParams(), 3)
+    sched.start()
+    assert a.wait(10) == _expected(list(range(600)), 3)
+    sched.stop()
+    assert [e[3] for e in eng.log if e[0] == "prefill"] == [256, 256, 88]
