@@ -93,7 +93,7 @@ def main() -> None:
     ap.add_argument("--replicas", type=int, default=1)
     ap.add_argument("--tensor-parallel", type=int, default=1)
     ap.add_argument("--kv-policy", default="off")
-    ap.add_argument("--prefill-chunk-boost", type=int, default=1)
+    ap.add_argument("--prefill-chunk-boost", type=int, default=4)
     ap.add_argument("--model-dir", default=os.environ.get("BONSAI_BENCH_DIR", "/tmp/oxibonsai_b200_bench"))
     a = ap.parse_args()
 

@@ -40,7 +40,7 @@ class ServerConfig:
     tensor_parallel: int = 1          # > 1: launch with torchrun, one process per GPU; rank 0 serves HTTP, the others follow its commands
     replicas: int = 1                 # > 1: one engine + scheduler per GPU (cuda:0 .. cuda:N-1) in this process, requests routed between them
     prefill_chunk_tokens: int = 512   # prompt tokens prefilled between two decode steps of the running streams
-    prefill_chunk_boost: int = 1      # chunks this many times as long while fewer than a quarter of the slots decode
+    prefill_chunk_boost: int = 4      # chunks this many times as long while fewer than a quarter of the slots decode
     kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
 
