@@ -178,6 +178,35 @@ def cuda_timer(result: dict, key: str):
 
 
 # ---- memory --------------------------------------------------------------------------------------------------------------------
+def kernel_histogram(run, iterations: int = 3, warmup: int = 1) -> dict[str, dict]:
+    """Per-kernel device-time table of ``run()`` (a callable that launches GPU work, e.g. ``lambda: runner.step(1)``): kernel
+    name -> {"count", "total_us", "mean_us", "max_us"} over ``iterations`` calls after ``warmup`` unrecorded ones, from the
+    CUDA activity records of ``torch.profiler`` (kernels replayed from a CUDA graph are recorded like any other).  A
+    diagnostic view of where a step's device time goes - the counterpart of the reference profiler's per-operation table
+    (crates/oxibonsai-runtime/src/profiler.rs); figures taken this way carry the profiler's overhead and are not benchmark
+    numbers."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    for _ in range(max(0, warmup)):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(max(1, iterations)):
+            run()
+        torch.cuda.synchronize()
+    table: dict[str, dict] = {}
+    for ev in prof.events():
+        if str(getattr(ev, "device_type", "")).endswith("CUDA") and ev.name and not ev.name.startswith(("Memcpy", "Memset")):
+            dur = float(getattr(ev, "device_time", 0.0) or getattr(ev, "cuda_time", 0.0) or 0.0)
+            row = table.setdefault(ev.name, {"count": 0, "total_us": 0.0, "max_us": 0.0})
+            row["count"] += 1
+            row["total_us"] += dur
+            row["max_us"] = max(row["max_us"], dur)
+    for row in table.values():
+        row["mean_us"] = row["total_us"] / row["count"]
+    return dict(sorted(table.items(), key=lambda kv: -kv[1]["total_us"]))
+
+
 def get_rss_bytes() -> int:
     try:
         with open("/proc/self/statm") as f:

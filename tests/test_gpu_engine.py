@@ -122,3 +122,23 @@ def test_repacked_weight_cache_gives_the_same_engine(tiny_gguf, tmp_path):
     assert second.weights.from_cache and second.model_info()["weights_from_repack_cache"]
     assert second.generate(prompt, 12) == want
     assert second.weights.packed_bytes == first.weights.packed_bytes
+
+
+def test_kernel_histogram_lists_the_kernels_of_a_decode_step(tiny_gguf):
+    from oxibonsai_b200.runtime import EngineBuilder
+    from oxibonsai_b200.runtime.observability import kernel_histogram
+    eng = EngineBuilder().model_path(tiny_gguf).preset("greedy").max_seq_len(96).build()
+    eng.generate([3, 1, 4, 1, 5], 4, stop_at_eos=False)          # graph captured, slot released
+    eng._bind_slot(0, 32)
+    eng._upload(0, 7, 0)
+    try:
+        table = kernel_histogram(lambda: eng.runner.step(1, sample=True), iterations=2)
+    except Exception as e:                                       # no CUPTI on the box
+        pytest.skip(f"profiler unavailable: {e}")
+    finally:
+        eng._release_slot(0)
+    if not table:
+        pytest.skip("the profiler recorded no device activity")
+    gemv = [k for k in table if "bitgemv_s16" in k]
+    assert gemv and table[gemv[0]]["count"] == 2 * 4 * eng.config.layers      # four projections per layer and step
+    assert any("attn_decode" in k for k in table) and all(r["mean_us"] >= 0 for r in table.values())
