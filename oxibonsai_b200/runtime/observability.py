@@ -184,7 +184,8 @@ def kernel_histogram(run, iterations: int = 3, warmup: int = 1) -> dict[str, dic
     CUDA activity records of ``torch.profiler`` (kernels replayed from a CUDA graph are recorded like any other).  A
     diagnostic view of where a step's device time goes - the counterpart of the reference profiler's per-operation table
     (crates/oxibonsai-runtime/src/profiler.rs); figures taken this way carry the profiler's overhead and are not benchmark
-    numbers."""
+    numbers, and a kernel launched with programmatic dependent launch is on the device while it still waits for its
+    predecessor, so the durations of a chained step overlap and add up to more than the step's wall time."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     for _ in range(max(0, warmup)):
