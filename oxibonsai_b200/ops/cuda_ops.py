@@ -238,6 +238,35 @@ def quant_gemv(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, n
     return out
 
 
+_elt_declared = False
+
+
+def _elt():
+    global _elt_declared
+    l = lib()
+    if not _elt_declared:
+        declare({"bonsai_rmsnorm_rows": [_vp, _i, _vp, _f, _i, _i, _vp, _i, _vp], "bonsai_residual_add": [_vp, _vp, C.c_size_t, _vp]})
+        _elt_declared = True
+    return l
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Weighted RMSNorm over the rows of ``x`` (f32 [T, K] or [K]); the stand-alone form of what the GEMV / GEMM kernels fuse."""
+    x2 = x if x.dim() == 2 else x.view(1, -1)
+    assert x2.is_cuda and x2.dtype == torch.float32 and x2.stride(1) == 1
+    o = torch.empty_like(x2) if out is None else (out if out.dim() == 2 else out.view(1, -1))
+    check(_elt().bonsai_rmsnorm_rows(x2.data_ptr(), x2.stride(0), ptr(w), eps, x2.shape[0], x2.shape[1], o.data_ptr(), o.stride(0), stream()), "rmsnorm")
+    return o if x.dim() == 2 else o.view(-1)
+
+
+def residual_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a += b in place (contiguous f32 tensors of one size)."""
+    _f32c(a), _f32c(b)
+    assert a.numel() == b.numel()
+    check(_elt().bonsai_residual_add(a.data_ptr(), b.data_ptr(), a.numel(), stream()), "residual_add")
+    return a
+
+
 def quant_gemv_batched(type_id: int, w: torch.Tensor, n: int, k: int, x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 1e-6,
                        residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """:func:`quant_gemv` for a batch: ``x`` [B, k] f32 (row stride >= k), ``out`` and ``residual`` [B, n] with one common row stride."""

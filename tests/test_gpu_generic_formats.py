@@ -181,3 +181,19 @@ def test_generic_engine_batched_decode_through_the_scheduler(fmt, tiny_gguf, tmp
     agree = sum(x == y for a, b in zip(alone, got) for x, y in zip(a, b))
     assert agree >= sum(lens) - 2, (alone, got)       # f32 everywhere; the batched GEMV only changes nothing but launch shapes
     assert eng.kv_utilization() == 0.0
+
+
+def test_standalone_rmsnorm_and_residual_add():
+    from oxibonsai_b200.ops import cuda_ops as K
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(3)
+    x, w = torch.randn(5, 2560, generator=g).to(dev), (torch.rand(2560, generator=g) + 0.5).to(dev)
+    ref = x * torch.rsqrt((x * x).mean(dim=1, keepdim=True) + 1e-6) * w
+    assert torch.allclose(K.rmsnorm(x, w, 1e-6), ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(K.rmsnorm(x[0], None, 1e-6), x[0] * torch.rsqrt((x[0] * x[0]).mean() + 1e-6), rtol=1e-5, atol=1e-6)
+    wide = torch.randn(3, 300, generator=g).to(dev)
+    view = wide[:, :128]                                       # rows with a stride
+    assert torch.allclose(K.rmsnorm(view, None), view * torch.rsqrt((view * view).mean(dim=1, keepdim=True) + 1e-6), rtol=1e-5, atol=1e-6)
+    a, b = torch.randn(100003, generator=g).to(dev), torch.randn(100003, generator=g).to(dev)
+    want = a + b
+    assert torch.equal(K.residual_add(a, b), want)
