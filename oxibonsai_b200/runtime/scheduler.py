@@ -108,11 +108,19 @@ class BatchScheduler:
     """Owns an ``InferenceEngine`` (max_batch > 1) and serves requests with continuous batching."""
 
     def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
-                 prefill_chunk_tokens: int = 512, kv_policy=None, prefill_chunk_boost: int = 1):
+                 prefill_chunk_tokens: int = 512, kv_policy=None, prefill_chunk_boost: int = 1,
+                 before_launch: Callable[[], None] | None = None, on_fatal: Callable[[Exception], bool] | None = None,
+                 idle_hook: Callable[[], None] | None = None, idle_hook_seconds: float = 30.0):
         """``kv_policy``: a :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy`; when given, the scheduler feeds it the
         engine's KV utilisation after every admission and retirement, and every newly admitted sequence gets its pages in the
         format of the policy's current level (FP16 / Q8 / Q4, as far as the engine has pools for them)."""
         self.kv_policy = kv_policy
+        # ``before_launch`` runs at the top of every loop iteration that has work (a watchdog's check: it raises before
+        # kernels that need a lost peer are launched).  ``on_fatal(error)`` sees every exception that failed the live
+        # requests; when it returns True the loop ends (the owner rebuilds the engine and starts a new scheduler).
+        # ``idle_hook`` runs every ``idle_hook_seconds`` while nothing is live (a tensor-parallel leader's keep-alive).
+        self.before_launch, self.on_fatal, self.idle_hook, self.idle_hook_seconds = before_launch, on_fatal, idle_hook, idle_hook_seconds
+        self.fatal: Exception | None = None
         from ..core.oracle import EOS_TOKEN
         self.engine = engine
         self.prefill_chunk_tokens = max(16, int(prefill_chunk_tokens))
@@ -163,26 +171,47 @@ class BatchScheduler:
     def _loop(self) -> None:
         eng = self.engine
         eng.bind_thread()
+        last_idle = time.monotonic()
         while not self._stop.is_set():
             try:
+                if self.before_launch is not None and (self.live or self._pending is not None or len(self.queue)):
+                    self.before_launch()
                 admitted = self._admit()
                 if not self.live:
                     if not admitted:
+                        if self.idle_hook is not None and time.monotonic() - last_idle >= self.idle_hook_seconds:
+                            last_idle = time.monotonic()
+                            self.idle_hook()
                         time.sleep(self.idle_sleep)
                     continue
+                last_idle = time.monotonic()
                 self._step()
             except Exception as e:  # a failing step must not wedge the waiting clients
+                fatal = False
+                if self.on_fatal is not None:
+                    try:
+                        fatal = bool(self.on_fatal(e))
+                    except Exception:  # noqa: BLE001 - the hook must not keep the clients waiting
+                        fatal = False
                 for r in self.live:
                     r.error = e
                     r.done.set()
-                for s in range(len(self.live)):
-                    eng.close_sequence(s)
-                self.live, self._pos = [], []
                 if self._pending is not None:
                     self._pending["r"].error = e
                     self._pending["r"].done.set()
-                    eng.close_sequence(self._pending["slot"])
-                    self._pending = None
+                slots = list(range(len(self.live))) + ([self._pending["slot"]] if self._pending is not None else [])
+                self.live, self._pos, self._pending = [], [], None
+                if fatal:                          # the engine is about to be torn down: its slots go with it
+                    self.fatal = e
+                    while (r := self.queue.get_nowait()) is not None:
+                        r.error = e
+                        r.done.set()
+                    return
+                for s in slots:
+                    try:
+                        eng.close_sequence(s)
+                    except Exception:  # noqa: BLE001 - a second failure while cleaning up changes nothing for the clients
+                        pass
 
     def _admit(self) -> bool:
         """Makes progress on admission: at most one prompt chunk per call.  Returns True when something was done."""

@@ -55,6 +55,8 @@ def main(argv: list[str] | None = None) -> int:
             print(f"error: --tensor-parallel {tp} needs {tp} processes (torchrun --nproc-per-node {tp}), found WORLD_SIZE={world}", file=sys.stderr)
             return 2
         torch.cuda.set_device(local)
+        if cfg.tp_elastic:
+            return _serve_elastic(cfg, tokenizer, builder, rank, world, local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         channel = CommandChannel(dist.new_group(backend="gloo"))
         engine = builder(f"cuda:{local}").tensor_parallel(rank, world).build()
@@ -78,7 +80,7 @@ def main(argv: list[str] | None = None) -> int:
                 if policy is not None:
                     e.enable_kv_formats(("f16", "q8", "q4"))      # the levels of the policy that the engine does not have yet
             scheds.append(BatchScheduler(e, queue_capacity=cfg.queue_capacity, prefill_chunk_tokens=cfg.prefill_chunk_tokens, prefill_chunk_boost=cfg.prefill_chunk_boost,
-                                         kv_policy=policy).start())
+                                         kv_policy=policy, idle_hook=getattr(leader, "keepalive", None)).start())
         backend = SchedulerBackend(scheds[0], engine.config.name) if len(scheds) == 1 else ReplicaBackend(scheds, engine.config.name)
     else:                                         # an engine without sequence slots: one request at a time
         backend = SerialBackend(engine, engine.config.name)
@@ -92,6 +94,77 @@ def main(argv: list[str] | None = None) -> int:
             sc.stop()
         if leader is not None:
             leader.shutdown()
+    return 0
+
+
+def _serve_elastic(cfg, tokenizer, builder, uid: int, world: int, local: int) -> int:
+    """Tensor-parallel serving that survives the loss of a follower rank: heartbeats through the job's TCP store, a check
+    before every launch, and on a loss a new generation at the largest degree the survivors fill (8 -> 4 -> 2 -> 1), the
+    engine rebuilt from the checkpoint for that degree.  Rank 0 keeps the HTTP front up throughout; requests that arrive
+    while the group re-forms get 503."""
+    import os
+    import threading
+
+    import torch
+    import torch.distributed as dist
+
+    from ..runtime.elastic import ElasticGroup, RankLost
+    from ..runtime.scheduler import BatchScheduler
+    from ..runtime.tp_serving import CommandChannel, ElasticBackend, lead_with_scheduler, run_elastic_rank
+    from .app import create_app
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 1          # next to torchrun's own rendezvous store
+    store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, is_master=(uid == 0), wait_for_workers=False)
+    device = torch.device("cuda", local)
+
+    def init_group(prefix_store, rank, size):
+        from datetime import timedelta
+        dist.init_process_group("nccl", store=prefix_store, rank=rank, world_size=size, device_id=device, timeout=timedelta(seconds=60))
+
+    group = ElasticGroup(store, uid, world, backend="nccl", interval=min(0.5, cfg.tp_heartbeat_timeout / 5), timeout=cfg.tp_heartbeat_timeout,
+                         init_group=init_group)
+
+    def build_engine(rank: int, size: int):
+        b = builder(f"cuda:{local}")
+        return (b.tensor_parallel(rank, size) if size > 1 else b).build()
+
+    stop = threading.Event()
+    backend = ElasticBackend(os.path.basename(cfg.model_path), cfg.max_seq_len)
+
+    def fatal(e: Exception) -> bool:
+        # a lost rank shows up as the watchdog's exception, or first as a kernel whose bounded wait ran out
+        return isinstance(e, RankLost) or (type(e).__name__ == "CudaKernelError" and group.confirm_loss())
+
+    def make_scheduler(le, g):
+        if hasattr(le, "enable_prefix_cache") and not le.exact:
+            le.enable_prefix_cache()
+        return BatchScheduler(le, queue_capacity=cfg.queue_capacity, prefill_chunk_tokens=cfg.prefill_chunk_tokens,
+                              prefill_chunk_boost=cfg.prefill_chunk_boost, before_launch=g.check,
+                              on_fatal=lambda e: fatal(e), idle_hook=le.keepalive)
+
+    def lead(le, g):
+        inner = lead_with_scheduler(make_scheduler, backend, stop)
+        try:
+            inner(le, g)
+        except Exception as e:  # noqa: BLE001 - a kernel time-out that the watchdog attributes to a lost rank re-forms the group
+            if isinstance(e, RankLost) or g.confirm_loss(0.0):
+                raise RankLost(g.lost(), g.generation) from e
+            raise
+
+    make_channel = lambda: CommandChannel(dist.new_group(backend="gloo"))
+    on_error = lambda op, e: print(f"[uid {uid}] {op}: {e}", file=sys.stderr)
+    if uid != 0:
+        history = run_elastic_rank(group, build_engine, make_channel, lead, on_error)
+        print(f"[uid {uid}] done after {len(history)} re-formation(s)", file=sys.stderr)
+        return 0
+    worker = threading.Thread(target=lambda: run_elastic_rank(group, build_engine, make_channel, lead, on_error), name="bonsai-elastic-leader", daemon=True)
+    worker.start()
+    app = create_app(backend, tokenizer, cfg)
+    import uvicorn
+    try:
+        uvicorn.run(app, host=cfg.host, port=cfg.port, log_level=cfg.log_level if cfg.log_level in ("debug", "info", "warning", "error") else "info")
+    finally:
+        stop.set()
+        worker.join(timeout=30)
     return 0
 
 

@@ -38,6 +38,8 @@ class ServerConfig:
     quantization_hint: str | None = None
     kv_cache: str = "f16"
     tensor_parallel: int = 1          # > 1: launch with torchrun, one process per GPU; rank 0 serves HTTP, the others follow its commands
+    tp_elastic: bool = False          # with tensor_parallel > 1: watch the ranks' heartbeats and re-form the group at a smaller degree when one is lost
+    tp_heartbeat_timeout: float = 5.0 # seconds without a heartbeat after which a rank counts as lost
     replicas: int = 1                 # > 1: one engine + scheduler per GPU (cuda:0 .. cuda:N-1) in this process, requests routed between them
     prefill_chunk_tokens: int = 512   # prompt tokens prefilled between two decode steps of the running streams
     prefill_chunk_boost: int = 4      # chunks this many times as long while fewer than a quarter of the slots decode
@@ -82,7 +84,7 @@ _TOML_MAP = {
     ("sampling", "temperature"): "temperature", ("sampling", "top_k"): "top_k", ("sampling", "top_p"): "top_p",
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
-    ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "kv_policy"): "kv_policy",
+    ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "tp_elastic"): "tp_elastic", ("model", "tp_heartbeat_timeout"): "tp_heartbeat_timeout", ("model", "kv_policy"): "kv_policy",
     ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",

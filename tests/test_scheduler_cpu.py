@@ -244,3 +244,38 @@ def test_prompt_chunks_are_longer_while_few_streams_decode():
     assert a.wait(10) == _expected(list(range(600)), 3)
     sched.stop()
     assert [e[3] for e in eng.log if e[0] == "prefill"] == [256, 256, 88]
+
+
+def test_watchdog_hook_stops_launches_and_a_fatal_error_ends_the_loop():
+    """``before_launch`` runs before work is launched (not while idle); an error that ``on_fatal`` claims fails the live and
+    the queued requests and ends the loop with ``fatal`` set, so the owner can rebuild the engine; ``idle_hook`` fires while
+    nothing is live."""
+    eng = FakeEngine(step_delay=0.002)
+    state = {"checks": 0, "lost": False, "idle": 0}
+
+    class Lost(RuntimeError):
+        pass
+
+    def check():
+        state["checks"] += 1
+        if state["lost"]:
+            raise Lost("rank 1 lost")
+
+    sched = BatchScheduler(eng, prefill_chunk_tokens=16, before_launch=check, on_fatal=lambda e: isinstance(e, Lost),
+                           idle_hook=lambda: state.__setitem__("idle", state["idle"] + 1), idle_hook_seconds=0.02).start()
+    time.sleep(0.15)
+    assert state["checks"] == 0 and state["idle"] >= 2                  # idle: the keep-alive runs, the watchdog is not asked
+    a = sched.submit(list(range(20)), SamplingParams(), 400)
+    while len(a.tokens) < 5:
+        time.sleep(0.005)
+    assert state["checks"] >= 5
+    steps_before = sum(1 for e in eng.log if e[0] == "step")
+    state["lost"] = True
+    b = sched.submit(list(range(30)), SamplingParams(), 5)             # may or may not be picked up before the loss is seen
+    assert a.done.wait(5) and b.done.wait(5)
+    assert isinstance(a.error, Lost) and isinstance(b.error, Lost) and isinstance(sched.fatal, Lost)
+    assert sum(1 for e in eng.log if e[0] == "step") <= steps_before + 1   # nothing was launched after the check raised
+    sched._thread.join(2)
+    assert not sched._thread.is_alive()
+    assert not any(e[0] == "close" for e in eng.log[-2:])              # the slots are left to the engine that is torn down
+    sched.stop()
