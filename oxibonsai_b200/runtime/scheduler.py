@@ -61,6 +61,17 @@ class Request:
     constraint: object | None = None       # TokenConstraint: the sampler only picks tokens it allows; ends the request when complete
     logprobs: int | None = None            # not None: record the log-probability of every token and of the top `logprobs` ones
     token_logprobs: list = field(default_factory=list)   # [(logprob, [(token, logprob), ...]), ...] when `logprobs` is set
+    on_done: Callable[["Request"], None] | None = None   # called once, on the scheduler's thread, when the request has ended (any way)
+
+    def finish(self) -> None:
+        """Marks the request as ended and tells its owner (once)."""
+        cb, self.on_done = self.on_done, None
+        self.done.set()
+        if cb is not None:
+            try:
+                cb(self)
+            except Exception:  # noqa: BLE001 - the owner's bookkeeping must not stop the scheduler
+                pass
 
     def wait(self, timeout: float | None = None) -> list[int]:
         if not self.done.wait(timeout):
@@ -195,17 +206,17 @@ class BatchScheduler:
                         fatal = False
                 for r in self.live:
                     r.error = e
-                    r.done.set()
+                    r.finish()
                 if self._pending is not None:
                     self._pending["r"].error = e
-                    self._pending["r"].done.set()
+                    self._pending["r"].finish()
                 slots = list(range(len(self.live))) + ([self._pending["slot"]] if self._pending is not None else [])
                 self.live, self._pos, self._pending = [], [], None
                 if fatal:                          # the engine is about to be torn down: its slots go with it
                     self.fatal = e
                     while (r := self.queue.get_nowait()) is not None:
                         r.error = e
-                        r.done.set()
+                        r.finish()
                     return
                 for s in slots:
                     try:
@@ -226,7 +237,7 @@ class BatchScheduler:
                     return False
                 if r.cancelled:
                     r.finish_reason = "cancelled"
-                    r.done.set()
+                    r.finish()
                     r = None
             slot = len(self.live)
             total = min(eng.max_seq_len, len(r.prompt) + r.max_tokens)
@@ -245,7 +256,7 @@ class BatchScheduler:
             except Exception as e:
                 eng.close_sequence(slot)
                 r.error = e
-                r.done.set()
+                r.finish()
                 return True
             self._pending = {"r": r, "slot": slot, "done": covered}
         p = self._pending
@@ -270,13 +281,13 @@ class BatchScheduler:
         except _Cancelled:
             eng.close_sequence(slot)
             r.finish_reason = "cancelled"
-            r.done.set()
+            r.finish()
             self._pending = None
             return True
         except Exception as e:
             eng.close_sequence(slot)
             r.error = e
-            r.done.set()
+            r.finish()
             self._pending = None
             return True
         self._pending = None
@@ -329,7 +340,7 @@ class BatchScheduler:
         eng = self.engine
         r = self.live[slot]
         r.t_done = time.perf_counter()
-        r.done.set()
+        r.finish()
         last = len(self.live) - 1
         eng.close_sequence(slot)
         if self.kv_policy is not None:

@@ -162,6 +162,8 @@ class ElasticBackend:
     ``submit`` raises :class:`Unavailable` (the server answers 503), otherwise it goes to the current generation's
     scheduler."""
 
+    supports_on_done = True
+
     def __init__(self, model_name: str, max_seq_len: int):
         self.model_name, self.max_seq_len = model_name, max_seq_len
         self.s = None

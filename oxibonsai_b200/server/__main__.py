@@ -16,7 +16,7 @@ def banner(cfg, info: dict) -> str:
              f"  weights      {info.get('weight_bytes', 0) / 1e9:.2f} GB on device, KV cache {cfg.kv_cache} ({info.get('kv_bytes', 0) / 1e9:.2f} GB)",
              f"  batching     up to {cfg.max_concurrent} concurrent sequences per engine, max_seq_len {cfg.max_seq_len}",
              f"  GPUs         " + (f"tensor parallel over {cfg.tensor_parallel}" if cfg.tensor_parallel > 1 else f"{cfg.replicas} replica(s)"),
-             f"  listening    http://{cfg.host}:{cfg.port}  (metrics {cfg.metrics_path if cfg.metrics_enabled else 'off'}, auth {'on' if cfg.bearer_token else 'off'})"]
+             f"  listening    http://{cfg.host}:{cfg.port}  (metrics {cfg.metrics_path if cfg.metrics_enabled else 'off'}, auth {'on' if cfg.bearer_token else 'off'}, front {'native' if cfg.native_front else 'uvicorn'})"]
     return "\n".join(lines)
 
 
@@ -86,9 +86,9 @@ def main(argv: list[str] | None = None) -> int:
         backend = SerialBackend(engine, engine.config.name)
     app = create_app(backend, tokenizer, cfg, kv_policy=policy)
     print(banner(cfg, engine.model_info()), file=sys.stderr)
-    import uvicorn
+    from .app import serve
     try:
-        uvicorn.run(app, host=cfg.host, port=cfg.port, log_level=cfg.log_level if cfg.log_level in ("debug", "info", "warning", "error") else "info")
+        serve(app, cfg.host, cfg.port, cfg.log_level, tokenizer=tokenizer, native=cfg.native_front, vocab_size=engine.config.vocab)
     finally:
         for sc in scheds:
             sc.stop()
@@ -159,9 +159,9 @@ def _serve_elastic(cfg, tokenizer, builder, uid: int, world: int, local: int) ->
     worker = threading.Thread(target=lambda: run_elastic_rank(group, build_engine, make_channel, lead, on_error), name="bonsai-elastic-leader", daemon=True)
     worker.start()
     app = create_app(backend, tokenizer, cfg)
-    import uvicorn
+    from .app import serve
     try:
-        uvicorn.run(app, host=cfg.host, port=cfg.port, log_level=cfg.log_level if cfg.log_level in ("debug", "info", "warning", "error") else "info")
+        serve(app, cfg.host, cfg.port, cfg.log_level, tokenizer=tokenizer, native=cfg.native_front)
     finally:
         stop.set()
         worker.join(timeout=30)

@@ -49,6 +49,8 @@ class Backend(Protocol):
 class SchedulerBackend:
     """Backend over a :class:`BatchScheduler` (GPU)."""
 
+    supports_on_done = True            # ``submit(..., on_done=callback)``: called on the scheduler's thread when the request ends
+
     def __init__(self, scheduler, model_name: str):
         self.s = scheduler
         self.model_name = model_name
@@ -67,6 +69,8 @@ class ReplicaBackend:
     """Backend over several :class:`BatchScheduler` s, one per GPU (data-parallel replicas of the whole model): a request goes
     to the replica that its session key hashes to while that replica is healthy and not overloaded, else to the least loaded
     one (``runtime.distributed.ReplicaPool``), so a conversation keeps hitting the replica that holds its prefix cache."""
+
+    supports_on_done = True
 
     def __init__(self, schedulers: list, model_name: str):
         from ..runtime.distributed import ReplicaPool
@@ -373,6 +377,75 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             if completed:
                 breaker.record_success()
 
+    async def native_stream(handle, chat: bool, prompt_ids, params, max_tokens, rid, stops, extra, obj_id, created, model):
+        loop = asyncio.get_running_loop()
+        await sem.acquire()
+        if not breaker.allow():
+            sem.release()
+            metrics.errors.inc()
+            return error(503, "circuit open", "server_error", rid)
+        kind = "chat.completion.chunk" if chat else "text_completion"
+        head = (f'{{"id": {json.dumps(obj_id)}, "object": "{kind}", "created": {created}, "model": {json.dumps(model)}, '
+                f'"choices": [{{"index": 0, ')
+        first = ""
+        if chat:
+            first = "data: " + json.dumps({"id": obj_id, "object": kind, "created": created, "model": model,
+                                           "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
+        try:
+            stream = handle.open_stream(head, chat, stops, first, cfg.request_timeout_ms)
+        except ConnectionError:
+            sem.release()
+            return error(499, "client closed the connection", "server_error", rid)
+        t0 = time.perf_counter()
+        metrics.active_requests.inc()
+
+        def on_done(req):                      # the scheduler's thread
+            try:
+                err = None if req.error is None else str(req.error)
+                if stream.state == 3:
+                    err = "request timed out"
+                n_tok = stream.finish(req.finish_reason, err)
+                dt = time.perf_counter() - t0
+                tracker = RequestRateTracker()
+                tracker.t_admit = t0
+                for t in req.token_times:
+                    tracker.on_token(t)
+                if req.t_first_token is not None:
+                    metrics.prefill_seconds.observe(req.t_first_token - t0)
+                metrics.tokens_generated.inc(max(0, n_tok))
+                metrics.request_seconds.observe(dt)
+                if n_tok > 0 and dt > 0:
+                    metrics.tokens_per_second.observe(n_tok / dt)
+                metrics.aggregator.record(tracker)
+                util = backend.kv_utilization()
+                metrics.kv_utilization.set(util)
+                kv_policy.observe(util)
+                metrics.kv_level.set(kv_policy.metric_value())
+                if err is not None:
+                    metrics.errors.inc()
+                    breaker.record_failure()
+                elif stream.state != 2:        # a client that went away is neither a success nor a failure of the engine
+                    breaker.record_success()
+            finally:
+                metrics.active_requests.dec()
+                loop.call_soon_threadsafe(sem.release)
+
+        try:
+            backend.submit(prompt_ids, params, max_tokens, stream.push, rid, on_done=on_done, **extra)
+        except Exception as e:  # noqa: BLE001
+            breaker.record_failure()
+            metrics.errors.inc()
+            metrics.active_requests.dec()
+            sem.release()
+            stream.abandon()
+            handle.stream = None
+            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ in ("QueueFull", "Unavailable") else 500
+            return error(status, str(e), "server_error", rid)
+        metrics.prompt_tokens.inc(len(prompt_ids))
+        from .native_front import NATIVE_STREAM_HEADER
+        return PlainTextResponse("", headers={NATIVE_STREAM_HEADER.decode(): "1", "content-type": "text/event-stream", "x-request-id": rid,
+                                              "cache-control": "no-cache"})
+
     def encode_chat(messages: list[dict]) -> list[int]:
         return tokenizer.encode(chat_prompt(messages, "chatml"))
 
@@ -455,6 +528,12 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                         "top_logprobs": [{"token": piece(t), "logprob": l} for t, l in top]}
                        for tok, (lp, top) in zip(req.tokens, getattr(req, "token_logprobs", []))]
             return {"content": content}
+
+        front = request.scope.get("extensions", {}).get("oxibonsai.front")
+        if body.get("stream") and front is not None and front.front.has_vocab and getattr(backend, "supports_on_done", False):
+            # Behind the native front the stream never comes back through this coroutine: sampled token ids go from the
+            # scheduler's thread straight into the front, which detokenises, holds back stop sequences, frames and writes.
+            return await native_stream(front, chat, prompt_ids, params, max_tokens, rid, stops, extras(), obj_id, created, model)
 
         if body.get("stream"):
             async def sse():
@@ -644,6 +723,12 @@ def generate_json(engine_generate, tokenizer, request_json: str) -> str:
         return _json.dumps({"text": "", "tokens": 0, "error": str(e)})
 
 
-def serve(app, host: str, port: int, log_level: str = "info") -> None:
+def serve(app, host: str, port: int, log_level: str = "info", tokenizer=None, native: bool = True, vocab_size: int | None = None) -> None:
+    """Serves the application: through the native front (``csrc/runtime/http_front.cpp``; with ``tokenizer`` it also streams
+    completions without the interpreter) or, with ``native=False``, through uvicorn."""
+    if native:
+        from .native_front import serve as serve_native
+        serve_native(app, host, port, tokenizer=tokenizer, vocab_size=vocab_size)
+        return
     import uvicorn
-    uvicorn.run(app, host=host, port=port, log_level=log_level)
+    uvicorn.run(app, host=host, port=port, log_level=log_level if log_level in ("debug", "info", "warning", "error") else "info")
