@@ -1,5 +1,5 @@
 """Worker of tests/test_host_sanitizers.py: drives the native host library (loaded from OXIBONSAI_HOST_LIB, an ASan + UBSan
-build) through its codecs, GGUF reader / writer, CPU kernels, tokenizer merges and vocabulary masks."""
+build) through its codecs, GGUF reader / writer, CPU kernels, tokenizer merges, vocabulary masks and the HTTP / SSE front."""
 import os
 import sys
 import tempfile
@@ -56,6 +56,60 @@ def main() -> None:
     table = TokenTable([bytes([b]) for b in range(256)] + [b"true", b"false"])
     c = DfaConstraint.from_regex(table, r"(true|false)+", eos_token=None)
     assert c.allowed_mask().any() and c.advance(256) and c.is_complete()
+    # HTTP / SSE front: requests (whole, split, malformed), a token stream with stop sequences and broken UTF-8, a client
+    # that leaves in mid-stream, shutdown with open connections
+    import http.client
+    import socket
+    import threading
+    from oxibonsai_b200.server.native_front import NativeFront, StreamClosed
+    from oxibonsai_b200.tokenizer import ByteTokenizer
+    front = NativeFront("127.0.0.1", 0)
+    front.set_vocab(ByteTokenizer(), 300)
+    front.start()
+
+    def answer():
+        while True:
+            try:
+                ev = front.next_event(100)
+            except EOFError:
+                return
+            if ev is None or ev[0] != 1:
+                continue
+            conn, target = ev[1], ev[3]
+            if target == "/stream":
+                st = front.open_stream(conn, '{"choices": [{"index": 0, ', True, ["END", "é!"], 'data: {"first": 1}\n\n', 0)
+                st.begin([(b"content-type", b"text/event-stream")])
+                try:
+                    for t in list("héllo \"wörld\" 日本".encode()) + [0xE6, 0x97, 0xFF, 299, 7] + list(b"the END never"):
+                        st.push(t)
+                except StreamClosed:
+                    pass
+                st.finish("length")
+            else:
+                front.respond(conn, 200, [(b"content-type", b"text/plain")], b"x" * 100000)
+
+    threading.Thread(target=answer, daemon=True).start()
+    hc = http.client.HTTPConnection("127.0.0.1", front.port, timeout=10)
+    for target in ("/a", "/stream", "/b"):
+        hc.request("GET", target)
+        assert hc.getresponse().read()
+    for raw in (b"GET / HTTP/1.1\r\nHost: x\r\n\r\nGET /2 HTTP/1.1\r\n\r\n", b"BROKEN\r\n\r\n", b"POST / HTTP/1.1\r\nContent-Length: 10\r\n\r\nabc"):
+        sk = socket.create_connection(("127.0.0.1", front.port))
+        sk.sendall(raw)
+        sk.settimeout(0.3)
+        try:
+            sk.recv(1 << 20)
+        except OSError:
+            pass
+        sk.close()
+    sk = socket.create_connection(("127.0.0.1", front.port))
+    sk.sendall(b"GET /stream HTTP/1.1\r\n\r\n")
+    sk.close()
+    dangling = socket.create_connection(("127.0.0.1", front.port))      # still open when the front shuts down
+    import time
+    time.sleep(0.3)
+    front.close()
+    dangling.close()
     print("sanitizer worker ok")
 
 
