@@ -91,6 +91,7 @@ struct Front {
     std::thread io;
     std::atomic<bool> stopping{false};
     std::atomic<bool> wake_pending{false};
+    std::atomic<bool> lazy{false};      // token pushes do not wake the I/O thread; the producer calls bfront_kick() once per step
     std::mutex mu;
     std::condition_variable cv;
     std::deque<Event> events;
@@ -519,7 +520,7 @@ static void io_loop(Front* f) {
     std::vector<char> buf(1 << 16);
     auto last_sweep = Clock::now();
     while (!f->stopping.load()) {
-        int n = epoll_wait(f->ep, evs.data(), int(evs.size()), 200);
+        int n = epoll_wait(f->ep, evs.data(), int(evs.size()), f->lazy.load(std::memory_order_relaxed) ? 5 : 200);
         if (n < 0 && errno != EINTR) break;
         for (int i = 0; i < n; ++i) {
             uint64_t tag = evs[i].data.u64;
@@ -901,10 +902,17 @@ int bfront_stream_push(void* h, int64_t stream, int32_t token) {
     f->n_stream_events += s->events - before;
     if (!framed.empty()) {
         stream_emit(f, s, framed);
-        if (s->begun) wake_io(f);
+        if (s->begun && !f->lazy.load(std::memory_order_relaxed)) wake_io(f);
     }
     return s->state;
 }
+
+// With lazy wake-ups on, bfront_stream_push() only queues; the producer calls bfront_kick() after the tokens of a decode
+// step (one wake-up and one pass over the connections per step instead of one per token).  The I/O thread still looks at
+// the queue every few milliseconds, so a missing kick delays output, it does not lose it.
+void bfront_set_lazy(void* h, int on) { static_cast<Front*>(h)->lazy.store(on != 0); }
+
+void bfront_kick(void* h) { wake_io(static_cast<Front*>(h)); }
 
 // Ends a stream: the held-back text (unless a stop sequence was hit), the finish chunk, "[DONE]" and the terminating chunk;
 // with ``error`` an error event instead.  The connection goes back to reading requests.  Returns the number of tokens pushed.

@@ -132,6 +132,8 @@ class BatchScheduler:
         # ``idle_hook`` runs every ``idle_hook_seconds`` while nothing is live (a tensor-parallel leader's keep-alive).
         self.before_launch, self.on_fatal, self.idle_hook, self.idle_hook_seconds = before_launch, on_fatal, idle_hook, idle_hook_seconds
         self.fatal: Exception | None = None
+        self.after_step: Callable[[], None] | None = None     # called once after the tokens of a decode step (or of an admission)
+                                                               # have been delivered: a front that batches its writes per step
         from ..core.oracle import EOS_TOKEN
         self.engine = engine
         self.prefill_chunk_tokens = max(16, int(prefill_chunk_tokens))
@@ -301,6 +303,8 @@ class BatchScheduler:
         self._pos.append(len(r.prompt))
         if self._emit(dst, first):
             self._retire(dst)
+        if self.after_step is not None:
+            self.after_step()
         return True
 
     def _emit(self, slot: int, tok: int) -> bool:
@@ -366,3 +370,5 @@ class BatchScheduler:
         for s in range(B - 1, -1, -1):
             if self._emit(s, toks[s]):
                 self._retire(s)
+        if self.after_step is not None:
+            self.after_step()

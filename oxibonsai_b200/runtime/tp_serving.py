@@ -167,11 +167,18 @@ class ElasticBackend:
     def __init__(self, model_name: str, max_seq_len: int):
         self.model_name, self.max_seq_len = model_name, max_seq_len
         self.s = None
+        self._after_step = None
         self.generations = 0
 
     def attach(self, scheduler) -> None:
+        scheduler.after_step = self._after_step
         self.s = scheduler
         self.generations += 1
+
+    def set_after_step(self, fn) -> None:
+        self._after_step = fn
+        if self.s is not None:
+            self.s.after_step = fn
 
     def detach(self) -> None:
         self.s = None

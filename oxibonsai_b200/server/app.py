@@ -64,6 +64,9 @@ class SchedulerBackend:
         e = self.s.engine
         return e.kv_utilization() if hasattr(e, "kv_utilization") else e.kv.utilization
 
+    def set_after_step(self, fn) -> None:
+        self.s.after_step = fn
+
 
 class ReplicaBackend:
     """Backend over several :class:`BatchScheduler` s, one per GPU (data-parallel replicas of the whole model): a request goes
@@ -88,6 +91,10 @@ class ReplicaBackend:
 
     def kv_utilization(self) -> float:
         return max(s.engine.kv_utilization() for s in self.schedulers.values())
+
+    def set_after_step(self, fn) -> None:
+        for s in self.schedulers.values():
+            s.after_step = fn
 
     def replica_loads(self) -> dict:
         return {k: {"live": s.active, "queued": len(s.queue)} for k, s in self.schedulers.items()}
@@ -728,7 +735,14 @@ def serve(app, host: str, port: int, log_level: str = "info", tokenizer=None, na
     completions without the interpreter) or, with ``native=False``, through uvicorn."""
     if native:
         from .native_front import serve as serve_native
-        serve_native(app, host, port, tokenizer=tokenizer, vocab_size=vocab_size)
+
+        def ready(front) -> None:
+            # the schedulers tell the front when a step's tokens are all in: one wake-up of its I/O thread per step
+            backend = getattr(app.state, "backend", None)
+            if hasattr(backend, "set_after_step"):
+                backend.set_after_step(front.kick)
+                front.set_lazy(True)
+        serve_native(app, host, port, tokenizer=tokenizer, vocab_size=vocab_size, on_ready=ready)
         return
     import uvicorn
     uvicorn.run(app, host=host, port=port, log_level=log_level if log_level in ("debug", "info", "warning", "error") else "info")

@@ -52,6 +52,10 @@ def _lib():
         lib.bfront_stream_finish.argtypes = [C.c_void_p, C.c_int64, C.c_char_p, C.c_char_p]
         lib.bfront_stream_abandon.argtypes = [C.c_void_p, C.c_int64]
         lib.bfront_stream_abandon.restype = None
+        lib.bfront_set_lazy.argtypes = [C.c_void_p, C.c_int]
+        lib.bfront_set_lazy.restype = None
+        lib.bfront_kick.argtypes = [C.c_void_p]
+        lib.bfront_kick.restype = None
         lib.bfront_stats.argtypes = [C.c_void_p, C.POINTER(C.c_uint64)]
         lib.bfront_stats.restype = None
         # The per-token call is a few hundred nanoseconds of work under a mutex: it keeps the interpreter lock (``PyDLL``).
@@ -59,7 +63,10 @@ def _lib():
         # (milliseconds) to get it back - once per token.
         held = C.PyDLL(lib._name)
         held.bfront_stream_push.argtypes = [C.c_void_p, C.c_int64, C.c_int32]
+        held.bfront_kick.argtypes = [C.c_void_p]
+        held.bfront_kick.restype = None
         lib._bfront_push_held = held.bfront_stream_push
+        lib._bfront_kick_held = held.bfront_kick
         lib._bfront_ready = True
     return lib
 
@@ -195,6 +202,14 @@ class NativeFront:
         if sid <= 0:
             raise ConnectionError("the connection is gone")
         return NativeStream(self, sid)
+
+    def set_lazy(self, on: bool) -> None:
+        """Lazy wake-ups: pushed tokens are written when :meth:`kick` is called (the producer does that once per decode
+        step) or, failing that, within a few milliseconds."""
+        self._lib.bfront_set_lazy(self._h, 1 if on else 0)
+
+    def kick(self) -> None:
+        self._lib._bfront_kick_held(self._h)
 
     def stats(self) -> dict:
         out = (C.c_uint64 * 7)()
