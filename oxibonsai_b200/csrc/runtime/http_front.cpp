@@ -222,6 +222,7 @@ static size_t utf8_complete_prefix(const char* s, size_t n) {
 }
 
 static void wake_io(Front* f) {
+    if (f->stopping.load(std::memory_order_relaxed)) return;
     if (!f->wake_pending.exchange(true)) {
         uint64_t one = 1;
         ssize_t r = write(f->wake, &one, sizeof one);
@@ -665,7 +666,11 @@ void* bfront_create(const char* host, int port, int backlog) {
     epoll_ctl(f->ep, EPOLL_CTL_ADD, f->listen_fd, &ev);
     ev.data.u64 = UINT64_MAX;
     epoll_ctl(f->ep, EPOLL_CTL_ADD, f->wake, &ev);
-    return f.release();
+    static std::mutex reg_mu;
+    static std::vector<std::unique_ptr<Front>> registry;      // fronts live as long as the process (see bfront_destroy)
+    std::lock_guard<std::mutex> lk(reg_mu);
+    registry.push_back(std::move(f));
+    return registry.back().get();
 }
 
 int bfront_port(void* h) { return static_cast<Front*>(h)->port; }
@@ -679,8 +684,10 @@ int bfront_start(void* h) {
 
 void bfront_stop(void* h) {
     Front* f = static_cast<Front*>(h);
-    f->stopping.store(true);
-    wake_io(f);
+    if (f->stopping.exchange(true)) return;
+    uint64_t one = 1;
+    ssize_t r = write(f->wake, &one, sizeof one);       // wake_io() is a no-op once the front is stopping
+    (void)r;
     if (f->io.joinable()) f->io.join();
     std::lock_guard<std::mutex> lk(f->mu);
     for (auto& kv : f->conns) close(kv.second->fd);
@@ -692,12 +699,20 @@ void bfront_stop(void* h) {
     f->cv.notify_all();
 }
 
+// Stops the front and releases its descriptors.  The object itself stays valid until the process ends: a scheduler thread
+// may still push a token, and an event waiter may still be on its way out, after the owner has closed the front; every
+// call on a stopped front returns "gone" instead of touching freed memory.
 void bfront_destroy(void* h) {
     Front* f = static_cast<Front*>(h);
-    if (!f->stopping.load()) bfront_stop(h);
+    bfront_stop(h);
+    std::lock_guard<std::mutex> lk(f->mu);
     if (f->ep >= 0) close(f->ep);
     if (f->wake >= 0) close(f->wake);
-    delete f;
+    f->ep = f->wake = -1;
+    f->streams.clear();
+    f->events.clear();
+    f->vocab_bytes.clear();
+    f->vocab_bytes.shrink_to_fit();
 }
 
 // Token id -> bytes table: ``offsets`` has n + 1 entries into ``bytes``.

@@ -125,6 +125,7 @@ class NativeFront:
             raise OSError(f"cannot listen on {host}:{port}")
         self.host, self.port = host, int(self._lib.bfront_port(self._h))
         self._stopped = False
+        self._closed = False
         self.has_vocab = False
 
     def start(self) -> "NativeFront":
@@ -137,10 +138,12 @@ class NativeFront:
             self._lib.bfront_stop(self._h)
 
     def close(self) -> None:
-        if self._h:
+        """Stops the I/O thread and closes every socket.  The native object stays valid for the rest of the process, so a
+        thread that still holds a stream or waits for an event gets "gone" / end-of-events instead of a dangling pointer."""
+        if not self._closed:
+            self._closed = True
             self.stop()
             self._lib.bfront_destroy(self._h)
-            self._h = None
 
     def set_vocab(self, tokenizer, vocab_size: int | None = None) -> None:
         """Token id -> bytes for every id, so that streams detokenise without the interpreter."""

@@ -293,3 +293,23 @@ def test_application_behind_the_front_streams_like_the_python_path():
         thread.join(5)
         front.close()
         sched.stop()
+
+
+def test_front_is_race_free_under_thread_sanitizer(tmp_path):
+    """The front's C++ compiled with -fsanitize=thread together with a driver that runs clients, a dispatcher and a token
+    producer concurrently (tests/front_tsan_driver.cpp): no data race may be reported."""
+    import os
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    src = os.path.join(os.path.dirname(here), "oxibonsai_b200", "csrc", "runtime", "http_front.cpp")
+    exe = str(tmp_path / "front_tsan")
+    probe = subprocess.run(["g++", "-fsanitize=thread", "-x", "c++", "-", "-o", str(tmp_path / "probe")], input="int main(){return 0;}", capture_output=True, text=True)
+    if probe.returncode != 0:
+        pytest.skip("the host compiler has no ThreadSanitizer runtime")
+    build = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-pthread", "-fsanitize=thread", src, os.path.join(here, "front_tsan_driver.cpp"), "-o", exe],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-3000:]
+    for _ in range(2):
+        run = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0"))
+        assert run.returncode == 0 and "tsan driver ok" in run.stdout, run.stdout[-1000:] + run.stderr[-3000:]
+        assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
