@@ -239,13 +239,23 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         return _table[0]
 
     def constraint_from(body: dict):
-        """``response_format`` of the request as a token constraint: ``{"type": "json_object"}`` -> any JSON value,
+        """The request's token constraint.  ``tool_choice`` "required" / a named function (with ``tools``) -> a call of one of
+        those tools with arguments of the tool's schema; ``response_format`` ``{"type": "json_object"}`` -> any JSON value,
         ``{"type": "json_schema", "json_schema": {"schema": {...}}}`` -> JSON of that shape; None for plain text."""
+        eos = getattr(tokenizer, "eos_token_id", None)
+        if body.get("tools") and body.get("tool_choice") not in (None, "auto", "none"):
+            # a forced tool call: the sampler may only write <tool_call>{"name":...,"arguments":<the tool's schema>}</tool_call>
+            from ..runtime.tools import ToolCallError, build_tool_constraint, tool_choice_names
+            try:
+                names = tool_choice_names(body["tool_choice"], body["tools"])
+                if names is not None:
+                    return build_tool_constraint(token_table(), body["tools"], names, eos)
+            except ToolCallError as e:
+                raise ValueError(str(e)) from e
         rf = body.get("response_format")
         if not isinstance(rf, dict) or rf.get("type") in (None, "text"):
             return None
         from ..runtime.constrained import json_constraint, json_schema_constraint
-        eos = getattr(tokenizer, "eos_token_id", None)
         if rf["type"] == "json_object":
             return json_constraint(token_table(), eos)
         if rf["type"] == "json_schema":

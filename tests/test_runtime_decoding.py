@@ -282,3 +282,84 @@ def test_finished_is_asked_for_by_bounded_constraints_only():
     assert not end.finished() and end.advance(263) and end.is_complete() and end.finished()
     both = AllOf(AllowListConstraint(t, [7, 8]), SequenceConstraint(t, [7]))
     assert not both.finished() and both.advance(7) and both.finished()
+
+
+WEATHER = {"type": "function", "function": {"name": "get_weather", "description": "current weather",
+                                            "parameters": {"type": "object", "required": ["city"],
+                                                           "properties": {"city": {"type": "string", "maxLength": 12}, "celsius": {"type": "boolean"}}}}}
+CLOCK = {"type": "function", "function": {"name": "get_time", "parameters": {"type": "object", "properties": {"tz": {"enum": ["UTC", "JST"]}}}}}
+
+
+def test_tool_selection_validation_and_errors():
+    from oxibonsai_b200.runtime import tools as T
+    call = T.select_tool('I will check. {"name": "get_weather", "arguments": {"city": "Kyoto"}}', [WEATHER, CLOCK])
+    assert call["id"].startswith("call_") and len(call["id"]) == 29 and call["type"] == "function"
+    assert call["function"]["name"] == "get_weather" and json.loads(call["function"]["arguments"]) == {"city": "Kyoto"}
+    assert T.make_tool_call("call_x", "f", {"a": 1}) == {"id": "call_x", "type": "function", "function": {"name": "f", "arguments": '{"a": 1}'}}
+    with pytest.raises(T.NoToolCallFound):
+        T.select_tool("no call here", [WEATHER])
+    with pytest.raises(T.UnknownTool, match="unknown tool: 'launch'"):
+        T.select_tool('{"name": "launch", "arguments": {}}', [WEATHER])
+    assert T.select_tool('{"name": "launch", "arguments": {}}', [])["function"]["name"] == "launch"      # no list: any name passes
+    with pytest.raises(T.MalformedArguments):
+        T.select_tool('{"name": "get_weather", "arguments": "{not json"}', [WEATHER])
+    reg = T.ToolRegistry([WEATHER, CLOCK])
+    assert len(reg) == 2 and set(reg.names()) == {"get_weather", "get_time"} and reg.get("get_time") is CLOCK and reg.get("x") is None
+    assert not reg.is_empty() and T.ToolRegistry([]).is_empty() and "get_time" in reg
+    assert T.validate_tool_arguments('{"city": "Nara", "extra": 1}', WEATHER) == {"city": "Nara", "extra": 1}
+    for bad, why in (('{"celsius": true}', "missing required field 'city'"), ("[1]", "must be a JSON object"), ("{", "malformed")):
+        with pytest.raises(T.MalformedArguments, match=why):
+            T.validate_tool_arguments(bad, WEATHER)
+    with pytest.raises(T.MalformedArguments):
+        T.validate_tool_arguments('{"city": 5}', WEATHER, strict=True)                                      # wrong type: only the strict check sees it
+    assert T.validate_tool_arguments('{"city": 5}', WEATHER) == {"city": 5}
+    assert [e.kind for e in (T.NoToolCallFound(), T.UnknownTool("x"), T.MalformedArguments("r"), T.GrammarCompileError("r"), T.EmptyToolList())] == \
+        ["NoToolCallFound", "UnknownTool", "MalformedArguments", "GrammarCompileError", "EmptyToolList"]
+    assert T.tool_choice_names("auto", [WEATHER]) is None and T.tool_choice_names(None, [WEATHER]) is None
+    assert T.tool_choice_names("required", [WEATHER, CLOCK]) == ["get_weather", "get_time"]
+    assert T.tool_choice_names({"type": "function", "function": {"name": "get_time"}}, [WEATHER, CLOCK]) == ["get_time"]
+    with pytest.raises(T.UnknownTool):
+        T.tool_choice_names({"type": "function", "function": {"name": "nope"}}, [WEATHER])
+
+
+def test_tool_constraint_only_admits_well_formed_calls():
+    from oxibonsai_b200.runtime import tools as T
+    from oxibonsai_b200.runtime.constrained import ConstrainedSampler
+    with pytest.raises(T.EmptyToolList):
+        T.build_tool_grammar([])
+    t = _table()
+    eos = 264
+    rng = np.random.default_rng(1)
+    seen = set()
+    for trial in range(6):
+        c = T.build_tool_constraint(t, [WEATHER, CLOCK], None if trial < 4 else ["get_time"], eos_token=eos)
+        out = bytearray()
+
+        def pick(logits):
+            ok = np.flatnonzero(np.isfinite(logits))
+            if eos in ok:
+                return eos
+            printable = [i for i in ok if i >= 256 or 32 <= i < 127]      # keep the random strings short and readable
+            return int(rng.choice(printable if printable else ok))
+        s = ConstrainedSampler(c, pick, t.n)
+        for _ in range(400):
+            tok = s.sample(np.zeros(t.n))
+            if tok == eos:
+                break
+            out += t.tokens[tok]
+        text = out.decode("utf-8", errors="replace")
+        assert text.startswith('<tool_call>{"name":"get_') and text.endswith("}</tool_call>"), text
+        call = T.select_tool(text, [WEATHER, CLOCK])
+        tool = T.ToolRegistry([WEATHER, CLOCK]).get(call["function"]["name"])
+        T.validate_tool_arguments(call["function"]["arguments"], tool, strict=True)
+        seen.add(call["function"]["name"])
+        if trial >= 4:
+            assert call["function"]["name"] == "get_time"
+    assert seen <= {"get_weather", "get_time"} and seen
+    # the constraint refuses a call of a tool that is not in the list, byte by byte
+    c = T.build_tool_constraint(t, [WEATHER], eos_token=eos)
+    for b in b'<tool_call>{"name":"get_':
+        assert c.advance(b)
+    from oxibonsai_b200.runtime.constrained import mask_to_bool
+    allowed = mask_to_bool(c.allowed_mask(), t.n)
+    assert allowed[ord("w")] and not allowed[ord("t")] and allowed.sum() == 1

@@ -363,3 +363,52 @@ def test_response_format_becomes_a_token_constraint_and_logprobs_are_returned():
     assert be.extra == {} and "logprobs" not in j["choices"][0]
     assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "yaml"}}).status_code == 400
     assert c.post("/v1/completions", json={"prompt": "x", "logprobs": 3, "max_tokens": 4}).json()["choices"][0]["logprobs"]["content"]
+
+
+def test_forced_tool_choice_constrains_the_generation():
+    """``tool_choice`` with ``tools``: the backend receives a constraint that only admits a call of the named tool; the
+    response carries it as ``tool_calls``.  A tool that is not defined is a 400."""
+    import numpy as np
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.runtime.constrained import mask_to_bool
+    from oxibonsai_b200.server.app import create_app
+
+    class ConstraintFollower(FakeBackend):
+        def submit(self, prompt, params, max_tokens, on_token, request_id, constraint=None, **extra):
+            r = _Req()
+            self.seen.append(constraint)
+
+            def run():
+                for _ in range(max_tokens):
+                    if constraint is None or constraint.finished():
+                        break
+                    ok = np.flatnonzero(mask_to_bool(constraint.allowed_mask(), 256))
+                    pick = next((int(t) for t in ok if 97 <= t < 123 or t in b'"{}<>/_:,'), int(ok[0]))
+                    constraint.advance(pick)
+                    r.tokens.append(pick)
+                    if on_token:
+                        on_token(pick)
+                r.finish_reason = "stop"
+                r.done.set()
+            threading.Thread(target=run, daemon=True).start()
+            return r
+
+    be = ConstraintFollower()
+    c = TestClient(create_app(be, ByteTokenizer(), ServerConfig()))
+    tools = [{"type": "function", "function": {"name": "get_time", "parameters": {"type": "object", "required": ["tz"], "properties": {"tz": {"enum": ["utc", "jst"]}}}}},
+             {"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+    body = {"messages": [{"role": "user", "content": "what time is it"}], "tools": tools, "max_tokens": 200,
+            "tool_choice": {"type": "function", "function": {"name": "get_time"}}}
+    r = c.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    choice = r.json()["choices"][0]
+    assert choice["finish_reason"] == "tool_calls" and choice["message"]["content"] is None
+    call = choice["message"]["tool_calls"][0]
+    assert call["function"]["name"] == "get_time" and json.loads(call["function"]["arguments"])["tz"] in ("utc", "jst")
+    assert be.seen[-1] is not None
+    body["tool_choice"] = "auto"
+    c.post("/v1/chat/completions", json=body)
+    assert be.seen[-1] is None                                   # free text: no constraint
+    body["tool_choice"] = {"type": "function", "function": {"name": "launch_rocket"}}
+    r = c.post("/v1/chat/completions", json=body)
+    assert r.status_code == 400 and "unknown tool" in r.json()["error"]["message"]
