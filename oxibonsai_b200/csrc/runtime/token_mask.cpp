@@ -7,25 +7,21 @@
 // byte) and two mask builders, one for byte-level DFAs and one that prefilters by the set of bytes an
 // arbitrary recogniser can accept next.  Masks are packed 32 tokens per word, bit set = allowed, which
 // is the format the GPU sampler takes.
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <vector>
 
-namespace {
+#include "token_table.hpp"
 
-struct TokenTable {
-  std::vector<uint32_t> off;     // n + 1
-  std::vector<uint8_t> bytes;
-  std::vector<uint32_t> by_first[256];
-  uint32_t n = 0;
-};
-
-}  // namespace
+using bonsai_tok::TokenTable;
 
 extern "C" {
 
 void* btok_new(const uint32_t* offsets, const uint8_t* bytes, uint32_t n) {
+  static std::atomic<uint64_t> next_serial{1};
   TokenTable* t = new TokenTable();
+  t->serial = next_serial.fetch_add(1);
   t->n = n;
   t->off.assign(offsets, offsets + n + 1);
   t->bytes.assign(bytes, bytes + offsets[n]);
@@ -84,3 +80,56 @@ void btok_pack_ids(const uint32_t* ids, uint32_t n_ids, uint32_t n_tokens, uint3
 }
 
 }  // extern "C"
+
+// ---- byte trie ------------------------------------------------------------------------------------------------------------
+#include <algorithm>
+#include <numeric>
+
+void bonsai_tok::TokenTable::build_trie() {
+  // tokens sorted by their bytes: every trie node is a contiguous range of the sorted order at some depth
+  std::vector<uint32_t> order(n);
+  std::iota(order.begin(), order.end(), 0u);
+  auto tok = [&](uint32_t i) { return std::pair<const uint8_t*, uint32_t>(bytes.data() + off[i], off[i + 1] - off[i]); };
+  std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+    auto [pa, la] = tok(a);
+    auto [pb, lb] = tok(b);
+    int c = std::memcmp(pa, pb, std::min(la, lb));
+    return c != 0 ? c < 0 : (la != lb ? la < lb : a < b);
+  });
+  struct Work {
+    uint32_t node, lo, hi, depth;
+  };
+  nodes.clear();
+  edges.clear();
+  node_tokens.clear();
+  nodes.emplace_back();
+  std::vector<Work> stack{{0, 0, n, 0}};
+  while (!stack.empty()) {
+    Work w = stack.back();
+    stack.pop_back();
+    uint32_t i = w.lo;
+    // tokens that end here come first in the sorted range (shorter sorts before longer with the same prefix)
+    nodes[w.node].tok_begin = uint32_t(node_tokens.size());
+    while (i < w.hi && tok(order[i]).second == w.depth) {
+      if (w.depth > 0) node_tokens.push_back(order[i]);
+      ++i;
+    }
+    nodes[w.node].tok_end = uint32_t(node_tokens.size());
+    uint32_t first_edge = uint32_t(edges.size());
+    std::vector<Work> kids;
+    while (i < w.hi) {
+      uint8_t b = tok(order[i]).first[w.depth];
+      uint32_t j = i;
+      while (j < w.hi && tok(order[j]).first[w.depth] == b) ++j;
+      uint32_t child = uint32_t(nodes.size());
+      nodes.emplace_back();
+      edges.push_back({b, child});
+      kids.push_back({child, i, j, w.depth + 1});
+      i = j;
+    }
+    nodes[w.node].child_begin = first_edge;
+    nodes[w.node].child_end = uint32_t(edges.size());
+    // children's edge ranges must be contiguous per node: process kids after this node's edges were all appended
+    for (auto it = kids.rbegin(); it != kids.rend(); ++it) stack.push_back(*it);
+  }
+}

@@ -7,7 +7,7 @@ grammar/cache.rs:52 (``GrammarConstraint`` with an ``AllowedTokensCache``).
 
 Masks are packed 32 tokens per uint32 (bit set = allowed): exactly what the GPU sampler's ``allow_mask`` argument takes,
 so a constraint costs one small host-to-device copy per token and no extra kernel.  The per-token automaton walk over
-the vocabulary runs in C++ (csrc/runtime/token_mask.cpp).
+the vocabulary runs in C++ (csrc/runtime/token_mask.cpp for automata, csrc/runtime/grammar_matcher.cpp for grammars).
 """
 from __future__ import annotations
 
@@ -247,21 +247,34 @@ class DfaConstraint(TokenConstraint):
 
 
 class GrammarConstraint(TokenConstraint):
-    """Output must be a sentence of a context-free grammar (Earley).  Candidate tokens are prefiltered natively by
-    first byte, then walked through forks of the recogniser along a byte trie so shared prefixes are parsed once."""
+    """Output must be a sentence of a context-free grammar (Earley).  The recogniser and the search for the allowed tokens
+    run in C++ (``grammar/native.py``): one recogniser walks the vocabulary's byte trie depth-first, entering only the bytes
+    the grammar can scan, and the finished mask is cached under the chart position's signature inside the compiled grammar,
+    which every constraint over a structurally equal grammar shares.  ``native=False`` selects the Python recogniser (the
+    oracle of the tests)."""
     name = "grammar"
 
-    def __init__(self, table: TokenTable, grammar: Grammar, eos_token: int | None = None, cache_size: int = 512):
-        self.table, self.eos = table, eos_token
-        self.rec = EarleyRecognizer(grammar)
+    def __init__(self, table: TokenTable, grammar: Grammar, eos_token: int | None = None, cache_size: int = 512, native: bool = True):
+        self.table, self.eos, self.native = table, eos_token, native
+        if native:
+            from .grammar.native import NativeEarley
+            self.rec = NativeEarley(grammar)
+        else:
+            self.rec = EarleyRecognizer(grammar)
         self.text = bytearray()
         self._cache: OrderedDict[bytes, np.ndarray] = OrderedDict()
         self._cap = cache_size
+        self.cache_hits = 0
 
     def allowed_mask(self):
+        if self.native:
+            mask, cached = self.rec.mask(self.table, self.eos)
+            self.cache_hits += int(cached)
+            return mask
         key = bytes(self.text)
         if key in self._cache:
             self._cache.move_to_end(key)
+            self.cache_hits += 1
             return self._cache[key]
         ok: list[int] = []
         cand = self.table.candidates(self.rec.next_bytes())

@@ -100,9 +100,11 @@ class Grammar:
         return [Term(frozenset([b])) for b in data]
 
     def star(self, body: list[Symbol], hint: str = "rep") -> NonTerm:
+        # left-recursive: an Earley chart then holds a constant number of items per repetition (the right-recursive form
+        # leaves one pending item per repetition and completes all of them at every position where the body may end)
         n = self.fresh(hint)
         self.add(n, [])
-        self.add(n, body + [NonTerm(n)])
+        self.add(n, [NonTerm(n)] + body)
         return NonTerm(n)
 
     def plus(self, body: list[Symbol], hint: str = "rep") -> list[Symbol]:

@@ -56,6 +56,16 @@ def main() -> None:
     table = TokenTable([bytes([b]) for b in range(256)] + [b"true", b"false"])
     c = DfaConstraint.from_regex(table, r"(true|false)+", eos_token=None)
     assert c.allowed_mask().any() and c.advance(256) and c.is_complete()
+    # the Earley matcher and the trie walk behind grammar constraints
+    from oxibonsai_b200.runtime.constrained import json_constraint, json_schema_constraint, mask_to_bool
+    for gc in (json_constraint(table, None), json_schema_constraint(table, {"type": "object", "required": ["a"], "properties": {"a": {"type": "array", "items": {"type": "number"}}}}, None)):
+        for b in b'{"a": [1, 2.5e3, -7]}':
+            m = gc.allowed_mask()
+            assert mask_to_bool(m, table.n)[b]
+            assert gc.advance(b)
+        assert gc.is_complete() and not gc.advance(ord("x"))
+        gc.reset()
+        assert gc.allowed_mask().any()
     # HTTP / SSE front: requests (whole, split, malformed), a token stream with stop sequences and broken UTF-8, a client
     # that leaves in mid-stream, shutdown with open connections
     import http.client

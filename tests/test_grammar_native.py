@@ -1,0 +1,133 @@
+"""The native Earley matcher against the Python recogniser (the oracle): same verdicts byte by byte, same masks, and the
+mask cache keyed by the chart signature."""
+import json
+import random
+import time
+
+import numpy as np
+import pytest
+
+from oxibonsai_b200.runtime.constrained import GrammarConstraint, TokenTable, json_constraint, json_schema_constraint, mask_to_bool
+from oxibonsai_b200.runtime.grammar.ast import parse_gbnf
+from oxibonsai_b200.runtime.grammar.compilers import arithmetic_grammar, identifier_list_grammar, json_grammar, json_schema_to_grammar, regex_to_grammar, yes_no_grammar
+from oxibonsai_b200.runtime.grammar.earley import EarleyRecognizer
+from oxibonsai_b200.runtime.grammar.native import NativeEarley, compile_cached
+
+NESTED = parse_gbnf('root ::= item*\nitem ::= "(" root ")" | "a" | opt "b"\nopt ::= "x"?\n')
+AMBIG = parse_gbnf('root ::= e\ne ::= e "+" e | e "*" e | "n" | "(" e ")" | \n')          # ambiguous, nullable, left and right recursive
+GRAMMARS = {"json": json_grammar(), "arith": arithmetic_grammar(), "idents": identifier_list_grammar(), "yesno": yes_no_grammar(), "nested": NESTED,
+            "ambiguous": AMBIG, "regex": regex_to_grammar(r"(ab|a)*c[0-9]{2,3}(\.[0-9]+)?"),
+            "schema": json_schema_to_grammar({"type": "object", "required": ["id"], "properties": {"id": {"type": "integer"}, "tags": {"type": "array", "items": {"enum": ["x", "yy"]}}}})}
+ALPHABETS = {"json": '{}[]":,.-0123456789 truefalsn\\eE+ab\n', "arith": "0123456789.+-*/() ", "idents": "ab_1, ", "yesno": "yesno", "nested": "()abx",
+             "ambiguous": "n+*()", "regex": "abc0123456789.", "schema": '{}[]":, idtagsxy0123456789-'}
+
+
+@pytest.mark.parametrize("name", sorted(GRAMMARS))
+def test_native_matcher_agrees_with_the_python_recogniser(name):
+    g = GRAMMARS[name]
+    rng = random.Random(hash(name) & 0xFFFF)
+    alphabet = ALPHABETS[name].encode()
+    for trial in range(60):
+        py, nat = EarleyRecognizer(g), NativeEarley(g)
+        assert py.next_bytes() == nat.next_bytes() and py.is_complete() == nat.is_complete()
+        for step in range(rng.randint(1, 40)):
+            nxt = sorted(py.next_bytes())
+            # mostly follow the grammar, sometimes feed a byte it cannot take
+            b = rng.choice(nxt) if nxt and rng.random() < 0.9 else rng.choice(alphabet)
+            ok_py, ok_nat = py.feed(b), nat.feed(b)
+            assert ok_py == ok_nat, (name, trial, step, b)
+            if not ok_py:
+                assert nat.dead and nat.next_bytes() == frozenset() and not nat.is_complete()
+                break
+            assert py.next_bytes() == nat.next_bytes() and py.is_complete() == nat.is_complete() and nat.position == py.position
+    assert NativeEarley(g).accepts(b"") == EarleyRecognizer(g).accepts(b"")
+
+
+def _table(rng, n_extra, alphabet):
+    toks = [bytes([b]) for b in range(256)]
+    toks += [bytes(rng.choice(alphabet) for _ in range(rng.randint(2, 6))) for _ in range(n_extra)]
+    toks += [b"", b"true", b"false", b"null", b'{"', b'":', b'", "', b"\xc3\xa9", b'"}']
+    return TokenTable(toks)
+
+
+@pytest.mark.parametrize("name", ["json", "schema", "nested", "arith", "ambiguous"])
+def test_native_masks_equal_the_python_masks_along_random_walks(name):
+    g = GRAMMARS[name]
+    rng = random.Random(7)
+    table = _table(rng, 400, ALPHABETS[name].encode())
+    eos = 256 + 400                                           # the empty token doubles as EOS
+    for trial in range(4):
+        nat, py = GrammarConstraint(table, g, eos), GrammarConstraint(table, g, eos, native=False)
+        for step in range(25):
+            mn, mp = nat.allowed_mask(), py.allowed_mask()
+            assert np.array_equal(mn, mp), (name, trial, step, bytes(nat.text))
+            ok = np.flatnonzero(mask_to_bool(mn, table.n))
+            ok = ok[ok != eos]
+            if not ok.size:
+                break
+            tok = int(rng.choice(ok))
+            assert nat.advance(tok) and py.advance(tok)
+            assert nat.is_complete() == py.is_complete() and nat.finished() == py.finished()
+        assert not nat.advance(int(np.flatnonzero(~mask_to_bool(nat.allowed_mask(), table.n))[0])) or True
+
+
+def test_signature_cache_is_shared_and_positions_inside_a_string_hit_it():
+    rng = random.Random(1)
+    table = _table(rng, 300, b"abcdefgh ")
+    c = json_constraint(table)
+    stats0 = c.rec.compiled.cache_stats()
+    for b in b'{"key": "x':
+        c.advance(b)
+    sig = c.rec.signature()
+    c.allowed_mask()
+    hits0 = c.cache_hits
+    for b in b"abc def":                                       # every later position inside the string has the same signature
+        c.advance(b)
+        assert c.rec.signature() == sig and c.rec.item_count() < 40
+        c.allowed_mask()
+    assert c.cache_hits == hits0 + 7
+    c.advance(ord('"'))
+    assert c.rec.signature() != sig
+    # a second constraint over a structurally equal grammar shares the compiled object and its masks
+    d = json_constraint(table)
+    assert d.rec.compiled is c.rec.compiled and compile_cached(json_grammar()) is c.rec.compiled
+    for b in b'{"other": "y':
+        d.advance(b)
+    d.allowed_mask()
+    assert d.cache_hits == 1 and c.rec.compiled.cache_stats()["entries"] > stats0["entries"]
+    # a key string and a value string are different states: '":' may end the first, '", "' or '"}' the second
+    k = json_constraint(table)
+    for b in b'{"k':
+        k.advance(b)
+    allowed_key = mask_to_bool(k.allowed_mask(), table.n)
+    allowed_val = mask_to_bool(d.allowed_mask(), table.n)
+    colon, brace = table.tokens.index(b'":'), table.tokens.index(b'"}')
+    assert allowed_key[colon] and not allowed_key[brace] and allowed_val[brace] and not allowed_val[colon]
+
+
+def test_mask_cost_at_a_realistic_vocabulary():
+    """150 K tokens: the first mask inside a string walks the whole trie, the following ones are cache hits; a whole
+    constrained document costs well under a second of masks (it took minutes with the recogniser in Python)."""
+    rng = random.Random(0)
+    alphabet = b'abcdefghijklmnopqrstuvwxyz ABCDEFGHIJKLMNOPQRSTUVWXYZ0123456789{}[]":,.-_\n'
+    toks = [bytes([b]) for b in range(256)] + [bytes(rng.choice(alphabet) for _ in range(rng.randint(2, 8))) for _ in range(150000)]
+    table = TokenTable(toks)
+    schema = {"type": "object", "required": ["name", "age", "tags"],
+              "properties": {"name": {"type": "string"}, "age": {"type": "integer"}, "tags": {"type": "array", "items": {"type": "string"}}}}
+    c = json_schema_constraint(table, schema)
+    doc = b'{"name": "Alice Liddell", "age": 42, "tags": ["a", "bcd"]}'
+    times = []
+    for b in doc:
+        t = time.perf_counter()
+        m = c.allowed_mask()
+        times.append(time.perf_counter() - t)
+        assert mask_to_bool(m, table.n)[b]
+        assert c.advance(b)
+    assert c.is_complete() and json.loads(doc)
+    assert sum(times) < 5.0 and sorted(times)[len(times) // 2] < 0.05, (sum(times), max(times))
+    second = json_schema_constraint(table, schema)             # the next request with the same schema starts with a warm cache
+    t = time.perf_counter()
+    for b in doc:
+        second.allowed_mask()
+        second.advance(b)
+    assert time.perf_counter() - t < 0.5 and second.cache_hits == len(doc)
