@@ -101,6 +101,17 @@ struct Front {
     int64_t next_id = 1;
     std::vector<uint8_t> vocab_bytes;
     std::vector<uint32_t> vocab_off;    // n + 1 offsets
+    ~Front() {                        // process exit with the front still running: stop the I/O thread before it is destroyed
+        if (io.joinable()) {
+            stopping.store(true);
+            uint64_t one = 1;
+            if (wake >= 0) {
+                ssize_t r = write(wake, &one, sizeof one);
+                (void)r;
+            }
+            io.join();
+        }
+    }
     // counters (read through bfront_stats)
     uint64_t n_accepted = 0, n_requests = 0, n_stream_events = 0, n_stream_tokens = 0;
     std::atomic<uint64_t> n_bytes_out{0};

@@ -418,7 +418,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
 
         def on_done(req):                      # the scheduler's thread
             try:
-                err = None if req.error is None else str(req.error)
+                err = None if req.error is None else (str(req.error) or type(req.error).__name__)
                 if stream.state == 3:
                     err = "request timed out"
                 n_tok = stream.finish(req.finish_reason, err)

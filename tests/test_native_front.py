@@ -313,3 +313,65 @@ def test_front_is_race_free_under_thread_sanitizer(tmp_path):
         run = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0"))
         assert run.returncode == 0 and "tsan driver ok" in run.stdout, run.stdout[-1000:] + run.stderr[-3000:]
         assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
+
+
+def test_client_that_leaves_frees_its_slot_and_failed_submits_answer_503():
+    """Behind the front a stream whose client goes away is cancelled at its next token (the scheduler frees the slot), and a
+    backend that refuses a request (queue full) answers 503 on the same connection instead of opening a stream."""
+    import socket
+    from test_scheduler_cpu import FakeEngine
+    from oxibonsai_b200.runtime.scheduler import BatchScheduler
+    from oxibonsai_b200.server.app import SchedulerBackend, create_app
+    from oxibonsai_b200.server.config import ServerConfig
+
+    class SlowBytes(FakeEngine):
+        def finish_sequence(self, prompt, slot):
+            return 97 + super().finish_sequence(prompt, slot) % 26
+
+        def step_batch(self, positions):
+            return [97 + t % 26 for t in super().step_batch(positions)]
+
+        def kv_utilization(self):
+            return 0.0
+
+    eng = SlowBytes(step_delay=0.01)
+    eng.config = type("C", (), {"name": "fake"})()
+    sched = BatchScheduler(eng, prefill_chunk_tokens=16, eos_token=-1, queue_capacity=1).start()
+    tok = ByteTokenizer()
+    app = create_app(SchedulerBackend(sched, "fake"), tok, ServerConfig())
+    front, stop, thread = _serve_app(app, tok)
+    app.state.backend.set_after_step(front.kick)
+    front.set_lazy(True)
+    try:
+        body = json.dumps({"prompt": "abcdefgh", "max_tokens": 2000, "stream": True}).encode()
+        s = socket.create_connection(("127.0.0.1", front.port))
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: " + str(len(body)).encode() + b"\r\n\r\n" + body)
+        got = b""
+        while got.count(b"data: ") < 5:
+            got += s.recv(65536)
+        assert sched.active == 1
+        s.close()                                              # the client leaves after a few tokens
+        deadline = time.monotonic() + 5
+        while sched.active and time.monotonic() < deadline:
+            time.sleep(0.01)
+        assert sched.active == 0 and sched.tokens_generated < 1500        # cancelled long before max_tokens
+        assert front.stats()["open_streams"] == 0 and app.state.metrics.active_requests.get() == 0
+        # the admission queue holds one request: a burst of eight is partly refused with 503 (how many depends on timing), not hung
+        conns = []
+        for _ in range(8):
+            c = http.client.HTTPConnection("127.0.0.1", front.port, timeout=20)
+            c.request("POST", "/v1/completions", body=json.dumps({"prompt": "abcdefgh", "max_tokens": 40, "stream": True}), headers={"Content-Type": "application/json"})
+            conns.append(c)
+        statuses = []
+        for c in conns:
+            r = c.getresponse()
+            statuses.append(r.status)
+            data = r.read()
+            assert (b"[DONE]" in data) if r.status == 200 else (b"error" in data)
+        assert statuses.count(200) >= 1 and statuses.count(503) >= 1 and set(statuses) <= {200, 503}
+        assert app.state.metrics.active_requests.get() == 0
+    finally:
+        stop.set()
+        thread.join(5)
+        front.close()
+        sched.stop()
