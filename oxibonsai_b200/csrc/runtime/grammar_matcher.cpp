@@ -16,6 +16,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <shared_mutex>
 #include <unordered_map>
 #include <vector>
 
@@ -50,6 +51,15 @@ struct MaskKeyHash {
   }
 };
 
+struct TransKey {
+  uint64_t sig;
+  uint8_t byte;
+  bool operator==(const TransKey& o) const { return sig == o.sig && byte == o.byte; }
+};
+struct TransKeyHash {
+  size_t operator()(const TransKey& k) const { return size_t((k.sig ^ (uint64_t(k.byte) * 0x9E3779B97F4A7C15ull)) * 0xff51afd7ed558ccdull); }
+};
+
 struct Grammar {
   std::vector<ByteSet> terms;
   std::vector<int32_t> syms;          // >= 0: rule id, < 0: terminal -(id + 1)
@@ -62,6 +72,13 @@ struct Grammar {
   std::unordered_map<MaskKey, std::shared_ptr<std::vector<uint32_t>>, MaskKeyHash> masks;
   uint64_t hits = 0, misses = 0;
   size_t cap = 4096;
+  // Lazily built automaton over chart signatures: (signature, byte) -> signature after the byte, and the bytes a signature
+  // can scan.  A signature stands for everything that can still follow, so once a transition has been seen the trie walk
+  // takes it without touching the chart; only unseen transitions run the recogniser.
+  std::shared_mutex tmu;
+  std::unordered_map<TransKey, uint64_t, TransKeyHash> trans;
+  std::unordered_map<uint64_t, ByteSet> info;
+  uint64_t walked_real = 0, walked_cached = 0;
 };
 
 // item = prod (24 bits) | dot (8 bits) | origin (32 bits)
@@ -233,22 +250,105 @@ struct Matcher {
 };
 
 // Depth-first over the vocabulary trie from the matcher's current position; sets the bit of every token that can be fed.
-uint32_t walk(Matcher& m, const TokenTable& t, uint32_t node, uint32_t* mask) {
+// The walk moves through chart signatures: a transition that the grammar's automaton already knows costs a hash lookup; an
+// unknown one materialises the chart at that trie node (replaying the bytes of the path that were taken virtually), feeds
+// the byte for real and records where it led.
+struct Walker {
+  Matcher& m;
+  const TokenTable& t;
+  Grammar& g;
+  uint32_t* mask;
+  size_t root_depth;
+  std::vector<uint8_t> path;          // bytes from the walk's root to the current trie node
+  size_t real = 0;                    // how many of them the chart holds (chart depth = root_depth + real)
+  std::unordered_map<TransKey, uint64_t, TransKeyHash> new_trans;
+  std::unordered_map<uint64_t, ByteSet> new_info;
   uint32_t allowed = 0;
-  const auto& nd = t.nodes[node];
-  for (uint32_t k = nd.tok_begin; k < nd.tok_end; ++k) {
-    uint32_t id = t.node_tokens[k];
-    mask[id >> 5] |= 1u << (id & 31);
-    ++allowed;
+  uint64_t n_real = 0, n_cached = 0;
+
+  const ByteSet* info(uint64_t sig) const {
+    auto a = new_info.find(sig);
+    if (a != new_info.end()) return &a->second;
+    auto b = g.info.find(sig);
+    return b == g.info.end() ? nullptr : &b->second;
   }
-  for (uint32_t e = nd.child_begin; e < nd.child_end; ++e) {
-    uint8_t b = t.edges[e].byte;
-    if (!m.chart[m.depth].next.has(b)) continue;
-    m.feed(b);
-    allowed += walk(m, t, t.edges[e].node, mask);
-    m.pop();
+  bool transition(uint64_t sig, uint8_t byte, uint64_t& out) const {
+    TransKey k{sig, byte};
+    auto a = new_trans.find(k);
+    if (a != new_trans.end()) {
+      out = a->second;
+      return true;
+    }
+    auto b = g.trans.find(k);
+    if (b == g.trans.end()) return false;
+    out = b->second;
+    return true;
   }
-  return allowed;
+  void materialise() {
+    while (real < path.size()) {
+      m.feed(path[real]);
+      ++real;
+    }
+  }
+  void visit(uint32_t node, uint64_t sig) {
+    const auto& nd = t.nodes[node];
+    for (uint32_t k = nd.tok_begin; k < nd.tok_end; ++k) {
+      uint32_t id = t.node_tokens[k];
+      mask[id >> 5] |= 1u << (id & 31);
+      ++allowed;
+    }
+    if (nd.child_begin == nd.child_end) return;
+    const ByteSet* known = info(sig);
+    if (!known) return;                                   // cannot happen: every signature handed to visit() was registered
+    const ByteSet next = *known;
+    for (uint32_t e = nd.child_begin; e < nd.child_end; ++e) {
+      uint8_t b = t.edges[e].byte;
+      if (!next.has(b)) continue;
+      uint64_t nsig;
+      if (transition(sig, b, nsig)) {
+        ++n_cached;
+      } else {
+        materialise();
+        if (!m.feed(b)) continue;                         // (the byte was in the scannable set, so this does not happen)
+        ++real;
+        ++n_real;
+        const ItemSet& s = m.chart[m.depth];
+        nsig = s.sig;
+        new_trans.emplace(TransKey{sig, b}, nsig);
+        if (!info(nsig)) new_info.emplace(nsig, s.next);
+      }
+      path.push_back(b);
+      visit(t.edges[e].node, nsig);
+      path.pop_back();
+      while (real > path.size()) {                        // the chart must stay a prefix of the path: drop what belonged to the child
+        m.pop();
+        --real;
+      }
+    }
+  }
+};
+
+uint32_t walk(Matcher& m, const TokenTable& t, uint32_t* mask) {
+  Grammar& g = *m.g;
+  Walker w{m, t, g, mask, m.depth, {}, 0, {}, {}, 0, 0, 0};
+  const uint64_t root_sig = m.chart[m.depth].sig;
+  {
+    std::shared_lock<std::shared_mutex> rd(g.tmu);
+    if (!w.info(root_sig)) w.new_info.emplace(root_sig, m.chart[m.depth].next);
+    w.visit(0, root_sig);
+  }
+  m.depth = w.root_depth;
+  m.dead = false;
+  std::unique_lock<std::shared_mutex> wr(g.tmu);
+  if (g.trans.size() + w.new_trans.size() > (1u << 21)) {          // a plain bound on the automaton
+    g.trans.clear();
+    g.info.clear();
+  }
+  for (auto& kv : w.new_trans) g.trans.emplace(kv.first, kv.second);
+  for (auto& kv : w.new_info) g.info.emplace(kv.first, kv.second);
+  g.walked_real += w.n_real;
+  g.walked_cached += w.n_cached;
+  return w.allowed;
 }
 
 }  // namespace
@@ -368,10 +468,7 @@ uint32_t bgram_matcher_mask(void* h, void* table, int32_t eos, uint32_t* mask, i
     }
     m.g->misses++;
   }
-  size_t depth0 = m.depth;
-  uint32_t allowed = walk(m, t, 0, mask);
-  m.depth = depth0;
-  m.dead = false;
+  uint32_t allowed = walk(m, t, mask);
   if (eos >= 0 && uint32_t(eos) < t.n && complete && !((mask[uint32_t(eos) >> 5] >> (uint32_t(eos) & 31)) & 1)) {
     mask[uint32_t(eos) >> 5] |= 1u << (uint32_t(eos) & 31);
     ++allowed;
@@ -383,13 +480,20 @@ uint32_t bgram_matcher_mask(void* h, void* table, int32_t eos, uint32_t* mask, i
   return allowed;
 }
 
-// out[0..2]: cache hits, misses, entries.
+// out[0..5]: mask-cache hits, misses, entries; automaton transitions known; trie edges taken through the recogniser and
+// through the automaton.
 void bgram_cache_stats(void* grammar, uint64_t* out) {
   Grammar* g = static_cast<Grammar*>(grammar);
-  std::lock_guard<std::mutex> lk(g->mu);
-  out[0] = g->hits;
-  out[1] = g->misses;
-  out[2] = g->masks.size();
+  {
+    std::lock_guard<std::mutex> lk(g->mu);
+    out[0] = g->hits;
+    out[1] = g->misses;
+    out[2] = g->masks.size();
+  }
+  std::shared_lock<std::shared_mutex> rd(g->tmu);
+  out[3] = g->trans.size();
+  out[4] = g->walked_real;
+  out[5] = g->walked_cached;
 }
 
 }  // extern "C"

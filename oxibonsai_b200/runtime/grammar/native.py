@@ -76,9 +76,10 @@ class CompiledGrammar:
             self._h = None
 
     def cache_stats(self) -> dict:
-        out = (C.c_uint64 * 3)()
+        out = (C.c_uint64 * 6)()
         self._lib.bgram_cache_stats(self._h, out)
-        return {"hits": int(out[0]), "misses": int(out[1]), "entries": int(out[2])}
+        return {"hits": int(out[0]), "misses": int(out[1]), "entries": int(out[2]), "transitions": int(out[3]),
+                "edges_through_recogniser": int(out[4]), "edges_through_automaton": int(out[5])}
 
 
 _COMPILED: "OrderedDict[bytes, CompiledGrammar]" = OrderedDict()
