@@ -183,9 +183,15 @@ class _SchemaCompiler:
             m = self.lit(json.dumps(key, ensure_ascii=False)) + [self.ws()] + self.lit(":") + [self.ws(), self.value(sub)]
             members.append((key in required, m))
         sep: list[Symbol] = [self.ws()] + self.lit(",") + [self.ws()]
-        # properties appear in declaration order; optional ones may be skipped.  state = "has a member been emitted yet"
+        # properties appear in declaration order; optional ones may be skipped.  state = (next property, "has a member been
+        # emitted yet"): one rule per state, so the grammar is linear in the number of properties however many are optional
+        states: dict[tuple[int, bool], Symbol] = {}
+
         def chain(i: int, emitted: bool) -> Symbol:
+            if (i, emitted) in states:
+                return states[(i, emitted)]
             nm = self.new("mem")
+            states[(i, emitted)] = NonTerm(nm)
             if i == len(members):
                 self.g.add(nm, [])
                 return NonTerm(nm)

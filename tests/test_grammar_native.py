@@ -131,3 +131,24 @@ def test_mask_cost_at_a_realistic_vocabulary():
         second.allowed_mask()
         second.advance(b)
     assert time.perf_counter() - t < 0.5 and second.cache_hits == len(doc)
+
+
+def test_schema_with_many_optional_properties_compiles_linearly():
+    """One grammar rule per (next property, "a member was already written") state: 40 properties, half of them optional,
+    give a grammar of a few hundred rules (an unmemoised chain is exponential in the optional ones)."""
+    from oxibonsai_b200.runtime.json_schema import schema_example
+    kinds = [{"type": "string"}, {"type": "integer"}, {"type": "boolean"}, {"enum": ["red", "green"]}, {"type": "array", "items": {"type": "number"}, "maxItems": 3},
+             {"type": "object", "properties": {"x": {"type": "number"}, "y": {"type": "string"}}, "required": ["x"]}]
+    schema = {"type": "object", "properties": {f"f{i}": kinds[i % 6] for i in range(40)}, "required": [f"f{i}" for i in range(0, 40, 2)]}
+    t = time.perf_counter()
+    g = json_schema_to_grammar(schema)
+    assert len(g.rules) < 600 and time.perf_counter() - t < 2.0
+    m = NativeEarley(g)
+    full = schema_example(schema)
+    required_only = {k: v for k, v in full.items() if k in schema["required"]}
+    some = {k: v for k, v in full.items() if k in schema["required"] or k in ("f1", "f7", "f39")}
+    assert m.accepts(json.dumps(full).encode()) and m.accepts(json.dumps(required_only).encode()) and m.accepts(json.dumps(some).encode())
+    missing = dict(required_only)
+    missing.pop("f0")
+    swapped = {"f2": full["f2"], "f0": full["f0"], **{k: v for k, v in required_only.items() if k not in ("f0", "f2")}}
+    assert not m.accepts(json.dumps(missing).encode()) and not m.accepts(json.dumps(swapped).encode())      # declaration order is part of the grammar
