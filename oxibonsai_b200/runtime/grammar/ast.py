@@ -110,6 +110,31 @@ class Grammar:
     def plus(self, body: list[Symbol], hint: str = "rep") -> list[Symbol]:
         return body + [self.star(body, hint)]
 
+    def repeat(self, body: list[Symbol], lo: int, hi: int | None, hint: str = "rep") -> list[Symbol]:
+        """``body{lo,hi}`` (``hi`` None: no upper bound) in a number of rules linear in the bounds: ``lo`` copies behind a
+        chain of rules of at most 64 copies each, then either ``body*`` or a chain of nested optionals
+        ``opt_k ::= | body opt_(k-1)``."""
+        out: list[Symbol] = []
+        if lo > 0:
+            copies = lo
+            while copies > 0:                                   # long runs are cut into rules of bounded length
+                n = min(copies, 64)
+                name = self.fresh(hint + "_n")
+                self.add(name, body * n)
+                out.append(NonTerm(name))
+                copies -= n
+        if hi is None:
+            out.append(self.star(body, hint))
+        elif hi > lo:
+            nxt: NonTerm | None = None
+            for _ in range(hi - lo):
+                name = self.fresh(hint + "_o")
+                self.add(name, [])
+                self.add(name, body + ([nxt] if nxt is not None else []))
+                nxt = NonTerm(name)
+            out.append(nxt)
+        return out
+
     def optional(self, body: list[Symbol], hint: str = "opt") -> NonTerm:
         n = self.fresh(hint)
         self.add(n, [])

@@ -143,12 +143,9 @@ class _SchemaCompiler:
         if lo is None and hi is None:
             return NonTerm("string")
         lo = int(lo or 0)
-        body: list[Symbol] = [NonTerm("char")] * lo
-        if hi is None:
-            body.append(self.g.star([NonTerm("char")], "chars"))
-        else:
-            for _ in range(int(hi) - lo):
-                body.append(self.g.optional([NonTerm("char")], "char"))
+        if hi is not None and int(hi) < lo:
+            raise GrammarError(f"maxLength {hi} is below minLength {lo}")
+        body = self.g.repeat([NonTerm("char")], lo, None if hi is None else int(hi), "chars")
         return self.g.group([self.lit('"') + body + self.lit('"')], "lenstr")
 
     def arr(self, sc: dict) -> Symbol:
@@ -157,19 +154,14 @@ class _SchemaCompiler:
         sep: list[Symbol] = [self.ws()] + self.lit(",") + [self.ws()]
         more: list[Symbol] = sep + [item]
         name = self.new("arr")
-        if hi is None:
-            tail = self.g.star(more, "items")
-            if lo == 0:
-                self.g.add(name, self.lit("[") + [self.ws()] + self.lit("]"))
-                self.g.add(name, self.lit("[") + [self.ws(), item, tail, self.ws()] + self.lit("]"))
-            else:
-                self.g.add(name, self.lit("[") + [self.ws(), item] + more * (lo - 1) + [tail, self.ws()] + self.lit("]"))
-        else:
-            hi = int(hi)
-            if lo == 0:
-                self.g.add(name, self.lit("[") + [self.ws()] + self.lit("]"))
-            for n in range(max(lo, 1), hi + 1):
-                self.g.add(name, self.lit("[") + [self.ws(), item] + more * (n - 1) + [self.ws()] + self.lit("]"))
+        if hi is not None and int(hi) < lo:
+            raise GrammarError(f"maxItems {hi} is below minItems {lo}")
+        if lo == 0:
+            self.g.add(name, self.lit("[") + [self.ws()] + self.lit("]"))
+        if hi is None or int(hi) >= 1:
+            # the first item, then (", " item){lo-1, hi-1}: rules linear in the bounds
+            rest = self.g.repeat(more, max(lo - 1, 0), None if hi is None else int(hi) - 1, "items")
+            self.g.add(name, self.lit("[") + [self.ws(), item] + rest + [self.ws()] + self.lit("]"))
         return NonTerm(name)
 
     def obj(self, sc: dict) -> Symbol:

@@ -37,25 +37,34 @@ def serialize(grammar: Grammar) -> np.ndarray:
     names = list(grammar.rules)
     idx = {n: i for i, n in enumerate(names)}
     terms: dict[frozenset, int] = {}
+
+    def code(s) -> int:
+        return -(terms.setdefault(s.bytes, len(terms)) + 1) if isinstance(s, Term) else idx[s.name]
+    # a production holds at most 255 symbols natively: longer ones continue in helper rules appended after the named ones
+    rules: list[list[list[int]]] = [[] for _ in names]
+    for r, n in enumerate(names):
+        for alt in grammar.rules[n].alternatives:
+            syms = [code(s) for s in alt]
+            target = r
+            while len(syms) > 200:
+                helper = len(rules)
+                rules.append([])
+                rules[target].append(syms[:200] + [helper])
+                syms, target = syms[200:], helper
+            rules[target].append(syms)
     body: list[int] = []
-    for n in names:
-        alts = grammar.rules[n].alternatives
+    for alts in rules:
         body.append(len(alts))
-        for alt in alts:
-            body.append(len(alt))
-            for s in alt:
-                if isinstance(s, Term):
-                    t = terms.setdefault(s.bytes, len(terms))
-                    body.append(-(t + 1))
-                else:
-                    body.append(idx[s.name])
+        for syms in alts:
+            body.append(len(syms))
+            body += syms
     words: list[int] = []
     for bs in terms:                                   # insertion order = id order
         bits = 0
         for b in bs:
             bits |= 1 << b
         words += [(bits >> (32 * k)) & 0xFFFFFFFF for k in range(8)]
-    head = [len(terms), len(names), idx[grammar.start]]
+    head = [len(terms), len(rules), idx[grammar.start]]
     return np.asarray(head + words + body, dtype=np.int64).astype(np.uint32).view(np.int32)
 
 

@@ -152,3 +152,32 @@ def test_schema_with_many_optional_properties_compiles_linearly():
     missing.pop("f0")
     swapped = {"f2": full["f2"], "f0": full["f0"], **{k: v for k, v in required_only.items() if k not in ("f0", "f2")}}
     assert not m.accepts(json.dumps(missing).encode()) and not m.accepts(json.dumps(swapped).encode())      # declaration order is part of the grammar
+
+
+@pytest.mark.parametrize("schema,good,bad", [
+    ({"type": "string", "maxLength": 300}, ["", "x" * 300], ["x" * 301]),
+    ({"type": "string", "minLength": 200, "maxLength": 1000}, ["y" * 200, "y" * 1000], ["y" * 199, "y" * 1001]),
+    ({"type": "array", "items": {"type": "integer"}, "minItems": 100, "maxItems": 300}, [list(range(100)), list(range(300))], [list(range(99)), list(range(301))]),
+    ({"type": "array", "items": {"type": "boolean"}, "maxItems": 2}, [[], [True], [True, False]], [[True] * 3]),
+    ({"type": "array", "items": {"type": "null"}, "minItems": 2}, [[None] * 2, [None] * 9], [[None], []]),
+    ({"type": "array", "items": {"type": "null"}, "maxItems": 0}, [[]], [[None]]),
+])
+def test_bounded_strings_and_arrays_compile_to_small_grammars(schema, good, bad):
+    g = json_schema_to_grammar(schema)
+    assert len(g.rules) < 1200                                    # linear in the bounds
+    m = NativeEarley(g)
+    assert all(m.accepts(json.dumps(x).encode()) for x in good) and not any(m.accepts(json.dumps(x).encode()) for x in bad)
+    if len(g.rules) < 100:                                        # small enough for the Python oracle to agree in reasonable time
+        py = EarleyRecognizer(g)
+        assert all(py.accepts(json.dumps(x).encode()) for x in good) and not any(py.accepts(json.dumps(x).encode()) for x in bad)
+
+
+def test_long_productions_and_bad_bounds():
+    from oxibonsai_b200.runtime.grammar.ast import Grammar, GrammarError, Term
+    g = Grammar("root")
+    g.add("root", [Term(frozenset([97]))] * 700)                  # longer than a native production: continued in helper rules
+    m = NativeEarley(g)
+    assert m.accepts(b"a" * 700) and not m.accepts(b"a" * 699) and not m.accepts(b"a" * 701)
+    for bad in ({"type": "string", "minLength": 5, "maxLength": 2}, {"type": "array", "minItems": 3, "maxItems": 1}):
+        with pytest.raises(GrammarError):
+            json_schema_to_grammar(bad)
