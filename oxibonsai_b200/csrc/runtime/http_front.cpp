@@ -60,6 +60,7 @@ struct Conn {
     bool close_after_flush = false;
     bool want_write = false;            // EPOLLOUT registered
     bool continued = false;             // "100 Continue" already sent for the request being read
+    bool head_only = false;             // the request being answered is a HEAD: headers as for GET, no body bytes
     int64_t stream = 0;
     std::string peer;
 };
@@ -463,6 +464,7 @@ static bool try_parse(Front* f, Conn* c) {
         c->in.erase(0, total);
         c->keep_alive = keep;
         c->continued = false;
+        c->head_only = e.method == "HEAD";
         c->state = DISPATCHED;
         f->n_requests++;
         f->events.push_back(std::move(e));
@@ -781,7 +783,7 @@ int bfront_respond(void* h, int64_t conn, int status, const char* headers, const
     k = snprintf(line, sizeof line, "content-length: %llu\r\n%s\r\n", static_cast<unsigned long long>(n), c->keep_alive ? "" : "connection: close\r\n");
     head.append(line, size_t(k));
     queue_out(f, c, head.data(), head.size());
-    if (n) queue_out(f, c, reinterpret_cast<const char*>(body), size_t(n));
+    if (n && !c->head_only) queue_out(f, c, reinterpret_cast<const char*>(body), size_t(n));
     response_done(f, c);
     wake_io(f);
     return 0;
@@ -813,6 +815,7 @@ int bfront_respond_chunk(void* h, int64_t conn, const uint8_t* data, uint64_t n)
     std::lock_guard<std::mutex> lk(f->mu);
     auto it = f->conns.find(conn);
     if (it == f->conns.end() || it->second->state != RESPONDING) return -1;
+    if (it->second->head_only) return 0;
     std::string framed;
     append_chunk(framed, std::string(reinterpret_cast<const char*>(data), size_t(n)));
     bool ok = queue_out(f, it->second.get(), framed.data(), framed.size());
@@ -826,7 +829,7 @@ int bfront_respond_end(void* h, int64_t conn) {
     auto it = f->conns.find(conn);
     if (it == f->conns.end() || it->second->state != RESPONDING) return -1;
     Conn* c = it->second.get();
-    queue_out(f, c, "0\r\n\r\n", 5);
+    if (!c->head_only) queue_out(f, c, "0\r\n\r\n", 5);
     response_done(f, c);
     wake_io(f);
     return 0;

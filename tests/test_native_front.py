@@ -69,6 +69,11 @@ def test_requests_keep_alive_pipelining_and_errors(front):
     assert r.status == 200 and d["method"] == "GET" and d["target"] == "/a/b?x=1" and "X-Thing: v" in d["headers"]
     c.request("POST", "/p", body=b"z" * 300000)                          # larger than one read; same connection
     assert json.loads(c.getresponse().read())["body"] == 300000
+    c.request("HEAD", "/h")                                              # headers as for GET, no body; the connection stays usable
+    r = c.getresponse()
+    assert r.status == 200 and int(r.getheader("content-length")) > 0 and r.read() == b""
+    c.request("GET", "/after-head")
+    assert json.loads(c.getresponse().read())["target"] == "/after-head"
     # two requests in one write, answered in order on one connection
     s = socket.create_connection(("127.0.0.1", front.port))
     s.sendall(b"GET /one HTTP/1.1\r\nHost: x\r\n\r\nPOST /two HTTP/1.1\r\nHost: x\r\nContent-Length: 3\r\nConnection: close\r\n\r\nabc")
@@ -90,7 +95,7 @@ def test_requests_keep_alive_pipelining_and_errors(front):
         assert s.recv(200).split(b" ")[1] == status
         s.close()
     st = front.stats()
-    assert st["requests"] == 5 and st["connections_accepted"] == 7
+    assert st["requests"] == 7 and st["connections_accepted"] == 7
 
 
 def _reference_stream(tokens, stops):
