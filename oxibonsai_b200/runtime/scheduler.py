@@ -27,6 +27,10 @@ class _Cancelled(Exception):
     pass
 
 
+class SchedulerStopped(RuntimeError):
+    """The scheduler's loop has ended on a fatal error (its engine is being torn down): it takes no more requests."""
+
+
 class QueueFull(RuntimeError):
     """Raised when the admission queue is at capacity (maps to HTTP 503)."""
 
@@ -173,7 +177,10 @@ class BatchScheduler:
         if len(prompt) + 1 > self.engine.max_seq_len:
             raise ValueError(f"prompt of {len(prompt)} tokens does not fit max_seq_len {self.engine.max_seq_len}")
         r = Request(list(prompt), params.validate(), max_tokens, t_submit=time.perf_counter(), **kw)
-        self.queue.put(r)
+        with self.lock:                      # against the fatal path, which closes the scheduler and then empties the queue
+            if self.fatal is not None:
+                raise SchedulerStopped(f"the scheduler stopped: {self.fatal}")
+            self.queue.put(r)
         return r
 
     @property
@@ -215,7 +222,8 @@ class BatchScheduler:
                 slots = list(range(len(self.live))) + ([self._pending["slot"]] if self._pending is not None else [])
                 self.live, self._pos, self._pending = [], [], None
                 if fatal:                          # the engine is about to be torn down: its slots go with it
-                    self.fatal = e
+                    with self.lock:
+                        self.fatal = e             # from here on submit() refuses, so the queue emptied below stays empty
                     while (r := self.queue.get_nowait()) is not None:
                         r.error = e
                         r.finish()

@@ -187,7 +187,12 @@ class ElasticBackend:
         s = self.s
         if s is None:
             raise Unavailable("the tensor-parallel group is re-forming after a lost rank; retry shortly")
-        return s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id, **extra)
+        try:
+            return s.submit(prompt, params, max_tokens, on_token=on_token, request_id=request_id, **extra)
+        except Exception as e:  # noqa: BLE001
+            if type(e).__name__ == "SchedulerStopped":      # the generation has just ended; the next one is not attached yet
+                raise Unavailable("the tensor-parallel group is re-forming after a lost rank; retry shortly") from e
+            raise
 
     def kv_utilization(self) -> float:
         s = self.s

@@ -120,3 +120,30 @@ def test_gloo_ranks_lose_two_members_and_keep_serving(tmp_path):
     builds2 = [e for e in r[2]["log"] if e[0] == "build"]
     assert builds2 == [["build", 0, 2, 4], ["build", 2, 1, 2]]                                   # parked as a spare during generation 1
     assert all(h["seconds"] < 30 for h in r[0]["history"])
+
+
+def test_scheduler_behind_an_elastic_backend_survives_a_lost_follower(tmp_path):
+    """The serving path: real scheduler + leader engine + ``ElasticBackend`` on the leader, followers mirroring its commands.
+    A follower exits in the middle of the first requests: those fail (the client sees an error, not a hang), the group
+    re-forms at degree 2, the retried request is served by two ranks."""
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "elastic_sched_worker.py")
+    port = _free_port()
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    procs = [subprocess.Popen([sys.executable, worker, str(u), "3", str(port), str(tmp_path)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for u in range(3)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=180)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append(p.communicate()[0])
+    assert all(p.returncode == 0 for p in procs), "\n----\n".join(o[-1500:] for o in outs)
+    r = {u: json.load(open(tmp_path / f"uid{u}.json")) for u in range(3)}
+    assert r[2]["left"] and not r[0]["left"] and not r[1]["left"]
+    rec = r[0]["record"]
+    assert len(rec["first"]) == 3 and all(f["error"] == "RankLost" for f in rec["first"])            # in flight when the rank went: failed, not hung
+    assert all(set(f["tokens"]) <= {1, 3} for f in rec["first"])                                     # what they got before came from three ranks
+    assert rec["retry"] and set(rec["retry"][1:]) == {2} and len(rec["retry"]) == 8                  # served by the two survivors
+    assert r[0]["generations"] == 2 and [h["lost"] for h in r[0]["history"]] == [[2]]
+    assert r[0]["builds"] == [[0, 0, 3], [1, 0, 2]] and r[1]["builds"] == [[0, 1, 3], [1, 1, 2]]
