@@ -399,7 +399,7 @@ static bool try_parse(Front* f, Conn* c) {
             return true;
         }
         size_t content_length = 0;
-        bool chunked = false, expect = false, keep = !http10;
+        bool chunked = false, expect = false, keep = !http10, have_length = false;
         size_t pos = le + 2;
         while (pos < he + 2) {
             size_t eol = c->in.find("\r\n", pos);
@@ -415,6 +415,9 @@ static bool try_parse(Front* f, Conn* c) {
             const char* name = p + pos;
             size_t nlen = colon - pos;
             if (ieq(name, nlen, "content-length")) {
+                const size_t previous = content_length;
+                const bool repeated = have_length;
+                have_length = true;
                 content_length = 0;
                 if (ve == vs) {
                     simple_response(f, c, 400, "bad content-length");
@@ -426,6 +429,10 @@ static bool try_parse(Front* f, Conn* c) {
                         return true;
                     }
                     content_length = content_length * 10 + size_t(p[i] - '0');
+                }
+                if (repeated && previous != content_length) {                     // two lengths that disagree: refuse, do not guess
+                    simple_response(f, c, 400, "conflicting content-length headers");
+                    return true;
                 }
             } else if (ieq(name, nlen, "transfer-encoding")) {
                 chunked = !ieq(p + vs, ve - vs, "identity");

@@ -334,8 +334,7 @@ class AsgiBridge:
         finally:
             if handle.stream is not None and started.get("mode") != "native":
                 handle.stream.abandon()               # a stream was opened but the route answered in another way
-            if started.get("mode") != "native":
-                self._gone.pop(conn, None)
+            self._gone.pop(conn, None)
 
     async def serve(self, stop: threading.Event | None = None) -> None:
         loop = asyncio.get_running_loop()

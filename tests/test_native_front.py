@@ -89,13 +89,14 @@ def test_requests_keep_alive_pipelining_and_errors(front):
     assert b'"body": 4' in s.recv(65536)
     s.close()
     for bad, status in ((b"NONSENSE\r\n\r\n", b"400"), (b"GET / HTTP/1.1\r\nContent-Length: x\r\n\r\n", b"400"),
-                        (b"POST / HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\n", b"501"), (b"GET / HTTP/1.1\r\nA: " + b"a" * 70000 + b"\r\n\r\n", b"431")):
+                        (b"POST / HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\n", b"501"),
+                        (b"POST / HTTP/1.1\r\nContent-Length: 3\r\nContent-Length: 5\r\n\r\nabcde", b"400"), (b"GET / HTTP/1.1\r\nA: " + b"a" * 70000 + b"\r\n\r\n", b"431")):
         s = socket.create_connection(("127.0.0.1", front.port))
         s.sendall(bad)
         assert s.recv(200).split(b" ")[1] == status
         s.close()
     st = front.stats()
-    assert st["requests"] == 7 and st["connections_accepted"] == 7
+    assert st["requests"] == 7 and st["connections_accepted"] == 8
 
 
 def _reference_stream(tokens, stops):
