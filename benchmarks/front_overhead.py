@@ -53,6 +53,20 @@ class SyntheticEngine:
         self.n += 1
         return [97 + (self.n + b) % 26 for b in range(len(positions))]
 
+    # the split step: the "GPU" is busy for step_ms from the launch on, whatever the host does meanwhile
+    supports_overlap = True
+
+    def launch_batch(self, positions):
+        self._ready = time.perf_counter() + self.step_s
+        self._batch = len(positions)
+
+    def collect_batch(self, batch):
+        wait = self._ready - time.perf_counter()
+        if wait > 0:
+            time.sleep(wait)
+        self.n += 1
+        return [97 + (self.n + b) % 26 for b in range(batch)]
+
     def move_slot(self, src, dst):
         pass
 
@@ -63,12 +77,12 @@ class SyntheticEngine:
         return 0.0
 
 
-def run_server(front: str, port: int, streams: int, step_ms: float) -> None:
+def run_server(front: str, port: int, streams: int, step_ms: float, overlap: bool = False) -> None:
     from oxibonsai_b200.runtime.scheduler import BatchScheduler
     from oxibonsai_b200.server.app import SchedulerBackend, create_app, serve
     from oxibonsai_b200.server.config import ServerConfig
     from oxibonsai_b200.tokenizer import ByteTokenizer
-    sched = BatchScheduler(SyntheticEngine(streams, step_ms), eos_token=-1).start()
+    sched = BatchScheduler(SyntheticEngine(streams, step_ms), eos_token=-1, overlap=overlap).start()
     tok = ByteTokenizer()
     app = create_app(SchedulerBackend(sched, "synthetic"), tok, ServerConfig(max_concurrent=streams))
     serve(app, "127.0.0.1", port, "error", tokenizer=tok, native=(front == "native"))
@@ -112,13 +126,14 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--step-ms", type=float, default=0.0)
     ap.add_argument("--port", type=int, default=18431)
+    ap.add_argument("--overlap", action="store_true", help="overlapped decode steps in the scheduler")
     ap.add_argument("--serve", action="store_true", help=argparse.SUPPRESS)
     a = ap.parse_args()
     if a.serve:
-        run_server(a.front, a.port, a.streams, a.step_ms)
+        run_server(a.front, a.port, a.streams, a.step_ms, a.overlap)
         return 0
     child = subprocess.Popen([sys.executable, os.path.abspath(__file__), "--serve", "--front", a.front, "--port", str(a.port),
-                              "--streams", str(a.streams), "--step-ms", str(a.step_ms)], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+                              "--streams", str(a.streams), "--step-ms", str(a.step_ms)] + (["--overlap"] if a.overlap else []), env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     try:
         import socket
         for _ in range(200):
@@ -133,7 +148,7 @@ def main() -> int:
         child.terminate()
         child.wait(10)
     total = a.streams * a.tokens
-    print(json.dumps({"front": a.front, "streams": a.streams, "tokens_per_stream": a.tokens, "engine_step_ms": a.step_ms,
+    print(json.dumps({"front": a.front, "overlap": a.overlap, "streams": a.streams, "tokens_per_stream": a.tokens, "engine_step_ms": a.step_ms,
                       "tokens_per_s": round(total / r["wall_s"], 1), "wall_s": round(r["wall_s"], 3), "sse_events": r["events"],
                       "engine_ceiling_tokens_per_s": round(a.streams / (a.step_ms / 1e3), 1) if a.step_ms else None}))
     return 0

@@ -95,6 +95,7 @@ def main() -> None:
     ap.add_argument("--kv-policy", default="off")
     ap.add_argument("--prefill-chunk-boost", type=int, default=4)
     ap.add_argument("--front", choices=("native", "uvicorn"), default="native", help="the server's HTTP front")
+    ap.add_argument("--overlap", action="store_true", help="the server launches decode step k + 1 before delivering the tokens of step k")
     ap.add_argument("--model-dir", default=os.environ.get("BONSAI_BENCH_DIR", "/tmp/oxibonsai_b200_bench"))
     a = ap.parse_args()
 
@@ -110,7 +111,7 @@ def main() -> None:
     args = ["--model-path", path, "--host", "127.0.0.1", "--port", str(port), "--kv-cache", a.kv, "--max-seq-len", str(a.prompt_max + a.max_tokens + 64),
             "--max-concurrent", str(per_engine), "--max-input-tokens", str(a.prompt_max + 64), "--log-level", "warning", "--kv-policy", a.kv_policy,
             "--replicas", str(a.replicas), "--tensor-parallel", str(a.tensor_parallel), "--prefill-chunk-boost", str(a.prefill_chunk_boost),
-            "--native-front" if a.front == "native" else "--no-native-front"]
+            "--native-front" if a.front == "native" else "--no-native-front", "--overlap-steps" if a.overlap else "--no-overlap-steps"]
     if a.tensor_parallel > 1:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.tensor_parallel}", "--master-addr", "127.0.0.1",
                "--master-port", str(free_port()), "-m", "oxibonsai_b200.server", *args]
@@ -168,7 +169,7 @@ def main() -> None:
     print(json.dumps({
         "metric": f"aggregate decode tok/s over {a.streams} concurrent SSE streams", "model": SHAPES[a.model]["name"], "kv_cache": a.kv,
         "parallelism": f"tp{a.tensor_parallel}" if a.tensor_parallel > 1 else f"{a.replicas} replica(s)",
-        "front": a.front, "prefill_chunk_boost": a.prefill_chunk_boost, "prompt_tokens": [a.prompt_min, a.prompt_max], "max_tokens": a.max_tokens, "preset": "balanced (T 0.7, top-k 40, top-p 0.9)",
+        "front": a.front, "overlap_steps": a.overlap, "prefill_chunk_boost": a.prefill_chunk_boost, "prompt_tokens": [a.prompt_min, a.prompt_max], "max_tokens": a.max_tokens, "preset": "balanced (T 0.7, top-k 40, top-p 0.9)",
         "streams_ok": sum(1 for r in res if r["status"] == 200 and not r["error"]), "finish_reasons": finishes, "errors": errors[:3],
         "generated_tokens_server_count": int(generated), "content_chunks": chunks, "wall_s": round(wall, 3),
         "tokens_per_s_overall": round(generated / wall, 1), "chunks_per_s_overall": round(chunks / wall, 1),

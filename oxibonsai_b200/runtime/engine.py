@@ -446,6 +446,21 @@ class InferenceEngine:
         r.step(B, sample=True, masked=bool(masks))
         return self._read_tokens(B)
 
+    supports_overlap = True
+
+    def launch_batch(self, positions: Sequence[int]) -> None:
+        """First half of :meth:`step_batch` (no masks): uploads the positions and enqueues the decode step of slots
+        0..len(positions)-1 without waiting for it."""
+        B = len(positions)
+        r = self.runner
+        self._pos_host[:B] = torch.tensor(list(positions), dtype=torch.int32)
+        r.positions[:B].copy_(self._pos_host[:B], non_blocking=True)
+        r.step(B, sample=True, masked=False)
+
+    def collect_batch(self, batch: int) -> list[int]:
+        """Second half: waits for the step launched last and returns its tokens (raises on an expired wait)."""
+        return self._read_tokens(batch)
+
     def bind_thread(self) -> None:
         """Makes this engine's GPU the calling thread's current device (a scheduler thread calls it once)."""
         torch.cuda.set_device(self.device)

@@ -125,7 +125,7 @@ class BatchScheduler:
     def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
                  prefill_chunk_tokens: int = 512, kv_policy=None, prefill_chunk_boost: int = 1,
                  before_launch: Callable[[], None] | None = None, on_fatal: Callable[[Exception], bool] | None = None,
-                 idle_hook: Callable[[], None] | None = None, idle_hook_seconds: float = 30.0):
+                 idle_hook: Callable[[], None] | None = None, idle_hook_seconds: float = 30.0, overlap: bool = False):
         """``kv_policy``: a :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy`; when given, the scheduler feeds it the
         engine's KV utilisation after every admission and retirement, and every newly admitted sequence gets its pages in the
         format of the policy's current level (FP16 / Q8 / Q4, as far as the engine has pools for them)."""
@@ -136,6 +136,15 @@ class BatchScheduler:
         # ``idle_hook`` runs every ``idle_hook_seconds`` while nothing is live (a tensor-parallel leader's keep-alive).
         self.before_launch, self.on_fatal, self.idle_hook, self.idle_hook_seconds = before_launch, on_fatal, idle_hook, idle_hook_seconds
         self.fatal: Exception | None = None
+        # ``overlap``: launch decode step k + 1 as soon as the tokens of step k are on the host, and deliver those tokens
+        # (callbacks, bookkeeping, the front's writes) while the GPU runs it.  Taken only when the batch cannot change under
+        # the step in flight: no constrained or log-probability request, nobody at a length limit or an end-of-sequence
+        # token.  A request that ends unpredictably (its client left, a stop sequence) has one token too many computed; that
+        # token is dropped and the slot is freed after the step.  Needs ``launch_batch`` / ``collect_batch`` on the engine.
+        self.overlap = bool(overlap) and bool(getattr(engine, "supports_overlap", False))
+        self._inflight: int | None = None      # number of slots of the decode step that has been launched and not collected
+        self._zombies: set[int] = set()        # slots of requests that ended while that step was in flight
+        self.overlapped_steps = 0
         self.after_step: Callable[[], None] | None = None     # called once after the tokens of a decode step (or of an admission)
                                                                # have been delivered: a front that batches its writes per step
         from ..core.oracle import EOS_TOKEN
@@ -205,7 +214,10 @@ class BatchScheduler:
                         time.sleep(self.idle_sleep)
                     continue
                 last_idle = time.monotonic()
-                self._step()
+                if self.overlap:
+                    self._step_overlapped()
+                else:
+                    self._step()
             except Exception as e:  # a failing step must not wedge the waiting clients
                 fatal = False
                 if self.on_fatal is not None:
@@ -221,6 +233,7 @@ class BatchScheduler:
                     self._pending["r"].finish()
                 slots = list(range(len(self.live))) + ([self._pending["slot"]] if self._pending is not None else [])
                 self.live, self._pos, self._pending = [], [], None
+                self._inflight, self._zombies = None, set()
                 if fatal:                          # the engine is about to be torn down: its slots go with it
                     with self.lock:
                         self.fatal = e             # from here on submit() refuses, so the queue emptied below stays empty
@@ -233,6 +246,55 @@ class BatchScheduler:
                         eng.close_sequence(s)
                     except Exception:  # noqa: BLE001 - a second failure while cleaning up changes nothing for the clients
                         pass
+
+    def _speculation_safe(self, B: int, toks: Sequence[int]) -> bool:
+        """True when delivering ``toks`` cannot end or alter any of the B sequences in a way the scheduler can foresee."""
+        limit = self.engine.max_seq_len
+        for s in range(B):
+            r = self.live[s]
+            if r.cancelled or r.constraint is not None or r.logprobs is not None or (r.stop_at_eos and toks[s] == self.eos):
+                return False
+            if len(r.tokens) + 2 > r.max_tokens or self._pos[s] + 2 >= limit:      # this token or the next one is the last
+                return False
+        return True
+
+    def _step_overlapped(self) -> None:
+        eng = self.engine
+        if self._inflight is None:
+            if any(r.constraint is not None for r in self.live):                   # masks depend on the token before: plain step
+                self._step()
+                return
+            self._inflight = len(self.live)
+            eng.launch_batch(self._pos[:self._inflight])
+        B = self._inflight
+        toks = eng.collect_batch(B)                                                # raises on an expired wait, like step_batch
+        self._inflight = None
+        self.steps += 1
+        for s in range(B):
+            self._pos[s] += 1
+        zombies, self._zombies = self._zombies, set()
+        # (a sequence admitted while the step was in flight joins at the next launch: no speculation past it)
+        if not zombies and B == len(self.live) and not self._stop.is_set() and self._speculation_safe(B, toks):
+            eng.launch_batch(self._pos[:B])                                        # step k + 1 runs while step k's tokens go out
+            self._inflight = B
+            self.overlapped_steps += 1
+        ended = []
+        for s in range(B - 1, -1, -1):
+            if s in zombies:                       # computed for a request that had already ended: dropped
+                ended.append(s)
+            elif self._emit(s, toks[s]):
+                ended.append(s)
+        if self._inflight is not None:
+            for s in ended:                        # the step in flight still uses these slots: end the requests now, free the slots after it
+                r = self.live[s]
+                r.t_done = time.perf_counter()
+                r.finish()
+            self._zombies = set(ended)
+        else:
+            for s in ended:                        # highest slot first, so moves never touch an unprocessed slot
+                self._retire(s)
+        if self.after_step is not None:
+            self.after_step()
 
     def _admit(self) -> bool:
         """Makes progress on admission: at most one prompt chunk per call.  Returns True when something was done."""
@@ -349,10 +411,14 @@ class BatchScheduler:
         return False
 
     def _retire(self, slot: int) -> None:
-        eng = self.engine
         r = self.live[slot]
-        r.t_done = time.perf_counter()
-        r.finish()
+        if not r.done.is_set():
+            r.t_done = time.perf_counter()
+            r.finish()
+        self._free_slot(slot)
+
+    def _free_slot(self, slot: int) -> None:
+        eng = self.engine
         last = len(self.live) - 1
         eng.close_sequence(slot)
         if self.kv_policy is not None:

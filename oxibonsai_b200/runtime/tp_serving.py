@@ -65,6 +65,8 @@ class LeaderEngine:
     so a call whose kernels would wait for a lost rank is never launched, and a broadcast that fails because a follower is
     gone surfaces as :class:`~oxibonsai_b200.runtime.elastic.RankLost`."""
 
+    supports_overlap = False           # a step is one mirrored command: launch and collect are not split across ranks
+
     def __init__(self, engine, channel: CommandChannel, group=None):
         self._engine, self._channel, self._group = engine, channel, group
 

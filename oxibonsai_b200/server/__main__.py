@@ -80,7 +80,7 @@ def main(argv: list[str] | None = None) -> int:
                 if policy is not None:
                     e.enable_kv_formats(("f16", "q8", "q4"))      # the levels of the policy that the engine does not have yet
             scheds.append(BatchScheduler(e, queue_capacity=cfg.queue_capacity, prefill_chunk_tokens=cfg.prefill_chunk_tokens, prefill_chunk_boost=cfg.prefill_chunk_boost,
-                                         kv_policy=policy, idle_hook=getattr(leader, "keepalive", None)).start())
+                                         kv_policy=policy, idle_hook=getattr(leader, "keepalive", None), overlap=cfg.overlap_steps).start())
         backend = SchedulerBackend(scheds[0], engine.config.name) if len(scheds) == 1 else ReplicaBackend(scheds, engine.config.name)
     else:                                         # an engine without sequence slots: one request at a time
         backend = SerialBackend(engine, engine.config.name)

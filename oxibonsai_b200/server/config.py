@@ -45,6 +45,7 @@ class ServerConfig:
     prefill_chunk_boost: int = 4      # chunks this many times as long while fewer than a quarter of the slots decode
     kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
+    overlap_steps: bool = False       # launch decode step k + 1 before the tokens of step k are delivered (single-process engines)
     native_front: bool = True         # C++ HTTP / SSE front (sockets, parsing, token streaming); off: uvicorn
 
     def validate(self, check_paths: bool = True) -> "ServerConfig":
@@ -86,7 +87,7 @@ _TOML_MAP = {
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
     ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "tp_elastic"): "tp_elastic", ("model", "tp_heartbeat_timeout"): "tp_heartbeat_timeout", ("model", "kv_policy"): "kv_policy",
-    ("server", "native_front"): "native_front", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
+    ("server", "native_front"): "native_front", ("server", "overlap_steps"): "overlap_steps", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",
 }

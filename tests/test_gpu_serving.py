@@ -218,3 +218,44 @@ def test_sequences_in_different_kv_page_formats_share_a_decode_batch(tiny_gguf):
     assert outs == [want["f16"], want["q8"], want["q4"]]
     assert {k: len(p.free_pages) for k, p in eng.runner.kv_pools.items()} == free0      # every pool got its pages back
     assert eng.runner.slot_formats == [K.KV_F16] * 4
+
+
+def test_overlapped_steps_match_plain_steps_on_the_gpu(tiny_gguf):
+    """The scheduler with ``overlap`` launches step k + 1 before it delivers the tokens of step k.  Submitted together on a
+    batch that never changes composition unpredictably, the streams are those of the plain scheduler token for token
+    (same batch sizes at every step, hence the same kernels); a request whose callback raises is cut at that token and its
+    slot is freed after the step that was already in flight."""
+    from oxibonsai_b200.runtime.presets import SamplingPreset
+    from oxibonsai_b200.runtime.scheduler import BatchScheduler
+    greedy = SamplingPreset.GREEDY.params()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (20, 33, 17, 26)]
+    lens = [24, 9, 30, 16]
+
+    def run(overlap):
+        eng = _engine(tiny_gguf, max_batch=4)
+        assert eng.supports_overlap
+        sched = BatchScheduler(eng, eos_token=-1, overlap=overlap)
+        seen = []
+
+        def bail(tok):
+            seen.append(tok)
+            if len(seen) == 5:
+                raise RuntimeError("client went away")
+        reqs = [sched.submit(p, greedy, n) for p, n in zip(prompts[:3], lens[:3])]
+        reqs.append(sched.submit(prompts[3], greedy, lens[3], on_token=bail))
+        sched.start()
+        try:
+            for r in reqs:
+                assert r.done.wait(120)
+        finally:
+            sched.stop()
+        assert sched.active == 0 and all(r.error is None for r in reqs)
+        return [list(r.tokens) for r in reqs], [r.finish_reason for r in reqs], sched
+
+    plain, why_plain, _ = run(False)
+    over, why_over, sched = run(True)
+    assert why_plain == why_over == ["length", "length", "length", "cancelled"]
+    assert [len(t) for t in over] == [24, 9, 30, 5]
+    assert over == plain
+    assert sched.overlapped_steps >= 10

@@ -279,3 +279,112 @@ def test_watchdog_hook_stops_launches_and_a_fatal_error_ends_the_loop():
     assert not sched._thread.is_alive()
     assert not any(e[0] == "close" for e in eng.log[-2:])              # the slots are left to the engine that is torn down
     sched.stop()
+
+
+class OverlapEngine(FakeEngine):
+    """FakeEngine with the split step: ``launch_batch`` computes the step, ``collect_batch`` hands it out.  Checks the rules
+    of a step in flight: its slots are neither closed nor moved nor stepped again before it is collected."""
+    supports_overlap = True
+
+    def __init__(self, step_delay=0.0):
+        super().__init__(step_delay)
+        self.inflight = None
+
+    def launch_batch(self, positions):
+        assert self.inflight is None, "a second step was launched before the first was collected"
+        self.inflight = (len(positions), super().step_batch(list(positions)))
+        self.log.append(("launch", len(positions)))
+
+    def collect_batch(self, batch):
+        assert self.inflight is not None and self.inflight[0] == batch
+        toks, self.inflight = self.inflight[1], None
+        return toks
+
+    def step_batch(self, positions, masks=None):
+        assert self.inflight is None, "a plain step while another one is in flight"
+        return super().step_batch(positions)
+
+    def finish_sequence(self, prompt, slot, mask=None):
+        return super().finish_sequence(prompt, slot)
+
+    def close_sequence(self, slot):
+        assert self.inflight is None or slot >= self.inflight[0], "a slot of the step in flight was closed"
+        super().close_sequence(slot)
+
+    def move_slot(self, src, dst):
+        assert self.inflight is None or (src >= self.inflight[0] and dst >= self.inflight[0]), "a slot of the step in flight was moved"
+        super().move_slot(src, dst)
+
+
+def test_overlapped_steps_give_the_same_streams_and_respect_the_step_in_flight():
+    """With ``overlap`` the next decode step is launched before the tokens of the last one are delivered.  The streams are
+    the same as without it, natural endings never cost an extra token, and a request that ends unpredictably (a callback
+    that raises) is dropped after the step that was already running."""
+    def run(overlap):
+        eng = OverlapEngine()
+        sched = BatchScheduler(eng, eos_token=-1, prefill_chunk_tokens=32, overlap=overlap)
+        assert sched.overlap == overlap
+        seen = []
+
+        def bail(tok):
+            seen.append(tok)
+            if len(seen) == 7:
+                raise RuntimeError("client went away")
+        reqs = [sched.submit(list(range(10 + i, 40 + 3 * i)), SamplingParams(), 20 + 9 * i) for i in range(3)]
+        reqs.append(sched.submit(list(range(5, 25)), SamplingParams(), 100, on_token=bail))
+        sched.start()
+        late = sched.submit(list(range(50, 90)), SamplingParams(), 15)          # admitted while the others decode
+        for r in reqs + [late]:
+            assert r.done.wait(10)
+        sched.stop()
+        assert eng.inflight is None and not eng.slots and sched.active == 0
+        return [list(r.tokens) for r in reqs + [late]], [r.finish_reason for r in reqs + [late]], eng, sched
+
+    plain, why_plain, _, _ = run(False)
+    over, why_over, eng, sched = run(True)
+    assert over == plain and why_over == why_plain == ["length", "length", "length", "cancelled", "length"]
+    assert [len(t) for t in over] == [20, 29, 38, 7, 15]
+    assert sched.overlapped_steps > 20 and sum(1 for e in eng.log if e[0] == "launch") >= sched.overlapped_steps
+    # with nothing but predictable endings every launched step is used: tokens computed == tokens delivered
+    eng2 = OverlapEngine()
+    s2 = BatchScheduler(eng2, eos_token=-1, overlap=True)
+    rs = [s2.submit(list(range(3, 30)), SamplingParams(), n) for n in (5, 9, 9, 30)]
+    s2.start()
+    for r in rs:
+        assert r.done.wait(10)
+    s2.stop()
+    computed = sum(e[1] for e in eng2.log if e[0] == "step")
+    assert computed == sum(len(r.tokens) - 1 for r in rs)                      # (the first token of a stream comes from its prefill)
+
+
+def test_overlap_is_off_for_constrained_requests_and_unsupported_engines():
+    eng = FakeEngine()
+    assert BatchScheduler(eng, eos_token=-1, overlap=True).overlap is False     # no launch / collect on this engine
+
+    class Until3:
+        def __init__(self):
+            self.n = 0
+
+        def reset(self):
+            self.n = 0
+
+        def allowed_mask(self):
+            return None
+
+        def advance(self, tok):
+            self.n += 1
+            return True
+
+        def finished(self):
+            return self.n >= 3
+
+    eng = OverlapEngine()
+    sched = BatchScheduler(eng, eos_token=-1, overlap=True).start()
+    a = sched.submit(list(range(20)), SamplingParams(), 50, constraint=Until3())
+    b = sched.submit(list(range(20, 45)), SamplingParams(), 12)
+    assert a.done.wait(10) and b.done.wait(10)
+    sched.stop()
+    assert len(a.tokens) == 3 and a.finish_reason == "stop" and len(b.tokens) == 12
+    first_launch = next(i for i, e in enumerate(eng.log) if e[0] == "launch")
+    steps_before = [e for e in eng.log[:first_launch] if e[0] == "step"]
+    assert steps_before                                                         # while the constrained request lived, plain steps were taken
