@@ -61,6 +61,7 @@ struct Conn {
     bool want_write = false;            // EPOLLOUT registered
     bool continued = false;             // "100 Continue" already sent for the request being read
     bool head_only = false;             // the request being answered is a HEAD: headers as for GET, no body bytes
+    Clock::time_point last_io = Clock::now();   // last byte received or sent (I/O thread only)
     int64_t stream = 0;
     std::string peer;
 };
@@ -92,6 +93,7 @@ struct Front {
     std::thread io;
     std::atomic<bool> stopping{false};
     std::atomic<bool> wake_pending{false};
+    std::atomic<int> idle_timeout_ms{75000};   // a connection that waits for a request and moves no byte for this long is closed (0: never)
     std::atomic<bool> lazy{false};      // token pushes do not wake the I/O thread; the producer calls bfront_kick() once per step
     std::mutex mu;
     std::condition_variable cv;
@@ -114,7 +116,7 @@ struct Front {
         }
     }
     // counters (read through bfront_stats)
-    uint64_t n_accepted = 0, n_requests = 0, n_stream_events = 0, n_stream_tokens = 0;
+    uint64_t n_accepted = 0, n_requests = 0, n_stream_events = 0, n_stream_tokens = 0, n_idle_closed = 0;
     std::atomic<uint64_t> n_bytes_out{0};
 };
 
@@ -503,6 +505,7 @@ static bool flush_conn(Front* f, Conn* c) {
         }
         ssize_t n = send(c->fd, c->wire.data() + c->wire_off, c->wire.size() - c->wire_off, MSG_NOSIGNAL);
         if (n > 0) {
+            c->last_io = Clock::now();
             c->wire_off += size_t(n);
             f->n_bytes_out.fetch_add(uint64_t(n), std::memory_order_relaxed);
             continue;
@@ -584,6 +587,7 @@ static void io_loop(Front* f) {
                 while (alive) {
                     ssize_t r = recv(c->fd, buf.data(), buf.size(), 0);
                     if (r > 0) {
+                        c->last_io = Clock::now();
                         if (c->in.size() + size_t(r) > kMaxBody + kMaxHeader) {
                             alive = false;
                             break;
@@ -639,6 +643,17 @@ static void io_loop(Front* f) {
             for (auto& kv : f->streams) {
                 Stream* s = kv.second.get();
                 if (s->state == LIVE && s->has_deadline && now > s->deadline) s->state = TIMED_OUT;
+            }
+            // connections that wait for a request (or sit on half of one) without moving a byte
+            const int idle_ms = f->idle_timeout_ms.load(std::memory_order_relaxed);
+            if (idle_ms > 0) {
+                std::vector<int64_t> idle;
+                for (auto& kv : f->conns) {
+                    Conn* c = kv.second.get();
+                    if (c->state == READING && now - c->last_io > std::chrono::milliseconds(idle_ms)) idle.push_back(c->id);
+                }
+                for (int64_t id : idle) close_conn(f, id);
+                f->n_idle_closed += idle.size();
             }
         }
     }
@@ -950,6 +965,10 @@ void bfront_set_lazy(void* h, int on) { static_cast<Front*>(h)->lazy.store(on !=
 
 void bfront_kick(void* h) { wake_io(static_cast<Front*>(h)); }
 
+// Connections that wait for a request without receiving or sending a byte for this long are closed (0: never).  Connections
+// whose request is being answered or streamed are not subject to it.
+void bfront_set_idle_timeout(void* h, int milliseconds) { static_cast<Front*>(h)->idle_timeout_ms.store(milliseconds < 0 ? 0 : milliseconds); }
+
 // Ends a stream: the held-back text (unless a stop sequence was hit), the finish chunk, "[DONE]" and the terminating chunk;
 // with ``error`` an error event instead.  The connection goes back to reading requests.  Returns the number of tokens pushed.
 int64_t bfront_stream_finish(void* h, int64_t stream, const char* finish_reason, const char* error) {
@@ -1004,7 +1023,8 @@ void bfront_stream_abandon(void* h, int64_t stream) {
     f->streams.erase(st);
 }
 
-// out[0..6]: connections accepted, requests parsed, stream tokens, stream events, bytes written, open connections, open streams.
+// out[0..7]: connections accepted, requests parsed, stream tokens, stream events, bytes written, open connections, open
+// streams, connections closed for idleness.
 void bfront_stats(void* h, uint64_t* out) {
     Front* f = static_cast<Front*>(h);
     std::lock_guard<std::mutex> lk(f->mu);
@@ -1015,6 +1035,7 @@ void bfront_stats(void* h, uint64_t* out) {
     out[4] = f->n_bytes_out.load();
     out[5] = f->conns.size();
     out[6] = f->streams.size();
+    out[7] = f->n_idle_closed;
 }
 
 }  // extern "C"

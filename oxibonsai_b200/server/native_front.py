@@ -56,6 +56,8 @@ def _lib():
         lib.bfront_set_lazy.restype = None
         lib.bfront_kick.argtypes = [C.c_void_p]
         lib.bfront_kick.restype = None
+        lib.bfront_set_idle_timeout.argtypes = [C.c_void_p, C.c_int]
+        lib.bfront_set_idle_timeout.restype = None
         lib.bfront_stats.argtypes = [C.c_void_p, C.POINTER(C.c_uint64)]
         lib.bfront_stats.restype = None
         # The per-token call is a few hundred nanoseconds of work under a mutex: it keeps the interpreter lock (``PyDLL``).
@@ -214,10 +216,14 @@ class NativeFront:
     def kick(self) -> None:
         self._lib._bfront_kick_held(self._h)
 
+    def set_idle_timeout(self, seconds: float) -> None:
+        """Keep-alive connections that wait for a request and move no byte for this long are closed (default 75 s; 0: never)."""
+        self._lib.bfront_set_idle_timeout(self._h, int(seconds * 1000))
+
     def stats(self) -> dict:
-        out = (C.c_uint64 * 7)()
+        out = (C.c_uint64 * 8)()
         self._lib.bfront_stats(self._h, out)
-        keys = ("connections_accepted", "requests", "stream_tokens", "stream_events", "bytes_out", "open_connections", "open_streams")
+        keys = ("connections_accepted", "requests", "stream_tokens", "stream_events", "bytes_out", "open_connections", "open_streams", "idle_closed")
         return dict(zip(keys, (int(v) for v in out)))
 
 

@@ -142,7 +142,7 @@ int main() {
     done.store(true);
     producer.join();
     int dangling = connect_to(port);                        // open while the front shuts down
-    uint64_t st[7];
+    uint64_t st[8];
     bfront_stats(f, st);
     bfront_stop(f);
     dispatcher.join();

@@ -381,3 +381,30 @@ def test_client_that_leaves_frees_its_slot_and_failed_submits_answer_503():
         thread.join(5)
         front.close()
         sched.stop()
+
+
+def test_idle_connections_are_closed_but_streams_are_not(front):
+    """A connection that waits for a request (or sits on half of one) without moving a byte is closed after the idle
+    time-out; a connection whose stream is being produced slowly is not."""
+    front.set_idle_timeout(0.3)
+
+    def script(f, conn):
+        s = f.open_stream(conn, HEAD, False, [], "", 0)
+        s.begin([(b"content-type", b"text/event-stream")])
+        time.sleep(0.8)                                    # longer than the idle time-out, no byte in between
+        s.push(ord("z"))
+        s.finish("stop")
+
+    _Echo(front, script).start()
+    idle = socket.create_connection(("127.0.0.1", front.port))
+    half = socket.create_connection(("127.0.0.1", front.port))
+    half.sendall(b"POST /x HTTP/1.1\r\nContent-Length: 100\r\n\r\npartial")
+    c = http.client.HTTPConnection("127.0.0.1", front.port, timeout=10)
+    c.request("GET", "/stream")
+    evs = _events(c.getresponse().read().decode())
+    assert [e["choices"][0]["text"] for e in evs[:-1]] == ["z", ""] and evs[-1] == "[DONE]"
+    for sk in (idle, half):
+        sk.settimeout(3)
+        assert sk.recv(100) == b""                         # closed by the server
+        sk.close()
+    assert front.stats()["idle_closed"] == 2
