@@ -115,6 +115,32 @@ def main() -> None:
     sk = socket.create_connection(("127.0.0.1", front.port))
     sk.sendall(b"GET /stream HTTP/1.1\r\n\r\n")
     sk.close()
+    # the parser against noise: random bytes, and valid requests with random mutations (a byte changed, cut short, doubled)
+    import random
+    fuzz = random.Random(5)
+    valid = b"POST /v1/x?y=1 HTTP/1.1\r\nHost: a\r\nContent-Length: 12\r\nExpect: 100-continue\r\nConnection: keep-alive\r\n\r\nhello world!"
+    for i in range(150):
+        kind = i % 4
+        if kind == 0:
+            payload = bytes(fuzz.randrange(256) for _ in range(fuzz.randint(1, 400)))
+        elif kind == 1:
+            b = bytearray(valid)
+            for _ in range(fuzz.randint(1, 4)):
+                b[fuzz.randrange(len(b))] = fuzz.randrange(256)
+            payload = bytes(b)
+        elif kind == 2:
+            payload = valid[:fuzz.randrange(len(valid))]
+        else:
+            cut = fuzz.randrange(len(valid))
+            payload = valid[:cut] + valid[cut:] * 2 + b"\r\n" * fuzz.randint(0, 3)
+        sk = socket.create_connection(("127.0.0.1", front.port))
+        sk.sendall(payload)
+        sk.settimeout(0.02)
+        try:
+            sk.recv(1 << 16)
+        except OSError:
+            pass
+        sk.close()
     dangling = socket.create_connection(("127.0.0.1", front.port))      # still open when the front shuts down
     import time
     time.sleep(0.3)
