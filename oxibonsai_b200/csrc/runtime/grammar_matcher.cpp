@@ -357,14 +357,26 @@ extern "C" {
 
 // blob (int32): n_terms, n_rules, start, then n_terms x 8 words (256-bit sets, little end first), then per rule:
 // n_alternatives, per alternative: length, symbols (>= 0 rule id, < 0 terminal -(id + 1)).  Returns nullptr on a malformed blob.
+static void* compile_checked(const int32_t* blob, uint32_t n);
+
 void* bgram_compile(const int32_t* blob, uint32_t n) {
+  try {
+    return blob ? compile_checked(blob, n) : nullptr;
+  } catch (...) {                       // out of memory on an absurd but well-formed blob: refused like a malformed one
+    return nullptr;
+  }
+}
+
+static void* compile_checked(const int32_t* blob, uint32_t n) {
   auto g = std::make_unique<Grammar>();
   uint32_t p = 0;
-  auto need = [&](uint32_t k) { return p + k <= n; };
+  auto need = [&](uint64_t k) { return uint64_t(p) + k <= uint64_t(n); };
   if (!need(3)) return nullptr;
+  if (blob[0] < 0 || blob[1] <= 0 || blob[2] < 0) return nullptr;
   uint32_t n_terms = uint32_t(blob[p++]), n_rules = uint32_t(blob[p++]);
   g->start = uint32_t(blob[p++]);
-  if (g->start >= n_rules || !need(n_terms * 8)) return nullptr;
+  // every terminal set takes 8 words and every rule at least one, so both counts are bounded by the blob's length
+  if (g->start >= n_rules || n_rules > n || !need(uint64_t(n_terms) * 8)) return nullptr;
   g->terms.resize(n_terms);
   for (uint32_t t = 0; t < n_terms; ++t)
     for (int w = 0; w < 4; ++w) {
@@ -375,9 +387,11 @@ void* bgram_compile(const int32_t* blob, uint32_t n) {
   g->rule_prods.resize(n_rules);
   for (uint32_t r = 0; r < n_rules; ++r) {
     if (!need(1)) return nullptr;
+    if (blob[p] < 0) return nullptr;
     uint32_t alts = uint32_t(blob[p++]);
+    if (!need(alts)) return nullptr;                    // every alternative takes at least its length word
     for (uint32_t a = 0; a < alts; ++a) {
-      if (!need(1)) return nullptr;
+      if (!need(1) || blob[p] < 0) return nullptr;
       uint32_t len = uint32_t(blob[p++]);
       if (!need(len) || len > 255 || g->prods.size() >= (1u << 24)) return nullptr;
       Prod pr{r, uint32_t(g->syms.size()), len};

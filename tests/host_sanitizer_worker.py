@@ -66,6 +66,29 @@ def main() -> None:
         assert gc.is_complete() and not gc.advance(ord("x"))
         gc.reset()
         assert gc.allowed_mask().any()
+    # malformed grammar blobs are refused by the compiler, never read past their end
+    import ctypes as C
+    from oxibonsai_b200.runtime.grammar.compilers import json_grammar
+    from oxibonsai_b200.runtime.grammar import native as GN
+    lib = GN._lib()
+    good = GN.serialize(json_grammar())
+    noise = np.random.default_rng(9)
+    for trial in range(300):
+        blob = good.copy()
+        if trial % 3 == 0:
+            blob = blob[: int(noise.integers(0, blob.size))]
+        elif trial % 3 == 1:
+            for _ in range(int(noise.integers(1, 6))):
+                blob[int(noise.integers(0, blob.size))] = int(noise.integers(-5000, 5000))
+        else:
+            blob = noise.integers(-300, 300, size=int(noise.integers(0, 200))).astype(np.int32)
+        blob = np.ascontiguousarray(blob, dtype=np.int32)
+        hg = lib.bgram_compile(blob.ctypes.data if blob.size else None, blob.size)
+        if hg:                                          # still a well-formed grammar: it must also run
+            hm = lib.bgram_matcher_new(hg)
+            lib.bgram_matcher_feed(hm, b'{"a": [1, "x"]}', 15)
+            lib.bgram_matcher_free(hm)
+            lib.bgram_free(hg)
     # HTTP / SSE front: requests (whole, split, malformed), a token stream with stop sequences and broken UTF-8, a client
     # that leaves in mid-stream, shutdown with open connections
     import http.client
