@@ -181,3 +181,22 @@ def test_long_productions_and_bad_bounds():
     for bad in ({"type": "string", "minLength": 5, "maxLength": 2}, {"type": "array", "minItems": 3, "maxItems": 1}):
         with pytest.raises(GrammarError):
             json_schema_to_grammar(bad)
+
+
+def test_shared_caches_are_race_free_under_thread_sanitizer(tmp_path):
+    """Four threads with their own matchers over one compiled grammar and one vocabulary (tests/grammar_tsan_driver.cpp),
+    built with -fsanitize=thread: no data race, and every mask equals the single-threaded one."""
+    import os
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    rt = os.path.join(os.path.dirname(here), "oxibonsai_b200", "csrc", "runtime")
+    probe = subprocess.run(["g++", "-fsanitize=thread", "-x", "c++", "-", "-o", str(tmp_path / "probe")], input="int main(){return 0;}", capture_output=True, text=True)
+    if probe.returncode != 0:
+        pytest.skip("the host compiler has no ThreadSanitizer runtime")
+    exe = str(tmp_path / "gram_tsan")
+    build = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-pthread", "-fsanitize=thread", f"-I{rt}", os.path.join(rt, "grammar_matcher.cpp"),
+                            os.path.join(rt, "token_mask.cpp"), os.path.join(here, "grammar_tsan_driver.cpp"), "-o", exe], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=dict(os.environ, TSAN_OPTIONS="halt_on_error=0"))
+    assert run.returncode == 0 and "grammar tsan driver ok" in run.stdout, run.stdout[-1000:] + run.stderr[-3000:]
+    assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-4000:]
