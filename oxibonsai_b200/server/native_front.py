@@ -342,7 +342,8 @@ class AsgiBridge:
                 handle.stream.abandon()               # a stream was opened but the route answered in another way
             self._gone.pop(conn, None)
 
-    async def serve(self, stop: threading.Event | None = None) -> None:
+    async def serve(self, stop: threading.Event | None = None, grace_seconds: float = 5.0) -> None:
+        """Dispatches requests until ``stop`` is set; requests that are being answered then get ``grace_seconds`` to finish."""
         loop = asyncio.get_running_loop()
         state: dict = {}
         await self._lifespan("startup", state)
@@ -365,24 +366,41 @@ class AsgiBridge:
                 self._tasks.add(task)
                 task.add_done_callback(self._tasks.discard)
         finally:
+            if self._tasks and grace_seconds > 0:
+                await asyncio.wait(list(self._tasks), timeout=grace_seconds)
             for t in list(self._tasks):
                 t.cancel()
             await self._lifespan("shutdown", state)
 
 
-def serve(app, host: str, port: int, tokenizer=None, stop: threading.Event | None = None, on_ready=None, vocab_size: int | None = None) -> None:
-    """Serves ``app`` until ``stop`` is set (or the process is interrupted).  With ``tokenizer`` the front detokenises
-    streamed completions itself; ``vocab_size``: the model's vocabulary when it is larger than the tokenizer's."""
+def serve(app, host: str, port: int, tokenizer=None, stop: threading.Event | None = None, on_ready=None, vocab_size: int | None = None,
+          grace_seconds: float = 5.0) -> None:
+    """Serves ``app`` until ``stop`` is set or the process receives SIGINT / SIGTERM, then shuts down gracefully: no new
+    requests are dispatched, requests being answered and token streams being produced get ``grace_seconds`` to finish, then
+    every socket is closed.  With ``tokenizer`` the front detokenises streamed completions itself; ``vocab_size``: the
+    model's vocabulary when it is larger than the tokenizer's."""
+    import signal
+    import time
     front = NativeFront(host, port)
     if tokenizer is not None:
         front.set_vocab(tokenizer, vocab_size)
     front.start()
     if on_ready is not None:
         on_ready(front)
+    stop = stop or threading.Event()
+    previous = {}
+    if threading.current_thread() is threading.main_thread():
+        for sig in (signal.SIGINT, signal.SIGTERM):
+            previous[sig] = signal.signal(sig, lambda *_: stop.set())
     bridge = AsgiBridge(app, front)
     try:
-        asyncio.run(bridge.serve(stop))
+        asyncio.run(bridge.serve(stop, grace_seconds))
+        deadline = time.monotonic() + grace_seconds
+        while front.stats()["open_streams"] and time.monotonic() < deadline:      # streams are fed by the scheduler, not by a task
+            time.sleep(0.02)
     except KeyboardInterrupt:
         pass
     finally:
+        for sig, handler in previous.items():
+            signal.signal(sig, handler)
         front.close()

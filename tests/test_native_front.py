@@ -408,3 +408,48 @@ def test_idle_connections_are_closed_but_streams_are_not(front):
         assert sk.recv(100) == b""                         # closed by the server
         sk.close()
     assert front.stats()["idle_closed"] == 2
+
+
+def test_sigterm_shuts_the_server_down_gracefully(tmp_path):
+    """``serve()`` in a child process: SIGTERM while a stream is being produced lets that stream finish ("[DONE]" arrives),
+    then the process exits with status 0."""
+    import os
+    import signal
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = f"""
+import sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, {os.path.join(root, 'benchmarks')!r})
+from front_overhead import run_server
+run_server("native", int(sys.argv[1]), 4, 20.0)
+"""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    child = subprocess.Popen([sys.executable, "-c", code, str(port)], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    try:
+        for _ in range(200):
+            try:
+                socket.create_connection(("127.0.0.1", port), timeout=0.2).close()
+                break
+            except OSError:
+                time.sleep(0.1)
+        body = json.dumps({"prompt": "abc", "max_tokens": 40, "stream": True}).encode()
+        s = socket.create_connection(("127.0.0.1", port))
+        s.sendall(b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: " + str(len(body)).encode() + b"\r\n\r\n" + body)
+        got = b""
+        while got.count(b"data: ") < 3:
+            got += s.recv(65536)
+        child.send_signal(signal.SIGTERM)                  # 40 tokens at 20 ms per step: the stream still has ~0.7 s to go
+        s.settimeout(10)
+        while True:
+            chunk = s.recv(65536)
+            if not chunk:
+                break
+            got += chunk
+        assert b"data: [DONE]" in got and got.count(b"data: ") == 40 + 2      # 40 tokens, the finish chunk, [DONE]
+        assert child.wait(15) == 0
+    finally:
+        if child.poll() is None:
+            child.kill()
