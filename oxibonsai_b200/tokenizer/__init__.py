@@ -221,6 +221,16 @@ class HfTokenizerBridge:
         from tokenizers import Tokenizer
         self._t = Tokenizer.from_file(path)
         self.vocab_size = self._t.get_vocab_size()
+        # Byte-level models spell every token in the 256-character byte alphabet; a token may be a fragment of a UTF-8
+        # character, which ``decode`` would turn into U+FFFD.  Streaming needs the real bytes.
+        spec = json.loads(self._t.to_str())
+
+        def byte_level(node) -> bool:
+            if isinstance(node, dict):
+                return node.get("type") == "ByteLevel" or any(byte_level(v) for v in node.values())
+            return isinstance(node, list) and any(byte_level(v) for v in node)
+        self._u2b = {u: b for b, u in bytes_to_unicode().items()} if byte_level(spec.get("decoder")) else None
+        self._special = {t["id"] for t in spec.get("added_tokens", []) if t.get("special")}
 
     def encode(self, text: str) -> list[int]:
         return self._t.encode(text, add_special_tokens=False).ids
@@ -229,7 +239,15 @@ class HfTokenizerBridge:
         return self._t.decode(list(ids), skip_special_tokens=False)
 
     def token_bytes(self, i: int) -> bytes:
-        return self._t.decode([int(i)], skip_special_tokens=False).encode("utf-8")
+        i = int(i)
+        if self._u2b is not None and i not in self._special:
+            piece = self._t.id_to_token(i)
+            if piece is not None:
+                try:
+                    return bytes(self._u2b[ch] for ch in piece)
+                except KeyError:            # an added token written in plain text
+                    return piece.encode("utf-8")
+        return self._t.decode([i], skip_special_tokens=False).encode("utf-8")
 
 
 # ---- chat templates -------------------------------------------------------------------------------------

@@ -86,3 +86,24 @@ def test_unigram_wordpiece_char_and_byte_fallback():
     ids = X.encode_with_byte_fallback("aé", vocab)
     assert ids == [1, 10 + 0xC3, 10 + 0xA9] and X.decode_with_byte_fallback(ids, {v: k for k, v in vocab.items()}) == "aé"
     assert X.parse_byte_fallback("<0x0A>") == 10 and X.parse_byte_fallback("<0xZZ>") is None and X.parse_byte_fallback("abc") is None
+
+
+def test_hf_bridge_gives_the_real_bytes_of_byte_level_tokens(tmp_path):
+    """A byte-level BPE token may be a fragment of a UTF-8 character; ``decode`` turns that into U+FFFD, the bridge must
+    not: streaming joins fragments of several tokens into one character."""
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=["<|endoftext|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["héllo wörld 日本語 " * 20, "the quick brown fox 🙂 " * 20], trainer)
+    path = str(tmp_path / "tokenizer.json")
+    tok.save(path)
+    hf, native = T.HfTokenizerBridge(path), T.BpeTokenizer.from_hf_json(path)
+    text = "héllo 日本語 🙂 fox"
+    assert hf.encode(text) == native.encode(text)
+    assert all(hf.token_bytes(i) == native.token_bytes(i) for i in range(1, hf.vocab_size))           # (id 0 is the special token)
+    assert hf.token_bytes(0) == b"<|endoftext|>"
+    dec = T.StreamingDecoder()
+    assert "".join(dec.push(hf.token_bytes(i)) for i in hf.encode(text)) + dec.flush() == text
