@@ -124,6 +124,30 @@ class BpeTokenizer:
             raise ValueError(f"unsupported tokenizer model type {model.get('type')}")
         merges = [tuple(m.split(" ", 1)) if isinstance(m, str) else tuple(m) for m in model.get("merges", [])]
         special = {t["content"]: t["id"] for t in j.get("added_tokens", [])}
+
+        def split_pattern(node) -> str | None:
+            """The regular expression of the file's ``Split`` pre-tokenizer (Qwen, Llama-3 ... ship their own)."""
+            if isinstance(node, dict):
+                if node.get("type") == "Split" and isinstance(node.get("pattern"), dict) and "Regex" in node["pattern"]:
+                    return node["pattern"]["Regex"]
+                for v in node.values():
+                    found = split_pattern(v)
+                    if found:
+                        return found
+            elif isinstance(node, list):
+                for v in node:
+                    found = split_pattern(v)
+                    if found:
+                        return found
+            return None
+        pattern = split_pattern(j.get("pre_tokenizer"))
+        if pattern:
+            try:
+                import regex
+                regex.compile(pattern)
+                return cls(model["vocab"], merges, special, pattern)
+            except Exception:  # noqa: BLE001 - a dialect the regex module does not take: the GPT-2 pattern is the fallback
+                pass
         return cls(model["vocab"], merges, special)
 
     def _encode_piece(self, piece: str) -> list[int]:

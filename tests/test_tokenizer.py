@@ -107,3 +107,25 @@ def test_hf_bridge_gives_the_real_bytes_of_byte_level_tokens(tmp_path):
     assert hf.token_bytes(0) == b"<|endoftext|>"
     dec = T.StreamingDecoder()
     assert "".join(dec.push(hf.token_bytes(i)) for i in hf.encode(text)) + dec.flush() == text
+
+
+def test_native_bpe_uses_the_files_own_split_pattern(tmp_path):
+    """Qwen-style files carry their pre-tokenizer's regular expression (digits one by one, contractions case-insensitive);
+    the native tokenizer takes it from the file and agrees with the ``tokenizers`` library on text where the GPT-2 pattern
+    would split differently."""
+    pytest.importorskip("tokenizers")
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    qwen = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(qwen), behavior="isolated"),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|endoftext|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["call 911 or 1234567 now, it's 12:30pm!! " * 30, "the quick brown fox's 42 jumps\n\nnew line " * 30, "IT'S DONE, I'LL go.  ok\t\tthen" * 30], trainer)
+    path = str(tmp_path / "tokenizer.json")
+    tok.save(path)
+    native = T.BpeTokenizer.from_hf_json(path)
+    assert native._split.pattern == qwen
+    for text in ("call 911 or 1234567 now", "it's 12:30pm!!\n\nnew", "fox's  42   jumps", "IT'S DONE, I'LL go.", "a\t\tb  \n c", "x=3.14159;y=-2"):
+        assert native.encode(text) == tok.encode(text, add_special_tokens=False).ids, text
+        assert native.decode(native.encode(text)) == text
