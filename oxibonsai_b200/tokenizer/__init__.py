@@ -141,14 +141,27 @@ class BpeTokenizer:
                         return found
             return None
         pattern = split_pattern(j.get("pre_tokenizer"))
+        tok = None
         if pattern:
             try:
                 import regex
                 regex.compile(pattern)
-                return cls(model["vocab"], merges, special, pattern)
+                tok = cls(model["vocab"], merges, special, pattern)
             except Exception:  # noqa: BLE001 - a dialect the regex module does not take: the GPT-2 pattern is the fallback
-                pass
-        return cls(model["vocab"], merges, special)
+                tok = None
+        tok = tok or cls(model["vocab"], merges, special)
+
+        def normal_form(node) -> str | None:
+            """Unicode normalisation the file asks for (Qwen: NFC), applied to plain text before splitting."""
+            if isinstance(node, dict):
+                if node.get("type") in ("NFC", "NFD", "NFKC", "NFKD"):
+                    return node["type"]
+                return next((f for f in (normal_form(v) for v in node.values()) if f), None)
+            if isinstance(node, list):
+                return next((f for f in (normal_form(v) for v in node) if f), None)
+            return None
+        tok.normal_form = normal_form(j.get("normalizer"))
+        return tok
 
     def _encode_piece(self, piece: str) -> list[int]:
         raw = piece.encode("utf-8")
@@ -175,10 +188,14 @@ class BpeTokenizer:
                 segments.append((text[pos:], False))
         else:
             segments = [(text, False)]
+        form = getattr(self, "normal_form", None)
         for seg, is_special in segments:
             if is_special:
                 out.append(self.special[seg])
             else:
+                if form:
+                    import unicodedata
+                    seg = unicodedata.normalize(form, seg)
                 for piece in self._split.findall(seg):
                     out.extend(self._encode_piece(piece))
         return out
