@@ -68,9 +68,13 @@ def summary_line(n_prompt: int, n_gen: int, seconds: float) -> str:
 def _load_tokenizer(model: str, explicit: str | None, quiet: bool = False):
     from .tokenizer import load_tokenizer
     path, searched = resolve_tokenizer(model, explicit)
+    tok = load_tokenizer(path, model_path=model)
     if path is None and not quiet:
-        print(no_tokenizer_warning(searched), file=sys.stderr)
-    return load_tokenizer(path)
+        if type(tok).__name__ == "BpeTokenizer":
+            print(f"no tokenizer.json found; using the vocabulary embedded in {model} ({tok.vocab_size} tokens)", file=sys.stderr)
+        else:
+            print(no_tokenizer_warning(searched), file=sys.stderr)
+    return tok
 
 
 def _engine(args, max_batch: int = 1):

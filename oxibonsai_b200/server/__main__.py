@@ -35,9 +35,12 @@ def main(argv: list[str] | None = None) -> int:
         return 2
     init_tracing(cfg.log_level, cfg.json_logs)
     tok_path, searched = resolve_tokenizer(cfg.model_path, cfg.tokenizer_path)
+    tokenizer = load_tokenizer(tok_path, cfg.tokenizer_kind, model_path=cfg.model_path)
     if tok_path is None:
-        print(no_tokenizer_warning(searched), file=sys.stderr)
-    tokenizer = load_tokenizer(tok_path, cfg.tokenizer_kind)
+        if type(tokenizer).__name__ == "BpeTokenizer":
+            print(f"no tokenizer.json found; using the vocabulary embedded in {cfg.model_path} ({tokenizer.vocab_size} tokens)", file=sys.stderr)
+        else:
+            print(no_tokenizer_warning(searched), file=sys.stderr)
     sp = SamplingParams(temperature=cfg.temperature, top_k=cfg.top_k, top_p=cfg.top_p, repetition_penalty=cfg.repetition_penalty,
                         max_tokens=cfg.max_tokens, seed=cfg.seed)
     import os

@@ -163,6 +163,40 @@ class BpeTokenizer:
         tok.normal_form = normal_form(j.get("normalizer"))
         return tok
 
+    QWEN_SPLIT = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+")
+
+    @classmethod
+    def from_gguf(cls, gguf) -> "BpeTokenizer":
+        """The byte-level BPE vocabulary a GGUF file carries in its metadata (``tokenizer.ggml.model = "gpt2"``:
+        ``tokens``, ``merges``, ``token_type`` with 3 = control and 4 = user-defined tokens, ``pre`` naming the split
+        pattern, ``bos`` / ``eos_token_id``).  ``gguf``: a path or an open ``GgufFile``.  The reference defines these keys
+        (crates/oxibonsai-core/src/gguf/tensor_info.rs:203-206) and loads tokenizers from ``tokenizer.json`` only; with this
+        a checkpoint that embeds its vocabulary needs no side file."""
+        if isinstance(gguf, (str, bytes)) or hasattr(gguf, "__fspath__"):
+            from ..core import GgufFile
+            gguf = GgufFile.open(str(gguf))
+        md = gguf.metadata
+        kind = md.get("tokenizer.ggml.model")
+        if kind != "gpt2":
+            raise ValueError(f"the file embeds no byte-level BPE vocabulary (tokenizer.ggml.model = {kind!r})")
+        tokens = list(md.get("tokenizer.ggml.tokens") or [])
+        if not tokens:
+            raise ValueError("tokenizer.ggml.tokens is empty")
+        types = list(md.get("tokenizer.ggml.token_type") or [])
+        vocab, special = {}, {}
+        for i, t in enumerate(tokens):
+            if i < len(types) and types[i] in (3, 4):
+                special[t] = i
+            else:
+                vocab[t] = i
+        merges = [tuple(m.split(" ", 1)) for m in md.get("tokenizer.ggml.merges") or [] if " " in m]
+        pre = str(md.get("tokenizer.ggml.pre") or "")
+        tok = cls(vocab, merges, special, cls.QWEN_SPLIT if pre.startswith("qwen") else _GPT2_SPLIT)
+        tok.normal_form = "NFC" if pre.startswith("qwen") else None
+        tok.eos_token_id = md.get("tokenizer.ggml.eos_token_id")
+        tok.bos_token_id = md.get("tokenizer.ggml.bos_token_id")
+        return tok
+
     def _encode_piece(self, piece: str) -> list[int]:
         raw = piece.encode("utf-8")
         ids = np.fromiter((self._byte_id[b] for b in raw), dtype=np.int64, count=len(raw))
@@ -318,10 +352,20 @@ def chat_prompt(messages: Sequence[dict], template: str = "chatml", add_generati
     raise ValueError(f"unknown chat template {template!r}")
 
 
-def load_tokenizer(path: str | None, kind: str = "auto"):
-    """``kind``: auto / native / hf / bytes.  ``auto`` prefers the native BPE for tokenizer.json files."""
-    if path is None or kind == "bytes":
+def load_tokenizer(path: str | None, kind: str = "auto", model_path: str | None = None):
+    """``kind``: auto / native / hf / bytes.  ``auto`` prefers the native BPE for tokenizer.json files.  Without a tokenizer
+    file, a vocabulary embedded in the checkpoint at ``model_path`` is used when there is one; raw bytes are the last resort."""
+    if kind == "bytes":
         return ByteTokenizer()
+    if path is None:
+        if model_path is not None:
+            try:
+                return BpeTokenizer.from_gguf(model_path)
+            except Exception:  # noqa: BLE001 - no embedded vocabulary (or not a GGUF file)
+                pass
+        return ByteTokenizer()
+    if str(path).endswith(".gguf"):
+        return BpeTokenizer.from_gguf(path)
     if kind in ("auto", "native"):
         try:
             return BpeTokenizer.from_hf_json(path)

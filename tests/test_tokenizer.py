@@ -129,3 +129,29 @@ def test_native_bpe_uses_the_files_own_split_pattern(tmp_path):
     for text in ("call 911 or 1234567 now", "it's 12:30pm!!\n\nnew", "fox's  42   jumps", "IT'S DONE, I'LL go.", "a\t\tb  \n c", "x=3.14159;y=-2"):
         assert native.encode(text) == tok.encode(text, add_special_tokens=False).ids, text
         assert native.decode(native.encode(text)) == text
+
+
+def test_tokenizer_embedded_in_a_gguf_file(tmp_path):
+    """``tokenizer.ggml.*`` metadata (tokens, merges, token types, eos) make a working tokenizer; ``load_tokenizer`` falls
+    back to it when no tokenizer file is given, and to raw bytes when the checkpoint embeds nothing."""
+    from oxibonsai_b200.core import GgufWriter, Qwen3Config, write_synthetic_gguf
+    tok = T.train_bpe(["the quick brown fox jumps over the lazy dog " * 10, "héllo wörld 日本 12345 " * 10], 420, special_tokens=["<|endoftext|>", "<|im_start|>"])
+    tokens = [tok.id_to_token[i] for i in range(tok.vocab_size)]
+    w = GgufWriter()
+    w.add("general.architecture", "qwen3").add("tokenizer.ggml.model", "gpt2").add("tokenizer.ggml.pre", "qwen2")
+    w.add("tokenizer.ggml.tokens", tokens).add("tokenizer.ggml.merges", [f"{tok.id_to_token[a]} {tok.id_to_token[b]}" for a, b, _ in tok.merges])
+    w.add("tokenizer.ggml.token_type", [3 if t in tok.special else 1 for t in tokens]).add("tokenizer.ggml.eos_token_id", tok.special["<|endoftext|>"])
+    path = str(tmp_path / "with_vocab.gguf")
+    w.write(path)
+    emb = T.BpeTokenizer.from_gguf(path)
+    text = "the quick dog says héllo 日本<|im_start|>ok"
+    assert emb.vocab_size == tok.vocab_size and emb.special == tok.special and emb.eos_token_id == tok.special["<|endoftext|>"]
+    ids = emb.encode(text)
+    assert tok.special["<|im_start|>"] in ids and emb.decode(ids) == text and emb.normal_form == "NFC"
+    assert emb.encode("abc 12345") != [] and all(emb.decode([i]) in "12345" for i in emb.encode("12345"))     # the Qwen pattern isolates digits
+    assert isinstance(T.load_tokenizer(None, model_path=path), T.BpeTokenizer) and isinstance(T.load_tokenizer(path), T.BpeTokenizer)
+    plain = str(tmp_path / "no_vocab.gguf")
+    write_synthetic_gguf(plain, Qwen3Config(hidden=256, inter=512, layers=1, heads=2, kv_heads=1, head_dim=128, vocab=300, context=64, name="t"), seed=1)
+    assert isinstance(T.load_tokenizer(None, model_path=plain), T.ByteTokenizer)
+    with pytest.raises(ValueError, match="embeds no"):
+        T.BpeTokenizer.from_gguf(plain)
