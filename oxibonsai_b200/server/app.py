@@ -463,8 +463,15 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         return PlainTextResponse("", headers={NATIVE_STREAM_HEADER.decode(): "1", "content-type": "text/event-stream", "x-request-id": rid,
                                               "cache-control": "no-cache"})
 
+    template = getattr(cfg, "chat_template", "auto")
+    if template == "auto":                    # the family the model's name points at (Llama-3, Mistral, Gemma, Qwen), else ChatML
+        from ..tokenizer.toolkit import ChatTemplateKind
+        kind = ChatTemplateKind.infer_from_name(str(getattr(backend, "model_name", "")))
+        template = kind.value if kind is not None else "chatml"
+    app.state.chat_template = template
+
     def encode_chat(messages: list[dict]) -> list[int]:
-        return tokenizer.encode(chat_prompt(messages, "chatml"))
+        return tokenizer.encode(chat_prompt(messages, template))
 
     # ---- routes -----------------------------------------------------------------------------------
     @app.get("/health")

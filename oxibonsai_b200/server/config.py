@@ -45,6 +45,7 @@ class ServerConfig:
     prefill_chunk_boost: int = 4      # chunks this many times as long while fewer than a quarter of the slots decode
     kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
+    chat_template: str = "auto"       # chatml | qwen | llama3 | mistral | gemma, or auto: inferred from the model's name, ChatML otherwise
     overlap_steps: bool = False       # launch decode step k + 1 before the tokens of step k are delivered (single-process engines)
     native_front: bool = True         # C++ HTTP / SSE front (sockets, parsing, token streaming); off: uvicorn
 
@@ -68,6 +69,8 @@ class ServerConfig:
             errs.append("tensor_parallel and replicas cannot be combined in one server")
         if self.kv_policy not in ("off", "adaptive", "aggressive"):
             errs.append("kv_policy must be one of off, adaptive, aggressive")
+        if self.chat_template not in ("auto", "chatml", "qwen", "llama3", "mistral", "gemma"):
+            errs.append("chat_template must be one of auto, chatml, qwen, llama3, mistral, gemma")
         if self.kv_cache.lower() not in ("f32", "f16", "q8", "q4"):
             errs.append("kv_cache must be one of f32, f16, q8, q4")
         if check_paths:
@@ -87,7 +90,7 @@ _TOML_MAP = {
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
     ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "tp_elastic"): "tp_elastic", ("model", "tp_heartbeat_timeout"): "tp_heartbeat_timeout", ("model", "kv_policy"): "kv_policy",
-    ("server", "native_front"): "native_front", ("server", "overlap_steps"): "overlap_steps", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
+    ("server", "native_front"): "native_front", ("model", "chat_template"): "chat_template", ("server", "overlap_steps"): "overlap_steps", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",
 }

@@ -412,3 +412,23 @@ def test_forced_tool_choice_constrains_the_generation():
     body["tool_choice"] = {"type": "function", "function": {"name": "launch_rocket"}}
     r = c.post("/v1/chat/completions", json=body)
     assert r.status_code == 400 and "unknown tool" in r.json()["error"]["message"]
+
+
+def test_chat_template_follows_the_model_name_or_the_configuration():
+    from fastapi.testclient import TestClient
+    from oxibonsai_b200.server.app import create_app
+
+    class Named(FakeBackend):
+        def __init__(self, name):
+            super().__init__()
+            self.model_name = name
+
+    def prompt_of(backend, cfg):
+        c = TestClient(create_app(backend, ByteTokenizer(), cfg))
+        assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2}).status_code == 200
+        return bytes(backend.seen[-1][0]).decode()
+    assert prompt_of(Named("Ternary-Bonsai-8B"), ServerConfig()).startswith("<|im_start|>user\nhi<|im_end|>")
+    assert prompt_of(Named("Meta-Llama-3-8B-Instruct"), ServerConfig()).startswith("<|begin_of_text|><|start_header_id|>user")
+    assert "[INST] hi [/INST]" in prompt_of(Named("whatever"), ServerConfig(chat_template="mistral"))
+    with pytest.raises(ValueError, match="chat_template"):
+        ServerConfig(chat_template="jinja").validate(check_paths=False)
