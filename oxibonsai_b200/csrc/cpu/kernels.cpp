@@ -414,6 +414,100 @@ void bcpu_rope_apply(float* x, uint64_t heads, uint64_t head_dim, const float* c
   }
 }
 
+// ---- vectorised float ops (reference: rope_apply_simd / swiglu_simd / silu_simd / softmax_simd,
+// crates/oxibonsai-kernels/src/simd_float_ops.rs:27-180).  tier 0 = the scalar bodies above; tier >= 1 = AVX2 + FMA where
+// the CPU has it.  The rotation is mul / sub / add only and equals the scalar result bit for bit; the ops that need exp() use
+// a degree-5 polynomial after range reduction (relative error below 2e-7), so they agree with the scalar bodies to
+// rounding, not bitwise.
+__attribute__((target("avx2,fma"))) static inline __m256 exp256(__m256 x) {
+  x = _mm256_min_ps(_mm256_max_ps(x, _mm256_set1_ps(-87.33654f)), _mm256_set1_ps(88.72283f));
+  __m256 fx = _mm256_floor_ps(_mm256_fmadd_ps(x, _mm256_set1_ps(1.44269504088896341f), _mm256_set1_ps(0.5f)));
+  x = _mm256_fnmadd_ps(fx, _mm256_set1_ps(0.693359375f), x);
+  x = _mm256_fnmadd_ps(fx, _mm256_set1_ps(-2.12194440e-4f), x);
+  __m256 y = _mm256_set1_ps(1.9875691500e-4f);
+  y = _mm256_fmadd_ps(y, x, _mm256_set1_ps(1.3981999507e-3f));
+  y = _mm256_fmadd_ps(y, x, _mm256_set1_ps(8.3334519073e-3f));
+  y = _mm256_fmadd_ps(y, x, _mm256_set1_ps(4.1665795894e-2f));
+  y = _mm256_fmadd_ps(y, x, _mm256_set1_ps(1.6666665459e-1f));
+  y = _mm256_fmadd_ps(y, x, _mm256_set1_ps(5.0000001201e-1f));
+  y = _mm256_fmadd_ps(y, _mm256_mul_ps(x, x), _mm256_add_ps(x, _mm256_set1_ps(1.0f)));
+  const __m256i e = _mm256_slli_epi32(_mm256_add_epi32(_mm256_cvtps_epi32(fx), _mm256_set1_epi32(127)), 23);
+  return _mm256_mul_ps(y, _mm256_castsi256_ps(e));
+}
+
+__attribute__((target("avx2,fma"))) static void silu_avx2(const float* x, const float* up, float* out, uint64_t n) {
+  uint64_t i = 0;
+  const __m256 one = _mm256_set1_ps(1.0f);
+  for (; i + 8 <= n; i += 8) {
+    const __m256 v = _mm256_loadu_ps(x + i);
+    __m256 r = _mm256_div_ps(v, _mm256_add_ps(one, exp256(_mm256_sub_ps(_mm256_setzero_ps(), v))));
+    if (up) r = _mm256_mul_ps(r, _mm256_loadu_ps(up + i));
+    _mm256_storeu_ps(out + i, r);
+  }
+  for (; i < n; ++i) out[i] = x[i] / (1.0f + std::exp(-x[i])) * (up ? up[i] : 1.0f);
+}
+
+__attribute__((target("avx2,fma"))) static void softmax_avx2(const float* x, float* out, uint64_t n) {
+  __m256 vm = _mm256_set1_ps(-INFINITY);
+  uint64_t i = 0;
+  for (; i + 8 <= n; i += 8) vm = _mm256_max_ps(vm, _mm256_loadu_ps(x + i));
+  float lanes[8];
+  _mm256_storeu_ps(lanes, vm);
+  float m = -INFINITY;
+  for (float l : lanes) m = std::max(m, l);
+  for (; i < n; ++i) m = std::max(m, x[i]);
+  const __m256 mm = _mm256_set1_ps(m);
+  __m256 acc = _mm256_setzero_ps();
+  for (i = 0; i + 8 <= n; i += 8) {
+    const __m256 e = exp256(_mm256_sub_ps(_mm256_loadu_ps(x + i), mm));
+    _mm256_storeu_ps(out + i, e);
+    acc = _mm256_add_ps(acc, e);
+  }
+  float s = bonsai::hsum256(acc);
+  for (; i < n; ++i) {
+    out[i] = std::exp(x[i] - m);
+    s += out[i];
+  }
+  const __m256 inv = _mm256_set1_ps(1.0f / s);
+  for (i = 0; i + 8 <= n; i += 8) _mm256_storeu_ps(out + i, _mm256_mul_ps(_mm256_loadu_ps(out + i), inv));
+  for (; i < n; ++i) out[i] *= 1.0f / s;
+}
+
+__attribute__((target("avx2"))) static void rope_avx2(float* x, uint64_t heads, uint64_t head_dim, const float* cos, const float* sin) {
+  const uint64_t h = head_dim / 2;
+  for (uint64_t hd = 0; hd < heads; ++hd) {
+    float* v = x + hd * head_dim;
+    uint64_t i = 0;
+    for (; i + 8 <= h; i += 8) {
+      const __m256 a = _mm256_loadu_ps(v + i), b = _mm256_loadu_ps(v + h + i), c = _mm256_loadu_ps(cos + i), s = _mm256_loadu_ps(sin + i);
+      _mm256_storeu_ps(v + i, _mm256_sub_ps(_mm256_mul_ps(a, c), _mm256_mul_ps(b, s)));        // no fused multiply-add: same
+      _mm256_storeu_ps(v + h + i, _mm256_add_ps(_mm256_mul_ps(a, s), _mm256_mul_ps(b, c)));    // roundings as the scalar body
+    }
+    for (; i < h; ++i) {
+      const float a = v[i], b = v[h + i];
+      v[i] = a * cos[i] - b * sin[i];
+      v[h + i] = a * sin[i] + b * cos[i];
+    }
+  }
+}
+
+void bcpu_silu_t(const float* x, float* out, uint64_t n, int tier) {
+  if (std::min(tier, bonsai::detect_tier()) >= 1) silu_avx2(x, nullptr, out, n);
+  else bcpu_silu(x, out, n);
+}
+void bcpu_swiglu_t(const float* gate, const float* up, float* out, uint64_t n, int tier) {
+  if (std::min(tier, bonsai::detect_tier()) >= 1) silu_avx2(gate, up, out, n);
+  else bcpu_swiglu_tiered(gate, up, out, n);
+}
+void bcpu_softmax_t(const float* x, float* out, uint64_t n, int tier) {
+  if (n > 0 && std::min(tier, bonsai::detect_tier()) >= 1) softmax_avx2(x, out, n);
+  else bcpu_softmax(x, out, n);
+}
+void bcpu_rope_apply_t(float* x, uint64_t heads, uint64_t head_dim, const float* cos, const float* sin, int tier) {
+  if (std::min(tier, bonsai::detect_tier()) >= 1) rope_avx2(x, heads, head_dim, cos, sin);
+  else bcpu_rope_apply(x, heads, head_dim, cos, sin);
+}
+
 // 64-byte aligned host buffers (for SIMD loads and for pinned-memory staging).
 void* bcpu_aligned_alloc(uint64_t bytes) {
   void* p = nullptr;

@@ -66,6 +66,8 @@ def _lib():
             "bcpu_gemv_tiered": (i, [u32, vp, u64, u64, vp, vp, i, i]), "bcpu_gemm_tiered": (i, [u32, vp, u64, u64, vp, u64, vp, i]),
             "bcpu_rmsnorm_tiered": (None, [vp, vp, vp, u64, f, i]), "bcpu_silu": (None, [vp, vp, u64]), "bcpu_swiglu_tiered": (None, [vp, vp, vp, u64]),
             "bcpu_softmax": (None, [vp, vp, u64]), "bcpu_rope_apply": (None, [vp, u64, u64, vp, vp]),
+            "bcpu_silu_t": (None, [vp, vp, u64, i]), "bcpu_swiglu_t": (None, [vp, vp, vp, u64, i]), "bcpu_softmax_t": (None, [vp, vp, u64, i]),
+            "bcpu_rope_apply_t": (None, [vp, u64, u64, vp, vp, i]),
             "bcpu_aligned_alloc": (vp, [u64]), "bcpu_aligned_free": (None, [vp]),
             "bcpu_working_set_bytes": (u64, [u32, u64, u64]), "bcpu_optimal_tile_rows": (u64, [u32, u64, u64]),
             "bcpu_select_strategy": (i, [u64, u64, u64]), "bcpu_prefetch_range": (None, [vp, u64, i, i]),
@@ -235,36 +237,38 @@ def rms_norm(x, w, eps: float = 1e-6, tier: int = 1) -> np.ndarray:
     return out
 
 
-def silu(x) -> np.ndarray:
+def silu(x, tier: int = 0) -> np.ndarray:
+    """``tier`` 0: scalar body (the oracle's arithmetic); >= 1: AVX2 + FMA with a polynomial exp (agrees to rounding)."""
     xv = _f32(x)
     out = np.empty_like(xv)
-    _lib().bcpu_silu(xv.ctypes.data, out.ctypes.data, xv.size)
+    _lib().bcpu_silu_t(xv.ctypes.data, out.ctypes.data, xv.size, int(tier))
     return out
 
 
-def swiglu(gate, up) -> np.ndarray:
+def swiglu(gate, up, tier: int = 0) -> np.ndarray:
     g, u = _f32(gate), _f32(up)
     if g.size != u.size:
         raise DimensionMismatch("gate and up differ in length")
     out = np.empty_like(g)
-    _lib().bcpu_swiglu_tiered(g.ctypes.data, u.ctypes.data, out.ctypes.data, g.size)
+    _lib().bcpu_swiglu_t(g.ctypes.data, u.ctypes.data, out.ctypes.data, g.size, int(tier))
     return out
 
 
-def softmax(x) -> np.ndarray:
+def softmax(x, tier: int = 0) -> np.ndarray:
     xv = _f32(x)
     out = np.empty_like(xv)
-    _lib().bcpu_softmax(xv.ctypes.data, out.ctypes.data, xv.size)
+    _lib().bcpu_softmax_t(xv.ctypes.data, out.ctypes.data, xv.size, int(tier))
     return out
 
 
-def rope_apply(x, cos, sin) -> np.ndarray:
-    """x [heads, head_dim] rotated in the half-split convention by cos / sin [head_dim / 2]."""
+def rope_apply(x, cos, sin, tier: int = 0) -> np.ndarray:
+    """x [heads, head_dim] rotated in the half-split convention by cos / sin [head_dim / 2].  The vectorised tier uses
+    separate multiplies and adds, so its result equals the scalar one bit for bit."""
     xv = np.array(x, dtype=np.float32, copy=True, order="C")
     c, s = _f32(cos), _f32(sin)
     if xv.ndim != 2 or c.size != xv.shape[1] // 2 or s.size != c.size:
         raise DimensionMismatch("need x [heads, head_dim] and cos / sin [head_dim / 2]")
-    _lib().bcpu_rope_apply(xv.ctypes.data, xv.shape[0], xv.shape[1], c.ctypes.data, s.ctypes.data)
+    _lib().bcpu_rope_apply_t(xv.ctypes.data, xv.shape[0], xv.shape[1], c.ctypes.data, s.ctypes.data, int(tier))
     return xv
 
 

@@ -164,3 +164,32 @@ def test_strategy_tiles_packing_and_prefetch_helpers():
     assert np.array_equal(CK.pack_rows_tiled(G.TQ2_0_G128, packed, rows, cols, tile=32, unpack=True), q.reshape(-1))
     CK.prefetch_range(q, locality=1)
     CK.prefetch_range(np.zeros(1000, np.float32), locality=3, write=True)     # hints only: nothing observable, must not fault
+
+
+def test_vectorised_float_ops_agree_with_the_scalar_bodies():
+    """SiLU / SwiGLU / softmax with the polynomial exp agree with the scalar bodies to rounding (relative 1e-6); the rotation
+    uses the same multiplies and adds and is equal bit for bit.  Lengths that are not multiples of the vector width and
+    extreme arguments are included."""
+    rng = np.random.default_rng(3)
+    for n in (1, 7, 8, 9, 64, 1000, 4099):
+        x = (rng.normal(size=n) * 4).astype(np.float32)
+        up = rng.normal(size=n).astype(np.float32)
+        np.testing.assert_allclose(CK.silu(x, tier=1), CK.silu(x, tier=0), rtol=2e-6, atol=1e-7)
+        np.testing.assert_allclose(CK.swiglu(x, up, tier=1), CK.swiglu(x, up, tier=0), rtol=2e-6, atol=1e-7)
+        a, b = CK.softmax(x, tier=1), CK.softmax(x, tier=0)
+        np.testing.assert_allclose(a, b, rtol=3e-6, atol=1e-9)
+        assert abs(float(a.sum()) - 1.0) < 1e-5
+    extreme = np.array([-200.0, -88.0, -30.0, 0.0, 30.0, 88.0, 200.0, -0.0, 1e-8], dtype=np.float32)
+    s1, s0 = CK.silu(extreme, tier=1), CK.silu(extreme, tier=0)
+    assert np.all(np.isfinite(s1)) and np.allclose(s1, s0, rtol=1e-5, atol=1e-30)
+    sm = CK.softmax(np.array([1000.0, 999.0, -1000.0] * 5, dtype=np.float32), tier=1)
+    assert np.all(np.isfinite(sm)) and abs(sm.sum() - 1.0) < 1e-5 and sm[2] < 1e-30      # (the vector body clamps exp at e^-87)
+    # against float64 references
+    x = (rng.normal(size=513) * 3).astype(np.float32)
+    ref = x.astype(np.float64) / (1.0 + np.exp(-x.astype(np.float64)))
+    assert np.abs(CK.silu(x, tier=1) - ref).max() < 2e-6
+    for heads, hd in ((1, 64), (4, 128), (3, 20), (2, 6)):
+        v = rng.normal(size=(heads, hd)).astype(np.float32)
+        ang = rng.uniform(0, 6.28, size=hd // 2)
+        c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+        assert np.array_equal(CK.rope_apply(v, c, s, tier=1), CK.rope_apply(v, c, s, tier=0))
