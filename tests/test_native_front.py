@@ -453,3 +453,39 @@ run_server("native", int(sys.argv[1]), 4, 20.0)
     finally:
         if child.poll() is None:
             child.kill()
+
+
+def test_python_driven_streams_and_errors_pass_through_the_bridge():
+    """A backend without completion callbacks streams through the application's own SSE generator: the bridge forwards its
+    chunks with chunked framing; an application error before the response starts becomes a 500; the connection survives."""
+    from test_server import FakeBackend
+    from oxibonsai_b200.server.app import create_app
+    from oxibonsai_b200.server.config import ServerConfig
+    tok = ByteTokenizer()
+    app = create_app(FakeBackend("héllo wörld"), tok, ServerConfig())
+
+    @app.get("/boom")
+    async def boom():
+        raise RuntimeError("kaput")
+
+    front, stop, thread = _serve_app(app, tok)
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", front.port, timeout=20)
+        c.request("POST", "/v1/chat/completions", body=json.dumps({"messages": [{"role": "user", "content": "x"}], "stream": True, "max_tokens": 64}),
+                  headers={"Content-Type": "application/json"})
+        r = c.getresponse()
+        evs = _events(r.read().decode())
+        assert r.status == 200 and r.getheader("transfer-encoding") == "chunked" and evs[-1] == "[DONE]"
+        assert "".join(e["choices"][0]["delta"].get("content", "") for e in evs[:-1]) == "héllo wörld"
+        assert front.stats()["stream_tokens"] == 0                      # not a native stream: the application produced the events
+        c.request("GET", "/boom")
+        r = c.getresponse()
+        assert r.status == 500 and r.read()
+        c.request("GET", "/v1/models")
+        assert json.loads(c.getresponse().read())["data"][0]["id"] == "fake-bonsai"
+        c.request("GET", "/nowhere")
+        assert c.getresponse().status == 404
+    finally:
+        stop.set()
+        thread.join(5)
+        front.close()
