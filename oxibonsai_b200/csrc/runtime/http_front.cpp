@@ -61,6 +61,7 @@ struct Conn {
     bool want_write = false;            // EPOLLOUT registered
     bool continued = false;             // "100 Continue" already sent for the request being read
     bool head_only = false;             // the request being answered is a HEAD: headers as for GET, no body bytes
+    bool http10 = false;                // the request came as HTTP/1.0: no chunked framing, the body ends with the connection
     Clock::time_point last_io = Clock::now();   // last byte received or sent (I/O thread only)
     int64_t stream = 0;
     std::string peer;
@@ -75,6 +76,7 @@ struct Stream {
     std::string held;                   // decoded bytes not sent yet: incomplete UTF-8 or a possible start of a stop sequence
     std::string early;                  // framed events produced before the response head was written
     bool begun = false;
+    bool raw = false;                   // HTTP/1.0 client: events go out unframed and the connection is closed at the end
     int state = LIVE;
     Clock::time_point deadline;
     bool has_deadline = false;
@@ -255,7 +257,11 @@ static bool queue_out(Front* f, Conn* c, const char* data, size_t n) {
     return true;
 }
 
-static void append_chunk(std::string& out, const std::string& payload) {
+static void append_chunk(std::string& out, const std::string& payload, bool raw = false) {
+    if (raw) {
+        out += payload;
+        return;
+    }
     char len[24];
     int k = snprintf(len, sizeof len, "%zx\r\n", payload.size());
     out.append(len, size_t(k));
@@ -274,7 +280,7 @@ static void stream_event_text(Stream* s, const char* text, size_t n, std::string
     utf8_sanitize(text, n, clean);
     json_escape(clean.data(), clean.size(), ev);
     ev += s->chat ? "\"}, \"finish_reason\": null}]}\n\n" : "\", \"finish_reason\": null}]}\n\n";
-    append_chunk(framed, ev);
+    append_chunk(framed, ev, s->raw);
     s->events++;
 }
 
@@ -474,6 +480,7 @@ static bool try_parse(Front* f, Conn* c) {
         c->keep_alive = keep;
         c->continued = false;
         c->head_only = e.method == "HEAD";
+        c->http10 = http10;
         c->state = DISPATCHED;
         f->n_requests++;
         f->events.push_back(std::move(e));
@@ -822,7 +829,8 @@ int bfront_respond_start(void* h, int64_t conn, int status, const char* headers)
     int k = snprintf(line, sizeof line, "HTTP/1.1 %d %s\r\n", status, reason(status));
     std::string head(line, size_t(k));
     head += headers ? headers : "";
-    head += "transfer-encoding: chunked\r\n";
+    if (c->http10) c->keep_alive = false;                   // the end of the body is the end of the connection
+    else head += "transfer-encoding: chunked\r\n";
     if (!c->keep_alive) head += "connection: close\r\n";
     head += "\r\n";
     c->state = RESPONDING;
@@ -839,7 +847,7 @@ int bfront_respond_chunk(void* h, int64_t conn, const uint8_t* data, uint64_t n)
     if (it == f->conns.end() || it->second->state != RESPONDING) return -1;
     if (it->second->head_only) return 0;
     std::string framed;
-    append_chunk(framed, std::string(reinterpret_cast<const char*>(data), size_t(n)));
+    append_chunk(framed, std::string(reinterpret_cast<const char*>(data), size_t(n)), it->second->http10);
     bool ok = queue_out(f, it->second.get(), framed.data(), framed.size());
     wake_io(f);
     return ok ? 0 : -1;
@@ -851,7 +859,7 @@ int bfront_respond_end(void* h, int64_t conn) {
     auto it = f->conns.find(conn);
     if (it == f->conns.end() || it->second->state != RESPONDING) return -1;
     Conn* c = it->second.get();
-    if (!c->head_only) queue_out(f, c, "0\r\n\r\n", 5);
+    if (!c->head_only && !c->http10) queue_out(f, c, "0\r\n\r\n", 5);
     response_done(f, c);
     wake_io(f);
     return 0;
@@ -883,7 +891,8 @@ int64_t bfront_stream_open(void* h, int64_t conn, const char* chunk_head, int ch
             off += len;
         }
     }
-    if (first_event && *first_event) append_chunk(s->early, first_event);
+    s->raw = it->second->http10;
+    if (first_event && *first_event) append_chunk(s->early, first_event, s->raw);
     if (timeout_ms > 0) {
         s->deadline = Clock::now() + std::chrono::milliseconds(timeout_ms);
         s->has_deadline = true;
@@ -915,7 +924,8 @@ int bfront_stream_begin(void* h, int64_t stream, const char* headers) {
     Conn* c = it->second.get();
     std::string head = "HTTP/1.1 200 OK\r\n";
     head += headers ? headers : "";
-    head += "transfer-encoding: chunked\r\n";
+    if (c->http10) c->keep_alive = false;
+    else head += "transfer-encoding: chunked\r\n";
     if (!c->keep_alive) head += "connection: close\r\n";
     head += "\r\n";
     c->state = STREAMING;
@@ -985,7 +995,7 @@ int64_t bfront_stream_finish(void* h, int64_t stream, const char* finish_reason,
         utf8_sanitize(error, strlen(error), clean);
         json_escape(clean.data(), clean.size(), ev);
         ev += "\", \"type\": \"server_error\"}}\n\n";
-        append_chunk(framed, ev);
+        append_chunk(framed, ev, s->raw);
     } else {
         bool stop_hit = s->state == STOP_HIT;
         if (!stop_hit && !s->held.empty()) stream_event_text(s, s->held.data(), s->held.size(), framed);
@@ -996,10 +1006,10 @@ int64_t bfront_stream_finish(void* h, int64_t stream, const char* finish_reason,
         const char* fr = stop_hit ? "stop" : (finish_reason && *finish_reason ? finish_reason : "stop");
         json_escape(fr, strlen(fr), ev);
         ev += "\"}]}\n\n";
-        append_chunk(framed, ev);
-        append_chunk(framed, "data: [DONE]\n\n");
+        append_chunk(framed, ev, s->raw);
+        append_chunk(framed, "data: [DONE]\n\n", s->raw);
     }
-    framed += "0\r\n\r\n";
+    if (!s->raw) framed += "0\r\n\r\n";
     bool was_live_conn = s->state != CLIENT_GONE;
     stream_emit(f, s, framed);
     s->state = FINISHED;

@@ -489,3 +489,29 @@ def test_python_driven_streams_and_errors_pass_through_the_bridge():
         stop.set()
         thread.join(5)
         front.close()
+
+
+def test_http10_clients_get_unframed_streams_that_end_with_the_connection(front):
+    def script(f, conn):
+        s = f.open_stream(conn, HEAD, False, [], "", 0)
+        s.begin([(b"content-type", b"text/event-stream")])
+        for t in b"ok":
+            s.push(t)
+        s.finish("stop")
+
+    _Echo(front, script).start()
+    s = socket.create_connection(("127.0.0.1", front.port))
+    s.sendall(b"GET /stream HTTP/1.0\r\nHost: x\r\n\r\n")
+    data = b""
+    while chunk := s.recv(65536):
+        data += chunk
+    head, _, body = data.partition(b"\r\n\r\n")
+    assert b"transfer-encoding" not in head.lower() and b"connection: close" in head
+    evs = _events(body.decode())                               # no chunk sizes between the events
+    assert [e["choices"][0]["text"] for e in evs[:-1]] == ["o", "k", ""] and evs[-1] == "[DONE]" and body.startswith(b"data: ")
+    s = socket.create_connection(("127.0.0.1", front.port))
+    s.sendall(b"GET /plain HTTP/1.0\r\n\r\n")
+    data = b""
+    while chunk := s.recv(65536):
+        data += chunk
+    assert data.startswith(b"HTTP/1.1 200 OK") and b"content-length" in data and b'"target": "/plain"' in data
