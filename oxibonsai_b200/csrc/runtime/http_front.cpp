@@ -452,21 +452,77 @@ static bool try_parse(Front* f, Conn* c) {
             }
             pos = eol + 2;
         }
-        if (chunked) {
-            simple_response(f, c, 501, "chunked request bodies are not supported; send content-length");
-            return true;
-        }
         if (content_length > kMaxBody) {
             simple_response(f, c, 413, "body too large");
             return true;
         }
-        size_t total = he + 4 + content_length;
-        if (c->in.size() < total) {
+        auto want_more = [&]() {                         // the request is not complete yet
             if (expect && !c->continued) {
                 c->out += "HTTP/1.1 100 Continue\r\n\r\n";
                 c->continued = true;
             }
-            return true;
+        };
+        std::string body;
+        size_t total;
+        if (chunked) {
+            // chunked transfer coding: "<hex size>[;extensions]\r\n<data>\r\n" ... "0\r\n" [trailers] "\r\n"
+            size_t q = he + 4;
+            bool done = false, bad = false;
+            while (!done) {
+                size_t eol = c->in.find("\r\n", q);
+                if (eol == std::string::npos) break;
+                size_t size = 0, digits = 0;
+                for (size_t i = q; i < eol && p[i] != ';'; ++i) {
+                    const char ch = p[i];
+                    int v = ch >= '0' && ch <= '9' ? ch - '0' : ch >= 'a' && ch <= 'f' ? ch - 'a' + 10 : ch >= 'A' && ch <= 'F' ? ch - 'A' + 10 : -1;
+                    if (v < 0 || ++digits > 8) {
+                        bad = true;
+                        break;
+                    }
+                    size = size * 16 + size_t(v);
+                }
+                if (bad || digits == 0 || body.size() + size > kMaxBody) {
+                    bad = true;
+                    break;
+                }
+                if (size == 0) {                                     // last chunk: skip the trailer section up to the blank line
+                    size_t t = eol + 2;
+                    while (true) {
+                        size_t e2 = c->in.find("\r\n", t);
+                        if (e2 == std::string::npos) break;
+                        if (e2 == t) {
+                            q = e2 + 2;
+                            done = true;
+                            break;
+                        }
+                        t = e2 + 2;
+                    }
+                    break;
+                }
+                if (c->in.size() < eol + 2 + size + 2) break;
+                if (p[eol + 2 + size] != '\r' || p[eol + 2 + size + 1] != '\n') {
+                    bad = true;
+                    break;
+                }
+                body.append(p + eol + 2, size);
+                q = eol + 2 + size + 2;
+            }
+            if (bad) {
+                simple_response(f, c, body.size() > kMaxBody / 2 ? 413 : 400, "malformed chunked body");
+                return true;
+            }
+            if (!done) {
+                want_more();
+                return true;
+            }
+            total = q;
+        } else {
+            total = he + 4 + content_length;
+            if (c->in.size() < total) {
+                want_more();
+                return true;
+            }
+            body.assign(p + he + 4, content_length);
         }
         Event e;
         e.kind = 1;
@@ -474,7 +530,7 @@ static bool try_parse(Front* f, Conn* c) {
         e.method = std::move(method);
         e.target = std::move(target);
         e.headers.assign(p + le + 2, he + 2 - (le + 2));
-        e.body.assign(p + he + 4, content_length);
+        e.body = std::move(body);
         e.peer = c->peer;
         c->in.erase(0, total);
         c->keep_alive = keep;

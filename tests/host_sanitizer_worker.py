@@ -142,7 +142,10 @@ def main() -> None:
     import random
     fuzz = random.Random(5)
     valid = b"POST /v1/x?y=1 HTTP/1.1\r\nHost: a\r\nContent-Length: 12\r\nExpect: 100-continue\r\nConnection: keep-alive\r\n\r\nhello world!"
-    for i in range(150):
+    chunky = b"POST /c HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\n5;x=y\r\nhello\r\n1a\r\nabcdefghijklmnopqrstuvwxyz\r\n0\r\nT: v\r\n\r\n"
+    for i in range(240):
+        if i >= 150:
+            valid = chunky
         kind = i % 4
         if kind == 0:
             payload = bytes(fuzz.randrange(256) for _ in range(fuzz.randint(1, 400)))

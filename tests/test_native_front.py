@@ -81,6 +81,15 @@ def test_requests_keep_alive_pipelining_and_errors(front):
     while chunk := s.recv(65536):
         data += chunk
     assert data.count(b"HTTP/1.1 200 OK") == 2 and data.index(b"/one") < data.index(b"/two") and b"connection: close" in data
+    # a chunked request body (with a chunk extension and a trailer), sent in two pieces, then a second request on the same connection
+    s = socket.create_connection(("127.0.0.1", front.port))
+    s.sendall(b"POST /chunked HTTP/1.1\r\nHost: x\r\nTransfer-Encoding: chunked\r\n\r\n5;ext=1\r\nhello\r\n")
+    time.sleep(0.05)
+    s.sendall(b"6\r\n world\r\n0\r\nX-Trailer: v\r\n\r\nGET /after-chunked HTTP/1.1\r\nConnection: close\r\n\r\n")
+    data = b""
+    while chunk := s.recv(65536):
+        data += chunk
+    assert b'"target": "/chunked", "body": 11' in data and b'"target": "/after-chunked"' in data
     # Expect: 100-continue is answered before the body is sent
     s = socket.create_connection(("127.0.0.1", front.port))
     s.sendall(b"POST /e HTTP/1.1\r\nHost: x\r\nContent-Length: 4\r\nExpect: 100-continue\r\n\r\n")
@@ -89,14 +98,15 @@ def test_requests_keep_alive_pipelining_and_errors(front):
     assert b'"body": 4' in s.recv(65536)
     s.close()
     for bad, status in ((b"NONSENSE\r\n\r\n", b"400"), (b"GET / HTTP/1.1\r\nContent-Length: x\r\n\r\n", b"400"),
-                        (b"POST / HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\n", b"501"),
+                        (b"POST / HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\nzz\r\nabc\r\n0\r\n\r\n", b"400"),
+                        (b"POST / HTTP/1.1\r\nTransfer-Encoding: chunked\r\n\r\n3\r\nabcXX0\r\n\r\n", b"400"),
                         (b"POST / HTTP/1.1\r\nContent-Length: 3\r\nContent-Length: 5\r\n\r\nabcde", b"400"), (b"GET / HTTP/1.1\r\nA: " + b"a" * 70000 + b"\r\n\r\n", b"431")):
         s = socket.create_connection(("127.0.0.1", front.port))
         s.sendall(bad)
         assert s.recv(200).split(b" ")[1] == status
         s.close()
     st = front.stats()
-    assert st["requests"] == 7 and st["connections_accepted"] == 8
+    assert st["requests"] == 9 and st["connections_accepted"] == 10
 
 
 def _reference_stream(tokens, stops):
