@@ -165,6 +165,8 @@ def model_info(path: str) -> dict:
             "estimated_parameters": card.estimated_param_count(), "file_size_bytes": os.path.getsize(path),
             "config": {"layers": cfg.layers, "hidden": cfg.hidden, "heads": cfg.heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
                        "intermediate": cfg.inter, "vocab": cfg.vocab, "context": cfg.context, "rope_base": cfg.rope_base, "rms_eps": cfg.eps},
+            "embedded_tokenizer": ({"model": f.metadata.get("tokenizer.ggml.model"), "tokens": len(f.metadata.get("tokenizer.ggml.tokens") or []),
+                                    "merges": len(f.metadata.get("tokenizer.ggml.merges") or [])} if f.metadata.get("tokenizer.ggml.tokens") else None),
             "valid": v.ok, "errors": v.errors, "warnings": v.warnings, "compat": build_compat_report(f).summary()}
 
 
@@ -176,7 +178,9 @@ def cmd_info(args) -> int:
         from .core import GgufFile
         from .core.compat import extract_model_card
         print(extract_model_card(GgufFile.open(args.model), info["file_size_bytes"]).to_markdown())
-        print(f"variant: {info['variant']}\nGPU engine: {info['gpu_engine']}\n{info['compat']}")
+        et = info["embedded_tokenizer"]
+        print(f"variant: {info['variant']}\nGPU engine: {info['gpu_engine']}\n"
+              f"embedded tokenizer: {'none' if et is None else '%s, %d tokens, %d merges' % (et['model'], et['tokens'], et['merges'])}\n{info['compat']}")
     return 0
 
 
