@@ -114,6 +114,7 @@ class ConvertStats:
     bytes_in: int = 0
     bytes_out: int = 0
     tied: bool = False
+    tokenizer_tokens: int = 0          # size of the vocabulary copied into the file's metadata (0: none found)
 
 
 def _shards(src: str) -> list[str]:
@@ -135,7 +136,7 @@ def _hf_config(src: str) -> dict:
 
 
 def convert_safetensors_to_gguf(src: str, dst: str, quant: str = "tq2_0_g128", quantize_embeddings: bool = True,
-                                key_prefix: str = "llm", name: str | None = None) -> ConvertStats:
+                                key_prefix: str = "llm", name: str | None = None, embed_tokenizer: bool = True) -> ConvertStats:
     """Converts a Hugging Face Qwen3 checkpoint (a directory of shards or a single file) to GGUF.
 
     ``quantize_embeddings=True`` reproduces the reference (embedding table and LM head in the block format too);
@@ -205,6 +206,45 @@ def convert_safetensors_to_gguf(src: str, dst: str, quant: str = "tq2_0_g128", q
     w.add(f"{p}.rope.freq_base", float(cfg.get("rope_theta", 1e6)))
     w.add(f"{p}.context_length", int(cfg.get("max_position_embeddings", 32768)))
     w.add(f"{p}.vocab_size", int(cfg.get("vocab_size", seen.get("token_embd.weight", (0, 0))[1])))
+    if embed_tokenizer:
+        stats.tokenizer_tokens = embed_tokenizer_metadata(w, src)
     w.write(dst)
     return stats
+
+
+def embed_tokenizer_metadata(w: "G.GgufWriter", src: str) -> int:
+    """Copies a byte-level BPE ``tokenizer.json`` found beside the checkpoint into the GGUF metadata (``tokenizer.ggml.model``
+    "gpt2", ``tokens``, ``token_type`` with 3 for added / special tokens, ``merges``, ``pre``, ``eos`` / ``bos_token_id``), so
+    that the converted file needs no side file.  Returns the number of tokens written (0: no usable tokenizer found)."""
+    folder = src if os.path.isdir(src) else os.path.dirname(os.path.abspath(src))
+    path = os.path.join(folder, "tokenizer.json")
+    if not os.path.exists(path):
+        return 0
+    try:
+        with open(path, encoding="utf-8") as f:
+            j = json.load(f)
+        model = j["model"]
+        if model.get("type", "BPE") != "BPE":
+            return 0
+        vocab: dict[str, int] = dict(model["vocab"])
+        added = {t["content"]: int(t["id"]) for t in j.get("added_tokens", [])}
+        size = 1 + max(list(vocab.values()) + list(added.values()))
+        tokens, types = [f"[PAD{i}]" for i in range(size)], [5] * size          # 5 = unused id
+        for t, i in vocab.items():
+            tokens[i], types[i] = t, 1
+        for t, i in added.items():
+            tokens[i], types[i] = t, 3
+        merges = [m if isinstance(m, str) else " ".join(m) for m in model.get("merges", [])]
+    except (KeyError, ValueError, TypeError, OSError):
+        return 0
+    w.add("tokenizer.ggml.model", "gpt2")
+    w.add("tokenizer.ggml.pre", "qwen2" if "Split" in json.dumps(j.get("pre_tokenizer")) else "default")
+    w.add("tokenizer.ggml.tokens", tokens)
+    w.add("tokenizer.ggml.token_type", types)
+    w.add("tokenizer.ggml.merges", merges)
+    for key, names in (("eos", ("<|im_end|>", "<|endoftext|>", "</s>")), ("bos", ("<|begin_of_text|>", "<s>"))):
+        tid = next((added[n] for n in names if n in added), None)
+        if tid is not None:
+            w.add(f"tokenizer.ggml.{key}_token_id", tid)
+    return size
 

@@ -348,6 +348,21 @@ def test_safetensors_to_gguf_conversion_roundtrip(tmp_path):
     assert g.metadata["llm.block_count"] == 2 and g.tensor_info("output.weight").type == G.TQ2_0_G128 and g.config().hidden == h
     with pytest.raises(ValueError):
         CV.convert_safetensors_to_gguf(str(d), out, quant="q9")
+    # a tokenizer.json beside the checkpoint travels into the GGUF metadata: the converted file is self-contained
+    assert st.tokenizer_tokens == 0 and "tokenizer.ggml.tokens" not in f.metadata
+    from oxibonsai_b200 import tokenizer as T
+    from oxibonsai_b200.tokenizer.extras import save_bpe_text                                   # noqa: F401 - (the text format is not the HF one)
+    tok = T.train_bpe(["the quick brown fox " * 10, "héllo wörld " * 10], 290, special_tokens=["<|endoftext|>", "<|im_end|>"])
+    hf = {"model": {"type": "BPE", "vocab": tok.vocab, "merges": [f"{tok.id_to_token[a]} {tok.id_to_token[b]}" for a, b, _ in tok.merges]},
+          "added_tokens": [{"id": i, "content": c, "special": True} for c, i in tok.special.items()],
+          "pre_tokenizer": {"type": "ByteLevel"}, "decoder": {"type": "ByteLevel"}}
+    (d / "tokenizer.json").write_text(json.dumps(hf))
+    st3 = CV.convert_safetensors_to_gguf(str(d), str(tmp_path / "with_tok.gguf"), key_prefix="qwen3")
+    assert st3.tokenizer_tokens == tok.vocab_size
+    emb = T.BpeTokenizer.from_gguf(str(tmp_path / "with_tok.gguf"))
+    text = "the quick héllo<|im_end|>"
+    assert emb.encode(text) == tok.encode(text) and emb.decode(emb.encode(text)) == text and emb.eos_token_id == tok.special["<|im_end|>"]
+    assert CV.convert_safetensors_to_gguf(str(d), str(tmp_path / "no_tok.gguf"), embed_tokenizer=False).tokenizer_tokens == 0
 
 
 def test_host_kv_caches_and_layer_stats(tiny_gguf):
