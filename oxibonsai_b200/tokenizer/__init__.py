@@ -92,6 +92,10 @@ class BpeTokenizer:
         import regex
         self.vocab = dict(vocab)
         self.special = dict(special_tokens or {})
+        # the token that ends an assistant turn, where the vocabulary names one (chat models end turns with <|im_end|> /
+        # <|eot_id|>, base models documents with <|endoftext|> / </s>)
+        self.eos_token_id: int | None = next((self.special[n] for n in ("<|im_end|>", "<|eot_id|>", "<|endoftext|>", "</s>", "<EOS>") if n in self.special), None)
+        self.bos_token_id: int | None = next((self.special[n] for n in ("<|begin_of_text|>", "<s>", "<BOS>") if n in self.special), None)
         self.id_to_token = {i: t for t, i in {**self.vocab, **self.special}.items()}
         self.vocab_size = max(self.id_to_token) + 1 if self.id_to_token else 0
         self._split = regex.compile(split_pattern)
@@ -193,8 +197,10 @@ class BpeTokenizer:
         pre = str(md.get("tokenizer.ggml.pre") or "")
         tok = cls(vocab, merges, special, cls.QWEN_SPLIT if pre.startswith("qwen") else _GPT2_SPLIT)
         tok.normal_form = "NFC" if pre.startswith("qwen") else None
-        tok.eos_token_id = md.get("tokenizer.ggml.eos_token_id")
-        tok.bos_token_id = md.get("tokenizer.ggml.bos_token_id")
+        if md.get("tokenizer.ggml.eos_token_id") is not None:
+            tok.eos_token_id = int(md["tokenizer.ggml.eos_token_id"])
+        if md.get("tokenizer.ggml.bos_token_id") is not None:
+            tok.bos_token_id = int(md["tokenizer.ggml.bos_token_id"])
         return tok
 
     def _encode_piece(self, piece: str) -> list[int]:
