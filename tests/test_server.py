@@ -145,7 +145,8 @@ def test_metrics_embeddings_admin(client):
     assert ws["kv_cache"]["level"] == "fp16" and ws["kv_cache"]["memory_factor"] == 1.0 and ws["kv_cache"]["samples"] == 1
     assert client.post("/admin/reset-metrics").json() == {"status": "ok"}
     assert "oxibonsai_requests_total 0" in client.get("/metrics").text
-    assert "<html>" in client.get("/ui").text
+    ui = client.get("/ui").text
+    assert "<html" in ui and "/v1/chat/completions" in ui and "getReader" in ui          # the page streams from the chat route
 
 
 def test_config_layering_and_validation(tmp_path):
