@@ -394,7 +394,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             if completed:
                 breaker.record_success()
 
-    async def native_stream(handle, chat: bool, prompt_ids, params, max_tokens, rid, stops, extra, obj_id, created, model):
+    async def native_stream(handle, chat: bool, prompt_ids, params, max_tokens, rid, stops, extra, obj_id, created, model, echo: str = ""):
         loop = asyncio.get_running_loop()
         await sem.acquire()
         if not breaker.allow():
@@ -408,6 +408,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         if chat:
             first = "data: " + json.dumps({"id": obj_id, "object": kind, "created": created, "model": model,
                                            "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
+        elif echo:
+            first = f'data: {head}"text": {json.dumps(echo)}, "finish_reason": null}}]}}\n\n'
         try:
             stream = handle.open_stream(head, chat, stops, first, cfg.request_timeout_ms)
         except ConnectionError:
@@ -530,6 +532,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             metrics.errors.inc()
             return error(400, str(e), rid=rid)
 
+        # completions only: the prompt comes back in front of the generated text (reference: ``echo``, completions.rs:88)
+        echo = prompt if (not chat and body.get("echo")) else ""
         created = int(time.time())
         obj_id = ("chatcmpl-" if chat else "cmpl-") + rid[:24]
         model = body.get("model") or backend.model_name
@@ -557,7 +561,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
         if body.get("stream") and front is not None and front.front.has_vocab and getattr(backend, "supports_on_done", False):
             # Behind the native front the stream never comes back through this coroutine: sampled token ids go from the
             # scheduler's thread straight into the front, which detokenises, holds back stop sequences, frames and writes.
-            return await native_stream(front, chat, prompt_ids, params, max_tokens, rid, stops, extras(), obj_id, created, model)
+            return await native_stream(front, chat, prompt_ids, params, max_tokens, rid, stops, extras(), obj_id, created, model, echo)
 
         if body.get("stream"):
             async def sse():
@@ -571,6 +575,8 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                         # the fixed part of every chunk is serialised once; per token only the text is encoded
                         head_json = (f'data: {{"id": {json.dumps(obj_id)}, "object": "{"chat.completion.chunk" if chat else "text_completion"}", '
                                      f'"created": {created}, "model": {json.dumps(model)}, "choices": [{{"index": 0, ')
+                        if echo:
+                            yield f'{head_json}"text": {json.dumps(echo)}, "finish_reason": null}}]}}\n\n'
                         async for delta, fin in run_generation(prompt_ids, params, max_tokens, rid, stops, extras()):
                             if not (delta or fin):
                                 continue
@@ -609,7 +615,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                                 fin = "tool_calls"
                         choices.append({"index": i, "message": msg, "finish_reason": fin, **({"logprobs": lpj} if lpj else {})})
                     else:
-                        choices.append({"index": i, "text": text, "finish_reason": fin, **({"logprobs": lpj} if lpj else {})})
+                        choices.append({"index": i, "text": echo + text, "finish_reason": fin, **({"logprobs": lpj} if lpj else {})})
         except TimeoutError as e:
             metrics.errors.inc()
             return error(504, str(e), "timeout", rid)

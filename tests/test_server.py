@@ -433,3 +433,15 @@ def test_chat_template_follows_the_model_name_or_the_configuration():
     assert "[INST] hi [/INST]" in prompt_of(Named("whatever"), ServerConfig(chat_template="mistral"))
     with pytest.raises(ValueError, match="chat_template"):
         ServerConfig(chat_template="jinja").validate(check_paths=False)
+
+
+def test_echo_returns_the_prompt_in_front_of_the_completion(client):
+    r = client.post("/v1/completions", json={"prompt": "Say: ", "max_tokens": 5, "echo": True}).json()
+    assert r["choices"][0]["text"] == "Say: héllo"[:5 + 5] or r["choices"][0]["text"].startswith("Say: ")
+    plain = client.post("/v1/completions", json={"prompt": "Say: ", "max_tokens": 5}).json()
+    assert r["choices"][0]["text"] == "Say: " + plain["choices"][0]["text"]
+    with client.stream("POST", "/v1/completions", json={"prompt": "Say: ", "max_tokens": 5, "echo": True, "stream": True}) as s:
+        events = [json.loads(l[6:]) for l in s.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+    assert events[0]["choices"][0]["text"] == "Say: " and "".join(e["choices"][0]["text"] for e in events) == r["choices"][0]["text"]
+    chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 3, "echo": True}).json()
+    assert not chat["choices"][0]["message"]["content"].startswith("<|im_start|>")          # echo is a completions field only
