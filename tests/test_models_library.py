@@ -420,3 +420,19 @@ def test_nvtx_ranges_are_off_by_default_and_nest():
     nvtx.pop(False)
     with nvtx.range("nothing happens on CPU when off"):
         pass
+
+
+def test_package_facade_resolves_lazily():
+    """``import oxibonsai_b200`` imports nothing heavy; every advertised name resolves to the object of its home module."""
+    import subprocess
+    import sys
+    code = ("import sys, oxibonsai_b200 as ob\n"
+            "assert 'torch' not in sys.modules and 'numpy' not in sys.modules\n"
+            "missing = [n for n in ob.__all__ if not hasattr(ob, n)]\n"
+            "assert not missing, missing\n"
+            "from oxibonsai_b200.runtime.presets import SamplingParams\n"
+            "assert ob.SamplingParams is SamplingParams and 'EngineBuilder' in dir(ob)\n"
+            "try:\n    ob.nothing_here\nexcept AttributeError as e:\n    assert 'nothing_here' in str(e)\nelse:\n    raise SystemExit(1)\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stderr[-2000:]
