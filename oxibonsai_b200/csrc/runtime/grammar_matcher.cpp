@@ -71,7 +71,7 @@ struct Grammar {
   std::mutex mu;
   std::unordered_map<MaskKey, std::shared_ptr<std::vector<uint32_t>>, MaskKeyHash> masks;
   uint64_t hits = 0, misses = 0;
-  size_t cap = 4096;
+  size_t cap_bytes = 32u << 20;        // finished masks kept per grammar (a 152 K-token mask is 19 KB: about 1700 states)
   // Lazily built automaton over chart signatures: (signature, byte) -> signature after the byte, and the bytes a signature
   // can scan.  A signature stands for everything that can still follow, so once a transition has been seen the trie walk
   // takes it without touching the chart; only unseen transitions run the recogniser.
@@ -340,7 +340,7 @@ uint32_t walk(Matcher& m, const TokenTable& t, uint32_t* mask) {
   m.depth = w.root_depth;
   m.dead = false;
   std::unique_lock<std::shared_mutex> wr(g.tmu);
-  if (g.trans.size() + w.new_trans.size() > (1u << 21)) {          // a plain bound on the automaton
+  if (g.trans.size() + w.new_trans.size() > (1u << 19)) {          // a plain bound on the automaton (tens of megabytes)
     g.trans.clear();
     g.info.clear();
   }
@@ -489,7 +489,7 @@ uint32_t bgram_matcher_mask(void* h, void* table, int32_t eos, uint32_t* mask, i
   }
   auto copy = std::make_shared<std::vector<uint32_t>>(mask, mask + words);
   std::lock_guard<std::mutex> lk(m.g->mu);
-  if (m.g->masks.size() >= m.g->cap) m.g->masks.clear();          // a plain bound: grammars rarely reach it
+  if ((m.g->masks.size() + 1) * size_t(words) * sizeof(uint32_t) > m.g->cap_bytes) m.g->masks.clear();      // a plain bound: grammars rarely reach it
   m.g->masks.emplace(key, std::move(copy));
   return allowed;
 }

@@ -93,11 +93,11 @@ class CompiledGrammar:
 
 _COMPILED: "OrderedDict[bytes, CompiledGrammar]" = OrderedDict()
 _COMPILED_LOCK = threading.Lock()
-_COMPILED_CAP = 64
+_COMPILED_CAP = 32
 
 
 def compile_cached(grammar: Grammar) -> CompiledGrammar:
-    """Structurally equal grammars share one compiled object, and with it the masks computed so far (an LRU of 64)."""
+    """Structurally equal grammars share one compiled object, and with it the masks computed so far (an LRU of 32; a grammar keeps at most 32 MB of masks)."""
     key = serialize(grammar).tobytes()
     with _COMPILED_LOCK:
         cg = _COMPILED.get(key)
