@@ -707,6 +707,12 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
                 for d in docs)
         return {"indexed_chunks": n, **app.state.rag.stats()}
 
+    @app.delete("/rag/index")
+    async def rag_clear():
+        # a fresh pipeline rather than an emptied one, so that a fitted embedder starts over too (rag_server.rs:456-474)
+        app.state.rag = RagPipeline()
+        return {"status": "cleared"}
+
     @app.post("/rag/query")
     async def rag_query(request: Request):
         body = await request.json()

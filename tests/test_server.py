@@ -172,6 +172,8 @@ def test_rag_routes_and_json_api(client):
     a = client.post("/rag/query", json={"query": "pines?", "generate": True, "max_tokens": 50}).json()
     assert a["answer"] == "héllo wörld" and a["usage"]["completion_tokens"] > 0
     assert client.get("/rag/stats").json()["chunks"] == 2 and client.post("/rag/query", json={}).status_code == 400
+    assert client.delete("/rag/index").json() == {"status": "cleared"} and client.get("/rag/stats").json()["chunks"] == 0
+    assert client.post("/rag/index", json={"text": "Maples turn red in autumn."}).json()["documents"] == 1
     from oxibonsai_b200.server.app import generate_json
     tok = ByteTokenizer()
     out = json.loads(generate_json(lambda ids, n: ids[:n], tok, json.dumps({"prompt": "abcdef", "max_tokens": 3})))
