@@ -281,33 +281,65 @@ class SearchHit:
 
 
 class VectorStore:
+    """Flat store: the vectors sit in one matrix that grows geometrically, with their norms beside them, so that indexing
+    and querying in turns costs no re-packing and a query is one matrix-vector product plus a partial sort."""
+
     def __init__(self, dim: int, distance: Distance = Distance.COSINE):
         self.dim, self.distance = dim, distance
-        self._vecs: list[np.ndarray] = []
+        self._buf = np.empty((0, dim), dtype=np.float32)
+        self._norms = np.empty(0, dtype=np.float32)
+        self._n = 0
         self.texts: list[str] = []
         self.metadata: list[dict] = []
-        self._matrix: np.ndarray | None = None
+
+    @property
+    def vectors(self) -> np.ndarray:
+        """The stored vectors as one [n, dim] view."""
+        return self._buf[:self._n]
 
     def add(self, vector: Sequence[float], text: str, metadata: dict | None = None) -> int:
         v = np.asarray(vector, dtype=np.float32)
         if v.shape != (self.dim,):
             raise ValueError(f"expected dimension {self.dim}, got {v.shape}")
-        self._vecs.append(v)
+        if self._n == len(self._buf):
+            cap = max(64, 2 * len(self._buf))
+            self._buf = np.concatenate([self._buf, np.empty((cap - self._n, self.dim), dtype=np.float32)])
+            self._norms = np.concatenate([self._norms, np.empty(cap - self._n, dtype=np.float32)])
+        self._buf[self._n] = v
+        self._norms[self._n] = np.linalg.norm(v)
+        self._n += 1
         self.texts.append(text)
         self.metadata.append(dict(metadata or {}))
-        self._matrix = None
-        return len(self._vecs) - 1
+        return self._n - 1
 
     def __len__(self) -> int:
-        return len(self._vecs)
+        return self._n
+
+    def clear(self) -> None:
+        self._buf, self._norms, self._n = np.empty((0, self.dim), dtype=np.float32), np.empty(0, dtype=np.float32), 0
+        self.texts.clear()
+        self.metadata.clear()
+
+    def _scores(self, q: np.ndarray) -> np.ndarray:
+        m = self.vectors
+        if self.distance == Distance.COSINE:                       # the stored norms save a pass over the matrix
+            n = self._norms[:self._n] * (np.linalg.norm(q) or 1.0)
+            return (m @ q) / np.where(n > 0, n, 1.0)
+        return self.distance.scores(m, q)
 
     def search(self, query: Sequence[float], k: int = 4, flt: MetadataFilter | None = None, min_score: float | None = None) -> list[SearchHit]:
-        if not self._vecs:
+        if self._n == 0 or k <= 0:
             return []
-        if self._matrix is None:
-            self._matrix = np.stack(self._vecs)
-        s = self.distance.scores(self._matrix, np.asarray(query, dtype=np.float32))
-        order = np.argsort(-s, kind="stable")
+        s = self._scores(np.asarray(query, dtype=np.float32))
+        # without a filter only the k best are ever looked at: select them first, sort those (ties by index, as a stable
+        # sort of the whole row would give them)
+        want = min(self._n, k if flt is None else self._n)
+        if want < self._n:
+            cut = np.partition(s, self._n - want)[self._n - want]
+            cand = np.flatnonzero(s >= cut)
+        else:
+            cand = np.arange(self._n)
+        order = cand[np.argsort(-s[cand], kind="stable")]
         out = []
         for i in order:
             if flt is not None and not flt.matches(self.metadata[i]):
@@ -320,14 +352,18 @@ class VectorStore:
         return out
 
     def remove(self, idx: int) -> None:
-        for l in (self._vecs, self.texts, self.metadata):
-            del l[idx]
-        self._matrix = None
+        if not -self._n <= idx < self._n:
+            raise IndexError(idx)
+        idx %= self._n
+        self._buf[idx:self._n - 1] = self._buf[idx + 1:self._n]
+        self._norms[idx:self._n - 1] = self._norms[idx + 1:self._n]
+        self._n -= 1
+        del self.texts[idx], self.metadata[idx]
 
     # JSON snapshots
     def to_json(self) -> str:
         return json.dumps({"version": 1, "dim": self.dim, "distance": self.distance.value, "entries": [
-            {"vector": [float(x) for x in v], "text": t, "metadata": m} for v, t, m in zip(self._vecs, self.texts, self.metadata)]})
+            {"vector": [float(x) for x in v], "text": t, "metadata": m} for v, t, m in zip(self.vectors, self.texts, self.metadata)]})
 
     @classmethod
     def from_json(cls, data: str) -> "VectorStore":

@@ -338,7 +338,7 @@ def to_score(d: Distance, value: float) -> float:
 
 
 def store_memory_bytes(store: VectorStore) -> int:
-    return sum(v.nbytes for v in store._vecs) + sum(len(t.encode("utf-8")) for t in store.texts) + sum(len(json.dumps(m)) for m in store.metadata)
+    return store.vectors.nbytes + sum(len(t.encode("utf-8")) for t in store.texts) + sum(len(json.dumps(m)) for m in store.metadata)
 
 
 def search_with_threshold(store: VectorStore, query: Sequence[float], k: int, threshold: float) -> list[SearchHit]:
@@ -346,10 +346,7 @@ def search_with_threshold(store: VectorStore, query: Sequence[float], k: int, th
 
 
 def clear_store(store: VectorStore) -> None:
-    store._vecs.clear()
-    store.texts.clear()
-    store.metadata.clear()
-    store._matrix = None
+    store.clear()
 
 
 # ---- retriever ----------------------------------------------------------------------------------------------------------------
