@@ -231,9 +231,13 @@ class Distance(Enum):
         if self == Distance.COSINE:
             n = np.linalg.norm(matrix, axis=1) * (np.linalg.norm(q) or 1.0)
             return (matrix @ q) / np.where(n > 0, n, 1.0)
-        if self == Distance.EUCLIDEAN:
-            return -np.linalg.norm(matrix - q[None, :], axis=1)
-        return -np.abs(matrix - q[None, :]).sum(1)
+        # the difference matrix is formed a cache-sized block of rows at a time (the whole of it is 100 MB at 100k x 256)
+        out = np.empty(len(matrix), dtype=np.float32)
+        step = max(1, (1 << 19) // max(1, matrix.shape[1]))
+        for a in range(0, len(matrix), step):
+            d = matrix[a:a + step] - q[None, :]
+            out[a:a + step] = -np.sqrt(np.einsum("ij,ij->i", d, d)) if self == Distance.EUCLIDEAN else -np.abs(d).sum(1)
+        return out
 
 
 @dataclass
