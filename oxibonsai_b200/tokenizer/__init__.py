@@ -38,7 +38,8 @@ def _declare():
     lib = _native.host()
     if "bbpe_new" not in lib._declared:
         _native.declare(lib, {"bbpe_new": (C.c_void_p, [C.c_void_p, C.c_uint64]), "bbpe_free": (None, [C.c_void_p]),
-                              "bbpe_merge": (C.c_uint64, [C.c_void_p, C.c_void_p, C.c_uint64])})
+                              "bbpe_merge": (C.c_uint64, [C.c_void_p, C.c_void_p, C.c_uint64]),
+                              "bbpe_encode": (C.c_uint64, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint64])})
         lib._declared.add("bbpe_new")
     return lib
 
@@ -103,6 +104,7 @@ class BpeTokenizer:
         self._b2u = bytes_to_unicode()
         self._u2b = {u: b for b, u in self._b2u.items()}
         self._byte_id = [self.vocab.get(self._b2u[b], -1) for b in range(256)]
+        self._byte_id_arr = np.asarray(self._byte_id, dtype=np.int32)
         trip = []
         for a, b in merges:
             ia, ib, im = self.vocab.get(a), self.vocab.get(b), self.vocab.get(a + b)
@@ -236,9 +238,22 @@ class BpeTokenizer:
                 if form:
                     import unicodedata
                     seg = unicodedata.normalize(form, seg)
-                for piece in self._split.findall(seg):
-                    out.extend(self._encode_piece(piece))
+                out.extend(self._encode_plain(seg))
         return out
+
+    def _encode_plain(self, seg: str) -> list[int]:
+        """Splits a segment without special tokens and merges all of its pieces in one native call."""
+        pieces = self._split.findall(seg) if not self._split.groups else [m.group() for m in self._split.finditer(seg)]
+        if not pieces:
+            return []
+        raw = "".join(pieces).encode("utf-8")                      # == seg for a pattern that tiles the text (the usual ones do)
+        lens = list(map(len, pieces))
+        if sum(lens) != len(raw):                                   # not ASCII: lengths in bytes
+            lens = list(map(len, map(str.encode, pieces)))
+        ends = np.cumsum(np.asarray(lens, dtype=np.uint64), dtype=np.uint64)
+        buf = np.empty(max(1, len(raw)), dtype=np.uint32)
+        n = self._lib.bbpe_encode(self._h, raw, ends.ctypes.data, len(ends), self._byte_id_arr.ctypes.data, buf.ctypes.data, buf.size)
+        return buf[:n].tolist()
 
     def token_bytes(self, i: int) -> bytes:
         t = self.id_to_token.get(int(i))
@@ -267,30 +282,16 @@ def train_bpe(corpus: Iterable[str], vocab_size: int, special_tokens: Sequence[s
             words[tuple(b2u[b] for b in piece.encode("utf-8"))] += 1
     vocab = {b2u[b]: b for b in range(256)}
     merges: list[tuple[str, str]] = []
+    from ._merge_learner import MergeLearner
+    learner = MergeLearner(words, make=lambda a, b, _i: a + b, tie=lambda pair: pair)       # ties: the larger pair wins
     while len(vocab) < vocab_size - len(special_tokens):
-        pairs: Counter = Counter()
-        for w, c in words.items():
-            for a, b in zip(w, w[1:]):
-                pairs[(a, b)] += c
-        if not pairs:
+        found = learner.best()
+        if found is None or found[1] < 2:
             break
-        (a, b), cnt = max(pairs.items(), key=lambda kv: (kv[1], kv[0]))
-        if cnt < 2:
-            break
+        a, b = found[0]
+        learner.merge(found[0])
         merges.append((a, b))
         vocab[a + b] = len(vocab)
-        new_words: Counter = Counter()
-        for w, c in words.items():
-            out, i = [], 0
-            while i < len(w):
-                if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
-                    out.append(a + b)
-                    i += 2
-                else:
-                    out.append(w[i])
-                    i += 1
-            new_words[tuple(out)] += c
-        words = new_words
     special = {s: len(vocab) + i for i, s in enumerate(special_tokens)}
     return BpeTokenizer(vocab, merges, special)
 

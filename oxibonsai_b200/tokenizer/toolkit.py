@@ -400,32 +400,19 @@ class BpeTrainer:
         merges: list[MergeRule] = []
         skipped = 0
         unique = len(words)
+        from ._merge_learner import MergeLearner
+        learner = MergeLearner(words, make=lambda _a, _b, i: base + 256 + i, tie=lambda pair: (-pair[0], -pair[1]))   # ties: the smallest ids win
         while base + 256 + len(merges) < cfg.vocab_size:
-            pairs: Counter = Counter()
-            for w, c in words.items():
-                for a, b in zip(w, w[1:]):
-                    pairs[(a, b)] += c
-            if not pairs:
+            found = learner.best()
+            if found is None:
                 break
-            (a, b), cnt = max(pairs.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))     # ties: the smallest ids win
+            (a, b), cnt = found
             if cnt < cfg.min_frequency:
-                skipped = sum(1 for v in pairs.values() if v < cfg.min_frequency)
+                skipped = sum(1 for v in learner.pairs.values() if v < cfg.min_frequency)
                 break
-            new_id = base + 256 + len(merges)
+            new_id = learner.merge((a, b))
             vocab[new_id] = vocab[a] + vocab[b]
             merges.append(MergeRule(a, b, new_id, cnt))
-            merged: Counter = Counter()
-            for w, c in words.items():
-                out, i = [], 0
-                while i < len(w):
-                    if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
-                        out.append(new_id)
-                        i += 2
-                    else:
-                        out.append(w[i])
-                        i += 1
-                merged[tuple(out)] += c
-            words = merged
         special = {t: i for i, t in enumerate(SPECIAL_TOKENS)} if cfg.add_special_tokens else {}
         stats = TrainingStats(base + 256, base + 256 + len(merges), len(merges), skipped, chars, unique)
         return TrainedTokenizer(vocab, merges, special, stats)

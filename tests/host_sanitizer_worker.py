@@ -52,6 +52,11 @@ def main() -> None:
     tok = train_bpe(["the quick brown fox jumps over the lazy dog " * 4, "pack my box with five dozen liquor jugs"], 300)
     ids = tok.encode("the quick dog jumps")
     assert tok.decode(ids) == "the quick dog jumps"
+    # long pieces (the heap and its linked list), empty and non-ASCII segments, bytes the vocabulary lacks
+    for text in ("thethe" * 700, "", " ", "wörd ☃ " * 90, "q" * 513 + " the " * 40):
+        assert tok.decode(tok.encode(text)) == text
+    gap = type(tok)({k: v for k, v in tok.vocab.items() if k != "q"}, [], {})
+    assert gap.decode(gap.encode("quick")) == "uick"
     from oxibonsai_b200.runtime.constrained import DfaConstraint, TokenTable
     table = TokenTable([bytes([b]) for b in range(256)] + [b"true", b"false"])
     c = DfaConstraint.from_regex(table, r"(true|false)+", eos_token=None)

@@ -155,3 +155,54 @@ def test_tokenizer_embedded_in_a_gguf_file(tmp_path):
     assert isinstance(T.load_tokenizer(None, model_path=plain), T.ByteTokenizer)
     with pytest.raises(ValueError, match="embeds no"):
         T.BpeTokenizer.from_gguf(plain)
+
+
+def _greedy_reference(ids: list[int], table: dict) -> list[int]:
+    """Lowest rank first, leftmost among equals, one merge at a time: the definition the native heap has to reproduce."""
+    ids = list(ids)
+    while len(ids) > 1:
+        best = min(((table[(a, b)][0], i) for i, (a, b) in enumerate(zip(ids, ids[1:])) if (a, b) in table), default=None)
+        if best is None:
+            break
+        i = best[1]
+        ids[i:i + 2] = [table[(ids[i], ids[i + 1])][1]]
+    return ids
+
+
+def test_native_merge_equals_the_one_merge_at_a_time_definition_on_long_pieces():
+    import random
+    rng = random.Random(7)
+    corpus = ["".join(rng.choice("abcd") for _ in range(rng.randint(1, 12))) for _ in range(400)]
+    tok = T.train_bpe([" ".join(corpus)], vocab_size=330)
+    table = {(a, b): (r, m) for r, (a, b, m) in enumerate(tok.merges)}
+    assert len(table) > 30
+    for n in (1, 2, 3, 17, 200, 3000):
+        for _ in range(5):
+            piece = "".join(rng.choice("abcd") for _ in range(n))            # no split point: one piece of n bytes
+            want = _greedy_reference([tok._byte_id[b] for b in piece.encode()], table)
+            assert tok.encode(piece) == want == tok._encode_piece(piece)
+    assert tok.encode("a" * 1001) == _greedy_reference([tok._byte_id[ord("a")]] * 1001, table)
+
+
+def test_encode_of_a_long_text_is_one_native_call_and_matches_piecewise_encoding():
+    import random
+    import time
+    rng = random.Random(3)
+    words = ["".join(rng.choice("abcdefghij") for _ in range(rng.randint(2, 8))) for _ in range(300)]
+    tok = T.train_bpe([" ".join(rng.choice(words) for _ in range(2000))], vocab_size=500, special_tokens=["<|sep|>"])
+    text = " ".join(rng.choice(words) for _ in range(40000)) + "<|sep|>" + "wörd ☃ 日本 " * 500 + "\n\n  tail"
+    t0 = time.perf_counter()
+    ids = tok.encode(text)
+    dt = time.perf_counter() - t0
+    piecewise = []
+    for seg in text.split("<|sep|>"):
+        for p in tok._split.findall(seg):
+            piecewise.extend(tok._encode_piece(p))
+        piecewise.append(tok.special["<|sep|>"])
+    assert ids == piecewise[:-1] and tok.decode(ids) == text
+    assert dt < 1.0                                                          # ~25 ms here; the per-piece path took ~0.3 s
+    # a piece without any split point, as long as a request can be: n log n, not n^2 (2 s at 200k characters before)
+    blob = "".join(rng.choice("abcdefghij") for _ in range(200000))
+    t0 = time.perf_counter()
+    out = tok.encode(blob)
+    assert time.perf_counter() - t0 < 1.0 and tok.decode(out) == blob

@@ -114,3 +114,48 @@ def test_token_stream_decoder():
     assert d.finish_lossy() == "�" and d.pending_len() == 0
     d.reset()
     assert d.total_tokens() == 0 and d.total_bytes() == 0
+
+
+def test_incremental_merge_learning_equals_a_full_recount_per_merge():
+    import random
+    from collections import Counter
+    from oxibonsai_b200.tokenizer._merge_learner import MergeLearner
+    rng = random.Random(11)
+    words = Counter()
+    for _ in range(300):
+        words[tuple(rng.choice("abc") for _ in range(rng.randint(1, 10)))] += rng.randint(1, 5)
+    words[tuple("aaaaaaa")] += 3                                           # overlapping occurrences of one pair
+
+    def naive(words, n):
+        words, out = Counter(words), []
+        for k in range(n):
+            pairs = Counter()
+            for w, c in words.items():
+                for p in zip(w, w[1:]):
+                    pairs[p] += c
+            if not pairs:
+                break
+            (a, b), cnt = max(pairs.items(), key=lambda kv: (kv[1], kv[0]))
+            new = f"<{k}>"
+            out.append(((a, b), cnt, new))
+            merged = Counter()
+            for w, c in words.items():
+                o, i = [], 0
+                while i < len(w):
+                    if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
+                        o.append(new)
+                        i += 2
+                    else:
+                        o.append(w[i])
+                        i += 1
+                merged[tuple(o)] += c
+            words = merged
+        return out
+    learner = MergeLearner(dict(words), make=lambda a, b, i: f"<{i}>", tie=lambda p: p)
+    got = list(learner.run(60, 1))
+    assert got == naive(words, 60) and len(got) == 60
+    # min_count ends the run early, and the counts that are left are those of the rewritten words
+    learner = MergeLearner(dict(words), make=lambda a, b, i: f"<{i}>", tie=lambda p: p)
+    early = list(learner.run(1000, 20))
+    assert early == [m for m in naive(words, 1000) if m[1] >= 20][:len(early)] and all(c >= 20 for _, c, _ in early)
+    assert learner.best() is None or learner.best()[1] < 20
