@@ -125,7 +125,7 @@ class BatchScheduler:
     def __init__(self, engine, queue_capacity: int = 1024, eos_token: int | None = None, idle_sleep: float = 0.0005,
                  prefill_chunk_tokens: int = 512, kv_policy=None, prefill_chunk_boost: int = 1,
                  before_launch: Callable[[], None] | None = None, on_fatal: Callable[[Exception], bool] | None = None,
-                 idle_hook: Callable[[], None] | None = None, idle_hook_seconds: float = 30.0, overlap: bool = False):
+                 idle_hook: Callable[[], None] | None = None, idle_hook_seconds: float = 30.0, overlap: bool = False, admit_tokens_per_step: int = 0):
         """``kv_policy``: a :class:`~oxibonsai_b200.runtime.kv_policy.KvCachePolicy`; when given, the scheduler feeds it the
         engine's KV utilisation after every admission and retirement, and every newly admitted sequence gets its pages in the
         format of the policy's current level (FP16 / Q8 / Q4, as far as the engine has pools for them)."""
@@ -154,6 +154,14 @@ class BatchScheduler:
         # wait behind the chunk then, and long chunks fill the GPU better (1 = always the same chunk length).
         self.prefill_chunk_boost = max(1, int(prefill_chunk_boost))
         self._pending: dict | None = None      # the request being prefilled: {"r", "slot", "done"} (slot >= len(live))
+        # One decode step admits one prompt chunk by default, so a workload of short generations never fills the batch
+        # (requests that live n steps keep ~n slots busy).  With ``admit_tokens_per_step`` > 0 further queued prompts are
+        # admitted before the step while their cost stays within that many prompt tokens, a prompt counting for at least
+        # ``admit_floor_tokens`` (the fixed cost of a prefill pass: one read of the weights and its launches).
+        self.admit_tokens_per_step = max(0, int(admit_tokens_per_step))
+        self.admit_floor_tokens = 128
+        self._admit_cost = 0                   # prompt tokens the last _admit() call put through the engine
+        self.admissions = 0
         self.prefill_chunks = 0
         self.eos = EOS_TOKEN if eos_token is None else eos_token
         self.queue = BoundedPriorityQueue(queue_capacity)
@@ -206,6 +214,11 @@ class BatchScheduler:
                 if self.before_launch is not None and (self.live or self._pending is not None or len(self.queue)):
                     self.before_launch()
                 admitted = self._admit()
+                if admitted and self.admit_tokens_per_step and not self.overlap:
+                    spent = max(self._admit_cost, self.admit_floor_tokens)
+                    while (spent < self.admit_tokens_per_step and self._pending is None and len(self.live) < eng.max_batch
+                           and len(self.queue) and self._admit()):
+                        spent += max(self._admit_cost, self.admit_floor_tokens)
                 if not self.live:
                     if not admitted:
                         if self.idle_hook is not None and time.monotonic() - last_idle >= self.idle_hook_seconds:
@@ -299,6 +312,7 @@ class BatchScheduler:
     def _admit(self) -> bool:
         """Makes progress on admission: at most one prompt chunk per call.  Returns True when something was done."""
         eng = self.engine
+        self._admit_cost = 0
         if self._pending is None:
             if len(self.live) >= eng.max_batch:
                 return False
@@ -342,6 +356,7 @@ class BatchScheduler:
             end = n if n - p["done"] <= chunk + eng.prefill_min_tokens else p["done"] + chunk
             eng.prefill(r.prompt[p["done"]:end], slot, p["done"])
             self.prefill_chunks += 1
+            self._admit_cost = end - p["done"]
             p["done"] = end
             if end < n:
                 return True
@@ -369,6 +384,7 @@ class BatchScheduler:
         if slot != dst:                          # sequences retired while this one was prefilling: close the gap
             eng.move_slot(slot, dst)
         self.prompt_tokens += len(r.prompt)
+        self.admissions += 1
         self.live.append(r)
         self._pos.append(len(r.prompt))
         if self._emit(dst, first):

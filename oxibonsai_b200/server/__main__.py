@@ -83,7 +83,8 @@ def main(argv: list[str] | None = None) -> int:
                 if policy is not None:
                     e.enable_kv_formats(("f16", "q8", "q4"))      # the levels of the policy that the engine does not have yet
             scheds.append(BatchScheduler(e, eos_token=getattr(tokenizer, "eos_token_id", None), queue_capacity=cfg.queue_capacity, prefill_chunk_tokens=cfg.prefill_chunk_tokens, prefill_chunk_boost=cfg.prefill_chunk_boost,
-                                         kv_policy=policy, idle_hook=getattr(leader, "keepalive", None), overlap=cfg.overlap_steps).start())
+                                         kv_policy=policy, idle_hook=getattr(leader, "keepalive", None), overlap=cfg.overlap_steps,
+                                         admit_tokens_per_step=cfg.admit_tokens_per_step).start())
         backend = SchedulerBackend(scheds[0], engine.config.name) if len(scheds) == 1 else ReplicaBackend(scheds, engine.config.name)
     else:                                         # an engine without sequence slots: one request at a time
         backend = SerialBackend(engine, engine.config.name)
@@ -142,7 +143,7 @@ def _serve_elastic(cfg, tokenizer, builder, uid: int, world: int, local: int) ->
             le.enable_prefix_cache()
         return BatchScheduler(le, eos_token=getattr(tokenizer, "eos_token_id", None), queue_capacity=cfg.queue_capacity,
                               prefill_chunk_tokens=cfg.prefill_chunk_tokens, prefill_chunk_boost=cfg.prefill_chunk_boost, before_launch=g.check,
-                              on_fatal=lambda e: fatal(e), idle_hook=le.keepalive)
+                              on_fatal=lambda e: fatal(e), idle_hook=le.keepalive, admit_tokens_per_step=cfg.admit_tokens_per_step)
 
     def lead(le, g):
         inner = lead_with_scheduler(make_scheduler, backend, stop)

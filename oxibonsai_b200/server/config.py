@@ -43,6 +43,8 @@ class ServerConfig:
     replicas: int = 1                 # > 1: one engine + scheduler per GPU (cuda:0 .. cuda:N-1) in this process, requests routed between them
     prefill_chunk_tokens: int = 512   # prompt tokens prefilled between two decode steps of the running streams
     prefill_chunk_boost: int = 4      # chunks this many times as long while fewer than a quarter of the slots decode
+    admit_tokens_per_step: int = 512  # queued prompts admitted before one decode step while they cost no more than this many prompt tokens (a prompt
+                                      # counts for at least 128); 0: one prompt chunk per step.  Fills the batch on short generations.
     kv_policy: str = "off"            # off | adaptive | aggressive: admit new sequences with Q8 / Q4 KV pages under memory pressure
     queue_capacity: int = 1024
     chat_template: str = "auto"       # chatml | qwen | llama3 | mistral | gemma, or auto: inferred from the model's name, ChatML otherwise
@@ -67,6 +69,8 @@ class ServerConfig:
             errs.append("tensor_parallel and replicas must be positive")
         if self.tensor_parallel > 1 and self.replicas > 1:
             errs.append("tensor_parallel and replicas cannot be combined in one server")
+        if self.admit_tokens_per_step < 0 or self.prefill_chunk_tokens < 1 or self.prefill_chunk_boost < 1 or self.queue_capacity < 1:
+            errs.append("prefill_chunk_tokens, prefill_chunk_boost and queue_capacity must be >= 1, admit_tokens_per_step >= 0")
         if self.kv_policy not in ("off", "adaptive", "aggressive"):
             errs.append("kv_policy must be one of off, adaptive, aggressive")
         if self.chat_template not in ("auto", "chatml", "qwen", "llama3", "mistral", "gemma"):
@@ -90,7 +94,7 @@ _TOML_MAP = {
     ("sampling", "repetition_penalty"): "repetition_penalty", ("sampling", "max_tokens"): "max_tokens", ("sampling", "seed"): "seed",
     ("model", "model_path"): "model_path", ("model", "tokenizer_path"): "tokenizer_path", ("model", "max_seq_len"): "max_seq_len",
     ("model", "kv_cache"): "kv_cache", ("model", "tensor_parallel"): "tensor_parallel", ("model", "replicas"): "replicas", ("model", "tp_elastic"): "tp_elastic", ("model", "tp_heartbeat_timeout"): "tp_heartbeat_timeout", ("model", "kv_policy"): "kv_policy",
-    ("server", "native_front"): "native_front", ("model", "chat_template"): "chat_template", ("server", "overlap_steps"): "overlap_steps", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost",
+    ("server", "native_front"): "native_front", ("model", "chat_template"): "chat_template", ("server", "overlap_steps"): "overlap_steps", ("server", "prefill_chunk_tokens"): "prefill_chunk_tokens", ("server", "prefill_chunk_boost"): "prefill_chunk_boost", ("server", "admit_tokens_per_step"): "admit_tokens_per_step",
     ("observability", "log_level"): "log_level", ("observability", "json_logs"): "json_logs",
     ("observability", "metrics_enabled"): "metrics_enabled", ("observability", "metrics_path"): "metrics_path",
 }

@@ -388,3 +388,46 @@ def test_overlap_is_off_for_constrained_requests_and_unsupported_engines():
     first_launch = next(i for i, e in enumerate(eng.log) if e[0] == "launch")
     steps_before = [e for e in eng.log[:first_launch] if e[0] == "step"]
     assert steps_before                                                         # while the constrained request lived, plain steps were taken
+
+
+def test_budgeted_admission_fills_the_batch_on_short_generations():
+    """One admission per decode step keeps about as many slots busy as a request lives steps; with a token budget several
+    queued prompts join before each step, within the budget, and a long prompt still goes in one chunk per step."""
+    class Wide(FakeEngine):
+        max_batch = 16
+
+    def run(budget):
+        eng = Wide()
+        sched = BatchScheduler(eng, eos_token=-1, queue_capacity=256, prefill_chunk_tokens=64, admit_tokens_per_step=budget)
+        sched.admit_floor_tokens = 16
+        prompts = [[i + 1] * 10 for i in range(100)]
+        reqs = [sched.submit(p, SamplingParams(), 6) for p in prompts]
+        long = sched.submit([3] * 300, SamplingParams(), 6)               # 300 tokens: chunks of 64, one per step
+        sched.start()
+        try:
+            for r, p in zip(reqs, prompts):
+                assert r.wait(timeout=30) == _expected(p, 6)
+            assert long.wait(timeout=30) == _expected([3] * 300, 6)
+        finally:
+            sched.stop()
+        assert sched.active == 0 and sched.admissions == 101 and not eng.slots
+        sizes = [e[1] for e in eng.log if e[0] == "step"]
+        # admissions between two decode steps
+        between, run_ = [], 0
+        for e in eng.log:
+            if e[0] == "finish":
+                run_ += 1
+            elif e[0] == "step":
+                between.append(run_)
+                run_ = 0
+        return sizes, between, eng.log
+
+    sizes1, between1, _ = run(0)
+    assert max(between1) == 1 and max(sizes1) <= 6                        # a request lives 5 steps after its admission
+    sizes4, between4, log = run(64)                                       # 64 tokens at a floor of 16: up to four prompts per step
+    assert max(between4) == 4 and max(sizes4) == 16 and len(sizes4) < 0.5 * len(sizes1)
+    # the long prompt never shared a step's budget with another admission once it was pending, and took one chunk per step
+    chunks = [i for i, e in enumerate(log) if e[0] == "prefill" and e[3] == 64]
+    assert len(chunks) >= 3
+    for a, b in zip(chunks, chunks[1:]):
+        assert any(e[0] == "step" for e in log[a:b])
