@@ -10,6 +10,7 @@ recomputed because its logits are needed.
 """
 from __future__ import annotations
 
+import heapq
 from dataclasses import dataclass, field
 from typing import Callable, Sequence
 
@@ -51,6 +52,11 @@ class PrefixCache:
         self.size = 0
         self.generation = 0
         self.stats = PrefixCacheStats()
+        # Eviction candidates: (last_used, serial, node) for every node that was a leaf when it was last touched.  Entries are
+        # not removed when a node gains a child, is used again or is evicted; one that no longer describes its node is
+        # skipped when it comes up, so that an eviction costs O(log n) instead of a walk over the trie.
+        self._heap: list[tuple[int, int, _Node]] = []
+        self._serial = 0
 
     def _blocks(self, tokens: Sequence[int]):
         ps = self.page_size
@@ -74,6 +80,7 @@ class PrefixCache:
             pages.append(nxt.page)
             node = nxt
         if pages:
+            self._candidate(node)
             self.stats.hits += 1
             self.stats.tokens_reused += len(pages) * self.page_size
         return pages
@@ -97,8 +104,19 @@ class PrefixCache:
                 added += 1
             nxt.last_used = self.generation
             node = nxt
+        self._candidate(node)
         self.stats.inserted_pages += added
         return added
+
+    def _candidate(self, node: _Node) -> None:
+        if node is self.root or node.children:
+            return
+        self._serial += 1
+        heapq.heappush(self._heap, (node.last_used, self._serial, node))
+        if len(self._heap) > 4 * self.size + 1024:                 # mostly entries of nodes that were used again: start over
+            self._heap = [(n.last_used, i, n) for i, n in enumerate(self._leaves())]
+            self._serial = len(self._heap)
+            heapq.heapify(self._heap)
 
     def _leaves(self):
         stack = [self.root]
@@ -109,18 +127,29 @@ class PrefixCache:
             stack.extend(n.children.values())
 
     def _evict_one(self, protect: _Node | None = None) -> bool:
-        victim = None
-        for leaf in self._leaves():
-            if leaf is protect:
+        """Drops the least recently used leaf other than ``protect``."""
+        victim, held = None, None
+        while self._heap:
+            entry = heapq.heappop(self._heap)
+            used, _, n = entry
+            if n.children or used != n.last_used or n.parent is None or n.parent.children.get(n.key) is not n:
+                continue                                           # gained a child, was used again, or is gone
+            if n is protect:
+                held = entry
                 continue
-            if victim is None or leaf.last_used < victim.last_used:
-                victim = leaf
+            victim = n
+            break
+        if held is not None:
+            heapq.heappush(self._heap, held)
         if victim is None:
             return False
-        del victim.parent.children[victim.key]
+        parent = victim.parent
+        del parent.children[victim.key]
+        victim.parent = None
         self._release([victim.page])
         self.size -= 1
         self.stats.evicted_pages += 1
+        self._candidate(parent)                                    # its last child went: it is a leaf now
         return True
 
     def evict(self, n_pages: int) -> int:
