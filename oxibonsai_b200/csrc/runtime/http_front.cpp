@@ -14,6 +14,7 @@
 #include <arpa/inet.h>
 #include <errno.h>
 #include <fcntl.h>
+#include <netdb.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <sys/epoll.h>
@@ -602,6 +603,25 @@ static Conn* find_conn(Front* f, int64_t id) {
     return it == f->conns.end() ? nullptr : it->second.get();      // stable: only the I/O thread erases connections
 }
 
+// "address:port" of a client; an IPv4 client of a dual-stack socket is named by its IPv4 address.
+std::string peer_name(const sockaddr_storage& ss) {
+    char ip[INET6_ADDRSTRLEN] = "";
+    int port = 0;
+    if (ss.ss_family == AF_INET6) {
+        const auto* a = reinterpret_cast<const sockaddr_in6*>(&ss);
+        port = ntohs(a->sin6_port);
+        if (IN6_IS_ADDR_V4MAPPED(&a->sin6_addr))
+            inet_ntop(AF_INET, a->sin6_addr.s6_addr + 12, ip, sizeof ip);
+        else
+            inet_ntop(AF_INET6, &a->sin6_addr, ip, sizeof ip);
+    } else {
+        const auto* a = reinterpret_cast<const sockaddr_in*>(&ss);
+        port = ntohs(a->sin_port);
+        inet_ntop(AF_INET, &a->sin_addr, ip, sizeof ip);
+    }
+    return std::string(ip) + ":" + std::to_string(port);
+}
+
 static void io_loop(Front* f) {
     std::vector<epoll_event> evs(256);
     std::vector<char> buf(1 << 16);
@@ -613,7 +633,7 @@ static void io_loop(Front* f) {
             uint64_t tag = evs[i].data.u64;
             if (tag == 0) {                                                       // the listening socket
                 while (true) {
-                    sockaddr_in addr{};
+                    sockaddr_storage addr{};
                     socklen_t al = sizeof addr;
                     int fd = accept4(f->listen_fd, reinterpret_cast<sockaddr*>(&addr), &al, SOCK_NONBLOCK | SOCK_CLOEXEC);
                     if (fd < 0) break;
@@ -621,9 +641,7 @@ static void io_loop(Front* f) {
                     setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
                     auto c = std::make_unique<Conn>();
                     c->fd = fd;
-                    char ip[64] = "";
-                    inet_ntop(AF_INET, &addr.sin_addr, ip, sizeof ip);
-                    c->peer = std::string(ip) + ":" + std::to_string(ntohs(addr.sin_port));
+                    c->peer = peer_name(addr);
                     std::lock_guard<std::mutex> lk(f->mu);
                     c->id = f->next_id++;
                     epoll_event ev{};
@@ -733,28 +751,36 @@ extern "C" {
 void* bfront_create(const char* host, int port, int backlog) {
     auto f = std::make_unique<Front>();
     f->host = host ? host : "127.0.0.1";
-    f->listen_fd = socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+    // A literal address of either family or a name; a name's IPv4 addresses are tried first (clients of "localhost" mostly
+    // dial 127.0.0.1), and "::" listens on both families.
+    addrinfo hints{};
+    hints.ai_family = AF_UNSPEC;
+    hints.ai_socktype = SOCK_STREAM;
+    hints.ai_flags = AI_PASSIVE | AI_NUMERICSERV;
+    addrinfo* res = nullptr;
+    const std::string service = std::to_string(port);
+    if (getaddrinfo(f->host.empty() ? nullptr : f->host.c_str(), service.c_str(), &hints, &res) != 0 || res == nullptr) return nullptr;
+    f->listen_fd = -1;
+    for (int family : {AF_INET, AF_INET6}) {
+        for (addrinfo* ai = res; ai != nullptr && f->listen_fd < 0; ai = ai->ai_next) {
+            if (ai->ai_family != family) continue;
+            int fd = socket(ai->ai_family, SOCK_STREAM | SOCK_CLOEXEC, 0);
+            if (fd < 0) continue;
+            int one = 1, zero = 0;
+            setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
+            if (family == AF_INET6) setsockopt(fd, IPPROTO_IPV6, IPV6_V6ONLY, f->host == "::" ? &zero : &one, sizeof one);
+            if (bind(fd, ai->ai_addr, ai->ai_addrlen) == 0 && listen(fd, backlog > 0 ? backlog : 1024) == 0)
+                f->listen_fd = fd;
+            else
+                close(fd);
+        }
+    }
+    freeaddrinfo(res);
     if (f->listen_fd < 0) return nullptr;
-    int one = 1;
-    setsockopt(f->listen_fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
-    sockaddr_in addr{};
-    addr.sin_family = AF_INET;
-    addr.sin_port = htons(uint16_t(port));
-    if (f->host == "0.0.0.0" || f->host.empty()) {
-        addr.sin_addr.s_addr = htonl(INADDR_ANY);
-    } else if (f->host == "localhost") {
-        addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
-    } else if (inet_pton(AF_INET, f->host.c_str(), &addr.sin_addr) != 1) {
-        close(f->listen_fd);
-        return nullptr;
-    }
-    if (bind(f->listen_fd, reinterpret_cast<sockaddr*>(&addr), sizeof addr) != 0 || listen(f->listen_fd, backlog > 0 ? backlog : 1024) != 0) {
-        close(f->listen_fd);
-        return nullptr;
-    }
-    socklen_t al = sizeof addr;
-    getsockname(f->listen_fd, reinterpret_cast<sockaddr*>(&addr), &al);
-    f->port = ntohs(addr.sin_port);
+    sockaddr_storage bound{};
+    socklen_t al = sizeof bound;
+    getsockname(f->listen_fd, reinterpret_cast<sockaddr*>(&bound), &al);
+    f->port = ntohs(bound.ss_family == AF_INET6 ? reinterpret_cast<sockaddr_in6*>(&bound)->sin6_port : reinterpret_cast<sockaddr_in*>(&bound)->sin_port);
     set_nonblock(f->listen_fd);
     f->ep = epoll_create1(EPOLL_CLOEXEC);
     f->wake = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);

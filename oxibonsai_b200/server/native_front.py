@@ -267,7 +267,9 @@ class AsgiBridge:
                 try:
                     await self.app({"type": "lifespan", "asgi": {"version": "3.0", "spec_version": "2.0"}, "state": state}, q_in.get, q_out.put)
                 except Exception:  # noqa: BLE001 - an application without lifespan support
-                    await q_out.put({"type": "lifespan.startup.failed.unsupported"})
+                    pass
+                # raised, or returned without taking part in the protocol: whoever still waits for an answer gets this one
+                await q_out.put({"type": "lifespan.startup.failed.unsupported"})
             self._life = (asyncio.ensure_future(run()), q_in, q_out)
             await q_in.put({"type": "lifespan.startup"})
             msg = await q_out.get()

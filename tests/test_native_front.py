@@ -525,3 +525,43 @@ def test_http10_clients_get_unframed_streams_that_end_with_the_connection(front)
     while chunk := s.recv(65536):
         data += chunk
     assert data.startswith(b"HTTP/1.1 200 OK") and b"content-length" in data and b'"target": "/plain"' in data
+
+
+def test_listen_address_may_be_a_name_or_an_ipv6_address():
+    """"::" listens on both families and names the client by its own family's address; a name resolves; a bad one is refused."""
+    import asyncio
+
+    async def app(scope, receive, send):
+        if scope["type"] != "http":
+            return
+        body = json.dumps({"client": scope["client"][0]}).encode()
+        await send({"type": "http.response.start", "status": 200, "headers": [(b"content-type", b"application/json"), (b"content-length", str(len(body)).encode())]})
+        await send({"type": "http.response.body", "body": body})
+
+    try:
+        front = NativeFront("::", 0)
+    except OSError:
+        pytest.skip("no IPv6 on this host")
+    front.start()
+    stop = threading.Event()
+    t = threading.Thread(target=lambda: asyncio.run(AsgiBridge(app, front).serve(stop)), daemon=True)
+    t.start()
+    try:
+        seen = {}
+        for host in ("127.0.0.1", "::1"):
+            c = http.client.HTTPConnection(host, front.port, timeout=10)
+            c.request("GET", "/whoami")
+            r = c.getresponse()
+            assert r.status == 200
+            seen[host] = json.loads(r.read())["client"]
+            c.close()
+        assert seen == {"127.0.0.1": "127.0.0.1", "::1": "::1"}
+    finally:
+        stop.set()
+        t.join(5)
+        front.close()
+    named = NativeFront("localhost", 0)
+    assert named.port > 0
+    named.close()
+    with pytest.raises(OSError):
+        NativeFront("no.such.host.invalid", 0)
