@@ -161,6 +161,7 @@ class BatchScheduler:
         self.admit_tokens_per_step = max(0, int(admit_tokens_per_step))
         self.admit_floor_tokens = 128
         self._admit_cost = 0                   # prompt tokens the last _admit() call put through the engine
+        self._deferred: Request | None = None  # popped from the queue, waiting for KV pages
         self.admissions = 0
         self.prefill_chunks = 0
         self.eos = EOS_TOKEN if eos_token is None else eos_token
@@ -211,7 +212,7 @@ class BatchScheduler:
         last_idle = time.monotonic()
         while not self._stop.is_set():
             try:
-                if self.before_launch is not None and (self.live or self._pending is not None or len(self.queue)):
+                if self.before_launch is not None and (self.live or self._pending is not None or self._deferred is not None or len(self.queue)):
                     self.before_launch()
                 admitted = self._admit()
                 if admitted and self.admit_tokens_per_step and not self.overlap:
@@ -250,6 +251,10 @@ class BatchScheduler:
                 if fatal:                          # the engine is about to be torn down: its slots go with it
                     with self.lock:
                         self.fatal = e             # from here on submit() refuses, so the queue emptied below stays empty
+                    if self._deferred is not None:
+                        self._deferred.error = e
+                        self._deferred.finish()
+                        self._deferred = None
                     while (r := self.queue.get_nowait()) is not None:
                         r.error = e
                         r.finish()
@@ -316,15 +321,17 @@ class BatchScheduler:
         if self._pending is None:
             if len(self.live) >= eng.max_batch:
                 return False
-            r = None
-            while r is None:
-                r = self.queue.get_nowait()
+            r, self._deferred = self._deferred, None
+            while True:
                 if r is None:
-                    return False
-                if r.cancelled:
-                    r.finish_reason = "cancelled"
-                    r.finish()
-                    r = None
+                    r = self.queue.get_nowait()
+                    if r is None:
+                        return False
+                if not r.cancelled:
+                    break
+                r.finish_reason = "cancelled"
+                r.finish()
+                r = None
             slot = len(self.live)
             total = min(eng.max_seq_len, len(r.prompt) + r.max_tokens)
             try:
@@ -334,10 +341,16 @@ class BatchScheduler:
                     self.kv_policy.observe(eng.kv_utilization())
                 else:
                     covered = eng.begin_sequence(r.prompt, total, slot, r.params)
-            except MemoryError:
-                # KV pool exhausted: put the request back and wait for a sequence to finish
+            except MemoryError as e:
                 eng.close_sequence(slot)
-                self.queue.put(r)
+                if not self.live:
+                    # nothing left to retire: the pool cannot hold this request at all
+                    r.error = e
+                    r.finish()
+                    return True
+                # KV pool exhausted: the request keeps its place at the head and is tried again once a sequence has finished
+                # (outside the queue, whose capacity a concurrent submit may have used up meanwhile)
+                self._deferred = r
                 return False
             except Exception as e:
                 eng.close_sequence(slot)

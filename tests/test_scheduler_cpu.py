@@ -431,3 +431,44 @@ def test_budgeted_admission_fills_the_batch_on_short_generations():
     assert len(chunks) >= 3
     for a, b in zip(chunks, chunks[1:]):
         assert any(e[0] == "step" for e in log[a:b])
+
+
+def test_a_request_without_kv_pages_keeps_its_place_and_does_not_need_queue_room():
+    """When the pool cannot take the next request it waits at the head, outside the queue: a submit that fills the queue
+    meanwhile cannot make the wait fail, later requests do not overtake it, and a request that no retirement can ever make room
+    for fails by itself."""
+    class Tight(FakeEngine):
+        max_batch = 4
+
+        def begin_sequence(self, prompt, max_total, slot, params):
+            if len(prompt) > 50:
+                raise MemoryError("KV cache exhausted: the prompt alone needs more pages than the pool has")
+            if len(self.slots) >= 2:                                     # pages for two sequences
+                raise MemoryError("KV cache exhausted")
+            return super().begin_sequence(prompt, max_total, slot, params)
+
+    eng = Tight(step_delay=0.002)
+    sched = BatchScheduler(eng, eos_token=-1, queue_capacity=2)
+    order = []
+    mk = lambda i, n: sched.submit([i + 1] * 5, SamplingParams(), n, on_done=lambda r, i=i: order.append(i))
+    a, b = mk(0, 30), mk(1, 30)
+    sched.start()
+    try:
+        while sched.active < 2:
+            time.sleep(0.001)
+        c = mk(2, 4)                                                     # popped, finds no pages, waits at the head
+        while len(sched.queue):
+            time.sleep(0.001)
+        d, e = mk(3, 4), mk(4, 4)                                        # the queue is full again while c waits
+        for r in (a, b, c, d, e):
+            r.wait(timeout=30)
+        assert all(r.error is None for r in (a, b, c, d, e))
+        assert [len(r.tokens) for r in (a, b, c, d, e)] == [30, 30, 4, 4, 4]
+        assert order.index(2) < order.index(3) < order.index(4)
+        big = sched.submit([7] * 60, SamplingParams(), 4)
+        big.done.wait(30)
+        assert isinstance(big.error, MemoryError)
+        assert mk(5, 3).wait(timeout=30) == _expected([6] * 5, 3)        # and the scheduler carries on
+    finally:
+        sched.stop()
+    assert sched.active == 0 and not eng.slots
