@@ -157,14 +157,8 @@ class RougeNScore:
 
 
 def lcs_length(a: Sequence, b: Sequence) -> int:
-    row = [0] * (len(b) + 1)
-    for x in a:
-        prev = 0
-        for j, y in enumerate(b, 1):
-            cur = row[j]
-            row[j] = prev + 1 if x == y else max(row[j], row[j - 1])
-            prev = cur
-    return row[-1]
+    from . import _lcs
+    return _lcs(a, b)
 
 
 @dataclass

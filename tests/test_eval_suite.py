@@ -195,3 +195,25 @@ def test_throughput_perplexity_and_report():
     assert doc["model"] == "bonsai" and [r["task"] for r in doc["results"]] == ["wikitext", "decode", "mmlu"] and doc["results"][2]["value"] == 0.75
     assert "| mmlu | accuracy | 0.7500 |" in rep.to_markdown() and "wikitext perplexity 12.5" in rep.summary()
     assert B.EvalSuiteReport("x").summary() == "x: no results"
+
+
+def test_bit_parallel_lcs_equals_the_dynamic_programme():
+    import random
+    from oxibonsai_b200.eval import _lcs
+    from oxibonsai_b200.eval.suite import lcs_length
+
+    def table(a, b):
+        row = [0] * (len(b) + 1)
+        for x in a:
+            prev = 0
+            for j, y in enumerate(b, 1):
+                cur = row[j]
+                row[j] = prev + 1 if x == y else max(row[j], row[j - 1])
+                prev = cur
+        return row[-1]
+    rng = random.Random(2)
+    for _ in range(200):
+        a = [rng.choice("abcde") for _ in range(rng.randrange(0, 70))]
+        b = [rng.choice("abcdef") for _ in range(rng.randrange(0, 130))]          # past one machine word
+        assert _lcs(a, b) == table(a, b) == lcs_length(a, b)
+    assert _lcs([], ["a"]) == 0 and _lcs(["a"], ["a"]) == 1 and _lcs("abc", "xyz") == 0
