@@ -458,7 +458,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             sem.release()
             stream.abandon()
             handle.stream = None
-            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ in ("QueueFull", "Unavailable", "SchedulerStopped") else 500
+            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ in ("QueueFull", "Unavailable", "SchedulerStopped", "MemoryError") else 500
             return error(status, str(e), "server_error", rid)
         metrics.prompt_tokens.inc(len(prompt_ids))
         from .native_front import NATIVE_STREAM_HEADER
@@ -621,7 +621,7 @@ def create_app(backend: Backend, tokenizer, config: ServerConfig | None = None, 
             return error(504, str(e), "timeout", rid)
         except Exception as e:  # noqa: BLE001
             metrics.errors.inc()
-            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ in ("QueueFull", "Unavailable", "SchedulerStopped") else 500
+            status = 503 if isinstance(e, CircuitOpenError) or type(e).__name__ in ("QueueFull", "Unavailable", "SchedulerStopped", "MemoryError") else 500
             return error(status, str(e), "server_error", rid)
         finally:
             metrics.active_requests.dec()
