@@ -167,6 +167,11 @@ class TokenBucket:
                 return True
             return False
 
+    def give_back(self, n: float = 1.0) -> None:
+        """Returns tokens taken for work that was then refused elsewhere."""
+        with self._lock:
+            self._tokens = min(self.burst, self._tokens + n)
+
 
 class RateLimiter:
     """Global bucket plus one bucket per client id (LRU-bounded)."""
@@ -191,7 +196,10 @@ class RateLimiter:
                     self._clients.popitem(last=False)
             else:
                 self._clients.move_to_end(client)
-        ok = b.try_acquire() and self._global.try_acquire()
+        ok = b.try_acquire()
+        if ok and not self._global.try_acquire():
+            b.give_back()                      # refused for everybody: the client's own allowance is not spent on it
+            ok = False
         if not ok:
             self.rejected += 1
         return ok

@@ -447,3 +447,21 @@ def test_echo_returns_the_prompt_in_front_of_the_completion(client):
     assert events[0]["choices"][0]["text"] == "Say: " and "".join(e["choices"][0]["text"] for e in events) == r["choices"][0]["text"]
     chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 3, "echo": True}).json()
     assert not chat["choices"][0]["message"]["content"].startswith("<|im_start|>")          # echo is a completions field only
+
+
+def test_rate_limiter_buckets_and_refund():
+    from oxibonsai_b200.runtime.resilience import RateLimiter, TokenBucket
+    now = [0.0]
+    clock = lambda: now[0]
+    b = TokenBucket(rate=2.0, burst=3.0, clock=clock)
+    assert [b.try_acquire() for _ in range(4)] == [True, True, True, False]
+    now[0] += 1.0                                                       # two tokens back
+    assert b.try_acquire() and b.try_acquire() and not b.try_acquire()
+    # the global bucket refuses: the client's allowance is untouched, so it can use all of it once the global one refills
+    rl = RateLimiter(global_rate=1.0, global_burst=2.0, client_rate=1.0, client_burst=4.0, max_clients=2, clock=clock)
+    assert rl.allow("a") and rl.allow("a") and not rl.allow("a") and not rl.allow("a") and rl.rejected == 2
+    now[0] += 2.0                                                       # global: two tokens again; "a" took only two of its four so far
+    assert rl.allow("a") and rl.allow("a") and not rl.allow("b")
+    # the table of clients is bounded: the least recently seen one goes
+    rl.allow("c")
+    assert list(rl._clients) == ["b", "c"]
